@@ -1,0 +1,165 @@
+"""CPU tests of the oracle: the reference's own known-answer vectors, then identities that pin the parts
+the reference never tested (backward, bias, dense, 8-product vs 16-product)."""
+import json
+import os
+
+import numpy as np
+import pytest
+
+from helpers import (QUAT_BLOCK, conv_bwd_f64, conv_fwd_f64, dense_bwd_f64, dense_fwd_f64, integers, normal,
+                     rel_err, uniform)
+
+GOLDEN = os.path.join(os.path.dirname(__file__), "golden", "reference_kats.json")
+ALG = {"complex": 1, "quaternion": 2}
+
+
+def _cases(op):
+    with open(GOLDEN) as f:
+        return [c for c in json.load(f)["cases"] if c["op"] == op]
+
+
+def _tensor(case, key):
+    shape = case[key + "_shape"]
+    if key + "_fill" in case:
+        return np.full(shape, case[key + "_fill"], np.float32)
+    return np.asarray(case[key], np.float32).reshape(shape)
+
+
+@pytest.mark.parametrize("case", _cases("conv2d_fwd"), ids=lambda c: c["name"])
+@pytest.mark.parametrize("variant", [0, 1])
+def test_reference_conv_kats(oracle, case, variant):
+    if variant == 1 and (case["algebra"] != "quaternion" or case["real_input"]):
+        pytest.skip("8-product form exists for full quaternion inputs only")
+    x, w, y = _tensor(case, "x"), _tensor(case, "w"), _tensor(case, "y")
+    got = oracle.conv2d_fwd(x, w, None, tuple(case["stride"]), tuple(case["dilation"]), (0, 0, 0, 0),
+                            ALG[case["algebra"]], variant, case["real_input"])
+    assert got.shape == tuple(case["y_shape"])
+    assert np.array_equal(got, y)       # the reference compares with threshold 0
+
+
+@pytest.mark.parametrize("case", _cases("dense_fwd"), ids=lambda c: c["name"])
+def test_reference_dense_kats(oracle, case):
+    x, w, y = _tensor(case, "x"), _tensor(case, "w"), _tensor(case, "y")
+    got = oracle.dense_fwd(x, w, None, False, ALG[case["algebra"]], 0)
+    assert np.array_equal(got, y)
+
+
+def test_reference_same_padding_shape(oracle):
+    (case,) = _cases("output_shape")
+    # NHWC input, OHWI filter: H = W = 224, kh = kw = 3
+    h = case["x_shape"][1]
+    k = case["w_shape"][2]
+    out, before, after = oracle.same_or_valid_padding(h, k, case["dilation"][0], case["stride"][0], oracle.SAME)
+    assert out == case["y_shape"][1]
+    assert oracle.output_size(h, k, case["dilation"][0], case["stride"][0], before, after) == out
+
+
+def test_sign_table_is_the_4x4_block(oracle):
+    table = oracle.quaternion_sign_table()
+    assert len(table) == 16
+    for idx, (l, r, s) in enumerate(table):
+        d = idx // 4
+        assert QUAT_BLOCK[l][d] == (r, s)
+
+
+def test_tf_padding_rules(oracle):
+    # SAME: out = ceil(in / stride), extra pixel goes after
+    assert oracle.same_or_valid_padding(7, 3, 1, 2, oracle.SAME) == (4, 1, 1)
+    assert oracle.same_or_valid_padding(8, 3, 1, 2, oracle.SAME) == (4, 0, 1)
+    assert oracle.same_or_valid_padding(224, 7, 1, 2, oracle.SAME) == (112, 2, 3)
+    assert oracle.same_or_valid_padding(5, 3, 1, 1, oracle.VALID) == (3, 0, 0)
+    assert oracle.same_or_valid_padding(5, 3, 2, 1, oracle.VALID) == (1, 0, 0)
+
+
+CONV_SHAPES = [
+    # n, ci, co, h, w, kh, kw, stride, pad(t,l,b,r)
+    (2, 3, 5, 7, 6, 3, 3, (1, 1), (1, 1, 1, 1)),
+    (1, 4, 2, 9, 8, 3, 3, (2, 2), (0, 0, 1, 1)),      # asymmetric SAME-style padding
+    (3, 2, 3, 5, 5, 1, 1, (1, 1), (0, 0, 0, 0)),
+    (2, 2, 4, 8, 7, 1, 1, (2, 2), (0, 0, 0, 0)),
+    (1, 3, 2, 10, 9, 5, 3, (2, 1), (2, 1, 2, 1)),
+]
+
+
+@pytest.mark.parametrize("shape", CONV_SHAPES)
+@pytest.mark.parametrize("variant", [0, 1])
+@pytest.mark.parametrize("use_bias", [False, True])
+def test_conv_fwd_matches_float64_block_form(oracle, shape, variant, use_bias):
+    n, ci, co, h, w_, kh, kw, stride, pad = shape
+    x = uniform(1, (4 * n, ci, h, w_))
+    w = uniform(2, (4, co, ci, kh, kw))
+    b = uniform(3, (4, co)) if use_bias else None
+    got = oracle.conv2d_fwd(x, w, b, stride, (1, 1), pad, oracle.QUATERNION, variant)
+    ref = conv_fwd_f64(x, w, b, stride, pad)
+    assert got.shape == ref.shape
+    assert rel_err(got, ref) < 2e-6
+
+
+@pytest.mark.parametrize("shape", CONV_SHAPES)
+@pytest.mark.parametrize("variant", [0, 1])
+def test_conv_bwd_matches_float64_autograd(oracle, shape, variant):
+    n, ci, co, h, w_, kh, kw, stride, pad = shape
+    x = uniform(4, (4 * n, ci, h, w_))
+    w = uniform(5, (4, co, ci, kh, kw))
+    y = oracle.conv2d_fwd(x, w, None, stride, (1, 1), pad)
+    dy = normal(6, y.shape)
+    dw, dx = oracle.conv2d_bwd(x, w, dy, stride, (1, 1), pad, oracle.QUATERNION, variant, True)
+    rdw, rdx = conv_bwd_f64(x, w, dy, stride, pad)
+    assert rel_err(dw, rdw) < 2e-6
+    assert rel_err(dx, rdx) < 2e-6
+    dw2, none = oracle.conv2d_bwd(x, w, dy, stride, (1, 1), pad, oracle.QUATERNION, variant, False)
+    assert none is None and np.array_equal(dw, dw2)
+
+
+def test_conv_integer_inputs_16p_equals_8p_exactly(oracle):
+    # with small integers every intermediate is exact in float, so the two forms must agree bit for bit
+    x = integers(7, (8, 3, 6, 6))
+    w = integers(8, (4, 4, 3, 3, 3)) * 2      # even weights keep the 0.5 factor of the 8-product form exact
+    a = oracle.conv2d_fwd(x, w, None, (1, 1), (1, 1), (1, 1, 1, 1), variant=0)
+    b = oracle.conv2d_fwd(x, w, None, (1, 1), (1, 1), (1, 1, 1, 1), variant=1)
+    assert np.array_equal(a, b)
+
+
+def test_conv_finite_difference(oracle):
+    """dW and dX of the oracle against central differences of its own forward, in one random direction."""
+    x = uniform(9, (4, 2, 5, 5))
+    w = uniform(10, (4, 3, 2, 3, 3))
+    pad, stride = (1, 1, 1, 1), (1, 1)
+    dy = normal(11, oracle.conv2d_fwd(x, w, None, stride, (1, 1), pad).shape)
+    dw, dx = oracle.conv2d_bwd(x, w, dy, stride, (1, 1), pad)
+    vx, vw = normal(12, x.shape), normal(13, w.shape)
+    eps = 1e-2
+
+    def loss(xx, ww):
+        return float(np.sum(conv_fwd_f64(xx, ww, None, stride, pad) * dy.astype(np.float64)))
+
+    fd_x = (loss(x + eps * vx, w) - loss(x - eps * vx, w)) / (2 * eps)
+    fd_w = (loss(x, w + eps * vw) - loss(x, w - eps * vw)) / (2 * eps)
+    assert abs(fd_x - float(np.sum(dx.astype(np.float64) * vx))) < 1e-3 * max(1.0, abs(fd_x))
+    assert abs(fd_w - float(np.sum(dw.astype(np.float64) * vw))) < 1e-3 * max(1.0, abs(fd_w))
+
+
+def test_conv_empty_input(oracle):
+    x = np.zeros((0, 3, 5, 5), np.float32)
+    w = uniform(14, (4, 2, 3, 3, 3))
+    y = oracle.conv2d_fwd(x, w, None, (1, 1), (1, 1), (1, 1, 1, 1))
+    assert y.shape == (0, 2, 5, 5)
+    dw, _ = oracle.conv2d_bwd(x, w, y, (1, 1), (1, 1), (1, 1, 1, 1))
+    assert np.all(dw == 0)
+
+
+@pytest.mark.parametrize("b,i,o", [(3, 5, 7), (8, 16, 4), (1, 1, 1)])
+@pytest.mark.parametrize("variant", [0, 1])
+@pytest.mark.parametrize("oi", [False, True])
+def test_dense_matches_float64(oracle, b, i, o, variant, oi):
+    x = normal(20, (4 * b, i))
+    w = normal(21, (4, o, i) if oi else (4, i, o))
+    bias = uniform(22, (4, o))
+    y = oracle.dense_fwd(x, w, bias, oi, oracle.QUATERNION, variant)
+    assert rel_err(y, dense_fwd_f64(x, w, bias, oi)) < 2e-6
+    dy = normal(23, y.shape)
+    dw, dx = oracle.dense_bwd(x, w, dy, oi, oracle.QUATERNION, variant, True)
+    rdw, rdx = dense_bwd_f64(x, w, dy, oi)
+    assert dw.shape == (4, i, o)        # always input-major, as both reference backends emit it
+    assert rel_err(dw, rdw) < 2e-6
+    assert rel_err(dx, rdx) < 2e-6
