@@ -1,0 +1,318 @@
+"""Benchmark of the quaternion conv2d hot path: forward + backward of the pointwise configuration.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference]
+
+Workload (one "step" = forward, backward-filter and backward-data of one batch): pointwise 1x1 quaternion
+conv2d, fp16 in/out, batch 64 per GPU, 128 -> 256 quaternion channels, 56x56, stride 1, NCHW, 16-product
+formulation on the tcgen05 kernels; activations N(0,1), weights He-normal, seeded synthetic data.
+Work per step and GPU: 3 passes x 32*N*H*W*Co*Ci = 631.4 GFLOP. Under torchrun every rank runs its own
+batch (weak scaling) and the filter gradient is summed across ranks with one NCCL all-reduce per step.
+
+Prints one JSON line: device-timed throughput with inputs resident in HBM (`value`), the same metric through
+the public API from pinned host buffers (`e2e`), the roofline of the slowest kernel, and a CPU baseline
+(the reference's 8-product orchestration over oneDNN via torch CPU ops) on a bounded sample.
+`--impl reference` times only that CPU orchestration.
+"""
+import argparse
+import json
+import os
+import statistics
+import subprocess
+import sys
+import time
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+if ROOT not in sys.path:
+    sys.path.insert(0, ROOT)
+
+WORKLOAD = dict(n=64, ci=128, co=256, h=56, w=56)
+SEED = 1234
+
+
+def flops_per_pass(n, ci, co, h, w):
+    return 32.0 * n * h * w * co * ci
+
+
+def read_peaks():
+    path = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.exists(path):
+        with open(path) as f:
+            p = json.load(f)
+        return dict(hbm_gbs=p["hbm_gbs"], tflops_burst=p["bf16_tflops"], tflops_sustained=p["bf16_tflops_sustained"],
+                    source="measured")
+    return dict(hbm_gbs=6650.0, tflops_burst=1590.0, tflops_sustained=1400.0, source="fallback")
+
+
+class ClockSampler:
+    """Samples SM clocks and throttle reasons with nvidia-smi while the timed region runs."""
+    QUERY = ("clocks.sm,clocks.max.sm,clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
+             "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, gpu_index):
+        self.proc = None
+        self.gpu_index = gpu_index
+
+    def start(self):
+        try:
+            self.proc = subprocess.Popen(
+                ["nvidia-smi", "-i", str(self.gpu_index), "--query-gpu=" + self.QUERY, "--format=csv,noheader,nounits",
+                 "-lms", "100"], stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+        except OSError:
+            self.proc = None
+
+    def stop(self):
+        if self.proc is None:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
+        self.proc.terminate()
+        try:
+            out, _ = self.proc.communicate(timeout=5)
+        except subprocess.TimeoutExpired:
+            self.proc.kill()
+            out, _ = self.proc.communicate()
+        sm, smax, reasons = [], [], set()
+        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+        for line in out.strip().splitlines():
+            parts = [p.strip() for p in line.split(",")]
+            if len(parts) < 6:
+                continue
+            try:
+                sm.append(float(parts[0]))
+                smax.append(float(parts[1]))
+            except ValueError:
+                continue
+            for name, val in zip(names, parts[2:6]):
+                if val.lower().startswith("active"):
+                    reasons.add(name)
+        return {"sm_mhz": statistics.median(sm) if sm else None, "sm_max_mhz": max(smax) if smax else None,
+                "samples": len(sm), "reasons": sorted(reasons)}
+
+
+def make_inputs(torch, n, ci, co, h, w, device, seed):
+    g = torch.Generator(device="cpu").manual_seed(seed)
+    x = torch.randn((4 * n, ci, h, w), generator=g, dtype=torch.float32).to(torch.float16)
+    wt = (torch.randn((4, co, ci, 1, 1), generator=g, dtype=torch.float32) * (2.0 / (4 * ci)) ** 0.5).to(torch.float16)
+    dy = torch.randn((4 * n, co, h, w), generator=g, dtype=torch.float32).to(torch.float16)
+    if device is None:
+        return x, wt, dy
+    return x.to(device), wt.to(device), dy.to(device)
+
+
+def cpu_baseline(torch, sample_n, reps):
+    """The reference's default (8-product) CPU orchestration over oneDNN, fp32, all host cores, on a reduced
+    batch of the same layer. Returns (TFLOP/s, cores, description)."""
+    from oracle import ref_orchestration as ro
+    cores = os.cpu_count() or 1
+    torch.set_num_threads(cores)
+    x, wt, dy = make_inputs(torch, sample_n, WORKLOAD["ci"], WORKLOAD["co"], WORKLOAD["h"], WORKLOAD["w"], None, SEED)
+    x, wt, dy = x.float(), wt.float(), dy.float()
+    pad, stride = (0, 0, 0, 0), (1, 1)
+    times = []
+    for r in range(reps + 1):
+        t0 = time.perf_counter()
+        ro.conv2d_fwd(x, wt, None, stride, pad, True)
+        ro.conv2d_bwd(x, wt, dy, stride, pad, True, True)
+        if r > 0:
+            times.append(time.perf_counter() - t0)
+    t = statistics.median(times)
+    fl = 3 * flops_per_pass(sample_n, WORKLOAD["ci"], WORKLOAD["co"], WORKLOAD["h"], WORKLOAD["w"])
+    sample = ("batch %d of the same layer (fp32, 8-product orchestration, torch CPU ops = oneDNN), median of %d steps"
+              % (sample_n, reps))
+    return fl / t / 1e12, cores, sample, t
+
+
+def run_reference(args):
+    import torch
+    rank = int(os.environ.get("RANK", "0"))
+    if rank != 0:
+        return
+    reps = max(1, args.steps)
+    value, cores, sample, t = cpu_baseline(torch, args.cpu_sample, reps)
+    line = {
+        "impl": "reference", "metric": "quaternion conv2d fwd+bwd TFLOP/s", "value": value, "unit": "TFLOP/s",
+        "n_gpus": args.gpus, "steps": reps, "warmup": 1, "ms_per_step": t * 1e3, "higher_is_better": True,
+        "scaling": "weak", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
+        "config": {"workload": "pointwise 1x1 quaternion conv2d fwd+bwd, 128->256 ch, 56x56 (CPU sample: batch %d)" % args.cpu_sample},
+        "cpu_baseline": {"value": value, "unit": "TFLOP/s", "cores": cores, "kind": "port", "sample": sample},
+        "e2e": {"value": value, "unit": "TFLOP/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+        "gpu_launches": 0,
+    }
+    print(json.dumps(line), flush=True)
+
+
+def run_ours(args):
+    import torch
+    import torch.distributed as dist
+    import phoenix_core_b200 as pcb
+    from phoenix_core_b200 import _lib
+    from phoenix_core_b200.context import Context
+
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    rank = int(os.environ.get("RANK", "0"))
+    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+    torch.cuda.set_device(local_rank)
+    device = torch.device("cuda", local_rank)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=device)
+
+    n, ci, co, h, w = (WORKLOAD[k] for k in ("n", "ci", "co", "h", "w"))
+    ctx16 = Context({"UPSTRIDE_MEMORY_OPTIMIZED": "1", "UPSTRIDE_CONV_FP16_POLICY": "full16"})
+    args_d = ((4 * n, ci, h, w), (4, co, ci, 1, 1), (1, 1), (1, 1), pcb.Padding.VALID, (), 1, pcb.Algebra.QUATERNION,
+              pcb.DataFormat.NCHW, pcb.FilterLayout.OIHW)
+    fwd_desc = pcb.Conv2DFwdDescriptor(*args_d, False)
+    bwd_desc = pcb.Conv2DBwdDescriptor(*args_d, True)
+
+    x, wt, dy = make_inputs(torch, n, ci, co, h, w, device, SEED + rank)
+    y = torch.empty(fwd_desc.getOutputShape(), dtype=torch.float16, device=device)
+    dw = torch.empty_like(wt)
+    dx = torch.empty_like(x)
+
+    def step():
+        pcb.conv2DFwd(x, wt, None, y, fwd_desc, ctx16)
+        pcb.conv2DBwd(x, wt, dy, dw, dx, bwd_desc, ctx16)
+        if world > 1:
+            dist.all_reduce(dw)
+
+    def sync_all():
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    for _ in range(max(3, args.warmup)):
+        step()
+    sync_all()
+    sampler = ClockSampler(local_rank)
+    if rank == 0:
+        sampler.start()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    sync_all()
+    e0.record()
+    for _ in range(args.steps):
+        step()
+    e1.record()
+    sync_all()
+    elapsed_ms = e0.elapsed_time(e1)
+    if world > 1:
+        tm = torch.tensor([elapsed_ms], device=device)
+        dist.all_reduce(tm, op=dist.ReduceOp.MAX)
+        elapsed_ms = float(tm.item())
+    clocks = sampler.stop() if rank == 0 else None
+
+    # per-kernel device times (same inputs, same stream), to find the kernel the roofline is quoted for
+    def timed(fn, reps):
+        a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        fn()
+        torch.cuda.synchronize()
+        a.record()
+        for _ in range(reps):
+            fn()
+        b.record()
+        torch.cuda.synchronize()
+        return a.elapsed_time(b) / reps
+
+    L = _lib.lib()
+    import ctypes
+    from phoenix_core_b200.ops import Device, _conv_desc, _ptr, _stream
+    d = _conv_desc(bwd_desc, torch.float16, ctx16, _lib.ENGINE_AUTO, require_input_grad=True)
+    ws = Device.get(device).requestWorkspace(L.pcb_qconv2d_bwd_workspace_size(ctypes.byref(d)))
+    kreps = max(3, args.steps)
+    t_fwd = timed(lambda: pcb.conv2DFwd(x, wt, None, y, fwd_desc, ctx16), kreps)
+    t_bwd_f = timed(lambda: _lib.check(L.pcb_qconv2d_bwd_filter(ctypes.byref(d), _ptr(x), _ptr(dy), _ptr(dw), _ptr(ws), ws.numel(), _stream())), kreps)
+    t_bwd_d = timed(lambda: _lib.check(L.pcb_qconv2d_bwd_data(ctypes.byref(d), _ptr(wt), _ptr(dy), _ptr(dx), _ptr(ws), ws.numel(), _stream())), kreps)
+    _lib.check(L.pcb_check_device_status(_ptr(ws), ws.numel(), _stream()))
+
+    # end to end through the public API from pinned host buffers
+    e2e = None
+    if rank == 0 or world > 1:
+        hx, hw, hdy = make_inputs(torch, n, ci, co, h, w, None, SEED + rank)
+        hx, hw, hdy = hx.pin_memory(), hw.pin_memory(), hdy.pin_memory()
+        hy = torch.empty(y.shape, dtype=torch.float16).pin_memory()
+        hdx = torch.empty(x.shape, dtype=torch.float16).pin_memory()
+        hdw = torch.empty(wt.shape, dtype=torch.float16).pin_memory()
+
+        def e2e_step():
+            x.copy_(hx, non_blocking=True)
+            wt.copy_(hw, non_blocking=True)
+            pcb.conv2DFwd(x, wt, None, y, fwd_desc, ctx16)
+            hy.copy_(y, non_blocking=True)
+            dy.copy_(hdy, non_blocking=True)
+            pcb.conv2DBwd(x, wt, dy, dw, dx, bwd_desc, ctx16)
+            if world > 1:
+                dist.all_reduce(dw)
+            hdw.copy_(dw, non_blocking=True)
+            hdx.copy_(dx, non_blocking=True)
+
+        e2e_steps = min(args.steps, 5)
+        e2e_step()
+        sync_all()
+        a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        a.record()
+        for _ in range(e2e_steps):
+            e2e_step()
+        b.record()
+        sync_all()
+        e2e_ms = a.elapsed_time(b)
+        if world > 1:
+            tm = torch.tensor([e2e_ms], device=device)
+            dist.all_reduce(tm, op=dist.ReduceOp.MAX)
+            e2e_ms = float(tm.item())
+        nb = lambda t_: t_.numel() * t_.element_size()
+        e2e = {"value": 3 * flops_per_pass(n, ci, co, h, w) * world * e2e_steps / (e2e_ms * 1e-3) / 1e12, "unit": "TFLOP/s",
+               "h2d_bytes_per_step": nb(hx) + nb(hw) + nb(hdy), "d2h_bytes_per_step": nb(hy) + nb(hdw) + nb(hdx),
+               "steps": e2e_steps, "ms_per_step": e2e_ms / e2e_steps}
+
+    if rank == 0:
+        peaks = read_peaks()
+        fl = flops_per_pass(n, ci, co, h, w)
+        total = 3 * fl * world * args.steps
+        value = total / (elapsed_ms * 1e-3) / 1e12
+        kernels = {"forward": t_fwd, "backward_filter": t_bwd_f, "backward_data": t_bwd_d}
+        worst = max(kernels, key=kernels.get)
+        achieved = fl / (kernels[worst] * 1e-3) / 1e12
+        traffic_path = os.path.join(ROOT, "profiles", "traffic.json")
+        traffic = None
+        if os.path.exists(traffic_path):
+            with open(traffic_path) as f:
+                traffic = json.load(f).get(worst)
+        cpu_v, cores, sample, _ = cpu_baseline(torch, args.cpu_sample, 5) if world == 1 else (None, None, None, None)
+        line = {
+            "metric": "quaternion conv2d fwd+bwd TFLOP/s", "value": value, "unit": "TFLOP/s", "n_gpus": world,
+            "steps": args.steps, "warmup": max(3, args.warmup), "ms_per_step": elapsed_ms / args.steps,
+            "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "f16", "data": "synthetic",
+            "config": {"workload": "pointwise 1x1 quaternion conv2d fwd+bwd, fp16 in/out, fp32 accumulate, batch %d/GPU, "
+                                   "%d->%d quaternion channels, %dx%d, 16-product, NCHW" % (n, ci, co, h, w),
+                       "parallelism": "dp%d" % world, "l2": "inputs (196 MiB) and outputs (392 MiB) exceed the 126 MB L2",
+                       "flop_per_step_per_gpu": 3 * fl},
+            "pct_of_tensor_peak": {"sustained": value / world / peaks["tflops_sustained"], "burst": value / world / peaks["tflops_burst"],
+                                   "peaks": peaks["source"]},
+            "kernel_ms": kernels,
+            "roofline": {"bound": "tensor", "kernel": worst, "achieved": achieved, "peak": peaks["tflops_sustained"],
+                         "unit": "TFLOP/s", "frac": achieved / peaks["tflops_sustained"], "peak_source": peaks["source"] + " (sustained bf16)",
+                         "traffic": traffic},
+            "clocks": clocks,
+            "e2e": e2e,
+            "gpu_launches": 4 * args.steps,
+        }
+        if cpu_v is not None:
+            line["cpu_baseline"] = {"value": cpu_v, "unit": "TFLOP/s", "cores": cores, "kind": "port", "sample": sample}
+        print(json.dumps(line), flush=True)
+    if world > 1:
+        dist.barrier()
+        dist.destroy_process_group()
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=20)
+    ap.add_argument("--warmup", type=int, default=3)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--cpu-sample", type=int, default=32, help="batch size of the CPU baseline sample")
+    args = ap.parse_args()
+    if args.impl == "reference":
+        run_reference(args)
+    else:
+        run_ours(args)
+
+
+if __name__ == "__main__":
+    main()

@@ -1,0 +1,427 @@
+// tcgen05 / TMEM kernels for the quaternion operators with 16-bit operands (fp16 or bf16, fp32
+// accumulation in tensor memory).
+//
+// Pointwise (1x1, stride 1, no padding) quaternion convolution, all three passes, as ONE real GEMM per
+// pass whose M x K operand carries the quaternion structure:
+//
+//   forward          D[(d,co), (img,p)] = sum_{(l,ci)}   s(l,d) w[l^d][co][ci]      * x[l][img][ci][p]
+//   backward-data    D[(l,ci), (img,p)] = sum_{(d,co)}   s(l,d) w[l^d][co][ci]      * dy[d][img][co][p]
+//   backward-filter  D[(r,co), ci]      = sum_{(l,img,p)} s(l,l^r) dy[l^r][img][co][p] * x[l][img][ci][p]
+//
+// The 4x4 signed / permuted weight block (reference sign table src/algebras.cc:28-49) is never stored in
+// global memory: producer warps read the four component tiles and write their signed copies straight into
+// the shared-memory operand tile in the tcgen05 canonical layout (sign = one XOR on the fp16/bf16 sign
+// bits, so it is exact). For the filter gradient the same is done to the dy operand. Replaces the
+// CUDA-core 1x1 kernels of src/backend/cudnn/quat_pointwise_conv2d.cu:33-607 and, for 1x1 shapes, the 16
+// cuDNN calls of src/conv2d.hpp:237-275 / :522-562.
+//
+// CTA = 5 warps. Warps 0-3 produce operand tiles (global -> registers -> swizzled shared memory) through a
+// 3-stage ring of mbarriers, then become the epilogue (TMEM -> registers -> global). Warp 4 allocates
+// tensor memory and its lane 0 issues tcgen05.mma. Tile 128 (M) x 128 (N) x 64 (K per stage); two CTAs
+// fit on an SM (96 KB shared memory and 128 TMEM columns each), so one CTA's epilogue overlaps the
+// other's main loop. Every barrier wait is bounded; on expiry a status word is set and the CTA runs to its
+// normal teardown (TMEM is always released).
+#include "tensor_path.cuh"
+#include "umma.cuh"
+
+namespace pcb {
+namespace {
+
+using namespace umma;
+
+constexpr int TBM = 128, TBN = 128, TBK = 64, STAGES = 3;
+constexpr int PRODUCER_THREADS = 128, TC_THREADS = 160;
+constexpr uint32_t A_STAGE_BYTES = TBM * TBK * 2, B_STAGE_BYTES = TBN * TBK * 2;
+constexpr uint32_t MN_BLOCK_BYTES = 64 * 128;          // one 64-element M/N block of an MN-major tile (64 K rows)
+constexpr uint32_t TMEM_COLS = 128;
+constexpr size_t TC_SMEM_BYTES = 1024 /*alignment slack*/ + STAGES * (A_STAGE_BYTES + B_STAGE_BYTES) +
+                                 STAGES * 64 * sizeof(int4) + 512;
+
+// status codes OR-ed into the workspace status word when a bounded wait expires
+constexpr int ST_PRODUCER_TIMEOUT = 1, ST_MMA_TIMEOUT = 2, ST_EPILOGUE_TIMEOUT = 4;
+
+struct TcParams {
+    Geom g;
+    int pass;
+    int fmt;            // 0 = f16, 1 = bf16
+    int M, N, K;
+    int k_per_split;    // multiple of TBK
+    int atomic_out;     // backward-filter: accumulate into fp32 scratch with atomics
+};
+
+__device__ __forceinline__ uint4 ld_chunk(const uint16_t* p) { return __ldg(reinterpret_cast<const uint4*>(p)); }
+__device__ __forceinline__ void st_chunk(uint8_t* tile, uint32_t off, uint4 v) { *reinterpret_cast<uint4*>(tile + off) = v; }
+__device__ __forceinline__ uint4 negate16(uint4 v) {
+    v.x ^= 0x80008000u; v.y ^= 0x80008000u; v.z ^= 0x80008000u; v.w ^= 0x80008000u;
+    return v;
+}
+
+// Row / column ("MN") part of an operand address: component selector `aux` (-1: out of range -> zeros)
+// and element offset.
+struct MnInfo { int aux; int off; };
+
+template <int PASS>
+__device__ __forceinline__ MnInfo a_mn_info(const Geom& g, int m, int M) {
+    if (m >= M) return {-1, 0};
+    const int HW = g.H * g.W;
+    if (PASS == PASS_FWD) { const int d = m / g.Co, co = m - d * g.Co; return {d, co * g.Ci}; }
+    if (PASS == PASS_BWD_DATA) { const int l = m / g.Ci, ci = m - l * g.Ci; return {l, ci}; }
+    const int r = m / g.Co, co = m - r * g.Co;
+    return {r, co * HW};
+}
+template <int PASS>
+__device__ __forceinline__ MnInfo b_mn_info(const Geom& g, int n, int N) {
+    if (n >= N) return {-1, 0};
+    const int HW = g.H * g.W;
+    if (PASS == PASS_BWD_FILTER) return {0, n * HW};                       // n = ci
+    const int img = n / HW, p = n - img * HW;
+    return {0, img * (PASS == PASS_FWD ? g.Ci : g.Co) * HW + p};
+}
+// K part: x = component selector (-1: beyond K), y = offset into the A operand, z = offset into B.
+template <int PASS>
+__device__ __forceinline__ int4 k_info(const Geom& g, int k, int kend) {
+    if (k >= kend) return make_int4(-1, 0, 0, 0);
+    const int HW = g.H * g.W;
+    if (PASS == PASS_FWD) { const int l = k / g.Ci, ci = k - l * g.Ci; return make_int4(l, ci, ci * HW, 0); }
+    if (PASS == PASS_BWD_DATA) { const int d = k / g.Co, co = k - d * g.Co; return make_int4(d, co * g.Ci, co * HW, 0); }
+    const int NP = g.Nb * HW;
+    const int l = k / NP, rem = k - l * NP;
+    const int img = rem / HW, p = rem - img * HW;
+    return make_int4(l, img * g.Co * HW + p, img * g.Ci * HW + p, 0);
+}
+
+// A operand is MN-major only for backward-data (ci is the contiguous index of the filters);
+// B operand is K-major only for backward-filter (pixels are the contiguous index of x).
+template <int PASS> struct Layout {
+    static constexpr bool A_MN = (PASS == PASS_BWD_DATA);
+    static constexpr bool B_MN = (PASS != PASS_BWD_FILTER);
+};
+
+template <int PASS>
+__global__ void __launch_bounds__(TC_THREADS)
+qgemm_tc_kernel(TcParams p, const uint16_t* __restrict__ a, const uint16_t* __restrict__ b, const uint16_t* __restrict__ bias,
+                uint16_t* __restrict__ out, float* __restrict__ out32, int* __restrict__ status) {
+    extern __shared__ uint8_t smem_raw[];
+    const Geom& g = p.g;
+    const int t = threadIdx.x, warp = t >> 5, lane = t & 31;
+    const int HW = g.H * g.W;
+
+    // carve shared memory: operand ring (1024-byte aligned), K tables, barriers, TMEM slot
+    uint8_t* base = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+    uint8_t* a_tiles = base;
+    uint8_t* b_tiles = base + STAGES * A_STAGE_BYTES;
+    int4* ktab = reinterpret_cast<int4*>(b_tiles + STAGES * B_STAGE_BYTES);
+    uint64_t* bars = reinterpret_cast<uint64_t*>(ktab + STAGES * 64);
+    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 3 * STAGES + 1);
+    const uint32_t full_bar = smem_u32(bars), empty_bar = smem_u32(bars + STAGES), ktab_bar = smem_u32(bars + 2 * STAGES),
+                   accum_bar = smem_u32(bars + 3 * STAGES);
+
+    const int m0 = blockIdx.y * TBM, n0 = blockIdx.x * TBN;
+    const int kbeg = blockIdx.z * p.k_per_split;
+    const int kend = min(p.K, kbeg + p.k_per_split);
+    const int num_it = (kend - kbeg + TBK - 1) / TBK;
+
+    if (t == 0) {
+        for (int s = 0; s < STAGES; ++s) {
+            mbar_init(full_bar + 8 * s, PRODUCER_THREADS);
+            mbar_init(empty_bar + 8 * s, 1);
+            mbar_init(ktab_bar + 8 * s, 64);
+        }
+        mbar_init(accum_bar, 1);
+        fence_barrier_init();
+    }
+    if (warp == 4) tmem_alloc(smem_u32(tmem_slot), TMEM_COLS);
+    tc_fence_before_sync();
+    __syncthreads();
+    tc_fence_after_sync();
+    const uint32_t tmem_base = *tmem_slot;
+
+    if (warp < 4) {
+        // ------------------------------------------------------------------ producers
+        // component strides of the two operands
+        const int a_comp = PASS == PASS_BWD_FILTER ? g.Nb * g.Co * HW : g.Co * g.Ci;
+        const int b_comp = PASS == PASS_BWD_DATA ? g.Nb * g.Co * HW : g.Nb * g.Ci * HW;
+        // stage-invariant part of this thread's chunk coordinates
+        MnInfo a_info[8], b_info[8];
+        if (Layout<PASS>::A_MN) {
+            a_info[0] = a_mn_info<PASS>(g, m0 + 8 * (t & 15), p.M);             // chunk column t%16 of an MN-major tile
+        } else {
+#pragma unroll
+            for (int j = 0; j < 8; ++j) a_info[j] = a_mn_info<PASS>(g, m0 + (t >> 3) + 16 * j, p.M);   // rows of a K-major tile
+        }
+        if (Layout<PASS>::B_MN) {
+            b_info[0] = b_mn_info<PASS>(g, n0 + 8 * (t & 15), p.N);
+        } else {
+#pragma unroll
+            for (int j = 0; j < 8; ++j) b_info[j] = b_mn_info<PASS>(g, n0 + (t >> 3) + 16 * j, p.N);
+        }
+
+        bool ok = true;
+        for (int it = 0; it < num_it && ok; ++it) {
+            const int s = it % STAGES;
+            const uint32_t parity = ((it / STAGES) & 1) ^ 1;
+            ok = mbar_wait_bounded(empty_bar + 8 * s, parity, status, ST_PRODUCER_TIMEOUT);
+            if (!ok) break;
+            const int k0 = kbeg + it * TBK;
+            int4* kt = ktab + s * 64;
+            if (t < 64) {
+                kt[t] = k_info<PASS>(g, k0 + t, kend);
+                mbar_arrive(ktab_bar + 8 * s);
+            }
+            ok = mbar_wait_bounded(ktab_bar + 8 * s, parity ^ 1, status, ST_PRODUCER_TIMEOUT);
+            if (!ok) break;
+
+            uint8_t* a_tile = a_tiles + s * A_STAGE_BYTES;
+            uint8_t* b_tile = b_tiles + s * B_STAGE_BYTES;
+            // ---- A operand: signed copies of the component tiles
+            if (Layout<PASS>::A_MN) {
+                const int c = t & 15;
+#pragma unroll
+                for (int j = 0; j < 8; ++j) {
+                    const int kr = (t >> 4) + 8 * j;
+                    const int4 ke = kt[kr];
+                    uint4 v = make_uint4(0, 0, 0, 0);
+                    if (a_info[0].aux >= 0 && ke.x >= 0) {
+                        const int l = a_info[0].aux, d = ke.x;                   // backward-data: rows carry l, K carries d
+                        v = ld_chunk(a + (size_t)(l ^ d) * a_comp + a_info[0].off + ke.y);
+                        if (quat_negative(l, d)) v = negate16(v);
+                    }
+                    st_chunk(a_tile, mnmajor_sw128_offset(kr, c, MN_BLOCK_BYTES), v);
+                }
+            } else {
+                const int kc = t & 7;
+                const int4 ke = kt[8 * kc];
+#pragma unroll
+                for (int j = 0; j < 8; ++j) {
+                    const int row = (t >> 3) + 16 * j;
+                    uint4 v = make_uint4(0, 0, 0, 0);
+                    if (a_info[j].aux >= 0 && ke.x >= 0) {
+                        int l, d;
+                        if (PASS == PASS_FWD) { d = a_info[j].aux; l = ke.x; }
+                        else { l = ke.x; d = l ^ a_info[j].aux; }                 // backward-filter: rows carry r
+                        v = ld_chunk(a + (size_t)(PASS == PASS_FWD ? (l ^ d) : d) * a_comp + a_info[j].off + ke.y);
+                        if (quat_negative(l, d)) v = negate16(v);
+                    }
+                    st_chunk(a_tile, kmajor_sw128_offset(row, kc), v);
+                }
+            }
+            // ---- B operand: activations, copied as they are
+            if (Layout<PASS>::B_MN) {
+                const int c = t & 15;
+#pragma unroll
+                for (int j = 0; j < 8; ++j) {
+                    const int kr = (t >> 4) + 8 * j;
+                    const int4 ke = kt[kr];
+                    uint4 v = make_uint4(0, 0, 0, 0);
+                    if (b_info[0].aux >= 0 && ke.x >= 0) v = ld_chunk(b + (size_t)ke.x * b_comp + b_info[0].off + ke.z);
+                    st_chunk(b_tile, mnmajor_sw128_offset(kr, c, MN_BLOCK_BYTES), v);
+                }
+            } else {
+                const int kc = t & 7;
+                const int4 ke = kt[8 * kc];
+#pragma unroll
+                for (int j = 0; j < 8; ++j) {
+                    const int row = (t >> 3) + 16 * j;
+                    uint4 v = make_uint4(0, 0, 0, 0);
+                    if (b_info[j].aux >= 0 && ke.x >= 0) v = ld_chunk(b + (size_t)ke.x * b_comp + b_info[j].off + ke.z);
+                    st_chunk(b_tile, kmajor_sw128_offset(row, kc), v);
+                }
+            }
+            fence_proxy_async_smem();
+            mbar_arrive(full_bar + 8 * s);
+        }
+
+        // ------------------------------------------------------------------ epilogue
+        if (ok) ok = mbar_wait_bounded(accum_bar, 0, status, ST_EPILOGUE_TIMEOUT);
+        // one decision per warp (tcgen05.ld is warp-collective); nothing is written once any wait has expired
+        ok = __all_sync(0xffffffffu, ok && (*reinterpret_cast<volatile int*>(status) == 0));
+        tc_fence_after_sync();
+        if (ok && num_it > 0) {
+            const int m = m0 + warp * 32 + lane;                                 // TMEM lane == tile row
+            const MnInfo mi = a_mn_info<PASS>(g, m, p.M);
+            size_t row_off = 0;
+            float badd = 0.f;
+            if (mi.aux >= 0) {
+                if (PASS == PASS_FWD) {
+                    const int d = mi.aux, co = m - d * g.Co;
+                    row_off = ((size_t)d * g.Nb * g.Co + co) * HW;
+                    if (g.has_bias) {
+                        const uint16_t raw = bias[d * g.Co + co];
+                        badd = p.fmt == 0 ? __half2float(__ushort_as_half(raw)) : __bfloat162float(__ushort_as_bfloat16(raw));
+                    }
+                } else if (PASS == PASS_BWD_DATA) {
+                    const int l = mi.aux, ci = m - l * g.Ci;
+                    row_off = ((size_t)l * g.Nb * g.Ci + ci) * HW;
+                } else {
+                    row_off = (size_t)m * g.Ci;                                  // dw[r][co][ci], m = r*Co + co
+                }
+            }
+#pragma unroll 1
+            for (int cb = 0; cb < TBN / 32; ++cb) {
+                uint32_t v[32];
+                tmem_ld_32x32b_x32(tmem_base + ((uint32_t)(warp * 32) << 16) + cb * 32, v);
+                tmem_ld_wait();
+                if (mi.aux < 0) continue;
+                if (PASS == PASS_BWD_FILTER) {
+#pragma unroll
+                    for (int c = 0; c < 32; ++c) {
+                        const int n = n0 + cb * 32 + c;
+                        if (n < p.N) {
+                            if (p.atomic_out) atomicAdd(out32 + row_off + n, __uint_as_float(v[c]));
+                            else out32[row_off + n] = __uint_as_float(v[c]);
+                        }
+                    }
+                } else {
+                    const int out_c = PASS == PASS_FWD ? g.Co : g.Ci;
+#pragma unroll
+                    for (int c8 = 0; c8 < 4; ++c8) {
+                        const int n = n0 + cb * 32 + c8 * 8;
+                        if (n >= p.N) continue;
+                        const int img = n / HW, px = n - img * HW;
+                        uint32_t packed[4];
+#pragma unroll
+                        for (int q = 0; q < 4; ++q) {
+                            const float f0 = __uint_as_float(v[c8 * 8 + 2 * q]) + badd;
+                            const float f1 = __uint_as_float(v[c8 * 8 + 2 * q + 1]) + badd;
+                            if (p.fmt == 0) {
+                                const __half2 h = __floats2half2_rn(f0, f1);
+                                packed[q] = *reinterpret_cast<const uint32_t*>(&h);
+                            } else {
+                                const __nv_bfloat162 h = __floats2bfloat162_rn(f0, f1);
+                                packed[q] = *reinterpret_cast<const uint32_t*>(&h);
+                            }
+                        }
+                        uint16_t* dst = out + row_off + (size_t)img * out_c * HW + px;
+                        *reinterpret_cast<uint4*>(dst) = make_uint4(packed[0], packed[1], packed[2], packed[3]);
+                    }
+                }
+            }
+        }
+    } else {
+        // ------------------------------------------------------------------ MMA issuer (warp 4)
+        const uint32_t idesc = make_idesc_f16(p.fmt, TBM, TBN, Layout<PASS>::A_MN, Layout<PASS>::B_MN);
+        bool ok = true;
+        for (int it = 0; it < num_it && ok; ++it) {
+            const int s = it % STAGES;
+            const uint32_t parity = (it / STAGES) & 1;
+            ok = mbar_wait_bounded(full_bar + 8 * s, parity, status, ST_MMA_TIMEOUT);
+            if (!ok) break;
+            tc_fence_after_sync();
+            if (lane == 0) {
+                const uint32_t a_addr = smem_u32(a_tiles + s * A_STAGE_BYTES);
+                const uint32_t b_addr = smem_u32(b_tiles + s * B_STAGE_BYTES);
+#pragma unroll
+                for (int j = 0; j < TBK / 16; ++j) {
+                    // 16 K-elements per instruction: 32 bytes along a K-major row, 16 K-rows (2048 bytes) of an MN-major tile
+                    const uint64_t ad = Layout<PASS>::A_MN ? make_desc_mnmajor(a_addr + j * 2048, MN_BLOCK_BYTES)
+                                                           : make_desc_kmajor(a_addr + j * 32);
+                    const uint64_t bd = Layout<PASS>::B_MN ? make_desc_mnmajor(b_addr + j * 2048, MN_BLOCK_BYTES)
+                                                           : make_desc_kmajor(b_addr + j * 32);
+                    mma_f16_ss(tmem_base, ad, bd, idesc, (it > 0 || j > 0) ? 1u : 0u);
+                }
+                mma_commit(empty_bar + 8 * s);          // frees the stage once these MMAs have read it
+            }
+            __syncwarp();
+        }
+        if (lane == 0 && num_it > 0 && ok) mma_commit(accum_bar);
+        if (lane == 0 && (num_it == 0 || !ok)) mbar_arrive(accum_bar);   // never leave the epilogue waiting
+        __syncwarp();
+    }
+
+    // ---------------------------------------------------------------------- teardown
+    tc_fence_before_sync();
+    __syncthreads();
+    if (warp == 4) tmem_dealloc(tmem_base, TMEM_COLS);
+}
+
+template <typename T>
+__global__ void cast_f32_to_16_kernel(const float* __restrict__ src, T* __restrict__ dst, size_t n) {
+    size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+    const size_t stride = (size_t)gridDim.x * blockDim.x;
+    for (; i < n; i += stride) DType<T>::store(dst + i, src[i]);
+}
+
+int sm_count() {
+    static int sms = 0;
+    if (sms == 0) {
+        int dev = 0;
+        if (cudaGetDevice(&dev) != cudaSuccess || cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || sms <= 0)
+            sms = 148;
+    }
+    return sms;
+}
+
+template <int PASS>
+int launch_tc(const TcParams& p, int splits, const void* a, const void* b, const void* bias, void* out, float* out32,
+              int* status, cudaStream_t stream) {
+    PCB_CUDA_TRY(cudaFuncSetAttribute(qgemm_tc_kernel<PASS>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)TC_SMEM_BYTES));
+    dim3 grid((p.N + TBN - 1) / TBN, (p.M + TBM - 1) / TBM, splits);
+    qgemm_tc_kernel<PASS><<<grid, TC_THREADS, TC_SMEM_BYTES, stream>>>(
+        p, (const uint16_t*)a, (const uint16_t*)b, (const uint16_t*)bias, (uint16_t*)out, out32, status);
+    PCB_CUDA_TRY(cudaGetLastError());
+    return PCB_OK;
+}
+
+bool pointwise(const Geom& g) {
+    return g.KH == 1 && g.KW == 1 && g.SH == 1 && g.SW == 1 && g.PT == 0 && g.PL == 0 && g.HO == g.H && g.WO == g.W &&
+           g.DH == 1 && g.DW == 1;
+}
+
+}  // namespace
+
+bool tensor_path_supported(Pass /*pass*/, int dtype, int variant, const Geom& g) {
+    if (dtype != PCB_F16 && dtype != PCB_BF16) return false;
+    if (variant != PCB_VARIANT_16_PRODUCT) return false;
+    if (g.real_in || g.w_io || g.dw_io) return false;
+    if (!pointwise(g)) return false;
+    // 16-byte operand chunks must not straddle a component, an image or a channel row
+    return (g.Ci % 8 == 0) && (g.Co % 8 == 0) && ((g.H * g.W) % 8 == 0);
+}
+
+size_t tensor_scratch_bytes(Pass pass, int dtype, int variant, int engine, const Geom& g) {
+    if (engine == PCB_ENGINE_SIMT || !tensor_path_supported(pass, dtype, variant, g)) return 0;
+    if (pass == PASS_BWD_FILTER) return (size_t)4 * g.Co * g.Ci * g.KH * g.KW * sizeof(float);
+    return 0;
+}
+
+int tensor_launch(Pass pass, int dtype, int /*variant*/, const Geom& g, const void* a, const void* b, const void* bias,
+                  void* out, float* scratch, int* status, cudaStream_t stream) {
+    TcParams p;
+    p.g = g;
+    p.pass = pass;
+    p.fmt = dtype == PCB_F16 ? 0 : 1;
+    const int HW = g.H * g.W;
+    if (pass == PASS_FWD)           { p.M = 4 * g.Co; p.N = g.Nb * HW; p.K = 4 * g.Ci; }
+    else if (pass == PASS_BWD_DATA) { p.M = 4 * g.Ci; p.N = g.Nb * HW; p.K = 4 * g.Co; }
+    else                            { p.M = 4 * g.Co; p.N = g.Ci;      p.K = 4 * g.Nb * HW; }
+    p.k_per_split = (p.K + TBK - 1) / TBK * TBK;
+    p.atomic_out = 0;
+    PCB_CUDA_TRY(cudaMemsetAsync(status, 0, sizeof(int), stream));
+    if (pass == PASS_FWD) return launch_tc<PASS_FWD>(p, 1, a, b, bias, out, nullptr, status, stream);
+    if (pass == PASS_BWD_DATA) return launch_tc<PASS_BWD_DATA>(p, 1, a, b, bias, out, nullptr, status, stream);
+
+    // backward-filter: the output is tiny and K is the whole batch of pixels -> split K across the grid,
+    // accumulate in fp32 scratch, then cast once.
+    if (scratch == nullptr) { set_error("backward-filter needs fp32 scratch"); return PCB_ERR_WORKSPACE; }
+    const int tiles = ((p.M + TBM - 1) / TBM) * ((p.N + TBN - 1) / TBN);
+    int splits = (2 * sm_count() + tiles - 1) / tiles;
+    const int max_splits = (p.K + 4 * TBK - 1) / (4 * TBK);
+    if (splits > max_splits) splits = max_splits;
+    if (splits < 1) splits = 1;
+    int kps = (p.K + splits - 1) / splits;
+    kps = (kps + TBK - 1) / TBK * TBK;
+    splits = (p.K + kps - 1) / kps;
+    p.k_per_split = kps;
+    p.atomic_out = splits > 1 ? 1 : 0;
+    const size_t numel = (size_t)4 * g.Co * g.Ci;
+    if (p.atomic_out) PCB_CUDA_TRY(cudaMemsetAsync(scratch, 0, numel * sizeof(float), stream));
+    int rc = launch_tc<PASS_BWD_FILTER>(p, splits, a, b, bias, out, scratch, status, stream);
+    if (rc != PCB_OK) return rc;
+    const int blocks = (int)((numel + 255) / 256 < 1184 ? (numel + 255) / 256 : 1184);
+    if (dtype == PCB_F16) cast_f32_to_16_kernel<__half><<<blocks, 256, 0, stream>>>(scratch, (__half*)out, numel);
+    else cast_f32_to_16_kernel<__nv_bfloat16><<<blocks, 256, 0, stream>>>(scratch, (__nv_bfloat16*)out, numel);
+    PCB_CUDA_TRY(cudaGetLastError());
+    return PCB_OK;
+}
+
+}  // namespace pcb

@@ -1,0 +1,15 @@
+// Interface of the tcgen05 (tensor-core) kernel family towards the C ABI dispatcher.
+#pragma once
+#include "common.cuh"
+
+namespace pcb {
+
+// True when a tensor-core kernel exists for this pass / dtype / variant / geometry.
+bool tensor_path_supported(Pass pass, int dtype, int variant, const Geom& g);
+// Scratch bytes (beyond the workspace header) the tensor-core kernel of this problem needs.
+size_t tensor_scratch_bytes(Pass pass, int dtype, int variant, int engine, const Geom& g);
+// Operand roles as for simt_launch. `status` is the device status word of the workspace header.
+int tensor_launch(Pass pass, int dtype, int variant, const Geom& g, const void* a, const void* b, const void* bias,
+                  void* out, float* scratch, int* status, cudaStream_t stream);
+
+}  // namespace pcb

@@ -1,0 +1,220 @@
+"""The four entry points of the engine on torch CUDA tensors: ``conv2DFwd``, ``conv2DBwd``, ``denseFwd``,
+``denseBwd`` (reference ``src/upstride.hpp:18-86``).
+
+torch is used only to own device memory and streams; the arithmetic happens in the CUDA backend behind the
+C ABI (``include/phoenix_core_b200.h``). Tensors are caller-owned and must be contiguous; work is enqueued
+on the current torch stream and the calls return without synchronising, like the reference's GPU backend.
+Only quaternion NCHW / OIHW (conv) and IO / OI (dense) problems are accepted; anything else raises (there
+is no CPU fallback).
+"""
+import ctypes
+import threading
+
+import torch
+
+from . import _lib
+from .context import Context
+from .descriptors import Algebra, DataFormat, FilterLayout
+
+_DTYPES = {torch.float32: _lib.PCB_F32, torch.float16: _lib.PCB_F16, torch.bfloat16: _lib.PCB_BF16}
+
+
+class Device:
+    """Per-CUDA-device state: an access mutex and one grow-only workspace, as the reference's
+    ``upstride::Device`` (``src/backend/device.hpp:12-110``: ``accessControl``, ``requestWorkspace``)."""
+    _devices = {}
+    _registry_lock = threading.Lock()
+
+    def __init__(self, index):
+        self.index = index
+        self.accessControl = threading.Lock()
+        self.workspace = None
+        self.context = Context()
+
+    @classmethod
+    def get(cls, torch_device):
+        idx = torch_device.index if torch_device.index is not None else torch.cuda.current_device()
+        with cls._registry_lock:
+            dev = cls._devices.get(idx)
+            if dev is None:
+                dev = cls._devices[idx] = Device(idx)
+            return dev
+
+    def requestWorkspace(self, nbytes):
+        if self.workspace is None or self.workspace.numel() < nbytes:
+            self.workspace = torch.empty(max(nbytes, 1 << 20), dtype=torch.uint8, device=torch.device("cuda", self.index))
+        return self.workspace
+
+    def getContext(self):
+        return self.context
+
+
+def _ptr(t):
+    return None if t is None else ctypes.c_void_p(t.data_ptr())
+
+
+def _check_tensor(t, name, dtype=None, shape=None):
+    if not t.is_cuda:
+        raise ValueError("%s must be a CUDA tensor (no CPU fallback exists)" % name)
+    if not t.is_contiguous():
+        raise ValueError("%s must be contiguous" % name)
+    if dtype is not None and t.dtype != dtype:
+        raise ValueError("%s dtype mismatch: %s vs %s" % (name, t.dtype, dtype))
+    if shape is not None and tuple(t.shape) != tuple(shape):
+        raise ValueError("%s shape mismatch: %s vs expected %s" % (name, tuple(t.shape), tuple(shape)))
+
+
+def _stream():
+    return ctypes.c_void_p(torch.cuda.current_stream().cuda_stream)
+
+
+def _conv_desc(descriptor, dtype, context, engine, has_bias=False, require_input_grad=False):
+    if descriptor.getAlgebra() != Algebra.QUATERNION:
+        raise _lib.BackendError(_lib.PCB_ERR_UNSUPPORTED, "only the quaternion algebra is implemented")
+    if descriptor.getDataFormat() != DataFormat.NCHW or descriptor.getFilterLayout() != FilterLayout.OIHW:
+        raise _lib.BackendError(_lib.PCB_ERR_UNSUPPORTED, "only NCHW activations with OIHW filters are implemented")
+    ishape, fshape = descriptor.getInputShape(), descriptor.getFilterShape()
+    real = descriptor.isRealValuedInput()
+    if not real and ishape[0] % 4 != 0:
+        raise ValueError("leading input dimension must be a multiple of 4 (components stacked on the batch axis)")
+    if ishape[1] != fshape[2] * descriptor.getGroups():
+        raise ValueError("input channels mismatch: %d vs %d" % (ishape[1], fshape[2]))
+    d = _lib.ConvDesc()
+    d.dtype = _DTYPES[dtype]
+    d.n = ishape[0] if real else ishape[0] // 4
+    d.ci, d.co = fshape[2], fshape[1]
+    d.h, d.w = ishape[2], ishape[3]
+    d.kh, d.kw = fshape[3], fshape[4]
+    d.stride_h, d.stride_w = descriptor.getStride()
+    d.dilation_h, d.dilation_w = descriptor.getDilation()
+    d.pad_top, d.pad_left = descriptor.getPaddingBefore()
+    d.pad_bottom, d.pad_right = descriptor.getPaddingAfter()
+    d.groups = descriptor.getGroups()
+    d.has_bias = int(has_bias)
+    d.require_input_grad = int(require_input_grad)
+    d.real_valued_input = int(real)
+    d.variant = context.variant()
+    d.fp16_policy = int(context.conv_fp16_policy)
+    d.engine = engine
+    return d
+
+
+def conv2DFwd(inputTensor, filterTensor, biasTensor, outputTensor, descriptor, context=None, engine=_lib.ENGINE_AUTO):
+    """y = x (*) w [+ bias]; mirrors ``upstride::conv2DFwd`` (reference ``src/upstride.hpp:18-33``)."""
+    dev = Device.get(inputTensor.device)
+    context = context or dev.getContext()
+    _check_tensor(inputTensor, "input", shape=descriptor.getInputShape())
+    _check_tensor(filterTensor, "filter", inputTensor.dtype, descriptor.getFilterShape())
+    _check_tensor(outputTensor, "output", inputTensor.dtype, descriptor.getOutputShape())
+    if biasTensor is not None:
+        if not descriptor.isBiasUsed():
+            raise ValueError("Bias application is not configured for this operation")
+        _check_tensor(biasTensor, "bias", inputTensor.dtype, descriptor.getBiasShape())
+    if inputTensor.numel() == 0:
+        return      # empty input: silent no-op (reference src/conv2d.hpp:81-82)
+    d = _conv_desc(descriptor, inputTensor.dtype, context, engine, has_bias=biasTensor is not None)
+    L = _lib.lib()
+    with dev.accessControl, torch.cuda.device(dev.index):
+        need = L.pcb_qconv2d_fwd_workspace_size(ctypes.byref(d))
+        ws = dev.requestWorkspace(need)
+        _lib.check(L.pcb_qconv2d_fwd(ctypes.byref(d), _ptr(inputTensor), _ptr(filterTensor), _ptr(biasTensor),
+                                     _ptr(outputTensor), _ptr(ws), ws.numel(), _stream()))
+
+
+def conv2DBwd(inputTensor, filterTensor, gradTensor, filterGradTensor, inputGradTensor, descriptor, context=None,
+              engine=_lib.ENGINE_AUTO):
+    """dW (always) and dX (when the descriptor requires it); mirrors ``upstride::conv2DBwd``
+    (reference ``src/upstride.hpp:35-51``)."""
+    dev = Device.get(filterTensor.device)
+    context = context or dev.getContext()
+    _check_tensor(inputTensor, "input", shape=descriptor.getInputShape())
+    _check_tensor(filterTensor, "filter", inputTensor.dtype, descriptor.getFilterShape())
+    _check_tensor(gradTensor, "grad", inputTensor.dtype, descriptor.getOutputShape())
+    _check_tensor(filterGradTensor, "filterGrad", inputTensor.dtype, descriptor.getFilterShape())
+    need_dx = descriptor.isInputGradientRequired()
+    if need_dx:
+        if descriptor.isRealValuedInput():
+            raise RuntimeError("Input gradient required for type0 input tensor")   # std::logic_error in the reference
+        _check_tensor(inputGradTensor, "inputGrad", inputTensor.dtype, descriptor.getInputShape())
+    if inputTensor.numel() == 0:
+        filterGradTensor.zero_()     # reference src/conv2d.hpp:341-344
+        return
+    d = _conv_desc(descriptor, inputTensor.dtype, context, engine, require_input_grad=need_dx)
+    L = _lib.lib()
+    with dev.accessControl, torch.cuda.device(dev.index):
+        need = L.pcb_qconv2d_bwd_workspace_size(ctypes.byref(d))
+        ws = dev.requestWorkspace(need)
+        _lib.check(L.pcb_qconv2d_bwd(ctypes.byref(d), _ptr(inputTensor), _ptr(filterTensor), _ptr(gradTensor),
+                                     _ptr(filterGradTensor), _ptr(inputGradTensor) if need_dx else None,
+                                     _ptr(ws), ws.numel(), _stream()))
+
+
+def _dense_desc(descriptor, dtype, context, engine, has_bias=False, require_input_grad=False):
+    if descriptor.getAlgebra() != Algebra.QUATERNION:
+        raise _lib.BackendError(_lib.PCB_ERR_UNSUPPORTED, "only the quaternion algebra is implemented")
+    ishape = descriptor.getInputShape()
+    if ishape[0] % 4 != 0:
+        raise ValueError("leading input dimension must be a multiple of 4 (components stacked on the batch axis)")
+    if ishape[1] != descriptor.getInputChannels():
+        raise ValueError("input features mismatch: %d vs %d" % (ishape[1], descriptor.getInputChannels()))
+    d = _lib.DenseDesc()
+    d.dtype = _DTYPES[dtype]
+    d.batch = ishape[0] // 4
+    d.in_features = ishape[1]
+    d.out_features = descriptor.getOutputChannels()
+    d.filter_oi = int(descriptor.getFilterLayout() == FilterLayout.OI)
+    d.has_bias = int(has_bias)
+    d.require_input_grad = int(require_input_grad)
+    d.variant = context.variant()
+    d.engine = engine
+    return d
+
+
+def denseFwd(inputTensor, filterTensor, biasTensor, outputTensor, descriptor, context=None, engine=_lib.ENGINE_AUTO):
+    """Mirrors ``upstride::denseFwd`` (reference ``src/upstride.hpp:53-68``)."""
+    dev = Device.get(inputTensor.device)
+    context = context or dev.getContext()
+    _check_tensor(inputTensor, "input", shape=descriptor.getInputShape())
+    _check_tensor(filterTensor, "filter", inputTensor.dtype, descriptor.getFilterShape())
+    _check_tensor(outputTensor, "output", inputTensor.dtype, descriptor.getOutputShape())
+    if biasTensor is not None:
+        if not descriptor.isBiasUsed():
+            raise ValueError("Bias application is not configured for this scalar Dense operation")
+        _check_tensor(biasTensor, "bias", inputTensor.dtype, descriptor.getBiasShape())
+    if inputTensor.numel() == 0:
+        return
+    d = _dense_desc(descriptor, inputTensor.dtype, context, engine, has_bias=biasTensor is not None)
+    L = _lib.lib()
+    with dev.accessControl, torch.cuda.device(dev.index):
+        need = L.pcb_qdense_fwd_workspace_size(ctypes.byref(d))
+        ws = dev.requestWorkspace(need)
+        _lib.check(L.pcb_qdense_fwd(ctypes.byref(d), _ptr(inputTensor), _ptr(filterTensor), _ptr(biasTensor),
+                                    _ptr(outputTensor), _ptr(ws), ws.numel(), _stream()))
+
+
+def denseBwd(inputTensor, filterTensor, gradTensor, filterGradTensor, inputGradTensor, descriptor, context=None,
+             engine=_lib.ENGINE_AUTO):
+    """Mirrors ``upstride::denseBwd`` (reference ``src/upstride.hpp:70-86``). The filter gradient is written
+    input-major, ``[4, I, O]``, whatever the filter layout, as both reference backends do."""
+    dev = Device.get(inputTensor.device)
+    context = context or dev.getContext()
+    _check_tensor(inputTensor, "input", shape=descriptor.getInputShape())
+    _check_tensor(filterTensor, "filter", inputTensor.dtype, descriptor.getFilterShape())
+    _check_tensor(gradTensor, "grad", inputTensor.dtype, descriptor.getOutputShape())
+    if filterGradTensor.numel() != filterTensor.numel():
+        raise ValueError("filterGrad size mismatch")
+    _check_tensor(filterGradTensor, "filterGrad", inputTensor.dtype)
+    need_dx = descriptor.isInputGradientRequired()
+    if need_dx:
+        _check_tensor(inputGradTensor, "inputGrad", inputTensor.dtype, descriptor.getInputShape())
+    if inputTensor.numel() == 0:
+        filterGradTensor.zero_()
+        return
+    d = _dense_desc(descriptor, inputTensor.dtype, context, engine, require_input_grad=need_dx)
+    L = _lib.lib()
+    with dev.accessControl, torch.cuda.device(dev.index):
+        need = L.pcb_qdense_bwd_workspace_size(ctypes.byref(d))
+        ws = dev.requestWorkspace(need)
+        _lib.check(L.pcb_qdense_bwd(ctypes.byref(d), _ptr(inputTensor), _ptr(filterTensor), _ptr(gradTensor),
+                                    _ptr(filterGradTensor), _ptr(inputGradTensor) if need_dx else None,
+                                    _ptr(ws), ws.numel(), _stream()))

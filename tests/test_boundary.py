@@ -1,0 +1,119 @@
+"""CPU tests of the drop-in boundary: the C-ABI library loads and exports every declared symbol, the
+descriptors reproduce the reference's geometry rules and error behaviour, and the policy context reads the
+reference's environment variables."""
+import ctypes
+import json
+import os
+import re
+
+import pytest
+
+import phoenix_core_b200 as pcb
+from phoenix_core_b200 import _lib
+from phoenix_core_b200.context import Context, ConvFp16ComputePolicy
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+GOLDEN = os.path.join(os.path.dirname(__file__), "golden", "reference_kats.json")
+
+
+@pytest.fixture(scope="module")
+def built_lib():
+    from phoenix_core_b200.csrc import build
+    build.build()
+    return _lib.lib()
+
+
+def test_library_exports_every_declared_symbol(built_lib):
+    header = open(os.path.join(ROOT, "include", "phoenix_core_b200.h")).read()
+    declared = set(re.findall(r"\b(pcb_[a-z0-9_]+)\s*\(", header))
+    assert declared, "no declarations found"
+    assert declared == set(_lib.SYMBOLS), declared ^ set(_lib.SYMBOLS)
+    raw = ctypes.CDLL(_lib.LIB_PATH)
+    for name in declared:
+        getattr(raw, name)
+
+
+def test_status_strings_and_version(built_lib):
+    assert b"sm_100a" in built_lib.pcb_version()
+    assert built_lib.pcb_status_string(0) == b"ok"
+    assert built_lib.pcb_status_string(_lib.PCB_ERR_UNSUPPORTED) == b"unsupported configuration"
+
+
+def test_c_abi_geometry_and_validation_without_gpu(built_lib):
+    d = _lib.ConvDesc(dtype=0, n=8, ci=16, co=16, h=32, w=32, kh=3, kw=3, stride_h=1, stride_w=1, dilation_h=1,
+                      dilation_w=1, pad_top=1, pad_left=1, pad_bottom=1, pad_right=1, groups=1)
+    oh, ow = ctypes.c_int32(), ctypes.c_int32()
+    assert built_lib.pcb_conv2d_output_size(ctypes.byref(d), ctypes.byref(oh), ctypes.byref(ow)) == 0
+    assert (oh.value, ow.value) == (32, 32)
+    d.groups = 2
+    assert built_lib.pcb_conv2d_output_size(ctypes.byref(d), None, None) == _lib.PCB_ERR_UNSUPPORTED
+    assert b"group" in built_lib.pcb_last_error_message()
+    d.groups, d.kh = 1, 0
+    assert built_lib.pcb_conv2d_output_size(ctypes.byref(d), None, None) == _lib.PCB_ERR_INVALID_ARGUMENT
+    # fp16 backward-filter needs fp32 scratch; fp32 forward needs only the status header
+    d.kh = 3
+    assert built_lib.pcb_qconv2d_fwd_workspace_size(ctypes.byref(d)) == 256
+    d.dtype = _lib.PCB_F16
+    assert built_lib.pcb_qconv2d_bwd_workspace_size(ctypes.byref(d)) == 256 + 4 * 16 * 16 * 9 * 4
+    # kernel-family selection: pointwise fp16 with aligned channel counts goes to the tensor cores
+    p = _lib.ConvDesc(dtype=_lib.PCB_F16, n=64, ci=128, co=256, h=56, w=56, kh=1, kw=1, stride_h=1, stride_w=1,
+                      dilation_h=1, dilation_w=1, groups=1)
+    for pass_ in range(3):
+        assert built_lib.pcb_qconv2d_engine_for(ctypes.byref(p), pass_) == _lib.ENGINE_TENSOR
+    p.dtype = _lib.PCB_F32
+    assert built_lib.pcb_qconv2d_engine_for(ctypes.byref(p), 0) == _lib.ENGINE_SIMT
+    p.engine = _lib.ENGINE_TENSOR
+    assert built_lib.pcb_qconv2d_engine_for(ctypes.byref(p), 0) == _lib.PCB_ERR_UNSUPPORTED
+
+
+def test_reference_same_padding_descriptor():
+    with open(GOLDEN) as f:
+        (case,) = [c for c in json.load(f)["cases"] if c["op"] == "output_shape"]
+    desc = pcb.Conv2DFwdDescriptor(case["x_shape"], case["w_shape"], case["stride"], case["dilation"], pcb.Padding.SAME,
+                                   (0, 0), 1, pcb.Algebra.QUATERNION, pcb.DataFormat.NHWC, pcb.FilterLayout.OHWI, False)
+    assert desc.getOutputShape() == tuple(case["y_shape"])
+
+
+def test_descriptor_shape_checks_and_padding():
+    q, nchw, oihw = pcb.Algebra.QUATERNION, pcb.DataFormat.NCHW, pcb.FilterLayout.OIHW
+    with pytest.raises(ValueError, match="Four-dimensional input"):
+        pcb.Conv2DFwdDescriptor((4, 3, 8), (4, 2, 3, 3, 3), 1, 1, pcb.Padding.VALID, (), 1, q, nchw, oihw, False)
+    with pytest.raises(ValueError, match="Five-dimensional filter"):
+        pcb.Conv2DFwdDescriptor((4, 3, 8, 8), (2, 3, 3, 3), 1, 1, pcb.Padding.VALID, (), 1, q, nchw, oihw, False)
+    with pytest.raises(ValueError, match="First filter dimension mismatch"):
+        pcb.Conv2DFwdDescriptor((4, 3, 8, 8), (2, 2, 3, 3, 3), 1, 1, pcb.Padding.VALID, (), 1, q, nchw, oihw, False)
+    d = pcb.Conv2DFwdDescriptor((4 * 2, 3, 224, 224), (4, 16, 3, 7, 7), 2, 1, pcb.Padding.SAME, (), 1, q, nchw, oihw, True)
+    assert d.getPaddingBefore() == (2, 2) and d.getPaddingAfter() == (3, 3)      # the extra pixel goes after
+    assert d.getOutputShape() == (8, 16, 112, 112)
+    assert d.getBiasShape() == (4, 16)
+    r = pcb.Conv2DFwdDescriptor((2, 3, 9, 9), (4, 5, 3, 3, 3), 1, 1, pcb.Padding.VALID, (), 1, q, nchw, oihw, False, True)
+    assert r.getOutputShape() == (8, 5, 7, 7)                                    # real-valued input: batch x 4
+    e = pcb.Conv2DBwdDescriptor((4, 3, 9, 8), (4, 5, 3, 3, 3), (2, 1), 1, pcb.Padding.EXPLICIT, (1, 0, 2, 1), 1, q, nchw, oihw)
+    assert e.getPaddingBefore() == (1, 0) and e.getPaddingAfter() == (2, 1)
+    assert e.getOutputShape() == (4, 5, 5, 7) and e.isInputGradientRequired()
+
+
+def test_dense_descriptor():
+    d = pcb.DenseFwdDescriptor((4 * 256, 512), (4, 512, 250), pcb.Algebra.QUATERNION, pcb.FilterLayout.IO, True)
+    assert d.getOutputShape() == (1024, 250) and d.getBiasShape() == (4, 250)
+    o = pcb.DenseBwdDescriptor((8, 6), (4, 3, 6), pcb.Algebra.QUATERNION, pcb.FilterLayout.OI, False)
+    assert o.getOutputChannels() == 3 and o.getInputChannels() == 6 and not o.isInputGradientRequired()
+
+
+def test_context_reads_reference_environment():
+    c = Context({})
+    assert c.preferSpeedToMemory() and c.conv_fp16_policy == ConvFp16ComputePolicy.FULL_32
+    assert c.variant() == _lib.VARIANT_8_PRODUCT                # the reference's default formulation
+    c = Context({"UPSTRIDE_MEMORY_OPTIMIZED": "1", "UPSTRIDE_CONV_FP16_POLICY": "backward32"})
+    assert not c.preferSpeedToMemory() and c.variant() == _lib.VARIANT_16_PRODUCT
+    assert c.isFp16ConvForwardAllowed() and not c.isFp16ConvBackwardAllowed()
+    c = Context({"UPSTRIDE_CONV_FP16_POLICY": "full16"})
+    assert c.isFp16ConvForwardAllowed() and c.isFp16ConvBackwardAllowed()
+
+
+def test_product_path_does_not_touch_the_oracle():
+    for dirpath, _, files in os.walk(os.path.join(ROOT, "phoenix_core_b200")):
+        for f in files:
+            if f.endswith((".py", ".cu", ".cuh", ".hpp", ".h")):
+                text = open(os.path.join(dirpath, f)).read()
+                assert "oracle" not in text.replace("the CPU oracle", ""), os.path.join(dirpath, f)

@@ -1,0 +1,212 @@
+"""GPU parity tests: the CUDA path (through the C ABI) against the CPU oracle on identical seeded inputs.
+
+Tolerances (max|got-ref| / max|ref| per output tensor): 1e-5 for fp32, 2e-2 for fp16 / bf16, the oracle
+running in fp32 on inputs already rounded to the storage type.
+"""
+import json
+import os
+
+import numpy as np
+import pytest
+import torch
+
+from helpers import normal, rel_err, uniform
+
+pytestmark = pytest.mark.gpu
+
+GOLDEN = os.path.join(os.path.dirname(__file__), "golden", "reference_kats.json")
+
+# n, ci, co, h, w, kh, kw, stride, pad(t,l,b,r)
+CONV_SHAPES = [
+    (2, 3, 5, 7, 6, 3, 3, (1, 1), (1, 1, 1, 1)),
+    (1, 4, 2, 9, 8, 3, 3, (2, 2), (0, 0, 1, 1)),         # asymmetric SAME-style padding, stride 2
+    (3, 2, 3, 5, 5, 1, 1, (1, 1), (0, 0, 0, 0)),
+    (2, 2, 4, 8, 7, 1, 1, (2, 2), (0, 0, 0, 0)),         # 1x1 stride 2
+    (1, 3, 2, 10, 9, 5, 3, (2, 1), (2, 1, 2, 1)),        # ragged everything
+    (2, 16, 16, 16, 16, 3, 3, (1, 1), (1, 1, 1, 1)),     # reduced copy of the 16->16 3x3 configuration
+    (1, 3, 16, 20, 20, 7, 7, (2, 2), (2, 2, 3, 3)),      # stem-like 7x7 stride 2 with TF SAME padding
+    (2, 40, 24, 6, 5, 1, 1, (1, 1), (0, 0, 0, 0)),
+]
+
+
+@pytest.fixture(scope="module")
+def gpu():
+    if not torch.cuda.is_available():
+        pytest.skip("no CUDA device")
+    import gpu_util
+    return gpu_util
+
+
+def _check(got, ref, dtype, gpu, what):
+    assert np.all(np.isfinite(got)), what + ": output not fully written"
+    err = rel_err(got, ref)
+    assert err <= gpu.TOL[dtype], "%s: relative error %.3e > %.1e" % (what, err, gpu.TOL[dtype])
+
+
+def test_reference_kats_on_gpu(gpu, oracle):
+    """The reference's own quaternion known-answer vectors (tests/tests.cpp:292-369), exact."""
+    with open(GOLDEN) as f:
+        cases = [c for c in json.load(f)["cases"] if c["op"] == "conv2d_fwd" and c["algebra"] == "quaternion"]
+    for case in cases:
+        x = (np.full(case["x_shape"], case["x_fill"], np.float32) if "x_fill" in case
+             else np.asarray(case["x"], np.float32).reshape(case["x_shape"]))
+        w = (np.full(case["w_shape"], case["w_fill"], np.float32) if "w_fill" in case
+             else np.asarray(case["w"], np.float32).reshape(case["w_shape"]))
+        want = np.asarray(case["y"], np.float32).reshape(case["y_shape"])
+        variants = ["16p"] if case["real_input"] else ["16p", "8p"]
+        for variant in variants:
+            got = gpu.run_conv_fwd(x, w, None, tuple(case["stride"]), (0, 0, 0, 0), "f32", variant, "auto",
+                                   case["real_input"])
+            assert np.array_equal(got, want), (case["name"], variant)
+
+
+@pytest.mark.parametrize("shape", CONV_SHAPES)
+@pytest.mark.parametrize("dtype", ["f32", "f16", "bf16"])
+@pytest.mark.parametrize("variant", ["16p", "8p"])
+def test_conv_fwd_bwd_vs_oracle(gpu, oracle, shape, dtype, variant):
+    n, ci, co, h, w_, kh, kw, stride, pad = shape
+    x = gpu.rounded(uniform(1, (4 * n, ci, h, w_)), dtype)
+    w = gpu.rounded(uniform(2, (4, co, ci, kh, kw)), dtype)
+    b = gpu.rounded(uniform(3, (4, co)), dtype)
+    ov = oracle.VARIANT_16P if variant == "16p" else oracle.VARIANT_8P
+    ref = oracle.conv2d_fwd(x, w, b, stride, (1, 1), pad, oracle.QUATERNION, ov)
+    got = gpu.run_conv_fwd(x, w, b, stride, pad, dtype, variant, "auto")
+    _check(got, ref, dtype, gpu, "y")
+    nob = gpu.run_conv_fwd(x, w, None, stride, pad, dtype, variant, "auto")
+    _check(nob, oracle.conv2d_fwd(x, w, None, stride, (1, 1), pad, oracle.QUATERNION, ov), dtype, gpu, "y (no bias)")
+
+    dy = gpu.rounded(normal(4, ref.shape), dtype)
+    rdw, rdx = oracle.conv2d_bwd(x, w, dy, stride, (1, 1), pad, oracle.QUATERNION, ov, True)
+    dw, dx = gpu.run_conv_bwd(x, w, dy, stride, pad, dtype, variant, "auto", True)
+    _check(dw, rdw, dtype, gpu, "dw")
+    _check(dx, rdx, dtype, gpu, "dx")
+    dw2, none = gpu.run_conv_bwd(x, w, dy, stride, pad, dtype, variant, "auto", False)
+    assert none is None
+    _check(dw2, rdw, dtype, gpu, "dw (no input gradient)")
+
+
+# pointwise shapes the tensor-core (tcgen05) kernels take: n, ci, co, h, w
+TENSOR_SHAPES = [
+    (1, 16, 32, 8, 8),        # one tile, K = 64: a single pipeline stage
+    (2, 32, 32, 8, 16),       # N = 256: two column tiles
+    (3, 24, 40, 4, 6),        # ragged M (160), N (72) and K (96) tiles; chunks cross no image boundary
+    (2, 128, 64, 16, 8),      # K = 512: the ring wraps around (8 iterations over 3 stages)
+    (1, 64, 256, 12, 12),     # M = 1024: eight row tiles
+    (4, 8, 8, 4, 2),          # the smallest legal sizes
+]
+
+
+@pytest.mark.parametrize("shape", TENSOR_SHAPES)
+@pytest.mark.parametrize("dtype", ["f16", "bf16"])
+def test_pointwise_tensor_core_vs_oracle(gpu, oracle, shape, dtype):
+    from phoenix_core_b200 import _lib
+    n, ci, co, h, w_ = shape
+    x = gpu.rounded(normal(11, (4 * n, ci, h, w_)), dtype)
+    w = gpu.rounded(normal(12, (4, co, ci, 1, 1), std=(2.0 / (4 * ci)) ** 0.5), dtype)
+    b = gpu.rounded(uniform(13, (4, co)), dtype)
+    pad, stride = (0, 0, 0, 0), (1, 1)
+    ref = oracle.conv2d_fwd(x, w, b, stride, (1, 1), pad)
+    got = gpu.run_conv_fwd(x, w, b, stride, pad, dtype, "16p", "tensor")
+    _check(got, ref, dtype, gpu, "y")
+    dy = gpu.rounded(normal(14, ref.shape), dtype)
+    rdw, rdx = oracle.conv2d_bwd(x, w, dy, stride, (1, 1), pad)
+    dw, dx = gpu.run_conv_bwd(x, w, dy, stride, pad, dtype, "16p", "tensor", True)
+    _check(dx, rdx, dtype, gpu, "dx")
+    _check(dw, rdw, dtype, gpu, "dw")
+    # and the two kernel families agree with each other far inside the tolerance
+    simt = gpu.run_conv_fwd(x, w, b, stride, pad, dtype, "16p", "simt")
+    assert rel_err(got, simt) <= 4e-3 if dtype == "f16" else 2e-2
+
+
+def test_tensor_engine_refuses_unsupported_shapes(gpu):
+    from phoenix_core_b200 import _lib
+    x = uniform(1, (4, 3, 5, 5))
+    w = uniform(2, (4, 2, 3, 3, 3))
+    with pytest.raises(_lib.BackendError) as e:
+        gpu.run_conv_fwd(x, w, None, (1, 1), (1, 1, 1, 1), "f16", "16p", "tensor")
+    assert e.value.status == _lib.PCB_ERR_UNSUPPORTED
+
+
+def test_real_valued_input(gpu, oracle):
+    x = uniform(21, (3, 4, 9, 7))
+    w = uniform(22, (4, 6, 4, 3, 3))
+    ref = oracle.conv2d_fwd(x, w, None, (2, 2), (1, 1), (1, 1, 1, 1), real_input=True)
+    got = gpu.run_conv_fwd(x, w, None, (2, 2), (1, 1, 1, 1), "f32", "8p", "auto", real_input=True)
+    _check(got, ref, "f32", gpu, "y (real input)")
+
+
+def test_empty_batch(gpu):
+    import phoenix_core_b200 as pcb
+    fwd, bwd = gpu.conv_descriptors((0, 3, 5, 5), (4, 2, 3, 3, 3), (1, 1), (1, 1, 1, 1), False, True)
+    x = torch.zeros((0, 3, 5, 5), device="cuda")
+    w = torch.ones((4, 2, 3, 3, 3), device="cuda")
+    y = torch.zeros(fwd.getOutputShape(), device="cuda")
+    pcb.conv2DFwd(x, w, None, y, fwd)
+    dw = torch.ones_like(w)
+    pcb.conv2DBwd(x, w, y, dw, x.clone(), bwd)
+    assert float(dw.abs().sum()) == 0.0
+
+
+DENSE_SHAPES = [(3, 5, 7), (8, 16, 4), (1, 1, 1), (32, 64, 48), (17, 130, 70)]
+
+
+@pytest.mark.parametrize("shape", DENSE_SHAPES)
+@pytest.mark.parametrize("dtype", ["f32", "f16", "bf16"])
+@pytest.mark.parametrize("variant", ["16p", "8p"])
+@pytest.mark.parametrize("oi", [False, True])
+def test_dense_fwd_bwd_vs_oracle(gpu, oracle, shape, dtype, variant, oi):
+    b_, i, o = shape
+    x = gpu.rounded(normal(31, (4 * b_, i)), dtype)
+    w = gpu.rounded(normal(32, (4, o, i) if oi else (4, i, o), std=(2.0 / (4 * i)) ** 0.5), dtype)
+    bias = gpu.rounded(uniform(33, (4, o)), dtype)
+    ov = oracle.VARIANT_16P if variant == "16p" else oracle.VARIANT_8P
+    ref = oracle.dense_fwd(x, w, bias, oi, oracle.QUATERNION, ov)
+    got = gpu.run_dense_fwd(x, w, bias, oi, dtype, variant, "auto")
+    _check(got, ref, dtype, gpu, "y")
+    dy = gpu.rounded(normal(34, ref.shape), dtype)
+    rdw, rdx = oracle.dense_bwd(x, w, dy, oi, oracle.QUATERNION, ov, True)
+    dw, dx = gpu.run_dense_bwd(x, w, dy, oi, dtype, variant, "auto", True)
+    _check(dw, rdw, dtype, gpu, "dw")
+    _check(dx, rdx, dtype, gpu, "dx")
+
+
+def test_baseline_config1_conv3x3_fp32(gpu, oracle):
+    """Single quaternion conv2d forward, fp32: N=8, 16->16 channels, 32x32, 3x3, stride 1, pad 1, U[-1,1]."""
+    x = uniform(101, (4 * 8, 16, 32, 32))
+    w = uniform(102, (4, 16, 16, 3, 3))
+    for variant, ov in (("16p", oracle.VARIANT_16P), ("8p", oracle.VARIANT_8P)):
+        ref = oracle.conv2d_fwd(x, w, None, (1, 1), (1, 1), (1, 1, 1, 1), oracle.QUATERNION, ov)
+        got = gpu.run_conv_fwd(x, w, None, (1, 1), (1, 1, 1, 1), "f32", variant, "auto")
+        _check(got, ref, "f32", gpu, "config 1 " + variant)
+
+
+def test_baseline_config2_dense_fp32(gpu, oracle):
+    """Quaternion dense fwd+bwd, fp32: batch 256, 512 -> 512, He-normal weights, N(0,1) upstream gradient."""
+    x = normal(201, (4 * 256, 512))
+    w = normal(202, (4, 512, 512), std=(2.0 / (4 * 512)) ** 0.5)
+    bias = np.zeros((4, 512), np.float32)
+    dy = normal(203, (4 * 256, 512))
+    for variant, ov in (("16p", oracle.VARIANT_16P), ("8p", oracle.VARIANT_8P)):
+        _check(gpu.run_dense_fwd(x, w, bias, False, "f32", variant, "auto"),
+               oracle.dense_fwd(x, w, bias, False, oracle.QUATERNION, ov), "f32", gpu, "config 2 y " + variant)
+        rdw, rdx = oracle.dense_bwd(x, w, dy, False, oracle.QUATERNION, ov, True)
+        dw, dx = gpu.run_dense_bwd(x, w, dy, False, "f32", variant, "auto", True)
+        _check(dw, rdw, "f32", gpu, "config 2 dw " + variant)
+        _check(dx, rdx, "f32", gpu, "config 2 dx " + variant)
+
+
+def test_baseline_config3_pointwise_fp16_reduced_batch(gpu, oracle):
+    """Pointwise 1x1 conv fwd+bwd, fp16 in/out, 128 -> 256 channels, 56x56 (batch reduced from 64 to 1 so that
+    the oracle finishes in seconds), both formulations; the 16-product one runs on the tensor cores."""
+    from phoenix_core_b200 import _lib
+    x = gpu.rounded(normal(301, (4 * 1, 128, 56, 56)), "f16")
+    w = gpu.rounded(normal(302, (4, 256, 128, 1, 1), std=(2.0 / (4 * 128)) ** 0.5), "f16")
+    pad, stride = (0, 0, 0, 0), (1, 1)
+    for variant, ov in (("16p", oracle.VARIANT_16P), ("8p", oracle.VARIANT_8P)):
+        ref = oracle.conv2d_fwd(x, w, None, stride, (1, 1), pad, oracle.QUATERNION, ov)
+        _check(gpu.run_conv_fwd(x, w, None, stride, pad, "f16", variant, "auto"), ref, "f16", gpu, "config 3 y " + variant)
+        dy = gpu.rounded(normal(303, ref.shape), "f16")
+        rdw, rdx = oracle.conv2d_bwd(x, w, dy, stride, (1, 1), pad, oracle.QUATERNION, ov, True)
+        dw, dx = gpu.run_conv_bwd(x, w, dy, stride, pad, "f16", variant, "auto", True)
+        _check(dw, rdw, "f16", gpu, "config 3 dw " + variant)
+        _check(dx, rdx, "f16", gpu, "config 3 dx " + variant)

@@ -163,3 +163,29 @@ def test_dense_matches_float64(oracle, b, i, o, variant, oi):
     assert dw.shape == (4, i, o)        # always input-major, as both reference backends emit it
     assert rel_err(dw, rdw) < 2e-6
     assert rel_err(dx, rdx) < 2e-6
+
+
+@pytest.mark.parametrize("variant8", [False, True])
+def test_library_orchestration_agrees_with_oracle(oracle, variant8):
+    """The torch-CPU (oneDNN) orchestration used as timed CPU baseline computes what the C oracle computes."""
+    import torch
+    from oracle import ref_orchestration as ro
+    x = uniform(41, (4 * 2, 6, 9, 8))
+    w = uniform(42, (4, 5, 6, 3, 3))
+    b = uniform(43, (4, 5))
+    stride, pad = (2, 2), (0, 0, 1, 1)
+    v = 1 if variant8 else 0
+    y = ro.conv2d_fwd(torch.from_numpy(x), torch.from_numpy(w), torch.from_numpy(b), stride, pad, variant8).numpy()
+    ref = oracle.conv2d_fwd(x, w, b, stride, (1, 1), pad, oracle.QUATERNION, v)
+    assert rel_err(y, ref) < 1e-5
+    dy = normal(44, ref.shape)
+    dw, dx = ro.conv2d_bwd(torch.from_numpy(x), torch.from_numpy(w), torch.from_numpy(dy), stride, pad, variant8)
+    rdw, rdx = oracle.conv2d_bwd(x, w, dy, stride, (1, 1), pad, oracle.QUATERNION, v)
+    assert rel_err(dw.numpy(), rdw) < 1e-5 and rel_err(dx.numpy(), rdx) < 1e-5
+    xd, wd, bd = normal(45, (4 * 7, 12)), normal(46, (4, 12, 9)), uniform(47, (4, 9))
+    yd = ro.dense_fwd(torch.from_numpy(xd), torch.from_numpy(wd), torch.from_numpy(bd), variant8).numpy()
+    assert rel_err(yd, oracle.dense_fwd(xd, wd, bd, False, oracle.QUATERNION, v)) < 1e-5
+    gd = normal(48, yd.shape)
+    ddw, ddx = ro.dense_bwd(torch.from_numpy(xd), torch.from_numpy(wd), torch.from_numpy(gd), variant8)
+    rddw, rddx = oracle.dense_bwd(xd, wd, gd, False, oracle.QUATERNION, v)
+    assert rel_err(ddw.numpy(), rddw) < 1e-5 and rel_err(ddx.numpy(), rddx) < 1e-5
