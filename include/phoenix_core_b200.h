@@ -125,6 +125,22 @@ int pcb_qconv2d_bwd_data(const pcb_conv2d_desc* desc, const void* w, const void*
 int pcb_qconv2d_bwd_filter(const pcb_conv2d_desc* desc, const void* x, const void* dy, void* dw,
                            void* workspace, size_t workspace_bytes, void* stream);
 
+/* Filter gradient for callers that must not allocate device memory and have no workspace to lend.
+ * (No counterpart in the reference: its operators always draw temporaries from Allocator::mallocTemp.)
+ * Who needs it: hosts that are forbidden to call cudaMalloc once running -- e.g. a plugin inside a framework
+ * that has given the whole device heap to its own arena, or a deployment whose memory plan is fixed at
+ * start-up -- and that cannot carve a workspace out of that plan either. The split-K accumulator that the
+ * fp16 / bf16 filter gradient needs is a fixed 16 MiB array inside the library image (held by every GPU that
+ * loads the library until the process exits), so the call takes inputs and the output only.
+ *   - Limit: 4*co*ci*kh*kw <= 4,194,304 elements; larger problems return PCB_ERR_TOO_LARGE.
+ *   - Runs the CUDA-core kernels (the `engine` field is ignored); same arithmetic as
+ *     pcb_qconv2d_bwd_filter with PCB_ENGINE_SIMT. Calls no cudaMalloc / cudaFree or allocating routine.
+ *   - The first call on each device resolves the array's device address (cudaGetSymbolAddress); make that
+ *     first call before any stream capture.
+ *   - All calls on a device share the array. Each call zeroes what it uses, so results do not depend on
+ *     earlier calls, but two calls that overlap on the GPU (different streams) race: serialise them. */
+int pcb_qconv2d_bwd_filter_noalloc(const pcb_conv2d_desc* desc, const void* x, const void* dy, void* dw, void* stream);
+
 /* Quaternion Dense forward / backward.
  * Replace UpstrideDenseFunctor::operator() (src/dense.hpp:64-181) and UpstrideDenseGradFunctor
  * (src/dense.hpp:238-378) with the cuBLAS calls of src/backend/cudnn/dense.hpp:102-133, :181-216 behind

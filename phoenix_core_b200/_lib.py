@@ -54,6 +54,7 @@ SYMBOLS = {
     "pcb_qconv2d_bwd": (_i, [_cd, _vp, _vp, _vp, _vp, _vp, _vp, _sz, _vp]),
     "pcb_qconv2d_bwd_data": (_i, [_cd, _vp, _vp, _vp, _vp, _sz, _vp]),
     "pcb_qconv2d_bwd_filter": (_i, [_cd, _vp, _vp, _vp, _vp, _sz, _vp]),
+    "pcb_qconv2d_bwd_filter_noalloc": (_i, [_cd, _vp, _vp, _vp, _vp]),
     "pcb_qdense_fwd": (_i, [_dd, _vp, _vp, _vp, _vp, _vp, _sz, _vp]),
     "pcb_qdense_bwd": (_i, [_dd, _vp, _vp, _vp, _vp, _vp, _vp, _sz, _vp]),
     "pcb_qconv2d_engine_for": (_i, [_cd, _i]),

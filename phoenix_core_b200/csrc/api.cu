@@ -202,6 +202,24 @@ int pcb_qconv2d_bwd_filter(const pcb_conv2d_desc* desc, const void* x, const voi
     return run_pass(PASS_BWD_FILTER, desc->dtype, desc->variant, desc->engine, g, dy, x, nullptr, dw, workspace, workspace_bytes_, (cudaStream_t)stream);
 }
 
+int pcb_qconv2d_bwd_filter_noalloc(const pcb_conv2d_desc* desc, const void* x, const void* dy, void* dw, void* stream) {
+    Geom g;
+    int rc = conv_geom(desc, g);
+    if (rc != PCB_OK) return rc;
+    if (!dw) { set_error("null tensor pointer"); return PCB_ERR_INVALID_ARGUMENT; }
+    if ((size_t)4 * g.Co * g.Ci * g.KH * g.KW > simt_static_scratch_capacity()) {
+        set_error("filter gradient of %zu elements exceeds the built-in scratch of %zu elements",
+                  (size_t)4 * g.Co * g.Ci * g.KH * g.KW, simt_static_scratch_capacity());
+        return PCB_ERR_TOO_LARGE;
+    }
+    if (g.Nb == 0) {
+        PCB_CUDA_TRY(cudaMemsetAsync(dw, 0, (size_t)4 * g.Co * g.Ci * g.KH * g.KW * dtype_size(desc->dtype), (cudaStream_t)stream));
+        return PCB_OK;
+    }
+    if (!x || !dy) { set_error("null tensor pointer"); return PCB_ERR_INVALID_ARGUMENT; }
+    return simt_bwd_filter_static(desc->dtype, desc->variant, g, dy, x, dw, (cudaStream_t)stream);
+}
+
 int pcb_qconv2d_bwd(const pcb_conv2d_desc* desc, const void* x, const void* w, const void* dy, void* dw, void* dx,
                     void* workspace, size_t workspace_bytes_, void* stream) {
     int rc = pcb_qconv2d_bwd_filter(desc, x, dy, dw, workspace, workspace_bytes_, stream);

@@ -73,5 +73,8 @@ void set_error(const char* fmt, ...);
 int simt_launch(Pass pass, int dtype, int variant, const Geom& g, const void* a, const void* b, const void* bias,
                 void* out, float* scratch, cudaStream_t stream);
 size_t simt_scratch_bytes(Pass pass, int dtype, int variant, const Geom& g);
+// Backward-filter whose split-K accumulator is a fixed array inside the library (no workspace, no allocation).
+int simt_bwd_filter_static(int dtype, int variant, const Geom& g, const void* dy, const void* x, void* dw, cudaStream_t stream);
+size_t simt_static_scratch_capacity();
 
 }  // namespace pcb

@@ -18,6 +18,8 @@
 // Index decoding is table driven: per CTA one table for its M rows and one for its N columns (built
 // once), and per K step a small table for the K slice, so the inner gather is two shared-memory reads,
 // a bounds test and one global load per element.
+#include <mutex>
+
 #include "common.cuh"
 
 namespace pcb {
@@ -599,6 +601,55 @@ int simt_launch(Pass pass, int dtype, int variant, const Geom& g, const void* a,
     }
     set_error("unknown dtype %d", dtype);
     return PCB_ERR_INVALID_ARGUMENT;
+}
+
+// ---------------------------------------------------------------------------------------------------
+// Backward-filter without any caller- or library-allocated scratch.
+//
+// Some hosts of this library may not allocate device memory at all once they are running: a plugin that
+// lives inside a framework which has handed the whole device heap to its own arena and forbids
+// cudaMalloc from operator callbacks, or a deployment whose memory plan is frozen at start-up. For them
+// the split-K accumulator of the filter gradient (needed when the tensors are fp16 / bf16) lives in a
+// fixed array in the library's own device image instead of a workspace. The array costs
+// STATIC_SCRATCH_FLOATS * 4 bytes on every GPU that loads the library, for the life of the process.
+//
+// The array's name is only a host-side handle; the device address is looked up once per device with
+// cudaGetSymbolAddress (with that device current) and cached. All calls on a device share the one
+// array and it keeps whatever the previous call left, so every call zeroes the part it accumulates
+// into first; two calls that overlap on the GPU (different streams) would race on it.
+// ---------------------------------------------------------------------------------------------------
+constexpr size_t STATIC_SCRATCH_FLOATS = size_t(4) << 20;     // 4 Mi floats = 16 MiB: up to 4*Co*Ci*kh*kw = 4,194,304
+static __device__ __align__(256) float g_static_scratch[STATIC_SCRATCH_FLOATS];
+
+namespace {
+constexpr int MAX_DEVICES = 64;
+float* g_static_scratch_addr[MAX_DEVICES] = {};
+std::mutex g_static_scratch_mutex;
+}  // namespace
+
+size_t simt_static_scratch_capacity() { return STATIC_SCRATCH_FLOATS; }
+
+int simt_bwd_filter_static(int dtype, int variant, const Geom& g, const void* dy, const void* x, void* dw, cudaStream_t stream) {
+    const size_t need = filter_numel(g);
+    if (need > STATIC_SCRATCH_FLOATS) {
+        set_error("filter gradient of %zu elements exceeds the built-in scratch of %zu elements", need, (size_t)STATIC_SCRATCH_FLOATS);
+        return PCB_ERR_TOO_LARGE;
+    }
+    int dev = -1;
+    PCB_CUDA_TRY(cudaGetDevice(&dev));
+    if (dev < 0 || dev >= MAX_DEVICES) { set_error("device index %d out of range", dev); return PCB_ERR_INVALID_ARGUMENT; }
+    float* scratch = nullptr;
+    {
+        std::lock_guard<std::mutex> lock(g_static_scratch_mutex);
+        if (g_static_scratch_addr[dev] == nullptr) {
+            // first call on this device: resolve the device address of the array (do this before any stream capture)
+            float* addr = nullptr;
+            PCB_CUDA_TRY(cudaGetSymbolAddress(reinterpret_cast<void**>(&addr), g_static_scratch));
+            g_static_scratch_addr[dev] = addr;
+        }
+        scratch = g_static_scratch_addr[dev];
+    }
+    return simt_launch(PASS_BWD_FILTER, dtype, variant, g, dy, x, nullptr, dw, scratch, stream);
 }
 
 }  // namespace pcb
