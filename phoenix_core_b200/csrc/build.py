@@ -8,7 +8,7 @@ import sys
 
 HERE = os.path.dirname(os.path.abspath(__file__))
 LIB = os.path.join(HERE, "libphoenix_core_b200.so")
-SOURCES = ["api.cu", "simt_qgemm.cu", "tensor_path.cu"]
+SOURCES = ["api.cu", "simt_qgemm.cu", "tensor_path.cu", "pointwise_tc.cu"]
 HEADERS = ["common.cuh", "tensor_path.cuh", "umma.cuh", os.path.join("..", "..", "include", "phoenix_core_b200.h")]
 NVCC_FLAGS = [
     "-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "-std=c++17",
@@ -32,7 +32,7 @@ def build(force=False, verbose=False):
     if not force and not _stale():
         return LIB
     nvcc = os.environ.get("NVCC", "nvcc")
-    cmd = [nvcc] + NVCC_FLAGS + (["-Xptxas", "-v"] if verbose else []) + ["-o", LIB] + SOURCES + ["-lcuda"]
+    cmd = [nvcc] + NVCC_FLAGS + (["-Xptxas", "-v"] if verbose else []) + ["-o", LIB] + SOURCES
     res = subprocess.run(cmd, cwd=HERE, capture_output=True, text=True)
     if res.returncode != 0:
         sys.stderr.write(res.stdout + res.stderr)

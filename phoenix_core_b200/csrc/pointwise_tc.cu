@@ -1,0 +1,334 @@
+// Persistent TMA-fed tcgen05 kernel for the pointwise (1x1, stride 1) quaternion convolution, forward and
+// backward-data, for layers with >= 96 output rows per component (the channel tile is 128 wide).
+//
+// The 4x4 signed weight block is not materialised at all here: the four output components live in four
+// TMEM accumulators and each of the 16 (input component, output component) pairs is one tcgen05.mma whose
+// A operand is the raw weight tile w[l^d] and whose sign s(l,d) is the instruction's negate-A flag:
+//
+//   forward        D_d[co, px] += s(l,d) * w[l^d][co, ci-slice] * x_l [ci-slice, px]        d, l = 0..3
+//   backward-data  D_l[ci, px] += s(l,d) * w[l^d][co-slice, ci]^T * dy_d[co-slice, px]
+//
+// (reference sign table src/algebras.cc:28-49; this replaces the CUDA-core 1x1 kernels of
+//  src/backend/cudnn/quat_pointwise_conv2d.cu:33-303.) Every weight tile is read once per stage and used
+// by 4 MMAs, every activation tile by 4 MMAs, so shared-memory traffic from L2 is 1/4 of what an expanded
+// 4Co x 4Ci GEMM would need and no thread ever touches an operand: both come by TMA
+// (cp.async.bulk.tensor, 128B / 64B swizzle) straight into the tcgen05 canonical layouts.
+//
+// CTA (persistent, one per SM): warp 0 = TMA producer, warp 1 = TMEM owner + MMA issuer, warps 2-9 =
+// epilogue (two warps per TMEM lane quadrant; each thread drains 2 components x 128 pixels of one output
+// channel into packed registers, releases the accumulators, then stores). Tile = 128 channels x 128
+// pixels x 4 components (all 512 TMEM columns); K slice per stage = 32 channels per component
+// (A 32 KB + B 32 KB), 3 stages. Every mbarrier wait is bounded; an expired wait sets the status word and
+// the CTA leaves through the common teardown.
+#include <cuda.h>
+
+#include "tensor_path.cuh"
+#include "umma.cuh"
+
+namespace pcb {
+namespace {
+
+using namespace umma;
+
+constexpr int CT = 128;             // channel tile (MMA M)
+constexpr int PT = 128;             // pixel tile (MMA N): two TMA boxes of 64 pixels
+constexpr int KS = 32;              // channels per component per stage
+constexpr int U_STAGES = 3;
+constexpr uint32_t A_BYTES = 4 * CT * KS * 2;      // 32 KB: 4 weight components
+constexpr uint32_t B_BYTES = 2 * 4 * KS * 64 * 2;  // 32 KB: 2 pixel boxes x 4 activation components
+constexpr uint32_t B_BOX_BYTES = 4 * KS * 64 * 2;  // 16 KB
+constexpr uint32_t STAGE_BYTES = A_BYTES + B_BYTES;
+constexpr int U_THREADS = 320;
+constexpr size_t U_SMEM_BYTES = 1024 + U_STAGES * STAGE_BYTES + 256;
+constexpr int ST_U_PRODUCER = 0x10, ST_U_MMA = 0x20, ST_U_EPILOGUE = 0x40;
+
+struct UParams {
+    int Nb, Cout, Cred;      // quaternion batch, output channels of the pass, reduced channels of the pass
+    int HW;
+    int blocks_per_image;    // ceil(HW / 64)
+    int n_px_tiles, n_c_tiles;
+    int fmt;                 // 0 f16, 1 bf16
+    int has_bias;
+    int bwd;                 // 0 forward, 1 backward-data
+};
+
+__device__ __forceinline__ void tma_load_4d(uint32_t dst, const CUtensorMap* map, int c0, int c1, int c2, int c3, uint32_t bar) {
+    asm volatile(
+        "cp.async.bulk.tensor.4d.shared::cluster.global.tile.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3, %4, %5}], [%6];"
+        ::"r"(dst), "l"(map), "r"(c0), "r"(c1), "r"(c2), "r"(c3), "r"(bar) : "memory");
+}
+__device__ __forceinline__ void tma_load_3d(uint32_t dst, const CUtensorMap* map, int c0, int c1, int c2, uint32_t bar) {
+    asm volatile(
+        "cp.async.bulk.tensor.3d.shared::cluster.global.tile.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3, %4}], [%5];"
+        ::"r"(dst), "l"(map), "r"(c0), "r"(c1), "r"(c2), "r"(bar) : "memory");
+}
+
+constexpr uint64_t DESC_SWIZZLE_64B = 4ull << 61;
+// K-major tile with 64-byte rows (32 16-bit K elements), 64-byte swizzle: 8-row groups are 512 bytes apart.
+__device__ __forceinline__ uint64_t make_desc_kmajor_sw64(uint32_t smem_addr) {
+    return (uint64_t)((smem_addr & 0x3FFFFu) >> 4) | ((uint64_t)1 << 16) | ((uint64_t)(512 >> 4) << 32) | DESC_VERSION_SM100 | DESC_SWIZZLE_64B;
+}
+
+template <bool BWD>
+__global__ void __launch_bounds__(U_THREADS, 1)
+qconv_pointwise_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant__ CUtensorMap map_act, UParams p,
+                          const uint16_t* __restrict__ bias, uint16_t* __restrict__ out, int* __restrict__ status) {
+    extern __shared__ uint8_t smem_raw[];
+    const int t = threadIdx.x, warp = t >> 5, lane = t & 31;
+    uint8_t* base = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+    uint64_t* bars = reinterpret_cast<uint64_t*>(base + U_STAGES * STAGE_BYTES);
+    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 2 * U_STAGES + 2);
+    const uint32_t tiles_addr = smem_u32(base);
+    const uint32_t full_bar = smem_u32(bars), empty_bar = smem_u32(bars + U_STAGES);
+    const uint32_t tmem_full = smem_u32(bars + 2 * U_STAGES), tmem_empty = smem_u32(bars + 2 * U_STAGES + 1);
+
+    const int n_tiles = p.n_px_tiles * p.n_c_tiles;
+    const int n_k = (p.Cred + KS - 1) / KS;
+
+    if (t == 0) {
+        for (int s = 0; s < U_STAGES; ++s) { mbar_init(full_bar + 8 * s, 1); mbar_init(empty_bar + 8 * s, 1); }
+        mbar_init(tmem_full, 1);
+        mbar_init(tmem_empty, 8);
+        fence_barrier_init();
+    }
+    if (warp == 1) tmem_alloc(smem_u32(tmem_slot), 512);
+    tc_fence_before_sync();
+    __syncthreads();
+    tc_fence_after_sync();
+    const uint32_t tmem_base = *tmem_slot;
+
+    if (warp == 0) {
+        // ---------------------------------------------------------------- TMA producer
+        if (lane == 0) {
+            int it = 0;
+            bool ok = true;
+            for (int tile = blockIdx.x; tile < n_tiles && ok; tile += gridDim.x) {
+                const int px_tile = tile / p.n_c_tiles, c_tile = tile - px_tile * p.n_c_tiles;
+                const int c0 = c_tile * CT;
+                int img[2], pix[2];
+#pragma unroll
+                for (int b = 0; b < 2; ++b) {
+                    const int blk = 2 * px_tile + b;
+                    img[b] = blk / p.blocks_per_image;          // == Nb for a block past the end: fully out of range -> zeros
+                    pix[b] = (blk - img[b] * p.blocks_per_image) * 64;
+                }
+                for (int k = 0; k < n_k && ok; ++k, ++it) {
+                    const int s = it % U_STAGES;
+                    ok = mbar_wait_bounded(empty_bar + 8 * s, ((it / U_STAGES) & 1) ^ 1, status, ST_U_PRODUCER);
+                    if (!ok) break;
+                    const uint32_t a_dst = tiles_addr + s * STAGE_BYTES, b_dst = a_dst + A_BYTES;
+                    const uint32_t bar = full_bar + 8 * s;
+                    mbar_arrive_expect_tx(bar, STAGE_BYTES);
+                    if (!BWD) {
+                        tma_load_3d(a_dst, &map_w, k * KS, c0, 0, bar);                 // [r][128 co][32 ci]
+                    } else {
+                        tma_load_3d(a_dst, &map_w, c0, k * KS, 0, bar);                 // [r][32 co][64 ci] x 2 ci blocks
+                        tma_load_3d(a_dst + A_BYTES / 2, &map_w, c0 + 64, k * KS, 0, bar);
+                    }
+                    tma_load_4d(b_dst, &map_act, pix[0], k * KS, img[0], 0, bar);       // [comp][32 ch][64 px]
+                    tma_load_4d(b_dst + B_BOX_BYTES, &map_act, pix[1], k * KS, img[1], 0, bar);
+                }
+            }
+        }
+        __syncwarp();
+    } else if (warp == 1) {
+        // ---------------------------------------------------------------- MMA issuer
+        int it = 0, local_tile = 0;
+        bool ok = true;
+        for (int tile = blockIdx.x; tile < n_tiles && ok; tile += gridDim.x, ++local_tile) {
+            if (local_tile > 0) {   // accumulators must have been drained by the epilogue of the previous tile
+                ok = mbar_wait_bounded(tmem_empty, (local_tile - 1) & 1, status, ST_U_MMA);
+                if (!ok) break;
+                tc_fence_after_sync();
+            }
+            for (int k = 0; k < n_k && ok; ++k, ++it) {
+                const int s = it % U_STAGES;
+                ok = mbar_wait_bounded(full_bar + 8 * s, (it / U_STAGES) & 1, status, ST_U_MMA);
+                if (!ok) break;
+                tc_fence_after_sync();
+                if (lane == 0) {
+                    const uint32_t a_addr = tiles_addr + s * STAGE_BYTES, b_addr = a_addr + A_BYTES;
+#pragma unroll
+                    for (int j = 0; j < KS / 16; ++j) {
+#pragma unroll
+                        for (int i = 0; i < 4; ++i) {          // component of the streamed activations (l forward, d backward)
+#pragma unroll
+                            for (int o = 0; o < 4; ++o) {      // component of the accumulator (d forward, l backward)
+                                const int r = i ^ o;
+                                const bool neg = BWD ? quat_negative(o, i) : quat_negative(i, o);
+                                const uint64_t ad = BWD ? make_desc_mnmajor(a_addr + r * (KS * 128) + j * 2048, A_BYTES / 2)
+                                                        : make_desc_kmajor_sw64(a_addr + r * (CT * KS * 2) + j * 32);
+                                const uint64_t bd = make_desc_mnmajor(b_addr + i * (KS * 128) + j * 2048, B_BOX_BYTES);
+                                const uint32_t idesc = make_idesc_f16(p.fmt, CT, PT, BWD, true, neg, false);
+                                mma_f16_ss(tmem_base + o * PT, ad, bd, idesc, (k > 0 || j > 0 || i > 0) ? 1u : 0u);
+                            }
+                        }
+                    }
+                    mma_commit(empty_bar + 8 * s);
+                    if (k == n_k - 1) mma_commit(tmem_full);
+                }
+                __syncwarp();
+            }
+        }
+    } else {
+        // ---------------------------------------------------------------- epilogue (warps 2..9)
+        const int q = warp & 3;                   // TMEM lane quadrant this warp may read
+        const int half = (warp - 2) >> 2;         // which pair of components
+        int local_tile = 0;
+        bool ok = true;
+        for (int tile = blockIdx.x; tile < n_tiles && ok; tile += gridDim.x, ++local_tile) {
+            const int px_tile = tile / p.n_c_tiles, c_tile = tile - px_tile * p.n_c_tiles;
+            const int c = c_tile * CT + q * 32 + lane;
+            ok = mbar_wait_bounded(tmem_full, local_tile & 1, status, ST_U_EPILOGUE);
+            ok = __all_sync(0xffffffffu, ok && (*reinterpret_cast<volatile int*>(status) == 0));
+            if (!ok) break;
+            tc_fence_after_sync();
+            uint32_t packed[2][4][16];
+#pragma unroll
+            for (int oo = 0; oo < 2; ++oo) {
+                const int o = 2 * half + oo;
+                float badd = 0.f;
+                if (!BWD && p.has_bias && c < p.Cout) {
+                    const uint16_t raw = bias[o * p.Cout + c];
+                    badd = p.fmt == 0 ? __half2float(__ushort_as_half(raw)) : __bfloat162float(__ushort_as_bfloat16(raw));
+                }
+#pragma unroll
+                for (int cb = 0; cb < 4; ++cb) {
+                    uint32_t v[32];
+                    tmem_ld_32x32b_x32(tmem_base + ((uint32_t)(q * 32) << 16) + o * PT + cb * 32, v);
+                    tmem_ld_wait();
+#pragma unroll
+                    for (int e = 0; e < 16; ++e) {
+                        const float f0 = __uint_as_float(v[2 * e]) + badd, f1 = __uint_as_float(v[2 * e + 1]) + badd;
+                        if (p.fmt == 0) { const __half2 h = __floats2half2_rn(f0, f1); packed[oo][cb][e] = *reinterpret_cast<const uint32_t*>(&h); }
+                        else { const __nv_bfloat162 h = __floats2bfloat162_rn(f0, f1); packed[oo][cb][e] = *reinterpret_cast<const uint32_t*>(&h); }
+                    }
+                }
+            }
+            // accumulators are in registers now: hand TMEM back to the MMA warp, then write out
+            tc_fence_before_sync();
+            __syncwarp();
+            if (lane == 0) mbar_arrive(tmem_empty);
+            if (c < p.Cout) {
+#pragma unroll
+                for (int oo = 0; oo < 2; ++oo) {
+                    const int o = 2 * half + oo;
+#pragma unroll
+                    for (int cb = 0; cb < 4; ++cb) {
+                        const int blk = 2 * px_tile + (cb >> 1);
+                        const int img = blk / p.blocks_per_image;
+                        if (img >= p.Nb) continue;
+                        const int px0 = (blk - img * p.blocks_per_image) * 64 + (cb & 1) * 32;
+                        uint16_t* dst = out + ((size_t)(o * p.Nb + img) * p.Cout + c) * p.HW + px0;
+#pragma unroll
+                        for (int g8 = 0; g8 < 4; ++g8) {
+                            if (px0 + g8 * 8 < p.HW)
+                                *reinterpret_cast<uint4*>(dst + g8 * 8) = make_uint4(packed[oo][cb][4 * g8], packed[oo][cb][4 * g8 + 1],
+                                                                                     packed[oo][cb][4 * g8 + 2], packed[oo][cb][4 * g8 + 3]);
+                        }
+                    }
+                }
+            }
+        }
+    }
+
+    tc_fence_before_sync();
+    __syncthreads();
+    if (warp == 1) tmem_dealloc(tmem_base, 512);
+}
+
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*, const cuuint64_t*,
+                                  const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
+                                  CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+EncodeTiledFn encode_fn() {
+    static EncodeTiledFn fn = nullptr;
+    if (!fn) {
+        void* sym = nullptr;
+        cudaDriverEntryPointQueryResult q;
+        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &sym, cudaEnableDefault, &q) == cudaSuccess && q == cudaDriverEntryPointSuccess)
+            fn = reinterpret_cast<EncodeTiledFn>(sym);
+    }
+    return fn;
+}
+
+int make_map(CUtensorMap* map, int fmt, const void* ptr, int rank, const cuuint64_t* dims, const cuuint64_t* strides_bytes,
+             const cuuint32_t* box, CUtensorMapSwizzle swizzle) {
+    EncodeTiledFn fn = encode_fn();
+    if (!fn) { set_error("cuTensorMapEncodeTiled is not available from the driver"); return PCB_ERR_CUDA; }
+    cuuint32_t ones[5] = {1, 1, 1, 1, 1};
+    const CUresult r = fn(map, fmt == 0 ? CU_TENSOR_MAP_DATA_TYPE_FLOAT16 : CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, (cuuint32_t)rank,
+                          const_cast<void*>(ptr), dims, strides_bytes, box, ones, CU_TENSOR_MAP_INTERLEAVE_NONE, swizzle,
+                          CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    if (r != CUDA_SUCCESS) { set_error("cuTensorMapEncodeTiled failed with code %d", (int)r); return PCB_ERR_CUDA; }
+    return PCB_OK;
+}
+
+int sm_count_u() {
+    static int sms = 0;
+    if (sms == 0) {
+        int dev = 0;
+        if (cudaGetDevice(&dev) != cudaSuccess || cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || sms <= 0)
+            sms = 148;
+    }
+    return sms;
+}
+
+}  // namespace
+
+bool pointwise_tc_supported(Pass pass, int dtype, int variant, const Geom& g) {
+    if (pass != PASS_FWD && pass != PASS_BWD_DATA) return false;
+    if (dtype != PCB_F16 && dtype != PCB_BF16) return false;
+    if (variant != PCB_VARIANT_16_PRODUCT || g.real_in || g.w_io || g.dw_io) return false;
+    if (!(g.KH == 1 && g.KW == 1 && g.SH == 1 && g.SW == 1 && g.PT == 0 && g.PL == 0 && g.HO == g.H && g.WO == g.W)) return false;
+    const int cout = pass == PASS_FWD ? g.Co : g.Ci;
+    // TMA: every global stride a multiple of 16 bytes; the channel tile is 128 wide, so narrow layers
+    // (which would waste most of each MMA) stay on the other kernel.
+    return (g.Ci % 8 == 0) && (g.Co % 8 == 0) && ((g.H * g.W) % 8 == 0) && cout >= 96;
+}
+
+int pointwise_tc_launch(Pass pass, int dtype, const Geom& g, const void* w, const void* act, const void* bias, void* out,
+                        int* status, cudaStream_t stream) {
+    const int fmt = dtype == PCB_F16 ? 0 : 1;
+    const int HW = g.H * g.W;
+    const bool bwd = pass == PASS_BWD_DATA;
+    UParams p;
+    p.Nb = g.Nb; p.HW = HW; p.fmt = fmt; p.has_bias = (!bwd && g.has_bias) ? 1 : 0; p.bwd = bwd ? 1 : 0;
+    p.Cout = bwd ? g.Ci : g.Co;
+    p.Cred = bwd ? g.Co : g.Ci;
+    p.blocks_per_image = (HW + 63) / 64;
+    const int blocks = p.blocks_per_image * g.Nb;
+    p.n_px_tiles = (blocks + 1) / 2;
+    p.n_c_tiles = (p.Cout + CT - 1) / CT;
+
+    alignas(64) CUtensorMap map_w, map_act;
+    {   // filters [4][Co][Ci]: (ci, co, r)
+        const cuuint64_t dims[3] = {(cuuint64_t)g.Ci, (cuuint64_t)g.Co, 4};
+        const cuuint64_t strides[2] = {(cuuint64_t)g.Ci * 2, (cuuint64_t)g.Co * g.Ci * 2};
+        int rc;
+        if (!bwd) { const cuuint32_t box[3] = {KS, CT, 4}; rc = make_map(&map_w, fmt, w, 3, dims, strides, box, CU_TENSOR_MAP_SWIZZLE_64B); }
+        else      { const cuuint32_t box[3] = {64, KS, 4}; rc = make_map(&map_w, fmt, w, 3, dims, strides, box, CU_TENSOR_MAP_SWIZZLE_128B); }
+        if (rc != PCB_OK) return rc;
+    }
+    {   // activations [4][Nb][C][HW]: (px, channel, image, component)
+        const int C = p.Cred;
+        const cuuint64_t dims[4] = {(cuuint64_t)HW, (cuuint64_t)C, (cuuint64_t)g.Nb, 4};
+        const cuuint64_t strides[3] = {(cuuint64_t)HW * 2, (cuuint64_t)C * HW * 2, (cuuint64_t)g.Nb * C * HW * 2};
+        const cuuint32_t box[4] = {64, KS, 1, 4};
+        const int rc = make_map(&map_act, fmt, act, 4, dims, strides, box, CU_TENSOR_MAP_SWIZZLE_128B);
+        if (rc != PCB_OK) return rc;
+    }
+    const int n_tiles = p.n_px_tiles * p.n_c_tiles;
+    const int grid = n_tiles < sm_count_u() ? n_tiles : sm_count_u();
+    if (!bwd) {
+        PCB_CUDA_TRY(cudaFuncSetAttribute(qconv_pointwise_tc_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)U_SMEM_BYTES));
+        qconv_pointwise_tc_kernel<false><<<grid, U_THREADS, U_SMEM_BYTES, stream>>>(map_w, map_act, p, (const uint16_t*)bias, (uint16_t*)out, status);
+    } else {
+        PCB_CUDA_TRY(cudaFuncSetAttribute(qconv_pointwise_tc_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)U_SMEM_BYTES));
+        qconv_pointwise_tc_kernel<true><<<grid, U_THREADS, U_SMEM_BYTES, stream>>>(map_w, map_act, p, (const uint16_t*)bias, (uint16_t*)out, status);
+    }
+    PCB_CUDA_TRY(cudaGetLastError());
+    return PCB_OK;
+}
+
+}  // namespace pcb

@@ -397,6 +397,7 @@ int tensor_launch(Pass pass, int dtype, int /*variant*/, const Geom& g, const vo
     p.k_per_split = (p.K + TBK - 1) / TBK * TBK;
     p.atomic_out = 0;
     PCB_CUDA_TRY(cudaMemsetAsync(status, 0, sizeof(int), stream));
+    if (pointwise_tc_supported(pass, dtype, PCB_VARIANT_16_PRODUCT, g)) return pointwise_tc_launch(pass, dtype, g, a, b, bias, out, status, stream);
     if (pass == PASS_FWD) return launch_tc<PASS_FWD>(p, 1, a, b, bias, out, nullptr, status, stream);
     if (pass == PASS_BWD_DATA) return launch_tc<PASS_BWD_DATA>(p, 1, a, b, bias, out, nullptr, status, stream);
 

@@ -12,4 +12,9 @@ size_t tensor_scratch_bytes(Pass pass, int dtype, int variant, int engine, const
 int tensor_launch(Pass pass, int dtype, int variant, const Geom& g, const void* a, const void* b, const void* bias,
                   void* out, float* scratch, int* status, cudaStream_t stream);
 
+// Persistent TMA-fed kernel for wide pointwise layers (forward and backward-data); see pointwise_tc.cu.
+bool pointwise_tc_supported(Pass pass, int dtype, int variant, const Geom& g);
+int pointwise_tc_launch(Pass pass, int dtype, const Geom& g, const void* w, const void* act, const void* bias, void* out,
+                        int* status, cudaStream_t stream);
+
 }  // namespace pcb

@@ -93,6 +93,12 @@ TENSOR_SHAPES = [
     (2, 128, 64, 16, 8),      # K = 512: the ring wraps around (8 iterations over 3 stages)
     (1, 64, 256, 12, 12),     # M = 1024: eight row tiles
     (4, 8, 8, 4, 2),          # the smallest legal sizes
+    # wide layers: the persistent TMA-fed kernel (four accumulators, sign by negate flag)
+    (1, 32, 128, 8, 8),       # one K stage, one tile
+    (2, 128, 256, 8, 16),     # K = 128: the stage ring wraps; two channel tiles
+    (3, 40, 160, 4, 6),       # ragged: partial K stage, partial channel tile, 24-pixel images (partial TMA boxes)
+    (1, 136, 96, 12, 12),     # backward-data with 136 output rows per component (partial second tile)
+    (5, 96, 128, 10, 8),      # odd number of 64-pixel blocks per image and in total
 ]
 
 
