@@ -44,47 +44,60 @@ def read_peaks():
 
 
 class ClockSampler:
-    """Samples SM clocks and throttle reasons with nvidia-smi while the timed region runs."""
-    QUERY = ("clocks.sm,clocks.max.sm,clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
-             "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+    """Samples SM clocks and throttle reasons through NVML (read-only) from a thread while the timed region
+    runs; falls back to one nvidia-smi query if NVML is not importable."""
+    REASONS = {0x4: "sw_power_cap", 0x8: "hw_slowdown", 0x20: "sw_thermal_slowdown", 0x40: "hw_thermal_slowdown",
+               0x80: "hw_power_brake_slowdown"}
 
     def __init__(self, gpu_index):
-        self.proc = None
         self.gpu_index = gpu_index
+        self.samples, self.reason_bits, self.max_mhz = [], 0, None
+        self._stop = False
+        self._thread = None
+
+    def _loop(self, nvml, handle):
+        while not self._stop:
+            try:
+                self.samples.append(nvml.nvmlDeviceGetClockInfo(handle, nvml.NVML_CLOCK_SM))
+                get = getattr(nvml, "nvmlDeviceGetCurrentClocksEventReasons", None) or nvml.nvmlDeviceGetCurrentClocksThrottleReasons
+                self.reason_bits |= int(get(handle))
+            except Exception:
+                pass
+            time.sleep(0.004)
 
     def start(self):
+        import threading
         try:
-            self.proc = subprocess.Popen(
-                ["nvidia-smi", "-i", str(self.gpu_index), "--query-gpu=" + self.QUERY, "--format=csv,noheader,nounits",
-                 "-lms", "100"], stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
-        except OSError:
-            self.proc = None
+            import pynvml as nvml
+            nvml.nvmlInit()
+            visible = os.environ.get("CUDA_VISIBLE_DEVICES")
+            index = self.gpu_index
+            if visible:
+                try:
+                    index = int(visible.split(",")[self.gpu_index])
+                except ValueError:
+                    index = self.gpu_index
+            handle = nvml.nvmlDeviceGetHandleByIndex(index)
+            self.max_mhz = nvml.nvmlDeviceGetMaxClockInfo(handle, nvml.NVML_CLOCK_SM)
+            self._thread = threading.Thread(target=self._loop, args=(nvml, handle), daemon=True)
+            self._thread.start()
+        except Exception:
+            self._thread = None
 
     def stop(self):
-        if self.proc is None:
-            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
-        self.proc.terminate()
+        if self._thread is not None:
+            self._stop = True
+            self._thread.join(timeout=2)
+            reasons = sorted(name for bit, name in self.REASONS.items() if self.reason_bits & bit)
+            return {"sm_mhz": statistics.median(self.samples) if self.samples else None, "sm_max_mhz": self.max_mhz,
+                    "samples": len(self.samples), "reasons": reasons, "source": "nvml"}
         try:
-            out, _ = self.proc.communicate(timeout=5)
-        except subprocess.TimeoutExpired:
-            self.proc.kill()
-            out, _ = self.proc.communicate()
-        sm, smax, reasons = [], [], set()
-        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
-        for line in out.strip().splitlines():
-            parts = [p.strip() for p in line.split(",")]
-            if len(parts) < 6:
-                continue
-            try:
-                sm.append(float(parts[0]))
-                smax.append(float(parts[1]))
-            except ValueError:
-                continue
-            for name, val in zip(names, parts[2:6]):
-                if val.lower().startswith("active"):
-                    reasons.add(name)
-        return {"sm_mhz": statistics.median(sm) if sm else None, "sm_max_mhz": max(smax) if smax else None,
-                "samples": len(sm), "reasons": sorted(reasons)}
+            out = subprocess.run(["nvidia-smi", "-i", str(self.gpu_index), "--query-gpu=clocks.sm,clocks.max.sm",
+                                  "--format=csv,noheader,nounits"], capture_output=True, text=True, timeout=20).stdout
+            a, b = [float(v) for v in out.strip().split(",")[:2]]
+            return {"sm_mhz": a, "sm_max_mhz": b, "samples": 1, "reasons": [], "source": "nvidia-smi after the run"}
+        except Exception:
+            return {"sm_mhz": None, "sm_max_mhz": None, "samples": 0, "reasons": ["clock query unavailable"]}
 
 
 def make_inputs(torch, n, ci, co, h, w, device, seed):
@@ -303,7 +316,7 @@ def run_ours(args):
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
-    ap.add_argument("--steps", type=int, default=20)
+    ap.add_argument("--steps", type=int, default=200)
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--cpu-sample", type=int, default=32, help="batch size of the CPU baseline sample")

@@ -237,6 +237,147 @@ qconv_pointwise_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __gri
     if (warp == 1) tmem_dealloc(tmem_base, 512);
 }
 
+
+// ===================================================================================================
+// Backward-filter of the pointwise convolution, same idea: one accumulator per filter component r,
+//   D_r[co, ci] += s(l, l^r) * dy_{l^r}[co, px-slice] * x_l[ci, px-slice]^T          l, r = 0..3
+// Both operands are K-major here (pixels are contiguous in memory), 32 pixels per stage and component
+// (64-byte rows, 64-byte swizzle). K = all pixels of all images, split across the grid; every CTA adds its
+// 4 x 128 x 128 partial sums into the fp32 scratch with vector reductions and a last pass casts to the
+// tensor type (replaces src/backend/cudnn/quat_pointwise_conv2d.cu:331-607).
+// ===================================================================================================
+constexpr int FKP = 32;                                  // pixels per stage
+constexpr uint32_t F_OP_BYTES = 4 * 128 * FKP * 2;       // 32 KB per operand per stage
+constexpr uint32_t F_STAGE_BYTES = 2 * F_OP_BYTES;
+constexpr size_t F_SMEM_BYTES = 1024 + U_STAGES * F_STAGE_BYTES + 256;
+
+struct FParams {
+    int Nb, Co, Ci, HW;
+    int blocks_per_image;     // ceil(HW / 32)
+    int n_co_tiles, n_ci_tiles;
+    int steps_total;          // Nb * blocks_per_image
+    int steps_per_split;
+    int fmt;
+};
+
+__device__ __forceinline__ void red_add_v4(float* addr, float a, float b, float c, float d) {
+    asm volatile("red.global.add.v4.f32 [%0], {%1, %2, %3, %4};" ::"l"(addr), "f"(a), "f"(b), "f"(c), "f"(d) : "memory");
+}
+
+__global__ void __launch_bounds__(U_THREADS, 1)
+qconv_pointwise_filter_tc_kernel(const __grid_constant__ CUtensorMap map_dy, const __grid_constant__ CUtensorMap map_x, FParams p,
+                                 float* __restrict__ dw32, int* __restrict__ status) {
+    extern __shared__ uint8_t smem_raw[];
+    const int t = threadIdx.x, warp = t >> 5, lane = t & 31;
+    uint8_t* base = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+    uint64_t* bars = reinterpret_cast<uint64_t*>(base + U_STAGES * F_STAGE_BYTES);
+    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 2 * U_STAGES + 1);
+    const uint32_t tiles_addr = smem_u32(base);
+    const uint32_t full_bar = smem_u32(bars), empty_bar = smem_u32(bars + U_STAGES), tmem_full = smem_u32(bars + 2 * U_STAGES);
+
+    const int n_out_tiles = p.n_co_tiles * p.n_ci_tiles;
+    const int out_tile = blockIdx.x % n_out_tiles, split = blockIdx.x / n_out_tiles;
+    const int co0 = (out_tile / p.n_ci_tiles) * 128, ci0 = (out_tile % p.n_ci_tiles) * 128;
+    const int step_beg = split * p.steps_per_split;
+    const int step_end = min(p.steps_total, step_beg + p.steps_per_split);
+    const int n_steps = max(0, step_end - step_beg);
+
+    if (t == 0) {
+        for (int s = 0; s < U_STAGES; ++s) { mbar_init(full_bar + 8 * s, 1); mbar_init(empty_bar + 8 * s, 1); }
+        mbar_init(tmem_full, 1);
+        fence_barrier_init();
+    }
+    if (warp == 1) tmem_alloc(smem_u32(tmem_slot), 512);
+    tc_fence_before_sync();
+    __syncthreads();
+    tc_fence_after_sync();
+    const uint32_t tmem_base = *tmem_slot;
+
+    if (warp == 0) {
+        if (lane == 0) {
+            bool ok = true;
+            for (int it = 0; it < n_steps && ok; ++it) {
+                const int s = it % U_STAGES;
+                ok = mbar_wait_bounded(empty_bar + 8 * s, ((it / U_STAGES) & 1) ^ 1, status, ST_U_PRODUCER);
+                if (!ok) break;
+                const int step = step_beg + it;
+                const int img = step / p.blocks_per_image, px0 = (step - img * p.blocks_per_image) * FKP;
+                const uint32_t a_dst = tiles_addr + s * F_STAGE_BYTES, bar = full_bar + 8 * s;
+                mbar_arrive_expect_tx(bar, F_STAGE_BYTES);
+                tma_load_4d(a_dst, &map_dy, px0, co0, img, 0, bar);                 // [d][128 co][32 px]
+                tma_load_4d(a_dst + F_OP_BYTES, &map_x, px0, ci0, img, 0, bar);     // [l][128 ci][32 px]
+            }
+        }
+        __syncwarp();
+    } else if (warp == 1) {
+        bool ok = true;
+        for (int it = 0; it < n_steps && ok; ++it) {
+            const int s = it % U_STAGES;
+            ok = mbar_wait_bounded(full_bar + 8 * s, (it / U_STAGES) & 1, status, ST_U_MMA);
+            if (!ok) break;
+            tc_fence_after_sync();
+            if (lane == 0) {
+                const uint32_t a_addr = tiles_addr + s * F_STAGE_BYTES, b_addr = a_addr + F_OP_BYTES;
+#pragma unroll
+                for (int j = 0; j < FKP / 16; ++j) {
+#pragma unroll
+                    for (int l = 0; l < 4; ++l) {
+#pragma unroll
+                        for (int r = 0; r < 4; ++r) {
+                            const int d = l ^ r;
+                            const uint64_t ad = make_desc_kmajor_sw64(a_addr + d * (128 * FKP * 2) + j * 32);
+                            const uint64_t bd = make_desc_kmajor_sw64(b_addr + l * (128 * FKP * 2) + j * 32);
+                            const uint32_t idesc = make_idesc_f16(p.fmt, 128, 128, false, false, quat_negative(l, d), false);
+                            mma_f16_ss(tmem_base + r * 128, ad, bd, idesc, (it > 0 || j > 0 || l > 0) ? 1u : 0u);
+                        }
+                    }
+                }
+                mma_commit(empty_bar + 8 * s);
+                if (it == n_steps - 1) mma_commit(tmem_full);
+            }
+            __syncwarp();
+        }
+        if (n_steps == 0 && lane == 0) mbar_arrive(tmem_full);
+        __syncwarp();
+    } else {
+        const int q = warp & 3, half = (warp - 2) >> 2;
+        bool ok = mbar_wait_bounded(tmem_full, 0, status, ST_U_EPILOGUE);
+        ok = __all_sync(0xffffffffu, ok && (*reinterpret_cast<volatile int*>(status) == 0));
+        tc_fence_after_sync();
+        if (ok && n_steps > 0) {
+            const int co = co0 + q * 32 + lane;
+#pragma unroll 1
+            for (int rr = 0; rr < 2; ++rr) {
+                const int r = 2 * half + rr;
+#pragma unroll 1
+                for (int cb = 0; cb < 4; ++cb) {
+                    uint32_t v[32];
+                    tmem_ld_32x32b_x32(tmem_base + ((uint32_t)(q * 32) << 16) + r * 128 + cb * 32, v);
+                    tmem_ld_wait();
+                    if (co >= p.Co) continue;
+                    float* dst = dw32 + ((size_t)r * p.Co + co) * p.Ci + ci0 + cb * 32;
+#pragma unroll
+                    for (int g4 = 0; g4 < 8; ++g4) {
+                        if (ci0 + cb * 32 + g4 * 4 < p.Ci)
+                            red_add_v4(dst + g4 * 4, __uint_as_float(v[4 * g4]), __uint_as_float(v[4 * g4 + 1]),
+                                       __uint_as_float(v[4 * g4 + 2]), __uint_as_float(v[4 * g4 + 3]));
+                    }
+                }
+            }
+        }
+    }
+    tc_fence_before_sync();
+    __syncthreads();
+    if (warp == 1) tmem_dealloc(tmem_base, 512);
+}
+
+template <typename T>
+__global__ void cast_f32_kernel(const float* __restrict__ src, T* __restrict__ dst, size_t n) {
+    size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+    const size_t stride = (size_t)gridDim.x * blockDim.x;
+    for (; i < n; i += stride) DType<T>::store(dst + i, src[i]);
+}
+
 typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*, const cuuint64_t*,
                                   const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
                                   CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
@@ -327,6 +468,56 @@ int pointwise_tc_launch(Pass pass, int dtype, const Geom& g, const void* w, cons
         PCB_CUDA_TRY(cudaFuncSetAttribute(qconv_pointwise_tc_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)U_SMEM_BYTES));
         qconv_pointwise_tc_kernel<true><<<grid, U_THREADS, U_SMEM_BYTES, stream>>>(map_w, map_act, p, (const uint16_t*)bias, (uint16_t*)out, status);
     }
+    PCB_CUDA_TRY(cudaGetLastError());
+    return PCB_OK;
+}
+
+bool pointwise_filter_tc_supported(int dtype, int variant, const Geom& g) {
+    if (dtype != PCB_F16 && dtype != PCB_BF16) return false;
+    if (variant != PCB_VARIANT_16_PRODUCT || g.real_in || g.w_io || g.dw_io) return false;
+    if (!(g.KH == 1 && g.KW == 1 && g.SH == 1 && g.SW == 1 && g.PT == 0 && g.PL == 0 && g.HO == g.H && g.WO == g.W)) return false;
+    return (g.Ci % 8 == 0) && (g.Co % 8 == 0) && ((g.H * g.W) % 8 == 0) && g.Co >= 96 && g.Ci >= 64;
+}
+
+int pointwise_filter_tc_launch(int dtype, const Geom& g, const void* dy, const void* x, void* dw, float* scratch, int* status,
+                               cudaStream_t stream) {
+    const int fmt = dtype == PCB_F16 ? 0 : 1;
+    const int HW = g.H * g.W;
+    FParams p;
+    p.Nb = g.Nb; p.Co = g.Co; p.Ci = g.Ci; p.HW = HW; p.fmt = fmt;
+    p.blocks_per_image = (HW + FKP - 1) / FKP;
+    p.n_co_tiles = (g.Co + 127) / 128;
+    p.n_ci_tiles = (g.Ci + 127) / 128;
+    p.steps_total = g.Nb * p.blocks_per_image;
+    const int n_out_tiles = p.n_co_tiles * p.n_ci_tiles;
+    int splits = sm_count_u() / n_out_tiles;
+    if (splits < 1) splits = 1;
+    if (splits > p.steps_total) splits = p.steps_total;
+    p.steps_per_split = (p.steps_total + splits - 1) / splits;
+    splits = (p.steps_total + p.steps_per_split - 1) / p.steps_per_split;
+
+    alignas(64) CUtensorMap map_dy, map_x;
+    const cuuint32_t box[4] = {FKP, 128, 1, 4};
+    {
+        const cuuint64_t dims[4] = {(cuuint64_t)HW, (cuuint64_t)g.Co, (cuuint64_t)g.Nb, 4};
+        const cuuint64_t strides[3] = {(cuuint64_t)HW * 2, (cuuint64_t)g.Co * HW * 2, (cuuint64_t)g.Nb * g.Co * HW * 2};
+        const int rc = make_map(&map_dy, fmt, dy, 4, dims, strides, box, CU_TENSOR_MAP_SWIZZLE_64B);
+        if (rc != PCB_OK) return rc;
+    }
+    {
+        const cuuint64_t dims[4] = {(cuuint64_t)HW, (cuuint64_t)g.Ci, (cuuint64_t)g.Nb, 4};
+        const cuuint64_t strides[3] = {(cuuint64_t)HW * 2, (cuuint64_t)g.Ci * HW * 2, (cuuint64_t)g.Nb * g.Ci * HW * 2};
+        const int rc = make_map(&map_x, fmt, x, 4, dims, strides, box, CU_TENSOR_MAP_SWIZZLE_64B);
+        if (rc != PCB_OK) return rc;
+    }
+    const size_t numel = (size_t)4 * g.Co * g.Ci;
+    PCB_CUDA_TRY(cudaMemsetAsync(scratch, 0, numel * sizeof(float), stream));
+    PCB_CUDA_TRY(cudaFuncSetAttribute(qconv_pointwise_filter_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)F_SMEM_BYTES));
+    qconv_pointwise_filter_tc_kernel<<<n_out_tiles * splits, U_THREADS, F_SMEM_BYTES, stream>>>(map_dy, map_x, p, scratch, status);
+    PCB_CUDA_TRY(cudaGetLastError());
+    const int blocks = (int)((numel + 255) / 256 < 1184 ? (numel + 255) / 256 : 1184);
+    if (dtype == PCB_F16) cast_f32_kernel<__half><<<blocks, 256, 0, stream>>>(scratch, (__half*)dw, numel);
+    else cast_f32_kernel<__nv_bfloat16><<<blocks, 256, 0, stream>>>(scratch, (__nv_bfloat16*)dw, numel);
     PCB_CUDA_TRY(cudaGetLastError());
     return PCB_OK;
 }

@@ -404,6 +404,7 @@ int tensor_launch(Pass pass, int dtype, int /*variant*/, const Geom& g, const vo
     // backward-filter: the output is tiny and K is the whole batch of pixels -> split K across the grid,
     // accumulate in fp32 scratch, then cast once.
     if (scratch == nullptr) { set_error("backward-filter needs fp32 scratch"); return PCB_ERR_WORKSPACE; }
+    if (pointwise_filter_tc_supported(dtype, PCB_VARIANT_16_PRODUCT, g)) return pointwise_filter_tc_launch(dtype, g, a, b, out, scratch, status, stream);
     const int tiles = ((p.M + TBM - 1) / TBM) * ((p.N + TBN - 1) / TBN);
     int splits = (2 * sm_count() + tiles - 1) / tiles;
     const int max_splits = (p.K + 4 * TBK - 1) / (4 * TBK);

@@ -17,4 +17,8 @@ bool pointwise_tc_supported(Pass pass, int dtype, int variant, const Geom& g);
 int pointwise_tc_launch(Pass pass, int dtype, const Geom& g, const void* w, const void* act, const void* bias, void* out,
                         int* status, cudaStream_t stream);
 
+bool pointwise_filter_tc_supported(int dtype, int variant, const Geom& g);
+int pointwise_filter_tc_launch(int dtype, const Geom& g, const void* dy, const void* x, void* dw, float* scratch, int* status,
+                               cudaStream_t stream);
+
 }  // namespace pcb
