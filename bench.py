@@ -227,7 +227,7 @@ def run_ours(args):
     from phoenix_core_b200.ops import Device, _conv_desc, _ptr, _stream
     d = _conv_desc(bwd_desc, torch.float16, ctx16, _lib.ENGINE_AUTO, require_input_grad=True)
     ws = Device.get(device).requestWorkspace(L.pcb_qconv2d_bwd_workspace_size(ctypes.byref(d)))
-    kreps = max(3, args.steps)
+    kreps = 1 if args.kernels_only else max(3, args.steps)
     t_fwd = timed(lambda: pcb.conv2DFwd(x, wt, None, y, fwd_desc, ctx16), kreps)
     t_bwd_f = timed(lambda: _lib.check(L.pcb_qconv2d_bwd_filter(ctypes.byref(d), _ptr(x), _ptr(dy), _ptr(dw), _ptr(ws), ws.numel(), _stream())), kreps)
     t_bwd_d = timed(lambda: _lib.check(L.pcb_qconv2d_bwd_data(ctypes.byref(d), _ptr(wt), _ptr(dy), _ptr(dx), _ptr(ws), ws.numel(), _stream())), kreps)
@@ -235,7 +235,7 @@ def run_ours(args):
 
     # end to end through the public API from pinned host buffers
     e2e = None
-    if rank == 0 or world > 1:
+    if (rank == 0 or world > 1) and not args.kernels_only:
         hx, hw, hdy = make_inputs(torch, n, ci, co, h, w, None, SEED + rank)
         hx, hw, hdy = hx.pin_memory(), hw.pin_memory(), hdy.pin_memory()
         hy = torch.empty(y.shape, dtype=torch.float16).pin_memory()
@@ -286,7 +286,8 @@ def run_ours(args):
         if os.path.exists(traffic_path):
             with open(traffic_path) as f:
                 traffic = json.load(f).get(worst)
-        cpu_v, cores, sample, _ = cpu_baseline(torch, args.cpu_sample, 5) if world == 1 else (None, None, None, None)
+        cpu_v, cores, sample, _ = (cpu_baseline(torch, args.cpu_sample, 5) if world == 1 and not args.kernels_only
+                                   else (None, None, None, None))
         line = {
             "metric": "quaternion conv2d fwd+bwd TFLOP/s", "value": value, "unit": "TFLOP/s", "n_gpus": world,
             "steps": args.steps, "warmup": max(3, args.warmup), "ms_per_step": elapsed_ms / args.steps,
@@ -305,6 +306,8 @@ def run_ours(args):
             "e2e": e2e,
             "gpu_launches": 4 * args.steps,
         }
+        if args.batch is not None:
+            line["reduced_batch"] = "profiling run, not a benchmark value"
         if cpu_v is not None:
             line["cpu_baseline"] = {"value": cpu_v, "unit": "TFLOP/s", "cores": cores, "kind": "port", "sample": sample}
         print(json.dumps(line), flush=True)
@@ -320,7 +323,13 @@ def main():
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--cpu-sample", type=int, default=32, help="batch size of the CPU baseline sample")
+    ap.add_argument("--batch", type=int, default=None,
+                    help="profiling only: per-GPU batch instead of 64 (the line is then marked 'reduced_batch' and is not a benchmark value)")
+    ap.add_argument("--kernels-only", action="store_true",
+                    help="profiling only: skip the end-to-end, per-kernel and CPU-baseline legs")
     args = ap.parse_args()
+    if args.batch is not None:
+        WORKLOAD["n"] = args.batch
     if args.impl == "reference":
         run_reference(args)
     else:
