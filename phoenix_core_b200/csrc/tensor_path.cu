@@ -369,7 +369,10 @@ bool pointwise(const Geom& g) {
 
 }  // namespace
 
-bool tensor_path_supported(Pass /*pass*/, int dtype, int variant, const Geom& g) {
+namespace {
+// The first tensor-core kernels of this backend (producer warps copy operand chunks): still used for the
+// filter gradient of narrow pointwise layers.
+bool legacy_supported(int dtype, int variant, const Geom& g) {
     if (dtype != PCB_F16 && dtype != PCB_BF16) return false;
     if (variant != PCB_VARIANT_16_PRODUCT) return false;
     if (g.real_in || g.w_io || g.dw_io) return false;
@@ -377,10 +380,19 @@ bool tensor_path_supported(Pass /*pass*/, int dtype, int variant, const Geom& g)
     // 16-byte operand chunks must not straddle a component, an image or a channel row
     return (g.Ci % 8 == 0) && (g.Co % 8 == 0) && ((g.H * g.W) % 8 == 0);
 }
+}  // namespace
+
+bool tensor_path_supported(Pass pass, int dtype, int variant, const Geom& g) {
+    if (pass == PASS_BWD_FILTER) return pointwise_filter_tc_supported(dtype, variant, g) || legacy_supported(dtype, variant, g);
+    return pointwise_tc_supported(pass, dtype, variant, g) || conv_tc_supported(pass, dtype, variant, g) ||
+           legacy_supported(dtype, variant, g);
+}
 
 size_t tensor_scratch_bytes(Pass pass, int dtype, int variant, int engine, const Geom& g) {
     if (engine == PCB_ENGINE_SIMT || !tensor_path_supported(pass, dtype, variant, g)) return 0;
     if (pass == PASS_BWD_FILTER) return (size_t)4 * g.Co * g.Ci * g.KH * g.KW * sizeof(float);
+    if (pointwise_tc_supported(pass, dtype, variant, g)) return 0;
+    if (conv_tc_supported(pass, dtype, variant, g)) return conv_tc_scratch_bytes(pass, g);
     return 0;
 }
 
@@ -398,6 +410,8 @@ int tensor_launch(Pass pass, int dtype, int /*variant*/, const Geom& g, const vo
     p.atomic_out = 0;
     PCB_CUDA_TRY(cudaMemsetAsync(status, 0, sizeof(int), stream));
     if (pointwise_tc_supported(pass, dtype, PCB_VARIANT_16_PRODUCT, g)) return pointwise_tc_launch(pass, dtype, g, a, b, bias, out, status, stream);
+    if (pass != PASS_BWD_FILTER && conv_tc_supported(pass, dtype, PCB_VARIANT_16_PRODUCT, g))
+        return conv_tc_launch(pass, dtype, g, a, b, bias, out, scratch, status, stream);
     if (pass == PASS_FWD) return launch_tc<PASS_FWD>(p, 1, a, b, bias, out, nullptr, status, stream);
     if (pass == PASS_BWD_DATA) return launch_tc<PASS_BWD_DATA>(p, 1, a, b, bias, out, nullptr, status, stream);
 

@@ -21,4 +21,10 @@ bool pointwise_filter_tc_supported(int dtype, int variant, const Geom& g);
 int pointwise_filter_tc_launch(int dtype, const Geom& g, const void* dy, const void* x, void* dw, float* scratch, int* status,
                                cudaStream_t stream);
 
+// General implicit-GEMM convolution (any taps / stride <= 2 / padding) on staged operands; see conv_tc.cu.
+bool conv_tc_supported(Pass pass, int dtype, int variant, const Geom& g);
+size_t conv_tc_scratch_bytes(Pass pass, const Geom& g);
+int conv_tc_launch(Pass pass, int dtype, const Geom& g, const void* w, const void* act, const void* bias, void* out,
+                   void* scratch, int* status, cudaStream_t stream);
+
 }  // namespace pcb

@@ -1,0 +1,115 @@
+"""Shape sweep of the quaternion conv2d kernels at ResNet-stage shapes.
+
+    python -m phoenix_core_b200.sweep [--batch 128] [--dtypes f16,f32] [--reps 10] [--variant 16p|8p] [--quick]
+
+For every shape times forward, backward-data and backward-filter separately (CUDA events on the current stream,
+3 warm-up + `reps` timed launches; every shape's tensors exceed L2 or the output is overwritten between
+iterations by the next launch of the same kernel) and prints one JSON line per (shape, dtype, pass) with
+TFLOP/s (F = 32*N*Ho*Wo*Co*Ci*kh*kw per pass), algorithmic GB/s and both fractions of the measured peaks,
+plus the kernel family that ran (1 = CUDA-core, 2 = tcgen05).
+Shapes: quaternion channels 16@112, 64@56, 128@28, 256@14, 512@7; 3x3 (pad 1) and 1x1; stride 1 and 2.
+"""
+import argparse
+import ctypes
+import json
+import os
+import sys
+
+import torch
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+if ROOT not in sys.path:
+    sys.path.insert(0, ROOT)
+
+import phoenix_core_b200 as pcb  # noqa: E402
+from phoenix_core_b200 import _lib  # noqa: E402
+from phoenix_core_b200.context import Context  # noqa: E402
+from phoenix_core_b200.ops import Device, _conv_desc, _ptr, _stream  # noqa: E402
+
+STAGES = [(16, 112), (64, 56), (128, 28), (256, 14), (512, 7)]
+TORCH = {"f16": torch.float16, "bf16": torch.bfloat16, "f32": torch.float32}
+
+
+def peaks():
+    path = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.exists(path):
+        with open(path) as f:
+            p = json.load(f)
+        return p["hbm_gbs"], p["bf16_tflops_sustained"], "measured"
+    return 6650.0, 1400.0, "fallback"
+
+
+def timed(fn, reps):
+    for _ in range(3):
+        fn()
+    torch.cuda.synchronize()
+    a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    a.record()
+    for _ in range(reps):
+        fn()
+    b.record()
+    torch.cuda.synchronize()
+    return a.elapsed_time(b) / reps * 1e-3
+
+
+def run_shape(n, c, hw, k, stride, dtype, variant, reps):
+    pad = 1 if k == 3 else 0
+    ctx = Context({"UPSTRIDE_MEMORY_OPTIMIZED": "1" if variant == "16p" else "0"})
+    args = ((4 * n, c, hw, hw), (4, c, c, k, k), stride, 1, pcb.Padding.EXPLICIT, (pad, pad, pad, pad), 1, pcb.Algebra.QUATERNION,
+            pcb.DataFormat.NCHW, pcb.FilterLayout.OIHW)
+    fwd = pcb.Conv2DFwdDescriptor(*args, False)
+    bwd = pcb.Conv2DBwdDescriptor(*args, True)
+    tdt = TORCH[dtype]
+    dev = torch.device("cuda")
+    g = torch.Generator(device="cpu").manual_seed(7)
+    x = (torch.rand((4 * n, c, hw, hw), generator=g) * 2 - 1).to(tdt).to(dev)
+    w = (torch.rand((4, c, c, k, k), generator=g) * 2 - 1).to(tdt).to(dev)
+    y = torch.empty(fwd.getOutputShape(), dtype=tdt, device=dev)
+    dy = (torch.rand(tuple(y.shape), generator=g) * 2 - 1).to(tdt).to(dev)
+    dw, dx = torch.empty_like(w), torch.empty_like(x)
+    L = _lib.lib()
+    d = _conv_desc(bwd, tdt, ctx, _lib.ENGINE_AUTO, require_input_grad=True)
+    ws = Device.get(dev).requestWorkspace(max(L.pcb_qconv2d_bwd_workspace_size(ctypes.byref(d)),
+                                              L.pcb_qconv2d_fwd_workspace_size(ctypes.byref(d))))
+    ho = y.shape[2]
+    flops = 32.0 * n * ho * ho * c * c * k * k
+    eb = 4 if dtype == "f32" else 2
+    xb, yb, wb = x.numel() * eb, y.numel() * eb, w.numel() * eb
+    passes = {
+        "fwd": (lambda: pcb.conv2DFwd(x, w, None, y, fwd, ctx), xb + yb + wb, 0),
+        "bwd_data": (lambda: _lib.check(L.pcb_qconv2d_bwd_data(ctypes.byref(d), _ptr(w), _ptr(dy), _ptr(dx), _ptr(ws), ws.numel(), _stream())),
+                     yb + wb + xb, 1),
+        "bwd_filter": (lambda: _lib.check(L.pcb_qconv2d_bwd_filter(ctypes.byref(d), _ptr(x), _ptr(dy), _ptr(dw), _ptr(ws), ws.numel(), _stream())),
+                       xb + yb + w.numel() * 4, 2),
+    }
+    hbm, tf, src = peaks()
+    out = []
+    for name, (fn, nbytes, pass_id) in passes.items():
+        t = timed(fn, reps)
+        out.append({"c": c, "hw": hw, "k": k, "stride": stride, "n": n, "dtype": dtype, "variant": variant, "pass": name,
+                    "engine": L.pcb_qconv2d_engine_for(ctypes.byref(d), pass_id), "ms": t * 1e3, "tflops": flops / t / 1e12,
+                    "gbs": nbytes / t / 1e9, "frac_tensor_peak": flops / t / 1e12 / tf, "frac_hbm_peak": nbytes / t / 1e9 / hbm,
+                    "peaks": src})
+    _lib.check(L.pcb_check_device_status(_ptr(ws), ws.numel(), _stream()))
+    return out
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--batch", type=int, default=128)
+    ap.add_argument("--dtypes", default="f16,f32")
+    ap.add_argument("--reps", type=int, default=10)
+    ap.add_argument("--variant", default="16p")
+    ap.add_argument("--quick", action="store_true", help="3x3 stride 1 and 1x1 stride 1 only")
+    a = ap.parse_args()
+    for dtype in a.dtypes.split(","):
+        for c, hw in STAGES:
+            for k in (3, 1):
+                for stride in ((1,) if a.quick else (1, 2)):
+                    for rec in run_shape(a.batch, c, hw, k, stride, dtype, a.variant, a.reps if dtype != "f32" else max(2, a.reps // 3)):
+                        print(json.dumps(rec), flush=True)
+                    torch.cuda.empty_cache()
+
+
+if __name__ == "__main__":
+    main()

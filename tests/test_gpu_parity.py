@@ -124,12 +124,46 @@ def test_pointwise_tensor_core_vs_oracle(gpu, oracle, shape, dtype):
     assert rel_err(got, simt) <= 4e-3 if dtype == "f16" else 2e-2
 
 
+# shapes for the general implicit-GEMM tensor-core kernel (staged channels-last activations, expanded filters):
+# n, ci, co, h, w, kh, kw, stride, pad(t,l,b,r)
+GENERAL_TENSOR_SHAPES = [
+    (2, 16, 16, 14, 14, 3, 3, (1, 1), (1, 1, 1, 1)),     # 16-channel K slices (32-byte swizzle), M = 64 padded to 128
+    (2, 32, 64, 14, 14, 3, 3, (2, 2), (0, 0, 1, 1)),     # stride 2 through the tensor map's element stride; M = 256
+    (1, 3, 16, 32, 32, 7, 7, (2, 2), (2, 2, 3, 3)),      # stem: 3 channels padded to 16, 49 taps
+    (3, 64, 32, 7, 7, 3, 3, (1, 1), (1, 1, 1, 1)),       # 7x7 images: tile box spans images
+    (2, 16, 32, 28, 28, 1, 1, (2, 2), (0, 0, 0, 0)),     # 1x1 stride 2 (downsample branch)
+    (2, 24, 16, 6, 5, 1, 1, (1, 1), (0, 0, 0, 0)),       # narrow pointwise layer with unaligned planes
+    (1, 48, 40, 9, 11, 3, 2, (1, 2), (1, 0, 1, 1)),      # ragged everything, mixed strides, 48 = 3 x 16 channels
+    (5, 32, 32, 28, 28, 3, 3, (1, 1), (1, 1, 1, 1)),     # several tiles per CTA: both accumulator buffers in use
+]
+
+
+@pytest.mark.parametrize("shape", GENERAL_TENSOR_SHAPES)
+@pytest.mark.parametrize("dtype", ["f16", "bf16"])
+def test_general_conv_tensor_core_vs_oracle(gpu, oracle, shape, dtype):
+    n, ci, co, h, w_, kh, kw, stride, pad = shape
+    x = gpu.rounded(uniform(41, (4 * n, ci, h, w_)), dtype)
+    w = gpu.rounded(normal(42, (4, co, ci, kh, kw), std=(2.0 / (4 * ci * kh * kw)) ** 0.5), dtype)
+    b = gpu.rounded(uniform(43, (4, co)), dtype)
+    ref = oracle.conv2d_fwd(x, w, b, stride, (1, 1), pad)
+    got = gpu.run_conv_fwd(x, w, b, stride, pad, dtype, "16p", "tensor")
+    _check(got, ref, dtype, gpu, "y")
+    dy = gpu.rounded(normal(44, ref.shape), dtype)
+    rdw, rdx = oracle.conv2d_bwd(x, w, dy, stride, (1, 1), pad)
+    dw, dx = gpu.run_conv_bwd(x, w, dy, stride, pad, dtype, "16p", "auto", True)
+    _check(dx, rdx, dtype, gpu, "dx")
+    _check(dw, rdw, dtype, gpu, "dw")
+
+
 def test_tensor_engine_refuses_unsupported_shapes(gpu):
     from phoenix_core_b200 import _lib
     x = uniform(1, (4, 3, 5, 5))
     w = uniform(2, (4, 2, 3, 3, 3))
-    with pytest.raises(_lib.BackendError) as e:
-        gpu.run_conv_fwd(x, w, None, (1, 1), (1, 1, 1, 1), "f16", "16p", "tensor")
+    with pytest.raises(_lib.BackendError) as e:      # stride 3 has no tensor-core kernel
+        gpu.run_conv_fwd(x, w, None, (3, 3), (1, 1, 1, 1), "f16", "16p", "tensor")
+    assert e.value.status == _lib.PCB_ERR_UNSUPPORTED
+    with pytest.raises(_lib.BackendError) as e:      # fp32 tensors stay on the CUDA-core kernels
+        gpu.run_conv_fwd(x, w, None, (1, 1), (1, 1, 1, 1), "f32", "16p", "tensor")
     assert e.value.status == _lib.PCB_ERR_UNSUPPORTED
 
 
