@@ -1,5 +1,5 @@
 // General quaternion convolution on the tensor cores (tcgen05 / TMEM / TMA): any filter size, stride 1 or 2,
-// any TF-style padding, any channel count; forward and (stride 1) backward-data.
+// any TF-style padding, any channel count; forward, backward-data and backward-filter.
 //
 // The reference layout (NCHW, components stacked on the batch axis) cannot feed tap-shifted TMA boxes: the
 // innermost TMA coordinate must be a multiple of 16 bytes, and a filter tap shifts the pixel axis by single
@@ -225,7 +225,7 @@ qconv_general_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_
 // One thread per (pixel, 8-channel group): reads are coalesced along w, writes are 16-byte vectors.
 template <typename T>
 __global__ void pack_activations_kernel(const T* __restrict__ x, T* __restrict__ xp, int planes /*4*Nb*/, int C, int H, int W,
-                                        int Hp, int Wp, int Cp, int pad_top, int pad_left) {
+                                        int Hp, int Wp, int Cp, int pad_top, int pad_left, int ins_h = 1, int ins_w = 1) {
     const int groups = Cp / 8;
     const size_t total = (size_t)planes * Hp * Wp * groups;
     for (size_t idx = (size_t)blockIdx.x * blockDim.x + threadIdx.x; idx < total; idx += (size_t)gridDim.x * blockDim.x) {
@@ -235,13 +235,21 @@ __global__ void pack_activations_kernel(const T* __restrict__ x, T* __restrict__
         const int grp = (int)(rest % groups); rest /= groups;
         const int hp = (int)(rest % Hp);
         const int plane = (int)(rest / Hp);
-        const int ih = hp - pad_top, iw = wp - pad_left;
+        // ins_h / ins_w > 1 spread the source pixels ins apart with zeros between them (the zero-insertion that
+        // turns the backward-data pass of a strided convolution into a stride-1 correlation)
+        int ih = hp - pad_top, iw = wp - pad_left;
+        bool inside = ih >= 0 && iw >= 0;
+        if (inside && (ins_h > 1 || ins_w > 1)) {
+            inside = (ih % ins_h == 0) && (iw % ins_w == 0);
+            ih /= ins_h; iw /= ins_w;
+        }
+        inside = inside && ih < H && iw < W;
         alignas(16) T vals[8];
 #pragma unroll
         for (int e = 0; e < 8; ++e) {
             const int c = grp * 8 + e;
             T v = T(0.f);
-            if (c < C && (unsigned)ih < (unsigned)H && (unsigned)iw < (unsigned)W) v = x[(((size_t)plane * C + c) * H + ih) * W + iw];
+            if (c < C && inside) v = x[(((size_t)plane * C + c) * H + ih) * W + iw];
             vals[e] = v;
         }
         *reinterpret_cast<uint4*>(xp + (((size_t)plane * Hp + hp) * Wp + wp) * Cp + grp * 8) = *reinterpret_cast<const uint4*>(vals);
@@ -271,6 +279,199 @@ __global__ void pack_filters_kernel(const T* __restrict__ w, T* __restrict__ wex
             if (quat_negative(l, d)) v = -v;
         }
         DType<T>::store(wexp + idx, v);
+    }
+}
+
+
+// ===================================================================================================
+// General backward-filter. Both operands come from channels-last staged copies (dy unpadded, x padded as for
+// the forward pass) and are MN-major: K = output pixels, M = (d, co), N = (l, ci). One work item = one
+// filter tap, one 128-row M tile, one <=256-column N tile and one slice of the pixels; its accumulator is
+// the real-valued gradient block G[(d,co),(l,ci)] which the epilogue folds through the quaternion table,
+//   dw[l^d][co][ci][tap] += s(l,d) * G[(d,co),(l,ci)],
+// into an fp32 scratch laid out [tap][r][co][ci] with vector reductions; a last kernel transposes and casts.
+// (replaces the 8/16 cudnnConvolutionBackwardFilter calls and accumulate passes of src/conv2d.hpp:433-562.)
+// ===================================================================================================
+constexpr int FK = 32;                               // pixels per stage
+constexpr int F_STAGES = 8;
+constexpr uint32_t F_STAGE = (GM + GN) * FK * 2;     // 24 KB
+constexpr size_t FG_SMEM = 1024 + F_STAGES * F_STAGE + 512;
+
+struct FGParams {
+    int Nb, Co, Ci, HO, WO;
+    int Cop, Cip;                 // padded channels per component of dy / x
+    int cbA, cbB;                 // channel-block width (elements) of the two operands: 64, 32 or 16
+    int KH, KW, SH, SW, DH, DW;
+    int PW, PH, PN;               // pixel box per stage, PW*PH*PN == FK
+    int tiles_w, tiles_h, tiles_n;
+    int m_tiles, n_tiles, n_tile_cols;   // N columns per tile (multiple of 16, <= 256)
+    int splits, steps_per_split;
+    int merged_a, merged_b;       // one TMA box brings all channel blocks of the tile (one block per component)
+    int fmt;
+};
+
+__device__ __forceinline__ uint64_t make_desc_mn_blocks(uint32_t smem_addr, int cb, uint32_t block_bytes) {
+    // MN-major tile made of blocks of `cb` elements: K-rows of cb*2 bytes, 8-row groups contiguous.
+    const uint64_t layout = cb == 64 ? 2ull : (cb == 32 ? 4ull : 6ull);
+    return (uint64_t)((smem_addr & 0x3FFFFu) >> 4) | ((uint64_t)((block_bytes >> 4) & 0x3FFFu) << 16) |
+           ((uint64_t)(((8u * cb * 2u) >> 4) & 0x3FFFu) << 32) | DESC_VERSION_SM100 | (layout << 61);
+}
+
+__device__ __forceinline__ void red_add_f32x4(float* addr, float a, float b, float c, float d) {
+    asm volatile("red.global.add.v4.f32 [%0], {%1, %2, %3, %4};" ::"l"(addr), "f"(a), "f"(b), "f"(c), "f"(d) : "memory");
+}
+
+__global__ void __launch_bounds__(G_THREADS, 1)
+qconv_filter_general_tc_kernel(const __grid_constant__ CUtensorMap map_dy, const __grid_constant__ CUtensorMap map_x, FGParams p,
+                               float* __restrict__ dw32, int* __restrict__ status) {
+    extern __shared__ uint8_t smem_raw[];
+    const int t = threadIdx.x, warp = t >> 5, lane = t & 31;
+    uint8_t* base = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+    uint64_t* bars = reinterpret_cast<uint64_t*>(base + F_STAGES * F_STAGE);
+    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 2 * F_STAGES + 1);
+    const uint32_t tiles_addr = smem_u32(base);
+    const uint32_t full_bar = smem_u32(bars), empty_bar = smem_u32(bars + F_STAGES), tmem_full = smem_u32(bars + 2 * F_STAGES);
+
+    // work item of this CTA
+    // items (tap, tiles) vary fastest so that the CTAs running at the same time read the same pixel slice (L2 reuse)
+    const int n_items = p.m_tiles * p.n_tiles * p.KH * p.KW;
+    int item = blockIdx.x % n_items;
+    const int split = blockIdx.x / n_items;
+    const int mt = item % p.m_tiles; item /= p.m_tiles;
+    const int nt = item % p.n_tiles;
+    const int tap = item / p.n_tiles;
+    const int kh = tap / p.KW, kw = tap - kh * p.KW;
+    const int steps_total = p.tiles_w * p.tiles_h * p.tiles_n;
+    const int step_beg = split * p.steps_per_split;
+    const int n_steps = max(0, min(steps_total, step_beg + p.steps_per_split) - step_beg);
+
+    const int nblkA = GM / p.cbA, nblkB = p.n_tile_cols / p.cbB;
+    const int bpcA = p.Cop / p.cbA, bpcB = p.Cip / p.cbB;               // channel blocks per component
+    const uint32_t blkA_bytes = FK * p.cbA * 2, blkB_bytes = FK * p.cbB * 2;
+    const uint32_t a_bytes = nblkA * blkA_bytes, b_bytes = nblkB * blkB_bytes;
+    const int blockA0 = mt * nblkA, blockB0 = nt * (GN / p.cbB);
+
+    if (t == 0) {
+        for (int s = 0; s < F_STAGES; ++s) { mbar_init(full_bar + 8 * s, 1); mbar_init(empty_bar + 8 * s, 1); }
+        mbar_init(tmem_full, 1);
+        fence_barrier_init();
+    }
+    if (warp == 1) tmem_alloc(smem_u32(tmem_slot), 256);
+    tc_fence_before_sync();
+    __syncthreads();
+    tc_fence_after_sync();
+    const uint32_t tmem_base = *tmem_slot;
+
+    if (warp == 0) {
+        if (lane == 0) {
+            bool ok = true;
+            for (int it = 0; it < n_steps && ok; ++it) {
+                const int s = it % F_STAGES;
+                ok = mbar_wait_bounded(empty_bar + 8 * s, ((it / F_STAGES) & 1) ^ 1, status, ST_G_PRODUCER);
+                if (!ok) break;
+                int step = step_beg + it;
+                const int tw = step % p.tiles_w; step /= p.tiles_w;
+                const int th = step % p.tiles_h;
+                const int tn = step / p.tiles_h;
+                const int ow0 = tw * p.PW, oh0 = th * p.PH, n0 = tn * p.PN;
+                const uint32_t a_dst = tiles_addr + s * F_STAGE, b_dst = a_dst + GM * FK * 2, bar = full_bar + 8 * s;
+                mbar_arrive_expect_tx(bar, a_bytes + b_bytes);
+                if (p.merged_a) {
+                    tma_load_5d_g(a_dst, &map_dy, 0, ow0, oh0, n0, blockA0, bar);
+                } else {
+                    for (int b = 0; b < nblkA; ++b) {
+                        const int blk = blockA0 + b;
+                        tma_load_5d_g(a_dst + b * blkA_bytes, &map_dy, (blk % bpcA) * p.cbA, ow0, oh0, n0, blk / bpcA, bar);
+                    }
+                }
+                const int wp0 = ow0 * p.SW + kw * p.DW, hp0 = oh0 * p.SH + kh * p.DH;
+                if (p.merged_b) {
+                    tma_load_5d_g(b_dst, &map_x, 0, wp0, hp0, n0, blockB0, bar);
+                } else {
+                    for (int b = 0; b < nblkB; ++b) {
+                        const int blk = blockB0 + b;
+                        tma_load_5d_g(b_dst + b * blkB_bytes, &map_x, (blk % bpcB) * p.cbB, wp0, hp0, n0, blk / bpcB, bar);
+                    }
+                }
+            }
+        }
+        __syncwarp();
+    } else if (warp == 1) {
+        const uint32_t idesc = make_idesc_f16(p.fmt, GM, p.n_tile_cols, true, true);
+        bool ok = true;
+        for (int it = 0; it < n_steps && ok; ++it) {
+            const int s = it % F_STAGES;
+            ok = mbar_wait_bounded(full_bar + 8 * s, (it / F_STAGES) & 1, status, ST_G_MMA);
+            if (!ok) break;
+            tc_fence_after_sync();
+            if (lane == 0) {
+                const uint32_t a_addr = tiles_addr + s * F_STAGE, b_addr = a_addr + GM * FK * 2;
+#pragma unroll
+                for (int j = 0; j < FK / 16; ++j)
+                    mma_f16_ss(tmem_base, make_desc_mn_blocks(a_addr + j * 16 * p.cbA * 2, p.cbA, blkA_bytes),
+                               make_desc_mn_blocks(b_addr + j * 16 * p.cbB * 2, p.cbB, blkB_bytes), idesc, (it > 0 || j > 0) ? 1u : 0u);
+                mma_commit(empty_bar + 8 * s);
+                if (it == n_steps - 1) mma_commit(tmem_full);
+            }
+            __syncwarp();
+        }
+        if (n_steps == 0 && lane == 0) mbar_arrive(tmem_full);
+        __syncwarp();
+    } else {
+        const int q = warp & 3, chalf = (warp - 2) >> 2;
+        bool ok = mbar_wait_bounded(tmem_full, 0, status, ST_G_EPILOGUE);
+        ok = __all_sync(0xffffffffu, ok && (*reinterpret_cast<volatile int*>(status) == 0));
+        tc_fence_after_sync();
+        if (ok && n_steps > 0) {
+            // row of the tile -> (output component d, channel co)
+            const int row = q * 32 + lane;
+            const int blk = blockA0 + row / p.cbA;
+            const int d = blk / bpcA, co = (blk % bpcA) * p.cbA + row % p.cbA;
+            const bool row_ok = d < 4 && co < p.Co;
+            const size_t comp_stride = (size_t)p.Co * p.Ci;
+            float* tap_base = dw32 + (size_t)tap * 4 * comp_stride;
+#pragma unroll 1
+            for (int cb = 0; cb < 4; ++cb) {
+                const int col0 = chalf * 128 + cb * 32;
+                if (col0 >= p.n_tile_cols) break;                         // warp-uniform
+                uint32_t v[32];
+                tmem_ld_32x32b_x32(tmem_base + ((uint32_t)(q * 32) << 16) + col0, v);
+                tmem_ld_wait();
+                if (!row_ok) continue;
+#pragma unroll
+                for (int g4 = 0; g4 < 8; ++g4) {
+                    const int col = col0 + g4 * 4;                        // 4 consecutive columns share (l, channel block)
+                    if (col >= p.n_tile_cols) continue;
+                    const int nblk = blockB0 + col / p.cbB;
+                    const int l = nblk / bpcB, ci = (nblk % bpcB) * p.cbB + col % p.cbB;
+                    if (l >= 4 || ci >= p.Ci) continue;
+                    const float sgn = quat_negative(l, d) ? -1.f : 1.f;
+                    float* dst = tap_base + (size_t)(l ^ d) * comp_stride + (size_t)co * p.Ci + ci;
+                    if ((p.Ci & 3) == 0) {
+                        red_add_f32x4(dst, sgn * __uint_as_float(v[4 * g4]), sgn * __uint_as_float(v[4 * g4 + 1]),
+                                      sgn * __uint_as_float(v[4 * g4 + 2]), sgn * __uint_as_float(v[4 * g4 + 3]));
+                    } else {
+#pragma unroll
+                        for (int e = 0; e < 4; ++e)
+                            if (ci + e < p.Ci) atomicAdd(dst + e, sgn * __uint_as_float(v[4 * g4 + e]));
+                    }
+                }
+            }
+        }
+    }
+    tc_fence_before_sync();
+    __syncthreads();
+    if (warp == 1) tmem_dealloc(tmem_base, 256);
+}
+
+// scratch [tap][r][co][ci] fp32 -> dw [r][co][ci][tap] in the tensor type
+template <typename T>
+__global__ void unpack_filter_grad_kernel(const float* __restrict__ src, T* __restrict__ dw, int taps, size_t per_tap) {
+    const size_t total = per_tap * taps;
+    for (size_t idx = (size_t)blockIdx.x * blockDim.x + threadIdx.x; idx < total; idx += (size_t)gridDim.x * blockDim.x) {
+        const int tap = (int)(idx % taps);
+        const size_t e = idx / taps;
+        DType<T>::store(dw + idx, src[(size_t)tap * per_tap + e]);
     }
 }
 
@@ -308,6 +509,7 @@ struct Plan {
     int Hin, Win, Hout, Wout;
     int pad_top, pad_left;         // zero padding materialised in the staged copy
     int SH, SW;
+    int ins_h, ins_w;              // zero-insertion factors of the staged copy (strided backward-data)
     int Cp, Hp, Wp, Mp, Kp;
     int KS;
     size_t xp_bytes, w_bytes;
@@ -317,10 +519,12 @@ Plan make_plan(Pass pass, const Geom& g) {
     Plan pl;
     if (pass == PASS_FWD) {
         pl.Cin = g.Ci; pl.Cout = g.Co; pl.Hin = g.H; pl.Win = g.W; pl.Hout = g.HO; pl.Wout = g.WO;
-        pl.pad_top = g.PT; pl.pad_left = g.PL; pl.SH = g.SH; pl.SW = g.SW;
-    } else {   // backward-data, stride 1: correlation of dy (padded by k-1-pad) with the flipped, transposed filters
+        pl.pad_top = g.PT; pl.pad_left = g.PL; pl.SH = g.SH; pl.SW = g.SW; pl.ins_h = pl.ins_w = 1;
+    } else {   // backward-data: stride-1 correlation of dy (zero-inserted by the stride, padded by k-1-pad) with the
+               // flipped, transposed filters
         pl.Cin = g.Co; pl.Cout = g.Ci; pl.Hin = g.HO; pl.Win = g.WO; pl.Hout = g.H; pl.Wout = g.W;
         pl.pad_top = (g.KH - 1) * g.DH - g.PT; pl.pad_left = (g.KW - 1) * g.DW - g.PL; pl.SH = 1; pl.SW = 1;
+        pl.ins_h = g.SH; pl.ins_w = g.SW;
     }
     pl.Cp = round_up(pl.Cin, 16);
     pl.KS = (pl.Cp % 32 == 0) ? 32 : 16;
@@ -342,7 +546,6 @@ bool conv_tc_supported(Pass pass, int dtype, int variant, const Geom& g) {
     if (g.H * g.W == 1) return false;                                   // dense layers stay on the CUDA-core kernels
     if (g.SH > 2 || g.SW > 2) return false;
     if (pass == PASS_BWD_DATA) {
-        if (g.SH != 1 || g.SW != 1) return false;                       // strided backward-data: CUDA-core kernels
         if ((g.KH - 1) * g.DH < g.PT || (g.KW - 1) * g.DW < g.PL) return false;
     }
     const Plan pl = make_plan(pass, g);
@@ -374,12 +577,12 @@ int conv_tc_launch(Pass pass, int dtype, const Geom& g, const void* w, const voi
         const int wblocks = (int)((wtotal + 255) / 256 < (size_t)sm_count_g() * 8 ? (wtotal + 255) / 256 : (size_t)sm_count_g() * 8);
         if (fmt == 0) {
             pack_activations_kernel<__half><<<blocks, 256, 0, stream>>>((const __half*)act, (__half*)xp, 4 * g.Nb, pl.Cin, pl.Hin, pl.Win,
-                                                                       pl.Hp, pl.Wp, pl.Cp, pl.pad_top, pl.pad_left);
+                                                                       pl.Hp, pl.Wp, pl.Cp, pl.pad_top, pl.pad_left, pl.ins_h, pl.ins_w);
             pack_filters_kernel<__half><<<wblocks, 256, 0, stream>>>((const __half*)w, (__half*)wexp, g.Co, g.Ci, taps, pl.Mp, pl.Kp, pl.Cp,
                                                                     pass == PASS_BWD_DATA ? 1 : 0);
         } else {
             pack_activations_kernel<__nv_bfloat16><<<blocks, 256, 0, stream>>>((const __nv_bfloat16*)act, (__nv_bfloat16*)xp, 4 * g.Nb, pl.Cin,
-                                                                              pl.Hin, pl.Win, pl.Hp, pl.Wp, pl.Cp, pl.pad_top, pl.pad_left);
+                                                                              pl.Hin, pl.Win, pl.Hp, pl.Wp, pl.Cp, pl.pad_top, pl.pad_left, pl.ins_h, pl.ins_w);
             pack_filters_kernel<__nv_bfloat16><<<wblocks, 256, 0, stream>>>((const __nv_bfloat16*)w, (__nv_bfloat16*)wexp, g.Co, g.Ci, taps,
                                                                            pl.Mp, pl.Kp, pl.Cp, pass == PASS_BWD_DATA ? 1 : 0);
         }
@@ -439,6 +642,131 @@ int conv_tc_launch(Pass pass, int dtype, const Geom& g, const void* w, const voi
         PCB_CUDA_TRY(cudaFuncSetAttribute(qconv_general_tc_kernel<16>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
         qconv_general_tc_kernel<16><<<grid, G_THREADS, smem, stream>>>(map_w, map_x, p, (const uint16_t*)bias, (uint16_t*)out, status);
     }
+    PCB_CUDA_TRY(cudaGetLastError());
+    return PCB_OK;
+}
+
+namespace {
+int channel_block(int cp) { return cp % 64 == 0 ? 64 : (cp % 32 == 0 ? 32 : 16); }
+
+struct FilterPlan {
+    int Cop, Cip, Hp, Wp;
+    size_t xp_bytes, dyp_bytes, acc_bytes;
+};
+
+FilterPlan make_filter_plan(const Geom& g) {
+    FilterPlan f;
+    f.Cop = round_up(g.Co, 16);
+    f.Cip = round_up(g.Ci, 16);
+    f.Hp = (g.HO - 1) * g.SH + (g.KH - 1) * g.DH + 1;
+    f.Wp = (g.WO - 1) * g.SW + (g.KW - 1) * g.DW + 1;
+    f.xp_bytes = ((size_t)4 * g.Nb * f.Hp * f.Wp * f.Cip * 2 + 1023) / 1024 * 1024;
+    f.dyp_bytes = ((size_t)4 * g.Nb * g.HO * g.WO * f.Cop * 2 + 1023) / 1024 * 1024;
+    f.acc_bytes = ((size_t)4 * g.Co * g.Ci * g.KH * g.KW * sizeof(float) + 1023) / 1024 * 1024;
+    return f;
+}
+}  // namespace
+
+bool conv_filter_tc_supported(int dtype, int variant, const Geom& g) {
+    if (dtype != PCB_F16 && dtype != PCB_BF16) return false;
+    if (variant != PCB_VARIANT_16_PRODUCT || g.real_in || g.w_io || g.dw_io) return false;
+    if (g.H * g.W == 1) return false;
+    if (g.SH > 2 || g.SW > 2) return false;
+    const FilterPlan f = make_filter_plan(g);
+    if (f.Hp > 65535 || f.Wp > 65535 || f.xp_bytes + f.dyp_bytes > (size_t)12 << 30) return false;
+    return true;
+}
+
+size_t conv_filter_tc_scratch_bytes(const Geom& g) {
+    const FilterPlan f = make_filter_plan(g);
+    return f.xp_bytes + f.dyp_bytes + f.acc_bytes;
+}
+
+int conv_filter_tc_launch(int dtype, const Geom& g, const void* dy, const void* x, void* dw, void* scratch, int* status,
+                          cudaStream_t stream) {
+    EncodeTiledFnG encode = encode_fn_g();
+    if (!encode) { set_error("cuTensorMapEncodeTiled is not available from the driver"); return PCB_ERR_CUDA; }
+    const int fmt = dtype == PCB_F16 ? 0 : 1;
+    const FilterPlan f = make_filter_plan(g);
+    const int taps = g.KH * g.KW;
+    uint8_t* xp = static_cast<uint8_t*>(scratch);
+    uint8_t* dyp = xp + f.xp_bytes;
+    float* acc = reinterpret_cast<float*>(dyp + f.dyp_bytes);
+
+    {   // stage both activations channels-last
+        const size_t tx = (size_t)4 * g.Nb * f.Hp * f.Wp * (f.Cip / 8), ty = (size_t)4 * g.Nb * g.HO * g.WO * (f.Cop / 8);
+        const size_t cap = (size_t)sm_count_g() * 16;
+        const int bx = (int)((tx + 255) / 256 < cap ? (tx + 255) / 256 : cap), by = (int)((ty + 255) / 256 < cap ? (ty + 255) / 256 : cap);
+        if (fmt == 0) {
+            pack_activations_kernel<__half><<<bx, 256, 0, stream>>>((const __half*)x, (__half*)xp, 4 * g.Nb, g.Ci, g.H, g.W, f.Hp, f.Wp, f.Cip, g.PT, g.PL);
+            pack_activations_kernel<__half><<<by, 256, 0, stream>>>((const __half*)dy, (__half*)dyp, 4 * g.Nb, g.Co, g.HO, g.WO, g.HO, g.WO, f.Cop, 0, 0);
+        } else {
+            pack_activations_kernel<__nv_bfloat16><<<bx, 256, 0, stream>>>((const __nv_bfloat16*)x, (__nv_bfloat16*)xp, 4 * g.Nb, g.Ci, g.H, g.W, f.Hp, f.Wp, f.Cip, g.PT, g.PL);
+            pack_activations_kernel<__nv_bfloat16><<<by, 256, 0, stream>>>((const __nv_bfloat16*)dy, (__nv_bfloat16*)dyp, 4 * g.Nb, g.Co, g.HO, g.WO, g.HO, g.WO, f.Cop, 0, 0);
+        }
+        PCB_CUDA_TRY(cudaGetLastError());
+        PCB_CUDA_TRY(cudaMemsetAsync(acc, 0, (size_t)4 * g.Co * g.Ci * taps * sizeof(float), stream));
+    }
+
+    FGParams p;
+    p.Nb = g.Nb; p.Co = g.Co; p.Ci = g.Ci; p.HO = g.HO; p.WO = g.WO; p.Cop = f.Cop; p.Cip = f.Cip;
+    p.cbA = channel_block(f.Cop); p.cbB = channel_block(f.Cip);
+    p.KH = g.KH; p.KW = g.KW; p.SH = g.SH; p.SW = g.SW; p.DH = g.DH; p.DW = g.DW; p.fmt = fmt;
+    {   // pixel box of FK = 32 pixels wasting the fewest K rows
+        long long best = -1;
+        for (int pw = 1; pw <= FK; pw *= 2)
+            for (int ph = 1; ph * pw <= FK; ph *= 2) {
+                const int pn = FK / (pw * ph);
+                const long long vol = (long long)round_up(g.WO, pw) * round_up(g.HO, ph) * round_up(g.Nb, pn);
+                if (best < 0 || vol < best || (vol == best && pw > p.PW)) { best = vol; p.PW = pw; p.PH = ph; p.PN = pn; }
+            }
+    }
+    p.tiles_w = (g.WO + p.PW - 1) / p.PW; p.tiles_h = (g.HO + p.PH - 1) / p.PH; p.tiles_n = (g.Nb + p.PN - 1) / p.PN;
+    const int m_cols = 4 * f.Cop, n_cols = 4 * f.Cip;
+    p.m_tiles = (m_cols + GM - 1) / GM;
+    p.n_tiles = (n_cols + GN - 1) / GN;
+    p.n_tile_cols = n_cols < GN ? n_cols : GN;           // 4*Cip is a multiple of 64; tiles of a multi-tile problem are full or padded by zero blocks
+    p.merged_a = (f.Cop == p.cbA) ? 1 : 0;
+    p.merged_b = (f.Cip == p.cbB) ? 1 : 0;
+    const int steps_total = p.tiles_w * p.tiles_h * p.tiles_n;
+    const int items = taps * p.m_tiles * p.n_tiles;
+    int splits = (2 * sm_count_g() + items - 1) / items;
+    if (splits > steps_total) splits = steps_total;
+    if (splits < 1) splits = 1;
+    p.steps_per_split = (steps_total + splits - 1) / splits;
+    p.splits = (steps_total + p.steps_per_split - 1) / p.steps_per_split;
+
+    const CUtensorMapDataType dt = fmt == 0 ? CU_TENSOR_MAP_DATA_TYPE_FLOAT16 : CU_TENSOR_MAP_DATA_TYPE_BFLOAT16;
+    auto swz = [](int cb) { return cb == 64 ? CU_TENSOR_MAP_SWIZZLE_128B : (cb == 32 ? CU_TENSOR_MAP_SWIZZLE_64B : CU_TENSOR_MAP_SWIZZLE_32B); };
+    alignas(64) CUtensorMap map_dy, map_x;
+    {
+        const cuuint64_t dims[5] = {(cuuint64_t)f.Cop, (cuuint64_t)g.WO, (cuuint64_t)g.HO, (cuuint64_t)g.Nb, 4};
+        const cuuint64_t strides[4] = {(cuuint64_t)f.Cop * 2, (cuuint64_t)g.WO * f.Cop * 2, (cuuint64_t)g.HO * g.WO * f.Cop * 2,
+                                       (cuuint64_t)g.Nb * g.HO * g.WO * f.Cop * 2};
+        const cuuint32_t box[5] = {(cuuint32_t)p.cbA, (cuuint32_t)p.PW, (cuuint32_t)p.PH, (cuuint32_t)p.PN, (cuuint32_t)(p.merged_a ? GM / p.cbA : 1)};
+        const cuuint32_t es[5] = {1, 1, 1, 1, 1};
+        const CUresult r = encode(&map_dy, dt, 5, dyp, dims, strides, box, es, CU_TENSOR_MAP_INTERLEAVE_NONE, swz(p.cbA),
+                                  CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+        if (r != CUDA_SUCCESS) { set_error("cuTensorMapEncodeTiled (dy) failed with code %d", (int)r); return PCB_ERR_CUDA; }
+    }
+    {
+        const cuuint64_t dims[5] = {(cuuint64_t)f.Cip, (cuuint64_t)f.Wp, (cuuint64_t)f.Hp, (cuuint64_t)g.Nb, 4};
+        const cuuint64_t strides[4] = {(cuuint64_t)f.Cip * 2, (cuuint64_t)f.Wp * f.Cip * 2, (cuuint64_t)f.Hp * f.Wp * f.Cip * 2,
+                                       (cuuint64_t)g.Nb * f.Hp * f.Wp * f.Cip * 2};
+        const cuuint32_t box[5] = {(cuuint32_t)p.cbB, (cuuint32_t)((p.PW - 1) * g.SW + 1), (cuuint32_t)((p.PH - 1) * g.SH + 1), (cuuint32_t)p.PN,
+                                   (cuuint32_t)(p.merged_b ? p.n_tile_cols / p.cbB : 1)};
+        const cuuint32_t es[5] = {1, (cuuint32_t)g.SW, (cuuint32_t)g.SH, 1, 1};
+        const CUresult r = encode(&map_x, dt, 5, xp, dims, strides, box, es, CU_TENSOR_MAP_INTERLEAVE_NONE, swz(p.cbB),
+                                  CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+        if (r != CUDA_SUCCESS) { set_error("cuTensorMapEncodeTiled (x) failed with code %d", (int)r); return PCB_ERR_CUDA; }
+    }
+    PCB_CUDA_TRY(cudaFuncSetAttribute(qconv_filter_general_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)FG_SMEM));
+    qconv_filter_general_tc_kernel<<<items * p.splits, G_THREADS, FG_SMEM, stream>>>(map_dy, map_x, p, acc, status);
+    PCB_CUDA_TRY(cudaGetLastError());
+    const size_t per_tap = (size_t)4 * g.Co * g.Ci, total = per_tap * taps;
+    const int blocks = (int)((total + 255) / 256 < 2368 ? (total + 255) / 256 : 2368);
+    if (fmt == 0) unpack_filter_grad_kernel<__half><<<blocks, 256, 0, stream>>>(acc, (__half*)dw, taps, per_tap);
+    else unpack_filter_grad_kernel<__nv_bfloat16><<<blocks, 256, 0, stream>>>(acc, (__nv_bfloat16*)dw, taps, per_tap);
     PCB_CUDA_TRY(cudaGetLastError());
     return PCB_OK;
 }

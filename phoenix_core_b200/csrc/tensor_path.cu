@@ -383,14 +383,19 @@ bool legacy_supported(int dtype, int variant, const Geom& g) {
 }  // namespace
 
 bool tensor_path_supported(Pass pass, int dtype, int variant, const Geom& g) {
-    if (pass == PASS_BWD_FILTER) return pointwise_filter_tc_supported(dtype, variant, g) || legacy_supported(dtype, variant, g);
+    if (pass == PASS_BWD_FILTER)
+        return pointwise_filter_tc_supported(dtype, variant, g) || conv_filter_tc_supported(dtype, variant, g) || legacy_supported(dtype, variant, g);
     return pointwise_tc_supported(pass, dtype, variant, g) || conv_tc_supported(pass, dtype, variant, g) ||
            legacy_supported(dtype, variant, g);
 }
 
 size_t tensor_scratch_bytes(Pass pass, int dtype, int variant, int engine, const Geom& g) {
     if (engine == PCB_ENGINE_SIMT || !tensor_path_supported(pass, dtype, variant, g)) return 0;
-    if (pass == PASS_BWD_FILTER) return (size_t)4 * g.Co * g.Ci * g.KH * g.KW * sizeof(float);
+    if (pass == PASS_BWD_FILTER) {
+        if (pointwise_filter_tc_supported(dtype, variant, g)) return (size_t)4 * g.Co * g.Ci * g.KH * g.KW * sizeof(float);
+        if (conv_filter_tc_supported(dtype, variant, g)) return conv_filter_tc_scratch_bytes(g);
+        return (size_t)4 * g.Co * g.Ci * g.KH * g.KW * sizeof(float);
+    }
     if (pointwise_tc_supported(pass, dtype, variant, g)) return 0;
     if (conv_tc_supported(pass, dtype, variant, g)) return conv_tc_scratch_bytes(pass, g);
     return 0;
@@ -419,6 +424,7 @@ int tensor_launch(Pass pass, int dtype, int /*variant*/, const Geom& g, const vo
     // accumulate in fp32 scratch, then cast once.
     if (scratch == nullptr) { set_error("backward-filter needs fp32 scratch"); return PCB_ERR_WORKSPACE; }
     if (pointwise_filter_tc_supported(dtype, PCB_VARIANT_16_PRODUCT, g)) return pointwise_filter_tc_launch(dtype, g, a, b, out, scratch, status, stream);
+    if (conv_filter_tc_supported(dtype, PCB_VARIANT_16_PRODUCT, g)) return conv_filter_tc_launch(dtype, g, a, b, out, scratch, status, stream);
     const int tiles = ((p.M + TBM - 1) / TBM) * ((p.N + TBN - 1) / TBN);
     int splits = (2 * sm_count() + tiles - 1) / tiles;
     const int max_splits = (p.K + 4 * TBK - 1) / (4 * TBK);

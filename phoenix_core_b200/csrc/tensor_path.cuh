@@ -27,4 +27,9 @@ size_t conv_tc_scratch_bytes(Pass pass, const Geom& g);
 int conv_tc_launch(Pass pass, int dtype, const Geom& g, const void* w, const void* act, const void* bias, void* out,
                    void* scratch, int* status, cudaStream_t stream);
 
+bool conv_filter_tc_supported(int dtype, int variant, const Geom& g);
+size_t conv_filter_tc_scratch_bytes(const Geom& g);
+int conv_filter_tc_launch(int dtype, const Geom& g, const void* dy, const void* x, void* dw, void* scratch, int* status,
+                          cudaStream_t stream);
+
 }  // namespace pcb

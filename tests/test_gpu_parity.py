@@ -135,6 +135,8 @@ GENERAL_TENSOR_SHAPES = [
     (2, 24, 16, 6, 5, 1, 1, (1, 1), (0, 0, 0, 0)),       # narrow pointwise layer with unaligned planes
     (1, 48, 40, 9, 11, 3, 2, (1, 2), (1, 0, 1, 1)),      # ragged everything, mixed strides, 48 = 3 x 16 channels
     (5, 32, 32, 28, 28, 3, 3, (1, 1), (1, 1, 1, 1)),     # several tiles per CTA: both accumulator buffers in use
+    (2, 128, 64, 8, 8, 3, 3, (1, 1), (1, 1, 1, 1)),      # filter gradient with two channel blocks per component (N = 512: two tiles)
+    (2, 64, 128, 10, 6, 3, 3, (2, 2), (1, 1, 1, 1)),     # strided backward-data by zero insertion; M = 512
 ]
 
 
@@ -150,7 +152,7 @@ def test_general_conv_tensor_core_vs_oracle(gpu, oracle, shape, dtype):
     _check(got, ref, dtype, gpu, "y")
     dy = gpu.rounded(normal(44, ref.shape), dtype)
     rdw, rdx = oracle.conv2d_bwd(x, w, dy, stride, (1, 1), pad)
-    dw, dx = gpu.run_conv_bwd(x, w, dy, stride, pad, dtype, "16p", "auto", True)
+    dw, dx = gpu.run_conv_bwd(x, w, dy, stride, pad, dtype, "16p", "tensor", True)
     _check(dx, rdx, dtype, gpu, "dx")
     _check(dw, rdw, dtype, gpu, "dw")
 
