@@ -7,7 +7,7 @@ Standard ResNet-18 topology with every real channel count divided by 4 (quaterni
 versions (`conv2DFwd/Bwd`, `denseFwd/Bwd` of this package). The UpStride engine itself contains no model code:
 batch-norm, ReLU, pooling, loss and optimiser are plain torch ops and are harness glue, not part of the
 drop-in path. Batch-norm normalises each quaternion channel with one mean / variance shared by its four
-components (a `BatchNorm2d` over the stacked `[4N, C, H, W]` tensor).
+components (statistics over the stacked `[4N, C, H, W]` tensor), written with torch reductions and broadcasts.
 
 Precision: fp16 activations and filters (the reference's fp16 tensors; every kernel accumulates in fp32),
 fp32 master weights, static loss scale. All filter gradients are written by the kernels straight into ONE
@@ -43,6 +43,56 @@ def reduce_and_apply(flat_w32, flat_mom, flat_grad, world, lr, momentum, loss_sc
     inv = 1.0 / (loss_scale * world)
     flat_mom.mul_(momentum).add_(flat_grad.float(), alpha=inv)
     flat_w32.add_(flat_mom, alpha=-lr)
+
+
+class _BNReLUFn(torch.autograd.Function):
+    """Batch-norm over the stacked [4N, C, H, W] tensor (one mean / variance per quaternion channel, shared by its
+    four components) with an optional fused ReLU, written with plain reductions and broadcast element-wise ops:
+    torch's own batch-norm kernels (native and cuDNN alike) launch one block per channel, which at 16 channels and
+    a stacked batch of 512 leaves the GPU idle. Harness glue, not part of the drop-in path."""
+
+    @staticmethod
+    def forward(ctx, x, gamma, beta, eps, relu):
+        var, mean = torch.var_mean(x.float() if x.numel() < (1 << 22) else x, dim=(0, 2, 3), unbiased=False)
+        var, mean = var.float(), mean.float()
+        invstd = torch.rsqrt(var + eps)
+        scale = (gamma * invstd)
+        shift = beta - mean * scale
+        y = torch.addcmul(shift.to(x.dtype).view(1, -1, 1, 1), x, scale.to(x.dtype).view(1, -1, 1, 1))
+        if relu:
+            y.clamp_min_(0)
+        ctx.relu = relu
+        ctx.save_for_backward(x, y if relu else None, mean, invstd, gamma)
+        return y
+
+    @staticmethod
+    def backward(ctx, dy):
+        x, y, mean, invstd, gamma = ctx.saved_tensors
+        g = dy * (y > 0) if ctx.relu else dy
+        m = x.numel() // x.shape[1]
+        sum_g = g.sum(dim=(0, 2, 3), dtype=torch.float32)
+        sum_gx = (g * x).sum(dim=(0, 2, 3), dtype=torch.float32)
+        # xhat = (x - mean) * invstd;  dgamma = sum(g * xhat);  dbeta = sum(g)
+        dgamma = (sum_gx - mean * sum_g) * invstd
+        dbeta = sum_g
+        # dx = gamma*invstd * (g - dbeta/m - xhat * dgamma/m)  =  a*g + b*x + c   per channel
+        a = gamma * invstd
+        b = -a * invstd * dgamma / m
+        c = -a * dbeta / m - b * mean
+        dx = g * a.to(g.dtype).view(1, -1, 1, 1)
+        dx.addcmul_(x, b.to(g.dtype).view(1, -1, 1, 1))
+        dx.add_(c.to(g.dtype).view(1, -1, 1, 1))
+        return dx, dgamma, dbeta, None, None
+
+
+class BNReLU:
+    def __init__(self, c, device, relu):
+        self.weight = torch.ones(c, dtype=torch.float32, device=device, requires_grad=True)
+        self.bias = torch.zeros(c, dtype=torch.float32, device=device, requires_grad=True)
+        self.relu = relu
+
+    def __call__(self, x, relu=None):
+        return _BNReLUFn.apply(x, self.weight, self.bias, 1e-5, self.relu if relu is None else relu)
 
 
 class _QConvFn(torch.autograd.Function):
@@ -190,8 +240,8 @@ class QResNet18:
         self.convs.append(c)
         return c
 
-    def _bn(self, c):
-        bn = torch.nn.BatchNorm2d(c).to(self.device)
+    def _bn(self, c, relu=True):
+        bn = BNReLU(c, self.device, relu)
         self.bns.append(bn)
         return bn
 
@@ -204,15 +254,15 @@ class QResNet18:
         n = images.shape[0]
         x = torch.zeros((4 * n,) + tuple(images.shape[1:]), dtype=torch.float16, device=images.device)
         x[:n] = images
-        x = F.relu_(self.bn1(self.conv1(x)))
+        x = self.bn1(self.conv1(x))
         x = F.max_pool2d(x, 3, 2, 1)
         for blocks in self.stages:
             for blk in blocks:
                 idt = x
-                out = F.relu_(blk["b1"](blk["c1"](x)))
-                out = blk["b2"](blk["c2"](out))
+                out = blk["b1"](blk["c1"](x))
+                out = blk["b2"](blk["c2"](out), relu=False)
                 if blk["ds"] is not None:
-                    idt = blk["ds"][1](blk["ds"][0](x))
+                    idt = blk["ds"][1](blk["ds"][0](x), relu=False)
                 x = F.relu_(out + idt)
         x = x.mean(dim=(2, 3))                                   # [4N, 128]
         y = self.fc(x.contiguous())                              # [4N, 250]
@@ -252,7 +302,7 @@ def run(batch, steps, warmup, image=224, quiet=False):
     if world > 1 and not dist.is_initialized():
         dist.init_process_group("nccl", device_id=device)
         own_pg = True
-    torch.backends.cudnn.enabled = False                         # glue runs on torch's native kernels, not cuDNN
+    torch.backends.cudnn.enabled = False                         # nothing here may fall into cuDNN
     model = QResNet18(device, seed=0)
     if world > 1:                                                # identical replicas
         dist.broadcast(model.flat_w32, 0)
@@ -285,7 +335,7 @@ def run(batch, steps, warmup, image=224, quiet=False):
         images.copy_(host_images, non_blocking=True)
         labels.copy_(host_labels, non_blocking=True)
         loss = model.train_step(images, labels, world)
-        loss_host = float(loss)
+        loss_host = float(loss.detach())
     b.record()
     sync()
     e2e_ms = a.elapsed_time(b)
@@ -302,7 +352,7 @@ def run(batch, steps, warmup, image=224, quiet=False):
                   "parameters": model.num_parameters(),
                   "e2e": {"value": batch * world * e2e_steps / (e2e_ms * 1e-3), "unit": "images/s",
                           "h2d_bytes_per_step": host_images.numel() * 2 + host_labels.numel() * 8, "d2h_bytes_per_step": 4},
-                  "glue": "batch-norm / ReLU / pooling / loss / SGD are torch ops (not in the reference); cuDNN disabled"}
+                  "glue": "batch-norm / ReLU / pooling / loss / SGD are torch ops (not in the reference); convolutions and dense: this package only"}
         if not quiet:
             print(json.dumps(result), flush=True)
     if own_pg:
