@@ -177,6 +177,29 @@ def test_real_valued_input(gpu, oracle):
     _check(got, ref, "f32", gpu, "y (real input)")
 
 
+@pytest.mark.parametrize("dtype", ["f16", "bf16"])
+def test_real_valued_input_on_tensor_cores(gpu, oracle, dtype):
+    """The stem configuration: real RGB input, 7x7 stride 2, SAME padding; forward and filter gradient (the
+    input gradient of a real-valued input does not exist)."""
+    import ctypes
+    import phoenix_core_b200 as pcb
+    from phoenix_core_b200 import _lib
+    x = gpu.rounded(uniform(23, (3, 3, 30, 26)), dtype)
+    w = gpu.rounded(normal(24, (4, 16, 3, 7, 7), std=0.08), dtype)
+    stride, pad = (2, 2), (2, 2, 3, 3)
+    ref = oracle.conv2d_fwd(x, w, None, stride, (1, 1), pad, real_input=True)
+    got = gpu.run_conv_fwd(x, w, None, stride, pad, dtype, "16p", "tensor", real_input=True)
+    _check(got, ref, dtype, gpu, "y (real input)")
+    # filter gradient: a real input is the quaternion input with zero imaginary parts
+    dy = gpu.rounded(normal(25, ref.shape), dtype)
+    xq = np.concatenate([x, np.zeros((9,) + x.shape[1:], np.float32)], 0)
+    rdw, _ = oracle.conv2d_bwd(xq, w, dy, stride, (1, 1), pad, need_dx=False)
+    _, bwd = gpu.conv_descriptors(x.shape, w.shape, stride, pad, False, False, real_input=True)
+    dw = torch.full(w.shape, float("nan"), dtype=gpu.TORCH_DTYPES[dtype], device="cuda")
+    pcb.conv2DBwd(gpu.dev(x, dtype), gpu.dev(w, dtype), gpu.dev(dy, dtype), dw, None, bwd, gpu.context("16p"), _lib.ENGINE_TENSOR)
+    _check(gpu.host(dw), rdw, dtype, gpu, "dw (real input)")
+
+
 def test_empty_batch(gpu):
     import phoenix_core_b200 as pcb
     fwd, bwd = gpu.conv_descriptors((0, 3, 5, 5), (4, 2, 3, 3, 3), (1, 1), (1, 1, 1, 1), False, True)
