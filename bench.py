@@ -11,6 +11,8 @@ batch (weak scaling) and the filter gradient is summed across ranks with one NCC
 Prints one JSON line: device-timed throughput with inputs resident in HBM (`value`), the same metric through
 the public API from pinned host buffers (`e2e`), the roofline of the slowest kernel, and a CPU baseline
 (the reference's 8-product orchestration over oneDNN via torch CPU ops) on a bounded sample.
+The same line carries `qresnet18`: images/s of a quaternion ResNet-18 training step (batch 128 per GPU, 224x224,
+fp16, data-parallel with one NCCL all-reduce of the flat filter-gradient bucket) from `phoenix_core_b200.qresnet`.
 `--impl reference` times only that CPU orchestration.
 """
 import argparse
@@ -273,6 +275,14 @@ def run_ours(args):
                "h2d_bytes_per_step": nb(hx) + nb(hw) + nb(hdy), "d2h_bytes_per_step": nb(hy) + nb(hdw) + nb(hdx),
                "steps": e2e_steps, "ms_per_step": e2e_ms / e2e_steps}
 
+    # second headline of the metric: quaternion ResNet-18 training images/s on the same ranks
+    qres = None
+    if not args.kernels_only and args.batch is None:
+        del hx, hw, hdy, hy, hdx, hdw
+        torch.cuda.empty_cache()
+        from phoenix_core_b200 import qresnet
+        qres = qresnet.run(batch=128, steps=max(3, min(args.steps, 10)), warmup=3, quiet=True)
+
     if rank == 0:
         peaks = read_peaks()
         fl = flops_per_pass(n, ci, co, h, w)
@@ -306,6 +316,8 @@ def run_ours(args):
             "e2e": e2e,
             "gpu_launches": 4 * args.steps,
         }
+        if qres is not None:
+            line["qresnet18"] = qres
         if args.batch is not None:
             line["reduced_batch"] = "profiling run, not a benchmark value"
         if cpu_v is not None:
