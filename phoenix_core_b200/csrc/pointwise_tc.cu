@@ -15,8 +15,9 @@
 // (cp.async.bulk.tensor, 128B / 64B swizzle) straight into the tcgen05 canonical layouts.
 //
 // CTA (persistent, one per SM): warp 0 = TMA producer, warp 1 = TMEM owner + MMA issuer, warps 2-9 =
-// epilogue (two warps per TMEM lane quadrant; each thread drains 2 components x 128 pixels of one output
-// channel into packed registers, releases the accumulators, then stores). Tile = 128 channels x 128
+// epilogue (two warps per TMEM lane quadrant, one per 64-pixel half; accumulators are drained component by
+// component into packed registers and released one at a time, so the next tile's MMAs overlap the drain; the
+// global stores come last). Tile = 128 channels x 128
 // pixels x 4 components (all 512 TMEM columns); K slice per stage = 32 channels per component
 // (A 32 KB + B 32 KB), 3 stages. Every mbarrier wait is bounded; an expired wait sets the status word and
 // the CTA leaves through the common teardown.
@@ -39,7 +40,8 @@ constexpr uint32_t B_BYTES = 2 * 4 * KS * 64 * 2;  // 32 KB: 2 pixel boxes x 4 a
 constexpr uint32_t B_BOX_BYTES = 4 * KS * 64 * 2;  // 16 KB
 constexpr uint32_t STAGE_BYTES = A_BYTES + B_BYTES;
 constexpr int U_THREADS = 320;
-constexpr size_t U_SMEM_BYTES = 1024 + U_STAGES * STAGE_BYTES + 256;
+constexpr int MAX_RESIDENT_K = 4;                  // weight K slices that may stay in shared memory (4 x 32 KB)
+constexpr size_t U_SMEM_BYTES = 1024 + (MAX_RESIDENT_K * A_BYTES + U_STAGES * B_BYTES) + 256;   // >= U_STAGES * STAGE_BYTES
 constexpr int ST_U_PRODUCER = 0x10, ST_U_MMA = 0x20, ST_U_EPILOGUE = 0x40;
 
 struct UParams {
@@ -50,6 +52,7 @@ struct UParams {
     int fmt;                 // 0 f16, 1 bf16
     int has_bias;
     int bwd;                 // 0 forward, 1 backward-data
+    int a_resident;          // forward: the CTA's weight slices are loaded once and stay in shared memory
 };
 
 __device__ __forceinline__ void tma_load_4d(uint32_t dst, const CUtensorMap* map, int c0, int c1, int c2, int c3, uint32_t bar) {
@@ -61,6 +64,12 @@ __device__ __forceinline__ void tma_load_3d(uint32_t dst, const CUtensorMap* map
     asm volatile(
         "cp.async.bulk.tensor.3d.shared::cluster.global.tile.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3, %4}], [%5];"
         ::"r"(dst), "l"(map), "r"(c0), "r"(c1), "r"(c2), "r"(bar) : "memory");
+}
+
+// 32-byte store: one full sector per thread and half as many store instructions as 16-byte stores.
+__device__ __forceinline__ void st_global_v8(void* addr, const uint32_t* v) {
+    asm volatile("st.global.v8.b32 [%0], {%1, %2, %3, %4, %5, %6, %7, %8};"
+                 ::"l"(addr), "r"(v[0]), "r"(v[1]), "r"(v[2]), "r"(v[3]), "r"(v[4]), "r"(v[5]), "r"(v[6]), "r"(v[7]) : "memory");
 }
 
 constexpr uint64_t DESC_SWIZZLE_64B = 4ull << 61;
@@ -76,19 +85,27 @@ qconv_pointwise_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __gri
     extern __shared__ uint8_t smem_raw[];
     const int t = threadIdx.x, warp = t >> 5, lane = t & 31;
     uint8_t* base = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
-    uint64_t* bars = reinterpret_cast<uint64_t*>(base + U_STAGES * STAGE_BYTES);
-    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 2 * U_STAGES + 2);
+    uint64_t* bars = reinterpret_cast<uint64_t*>(base + MAX_RESIDENT_K * A_BYTES + U_STAGES * B_BYTES);
+    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 2 * U_STAGES + 6);
     const uint32_t tiles_addr = smem_u32(base);
     const uint32_t full_bar = smem_u32(bars), empty_bar = smem_u32(bars + U_STAGES);
+    const uint32_t a_full = smem_u32(bars + 2 * U_STAGES + 5);
+    // one "accumulator drained" barrier per component, so the next tile's MMAs can start on component 0 while
+    // the epilogue is still reading components 1..3
     const uint32_t tmem_full = smem_u32(bars + 2 * U_STAGES), tmem_empty = smem_u32(bars + 2 * U_STAGES + 1);
 
     const int n_tiles = p.n_px_tiles * p.n_c_tiles;
     const int n_k = (p.Cred + KS - 1) / KS;
+    // shared-memory plan: either a ring of [A|B] stages, or all weight slices resident followed by a ring of B stages
+    const bool resident = !BWD && p.a_resident;
+    auto a_slot = [&](int k, int s) { return resident ? tiles_addr + k * A_BYTES : tiles_addr + s * STAGE_BYTES; };
+    auto b_slot = [&](int s) { return resident ? tiles_addr + n_k * A_BYTES + s * B_BYTES : tiles_addr + s * STAGE_BYTES + A_BYTES; };
 
     if (t == 0) {
         for (int s = 0; s < U_STAGES; ++s) { mbar_init(full_bar + 8 * s, 1); mbar_init(empty_bar + 8 * s, 1); }
         mbar_init(tmem_full, 1);
-        mbar_init(tmem_empty, 8);
+        mbar_init(a_full, 1);
+        for (int o = 0; o < 4; ++o) mbar_init(tmem_empty + 8 * o, 8);
         fence_barrier_init();
     }
     if (warp == 1) tmem_alloc(smem_u32(tmem_slot), 512);
@@ -102,6 +119,11 @@ qconv_pointwise_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __gri
         if (lane == 0) {
             int it = 0;
             bool ok = true;
+            if (resident && blockIdx.x < n_tiles) {
+                // the grid is a multiple of the channel tiles, so this CTA keeps one channel tile for all its pixel tiles
+                mbar_arrive_expect_tx(a_full, n_k * A_BYTES);
+                for (int k = 0; k < n_k; ++k) tma_load_3d(a_slot(k, 0), &map_w, k * KS, (blockIdx.x % p.n_c_tiles) * CT, 0, a_full);
+            }
             for (int tile = blockIdx.x; tile < n_tiles && ok; tile += gridDim.x) {
                 const int px_tile = tile / p.n_c_tiles, c_tile = tile - px_tile * p.n_c_tiles;
                 const int c0 = c_tile * CT;
@@ -116,11 +138,11 @@ qconv_pointwise_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __gri
                     const int s = it % U_STAGES;
                     ok = mbar_wait_bounded(empty_bar + 8 * s, ((it / U_STAGES) & 1) ^ 1, status, ST_U_PRODUCER);
                     if (!ok) break;
-                    const uint32_t a_dst = tiles_addr + s * STAGE_BYTES, b_dst = a_dst + A_BYTES;
+                    const uint32_t a_dst = a_slot(k, s), b_dst = b_slot(s);
                     const uint32_t bar = full_bar + 8 * s;
-                    mbar_arrive_expect_tx(bar, STAGE_BYTES);
+                    mbar_arrive_expect_tx(bar, resident ? B_BYTES : STAGE_BYTES);
                     if (!BWD) {
-                        tma_load_3d(a_dst, &map_w, k * KS, c0, 0, bar);                 // [r][128 co][32 ci]
+                        if (!resident) tma_load_3d(a_dst, &map_w, k * KS, c0, 0, bar);  // [r][128 co][32 ci]
                     } else {
                         tma_load_3d(a_dst, &map_w, c0, k * KS, 0, bar);                 // [r][32 co][64 ci] x 2 ci blocks
                         tma_load_3d(a_dst + A_BYTES / 2, &map_w, c0 + 64, k * KS, 0, bar);
@@ -135,35 +157,49 @@ qconv_pointwise_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __gri
         // ---------------------------------------------------------------- MMA issuer
         int it = 0, local_tile = 0;
         bool ok = true;
+        auto issue = [&](uint32_t a_addr, uint32_t b_addr, int j, int i, int o, uint32_t accumulate) {
+            const int r = i ^ o;
+            const bool neg = BWD ? quat_negative(o, i) : quat_negative(i, o);
+            const uint64_t ad = BWD ? make_desc_mnmajor(a_addr + r * (KS * 128) + j * 2048, A_BYTES / 2)
+                                    : make_desc_kmajor_sw64(a_addr + r * (CT * KS * 2) + j * 32);
+            const uint64_t bd = make_desc_mnmajor(b_addr + i * (KS * 128) + j * 2048, B_BOX_BYTES);
+            mma_f16_ss(tmem_base + o * PT, ad, bd, make_idesc_f16(p.fmt, CT, PT, BWD, true, neg, false), accumulate);
+        };
+        if (resident && blockIdx.x < n_tiles) ok = mbar_wait_bounded(a_full, 0, status, ST_U_MMA);
         for (int tile = blockIdx.x; tile < n_tiles && ok; tile += gridDim.x, ++local_tile) {
-            if (local_tile > 0) {   // accumulators must have been drained by the epilogue of the previous tile
-                ok = mbar_wait_bounded(tmem_empty, (local_tile - 1) & 1, status, ST_U_MMA);
-                if (!ok) break;
-                tc_fence_after_sync();
-            }
             for (int k = 0; k < n_k && ok; ++k, ++it) {
                 const int s = it % U_STAGES;
                 ok = mbar_wait_bounded(full_bar + 8 * s, (it / U_STAGES) & 1, status, ST_U_MMA);
                 if (!ok) break;
                 tc_fence_after_sync();
-                if (lane == 0) {
-                    const uint32_t a_addr = tiles_addr + s * STAGE_BYTES, b_addr = a_addr + A_BYTES;
-#pragma unroll
-                    for (int j = 0; j < KS / 16; ++j) {
-#pragma unroll
-                        for (int i = 0; i < 4; ++i) {          // component of the streamed activations (l forward, d backward)
-#pragma unroll
-                            for (int o = 0; o < 4; ++o) {      // component of the accumulator (d forward, l backward)
-                                const int r = i ^ o;
-                                const bool neg = BWD ? quat_negative(o, i) : quat_negative(i, o);
-                                const uint64_t ad = BWD ? make_desc_mnmajor(a_addr + r * (KS * 128) + j * 2048, A_BYTES / 2)
-                                                        : make_desc_kmajor_sw64(a_addr + r * (CT * KS * 2) + j * 32);
-                                const uint64_t bd = make_desc_mnmajor(b_addr + i * (KS * 128) + j * 2048, B_BOX_BYTES);
-                                const uint32_t idesc = make_idesc_f16(p.fmt, CT, PT, BWD, true, neg, false);
-                                mma_f16_ss(tmem_base + o * PT, ad, bd, idesc, (k > 0 || j > 0 || i > 0) ? 1u : 0u);
-                            }
+                const uint32_t a_addr = a_slot(k, s), b_addr = b_slot(s);
+                if (k == 0) {
+                    // first K slice of a tile: accumulator by accumulator, each as soon as the epilogue of the
+                    // previous tile has drained it (i = streamed component, o = accumulator component)
+                    for (int o = 0; o < 4 && ok; ++o) {
+                        if (local_tile > 0) {
+                            ok = mbar_wait_bounded(tmem_empty + 8 * o, (local_tile - 1) & 1, status, ST_U_MMA);
+                            if (!ok) break;
+                            tc_fence_after_sync();
                         }
+                        if (lane == 0) {
+#pragma unroll
+                            for (int j = 0; j < KS / 16; ++j)
+#pragma unroll
+                                for (int i = 0; i < 4; ++i) issue(a_addr, b_addr, j, i, o, (j > 0 || i > 0) ? 1u : 0u);
+                        }
+                        __syncwarp();
                     }
+                    if (!ok) break;
+                } else if (lane == 0) {
+#pragma unroll
+                    for (int j = 0; j < KS / 16; ++j)
+#pragma unroll
+                        for (int i = 0; i < 4; ++i)
+#pragma unroll
+                            for (int o = 0; o < 4; ++o) issue(a_addr, b_addr, j, i, o, 1u);
+                }
+                if (lane == 0) {
                     mma_commit(empty_bar + 8 * s);
                     if (k == n_k - 1) mma_commit(tmem_full);
                 }
@@ -173,7 +209,7 @@ qconv_pointwise_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __gri
     } else {
         // ---------------------------------------------------------------- epilogue (warps 2..9)
         const int q = warp & 3;                   // TMEM lane quadrant this warp may read
-        const int half = (warp - 2) >> 2;         // which pair of components
+        const int chalf = (warp - 2) >> 2;        // which 64-pixel block of the tile (64 accumulator columns)
         int local_tile = 0;
         bool ok = true;
         for (int tile = blockIdx.x; tile < n_tiles && ok; tile += gridDim.x, ++local_tile) {
@@ -183,48 +219,52 @@ qconv_pointwise_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __gri
             ok = __all_sync(0xffffffffu, ok && (*reinterpret_cast<volatile int*>(status) == 0));
             if (!ok) break;
             tc_fence_after_sync();
-            uint32_t packed[2][4][16];
+            // All eight warps drain component 0 (a 64-column half each) and release it, then 1, 2, 3: the MMA warp
+            // starts the next tile on component 0 while 1..3 are still being read. Values wait in packed registers.
+            uint32_t packed[4][2][16];
 #pragma unroll
-            for (int oo = 0; oo < 2; ++oo) {
-                const int o = 2 * half + oo;
+            for (int o = 0; o < 4; ++o) {
                 float badd = 0.f;
                 if (!BWD && p.has_bias && c < p.Cout) {
                     const uint16_t raw = bias[o * p.Cout + c];
                     badd = p.fmt == 0 ? __half2float(__ushort_as_half(raw)) : __bfloat162float(__ushort_as_bfloat16(raw));
                 }
 #pragma unroll
-                for (int cb = 0; cb < 4; ++cb) {
+                for (int cb = 0; cb < 2; ++cb) {
                     uint32_t v[32];
-                    tmem_ld_32x32b_x32(tmem_base + ((uint32_t)(q * 32) << 16) + o * PT + cb * 32, v);
+                    tmem_ld_32x32b_x32(tmem_base + ((uint32_t)(q * 32) << 16) + o * PT + chalf * 64 + cb * 32, v);
                     tmem_ld_wait();
 #pragma unroll
                     for (int e = 0; e < 16; ++e) {
                         const float f0 = __uint_as_float(v[2 * e]) + badd, f1 = __uint_as_float(v[2 * e + 1]) + badd;
-                        if (p.fmt == 0) { const __half2 h = __floats2half2_rn(f0, f1); packed[oo][cb][e] = *reinterpret_cast<const uint32_t*>(&h); }
-                        else { const __nv_bfloat162 h = __floats2bfloat162_rn(f0, f1); packed[oo][cb][e] = *reinterpret_cast<const uint32_t*>(&h); }
+                        if (p.fmt == 0) { const __half2 h = __floats2half2_rn(f0, f1); packed[o][cb][e] = *reinterpret_cast<const uint32_t*>(&h); }
+                        else { const __nv_bfloat162 h = __floats2bfloat162_rn(f0, f1); packed[o][cb][e] = *reinterpret_cast<const uint32_t*>(&h); }
                     }
                 }
+                tc_fence_before_sync();
+                __syncwarp();
+                if (lane == 0) mbar_arrive(tmem_empty + 8 * o);
             }
-            // accumulators are in registers now: hand TMEM back to the MMA warp, then write out
-            tc_fence_before_sync();
-            __syncwarp();
-            if (lane == 0) mbar_arrive(tmem_empty);
-            if (c < p.Cout) {
+            const int blk = 2 * px_tile + chalf;
+            const int img = blk / p.blocks_per_image;
+            if (c < p.Cout && img < p.Nb) {
+                const int pxb = (blk - img * p.blocks_per_image) * 64;
+                const bool wide = (p.HW & 15) == 0;       // rows start on 32-byte boundaries
 #pragma unroll
-                for (int oo = 0; oo < 2; ++oo) {
-                    const int o = 2 * half + oo;
+                for (int o = 0; o < 4; ++o) {
+                    uint16_t* dst = out + ((size_t)(o * p.Nb + img) * p.Cout + c) * p.HW + pxb;
 #pragma unroll
-                    for (int cb = 0; cb < 4; ++cb) {
-                        const int blk = 2 * px_tile + (cb >> 1);
-                        const int img = blk / p.blocks_per_image;
-                        if (img >= p.Nb) continue;
-                        const int px0 = (blk - img * p.blocks_per_image) * 64 + (cb & 1) * 32;
-                        uint16_t* dst = out + ((size_t)(o * p.Nb + img) * p.Cout + c) * p.HW + px0;
+                    for (int cb = 0; cb < 2; ++cb) {
+                        if (wide) {
 #pragma unroll
-                        for (int g8 = 0; g8 < 4; ++g8) {
-                            if (px0 + g8 * 8 < p.HW)
-                                *reinterpret_cast<uint4*>(dst + g8 * 8) = make_uint4(packed[oo][cb][4 * g8], packed[oo][cb][4 * g8 + 1],
-                                                                                     packed[oo][cb][4 * g8 + 2], packed[oo][cb][4 * g8 + 3]);
+                            for (int g16 = 0; g16 < 2; ++g16)
+                                if (pxb + cb * 32 + g16 * 16 < p.HW) st_global_v8(dst + cb * 32 + g16 * 16, &packed[o][cb][8 * g16]);
+                        } else {
+#pragma unroll
+                            for (int g8 = 0; g8 < 4; ++g8)
+                                if (pxb + cb * 32 + g8 * 8 < p.HW)
+                                    *reinterpret_cast<uint4*>(dst + cb * 32 + g8 * 8) = make_uint4(packed[o][cb][4 * g8], packed[o][cb][4 * g8 + 1],
+                                                                                                  packed[o][cb][4 * g8 + 2], packed[o][cb][4 * g8 + 3]);
                         }
                     }
                 }
@@ -460,7 +500,14 @@ int pointwise_tc_launch(Pass pass, int dtype, const Geom& g, const void* w, cons
         if (rc != PCB_OK) return rc;
     }
     const int n_tiles = p.n_px_tiles * p.n_c_tiles;
-    const int grid = n_tiles < sm_count_u() ? n_tiles : sm_count_u();
+    int grid = n_tiles < sm_count_u() ? n_tiles : sm_count_u();
+    // forward with at most 128 reduced channels: keep the CTA's weight slices in shared memory for all its tiles
+    // (halves the L2 -> shared-memory traffic); needs every CTA to stay on one channel tile
+    p.a_resident = 0;
+    if (!bwd && (p.Cred + KS - 1) / KS <= MAX_RESIDENT_K && grid >= p.n_c_tiles) {
+        grid -= grid % p.n_c_tiles;
+        p.a_resident = 1;
+    }
     if (!bwd) {
         PCB_CUDA_TRY(cudaFuncSetAttribute(qconv_pointwise_tc_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)U_SMEM_BYTES));
         qconv_pointwise_tc_kernel<false><<<grid, U_THREADS, U_SMEM_BYTES, stream>>>(map_w, map_act, p, (const uint16_t*)bias, (uint16_t*)out, status);
