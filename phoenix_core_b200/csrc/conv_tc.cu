@@ -42,6 +42,7 @@ struct GParams {
     int tiles_w, tiles_h, tiles_n, tiles_m;
     int fmt, has_bias;
     int LK;                      // input components along K: 4, or 1 for a real-valued (type-0) input
+    int store_vec;               // output pixels per store: largest power of two <= 16 dividing WO (and the pointer alignment)
 };
 
 __device__ __forceinline__ void tma_load_3d_g(uint32_t dst, const CUtensorMap* map, int c0, int c1, int c2, uint32_t bar) {
@@ -53,6 +54,12 @@ __device__ __forceinline__ void tma_load_5d_g(uint32_t dst, const CUtensorMap* m
     asm volatile(
         "cp.async.bulk.tensor.5d.shared::cluster.global.tile.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3, %4, %5, %6}], [%7];"
         ::"r"(dst), "l"(map), "r"(c0), "r"(c1), "r"(c2), "r"(c3), "r"(c4), "r"(bar) : "memory");
+}
+
+// 32-byte store: one full sector per thread and half as many store instructions as 16-byte stores.
+__device__ __forceinline__ void st_global_v8_g(void* addr, const uint32_t* v) {
+    asm volatile("st.global.v8.b32 [%0], {%1, %2, %3, %4, %5, %6, %7, %8};"
+                 ::"l"(addr), "r"(v[0]), "r"(v[1]), "r"(v[2]), "r"(v[3]), "r"(v[4]), "r"(v[5]), "r"(v[6]), "r"(v[7]) : "memory");
 }
 
 // K-major operand tile whose rows hold KS 16-bit elements (KS*2 bytes, swizzle span == row size):
@@ -157,7 +164,8 @@ qconv_general_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_
         // ---------------------------------------------------------------- epilogue (warps 2..9)
         const int q = warp & 3;                    // TMEM lane quadrant
         const int chalf = (warp - 2) >> 2;         // which 128 of the 256 columns
-        const bool vec_ok = (p.WO % 8) == 0;
+        const int sv = p.store_vec;                // pixels per store instruction: 16, 8, 4, 2 or 1
+        const bool vec_ok = sv >= 8;
         int local_tile = 0;
         bool ok = true;
         for (int tile = blockIdx.x; tile < n_tiles && ok; tile += gridDim.x, ++local_tile) {
@@ -187,26 +195,41 @@ qconv_general_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_
                 tmem_ld_32x32b_x32(tmem_base + ((uint32_t)(q * 32) << 16) + buf * GN + col0, v);
                 tmem_ld_wait();
                 if (!row_ok) continue;
+                // convert the 32 columns once, then store runs of 16 pixels (32 bytes) where a run stays inside one
+                // output row and rows are 32-byte aligned, runs of 8 pixels (16 bytes) where rows are 16-byte aligned,
+                // single elements otherwise
+                uint32_t packed[16];
+#pragma unroll
+                for (int e = 0; e < 16; ++e) {
+                    const float f0 = __uint_as_float(v[2 * e]) + badd, f1 = __uint_as_float(v[2 * e + 1]) + badd;
+                    if (p.fmt == 0) { const __half2 h = __floats2half2_rn(f0, f1); packed[e] = *reinterpret_cast<const uint32_t*>(&h); }
+                    else { const __nv_bfloat162 h = __floats2bfloat162_rn(f0, f1); packed[e] = *reinterpret_cast<const uint32_t*>(&h); }
+                }
+                const bool wide = sv >= 16 && (p.PW % 16) == 0;
 #pragma unroll
                 for (int g8 = 0; g8 < 4; ++g8) {
+                    if (wide && (g8 & 1)) continue;                      // the odd groups were written with their even neighbours
                     const int j = col0 + g8 * 8;                         // column -> (image, row, pixel) of the tile box
                     const int wl = j % p.PW, hl = (j / p.PW) % p.PH, nl = j / (p.PW * p.PH);
                     const int ow = ow0 + wl, oh = oh0 + hl, img = n0 + nl;
                     if (ow >= p.WO || oh >= p.HO || img >= p.Nb) continue;
                     uint16_t* dst = out + (((size_t)(d * p.Nb + img) * p.Cout + co) * p.HO + oh) * p.WO + ow;
-                    uint32_t packed[4];
+                    if (wide) {
+                        st_global_v8_g(dst, &packed[4 * g8]);
+                    } else if (vec_ok) {
+                        *reinterpret_cast<uint4*>(dst) = make_uint4(packed[4 * g8], packed[4 * g8 + 1], packed[4 * g8 + 2], packed[4 * g8 + 3]);
+                    } else if (sv == 4) {          // rows are 8-byte aligned: two 4-pixel stores
 #pragma unroll
-                    for (int e = 0; e < 4; ++e) {
-                        const float f0 = __uint_as_float(v[g8 * 8 + 2 * e]) + badd, f1 = __uint_as_float(v[g8 * 8 + 2 * e + 1]) + badd;
-                        if (p.fmt == 0) { const __half2 h = __floats2half2_rn(f0, f1); packed[e] = *reinterpret_cast<const uint32_t*>(&h); }
-                        else { const __nv_bfloat162 h = __floats2bfloat162_rn(f0, f1); packed[e] = *reinterpret_cast<const uint32_t*>(&h); }
-                    }
-                    if (vec_ok) {
-                        *reinterpret_cast<uint4*>(dst) = make_uint4(packed[0], packed[1], packed[2], packed[3]);
+                        for (int h = 0; h < 2; ++h)
+                            if (ow + 4 * h < p.WO) *reinterpret_cast<uint2*>(dst + 4 * h) = make_uint2(packed[4 * g8 + 2 * h], packed[4 * g8 + 2 * h + 1]);
+                    } else if (sv == 2) {          // rows are 4-byte aligned: pixel pairs
+#pragma unroll
+                        for (int h = 0; h < 4; ++h)
+                            if (ow + 2 * h < p.WO) *reinterpret_cast<uint32_t*>(dst + 2 * h) = packed[4 * g8 + h];
                     } else {
 #pragma unroll
                         for (int e = 0; e < 8; ++e)
-                            if (ow + e < p.WO) dst[e] = (uint16_t)((packed[e >> 1] >> ((e & 1) * 16)) & 0xffffu);
+                            if (ow + e < p.WO) dst[e] = (uint16_t)((packed[4 * g8 + (e >> 1)] >> ((e & 1) * 16)) & 0xffffu);
                     }
                 }
             }
@@ -734,6 +757,8 @@ int conv_tc_launch(Pass pass, int dtype, const Geom& g, const void* w, const voi
     p.tiles_m = pl.Mp / GM;
     p.fmt = fmt; p.has_bias = (pass == PASS_FWD && g.has_bias) ? 1 : 0;
     p.LK = pl.LK;
+    p.store_vec = 1;
+    while (p.store_vec < 16 && pl.Wout % (p.store_vec * 2) == 0 && (reinterpret_cast<uintptr_t>(out) % (size_t)(p.store_vec * 4)) == 0) p.store_vec *= 2;
 
     const CUtensorMapDataType dt = fmt == 0 ? CU_TENSOR_MAP_DATA_TYPE_FLOAT16 : CU_TENSOR_MAP_DATA_TYPE_BFLOAT16;
     const CUtensorMapSwizzle sw = pl.KS == 32 ? CU_TENSOR_MAP_SWIZZLE_64B : CU_TENSOR_MAP_SWIZZLE_32B;

@@ -249,7 +249,7 @@ qconv_pointwise_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __gri
             const int img = blk / p.blocks_per_image;
             if (c < p.Cout && img < p.Nb) {
                 const int pxb = (blk - img * p.blocks_per_image) * 64;
-                const bool wide = (p.HW & 15) == 0;       // rows start on 32-byte boundaries
+                const bool wide = (p.HW & 15) == 0 && (reinterpret_cast<uintptr_t>(out) & 31) == 0;   // rows start on 32-byte boundaries
 #pragma unroll
                 for (int o = 0; o < 4; ++o) {
                     uint16_t* dst = out + ((size_t)(o * p.Nb + img) * p.Cout + c) * p.HW + pxb;
