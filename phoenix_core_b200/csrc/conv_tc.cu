@@ -19,15 +19,14 @@
 // tcgen05.mma M=128 N=256 K=16; the accumulator is double-buffered in TMEM (2 x 256 columns) so the epilogue
 // (8 warps: TMEM -> bias -> cast -> NCHW stores) of tile i overlaps the main loop of tile i+1.
 // All mbarrier waits are bounded.
-#include <cuda.h>
-
+#include "tc_common.cuh"
 #include "tensor_path.cuh"
-#include "umma.cuh"
 
 namespace pcb {
 namespace {
 
 using namespace umma;
+using namespace tc;
 
 constexpr int GM = 128, GN = 256;
 constexpr int G_THREADS = 320;                       // warp 0 TMA, warp 1 MMA, warps 2..9 epilogue
@@ -44,23 +43,6 @@ struct GParams {
     int LK;                      // input components along K: 4, or 1 for a real-valued (type-0) input
     int store_vec;               // output pixels per store: largest power of two <= 16 dividing WO (and the pointer alignment)
 };
-
-__device__ __forceinline__ void tma_load_3d_g(uint32_t dst, const CUtensorMap* map, int c0, int c1, int c2, uint32_t bar) {
-    asm volatile(
-        "cp.async.bulk.tensor.3d.shared::cluster.global.tile.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3, %4}], [%5];"
-        ::"r"(dst), "l"(map), "r"(c0), "r"(c1), "r"(c2), "r"(bar) : "memory");
-}
-__device__ __forceinline__ void tma_load_5d_g(uint32_t dst, const CUtensorMap* map, int c0, int c1, int c2, int c3, int c4, uint32_t bar) {
-    asm volatile(
-        "cp.async.bulk.tensor.5d.shared::cluster.global.tile.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3, %4, %5, %6}], [%7];"
-        ::"r"(dst), "l"(map), "r"(c0), "r"(c1), "r"(c2), "r"(c3), "r"(c4), "r"(bar) : "memory");
-}
-
-// 32-byte store: one full sector per thread and half as many store instructions as 16-byte stores.
-__device__ __forceinline__ void st_global_v8_g(void* addr, const uint32_t* v) {
-    asm volatile("st.global.v8.b32 [%0], {%1, %2, %3, %4, %5, %6, %7, %8};"
-                 ::"l"(addr), "r"(v[0]), "r"(v[1]), "r"(v[2]), "r"(v[3]), "r"(v[4]), "r"(v[5]), "r"(v[6]), "r"(v[7]) : "memory");
-}
 
 // K-major operand tile whose rows hold KS 16-bit elements (KS*2 bytes, swizzle span == row size):
 // 8-row groups are 8*KS*2 bytes apart. KS = 32 -> 64-byte swizzle, KS = 16 -> 32-byte swizzle.
@@ -123,8 +105,8 @@ qconv_general_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_
                             if (!ok) break;
                             const uint32_t a_dst = tiles_addr + s * STAGE, bar = full_bar + 8 * s;
                             mbar_arrive_expect_tx(bar, STAGE);
-                            tma_load_3d_g(a_dst, &map_w, l * p.Cp + cs * KS, m0, tap, bar);
-                            tma_load_5d_g(a_dst + A_BYTES, &map_x, cs * KS, wp0, hp0, n0, l, bar);
+                            tma_load_3d(a_dst, &map_w, l * p.Cp + cs * KS, m0, tap, bar);
+                            tma_load_5d(a_dst + A_BYTES, &map_x, cs * KS, wp0, hp0, n0, l, bar);
                         }
                     }
                 }
@@ -215,7 +197,7 @@ qconv_general_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_
                     if (ow >= p.WO || oh >= p.HO || img >= p.Nb) continue;
                     uint16_t* dst = out + (((size_t)(d * p.Nb + img) * p.Cout + co) * p.HO + oh) * p.WO + ow;
                     if (wide) {
-                        st_global_v8_g(dst, &packed[4 * g8]);
+                        st_global_v8(dst, &packed[4 * g8]);
                     } else if (vec_ok) {
                         *reinterpret_cast<uint4*>(dst) = make_uint4(packed[4 * g8], packed[4 * g8 + 1], packed[4 * g8 + 2], packed[4 * g8 + 3]);
                     } else if (sv == 4) {          // rows are 8-byte aligned: two 4-pixel stores
@@ -343,10 +325,6 @@ __device__ __forceinline__ uint64_t make_desc_mn_blocks(uint32_t smem_addr, int 
            ((uint64_t)(((8u * cb * 2u) >> 4) & 0x3FFFu) << 32) | DESC_VERSION_SM100 | (layout << 61);
 }
 
-__device__ __forceinline__ void red_add_f32x4(float* addr, float a, float b, float c, float d) {
-    asm volatile("red.global.add.v4.f32 [%0], {%1, %2, %3, %4};" ::"l"(addr), "f"(a), "f"(b), "f"(c), "f"(d) : "memory");
-}
-
 __global__ void __launch_bounds__(G_THREADS, 1)
 qconv_filter_general_tc_kernel(const __grid_constant__ CUtensorMap map_dy, const __grid_constant__ CUtensorMap map_x, FGParams p,
                                float* __restrict__ dw32, int* __restrict__ status) {
@@ -403,20 +381,20 @@ qconv_filter_general_tc_kernel(const __grid_constant__ CUtensorMap map_dy, const
                 const uint32_t a_dst = tiles_addr + s * F_STAGE, b_dst = a_dst + GM * FK * 2, bar = full_bar + 8 * s;
                 mbar_arrive_expect_tx(bar, a_bytes + b_bytes);
                 if (p.merged_a) {
-                    tma_load_5d_g(a_dst, &map_dy, 0, ow0, oh0, n0, blockA0, bar);
+                    tma_load_5d(a_dst, &map_dy, 0, ow0, oh0, n0, blockA0, bar);
                 } else {
                     for (int b = 0; b < nblkA; ++b) {
                         const int blk = blockA0 + b;
-                        tma_load_5d_g(a_dst + b * blkA_bytes, &map_dy, (blk % bpcA) * p.cbA, ow0, oh0, n0, blk / bpcA, bar);
+                        tma_load_5d(a_dst + b * blkA_bytes, &map_dy, (blk % bpcA) * p.cbA, ow0, oh0, n0, blk / bpcA, bar);
                     }
                 }
                 const int wp0 = ow0 * p.SW + kw * p.DW, hp0 = oh0 * p.SH + kh * p.DH;
                 if (p.merged_b) {
-                    tma_load_5d_g(b_dst, &map_x, 0, wp0, hp0, n0, blockB0, bar);
+                    tma_load_5d(b_dst, &map_x, 0, wp0, hp0, n0, blockB0, bar);
                 } else {
                     for (int b = 0; b < nblkB; ++b) {
                         const int blk = blockB0 + b;
-                        tma_load_5d_g(b_dst + b * blkB_bytes, &map_x, (blk % bpcB) * p.cbB, wp0, hp0, n0, blk / bpcB, bar);
+                        tma_load_5d(b_dst + b * blkB_bytes, &map_x, (blk % bpcB) * p.cbB, wp0, hp0, n0, blk / bpcB, bar);
                     }
                 }
             }
@@ -547,9 +525,9 @@ qconv_filter_xmajor_tc_kernel(const __grid_constant__ CUtensorMap map_x, const _
                     const int tap = tg * p.TPG + tl;
                     const int kh = tap / p.KW, kw = tap - kh * p.KW;
                     // a tap past the end is loaded from component LK: entirely out of range, i.e. zeros
-                    tma_load_5d_g(a_dst + tl * tap_bytes, &map_x, 0, ow0 * p.SW + kw * p.DW, oh0 * p.SH + kh * p.DH, n0, tap < taps ? 0 : p.LK, bar);
+                    tma_load_5d(a_dst + tl * tap_bytes, &map_x, 0, ow0 * p.SW + kw * p.DW, oh0 * p.SH + kh * p.DH, n0, tap < taps ? 0 : p.LK, bar);
                 }
-                tma_load_5d_g(b_dst, &map_dy, 0, ow0, oh0, n0, 0, bar);
+                tma_load_5d(b_dst, &map_dy, 0, ow0, oh0, n0, 0, bar);
             }
         }
         __syncwarp();
@@ -622,33 +600,6 @@ __global__ void unpack_filter_grad_kernel(const float* __restrict__ src, T* __re
     }
 }
 
-typedef CUresult (*EncodeTiledFnG)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*, const cuuint64_t*,
-                                   const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
-                                   CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
-
-EncodeTiledFnG encode_fn_g() {
-    static EncodeTiledFnG fn = nullptr;
-    if (!fn) {
-        void* sym = nullptr;
-        cudaDriverEntryPointQueryResult q;
-        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &sym, cudaEnableDefault, &q) == cudaSuccess && q == cudaDriverEntryPointSuccess)
-            fn = reinterpret_cast<EncodeTiledFnG>(sym);
-    }
-    return fn;
-}
-
-int sm_count_g() {
-    static int sms = 0;
-    if (sms == 0) {
-        int dev = 0;
-        if (cudaGetDevice(&dev) != cudaSuccess || cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || sms <= 0)
-            sms = 148;
-    }
-    return sms;
-}
-
-int round_up(int v, int m) { return (v + m - 1) / m * m; }
-
 // Geometry of one launch of the implicit-GEMM kernel: "input" is the tensor being convolved (x forward,
 // dy backward-data), "output" the tensor produced.
 struct Plan {
@@ -711,7 +662,7 @@ size_t conv_tc_scratch_bytes(Pass pass, const Geom& g) {
 
 int conv_tc_launch(Pass pass, int dtype, const Geom& g, const void* w, const void* act, const void* bias, void* out,
                    void* scratch, int* status, cudaStream_t stream) {
-    EncodeTiledFnG encode = encode_fn_g();
+    EncodeTiledFn encode = encode_fn();
     if (!encode) { set_error("cuTensorMapEncodeTiled is not available from the driver"); return PCB_ERR_CUDA; }
     const int fmt = dtype == PCB_F16 ? 0 : 1;
     const Plan pl = make_plan(pass, g);
@@ -722,9 +673,9 @@ int conv_tc_launch(Pass pass, int dtype, const Geom& g, const void* w, const voi
     // stage the operands
     {
         const size_t total = (size_t)pl.LK * g.Nb * pl.Hp * pl.Wp * (pl.Cp / 8);
-        const int blocks = (int)((total + 255) / 256 < (size_t)sm_count_g() * 16 ? (total + 255) / 256 : (size_t)sm_count_g() * 16);
+        const int blocks = (int)((total + 255) / 256 < (size_t)sm_count() * 16 ? (total + 255) / 256 : (size_t)sm_count() * 16);
         const size_t wtotal = (size_t)taps * pl.Mp * pl.Kp;
-        const int wblocks = (int)((wtotal + 255) / 256 < (size_t)sm_count_g() * 8 ? (wtotal + 255) / 256 : (size_t)sm_count_g() * 8);
+        const int wblocks = (int)((wtotal + 255) / 256 < (size_t)sm_count() * 8 ? (wtotal + 255) / 256 : (size_t)sm_count() * 8);
         if (fmt == 0) {
             pack_activations_kernel<__half><<<blocks, 256, 0, stream>>>((const __half*)act, (__half*)xp, pl.LK * g.Nb, pl.Cin, pl.Hin, pl.Win,
                                                                        pl.Hp, pl.Wp, pl.Cp, pl.pad_top, pl.pad_left, pl.ins_h, pl.ins_w);
@@ -785,7 +736,7 @@ int conv_tc_launch(Pass pass, int dtype, const Geom& g, const void* w, const voi
     }
 
     const int n_tiles = p.tiles_w * p.tiles_h * p.tiles_n * p.tiles_m;
-    const int grid = n_tiles < sm_count_g() ? n_tiles : sm_count_g();
+    const int grid = n_tiles < sm_count() ? n_tiles : sm_count();
     if (pl.KS == 32) {
         constexpr size_t smem = 1024 + 8 * (GM + GN) * 32 * 2 + 512;
         PCB_CUDA_TRY(cudaFuncSetAttribute(qconv_general_tc_kernel<32>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
@@ -847,7 +798,7 @@ size_t conv_filter_tc_scratch_bytes(const Geom& g) {
 
 int conv_filter_tc_launch(int dtype, const Geom& g, const void* dy, const void* x, void* dw, void* scratch, int* status,
                           cudaStream_t stream) {
-    EncodeTiledFnG encode = encode_fn_g();
+    EncodeTiledFn encode = encode_fn();
     if (!encode) { set_error("cuTensorMapEncodeTiled is not available from the driver"); return PCB_ERR_CUDA; }
     const int fmt = dtype == PCB_F16 ? 0 : 1;
     const FilterPlan f = make_filter_plan(g);
@@ -859,7 +810,7 @@ int conv_filter_tc_launch(int dtype, const Geom& g, const void* dy, const void* 
     {   // stage both activations channels-last
         const int lk = g.real_in ? 1 : 4;
         const size_t tx = (size_t)lk * g.Nb * f.Hp * f.Wp * (f.Cip / 8), ty = (size_t)4 * g.Nb * g.HO * g.WO * (f.Cop / 8);
-        const size_t cap = (size_t)sm_count_g() * 16;
+        const size_t cap = (size_t)sm_count() * 16;
         const int bx = (int)((tx + 255) / 256 < cap ? (tx + 255) / 256 : cap), by = (int)((ty + 255) / 256 < cap ? (ty + 255) / 256 : cap);
         if (fmt == 0) {
             pack_activations_kernel<__half><<<bx, 256, 0, stream>>>((const __half*)x, (__half*)xp, lk * g.Nb, g.Ci, g.H, g.W, f.Hp, f.Wp, f.Cip, g.PT, g.PL);
@@ -897,7 +848,7 @@ int conv_filter_tc_launch(int dtype, const Geom& g, const void* dy, const void* 
     p.TPG = xmajor ? GM / (p.LK * p.cbB) : 1;
     const int steps_total = p.tiles_w * p.tiles_h * p.tiles_n;
     const int items = xmajor ? (taps + p.TPG - 1) / p.TPG : taps * p.m_tiles * p.n_tiles;
-    int splits = (2 * sm_count_g() + items - 1) / items;
+    int splits = (2 * sm_count() + items - 1) / items;
     if (splits > steps_total) splits = steps_total;
     if (splits < 1) splits = 1;
     p.steps_per_split = (steps_total + splits - 1) / splits;

@@ -21,15 +21,14 @@
 // pixels x 4 components (all 512 TMEM columns); K slice per stage = 32 channels per component
 // (A 32 KB + B 32 KB), 3 stages. Every mbarrier wait is bounded; an expired wait sets the status word and
 // the CTA leaves through the common teardown.
-#include <cuda.h>
-
+#include "tc_common.cuh"
 #include "tensor_path.cuh"
-#include "umma.cuh"
 
 namespace pcb {
 namespace {
 
 using namespace umma;
+using namespace tc;
 
 constexpr int CT = 128;             // channel tile (MMA M)
 constexpr int PT = 128;             // pixel tile (MMA N): two TMA boxes of 64 pixels
@@ -54,23 +53,6 @@ struct UParams {
     int bwd;                 // 0 forward, 1 backward-data
     int a_resident;          // forward: the CTA's weight slices are loaded once and stay in shared memory
 };
-
-__device__ __forceinline__ void tma_load_4d(uint32_t dst, const CUtensorMap* map, int c0, int c1, int c2, int c3, uint32_t bar) {
-    asm volatile(
-        "cp.async.bulk.tensor.4d.shared::cluster.global.tile.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3, %4, %5}], [%6];"
-        ::"r"(dst), "l"(map), "r"(c0), "r"(c1), "r"(c2), "r"(c3), "r"(bar) : "memory");
-}
-__device__ __forceinline__ void tma_load_3d(uint32_t dst, const CUtensorMap* map, int c0, int c1, int c2, uint32_t bar) {
-    asm volatile(
-        "cp.async.bulk.tensor.3d.shared::cluster.global.tile.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3, %4}], [%5];"
-        ::"r"(dst), "l"(map), "r"(c0), "r"(c1), "r"(c2), "r"(bar) : "memory");
-}
-
-// 32-byte store: one full sector per thread and half as many store instructions as 16-byte stores.
-__device__ __forceinline__ void st_global_v8(void* addr, const uint32_t* v) {
-    asm volatile("st.global.v8.b32 [%0], {%1, %2, %3, %4, %5, %6, %7, %8};"
-                 ::"l"(addr), "r"(v[0]), "r"(v[1]), "r"(v[2]), "r"(v[3]), "r"(v[4]), "r"(v[5]), "r"(v[6]), "r"(v[7]) : "memory");
-}
 
 constexpr uint64_t DESC_SWIZZLE_64B = 4ull << 61;
 // K-major tile with 64-byte rows (32 16-bit K elements), 64-byte swizzle: 8-row groups are 512 bytes apart.
@@ -300,10 +282,6 @@ struct FParams {
     int fmt;
 };
 
-__device__ __forceinline__ void red_add_v4(float* addr, float a, float b, float c, float d) {
-    asm volatile("red.global.add.v4.f32 [%0], {%1, %2, %3, %4};" ::"l"(addr), "f"(a), "f"(b), "f"(c), "f"(d) : "memory");
-}
-
 __global__ void __launch_bounds__(U_THREADS, 1)
 qconv_pointwise_filter_tc_kernel(const __grid_constant__ CUtensorMap map_dy, const __grid_constant__ CUtensorMap map_x, FParams p,
                                  float* __restrict__ dw32, int* __restrict__ status) {
@@ -399,7 +377,7 @@ qconv_pointwise_filter_tc_kernel(const __grid_constant__ CUtensorMap map_dy, con
 #pragma unroll
                     for (int g4 = 0; g4 < 8; ++g4) {
                         if (ci0 + cb * 32 + g4 * 4 < p.Ci)
-                            red_add_v4(dst + g4 * 4, __uint_as_float(v[4 * g4]), __uint_as_float(v[4 * g4 + 1]),
+                            red_add_f32x4(dst + g4 * 4, __uint_as_float(v[4 * g4]), __uint_as_float(v[4 * g4 + 1]),
                                        __uint_as_float(v[4 * g4 + 2]), __uint_as_float(v[4 * g4 + 3]));
                     }
                 }
@@ -418,41 +396,10 @@ __global__ void cast_f32_kernel(const float* __restrict__ src, T* __restrict__ d
     for (; i < n; i += stride) DType<T>::store(dst + i, src[i]);
 }
 
-typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*, const cuuint64_t*,
-                                  const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
-                                  CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
-
-EncodeTiledFn encode_fn() {
-    static EncodeTiledFn fn = nullptr;
-    if (!fn) {
-        void* sym = nullptr;
-        cudaDriverEntryPointQueryResult q;
-        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &sym, cudaEnableDefault, &q) == cudaSuccess && q == cudaDriverEntryPointSuccess)
-            fn = reinterpret_cast<EncodeTiledFn>(sym);
-    }
-    return fn;
-}
-
 int make_map(CUtensorMap* map, int fmt, const void* ptr, int rank, const cuuint64_t* dims, const cuuint64_t* strides_bytes,
              const cuuint32_t* box, CUtensorMapSwizzle swizzle) {
-    EncodeTiledFn fn = encode_fn();
-    if (!fn) { set_error("cuTensorMapEncodeTiled is not available from the driver"); return PCB_ERR_CUDA; }
-    cuuint32_t ones[5] = {1, 1, 1, 1, 1};
-    const CUresult r = fn(map, fmt == 0 ? CU_TENSOR_MAP_DATA_TYPE_FLOAT16 : CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, (cuuint32_t)rank,
-                          const_cast<void*>(ptr), dims, strides_bytes, box, ones, CU_TENSOR_MAP_INTERLEAVE_NONE, swizzle,
-                          CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
-    if (r != CUDA_SUCCESS) { set_error("cuTensorMapEncodeTiled failed with code %d", (int)r); return PCB_ERR_CUDA; }
-    return PCB_OK;
-}
-
-int sm_count_u() {
-    static int sms = 0;
-    if (sms == 0) {
-        int dev = 0;
-        if (cudaGetDevice(&dev) != cudaSuccess || cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || sms <= 0)
-            sms = 148;
-    }
-    return sms;
+    return make_tensor_map(map, fmt == 0 ? CU_TENSOR_MAP_DATA_TYPE_FLOAT16 : CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, ptr, rank, dims, strides_bytes,
+                           box, nullptr, swizzle, "pointwise operand");
 }
 
 }  // namespace
@@ -500,7 +447,7 @@ int pointwise_tc_launch(Pass pass, int dtype, const Geom& g, const void* w, cons
         if (rc != PCB_OK) return rc;
     }
     const int n_tiles = p.n_px_tiles * p.n_c_tiles;
-    int grid = n_tiles < sm_count_u() ? n_tiles : sm_count_u();
+    int grid = n_tiles < sm_count() ? n_tiles : sm_count();
     // forward with at most 128 reduced channels: keep the CTA's weight slices in shared memory for all its tiles
     // (halves the L2 -> shared-memory traffic); needs every CTA to stay on one channel tile
     p.a_resident = 0;
@@ -537,7 +484,7 @@ int pointwise_filter_tc_launch(int dtype, const Geom& g, const void* dy, const v
     p.n_ci_tiles = (g.Ci + 127) / 128;
     p.steps_total = g.Nb * p.blocks_per_image;
     const int n_out_tiles = p.n_co_tiles * p.n_ci_tiles;
-    int splits = sm_count_u() / n_out_tiles;
+    int splits = sm_count() / n_out_tiles;
     if (splits < 1) splits = 1;
     if (splits > p.steps_total) splits = p.steps_total;
     p.steps_per_split = (p.steps_total + splits - 1) / splits;
