@@ -383,6 +383,7 @@ bool legacy_supported(int dtype, int variant, const Geom& g) {
 }  // namespace
 
 bool tensor_path_supported(Pass pass, int dtype, int variant, const Geom& g) {
+    if (dtype == PCB_F32) return conv_tf32_supported(pass, dtype, variant, g);
     if (pass == PASS_BWD_FILTER)
         return pointwise_filter_tc_supported(dtype, variant, g) || conv_filter_tc_supported(dtype, variant, g) || legacy_supported(dtype, variant, g);
     return pointwise_tc_supported(pass, dtype, variant, g) || conv_tc_supported(pass, dtype, variant, g) ||
@@ -391,6 +392,7 @@ bool tensor_path_supported(Pass pass, int dtype, int variant, const Geom& g) {
 
 size_t tensor_scratch_bytes(Pass pass, int dtype, int variant, int engine, const Geom& g) {
     if (engine == PCB_ENGINE_SIMT || !tensor_path_supported(pass, dtype, variant, g)) return 0;
+    if (dtype == PCB_F32) return conv_tf32_scratch_bytes(pass, g);
     if (pass == PASS_BWD_FILTER) {
         if (pointwise_filter_tc_supported(dtype, variant, g)) return (size_t)4 * g.Co * g.Ci * g.KH * g.KW * sizeof(float);
         if (conv_filter_tc_supported(dtype, variant, g)) return conv_filter_tc_scratch_bytes(g);
@@ -403,6 +405,10 @@ size_t tensor_scratch_bytes(Pass pass, int dtype, int variant, int engine, const
 
 int tensor_launch(Pass pass, int dtype, int /*variant*/, const Geom& g, const void* a, const void* b, const void* bias,
                   void* out, float* scratch, int* status, cudaStream_t stream) {
+    if (dtype == PCB_F32) {
+        PCB_CUDA_TRY(cudaMemsetAsync(status, 0, sizeof(int), stream));
+        return conv_tf32_launch(pass, g, a, b, bias, out, scratch, status, stream);
+    }
     TcParams p;
     p.g = g;
     p.pass = pass;

@@ -32,4 +32,10 @@ size_t conv_filter_tc_scratch_bytes(const Geom& g);
 int conv_filter_tc_launch(int dtype, const Geom& g, const void* dy, const void* x, void* dw, void* scratch, int* status,
                           cudaStream_t stream);
 
+// fp32 tensors on the tensor cores with error-compensated TF32 (convolution and dense); see conv_tf32.cu.
+bool conv_tf32_supported(Pass pass, int dtype, int variant, const Geom& g);
+size_t conv_tf32_scratch_bytes(Pass pass, const Geom& g);
+int conv_tf32_launch(Pass pass, const Geom& g, const void* a, const void* b, const void* bias, void* out, void* scratch, int* status,
+                     cudaStream_t stream);
+
 }  // namespace pcb

@@ -46,7 +46,7 @@ __device__ __forceinline__ uint64_t make_desc_mnmajor(uint32_t smem_addr, uint32
 }
 
 // Instruction descriptor of tcgen05.mma.kind::f16 with fp32 accumulation.
-//   fmt: 0 = f16, 1 = bf16.  a_mn / b_mn: operand is MN-major.  a_neg / b_neg: negate the operand.
+//   fmt: 0 = f16, 1 = bf16, 2 = tf32 (with kind::tf32).  a_mn / b_mn: operand is MN-major.  a_neg / b_neg: negate the operand.
 __host__ __device__ __forceinline__ uint32_t make_idesc_f16(int fmt, int M, int N, bool a_mn, bool b_mn,
                                                            bool a_neg = false, bool b_neg = false) {
     return (1u << 4) | ((uint32_t)fmt << 7) | ((uint32_t)fmt << 10) | ((uint32_t)a_neg << 13) | ((uint32_t)b_neg << 14) |
@@ -115,6 +115,14 @@ __device__ __forceinline__ void mma_f16_ss(uint32_t d_tmem, uint64_t a_desc, uin
         "{\n\t.reg .pred p;\n\t"
         "setp.ne.b32 p, %4, 0;\n\t"
         "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}"
+        ::"r"(d_tmem), "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate) : "memory");
+}
+// Same with fp32 operands read as TF32 (the 13 low mantissa bits are not used), 8 K-elements per instruction.
+__device__ __forceinline__ void mma_tf32_ss(uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc, uint32_t idesc, uint32_t accumulate) {
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "setp.ne.b32 p, %4, 0;\n\t"
+        "tcgen05.mma.cta_group::1.kind::tf32 [%0], %1, %2, %3, p;\n\t}"
         ::"r"(d_tmem), "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate) : "memory");
 }
 // Arrives on the mbarrier once every tcgen05.mma issued so far by this thread has completed.

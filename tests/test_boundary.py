@@ -52,7 +52,9 @@ def test_c_abi_geometry_and_validation_without_gpu(built_lib):
     assert built_lib.pcb_conv2d_output_size(ctypes.byref(d), None, None) == _lib.PCB_ERR_INVALID_ARGUMENT
     # fp16 backward-filter needs fp32 scratch; fp32 forward needs only the status header
     d.kh = 3
+    d.engine = _lib.ENGINE_SIMT
     assert built_lib.pcb_qconv2d_fwd_workspace_size(ctypes.byref(d)) == 256
+    d.engine = _lib.ENGINE_AUTO
     d.dtype = _lib.PCB_F16
     assert built_lib.pcb_qconv2d_bwd_workspace_size(ctypes.byref(d)) >= 256 + 4 * 16 * 16 * 9 * 4
     # kernel-family selection: pointwise fp16 with aligned channel counts goes to the tensor cores
@@ -60,7 +62,9 @@ def test_c_abi_geometry_and_validation_without_gpu(built_lib):
                       dilation_h=1, dilation_w=1, groups=1)
     for pass_ in range(3):
         assert built_lib.pcb_qconv2d_engine_for(ctypes.byref(p), pass_) == _lib.ENGINE_TENSOR
-    p.dtype = _lib.PCB_F32
+    p.dtype = _lib.PCB_F32                                   # fp32: error-compensated TF32 on the tensor cores
+    assert built_lib.pcb_qconv2d_engine_for(ctypes.byref(p), 0) == _lib.ENGINE_TENSOR
+    p.variant = _lib.VARIANT_8_PRODUCT                       # the factorised form exists on the CUDA cores only
     assert built_lib.pcb_qconv2d_engine_for(ctypes.byref(p), 0) == _lib.ENGINE_SIMT
     p.engine = _lib.ENGINE_TENSOR
     assert built_lib.pcb_qconv2d_engine_for(ctypes.byref(p), 0) == _lib.PCB_ERR_UNSUPPORTED

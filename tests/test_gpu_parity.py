@@ -157,6 +157,42 @@ def test_general_conv_tensor_core_vs_oracle(gpu, oracle, shape, dtype):
     _check(dw, rdw, dtype, gpu, "dw")
 
 
+@pytest.mark.parametrize("shape", GENERAL_TENSOR_SHAPES + [(2, 40, 24, 6, 5, 1, 1, (1, 1), (0, 0, 0, 0))])
+def test_fp32_on_tensor_cores_3xtf32_vs_oracle(gpu, oracle, shape):
+    """fp32 tensors through the error-compensated TF32 kernels must hold the fp32 tolerance (1e-5), and agree with
+    the CUDA-core fp32 kernels."""
+    n, ci, co, h, w_, kh, kw, stride, pad = shape
+    x = uniform(51, (4 * n, ci, h, w_))
+    w = normal(52, (4, co, ci, kh, kw), std=(2.0 / (4 * ci * kh * kw)) ** 0.5)
+    b = uniform(53, (4, co))
+    ref = oracle.conv2d_fwd(x, w, b, stride, (1, 1), pad)
+    got = gpu.run_conv_fwd(x, w, b, stride, pad, "f32", "16p", "tensor")
+    _check(got, ref, "f32", gpu, "y")
+    dy = normal(54, ref.shape)
+    rdw, rdx = oracle.conv2d_bwd(x, w, dy, stride, (1, 1), pad)
+    dw, dx = gpu.run_conv_bwd(x, w, dy, stride, pad, "f32", "16p", "tensor", True)
+    _check(dx, rdx, "f32", gpu, "dx")
+    _check(dw, rdw, "f32", gpu, "dw")
+    simt = gpu.run_conv_fwd(x, w, b, stride, pad, "f32", "16p", "simt")
+    assert rel_err(got, simt) <= 1e-5
+
+
+@pytest.mark.parametrize("shape", [(3, 5, 7), (32, 64, 48), (17, 130, 70), (256, 512, 512)])
+@pytest.mark.parametrize("oi", [False, True])
+def test_dense_fp32_on_tensor_cores_vs_oracle(gpu, oracle, shape, oi):
+    b_, i, o = shape
+    x = normal(61, (4 * b_, i))
+    w = normal(62, (4, o, i) if oi else (4, i, o), std=(2.0 / (4 * i)) ** 0.5)
+    bias = uniform(63, (4, o))
+    ref = oracle.dense_fwd(x, w, bias, oi)
+    _check(gpu.run_dense_fwd(x, w, bias, oi, "f32", "16p", "tensor"), ref, "f32", gpu, "y")
+    dy = normal(64, ref.shape)
+    rdw, rdx = oracle.dense_bwd(x, w, dy, oi)
+    dw, dx = gpu.run_dense_bwd(x, w, dy, oi, "f32", "16p", "tensor", True)
+    _check(dw, rdw, "f32", gpu, "dw")
+    _check(dx, rdx, "f32", gpu, "dx")
+
+
 def test_tensor_engine_refuses_unsupported_shapes(gpu):
     from phoenix_core_b200 import _lib
     x = uniform(1, (4, 3, 5, 5))
@@ -164,8 +200,8 @@ def test_tensor_engine_refuses_unsupported_shapes(gpu):
     with pytest.raises(_lib.BackendError) as e:      # stride 3 has no tensor-core kernel
         gpu.run_conv_fwd(x, w, None, (3, 3), (1, 1, 1, 1), "f16", "16p", "tensor")
     assert e.value.status == _lib.PCB_ERR_UNSUPPORTED
-    with pytest.raises(_lib.BackendError) as e:      # fp32 tensors stay on the CUDA-core kernels
-        gpu.run_conv_fwd(x, w, None, (1, 1), (1, 1, 1, 1), "f32", "16p", "tensor")
+    with pytest.raises(_lib.BackendError) as e:      # the factorised 8-product form stays on the CUDA-core kernels
+        gpu.run_conv_fwd(x, w, None, (1, 1), (1, 1, 1, 1), "f16", "8p", "tensor")
     assert e.value.status == _lib.PCB_ERR_UNSUPPORTED
 
 
