@@ -6,7 +6,9 @@ For every shape times forward, backward-data and backward-filter separately (CUD
 3 warm-up + `reps` timed launches; every shape's tensors exceed L2 or the output is overwritten between
 iterations by the next launch of the same kernel) and prints one JSON line per (shape, dtype, pass) with
 TFLOP/s (F = 32*N*Ho*Wo*Co*Ci*kh*kw per pass), algorithmic GB/s and both fractions of the measured peaks,
-plus the kernel family that ran (1 = CUDA-core, 2 = tcgen05).
+plus the kernel family that ran (1 = CUDA-core, 2 = tcgen05). fp32 rows on the tensor cores execute three TF32
+MMAs per product: they also carry `executed_tflops` (3 F / t) and its fraction of a TF32 GEMM peak measured in the
+same run (cuBLAS, 8192^3, TF32 allowed). `--markdown` prints a table instead of JSON lines.
 Shapes: quaternion channels 16@112, 64@56, 128@28, 256@14, 512@7; 3x3 (pad 1) and 1x1; stride 1 and 2.
 """
 import argparse
@@ -37,6 +39,26 @@ def peaks():
             p = json.load(f)
         return p["hbm_gbs"], p["bf16_tflops_sustained"], "measured"
     return 6650.0, 1400.0, "fallback"
+
+
+_TF32_PEAK = None
+
+
+def tf32_peak():
+    """TFLOP/s of a square fp32 cuBLAS GEMM with TF32 tensor cores allowed, measured once per run."""
+    global _TF32_PEAK
+    if _TF32_PEAK is None:
+        keep = torch.backends.cuda.matmul.allow_tf32
+        torch.backends.cuda.matmul.allow_tf32 = True
+        n = 8192
+        a = torch.randn(n, n, device="cuda")
+        b = torch.randn(n, n, device="cuda")
+        c = torch.empty(n, n, device="cuda")
+        t = timed(lambda: torch.matmul(a, b, out=c), 20)
+        torch.backends.cuda.matmul.allow_tf32 = keep
+        _TF32_PEAK = 2.0 * n ** 3 / t / 1e12
+        del a, b, c
+    return _TF32_PEAK
 
 
 def timed(fn, reps):
@@ -86,10 +108,15 @@ def run_shape(n, c, hw, k, stride, dtype, variant, reps):
     out = []
     for name, (fn, nbytes, pass_id) in passes.items():
         t = timed(fn, reps)
-        out.append({"c": c, "hw": hw, "k": k, "stride": stride, "n": n, "dtype": dtype, "variant": variant, "pass": name,
-                    "engine": L.pcb_qconv2d_engine_for(ctypes.byref(d), pass_id), "ms": t * 1e3, "tflops": flops / t / 1e12,
-                    "gbs": nbytes / t / 1e9, "frac_tensor_peak": flops / t / 1e12 / tf, "frac_hbm_peak": nbytes / t / 1e9 / hbm,
-                    "peaks": src})
+        engine = L.pcb_qconv2d_engine_for(ctypes.byref(d), pass_id)
+        rec = {"c": c, "hw": hw, "k": k, "stride": stride, "n": n, "dtype": dtype, "variant": variant, "pass": name,
+               "engine": engine, "ms": t * 1e3, "tflops": flops / t / 1e12, "gbs": nbytes / t / 1e9,
+               "frac_tensor_peak": flops / t / 1e12 / tf, "frac_hbm_peak": nbytes / t / 1e9 / hbm, "peaks": src}
+        if dtype == "f32" and engine == 2:
+            rec["executed_tflops"] = 3.0 * flops / t / 1e12
+            rec["tf32_peak_tflops"] = tf32_peak()
+            rec["frac_tensor_peak"] = rec["executed_tflops"] / rec["tf32_peak_tflops"]
+        out.append(rec)
     _lib.check(L.pcb_check_device_status(_ptr(ws), ws.numel(), _stream()))
     return out
 
@@ -101,13 +128,22 @@ def main():
     ap.add_argument("--reps", type=int, default=10)
     ap.add_argument("--variant", default="16p")
     ap.add_argument("--quick", action="store_true", help="3x3 stride 1 and 1x1 stride 1 only")
+    ap.add_argument("--markdown", action="store_true", help="print a markdown table instead of JSON lines")
     a = ap.parse_args()
+    if a.markdown:
+        print("| c | hw | k | s | dtype | pass | fam | ms | TFLOP/s | GB/s | f_tensor | f_hbm |")
+        print("|---|---|---|---|---|---|---|---|---|---|---|---|")
     for dtype in a.dtypes.split(","):
         for c, hw in STAGES:
             for k in (3, 1):
                 for stride in ((1,) if a.quick else (1, 2)):
                     for rec in run_shape(a.batch, c, hw, k, stride, dtype, a.variant, a.reps if dtype != "f32" else max(2, a.reps // 3)):
-                        print(json.dumps(rec), flush=True)
+                        if a.markdown:
+                            print("| %d | %d | %d | %d | %s | %s | %d | %.3f | %.1f | %.0f | %.3f | %.3f |" % (
+                                rec["c"], rec["hw"], rec["k"], rec["stride"], rec["dtype"], rec["pass"], rec["engine"], rec["ms"],
+                                rec["tflops"], rec["gbs"], rec["frac_tensor_peak"], rec["frac_hbm_peak"]), flush=True)
+                        else:
+                            print(json.dumps(rec), flush=True)
                     torch.cuda.empty_cache()
 
 
