@@ -34,7 +34,7 @@ extern "C" {
 typedef enum {
     PCB_OK = 0,
     PCB_ERR_INVALID_ARGUMENT = -1,  /* bad shape / null pointer; the C++ layer rethrows std::invalid_argument */
-    PCB_ERR_UNSUPPORTED = -2,       /* dilation != 1, groups != 1, NHWC, ...: no CPU fallback exists         */
+    PCB_ERR_UNSUPPORTED = -2,       /* groups != 1, NHWC, ...: no CPU fallback exists                        */
     PCB_ERR_WORKSPACE = -3,         /* workspace missing or too small                                        */
     PCB_ERR_CUDA = -4,              /* a CUDA runtime call failed; see pcb_last_error_message()              */
     PCB_ERR_DEVICE_TIMEOUT = -5,    /* a bounded device-side wait expired (reported by pcb_check_device_status) */
@@ -42,6 +42,11 @@ typedef enum {
 } pcb_status;
 
 typedef enum { PCB_F32 = 0, PCB_F16 = 1, PCB_BF16 = 2 } pcb_dtype;
+
+/* Algebra of the layer (reference: upstride::Algebra, src/backend/types.hpp, product tables src/algebras.cc:5-145).
+ * Tensors carry D = 1 / 2 / 4 / 8 components on their leading axis. Zero is the quaternion algebra, so a
+ * zero-initialised descriptor describes a quaternion layer; host layers translate from the reference's enum. */
+typedef enum { PCB_ALGEBRA_QUATERNION = 0, PCB_ALGEBRA_REAL = 1, PCB_ALGEBRA_COMPLEX = 2, PCB_ALGEBRA_GA_300 = 3 } pcb_algebra;
 
 /* Formulation of the Hamilton product (reference: UPSTRIDE_MEMORY_OPTIMIZED, src/backend/backend.hpp:58):
  * 16 real products through the 4x4 signed block, or the factorised 8-product form. */
@@ -65,7 +70,7 @@ typedef struct {
     int32_t h, w;                   /* input height / width                                           */
     int32_t kh, kw;                 /* filter height / width                                          */
     int32_t stride_h, stride_w;
-    int32_t dilation_h, dilation_w; /* must be 1                                                      */
+    int32_t dilation_h, dilation_w; /* >= 1                                                           */
     int32_t pad_top, pad_left, pad_bottom, pad_right;
     int32_t groups;                 /* must be 1                                                      */
     int32_t has_bias;               /* forward only                                                   */
@@ -74,6 +79,7 @@ typedef struct {
     int32_t variant;                /* pcb_variant                                                    */
     int32_t fp16_policy;            /* pcb_fp16_policy                                                */
     int32_t engine;                 /* pcb_engine                                                     */
+    int32_t algebra;                /* pcb_algebra; n / ci / co count multivectors, tensors carry D*n etc. */
 } pcb_conv2d_desc;
 
 /* Mirrors upstride::DenseFwdDescriptor / DenseBwdDescriptor (src/backend/dense_descriptor.hpp:11-131). */
@@ -86,6 +92,7 @@ typedef struct {
     int32_t require_input_grad;
     int32_t variant;
     int32_t engine;
+    int32_t algebra;                /* pcb_algebra                                                    */
 } pcb_dense_desc;
 
 /* Library / build information. */

@@ -229,9 +229,75 @@ static const int QUAT_BACKPROP_ORDER[16] = {10, 11, 12, 13, 0, 1, 2, 3, 4, 5, 6,
 static const sign_entry COMPLEX_TABLE[4] = {{0, 0, 1}, {1, 1, 0}, {0, 1, 1}, {1, 0, 1}};
 static const int COMPLEX_BACKPROP_ORDER[4] = {2, 3, 0, 1};
 
-static int algebra_dims(int algebra) { return algebra == 1 ? 2 : (algebra == 2 ? 4 : 1); }
-static const sign_entry* algebra_table(int algebra) { return algebra == 1 ? COMPLEX_TABLE : QUAT_TABLE; }
-static const int* algebra_backprop(int algebra) { return algebra == 1 ? COMPLEX_BACKPROP_ORDER : QUAT_BACKPROP_ORDER; }
+/* GA(3,0,0) (src/algebras.cc:58-145). The reference lists 64 entries; here they are derived from the algebra
+ * itself and tests compare them, entry by entry, with the reference's list (tests/golden/reference_sign_tables.json).
+ * Components are the blades 1, e1, e2, e3, e12, e13, e23, e123; as generator bit sets: 0, 1, 2, 4, 3, 5, 6, 7.
+ * Blade a times blade b is +-blade (a XOR b); the sign is the parity of the transpositions that sort the
+ * generators (every generator squares to +1). Row `dim` holds, for left = 0..7, the right blade with
+ * left * right = +-dim, as the reference orders its rows. */
+static sign_entry GA300_TABLE[64];
+static int GA300_BACKPROP_ORDER[64];
+static int ga300_ready = 0;
+
+static int ga_bits(int c) { return c == 3 ? 4 : (c == 4 ? 3 : c); }
+
+static int ga_match(int k, int* used_l, int* used_r, int* pick) {
+    /* choose, for k = 0..7, a positive entry with right blade k and a left blade not used yet */
+    if (k == 8) return 1;
+    for (int j = 0; j < 64; ++j) {
+        if (!GA300_TABLE[j].positive || GA300_TABLE[j].right != k || used_l[GA300_TABLE[j].left]) continue;
+        used_l[GA300_TABLE[j].left] = 1; used_r[k] = 1; pick[k] = j;
+        if (ga_match(k + 1, used_l, used_r, pick)) return 1;
+        used_l[GA300_TABLE[j].left] = 0; used_r[k] = 0;
+    }
+    return 0;
+}
+
+static void ga300_init(void) {
+    if (ga300_ready) return;
+    for (int dim = 0; dim < 8; ++dim)
+        for (int left = 0; left < 8; ++left) {
+            const int a = ga_bits(left), b = a ^ ga_bits(dim);
+            int swaps = 0;
+            for (int s = a >> 1; s; s >>= 1) swaps += __builtin_popcount(s & b);
+            GA300_TABLE[dim * 8 + left].left = left;
+            GA300_TABLE[dim * 8 + left].right = ga_bits(b);
+            GA300_TABLE[dim * 8 + left].positive = !(swaps & 1);
+        }
+    /* Back-propagation visits first 8 positive entries that cover every left and every right blade once (they
+     * initialise the 8 + 8 gradient components), then the rest in table order, as the reference's order does
+     * (src/algebras.cc:135-145); which 8 come first only changes the order of the fp32 additions. */
+    int used_l[8] = {0}, used_r[8] = {0}, pick[8], taken[64] = {0}, n = 0;
+    ga_match(0, used_l, used_r, pick);
+    for (int k = 0; k < 8; ++k) { GA300_BACKPROP_ORDER[n++] = pick[k]; taken[pick[k]] = 1; }
+    for (int j = 0; j < 64; ++j) if (!taken[j]) GA300_BACKPROP_ORDER[n++] = j;
+    ga300_ready = 1;
+}
+
+static const int REAL_BACKPROP_ORDER[1] = {0};
+
+/* algebra: 0 = real, 1 = complex, 2 = quaternion, 3 = GA(3,0,0) (the order of upstride::Algebra) */
+static int algebra_dims(int algebra) { return algebra == 1 ? 2 : (algebra == 2 ? 4 : (algebra == 3 ? 8 : 1)); }
+static const sign_entry* algebra_table(int algebra) {
+    if (algebra == 3) { ga300_init(); return GA300_TABLE; }
+    return algebra == 1 ? COMPLEX_TABLE : QUAT_TABLE;      /* real: the first quaternion entry, {0, 0, +} */
+}
+static const int* algebra_backprop(int algebra) {
+    if (algebra == 3) { ga300_init(); return GA300_BACKPROP_ORDER; }
+    return algebra == 1 ? COMPLEX_BACKPROP_ORDER : (algebra == 2 ? QUAT_BACKPROP_ORDER : REAL_BACKPROP_ORDER);
+}
+
+/* Exposes a table so tests can compare it with the reference's list and with the signed block used on the GPU:
+ * out holds D*D triples (left, right, +1/-1), rows of D per output blade. */
+void orc_sign_table(int algebra, int* out) {
+    const int D = algebra_dims(algebra);
+    const sign_entry* T = algebra_table(algebra);
+    for (int i = 0; i < D * D; ++i) {
+        out[3 * i + 0] = T[i].left;
+        out[3 * i + 1] = T[i].right;
+        out[3 * i + 2] = T[i].positive ? 1 : -1;
+    }
+}
 
 /* Exposes the quaternion table so tests can compare it with the 4x4 signed block used on the GPU. */
 void orc_quaternion_sign_table(int* out48) {

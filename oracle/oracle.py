@@ -15,7 +15,8 @@ import numpy as np
 _HERE = os.path.dirname(os.path.abspath(__file__))
 _LIB_PATH = os.path.join(_HERE, "liboracle.so")
 
-REAL, COMPLEX, QUATERNION = 0, 1, 2
+REAL, COMPLEX, QUATERNION, GA_300 = 0, 1, 2, 3
+DIMS = {REAL: 1, COMPLEX: 2, QUATERNION: 4, GA_300: 8}
 VARIANT_16P, VARIANT_8P = 0, 1
 VALID, SAME = 0, 1
 
@@ -50,7 +51,7 @@ def lib():
         _lib.orc_real_conv_fwd.argtypes = [fp, fp, fp, fp, gp]
         _lib.orc_windowed_output_size_and_padding.argtypes = [ctypes.c_int] * 5 + [ctypes.POINTER(ctypes.c_int)] * 2
         _lib.orc_windowed_output_size.argtypes = [ctypes.c_int] * 6
-        _lib.orc_quaternion_sign_table.argtypes = [ctypes.POINTER(ctypes.c_int)]
+        _lib.orc_sign_table.argtypes = [ctypes.c_int, ctypes.POINTER(ctypes.c_int)]
     return _lib
 
 
@@ -72,10 +73,16 @@ def output_size(size, k, dilation, stride, before, after):
     return lib().orc_windowed_output_size(size, k, dilation, stride, before, after)
 
 
+def sign_table(algebra):
+    """The product table of an algebra: D*D triples (left, right, sign), rows of D per output component."""
+    n = DIMS[algebra] ** 2
+    out = (ctypes.c_int * (3 * n))()
+    lib().orc_sign_table(algebra, out)
+    return [(out[3 * i], out[3 * i + 1], out[3 * i + 2]) for i in range(n)]
+
+
 def quaternion_sign_table():
-    out = (ctypes.c_int * 48)()
-    lib().orc_quaternion_sign_table(out)
-    return [(out[3 * i], out[3 * i + 1], out[3 * i + 2]) for i in range(16)]
+    return sign_table(QUATERNION)
 
 
 def _geom(xshape, wshape, stride, dilation, pad, dims, real_input):
@@ -94,7 +101,7 @@ def _geom(xshape, wshape, stride, dilation, pad, dims, real_input):
 def conv2d_fwd(x, w, bias=None, stride=(1, 1), dilation=(1, 1), pad=(0, 0, 0, 0), algebra=QUATERNION,
                variant=VARIANT_16P, real_input=False):
     """Hyper-complex conv forward; ``pad`` = (top, left, bottom, right)."""
-    dims = {REAL: 1, COMPLEX: 2, QUATERNION: 4}[algebra]
+    dims = DIMS[algebra]
     x = np.ascontiguousarray(x, np.float32)
     w = np.ascontiguousarray(w, np.float32)
     bias = None if bias is None else np.ascontiguousarray(bias, np.float32)
@@ -109,7 +116,7 @@ def conv2d_fwd(x, w, bias=None, stride=(1, 1), dilation=(1, 1), pad=(0, 0, 0, 0)
 def conv2d_bwd(x, w, dy, stride=(1, 1), dilation=(1, 1), pad=(0, 0, 0, 0), algebra=QUATERNION,
                variant=VARIANT_16P, need_dx=True):
     """Returns (dW, dX or None)."""
-    dims = {REAL: 1, COMPLEX: 2, QUATERNION: 4}[algebra]
+    dims = DIMS[algebra]
     x = np.ascontiguousarray(x, np.float32)
     w = np.ascontiguousarray(w, np.float32)
     dy = np.ascontiguousarray(dy, np.float32)
@@ -124,7 +131,7 @@ def conv2d_bwd(x, w, dy, stride=(1, 1), dilation=(1, 1), pad=(0, 0, 0, 0), algeb
 
 
 def dense_fwd(x, w, bias=None, oi=False, algebra=QUATERNION, variant=VARIANT_16P):
-    dims = {REAL: 1, COMPLEX: 2, QUATERNION: 4}[algebra]
+    dims = DIMS[algebra]
     x = np.ascontiguousarray(x, np.float32)
     w = np.ascontiguousarray(w, np.float32)
     bias = None if bias is None else np.ascontiguousarray(bias, np.float32)
@@ -140,7 +147,7 @@ def dense_fwd(x, w, bias=None, oi=False, algebra=QUATERNION, variant=VARIANT_16P
 
 def dense_bwd(x, w, dy, oi=False, algebra=QUATERNION, variant=VARIANT_16P, need_dx=True):
     """Returns (dW in [D, I, O] orientation -- as both reference backends emit it -- and dX or None)."""
-    dims = {REAL: 1, COMPLEX: 2, QUATERNION: 4}[algebra]
+    dims = DIMS[algebra]
     x = np.ascontiguousarray(x, np.float32)
     w = np.ascontiguousarray(w, np.float32)
     dy = np.ascontiguousarray(dy, np.float32)

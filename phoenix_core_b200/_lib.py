@@ -28,14 +28,14 @@ class ConvDesc(ctypes.Structure):
     _fields_ = [(k, ctypes.c_int32) for k in (
         "dtype", "n", "ci", "co", "h", "w", "kh", "kw", "stride_h", "stride_w", "dilation_h", "dilation_w",
         "pad_top", "pad_left", "pad_bottom", "pad_right", "groups", "has_bias", "require_input_grad",
-        "real_valued_input", "variant", "fp16_policy", "engine")]
+        "real_valued_input", "variant", "fp16_policy", "engine", "algebra")]
 
 
 class DenseDesc(ctypes.Structure):
     """pcb_dense_desc"""
     _fields_ = [(k, ctypes.c_int32) for k in (
         "dtype", "batch", "in_features", "out_features", "filter_oi", "has_bias", "require_input_grad", "variant",
-        "engine")]
+        "engine", "algebra")]
 
 
 # name -> (restype, argtypes); this is every symbol include/phoenix_core_b200.h declares

@@ -39,6 +39,7 @@ int conv_geom(const pcb_conv2d_desc* d, Geom& g) {
     if (d->groups != 1) { set_error("grouped convolution is not supported (groups = %d)", d->groups); return PCB_ERR_UNSUPPORTED; }
     if (d->dilation_h < 1 || d->dilation_w < 1) { set_error("dilation must be >= 1"); return PCB_ERR_INVALID_ARGUMENT; }
     if (d->variant != PCB_VARIANT_16_PRODUCT && d->variant != PCB_VARIANT_8_PRODUCT) { set_error("unknown variant"); return PCB_ERR_INVALID_ARGUMENT; }
+    if (!algebra_setup(d->algebra, g)) { set_error("unknown algebra %d", d->algebra); return PCB_ERR_INVALID_ARGUMENT; }
     g.Nb = d->n; g.Ci = d->ci; g.Co = d->co; g.H = d->h; g.W = d->w;
     g.KH = d->kh; g.KW = d->kw; g.SH = d->stride_h; g.SW = d->stride_w; g.DH = d->dilation_h; g.DW = d->dilation_w;
     g.PT = d->pad_top; g.PL = d->pad_left;
@@ -46,9 +47,9 @@ int conv_geom(const pcb_conv2d_desc* d, Geom& g) {
     g.WO = out_size(d->w, d->kw, d->dilation_w, d->stride_w, d->pad_left, d->pad_right);
     if (g.HO <= 0 || g.WO <= 0) { set_error("empty convolution output (%d x %d)", g.HO, g.WO); return PCB_ERR_INVALID_ARGUMENT; }
     g.w_io = 0; g.dw_io = 0; g.real_in = d->real_valued_input ? 1 : 0; g.has_bias = d->has_bias ? 1 : 0;
-    const long long xn = (long long)(g.real_in ? 1 : 4) * g.Nb * g.Ci * g.H * g.W;
-    const long long yn = 4LL * g.Nb * g.Co * g.HO * g.WO;
-    const long long wn = 4LL * g.Co * g.Ci * g.KH * g.KW;
+    const long long xn = (long long)(g.real_in ? 1 : g.nc) * g.Nb * g.Ci * g.H * g.W;
+    const long long yn = (long long)g.nc * g.Nb * g.Co * g.HO * g.WO;
+    const long long wn = (long long)g.nc * g.Co * g.Ci * g.KH * g.KW;
     if (xn > MAX_NUMEL || yn > MAX_NUMEL || wn > MAX_NUMEL || g.H > 32767 || g.W > 32767) {
         set_error("tensor too large for 32-bit element offsets");
         return PCB_ERR_TOO_LARGE;
@@ -61,17 +62,22 @@ int dense_geom(const pcb_dense_desc* d, Geom& g) {
     if (d->dtype < PCB_F32 || d->dtype > PCB_BF16) { set_error("unknown dtype %d", d->dtype); return PCB_ERR_INVALID_ARGUMENT; }
     if (d->batch < 0 || d->in_features <= 0 || d->out_features <= 0) { set_error("invalid dense geometry"); return PCB_ERR_INVALID_ARGUMENT; }
     if (d->variant != PCB_VARIANT_16_PRODUCT && d->variant != PCB_VARIANT_8_PRODUCT) { set_error("unknown variant"); return PCB_ERR_INVALID_ARGUMENT; }
+    if (!algebra_setup(d->algebra, g)) { set_error("unknown algebra %d", d->algebra); return PCB_ERR_INVALID_ARGUMENT; }
     g.Nb = d->batch; g.Ci = d->in_features; g.Co = d->out_features;
     g.H = g.W = g.HO = g.WO = 1; g.KH = g.KW = 1; g.SH = g.SW = 1; g.DH = g.DW = 1; g.PT = g.PL = 0;
     g.w_io = d->filter_oi ? 0 : 1;
     g.dw_io = 1;   // both reference backends emit the filter gradient input-major (src/backend/cudnn/dense.hpp:187-195)
     g.real_in = 0; g.has_bias = d->has_bias ? 1 : 0;
-    if (4LL * g.Nb * g.Ci > MAX_NUMEL || 4LL * g.Nb * g.Co > MAX_NUMEL || 4LL * g.Ci * g.Co > MAX_NUMEL) {
+    if ((long long)g.nc * g.Nb * g.Ci > MAX_NUMEL || (long long)g.nc * g.Nb * g.Co > MAX_NUMEL || (long long)g.nc * g.Ci * g.Co > MAX_NUMEL) {
         set_error("tensor too large for 32-bit element offsets");
         return PCB_ERR_TOO_LARGE;
     }
     return PCB_OK;
 }
+
+// The factorised 8-product form exists for quaternions only (reference: src/conv2d.hpp:167, :433); every other
+// algebra runs the generic product whatever the variant says.
+int variant_for(const Geom& g, int variant) { return g.nc == 4 ? variant : (int)PCB_VARIANT_16_PRODUCT; }
 
 // Layout of the caller's workspace: [0, 256) status block (first word: device wait status), then scratch.
 constexpr size_t WS_HEADER = 256;
@@ -141,28 +147,28 @@ int pcb_conv2d_output_size(const pcb_conv2d_desc* desc, int32_t* out_h, int32_t*
 size_t pcb_qconv2d_fwd_workspace_size(const pcb_conv2d_desc* desc) {
     Geom g;
     if (conv_geom(desc, g) != PCB_OK) return 0;
-    return workspace_bytes(PASS_FWD, desc->dtype, desc->variant, desc->engine, g);
+    return workspace_bytes(PASS_FWD, desc->dtype, variant_for(g, desc->variant), desc->engine, g);
 }
 
 size_t pcb_qconv2d_bwd_workspace_size(const pcb_conv2d_desc* desc) {
     Geom g;
     if (conv_geom(desc, g) != PCB_OK) return 0;
-    const size_t a = workspace_bytes(PASS_BWD_DATA, desc->dtype, desc->variant, desc->engine, g);
-    const size_t b = workspace_bytes(PASS_BWD_FILTER, desc->dtype, desc->variant, desc->engine, g);
+    const size_t a = workspace_bytes(PASS_BWD_DATA, desc->dtype, variant_for(g, desc->variant), desc->engine, g);
+    const size_t b = workspace_bytes(PASS_BWD_FILTER, desc->dtype, variant_for(g, desc->variant), desc->engine, g);
     return a > b ? a : b;
 }
 
 size_t pcb_qdense_fwd_workspace_size(const pcb_dense_desc* desc) {
     Geom g;
     if (dense_geom(desc, g) != PCB_OK) return 0;
-    return workspace_bytes(PASS_FWD, desc->dtype, desc->variant, desc->engine, g);
+    return workspace_bytes(PASS_FWD, desc->dtype, variant_for(g, desc->variant), desc->engine, g);
 }
 
 size_t pcb_qdense_bwd_workspace_size(const pcb_dense_desc* desc) {
     Geom g;
     if (dense_geom(desc, g) != PCB_OK) return 0;
-    const size_t a = workspace_bytes(PASS_BWD_DATA, desc->dtype, desc->variant, desc->engine, g);
-    const size_t b = workspace_bytes(PASS_BWD_FILTER, desc->dtype, desc->variant, desc->engine, g);
+    const size_t a = workspace_bytes(PASS_BWD_DATA, desc->dtype, variant_for(g, desc->variant), desc->engine, g);
+    const size_t b = workspace_bytes(PASS_BWD_FILTER, desc->dtype, variant_for(g, desc->variant), desc->engine, g);
     return a > b ? a : b;
 }
 
@@ -174,7 +180,7 @@ int pcb_qconv2d_fwd(const pcb_conv2d_desc* desc, const void* x, const void* w, c
     if (g.Nb == 0) return PCB_OK;   // empty input: silent no-op, as the reference (src/conv2d.hpp:81-82)
     if (!x || !w || !y || (g.has_bias && !bias)) { set_error("null tensor pointer"); return PCB_ERR_INVALID_ARGUMENT; }
     if (g.real_in && g.has_bias) { set_error("bias addition is not supported for real-valued inputs"); return PCB_ERR_UNSUPPORTED; }
-    return run_pass(PASS_FWD, desc->dtype, desc->variant, desc->engine, g, w, x, bias, y, workspace, workspace_bytes_, (cudaStream_t)stream);
+    return run_pass(PASS_FWD, desc->dtype, variant_for(g, desc->variant), desc->engine, g, w, x, bias, y, workspace, workspace_bytes_, (cudaStream_t)stream);
 }
 
 int pcb_qconv2d_bwd_data(const pcb_conv2d_desc* desc, const void* w, const void* dy, void* dx,
@@ -185,7 +191,7 @@ int pcb_qconv2d_bwd_data(const pcb_conv2d_desc* desc, const void* w, const void*
     if (g.Nb == 0) return PCB_OK;
     if (g.real_in) { set_error("input gradient required for a real-valued input tensor"); return PCB_ERR_UNSUPPORTED; }
     if (!w || !dy || !dx) { set_error("null tensor pointer"); return PCB_ERR_INVALID_ARGUMENT; }
-    return run_pass(PASS_BWD_DATA, desc->dtype, desc->variant, desc->engine, g, w, dy, nullptr, dx, workspace, workspace_bytes_, (cudaStream_t)stream);
+    return run_pass(PASS_BWD_DATA, desc->dtype, variant_for(g, desc->variant), desc->engine, g, w, dy, nullptr, dx, workspace, workspace_bytes_, (cudaStream_t)stream);
 }
 
 int pcb_qconv2d_bwd_filter(const pcb_conv2d_desc* desc, const void* x, const void* dy, void* dw,
@@ -195,11 +201,11 @@ int pcb_qconv2d_bwd_filter(const pcb_conv2d_desc* desc, const void* x, const voi
     if (rc != PCB_OK) return rc;
     if (!dw) { set_error("null tensor pointer"); return PCB_ERR_INVALID_ARGUMENT; }
     if (g.Nb == 0) {   // empty input: zero filter gradient, as the reference (src/conv2d.hpp:341-344)
-        PCB_CUDA_TRY(cudaMemsetAsync(dw, 0, (size_t)4 * g.Co * g.Ci * g.KH * g.KW * dtype_size(desc->dtype), (cudaStream_t)stream));
+        PCB_CUDA_TRY(cudaMemsetAsync(dw, 0, (size_t)g.nc * g.Co * g.Ci * g.KH * g.KW * dtype_size(desc->dtype), (cudaStream_t)stream));
         return PCB_OK;
     }
     if (!x || !dy) { set_error("null tensor pointer"); return PCB_ERR_INVALID_ARGUMENT; }
-    return run_pass(PASS_BWD_FILTER, desc->dtype, desc->variant, desc->engine, g, dy, x, nullptr, dw, workspace, workspace_bytes_, (cudaStream_t)stream);
+    return run_pass(PASS_BWD_FILTER, desc->dtype, variant_for(g, desc->variant), desc->engine, g, dy, x, nullptr, dw, workspace, workspace_bytes_, (cudaStream_t)stream);
 }
 
 int pcb_qconv2d_bwd_filter_noalloc(const pcb_conv2d_desc* desc, const void* x, const void* dy, void* dw, void* stream) {
@@ -207,17 +213,17 @@ int pcb_qconv2d_bwd_filter_noalloc(const pcb_conv2d_desc* desc, const void* x, c
     int rc = conv_geom(desc, g);
     if (rc != PCB_OK) return rc;
     if (!dw) { set_error("null tensor pointer"); return PCB_ERR_INVALID_ARGUMENT; }
-    if ((size_t)4 * g.Co * g.Ci * g.KH * g.KW > simt_static_scratch_capacity()) {
+    if ((size_t)g.nc * g.Co * g.Ci * g.KH * g.KW > simt_static_scratch_capacity()) {
         set_error("filter gradient of %zu elements exceeds the built-in scratch of %zu elements",
-                  (size_t)4 * g.Co * g.Ci * g.KH * g.KW, simt_static_scratch_capacity());
+                  (size_t)g.nc * g.Co * g.Ci * g.KH * g.KW, simt_static_scratch_capacity());
         return PCB_ERR_TOO_LARGE;
     }
     if (g.Nb == 0) {
-        PCB_CUDA_TRY(cudaMemsetAsync(dw, 0, (size_t)4 * g.Co * g.Ci * g.KH * g.KW * dtype_size(desc->dtype), (cudaStream_t)stream));
+        PCB_CUDA_TRY(cudaMemsetAsync(dw, 0, (size_t)g.nc * g.Co * g.Ci * g.KH * g.KW * dtype_size(desc->dtype), (cudaStream_t)stream));
         return PCB_OK;
     }
     if (!x || !dy) { set_error("null tensor pointer"); return PCB_ERR_INVALID_ARGUMENT; }
-    return simt_bwd_filter_static(desc->dtype, desc->variant, g, dy, x, dw, (cudaStream_t)stream);
+    return simt_bwd_filter_static(desc->dtype, variant_for(g, desc->variant), g, dy, x, dw, (cudaStream_t)stream);
 }
 
 int pcb_qconv2d_bwd(const pcb_conv2d_desc* desc, const void* x, const void* w, const void* dy, void* dw, void* dx,
@@ -235,7 +241,7 @@ int pcb_qdense_fwd(const pcb_dense_desc* desc, const void* x, const void* w, con
     if (rc != PCB_OK) return rc;
     if (g.Nb == 0) return PCB_OK;
     if (!x || !w || !y || (g.has_bias && !bias)) { set_error("null tensor pointer"); return PCB_ERR_INVALID_ARGUMENT; }
-    return run_pass(PASS_FWD, desc->dtype, desc->variant, desc->engine, g, w, x, bias, y, workspace, workspace_bytes_, (cudaStream_t)stream);
+    return run_pass(PASS_FWD, desc->dtype, variant_for(g, desc->variant), desc->engine, g, w, x, bias, y, workspace, workspace_bytes_, (cudaStream_t)stream);
 }
 
 int pcb_qdense_bwd(const pcb_dense_desc* desc, const void* x, const void* w, const void* dy, void* dw, void* dx,
@@ -245,14 +251,14 @@ int pcb_qdense_bwd(const pcb_dense_desc* desc, const void* x, const void* w, con
     if (rc != PCB_OK) return rc;
     if (!dw) { set_error("null tensor pointer"); return PCB_ERR_INVALID_ARGUMENT; }
     if (g.Nb == 0) {   // src/dense.hpp:226-229
-        PCB_CUDA_TRY(cudaMemsetAsync(dw, 0, (size_t)4 * g.Co * g.Ci * dtype_size(desc->dtype), (cudaStream_t)stream));
+        PCB_CUDA_TRY(cudaMemsetAsync(dw, 0, (size_t)g.nc * g.Co * g.Ci * dtype_size(desc->dtype), (cudaStream_t)stream));
         return PCB_OK;
     }
     if (!x || !w || !dy || (desc->require_input_grad && !dx)) { set_error("null tensor pointer"); return PCB_ERR_INVALID_ARGUMENT; }
-    rc = run_pass(PASS_BWD_FILTER, desc->dtype, desc->variant, desc->engine, g, dy, x, nullptr, dw, workspace, workspace_bytes_, (cudaStream_t)stream);
+    rc = run_pass(PASS_BWD_FILTER, desc->dtype, variant_for(g, desc->variant), desc->engine, g, dy, x, nullptr, dw, workspace, workspace_bytes_, (cudaStream_t)stream);
     if (rc != PCB_OK) return rc;
     if (desc->require_input_grad)
-        rc = run_pass(PASS_BWD_DATA, desc->dtype, desc->variant, desc->engine, g, w, dy, nullptr, dx, workspace, workspace_bytes_, (cudaStream_t)stream);
+        rc = run_pass(PASS_BWD_DATA, desc->dtype, variant_for(g, desc->variant), desc->engine, g, w, dy, nullptr, dx, workspace, workspace_bytes_, (cudaStream_t)stream);
     return rc;
 }
 
@@ -261,7 +267,7 @@ int pcb_qconv2d_engine_for(const pcb_conv2d_desc* desc, int pass) {
     const int rc = conv_geom(desc, g);
     if (rc != PCB_OK) return rc;
     if (pass < 0 || pass > 2) { set_error("pass must be 0, 1 or 2"); return PCB_ERR_INVALID_ARGUMENT; }
-    if (desc->engine != PCB_ENGINE_SIMT && tensor_path_supported((Pass)pass, desc->dtype, desc->variant, g)) return PCB_ENGINE_TENSOR;
+    if (desc->engine != PCB_ENGINE_SIMT && tensor_path_supported((Pass)pass, desc->dtype, variant_for(g, desc->variant), g)) return PCB_ENGINE_TENSOR;
     return desc->engine == PCB_ENGINE_TENSOR ? (int)PCB_ERR_UNSUPPORTED : (int)PCB_ENGINE_SIMT;
 }
 
@@ -270,7 +276,7 @@ int pcb_qdense_engine_for(const pcb_dense_desc* desc, int pass) {
     const int rc = dense_geom(desc, g);
     if (rc != PCB_OK) return rc;
     if (pass < 0 || pass > 2) { set_error("pass must be 0, 1 or 2"); return PCB_ERR_INVALID_ARGUMENT; }
-    if (desc->engine != PCB_ENGINE_SIMT && tensor_path_supported((Pass)pass, desc->dtype, desc->variant, g)) return PCB_ENGINE_TENSOR;
+    if (desc->engine != PCB_ENGINE_SIMT && tensor_path_supported((Pass)pass, desc->dtype, variant_for(g, desc->variant), g)) return PCB_ENGINE_TENSOR;
     return desc->engine == PCB_ENGINE_TENSOR ? (int)PCB_ERR_UNSUPPORTED : (int)PCB_ENGINE_SIMT;
 }
 

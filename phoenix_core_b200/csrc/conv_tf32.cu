@@ -288,7 +288,7 @@ __global__ void pack_activations_f32_kernel(const float* __restrict__ x, float* 
 // Backward-data: Wexp[tap][m = l*Ci + ci][k = d*Cop + co] = s(l,d) * w[l^d](co, ci, taps-1-tap)
 // w_io: the filters are stored [r][ci][co] (dense input-major layout, one tap).
 __global__ void pack_filters_f32_kernel(const float* __restrict__ w, float* __restrict__ hi, float* __restrict__ lo, int Co, int Ci, int taps,
-                                        int Mp, int Kp, int Cp, int transposed, int w_io) {
+                                        int Mp, int Kp, int Cp, int transposed, int w_io, int nc, int ga, unsigned long long neg) {
     const size_t total = (size_t)taps * Mp * Kp;
     const int Cm = transposed ? Ci : Co, Ck = transposed ? Co : Ci;
     for (size_t idx = (size_t)blockIdx.x * blockDim.x + threadIdx.x; idx < total; idx += (size_t)gridDim.x * blockDim.x) {
@@ -298,13 +298,14 @@ __global__ void pack_filters_f32_kernel(const float* __restrict__ w, float* __re
         const int cm_comp = m / Cm, cm = m - cm_comp * Cm;
         const int ck_comp = k / Cp, ck = k - ck_comp * Cp;
         float v = 0.f;
-        if (cm_comp < 4 && ck < Ck) {
+        if (cm_comp < nc && ck_comp < nc && ck < Ck) {
             const int d = transposed ? ck_comp : cm_comp, l = transposed ? cm_comp : ck_comp;
             const int co = transposed ? ck : cm, ci = transposed ? cm : ck;
             const int src_tap = transposed ? taps - 1 - tap : tap;
-            const size_t src = w_io ? ((size_t)(l ^ d) * Ci + ci) * Co + co : ((size_t)((l ^ d) * Co + co) * Ci + ci) * taps + src_tap;
+            const int r = alg_pair(ga, l, d);
+            const size_t src = w_io ? ((size_t)r * Ci + ci) * Co + co : ((size_t)(r * Co + co) * Ci + ci) * taps + src_tap;
             v = __ldg(w + src);
-            if (quat_negative(l, d)) v = -v;
+            if (alg_negative(neg, l, d)) v = -v;
         }
         float h, lw;
         split_tf32(v, h, lw);
@@ -324,6 +325,8 @@ struct TFParams {
     int Nb, Co, Ci, HO, WO, Cop, Cip, cbA, cbB;             // channel-block width in fp32 elements: 32
     int KH, KW, SH, SW, DH, DW, PW, PH, PN, tiles_w, tiles_h, tiles_n;
     int m_tiles, n_tiles, n_tile_cols, splits, steps_per_split, merged_a, merged_b;
+    int nc, ga;                                              // algebra: components, GA(3,0,0) component order
+    unsigned long long neg;                                  // negative entries of the block, bit (8*l + d)
 };
 
 // leading offset = distance between 32-channel blocks, stride offset = distance between groups of 4 pixel rows
@@ -486,9 +489,9 @@ qconv_filter_tf32_kernel(const __grid_constant__ CUtensorMap map_dy_hi, const __
             const int row = q * 32 + lane;
             const int blk = blockA0 + row / p.cbA;
             const int d = blk / bpcA, co = (blk % bpcA) * p.cbA + row % p.cbA;
-            const bool row_ok = d < 4 && co < p.Co;
+            const bool row_ok = d < p.nc && co < p.Co;
             const size_t comp_stride = (size_t)p.Co * p.Ci;
-            float* tap_base = dw32 + (size_t)tap * 4 * comp_stride;
+            float* tap_base = dw32 + (size_t)tap * p.nc * comp_stride;
 #pragma unroll
             for (int cb = 0; cb < 4; ++cb) {
                 const int col0 = chalf * 128 + cb * 32;
@@ -505,9 +508,9 @@ qconv_filter_tf32_kernel(const __grid_constant__ CUtensorMap map_dy_hi, const __
                     if (col >= p.n_tile_cols) continue;
                     const int nblk = blockB0 + col / p.cbB;
                     const int l = nblk / bpcB, ci = (nblk % bpcB) * p.cbB + col % p.cbB;
-                    if (l >= 4 || ci >= p.Ci) continue;
-                    const float sgn = quat_negative(l, d) ? -1.f : 1.f;
-                    float* dst = tap_base + (size_t)(l ^ d) * comp_stride + (size_t)co * p.Ci + ci;
+                    if (l >= p.nc || ci >= p.Ci) continue;
+                    const float sgn = alg_negative(p.neg, l, d) ? -1.f : 1.f;
+                    float* dst = tap_base + (size_t)alg_pair(p.ga, l, d) * comp_stride + (size_t)co * p.Ci + ci;
                     if ((p.Ci & 3) == 0) {
                         red_add_f32x4(dst, sgn * __uint_as_float(v[4 * g4]), sgn * __uint_as_float(v[4 * g4 + 1]),
                                       sgn * __uint_as_float(v[4 * g4 + 2]), sgn * __uint_as_float(v[4 * g4 + 3]));
@@ -526,8 +529,8 @@ qconv_filter_tf32_kernel(const __grid_constant__ CUtensorMap map_dy_hi, const __
 }
 
 // scratch [tap][r][co][ci] -> dw [r][co][ci][tap], or [r][ci][co] for dense layers (input-major, one tap)
-__global__ void unpack_filter_grad_f32_kernel(const float* __restrict__ src, float* __restrict__ dw, int taps, int Co, int Ci, int dw_io) {
-    const size_t per_tap = (size_t)4 * Co * Ci, total = per_tap * taps;
+__global__ void unpack_filter_grad_f32_kernel(const float* __restrict__ src, float* __restrict__ dw, int taps, int Co, int Ci, int dw_io, int nc) {
+    const size_t per_tap = (size_t)nc * Co * Ci, total = per_tap * taps;
     for (size_t idx = (size_t)blockIdx.x * blockDim.x + threadIdx.x; idx < total; idx += (size_t)gridDim.x * blockDim.x) {
         if (dw_io) {
             const int co = (int)(idx % Co);
@@ -556,11 +559,11 @@ Plan32 make_plan32(Pass pass, const Geom& g) {
         pl.pad_top = (g.KH - 1) * g.DH - g.PT; pl.pad_left = (g.KW - 1) * g.DW - g.PL; pl.SH = 1; pl.SW = 1;
         pl.ins_h = g.SH; pl.ins_w = g.SW;
     }
-    pl.LK = (pass == PASS_FWD && g.real_in) ? 1 : 4;
+    pl.LK = (pass == PASS_FWD && g.real_in) ? 1 : g.nc;
     pl.Cp = round_up(pl.Cin, 16);
     pl.Hp = (pl.Hout - 1) * pl.SH + (g.KH - 1) * g.DH + 1;
     pl.Wp = (pl.Wout - 1) * pl.SW + (g.KW - 1) * g.DW + 1;
-    pl.Mp = round_up(4 * pl.Cout, TM);
+    pl.Mp = round_up(g.nc * pl.Cout, TM);
     pl.Kp = pl.LK * pl.Cp;
     pl.xp_bytes = ((size_t)pl.LK * g.Nb * pl.Hp * pl.Wp * pl.Cp * 4 + 1023) / 1024 * 1024;
     pl.w_bytes = ((size_t)g.KH * g.KW * pl.Mp * pl.Kp * 4 + 1023) / 1024 * 1024;
@@ -578,9 +581,9 @@ FilterPlan32 make_filter_plan32(const Geom& g) {
     f.Cip = round_up(g.Ci, 32);
     f.Hp = (g.HO - 1) * g.SH + (g.KH - 1) * g.DH + 1;
     f.Wp = (g.WO - 1) * g.SW + (g.KW - 1) * g.DW + 1;
-    f.xp_bytes = ((size_t)4 * g.Nb * f.Hp * f.Wp * f.Cip * 4 + 1023) / 1024 * 1024;
-    f.dyp_bytes = ((size_t)4 * g.Nb * g.HO * g.WO * f.Cop * 4 + 1023) / 1024 * 1024;
-    f.acc_bytes = ((size_t)4 * g.Co * g.Ci * g.KH * g.KW * 4 + 1023) / 1024 * 1024;
+    f.xp_bytes = ((size_t)g.nc * g.Nb * f.Hp * f.Wp * f.Cip * 4 + 1023) / 1024 * 1024;
+    f.dyp_bytes = ((size_t)g.nc * g.Nb * g.HO * g.WO * f.Cop * 4 + 1023) / 1024 * 1024;
+    f.acc_bytes = ((size_t)g.nc * g.Co * g.Ci * g.KH * g.KW * 4 + 1023) / 1024 * 1024;
     return f;
 }
 
@@ -624,14 +627,15 @@ static int conv_tf32_filter_launch(const Geom& g, const float* dy, const float* 
     float* y_hi = reinterpret_cast<float*>(s8 + 2 * f.xp_bytes);
     float* y_lo = reinterpret_cast<float*>(s8 + 2 * f.xp_bytes + f.dyp_bytes);
     float* acc = reinterpret_cast<float*>(s8 + 2 * f.xp_bytes + 2 * f.dyp_bytes);
-    pack_activations_f32_kernel<<<grid_cap((size_t)4 * g.Nb * f.Hp * f.Wp * (f.Cip / 4), 256, 16), 256, 0, stream>>>(
-        x, x_hi, x_lo, 4 * g.Nb, g.Ci, g.H, g.W, f.Hp, f.Wp, f.Cip, g.PT, g.PL, 1, 1);
-    pack_activations_f32_kernel<<<grid_cap((size_t)4 * g.Nb * g.HO * g.WO * (f.Cop / 4), 256, 16), 256, 0, stream>>>(
-        dy, y_hi, y_lo, 4 * g.Nb, g.Co, g.HO, g.WO, g.HO, g.WO, f.Cop, 0, 0, 1, 1);
+    pack_activations_f32_kernel<<<grid_cap((size_t)g.nc * g.Nb * f.Hp * f.Wp * (f.Cip / 4), 256, 16), 256, 0, stream>>>(
+        x, x_hi, x_lo, g.nc * g.Nb, g.Ci, g.H, g.W, f.Hp, f.Wp, f.Cip, g.PT, g.PL, 1, 1);
+    pack_activations_f32_kernel<<<grid_cap((size_t)g.nc * g.Nb * g.HO * g.WO * (f.Cop / 4), 256, 16), 256, 0, stream>>>(
+        dy, y_hi, y_lo, g.nc * g.Nb, g.Co, g.HO, g.WO, g.HO, g.WO, f.Cop, 0, 0, 1, 1);
     PCB_CUDA_TRY(cudaGetLastError());
-    PCB_CUDA_TRY(cudaMemsetAsync(acc, 0, (size_t)4 * g.Co * g.Ci * taps * sizeof(float), stream));
+    PCB_CUDA_TRY(cudaMemsetAsync(acc, 0, (size_t)g.nc * g.Co * g.Ci * taps * sizeof(float), stream));
 
     TFParams p;
+    p.nc = g.nc; p.ga = g.ga; p.neg = g.neg;
     p.Nb = g.Nb; p.Co = g.Co; p.Ci = g.Ci; p.HO = g.HO; p.WO = g.WO; p.Cop = f.Cop; p.Cip = f.Cip;
     p.cbA = 32; p.cbB = 32;
     p.KH = g.KH; p.KW = g.KW; p.SH = g.SH; p.SW = g.SW; p.DH = g.DH; p.DW = g.DW;
@@ -645,7 +649,7 @@ static int conv_tf32_filter_launch(const Geom& g, const float* dy, const float* 
             }
     }
     p.tiles_w = (g.WO + p.PW - 1) / p.PW; p.tiles_h = (g.HO + p.PH - 1) / p.PH; p.tiles_n = (g.Nb + p.PN - 1) / p.PN;
-    const int m_cols = 4 * f.Cop, n_cols = 4 * f.Cip;
+    const int m_cols = g.nc * f.Cop, n_cols = g.nc * f.Cip;
     p.m_tiles = (m_cols + TM - 1) / TM;
     p.n_tiles = (n_cols + TN - 1) / TN;
     p.n_tile_cols = n_cols < TN ? n_cols : TN;
@@ -662,7 +666,7 @@ static int conv_tf32_filter_launch(const Geom& g, const float* dy, const float* 
     auto swz = [](int) { return CU_TENSOR_MAP_SWIZZLE_128B_ATOM_32B; };
     alignas(64) CUtensorMap m_dy_hi, m_dy_lo, m_x_hi, m_x_lo;
     {
-        const cuuint64_t dims[5] = {(cuuint64_t)f.Cop, (cuuint64_t)g.WO, (cuuint64_t)g.HO, (cuuint64_t)g.Nb, 4};
+        const cuuint64_t dims[5] = {(cuuint64_t)f.Cop, (cuuint64_t)g.WO, (cuuint64_t)g.HO, (cuuint64_t)g.Nb, (cuuint64_t)g.nc};
         const cuuint64_t strides[4] = {(cuuint64_t)f.Cop * 4, (cuuint64_t)g.WO * f.Cop * 4, (cuuint64_t)g.HO * g.WO * f.Cop * 4,
                                        (cuuint64_t)g.Nb * g.HO * g.WO * f.Cop * 4};
         const cuuint32_t box[5] = {(cuuint32_t)p.cbA, (cuuint32_t)p.PW, (cuuint32_t)p.PH, (cuuint32_t)p.PN, (cuuint32_t)(p.merged_a ? TM / p.cbA : 1)};
@@ -671,7 +675,7 @@ static int conv_tf32_filter_launch(const Geom& g, const float* dy, const float* 
         if (rc != PCB_OK) return rc;
     }
     {
-        const cuuint64_t dims[5] = {(cuuint64_t)f.Cip, (cuuint64_t)f.Wp, (cuuint64_t)f.Hp, (cuuint64_t)g.Nb, 4};
+        const cuuint64_t dims[5] = {(cuuint64_t)f.Cip, (cuuint64_t)f.Wp, (cuuint64_t)f.Hp, (cuuint64_t)g.Nb, (cuuint64_t)g.nc};
         const cuuint64_t strides[4] = {(cuuint64_t)f.Cip * 4, (cuuint64_t)f.Wp * f.Cip * 4, (cuuint64_t)f.Hp * f.Wp * f.Cip * 4,
                                        (cuuint64_t)g.Nb * f.Hp * f.Wp * f.Cip * 4};
         const cuuint32_t box[5] = {(cuuint32_t)p.cbB, (cuuint32_t)((p.PW - 1) * g.SW + 1), (cuuint32_t)((p.PH - 1) * g.SH + 1), (cuuint32_t)p.PN,
@@ -685,7 +689,7 @@ static int conv_tf32_filter_launch(const Geom& g, const float* dy, const float* 
     PCB_CUDA_TRY(cudaFuncSetAttribute(qconv_filter_tf32_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
     qconv_filter_tf32_kernel<<<items * p.splits, T_THREADS, smem, stream>>>(m_dy_hi, m_dy_lo, m_x_hi, m_x_lo, p, acc, status);
     PCB_CUDA_TRY(cudaGetLastError());
-    unpack_filter_grad_f32_kernel<<<grid_cap((size_t)4 * g.Co * g.Ci * taps, 256, 16), 256, 0, stream>>>(acc, dw, taps, g.Co, g.Ci, g.dw_io);
+    unpack_filter_grad_f32_kernel<<<grid_cap((size_t)g.nc * g.Co * g.Ci * taps, 256, 16), 256, 0, stream>>>(acc, dw, taps, g.Co, g.Ci, g.dw_io, g.nc);
     PCB_CUDA_TRY(cudaGetLastError());
     return PCB_OK;
 }
@@ -704,7 +708,7 @@ int conv_tf32_launch(Pass pass, const Geom& g, const void* a, const void* b, con
     pack_activations_f32_kernel<<<grid_cap((size_t)pl.LK * g.Nb * pl.Hp * pl.Wp * (pl.Cp / 4), 256, 16), 256, 0, stream>>>(
         (const float*)b, x_hi, x_lo, pl.LK * g.Nb, pl.Cin, pl.Hin, pl.Win, pl.Hp, pl.Wp, pl.Cp, pl.pad_top, pl.pad_left, pl.ins_h, pl.ins_w);
     pack_filters_f32_kernel<<<grid_cap((size_t)taps * pl.Mp * pl.Kp, 256, 8), 256, 0, stream>>>(
-        (const float*)a, w_hi, w_lo, g.Co, g.Ci, taps, pl.Mp, pl.Kp, pl.Cp, pass == PASS_BWD_DATA ? 1 : 0, g.w_io);
+        (const float*)a, w_hi, w_lo, g.Co, g.Ci, taps, pl.Mp, pl.Kp, pl.Cp, pass == PASS_BWD_DATA ? 1 : 0, g.w_io, g.nc, g.ga, g.neg);
     PCB_CUDA_TRY(cudaGetLastError());
 
     TParams p;
@@ -719,7 +723,7 @@ int conv_tf32_launch(Pass pass, const Geom& g, const void* a, const void* b, con
                 if (best < 0 || vol < best || (vol == best && pw > p.PW)) { best = vol; p.PW = pw; p.PH = ph; p.PN = pn; }
             }
     }
-    p.Nb = g.Nb; p.Cout = pl.Cout; p.Mvalid = 4 * pl.Cout; p.HO = pl.Hout; p.WO = pl.Wout; p.Cp = pl.Cp;
+    p.Nb = g.Nb; p.Cout = pl.Cout; p.Mvalid = g.nc * pl.Cout; p.HO = pl.Hout; p.WO = pl.Wout; p.Cp = pl.Cp;
     p.KH = g.KH; p.KW = g.KW; p.SH = pl.SH; p.SW = pl.SW; p.DH = g.DH; p.DW = g.DW;
     p.tiles_w = (pl.Wout + p.PW - 1) / p.PW; p.tiles_h = (pl.Hout + p.PH - 1) / p.PH; p.tiles_n = (g.Nb + p.PN - 1) / p.PN;
     p.tiles_m = pl.Mp / TM;

@@ -407,7 +407,7 @@ int make_map(CUtensorMap* map, int fmt, const void* ptr, int rank, const cuuint6
 bool pointwise_tc_supported(Pass pass, int dtype, int variant, const Geom& g) {
     if (pass != PASS_FWD && pass != PASS_BWD_DATA) return false;
     if (dtype != PCB_F16 && dtype != PCB_BF16) return false;
-    if (variant != PCB_VARIANT_16_PRODUCT || g.real_in || g.w_io || g.dw_io) return false;
+    if (g.nc != 4 || variant != PCB_VARIANT_16_PRODUCT || g.real_in || g.w_io || g.dw_io) return false;   // quaternion-only kernels
     if (!(g.KH == 1 && g.KW == 1 && g.SH == 1 && g.SW == 1 && g.PT == 0 && g.PL == 0 && g.HO == g.H && g.WO == g.W)) return false;
     const int cout = pass == PASS_FWD ? g.Co : g.Ci;
     // TMA: every global stride a multiple of 16 bytes; the channel tile is 128 wide, so narrow layers
@@ -468,7 +468,7 @@ int pointwise_tc_launch(Pass pass, int dtype, const Geom& g, const void* w, cons
 
 bool pointwise_filter_tc_supported(int dtype, int variant, const Geom& g) {
     if (dtype != PCB_F16 && dtype != PCB_BF16) return false;
-    if (variant != PCB_VARIANT_16_PRODUCT || g.real_in || g.w_io || g.dw_io) return false;
+    if (g.nc != 4 || variant != PCB_VARIANT_16_PRODUCT || g.real_in || g.w_io || g.dw_io) return false;   // quaternion-only kernels
     if (!(g.KH == 1 && g.KW == 1 && g.SH == 1 && g.SW == 1 && g.PT == 0 && g.PL == 0 && g.HO == g.H && g.WO == g.W)) return false;
     return (g.Ci % 8 == 0) && (g.Co % 8 == 0) && ((g.H * g.W) % 8 == 0) && g.Co >= 96 && g.Ci >= 64;
 }

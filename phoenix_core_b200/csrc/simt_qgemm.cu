@@ -82,7 +82,7 @@ __device__ __forceinline__ int4 make_n_entry(const Geom& g, int n, int N) {
     }
 }
 
-// ck = number of quaternion components folded into the K index (4, or 1 when only one component runs
+// ck = number of components folded into the K index (all of the algebra's, or 1 when only one component runs
 // along K: real-valued inputs and the 8-product kernels).
 template <int PASS>
 __device__ __forceinline__ int4 make_k_entry(const Geom& g, int k, int kend, int ck) {
@@ -120,16 +120,16 @@ __device__ __forceinline__ float gather_a(const Geom& g, const T* __restrict__ a
     if (me.x < 0 || ke.x < 0) return 0.f;
     if (PASS == PASS_FWD) {
         const int d = me.x, l = ke.x;
-        const float v = DType<T>::load(a + (size_t)(l ^ d) * g.Co * g.Ci * g.KH * g.KW + me.y + ke.w);
-        return quat_negative(l, d) ? -v : v;
+        const float v = DType<T>::load(a + (size_t)alg_pair(g.ga, l, d) * g.Co * g.Ci * g.KH * g.KW + me.y + ke.w);
+        return alg_negative(g.neg, l, d) ? -v : v;
     } else if (PASS == PASS_BWD_DATA) {
         const int l = me.x, d = ke.x;
-        const float v = DType<T>::load(a + (size_t)(l ^ d) * g.Co * g.Ci * g.KH * g.KW + me.y + ke.w);
-        return quat_negative(l, d) ? -v : v;
+        const float v = DType<T>::load(a + (size_t)alg_pair(g.ga, l, d) * g.Co * g.Ci * g.KH * g.KW + me.y + ke.w);
+        return alg_negative(g.neg, l, d) ? -v : v;
     } else {
-        const int r = me.x, l = ke.x, d = l ^ r;
+        const int r = me.x, l = ke.x, d = alg_pair(g.ga, l, r);
         const float v = DType<T>::load(a + (size_t)(d * g.Nb) * g.Co * g.HO * g.WO + me.y + ke.y);
-        return quat_negative(l, d) ? -v : v;
+        return alg_negative(g.neg, l, d) ? -v : v;
     }
 }
 
@@ -268,13 +268,13 @@ int device_sm_count() {
 }
 
 void problem_dims(Pass pass, const Geom& g, int& M, int& N, int& K) {
-    const int T = g.KH * g.KW, P = g.HO * g.WO, LK = g.real_in ? 1 : 4;
-    if (pass == PASS_FWD)           { M = 4 * g.Co;  N = g.Nb * P;         K = T * LK * g.Ci; }
-    else if (pass == PASS_BWD_DATA) { M = 4 * g.Ci;  N = g.Nb * g.H * g.W; K = T * 4 * g.Co; }
-    else                            { M = 4 * g.Co;  N = g.Ci * T;         K = LK * g.Nb * P; }
+    const int T = g.KH * g.KW, P = g.HO * g.WO, LK = g.real_in ? 1 : g.nc;
+    if (pass == PASS_FWD)           { M = g.nc * g.Co;  N = g.Nb * P;         K = T * LK * g.Ci; }
+    else if (pass == PASS_BWD_DATA) { M = g.nc * g.Ci;  N = g.Nb * g.H * g.W; K = T * g.nc * g.Co; }
+    else                            { M = g.nc * g.Co;  N = g.Ci * T;         K = LK * g.Nb * P; }
 }
 
-size_t filter_numel(const Geom& g) { return (size_t)4 * g.Co * g.Ci * g.KH * g.KW; }
+size_t filter_numel(const Geom& g) { return (size_t)g.nc * g.Co * g.Ci * g.KH * g.KW; }
 
 template <int PASS, typename T, int BM, int BN, bool AK, bool BKF>
 int launch_one(const SimtParams& p, int splits, const void* a, const void* b, const void* bias, void* out, float* out32,
@@ -298,7 +298,7 @@ int launch_typed(Pass pass, const Geom& g, const void* a, const void* b, const v
     SimtParams p;
     p.g = g;
     problem_dims(pass, g, p.M, p.N, p.K);
-    p.ck = (pass == PASS_BWD_DATA || !g.real_in) ? 4 : 1;
+    p.ck = (pass == PASS_BWD_DATA || !g.real_in) ? g.nc : 1;
     p.k_per_split = p.K;
     p.atomic_out = 0;
     if (p.M == 0 || p.N == 0) return PCB_OK;

@@ -375,7 +375,7 @@ namespace {
 bool legacy_supported(int dtype, int variant, const Geom& g) {
     if (dtype != PCB_F16 && dtype != PCB_BF16) return false;
     if (variant != PCB_VARIANT_16_PRODUCT) return false;
-    if (g.real_in || g.w_io || g.dw_io) return false;
+    if (g.nc != 4 || g.real_in || g.w_io || g.dw_io) return false;     // quaternion-only kernel
     if (!pointwise(g)) return false;
     // 16-byte operand chunks must not straddle a component, an image or a channel row
     return (g.Ci % 8 == 0) && (g.Co % 8 == 0) && ((g.H * g.W) % 8 == 0);
@@ -394,9 +394,9 @@ size_t tensor_scratch_bytes(Pass pass, int dtype, int variant, int engine, const
     if (engine == PCB_ENGINE_SIMT || !tensor_path_supported(pass, dtype, variant, g)) return 0;
     if (dtype == PCB_F32) return conv_tf32_scratch_bytes(pass, g);
     if (pass == PASS_BWD_FILTER) {
-        if (pointwise_filter_tc_supported(dtype, variant, g)) return (size_t)4 * g.Co * g.Ci * g.KH * g.KW * sizeof(float);
+        if (pointwise_filter_tc_supported(dtype, variant, g)) return (size_t)g.nc * g.Co * g.Ci * g.KH * g.KW * sizeof(float);
         if (conv_filter_tc_supported(dtype, variant, g)) return conv_filter_tc_scratch_bytes(g);
-        return (size_t)4 * g.Co * g.Ci * g.KH * g.KW * sizeof(float);
+        return (size_t)g.nc * g.Co * g.Ci * g.KH * g.KW * sizeof(float);
     }
     if (pointwise_tc_supported(pass, dtype, variant, g)) return 0;
     if (conv_tc_supported(pass, dtype, variant, g)) return conv_tc_scratch_bytes(pass, g);

@@ -14,7 +14,7 @@ import torch
 
 from . import _lib
 from .context import Context
-from .descriptors import Algebra, DataFormat, FilterLayout
+from .descriptors import MULTIVECTOR_DIM, Algebra, DataFormat, FilterLayout
 
 _DTYPES = {torch.float32: _lib.PCB_F32, torch.float16: _lib.PCB_F16, torch.bfloat16: _lib.PCB_BF16}
 
@@ -68,23 +68,29 @@ def _stream():
     return ctypes.c_void_p(torch.cuda.current_stream().cuda_stream)
 
 
+# upstride::Algebra -> pcb_algebra (the C ABI keeps quaternion at zero)
+_ALGEBRAS = {Algebra.QUATERNION: 0, Algebra.REAL: 1, Algebra.COMPLEX: 2, Algebra.GA_300: 3}
+
+
 def _conv_desc(descriptor, dtype, context, engine, has_bias=False, require_input_grad=False):
-    if descriptor.getAlgebra() != Algebra.QUATERNION:
-        raise _lib.BackendError(_lib.PCB_ERR_UNSUPPORTED, "only the quaternion algebra is implemented")
+    algebra = descriptor.getAlgebra()
+    dim = MULTIVECTOR_DIM[algebra]
+    off = 0 if algebra == Algebra.REAL else 1       # real filters carry no leading component axis
     if descriptor.getDataFormat() != DataFormat.NCHW or descriptor.getFilterLayout() != FilterLayout.OIHW:
         raise _lib.BackendError(_lib.PCB_ERR_UNSUPPORTED, "only NCHW activations with OIHW filters are implemented")
     ishape, fshape = descriptor.getInputShape(), descriptor.getFilterShape()
-    real = descriptor.isRealValuedInput()
-    if not real and ishape[0] % 4 != 0:
-        raise ValueError("leading input dimension must be a multiple of 4 (components stacked on the batch axis)")
-    if ishape[1] != fshape[2] * descriptor.getGroups():
-        raise ValueError("input channels mismatch: %d vs %d" % (ishape[1], fshape[2]))
+    real = descriptor.isRealValuedInput() and algebra != Algebra.REAL
+    if not real and ishape[0] % dim != 0:
+        raise ValueError("leading input dimension must be a multiple of %d (components stacked on the batch axis)" % dim)
+    if ishape[1] != fshape[off + 1] * descriptor.getGroups():
+        raise ValueError("input channels mismatch: %d vs %d" % (ishape[1], fshape[off + 1]))
     d = _lib.ConvDesc()
     d.dtype = _DTYPES[dtype]
-    d.n = ishape[0] if real else ishape[0] // 4
-    d.ci, d.co = fshape[2], fshape[1]
+    d.algebra = _ALGEBRAS[algebra]
+    d.n = ishape[0] if real else ishape[0] // dim
+    d.ci, d.co = fshape[off + 1], fshape[off]
     d.h, d.w = ishape[2], ishape[3]
-    d.kh, d.kw = fshape[3], fshape[4]
+    d.kh, d.kw = fshape[off + 2], fshape[off + 3]
     d.stride_h, d.stride_w = descriptor.getStride()
     d.dilation_h, d.dilation_w = descriptor.getDilation()
     d.pad_top, d.pad_left = descriptor.getPaddingBefore()
@@ -150,16 +156,17 @@ def conv2DBwd(inputTensor, filterTensor, gradTensor, filterGradTensor, inputGrad
 
 
 def _dense_desc(descriptor, dtype, context, engine, has_bias=False, require_input_grad=False):
-    if descriptor.getAlgebra() != Algebra.QUATERNION:
-        raise _lib.BackendError(_lib.PCB_ERR_UNSUPPORTED, "only the quaternion algebra is implemented")
+    algebra = descriptor.getAlgebra()
+    dim = MULTIVECTOR_DIM[algebra]
     ishape = descriptor.getInputShape()
-    if ishape[0] % 4 != 0:
-        raise ValueError("leading input dimension must be a multiple of 4 (components stacked on the batch axis)")
+    if ishape[0] % dim != 0:
+        raise ValueError("leading input dimension must be a multiple of %d (components stacked on the batch axis)" % dim)
     if ishape[1] != descriptor.getInputChannels():
         raise ValueError("input features mismatch: %d vs %d" % (ishape[1], descriptor.getInputChannels()))
     d = _lib.DenseDesc()
     d.dtype = _DTYPES[dtype]
-    d.batch = ishape[0] // 4
+    d.algebra = _ALGEBRAS[algebra]
+    d.batch = ishape[0] // dim
     d.in_features = ishape[1]
     d.out_features = descriptor.getOutputChannels()
     d.filter_oi = int(descriptor.getFilterLayout() == FilterLayout.OI)

@@ -134,9 +134,25 @@ static void gpuTests() {
             CHECK(same(filterGrad, {1, -2, -3, -4}));      // d(y0)/dw = (x0, -x1, -x2, -x3)
             CHECK(same(inputGrad, {5, -6, -7, -8}));       // d(y0)/dx = (w0, -w1, -w2, -w3)
         }
-        {   // unsupported algebra: no scalar library, no CPU fallback
+        {   // complex convolution, the reference's known answer (tests/tests.cpp:224-290)
             AllocatedTensor<Device, float> input(device, {2, 3, 2, 2}), kernel(device, {2, 2, 3, 1, 1}), output(device, {2, 2, 2, 2});
+            input = {0, 0, 0, 0, -1, 0, 0, 0, 1, 2, 3, 4, 1, 1, 1, 1, 0, 0, 0, 0, -1, -2, -3, -4};
+            kernel = {1, 1, 1, 0, 0, 2, 0, 0, 0, -1, 0, 0};
             Conv2DFwdDescriptor descriptor(input.getShape(), kernel.getShape(), 1, 1, Padding::VALID, {}, 1, Algebra::COMPLEX, DataFormat::NCHW, FilterLayout::OIHW, false);
+            conv2DFwd<Device, float>(device, device, input, kernel, nullptr, output, descriptor);
+            CHECK(same(output, {0, 2, 3, 4, 3, 5, 7, 9, 0, -1, -2, -3, -2, -4, -6, -8}));
+        }
+        {   // GA(3,0,0) dense, the reference's known answer (tests/tests.cpp:604-648)
+            AllocatedTensor<Device, float> input(device, {8, 1}), filter(device, {8, 1, 2}), output(device, {8, 2});
+            input = {1, 0, 0, 0, 2, 4, 3, 0};
+            filter = {-1, 10, 0, 0, 0, 0, 0, 0, -2, 0, -4, 0, -3, 0, 0, 0};
+            DenseFwdDescriptor descriptor(input.getShape(), filter.getShape(), Algebra::GA_300, FilterLayout::IO, false);
+            denseFwd<Device, float>(device, device, input, filter, nullptr, output, descriptor);
+            CHECK(same(output, {28, 10, 0, 0, 0, 0, 0, 0, -4, 20, -8, 40, -6, 30, 0, 0}));
+        }
+        {   // unsupported layout: no CPU fallback
+            AllocatedTensor<Device, float> input(device, {4, 2, 2, 3}), kernel(device, {4, 2, 3, 1, 1}), output(device, {4, 2, 2, 2});
+            Conv2DFwdDescriptor descriptor(input.getShape(), kernel.getShape(), 1, 1, Padding::VALID, {}, 1, Algebra::QUATERNION, DataFormat::NHWC, FilterLayout::OIHW, false);
             CHECK_THROWS((conv2DFwd<Device, float>(device, device, input, kernel, nullptr, output, descriptor)), std::runtime_error);
         }
         {   // empty batch: forward is a no-op, backward zeroes the filter gradient

@@ -33,17 +33,19 @@ def host(t):
     return t.detach().to(torch.float32).cpu().numpy()
 
 
-def conv_descriptors(xshape, wshape, stride, pad, use_bias, need_dx, real_input=False):
+def conv_descriptors(xshape, wshape, stride, pad, use_bias, need_dx, real_input=False, algebra=pcb.Algebra.QUATERNION,
+                     dilation=(1, 1)):
     pt, pl, pb, pr = pad
-    args = (xshape, wshape, stride, (1, 1), pcb.Padding.EXPLICIT, (pt, pl, pb, pr), 1, pcb.Algebra.QUATERNION,
+    args = (xshape, wshape, stride, dilation, pcb.Padding.EXPLICIT, (pt, pl, pb, pr), 1, algebra,
             pcb.DataFormat.NCHW, pcb.FilterLayout.OIHW)
     fwd = pcb.Conv2DFwdDescriptor(*args, use_bias, real_input)
     bwd = pcb.Conv2DBwdDescriptor(*args, need_dx, real_input)
     return fwd, bwd
 
 
-def run_conv_fwd(x, w, bias, stride, pad, dtype, variant, engine, real_input=False):
-    fwd, _ = conv_descriptors(x.shape, w.shape, stride, pad, bias is not None, False, real_input)
+def run_conv_fwd(x, w, bias, stride, pad, dtype, variant, engine, real_input=False, algebra=pcb.Algebra.QUATERNION,
+                 dilation=(1, 1)):
+    fwd, _ = conv_descriptors(x.shape, w.shape, stride, pad, bias is not None, False, real_input, algebra, dilation)
     xd, wd = dev(x, dtype), dev(w, dtype)
     bd = None if bias is None else dev(bias, dtype)
     y = torch.full(fwd.getOutputShape(), float("nan"), dtype=TORCH_DTYPES[dtype], device="cuda")
@@ -51,8 +53,8 @@ def run_conv_fwd(x, w, bias, stride, pad, dtype, variant, engine, real_input=Fal
     return host(y)
 
 
-def run_conv_bwd(x, w, dy, stride, pad, dtype, variant, engine, need_dx=True):
-    _, bwd = conv_descriptors(x.shape, w.shape, stride, pad, False, need_dx)
+def run_conv_bwd(x, w, dy, stride, pad, dtype, variant, engine, need_dx=True, algebra=pcb.Algebra.QUATERNION, dilation=(1, 1)):
+    _, bwd = conv_descriptors(x.shape, w.shape, stride, pad, False, need_dx, False, algebra, dilation)
     xd, wd, gd = dev(x, dtype), dev(w, dtype), dev(dy, dtype)
     dw = torch.full(w.shape, float("nan"), dtype=TORCH_DTYPES[dtype], device="cuda")
     dx = torch.full(x.shape, float("nan"), dtype=TORCH_DTYPES[dtype], device="cuda") if need_dx else None
@@ -60,9 +62,9 @@ def run_conv_bwd(x, w, dy, stride, pad, dtype, variant, engine, need_dx=True):
     return host(dw), (host(dx) if need_dx else None)
 
 
-def run_dense_fwd(x, w, bias, oi, dtype, variant, engine):
+def run_dense_fwd(x, w, bias, oi, dtype, variant, engine, algebra=pcb.Algebra.QUATERNION):
     layout = pcb.FilterLayout.OI if oi else pcb.FilterLayout.IO
-    desc = pcb.DenseFwdDescriptor(x.shape, w.shape, pcb.Algebra.QUATERNION, layout, bias is not None)
+    desc = pcb.DenseFwdDescriptor(x.shape, w.shape, algebra, layout, bias is not None)
     xd, wd = dev(x, dtype), dev(w, dtype)
     bd = None if bias is None else dev(bias, dtype)
     y = torch.full(desc.getOutputShape(), float("nan"), dtype=TORCH_DTYPES[dtype], device="cuda")
@@ -70,12 +72,13 @@ def run_dense_fwd(x, w, bias, oi, dtype, variant, engine):
     return host(y)
 
 
-def run_dense_bwd(x, w, dy, oi, dtype, variant, engine, need_dx=True):
+def run_dense_bwd(x, w, dy, oi, dtype, variant, engine, need_dx=True, algebra=pcb.Algebra.QUATERNION):
     layout = pcb.FilterLayout.OI if oi else pcb.FilterLayout.IO
-    desc = pcb.DenseBwdDescriptor(x.shape, w.shape, pcb.Algebra.QUATERNION, layout, need_dx)
+    desc = pcb.DenseBwdDescriptor(x.shape, w.shape, algebra, layout, need_dx)
     xd, wd, gd = dev(x, dtype), dev(w, dtype), dev(dy, dtype)
     i, o = desc.getInputChannels(), desc.getOutputChannels()
-    dw = torch.full((4, i, o), float("nan"), dtype=TORCH_DTYPES[dtype], device="cuda")
+    dwshape = (i, o) if algebra == pcb.Algebra.REAL else (w.shape[0], i, o)
+    dw = torch.full(dwshape, float("nan"), dtype=TORCH_DTYPES[dtype], device="cuda")
     dx = torch.full(x.shape, float("nan"), dtype=TORCH_DTYPES[dtype], device="cuda") if need_dx else None
     pcb.denseBwd(xd, wd, gd, dw, dx, desc, context(variant), ENGINES[engine])
     return host(dw), (host(dx) if need_dx else None)

@@ -1,4 +1,7 @@
 """Shared helpers for the tests: seeded inputs, an independent float64 formulation, error norms."""
+import json
+import os
+
 import numpy as np
 import torch
 
@@ -10,6 +13,19 @@ QUAT_BLOCK = [
     [(2, -1), (3, +1), (0, +1), (1, -1)],
     [(3, -1), (2, -1), (1, +1), (0, +1)],
 ]
+
+
+def algebra_block(name):
+    """The D x D signed block of an algebra ("REAL", "COMPLEX", "QUATERNION", "GA_300") in the form of QUAT_BLOCK,
+    built from the reference's product table as transcribed in golden/reference_sign_tables.json."""
+    with open(os.path.join(os.path.dirname(__file__), "golden", "reference_sign_tables.json")) as f:
+        entries = json.load(f)[name]["entries"]
+    dims = int(round(len(entries) ** 0.5))
+    block = [[None] * dims for _ in range(dims)]
+    for idx, (l, r, s) in enumerate(entries):
+        block[l][idx // dims] = (r, s)
+    assert all(e is not None for row in block for e in row)
+    return block
 
 
 def rng(seed):
@@ -28,102 +44,107 @@ def integers(seed, shape, lo=-3, hi=4):
     return rng(seed).integers(lo, hi, size=shape).astype(np.float32)
 
 
-def block_weights_conv(w):
-    """[4, Co, Ci, kh, kw] -> real conv weights [4*Co, 4*Ci, kh, kw] (float64 torch tensor)."""
+def block_weights_conv(w, block=QUAT_BLOCK):
+    """[D, Co, Ci, kh, kw] -> real conv weights [D*Co, D*Ci, kh, kw] (float64 torch tensor)."""
+    D = len(block)
     w = torch.as_tensor(np.asarray(w), dtype=torch.float64)
     _, co, ci, kh, kw = w.shape
-    big = torch.zeros(4, co, 4, ci, kh, kw, dtype=torch.float64)
-    for l in range(4):
-        for d in range(4):
-            r, s = QUAT_BLOCK[l][d]
+    big = torch.zeros(D, co, D, ci, kh, kw, dtype=torch.float64)
+    for l in range(D):
+        for d in range(D):
+            r, s = block[l][d]
             big[d, :, l] = s * w[r]
-    return big.reshape(4 * co, 4 * ci, kh, kw)
+    return big.reshape(D * co, D * ci, kh, kw)
 
 
-def to_real_layout(x):
-    """[4*N, C, ...] (component-major on the batch axis) -> [N, 4*C, ...] float64 torch tensor."""
+def to_real_layout(x, D=4):
+    """[D*N, C, ...] (component-major on the batch axis) -> [N, D*C, ...] float64 torch tensor."""
     x = torch.as_tensor(np.asarray(x), dtype=torch.float64)
-    n = x.shape[0] // 4
-    x = x.reshape(4, n, *x.shape[1:])
+    n = x.shape[0] // D
+    x = x.reshape(D, n, *x.shape[1:])
     x = x.transpose(0, 1)
-    return x.reshape(n, 4 * x.shape[2], *x.shape[3:])
+    return x.reshape(n, D * x.shape[2], *x.shape[3:])
 
 
-def from_real_layout(y):
-    """[N, 4*C, ...] -> [4*N, C, ...] numpy float64."""
+def from_real_layout(y, D=4):
+    """[N, D*C, ...] -> [D*N, C, ...] numpy float64."""
     n = y.shape[0]
-    c = y.shape[1] // 4
-    y = y.reshape(n, 4, c, *y.shape[2:]).transpose(0, 1)
-    return y.reshape(4 * n, c, *y.shape[3:]).detach().numpy()
+    c = y.shape[1] // D
+    y = y.reshape(n, D, c, *y.shape[2:]).transpose(0, 1)
+    return y.reshape(D * n, c, *y.shape[3:]).detach().numpy()
 
 
-def conv_fwd_f64(x, w, bias, stride, pad):
-    """Independent float64 formulation: one real convolution with the 4x4 signed block (via torch, CPU)."""
-    xr = to_real_layout(x)
+def conv_fwd_f64(x, w, bias, stride, pad, block=QUAT_BLOCK, dilation=(1, 1)):
+    """Independent float64 formulation: one real convolution with the D x D signed block (via torch, CPU)."""
+    D = len(block)
+    xr = to_real_layout(x, D)
     pt, pl, pb, pr = pad
     xr = torch.nn.functional.pad(xr, (pl, pr, pt, pb))
     b = None if bias is None else torch.as_tensor(np.asarray(bias), dtype=torch.float64).reshape(-1)
-    y = torch.nn.functional.conv2d(xr, block_weights_conv(w), b, stride=stride)
-    return from_real_layout(y)
+    y = torch.nn.functional.conv2d(xr, block_weights_conv(w, block), b, stride=stride, dilation=dilation)
+    return from_real_layout(y, D)
 
 
-def conv_bwd_f64(x, w, dy, stride, pad):
+def conv_bwd_f64(x, w, dy, stride, pad, block=QUAT_BLOCK, dilation=(1, 1)):
     """dW, dX in float64 by automatic differentiation of the block-matrix formulation."""
+    D = len(block)
     xt = torch.as_tensor(np.asarray(x), dtype=torch.float64).requires_grad_(True)
     wt = torch.as_tensor(np.asarray(w), dtype=torch.float64).requires_grad_(True)
-    n = xt.shape[0] // 4
-    xr = xt.reshape(4, n, *xt.shape[1:]).transpose(0, 1).reshape(n, 4 * xt.shape[1], *xt.shape[2:])
+    n = xt.shape[0] // D
+    xr = xt.reshape(D, n, *xt.shape[1:]).transpose(0, 1).reshape(n, D * xt.shape[1], *xt.shape[2:])
     pt, pl, pb, pr = pad
     xr = torch.nn.functional.pad(xr, (pl, pr, pt, pb))
     _, co, ci, kh, kw = wt.shape
     rows = []
-    for d in range(4):
+    for d in range(D):
         cols = []
-        for l in range(4):
-            r, s = QUAT_BLOCK[l][d]
+        for l in range(D):
+            r, s = block[l][d]
             cols.append(s * wt[r])
         rows.append(torch.cat(cols, dim=1))
     big = torch.cat(rows, dim=0)
-    y = torch.nn.functional.conv2d(xr, big, None, stride=stride)
-    yq = y.reshape(n, 4, co, *y.shape[2:]).transpose(0, 1).reshape(4 * n, co, *y.shape[2:])
+    y = torch.nn.functional.conv2d(xr, big, None, stride=stride, dilation=dilation)
+    yq = y.reshape(n, D, co, *y.shape[2:]).transpose(0, 1).reshape(D * n, co, *y.shape[2:])
     yq.backward(torch.as_tensor(np.asarray(dy), dtype=torch.float64))
     return wt.grad.numpy(), xt.grad.numpy()
 
 
-def dense_fwd_f64(x, w, bias, oi=False):
+def dense_fwd_f64(x, w, bias, oi=False, block=QUAT_BLOCK):
+    D = len(block)
     x = np.asarray(x, np.float64)
     w = np.asarray(w, np.float64)
     if oi:
         w = np.swapaxes(w, 1, 2)
-    b = x.shape[0] // 4
-    xs = x.reshape(4, b, -1)
-    y = np.zeros((4, b, w.shape[2]))
-    for l in range(4):
-        for d in range(4):
-            r, s = QUAT_BLOCK[l][d]
+    b = x.shape[0] // D
+    xs = x.reshape(D, b, -1)
+    y = np.zeros((D, b, w.shape[2]))
+    for l in range(D):
+        for d in range(D):
+            r, s = block[l][d]
             y[d] += s * xs[l] @ w[r]
     if bias is not None:
         y += np.asarray(bias, np.float64)[:, None, :]
-    return y.reshape(4 * b, -1)
+    return y.reshape(D * b, -1)
 
 
-def dense_bwd_f64(x, w, dy, oi=False):
-    """Returns dW in [4, I, O] orientation and dX."""
+def dense_bwd_f64(x, w, dy, oi=False, block=QUAT_BLOCK):
+    """Returns dW in [D, I, O] orientation and dX."""
+    D = len(block)
     x = np.asarray(x, np.float64)
     w = np.asarray(w, np.float64)
     dy = np.asarray(dy, np.float64)
     if oi:
         w = np.swapaxes(w, 1, 2)
-    b = x.shape[0] // 4
-    xs, gs = x.reshape(4, b, -1), dy.reshape(4, b, -1)
+    b = x.shape[0] // D
+    xs, gs = x.reshape(D, b, -1), dy.reshape(D, b, -1)
     dw = np.zeros_like(w)
     dx = np.zeros_like(xs)
-    for l in range(4):
-        for d in range(4):
-            r, s = QUAT_BLOCK[l][d]
+    for l in range(D):
+        for d in range(D):
+            r, s = block[l][d]
             dw[r] += s * xs[l].T @ gs[d]
             dx[l] += s * gs[d] @ w[r].T
-    return dw, dx.reshape(4 * b, -1)
+    return dw, dx.reshape(D * b, -1)
 
 
 def rel_err(got, ref):

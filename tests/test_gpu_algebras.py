@@ -1,0 +1,156 @@
+"""GPU parity for the other algebras of the reference's Algebra enum (real, complex, GA(3,0,0)): the same kernels
+with a 1x1, 2x2 or 8x8 signed block (reference tables src/algebras.cc:5-145) against the CPU oracle, plus the
+reference's own known-answer vectors for them (tests/tests.cpp:224-290, :371-423, :562-648), plus dilation.
+
+Tolerances: 1e-5 (fp32), 2e-2 (fp16 / bf16), max|got-ref| / max|ref| per output tensor.
+"""
+import json
+import os
+
+import numpy as np
+import pytest
+import torch
+
+import phoenix_core_b200 as pcb
+from helpers import normal, rel_err, uniform
+
+pytestmark = pytest.mark.gpu
+
+GOLDEN = os.path.join(os.path.dirname(__file__), "golden", "reference_kats.json")
+# name -> (host-layer enum, oracle code, components)
+ALGEBRAS = {"real": (pcb.Algebra.REAL, 0, 1), "complex": (pcb.Algebra.COMPLEX, 1, 2),
+            "quaternion": (pcb.Algebra.QUATERNION, 2, 4), "ga_300": (pcb.Algebra.GA_300, 3, 8)}
+
+
+@pytest.fixture(scope="module")
+def gpu():
+    if not torch.cuda.is_available():
+        pytest.skip("no CUDA device")
+    import gpu_util
+    return gpu_util
+
+
+def _check(got, ref, dtype, gpu, what):
+    assert np.all(np.isfinite(got)), what + ": output not fully written"
+    err = rel_err(got, ref)
+    assert err <= gpu.TOL[dtype], "%s: relative error %.3e > %.1e" % (what, err, gpu.TOL[dtype])
+
+
+def _shapes(name, n, ci, co, h, w_, kh, kw):
+    """Tensor shapes in the reference's conventions: real tensors carry no component axis."""
+    D = ALGEBRAS[name][2]
+    if name == "real":
+        return (n, ci, h, w_), (co, ci, kh, kw), (co,)
+    return (D * n, ci, h, w_), (D, co, ci, kh, kw), (D, co)
+
+
+def _oracle_view(name, x, w, b=None):
+    """The oracle takes a leading component axis for every algebra."""
+    if name != "real":
+        return x, w, b
+    return x, w[None], (None if b is None else b[None])
+
+
+@pytest.mark.parametrize("engine", ["simt", "auto"])
+def test_reference_kats_other_algebras_on_gpu(gpu, engine):
+    """Complex and GA(3,0,0) known-answer vectors of the reference, exact (integer-valued data)."""
+    with open(GOLDEN) as f:
+        cases = [c for c in json.load(f)["cases"] if c.get("algebra") in ("complex", "ga_300")]
+    assert len(cases) == 4
+    for case in cases:
+        alg = ALGEBRAS[case["algebra"]][0]
+        x = np.asarray(case["x"], np.float32).reshape(case["x_shape"])
+        w = np.asarray(case["w"], np.float32).reshape(case["w_shape"])
+        want = np.asarray(case["y"], np.float32).reshape(case["y_shape"])
+        if case["op"] == "conv2d_fwd":
+            got = gpu.run_conv_fwd(x, w, None, tuple(case["stride"]), (0, 0, 0, 0), "f32", "16p", engine, False, alg)
+        else:
+            got = gpu.run_dense_fwd(x, w, None, False, "f32", "16p", engine, alg)
+        assert np.array_equal(got, want), (case["name"], engine)
+
+
+# n, ci, co, h, w, kh, kw, stride, pad(t,l,b,r)
+SHAPES = [
+    (2, 3, 5, 7, 6, 3, 3, (1, 1), (1, 1, 1, 1)),
+    (1, 4, 2, 9, 8, 3, 3, (2, 2), (0, 0, 1, 1)),
+    (2, 16, 32, 14, 14, 3, 3, (1, 1), (1, 1, 1, 1)),
+    (2, 40, 24, 6, 5, 1, 1, (1, 1), (0, 0, 0, 0)),
+    (3, 32, 16, 12, 12, 3, 3, (2, 2), (0, 0, 1, 1)),
+    (2, 64, 48, 8, 8, 1, 1, (1, 1), (0, 0, 0, 0)),
+]
+
+
+@pytest.mark.parametrize("name", ["real", "complex", "ga_300"])
+@pytest.mark.parametrize("shape", SHAPES)
+@pytest.mark.parametrize("dtype,engine", [("f32", "simt"), ("f32", "auto"), ("f16", "simt"), ("f16", "auto"), ("bf16", "auto")])
+def test_conv_other_algebras_vs_oracle(gpu, oracle, name, shape, dtype, engine):
+    n, ci, co, h, w_, kh, kw, stride, pad = shape
+    alg, code, D = ALGEBRAS[name]
+    xs, ws, bs = _shapes(name, n, ci, co, h, w_, kh, kw)
+    x = gpu.rounded(uniform(61, xs), dtype)
+    w = gpu.rounded(normal(62, ws, std=(2.0 / (D * ci * kh * kw)) ** 0.5), dtype)
+    b = gpu.rounded(uniform(63, bs), dtype)
+    ox, ow, ob = _oracle_view(name, x, w, b)
+    ref = oracle.conv2d_fwd(ox, ow, ob, stride, (1, 1), pad, code, 0)
+    got = gpu.run_conv_fwd(x, w, b, stride, pad, dtype, "8p", engine, False, alg)     # the variant is ignored off quaternions
+    _check(got, ref, dtype, gpu, "y")
+    dy = gpu.rounded(normal(64, ref.shape), dtype)
+    rdw, rdx = oracle.conv2d_bwd(ox, ow, dy, stride, (1, 1), pad, code, 0, True)
+    dw, dx = gpu.run_conv_bwd(x, w, dy, stride, pad, dtype, "16p", engine, True, alg)
+    _check(dx, rdx, dtype, gpu, "dx")
+    _check(dw.reshape(rdw.shape), rdw, dtype, gpu, "dw")
+
+
+@pytest.mark.parametrize("name", ["real", "complex", "ga_300"])
+@pytest.mark.parametrize("shape", [(3, 5, 7), (32, 64, 48), (17, 130, 70)])
+@pytest.mark.parametrize("dtype", ["f32", "f16"])
+@pytest.mark.parametrize("oi", [False, True])
+def test_dense_other_algebras_vs_oracle(gpu, oracle, name, shape, dtype, oi):
+    b_, i_, o_ = shape
+    alg, code, D = ALGEBRAS[name]
+    real = name == "real"
+    x = gpu.rounded(uniform(71, (D * b_, i_)), dtype)
+    wshape = (o_, i_) if oi else (i_, o_)
+    w = gpu.rounded(normal(72, wshape if real else (D,) + wshape, std=(2.0 / (D * i_)) ** 0.5), dtype)
+    bias = gpu.rounded(uniform(73, (o_,) if real else (D, o_)), dtype)
+    ow, ob = (w[None], bias[None]) if real else (w, bias)
+    ref = oracle.dense_fwd(x, ow, ob, oi, code, 0)
+    got = gpu.run_dense_fwd(x, w, bias, oi, dtype, "16p", "auto", alg)
+    _check(got, ref, dtype, gpu, "y")
+    dy = gpu.rounded(normal(74, ref.shape), dtype)
+    rdw, rdx = oracle.dense_bwd(x, ow, dy, oi, code, 0, True)
+    dw, dx = gpu.run_dense_bwd(x, w, dy, oi, dtype, "16p", "auto", True, alg)
+    _check(dx, rdx, dtype, gpu, "dx")
+    _check(dw.reshape(rdw.shape), rdw, dtype, gpu, "dw")
+
+
+@pytest.mark.parametrize("name", ["complex", "quaternion", "ga_300"])
+@pytest.mark.parametrize("dtype,engine", [("f32", "simt"), ("f32", "auto"), ("f16", "auto")])
+def test_dilated_conv_vs_oracle(gpu, oracle, name, dtype, engine):
+    """Dilation 2 (the reference passes it to its scalar convolutions, src/backend/onednn/conv2d.hpp:121)."""
+    alg, code, D = ALGEBRAS[name]
+    n, ci, co, h, w_, k = 2, 16, 16, 13, 12, 3
+    stride, dil, pad = (1, 1), (2, 2), (2, 2, 2, 2)
+    x = gpu.rounded(uniform(81, (D * n, ci, h, w_)), dtype)
+    w = gpu.rounded(normal(82, (D, co, ci, k, k), std=(2.0 / (D * ci * k * k)) ** 0.5), dtype)
+    ref = oracle.conv2d_fwd(x, w, None, stride, dil, pad, code, 0)
+    got = gpu.run_conv_fwd(x, w, None, stride, pad, dtype, "16p", engine, False, alg, dil)
+    _check(got, ref, dtype, gpu, "y")
+    dy = gpu.rounded(normal(84, ref.shape), dtype)
+    rdw, rdx = oracle.conv2d_bwd(x, w, dy, stride, dil, pad, code, 0, True)
+    dw, dx = gpu.run_conv_bwd(x, w, dy, stride, pad, dtype, "16p", engine, True, alg, dil)
+    _check(dx, rdx, dtype, gpu, "dx")
+    _check(dw, rdw, dtype, gpu, "dw")
+
+
+def test_engines_for_other_algebras(gpu):
+    """fp32 and 16-bit layers of every algebra reach the tensor-core kernels when the geometry allows."""
+    import ctypes
+    from phoenix_core_b200 import _lib
+    L = _lib.lib()
+    for algebra in (0, 1, 2, 3):
+        for dtype in (0, 1):
+            d = _lib.ConvDesc(dtype=dtype, n=4, ci=32, co=32, h=14, w=14, kh=3, kw=3, stride_h=1, stride_w=1, dilation_h=1,
+                              dilation_w=1, pad_top=1, pad_left=1, pad_bottom=1, pad_right=1, groups=1, algebra=algebra)
+            for p in (0, 1, 2):
+                assert L.pcb_qconv2d_engine_for(ctypes.byref(d), p) == _lib.ENGINE_TENSOR, (algebra, dtype, p)
