@@ -15,12 +15,15 @@
 // (cp.async.bulk.tensor, 128B / 64B swizzle) straight into the tcgen05 canonical layouts.
 //
 // CTA (persistent, one per SM): warp 0 = TMA producer, warp 1 = TMEM owner + MMA issuer, warps 2-9 =
-// epilogue (two warps per TMEM lane quadrant, one per 64-pixel half; accumulators are drained component by
-// component into packed registers and released one at a time, so the next tile's MMAs overlap the drain; the
-// global stores come last). Tile = 128 channels x 128
-// pixels x 4 components (all 512 TMEM columns); K slice per stage = 32 channels per component
-// (A 32 KB + B 32 KB), 3 stages. Every mbarrier wait is bounded; an expired wait sets the status word and
-// the CTA leaves through the common teardown.
+// epilogue (two warps per TMEM lane quadrant, one per 64-pixel half). Tile = 128 channels x 128 pixels x 4
+// components (all 512 TMEM columns); K slice per stage = 32 channels per component (A 32 KB + B 32 KB), 3
+// stages, or the weight slices resident (forward, <= 128 reduced channels) beside 2 activation stages.
+// The accumulators are drained component by component into packed registers and released one at a time, so the
+// next tile's first MMAs overlap the drain; the tile then leaves through a 32 KB shared-memory staging buffer and
+// TMA stores (measured: ordinary global stores from the epilogue warps, 32 scattered segments per instruction,
+// delayed the MMA warp's own instruction issue by ~4000 cycles per tile; the bulk stores do not).
+// Every mbarrier wait is bounded; an expired wait sets the status word and the CTA leaves through the common
+// teardown.
 #include "tc_common.cuh"
 #include "tensor_path.cuh"
 
@@ -40,7 +43,12 @@ constexpr uint32_t B_BOX_BYTES = 4 * KS * 64 * 2;  // 16 KB
 constexpr uint32_t STAGE_BYTES = A_BYTES + B_BYTES;
 constexpr int U_THREADS = 320;
 constexpr int MAX_RESIDENT_K = 4;                  // weight K slices that may stay in shared memory (4 x 32 KB)
-constexpr size_t U_SMEM_BYTES = 1024 + (MAX_RESIDENT_K * A_BYTES + U_STAGES * B_BYTES) + 256;   // >= U_STAGES * STAGE_BYTES
+constexpr int RB_STAGES = 2;                       // activation stages beside resident weights
+constexpr uint32_t OPERAND_BYTES = U_STAGES * STAGE_BYTES;       // 192 KB, also MAX_RESIDENT_K * A_BYTES + RB_STAGES * B_BYTES
+constexpr uint32_t OUT_HALF_BYTES = 64 * CT * 2;   // 16 KB: one component of a 64-pixel block, [128 channels][64 pixels]
+constexpr uint32_t OUT_BYTES = 2 * OUT_HALF_BYTES; // output staging for the TMA store: one component of a tile
+static_assert(MAX_RESIDENT_K * A_BYTES + RB_STAGES * B_BYTES <= OPERAND_BYTES, "resident plan must fit the operand region");
+constexpr size_t U_SMEM_BYTES = 1024 + OPERAND_BYTES + OUT_BYTES + 256;
 constexpr int ST_U_PRODUCER = 0x10, ST_U_MMA = 0x20, ST_U_EPILOGUE = 0x40;
 
 struct UParams {
@@ -62,16 +70,18 @@ __device__ __forceinline__ uint64_t make_desc_kmajor_sw64(uint32_t smem_addr) {
 
 template <bool BWD>
 __global__ void __launch_bounds__(U_THREADS, 1)
-qconv_pointwise_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant__ CUtensorMap map_act, UParams p,
-                          const uint16_t* __restrict__ bias, uint16_t* __restrict__ out, int* __restrict__ status) {
+qconv_pointwise_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant__ CUtensorMap map_act,
+                          const __grid_constant__ CUtensorMap map_out, UParams p, const uint16_t* __restrict__ bias, int* __restrict__ status) {
     extern __shared__ uint8_t smem_raw[];
     const int t = threadIdx.x, warp = t >> 5, lane = t & 31;
     uint8_t* base = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
-    uint64_t* bars = reinterpret_cast<uint64_t*>(base + MAX_RESIDENT_K * A_BYTES + U_STAGES * B_BYTES);
-    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 2 * U_STAGES + 6);
+    uint64_t* bars = reinterpret_cast<uint64_t*>(base + OPERAND_BYTES + OUT_BYTES);
+    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 2 * U_STAGES + 7);
     const uint32_t tiles_addr = smem_u32(base);
     const uint32_t full_bar = smem_u32(bars), empty_bar = smem_u32(bars + U_STAGES);
     const uint32_t a_full = smem_u32(bars + 2 * U_STAGES + 5);
+    const uint32_t epi_bar = smem_u32(bars + 2 * U_STAGES + 6);   // the eight epilogue warps among themselves
+    const uint32_t out_addr = tiles_addr + OPERAND_BYTES;         // staging for the TMA store
     // one "accumulator drained" barrier per component, so the next tile's MMAs can start on component 0 while
     // the epilogue is still reading components 1..3
     const uint32_t tmem_full = smem_u32(bars + 2 * U_STAGES), tmem_empty = smem_u32(bars + 2 * U_STAGES + 1);
@@ -80,6 +90,7 @@ qconv_pointwise_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __gri
     const int n_k = (p.Cred + KS - 1) / KS;
     // shared-memory plan: either a ring of [A|B] stages, or all weight slices resident followed by a ring of B stages
     const bool resident = !BWD && p.a_resident;
+    const int n_stages = resident ? RB_STAGES : U_STAGES;
     auto a_slot = [&](int k, int s) { return resident ? tiles_addr + k * A_BYTES : tiles_addr + s * STAGE_BYTES; };
     auto b_slot = [&](int s) { return resident ? tiles_addr + n_k * A_BYTES + s * B_BYTES : tiles_addr + s * STAGE_BYTES + A_BYTES; };
 
@@ -87,6 +98,7 @@ qconv_pointwise_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __gri
         for (int s = 0; s < U_STAGES; ++s) { mbar_init(full_bar + 8 * s, 1); mbar_init(empty_bar + 8 * s, 1); }
         mbar_init(tmem_full, 1);
         mbar_init(a_full, 1);
+        mbar_init(epi_bar, 8);
         for (int o = 0; o < 4; ++o) mbar_init(tmem_empty + 8 * o, 8);
         fence_barrier_init();
     }
@@ -117,8 +129,8 @@ qconv_pointwise_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __gri
                     pix[b] = (blk - img[b] * p.blocks_per_image) * 64;
                 }
                 for (int k = 0; k < n_k && ok; ++k, ++it) {
-                    const int s = it % U_STAGES;
-                    ok = mbar_wait_bounded(empty_bar + 8 * s, ((it / U_STAGES) & 1) ^ 1, status, ST_U_PRODUCER);
+                    const int s = it % n_stages;
+                    ok = mbar_wait_bounded(empty_bar + 8 * s, ((it / n_stages) & 1) ^ 1, status, ST_U_PRODUCER);
                     if (!ok) break;
                     const uint32_t a_dst = a_slot(k, s), b_dst = b_slot(s);
                     const uint32_t bar = full_bar + 8 * s;
@@ -150,17 +162,20 @@ qconv_pointwise_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __gri
         if (resident && blockIdx.x < n_tiles) ok = mbar_wait_bounded(a_full, 0, status, ST_U_MMA);
         for (int tile = blockIdx.x; tile < n_tiles && ok; tile += gridDim.x, ++local_tile) {
             for (int k = 0; k < n_k && ok; ++k, ++it) {
-                const int s = it % U_STAGES;
-                ok = mbar_wait_bounded(full_bar + 8 * s, (it / U_STAGES) & 1, status, ST_U_MMA);
+                const int s = it % n_stages;
+                ok = mbar_wait_bounded(full_bar + 8 * s, (it / n_stages) & 1, status, ST_U_MMA);
                 if (!ok) break;
                 tc_fence_after_sync();
                 const uint32_t a_addr = a_slot(k, s), b_addr = b_slot(s);
                 if (k == 0) {
-                    // first K slice of a tile: accumulator by accumulator, each as soon as the epilogue of the
-                    // previous tile has drained it (i = streamed component, o = accumulator component)
-                    for (int o = 0; o < 4 && ok; ++o) {
+                    // first K slice of a tile: the accumulators in two pairs, each pair as soon as the epilogue of the
+                    // previous tile has drained it. Inside a pair the MMAs alternate between the two accumulators:
+                    // back-to-back MMAs into one accumulator run at two thirds of the rate of independent ones.
+                    // (i = streamed component, o = accumulator component)
+                    for (int pair = 0; pair < 2 && ok; ++pair) {
                         if (local_tile > 0) {
-                            ok = mbar_wait_bounded(tmem_empty + 8 * o, (local_tile - 1) & 1, status, ST_U_MMA);
+                            ok = mbar_wait_bounded(tmem_empty + 8 * (2 * pair), (local_tile - 1) & 1, status, ST_U_MMA) &&
+                                 mbar_wait_bounded(tmem_empty + 8 * (2 * pair + 1), (local_tile - 1) & 1, status, ST_U_MMA);
                             if (!ok) break;
                             tc_fence_after_sync();
                         }
@@ -168,7 +183,9 @@ qconv_pointwise_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __gri
 #pragma unroll
                             for (int j = 0; j < KS / 16; ++j)
 #pragma unroll
-                                for (int i = 0; i < 4; ++i) issue(a_addr, b_addr, j, i, o, (j > 0 || i > 0) ? 1u : 0u);
+                                for (int i = 0; i < 4; ++i)
+#pragma unroll
+                                    for (int oo = 0; oo < 2; ++oo) issue(a_addr, b_addr, j, i, 2 * pair + oo, (j > 0 || i > 0) ? 1u : 0u);
                         }
                         __syncwarp();
                     }
@@ -190,20 +207,38 @@ qconv_pointwise_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __gri
         }
     } else {
         // ---------------------------------------------------------------- epilogue (warps 2..9)
+        // Ordinary global stores from here cost more than their bandwidth: every lane owns another channel row, so
+        // a warp store scatters 32 segments, and while those queue up the MMA warp's own instructions wait behind
+        // them. The tile therefore leaves through shared memory and TMA stores: each thread writes its row of one
+        // component into a 128-byte-swizzled [128 channels][64 pixels] box (conflict-free 16-byte stores), one
+        // thread issues the bulk stores, and out-of-range rows / pixels are clipped by the tensor map.
         const int q = warp & 3;                   // TMEM lane quadrant this warp may read
         const int chalf = (warp - 2) >> 2;        // which 64-pixel block of the tile (64 accumulator columns)
-        int local_tile = 0;
+        const bool issuer = warp == 2 && lane == 0;
+        const int row = q * 32 + lane;
+        const uint32_t my_out = out_addr + chalf * OUT_HALF_BYTES + row * 128;
+        int local_tile = 0, epi_phase = 0;
         bool ok = true;
+        // all eight warps meet; bounded like every other wait of the kernel
+        auto epi_sync = [&]() {
+            __syncwarp();
+            if (lane == 0) mbar_arrive(epi_bar);
+            const bool done = mbar_wait_bounded(epi_bar, epi_phase & 1, status, ST_U_EPILOGUE);
+            ++epi_phase;
+            return __all_sync(0xffffffffu, done);
+        };
         for (int tile = blockIdx.x; tile < n_tiles && ok; tile += gridDim.x, ++local_tile) {
             const int px_tile = tile / p.n_c_tiles, c_tile = tile - px_tile * p.n_c_tiles;
-            const int c = c_tile * CT + q * 32 + lane;
+            const int c = c_tile * CT + row;
             ok = mbar_wait_bounded(tmem_full, local_tile & 1, status, ST_U_EPILOGUE);
             ok = __all_sync(0xffffffffu, ok && (*reinterpret_cast<volatile int*>(status) == 0));
             if (!ok) break;
             tc_fence_after_sync();
-            // All eight warps drain component 0 (a 64-column half each) and release it, then 1, 2, 3: the MMA warp
-            // starts the next tile on component 0 while 1..3 are still being read. Values wait in packed registers.
-            uint32_t packed[4][2][16];
+            // Drain: all eight warps read component 0 (a 64-column half each) and release it, then 1, 2, 3, so the MMA
+            // warp starts the next tile on component 0 while the others are still being read. The values wait as
+            // packed 16-bit pairs in registers; nothing slow sits between two releases.
+            uint32_t packed[4][32];
+            const uint32_t lane_addr = tmem_base + ((uint32_t)(q * 32) << 16) + chalf * 64;
 #pragma unroll
             for (int o = 0; o < 4; ++o) {
                 float badd = 0.f;
@@ -211,47 +246,47 @@ qconv_pointwise_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __gri
                     const uint16_t raw = bias[o * p.Cout + c];
                     badd = p.fmt == 0 ? __half2float(__ushort_as_half(raw)) : __bfloat162float(__ushort_as_bfloat16(raw));
                 }
-#pragma unroll
-                for (int cb = 0; cb < 2; ++cb) {
-                    uint32_t v[32];
-                    tmem_ld_32x32b_x32(tmem_base + ((uint32_t)(q * 32) << 16) + o * PT + chalf * 64 + cb * 32, v);
-                    tmem_ld_wait();
-#pragma unroll
-                    for (int e = 0; e < 16; ++e) {
-                        const float f0 = __uint_as_float(v[2 * e]) + badd, f1 = __uint_as_float(v[2 * e + 1]) + badd;
-                        if (p.fmt == 0) { const __half2 h = __floats2half2_rn(f0, f1); packed[o][cb][e] = *reinterpret_cast<const uint32_t*>(&h); }
-                        else { const __nv_bfloat162 h = __floats2bfloat162_rn(f0, f1); packed[o][cb][e] = *reinterpret_cast<const uint32_t*>(&h); }
-                    }
-                }
+                uint32_t v[64];
+                tmem_ld_32x32b_x64(lane_addr + o * PT, v);
+                tmem_ld_wait();
+                tmem_regs_ready(v);
                 tc_fence_before_sync();
                 __syncwarp();
                 if (lane == 0) mbar_arrive(tmem_empty + 8 * o);
+#pragma unroll
+                for (int e = 0; e < 32; ++e) {
+                    const float f0 = __uint_as_float(v[2 * e]) + badd, f1 = __uint_as_float(v[2 * e + 1]) + badd;
+                    if (p.fmt == 0) { const __half2 h = __floats2half2_rn(f0, f1); packed[o][e] = *reinterpret_cast<const uint32_t*>(&h); }
+                    else { const __nv_bfloat162 h = __floats2bfloat162_rn(f0, f1); packed[o][e] = *reinterpret_cast<const uint32_t*>(&h); }
+                }
             }
-            const int blk = 2 * px_tile + chalf;
-            const int img = blk / p.blocks_per_image;
-            if (c < p.Cout && img < p.Nb) {
-                const int pxb = (blk - img * p.blocks_per_image) * 64;
-                const bool wide = (p.HW & 15) == 0 && (reinterpret_cast<uintptr_t>(out) & 31) == 0;   // rows start on 32-byte boundaries
+            int img[2], pix[2];
 #pragma unroll
-                for (int o = 0; o < 4; ++o) {
-                    uint16_t* dst = out + ((size_t)(o * p.Nb + img) * p.Cout + c) * p.HW + pxb;
+            for (int b = 0; b < 2; ++b) {
+                const int blk = 2 * px_tile + b;
+                img[b] = blk / p.blocks_per_image;
+                pix[b] = (blk - img[b] * p.blocks_per_image) * 64;
+            }
 #pragma unroll
-                    for (int cb = 0; cb < 2; ++cb) {
-                        if (wide) {
+            for (int o = 0; o < 4 && ok; ++o) {
+                if (issuer) bulk_wait_read_all();          // the previous component has left the staging buffer
+                ok = epi_sync();
+                if (!ok) break;
 #pragma unroll
-                            for (int g16 = 0; g16 < 2; ++g16)
-                                if (pxb + cb * 32 + g16 * 16 < p.HW) st_global_v8(dst + cb * 32 + g16 * 16, &packed[o][cb][8 * g16]);
-                        } else {
+                for (int ch = 0; ch < 8; ++ch)              // 16-byte chunk ch of this row sits at position ch ^ (row % 8)
+                    st_shared_v4(my_out + ((ch ^ (row & 7)) << 4), packed[o][4 * ch], packed[o][4 * ch + 1], packed[o][4 * ch + 2], packed[o][4 * ch + 3]);
+                fence_proxy_async_smem();
+                ok = epi_sync();
+                if (!ok) break;
+                if (issuer) {
 #pragma unroll
-                            for (int g8 = 0; g8 < 4; ++g8)
-                                if (pxb + cb * 32 + g8 * 8 < p.HW)
-                                    *reinterpret_cast<uint4*>(dst + cb * 32 + g8 * 8) = make_uint4(packed[o][cb][4 * g8], packed[o][cb][4 * g8 + 1],
-                                                                                                  packed[o][cb][4 * g8 + 2], packed[o][cb][4 * g8 + 3]);
-                        }
-                    }
+                    for (int b = 0; b < 2; ++b)
+                        if (img[b] < p.Nb) tma_store_4d(&map_out, out_addr + b * OUT_HALF_BYTES, pix[b], c_tile * CT, img[b], o);
+                    bulk_commit_group();
                 }
             }
         }
+        if (issuer) bulk_wait_read_all();                   // shared memory must outlive the last bulk store's reads
     }
 
     tc_fence_before_sync();
@@ -429,7 +464,7 @@ int pointwise_tc_launch(Pass pass, int dtype, const Geom& g, const void* w, cons
     p.n_px_tiles = (blocks + 1) / 2;
     p.n_c_tiles = (p.Cout + CT - 1) / CT;
 
-    alignas(64) CUtensorMap map_w, map_act;
+    alignas(64) CUtensorMap map_w, map_act, map_out;
     {   // filters [4][Co][Ci]: (ci, co, r)
         const cuuint64_t dims[3] = {(cuuint64_t)g.Ci, (cuuint64_t)g.Co, 4};
         const cuuint64_t strides[2] = {(cuuint64_t)g.Ci * 2, (cuuint64_t)g.Co * g.Ci * 2};
@@ -446,6 +481,13 @@ int pointwise_tc_launch(Pass pass, int dtype, const Geom& g, const void* w, cons
         const int rc = make_map(&map_act, fmt, act, 4, dims, strides, box, CU_TENSOR_MAP_SWIZZLE_128B);
         if (rc != PCB_OK) return rc;
     }
+    {   // output [4][Nb][Cout][HW]: (px, channel, image, component); the epilogue stores [128 channels][64 pixels] boxes
+        const cuuint64_t dims[4] = {(cuuint64_t)HW, (cuuint64_t)p.Cout, (cuuint64_t)g.Nb, 4};
+        const cuuint64_t strides[3] = {(cuuint64_t)HW * 2, (cuuint64_t)p.Cout * HW * 2, (cuuint64_t)g.Nb * p.Cout * HW * 2};
+        const cuuint32_t box[4] = {64, CT, 1, 1};
+        const int rc = make_map(&map_out, fmt, out, 4, dims, strides, box, CU_TENSOR_MAP_SWIZZLE_128B);
+        if (rc != PCB_OK) return rc;
+    }
     const int n_tiles = p.n_px_tiles * p.n_c_tiles;
     int grid = n_tiles < sm_count() ? n_tiles : sm_count();
     // forward with at most 128 reduced channels: keep the CTA's weight slices in shared memory for all its tiles
@@ -457,10 +499,10 @@ int pointwise_tc_launch(Pass pass, int dtype, const Geom& g, const void* w, cons
     }
     if (!bwd) {
         PCB_CUDA_TRY(cudaFuncSetAttribute(qconv_pointwise_tc_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)U_SMEM_BYTES));
-        qconv_pointwise_tc_kernel<false><<<grid, U_THREADS, U_SMEM_BYTES, stream>>>(map_w, map_act, p, (const uint16_t*)bias, (uint16_t*)out, status);
+        qconv_pointwise_tc_kernel<false><<<grid, U_THREADS, U_SMEM_BYTES, stream>>>(map_w, map_act, map_out, p, (const uint16_t*)bias, status);
     } else {
         PCB_CUDA_TRY(cudaFuncSetAttribute(qconv_pointwise_tc_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)U_SMEM_BYTES));
-        qconv_pointwise_tc_kernel<true><<<grid, U_THREADS, U_SMEM_BYTES, stream>>>(map_w, map_act, p, (const uint16_t*)bias, (uint16_t*)out, status);
+        qconv_pointwise_tc_kernel<true><<<grid, U_THREADS, U_SMEM_BYTES, stream>>>(map_w, map_act, map_out, p, (const uint16_t*)bias, status);
     }
     PCB_CUDA_TRY(cudaGetLastError());
     return PCB_OK;
