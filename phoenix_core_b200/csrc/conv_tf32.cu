@@ -657,7 +657,7 @@ static int conv_tf32_filter_launch(const Geom& g, const float* dy, const float* 
     p.merged_b = (f.Cip == p.cbB) ? 1 : 0;
     const int steps_total = p.tiles_w * p.tiles_h * p.tiles_n;
     const int items = taps * p.m_tiles * p.n_tiles;
-    int splits = (2 * sm_count() + items - 1) / items;
+    int splits = split_count(items, sm_count());
     if (splits > steps_total) splits = steps_total;
     if (splits < 1) splits = 1;
     p.steps_per_split = (steps_total + splits - 1) / splits;

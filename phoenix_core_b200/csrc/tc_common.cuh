@@ -87,6 +87,19 @@ inline int sm_count() {
 }
 
 inline int round_up(int v, int m) { return (v + m - 1) / m * m; }
+// Number of slices to cut each of `items` work items into when every CTA occupies a whole SM: the CTAs must fill
+// one, two or three rounds of the machine as exactly as possible (one CTA more than a round costs a whole round).
+inline int split_count(int items, int sms) {
+    int best = 1;
+    double best_util = 0.0;
+    for (int waves = 1; waves <= 3; ++waves) {
+        const int splits = waves * sms / items;
+        if (splits < 1) continue;
+        const double util = (double)items * splits / ((double)waves * sms);
+        if (util > best_util + 0.01) { best_util = util; best = splits; }
+    }
+    return best;
+}
 inline int grid_cap(size_t work_items, int per_block, int blocks_per_sm) {
     const size_t want = (work_items + per_block - 1) / per_block, cap = (size_t)sm_count() * blocks_per_sm;
     return (int)(want < cap ? (want > 0 ? want : 1) : cap);
