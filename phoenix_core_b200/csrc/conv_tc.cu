@@ -52,18 +52,7 @@ __device__ __forceinline__ uint64_t make_desc_kmajor_rows(uint32_t smem_addr) {
     return (uint64_t)((smem_addr & 0x3FFFFu) >> 4) | ((uint64_t)1 << 16) | ((uint64_t)((8 * KS * 2) >> 4) << 32) | DESC_VERSION_SM100 | layout;
 }
 
-// K-major operand tile in the layout without swizzle, used by the "planar" staging of 16-channel layers: the tile
-// is two planes of 8 channels, each plane rows of 16 bytes (8 rows = one 128-byte core matrix), planes
-// `plane_bytes` apart (leading offset), 8-row groups 128 bytes apart (stride offset).
-__device__ __forceinline__ uint64_t make_desc_kmajor_planar(uint32_t smem_addr, uint32_t plane_bytes) {
-    return (uint64_t)((smem_addr & 0x3FFFFu) >> 4) | ((uint64_t)((plane_bytes >> 4) & 0x3FFFu) << 16) | ((uint64_t)(128 >> 4) << 32) | DESC_VERSION_SM100;
-}
-
-// PLANAR (KS == 16 only): both operands come from staged copies that keep 8 channels per pixel (or per filter row)
-// contiguous and the two 8-channel halves in separate planes, so that a TMA box row is PW pixels x 16 bytes (or 32
-// filter rows x 16 bytes) instead of one pixel's 32 bytes. Measured: TMA delivers 32-byte rows at about one row per
-// 5.7 cycles per SM, which bounded every 16-channel layer.
-template <int KS, bool PLANAR>
+template <int KS>
 __global__ void __launch_bounds__(G_THREADS, 1)
 qconv_general_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant__ CUtensorMap map_x, GParams p,
                         const uint16_t* __restrict__ bias, uint16_t* __restrict__ out, int* __restrict__ status) {
@@ -116,13 +105,8 @@ qconv_general_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_
                             if (!ok) break;
                             const uint32_t a_dst = tiles_addr + s * STAGE, bar = full_bar + 8 * s;
                             mbar_arrive_expect_tx(bar, STAGE);
-                            if (PLANAR) {
-                                tma_load_4d(a_dst, &map_w, 0, m0 / 32, 2 * l, tap, bar);             // [2 planes][128 rows][8]
-                                tma_load_5d(a_dst + A_BYTES, &map_x, wp0 * 8, hp0, 0, n0, l, bar);   // [2 planes][PH][PW][8]
-                            } else {
-                                tma_load_3d(a_dst, &map_w, l * p.Cp + cs * KS, m0, tap, bar);
-                                tma_load_5d(a_dst + A_BYTES, &map_x, cs * KS, wp0, hp0, n0, l, bar);
-                            }
+                            tma_load_3d(a_dst, &map_w, l * p.Cp + cs * KS, m0, tap, bar);
+                            tma_load_5d(a_dst + A_BYTES, &map_x, cs * KS, wp0, hp0, n0, l, bar);
                         }
                     }
                 }
@@ -148,15 +132,10 @@ qconv_general_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_
                 tc_fence_after_sync();
                 if (lane == 0) {
                     const uint32_t a_addr = tiles_addr + s * STAGE, b_addr = a_addr + A_BYTES;
-                    if (PLANAR) {
-                        mma_f16_ss(tmem_base + buf * GN, make_desc_kmajor_planar(a_addr, GM * 16), make_desc_kmajor_planar(b_addr, GN * 16),
-                                   idesc, k > 0 ? 1u : 0u);
-                    } else {
 #pragma unroll
-                        for (int j = 0; j < KS / 16; ++j)
-                            mma_f16_ss(tmem_base + buf * GN, make_desc_kmajor_rows<KS>(a_addr + j * 32), make_desc_kmajor_rows<KS>(b_addr + j * 32),
-                                       idesc, (k > 0 || j > 0) ? 1u : 0u);
-                    }
+                    for (int j = 0; j < KS / 16; ++j)
+                        mma_f16_ss(tmem_base + buf * GN, make_desc_kmajor_rows<KS>(a_addr + j * 32), make_desc_kmajor_rows<KS>(b_addr + j * 32),
+                                   idesc, (k > 0 || j > 0) ? 1u : 0u);
                     mma_commit(empty_bar + 8 * s);
                     if (k == n_k - 1) mma_commit(tmem_full + 8 * buf);
                 }
@@ -252,7 +231,7 @@ qconv_general_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_
 // One thread per (pixel, 8-channel group): reads are coalesced along w, writes are 16-byte vectors.
 template <typename T>
 __global__ void pack_activations_kernel(const T* __restrict__ x, T* __restrict__ xp, int planes /*4*Nb*/, int C, int H, int W,
-                                        int Hp, int Wp, int Cp, int pad_top, int pad_left, int ins_h = 1, int ins_w = 1, int planar = 0) {
+                                        int Hp, int Wp, int Cp, int pad_top, int pad_left, int ins_h = 1, int ins_w = 1) {
     const int groups = Cp / 8;
     const size_t total = (size_t)planes * Hp * Wp * groups;
     for (size_t idx = (size_t)blockIdx.x * blockDim.x + threadIdx.x; idx < total; idx += (size_t)gridDim.x * blockDim.x) {
@@ -279,9 +258,7 @@ __global__ void pack_activations_kernel(const T* __restrict__ x, T* __restrict__
             if (c < C && inside) v = x[(((size_t)plane * C + c) * H + ih) * W + iw];
             vals[e] = v;
         }
-        // planar: xp[comp][img][8-channel group][hp][wp][8]
-        const size_t o = planar ? ((((size_t)plane * groups + grp) * Hp + hp) * Wp + wp) * 8 : (((size_t)plane * Hp + hp) * Wp + wp) * Cp + grp * 8;
-        *reinterpret_cast<uint4*>(xp + o) = *reinterpret_cast<const uint4*>(vals);
+        *reinterpret_cast<uint4*>(xp + (((size_t)plane * Hp + hp) * Wp + wp) * Cp + grp * 8) = *reinterpret_cast<const uint4*>(vals);
     }
 }
 
@@ -289,8 +266,7 @@ __global__ void pack_activations_kernel(const T* __restrict__ x, T* __restrict__
 // Backward-data: Wexp[tap][m = l*Ci + ci][k = d*Cop + co] = s(l,d) * w[l^d][co][ci][taps-1-tap]   (flipped taps)
 template <typename T>
 __global__ void pack_filters_kernel(const T* __restrict__ w, T* __restrict__ wexp, int Co, int Ci, int taps, int Mp, int Kp,
-                                    int Cp /*padded channels of the reduced side*/, int transposed, int nc, int ga, unsigned long long neg,
-                                    int planar = 0) {
+                                    int Cp /*padded channels of the reduced side*/, int transposed, int nc, int ga, unsigned long long neg) {
     const size_t total = (size_t)taps * Mp * Kp;
     const int Cm = transposed ? Ci : Co;     // channels on the M side
     const int Ck = transposed ? Co : Ci;     // channels on the K side
@@ -308,9 +284,7 @@ __global__ void pack_filters_kernel(const T* __restrict__ w, T* __restrict__ wex
             v = DType<T>::load(w + ((size_t)(alg_pair(ga, l, d) * Co + co) * Ci + ci) * taps + src_tap);
             if (alg_negative(neg, l, d)) v = -v;
         }
-        // planar: Wexp[tap][k / 8][m][k % 8]
-        const size_t o = planar ? (((size_t)tap * (Kp / 8) + k / 8) * Mp + m) * 8 + (k & 7) : idx;
-        DType<T>::store(wexp + o, v);
+        DType<T>::store(wexp + idx, v);
     }
 }
 
@@ -698,30 +672,6 @@ int conv_tc_launch(Pass pass, int dtype, const Geom& g, const void* w, const voi
     uint8_t* xp = static_cast<uint8_t*>(scratch);
     uint8_t* wexp = xp + pl.xp_bytes;
 
-    // pick the output tile box (PW x PH x PN = 256 pixels) that wastes the fewest MMA columns
-    GParams p;
-    long long best = -1;
-    for (int pw = 8; pw <= 128; pw *= 2)
-        for (int ph = 1; ph * pw <= 256; ph *= 2) {
-            const int pn = 256 / (pw * ph);
-            if (pw * pl.SW > 256 || ph * pl.SH > 256) continue;
-            const long long vol = (long long)round_up(pl.Wout, pw) * round_up(pl.Hout, ph) * round_up(g.Nb, pn);
-            if (best < 0 || vol < best || (vol == best && pw > p.PW)) { best = vol; p.PW = pw; p.PH = ph; p.PN = pn; }
-        }
-    // 16-channel stride-1 layers: planar staging (see the kernel) if a box of one image, 8..32 pixels wide, wastes
-    // at most a quarter more columns than the best box
-    bool planar = false;
-    if (pl.Cp == 16 && pl.SH == 1 && pl.SW == 1) {
-        long long pbest = -1;
-        int ppw = 0, pph = 0;
-        for (int pw = 8; pw <= 32; pw *= 2) {
-            const int ph = 256 / pw;
-            const long long vol = (long long)round_up(pl.Wout, pw) * round_up(pl.Hout, ph) * g.Nb;
-            if (pbest < 0 || vol < pbest) { pbest = vol; ppw = pw; pph = ph; }
-        }
-        if (pbest * 4 <= best * 5) { planar = true; p.PW = ppw; p.PH = pph; p.PN = 1; }
-    }
-
     // stage the operands
     {
         const size_t total = (size_t)pl.LK * g.Nb * pl.Hp * pl.Wp * (pl.Cp / 8);
@@ -730,18 +680,30 @@ int conv_tc_launch(Pass pass, int dtype, const Geom& g, const void* w, const voi
         const int wblocks = (int)((wtotal + 255) / 256 < (size_t)sm_count() * 8 ? (wtotal + 255) / 256 : (size_t)sm_count() * 8);
         if (fmt == 0) {
             pack_activations_kernel<__half><<<blocks, 256, 0, stream>>>((const __half*)act, (__half*)xp, pl.LK * g.Nb, pl.Cin, pl.Hin, pl.Win,
-                                                                       pl.Hp, pl.Wp, pl.Cp, pl.pad_top, pl.pad_left, pl.ins_h, pl.ins_w, planar);
+                                                                       pl.Hp, pl.Wp, pl.Cp, pl.pad_top, pl.pad_left, pl.ins_h, pl.ins_w);
             pack_filters_kernel<__half><<<wblocks, 256, 0, stream>>>((const __half*)w, (__half*)wexp, g.Co, g.Ci, taps, pl.Mp, pl.Kp, pl.Cp,
-                                                                    pass == PASS_BWD_DATA ? 1 : 0, g.nc, g.ga, g.neg, planar);
+                                                                    pass == PASS_BWD_DATA ? 1 : 0, g.nc, g.ga, g.neg);
         } else {
             pack_activations_kernel<__nv_bfloat16><<<blocks, 256, 0, stream>>>((const __nv_bfloat16*)act, (__nv_bfloat16*)xp, pl.LK * g.Nb, pl.Cin,
-                                                                              pl.Hin, pl.Win, pl.Hp, pl.Wp, pl.Cp, pl.pad_top, pl.pad_left, pl.ins_h, pl.ins_w, planar);
+                                                                              pl.Hin, pl.Win, pl.Hp, pl.Wp, pl.Cp, pl.pad_top, pl.pad_left, pl.ins_h, pl.ins_w);
             pack_filters_kernel<__nv_bfloat16><<<wblocks, 256, 0, stream>>>((const __nv_bfloat16*)w, (__nv_bfloat16*)wexp, g.Co, g.Ci, taps,
-                                                                           pl.Mp, pl.Kp, pl.Cp, pass == PASS_BWD_DATA ? 1 : 0, g.nc, g.ga, g.neg, planar);
+                                                                           pl.Mp, pl.Kp, pl.Cp, pass == PASS_BWD_DATA ? 1 : 0, g.nc, g.ga, g.neg);
         }
         PCB_CUDA_TRY(cudaGetLastError());
     }
 
+    // pick the output tile box (PW x PH x PN = 256 pixels) that wastes the fewest MMA columns
+    GParams p;
+    {
+        long long best = -1;
+        for (int pw = 8; pw <= 128; pw *= 2)
+            for (int ph = 1; ph * pw <= 256; ph *= 2) {
+                const int pn = 256 / (pw * ph);
+                if (pw * pl.SW > 256 || ph * pl.SH > 256) continue;
+                const long long vol = (long long)round_up(pl.Wout, pw) * round_up(pl.Hout, ph) * round_up(g.Nb, pn);
+                if (best < 0 || vol < best || (vol == best && pw > p.PW)) { best = vol; p.PW = pw; p.PH = ph; p.PN = pn; }
+            }
+    }
     p.Nb = g.Nb; p.Cout = pl.Cout; p.Mvalid = g.nc * pl.Cout; p.HO = pl.Hout; p.WO = pl.Wout; p.Cp = pl.Cp;
     p.KH = g.KH; p.KW = g.KW; p.SH = pl.SH; p.SW = pl.SW; p.DH = g.DH; p.DW = g.DW;
     p.tiles_w = (pl.Wout + p.PW - 1) / p.PW; p.tiles_h = (pl.Hout + p.PH - 1) / p.PH; p.tiles_n = (g.Nb + p.PN - 1) / p.PN;
@@ -754,23 +716,6 @@ int conv_tc_launch(Pass pass, int dtype, const Geom& g, const void* w, const voi
     const CUtensorMapDataType dt = fmt == 0 ? CU_TENSOR_MAP_DATA_TYPE_FLOAT16 : CU_TENSOR_MAP_DATA_TYPE_BFLOAT16;
     const CUtensorMapSwizzle sw = pl.KS == 32 ? CU_TENSOR_MAP_SWIZZLE_64B : CU_TENSOR_MAP_SWIZZLE_32B;
     alignas(64) CUtensorMap map_w, map_x;
-    if (planar) {
-        {   // Wexp[tap][k / 8][m][k % 8] seen as (32 rows x 8, m / 32, k / 8, tap); box = 2 planes of 128 rows
-            const cuuint64_t dims[4] = {256, (cuuint64_t)pl.Mp / 32, (cuuint64_t)pl.Kp / 8, (cuuint64_t)taps};
-            const cuuint64_t strides[3] = {512, (cuuint64_t)pl.Mp * 16, (cuuint64_t)(pl.Kp / 8) * pl.Mp * 16};
-            const cuuint32_t box[4] = {256, GM / 32, 2, 1};
-            const int rc = make_tensor_map(&map_w, dt, wexp, 4, dims, strides, box, nullptr, CU_TENSOR_MAP_SWIZZLE_NONE, "planar filters");
-            if (rc != PCB_OK) return rc;
-        }
-        {   // xp[comp][img][plane][hp][wp][8] seen as (wp x 8, hp, plane, img, comp); box = 2 planes of PH rows of PW pixels
-            const cuuint64_t dims[5] = {(cuuint64_t)pl.Wp * 8, (cuuint64_t)pl.Hp, 2, (cuuint64_t)g.Nb, (cuuint64_t)pl.LK};
-            const cuuint64_t strides[4] = {(cuuint64_t)pl.Wp * 16, (cuuint64_t)pl.Hp * pl.Wp * 16, (cuuint64_t)2 * pl.Hp * pl.Wp * 16,
-                                           (cuuint64_t)g.Nb * 2 * pl.Hp * pl.Wp * 16};
-            const cuuint32_t box[5] = {(cuuint32_t)p.PW * 8, (cuuint32_t)p.PH, 2, 1, 1};
-            const int rc = make_tensor_map(&map_x, dt, xp, 5, dims, strides, box, nullptr, CU_TENSOR_MAP_SWIZZLE_NONE, "planar activations");
-            if (rc != PCB_OK) return rc;
-        }
-    } else {
     {
         const cuuint64_t dims[3] = {(cuuint64_t)pl.Kp, (cuuint64_t)pl.Mp, (cuuint64_t)taps};
         const cuuint64_t strides[2] = {(cuuint64_t)pl.Kp * 2, (cuuint64_t)pl.Mp * pl.Kp * 2};
@@ -791,22 +736,17 @@ int conv_tc_launch(Pass pass, int dtype, const Geom& g, const void* w, const voi
                                   CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
         if (r != CUDA_SUCCESS) { set_error("cuTensorMapEncodeTiled (activations) failed with code %d", (int)r); return PCB_ERR_CUDA; }
     }
-    }
 
     const int n_tiles = p.tiles_w * p.tiles_h * p.tiles_n * p.tiles_m;
     const int grid = n_tiles < sm_count() ? n_tiles : sm_count();
     if (pl.KS == 32) {
         constexpr size_t smem = 1024 + 8 * (GM + GN) * 32 * 2 + 512;
-        PCB_CUDA_TRY(cudaFuncSetAttribute(qconv_general_tc_kernel<32, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
-        qconv_general_tc_kernel<32, false><<<grid, G_THREADS, smem, stream>>>(map_w, map_x, p, (const uint16_t*)bias, (uint16_t*)out, status);
-    } else if (planar) {
-        constexpr size_t smem = 1024 + 12 * (GM + GN) * 16 * 2 + 512;
-        PCB_CUDA_TRY(cudaFuncSetAttribute(qconv_general_tc_kernel<16, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
-        qconv_general_tc_kernel<16, true><<<grid, G_THREADS, smem, stream>>>(map_w, map_x, p, (const uint16_t*)bias, (uint16_t*)out, status);
+        PCB_CUDA_TRY(cudaFuncSetAttribute(qconv_general_tc_kernel<32>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+        qconv_general_tc_kernel<32><<<grid, G_THREADS, smem, stream>>>(map_w, map_x, p, (const uint16_t*)bias, (uint16_t*)out, status);
     } else {
         constexpr size_t smem = 1024 + 12 * (GM + GN) * 16 * 2 + 512;
-        PCB_CUDA_TRY(cudaFuncSetAttribute(qconv_general_tc_kernel<16, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
-        qconv_general_tc_kernel<16, false><<<grid, G_THREADS, smem, stream>>>(map_w, map_x, p, (const uint16_t*)bias, (uint16_t*)out, status);
+        PCB_CUDA_TRY(cudaFuncSetAttribute(qconv_general_tc_kernel<16>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+        qconv_general_tc_kernel<16><<<grid, G_THREADS, smem, stream>>>(map_w, map_x, p, (const uint16_t*)bias, (uint16_t*)out, status);
     }
     PCB_CUDA_TRY(cudaGetLastError());
     return PCB_OK;

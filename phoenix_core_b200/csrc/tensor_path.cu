@@ -385,9 +385,10 @@ bool legacy_supported(int dtype, int variant, const Geom& g) {
 bool tensor_path_supported(Pass pass, int dtype, int variant, const Geom& g) {
     if (dtype == PCB_F32) return conv_tf32_supported(pass, dtype, variant, g);
     if (pass == PASS_BWD_FILTER)
-        return pointwise_filter_tc_supported(dtype, variant, g) || conv_filter_tc_supported(dtype, variant, g) || legacy_supported(dtype, variant, g);
-    return pointwise_tc_supported(pass, dtype, variant, g) || conv_tc_supported(pass, dtype, variant, g) ||
-           legacy_supported(dtype, variant, g);
+        return pointwise_filter_tc_supported(dtype, variant, g) || narrow_filter_tc_supported(dtype, variant, g) ||
+               conv_filter_tc_supported(dtype, variant, g) || legacy_supported(dtype, variant, g);
+    return pointwise_tc_supported(pass, dtype, variant, g) || narrow_tc_supported(pass, dtype, variant, g) ||
+           conv_tc_supported(pass, dtype, variant, g) || legacy_supported(dtype, variant, g);
 }
 
 size_t tensor_scratch_bytes(Pass pass, int dtype, int variant, int engine, const Geom& g) {
@@ -395,10 +396,12 @@ size_t tensor_scratch_bytes(Pass pass, int dtype, int variant, int engine, const
     if (dtype == PCB_F32) return conv_tf32_scratch_bytes(pass, g);
     if (pass == PASS_BWD_FILTER) {
         if (pointwise_filter_tc_supported(dtype, variant, g)) return (size_t)g.nc * g.Co * g.Ci * g.KH * g.KW * sizeof(float);
+        if (narrow_filter_tc_supported(dtype, variant, g)) return narrow_filter_tc_scratch_bytes(g);
         if (conv_filter_tc_supported(dtype, variant, g)) return conv_filter_tc_scratch_bytes(g);
         return (size_t)g.nc * g.Co * g.Ci * g.KH * g.KW * sizeof(float);
     }
     if (pointwise_tc_supported(pass, dtype, variant, g)) return 0;
+    if (narrow_tc_supported(pass, dtype, variant, g)) return narrow_tc_scratch_bytes(pass, g);
     if (conv_tc_supported(pass, dtype, variant, g)) return conv_tc_scratch_bytes(pass, g);
     return 0;
 }
@@ -421,6 +424,8 @@ int tensor_launch(Pass pass, int dtype, int /*variant*/, const Geom& g, const vo
     p.atomic_out = 0;
     PCB_CUDA_TRY(cudaMemsetAsync(status, 0, sizeof(int), stream));
     if (pointwise_tc_supported(pass, dtype, PCB_VARIANT_16_PRODUCT, g)) return pointwise_tc_launch(pass, dtype, g, a, b, bias, out, status, stream);
+    if (pass != PASS_BWD_FILTER && narrow_tc_supported(pass, dtype, PCB_VARIANT_16_PRODUCT, g))
+        return narrow_tc_launch(pass, dtype, g, a, b, bias, out, scratch, status, stream);
     if (pass != PASS_BWD_FILTER && conv_tc_supported(pass, dtype, PCB_VARIANT_16_PRODUCT, g))
         return conv_tc_launch(pass, dtype, g, a, b, bias, out, scratch, status, stream);
     if (pass == PASS_FWD) return launch_tc<PASS_FWD>(p, 1, a, b, bias, out, nullptr, status, stream);
@@ -430,6 +435,7 @@ int tensor_launch(Pass pass, int dtype, int /*variant*/, const Geom& g, const vo
     // accumulate in fp32 scratch, then cast once.
     if (scratch == nullptr) { set_error("backward-filter needs fp32 scratch"); return PCB_ERR_WORKSPACE; }
     if (pointwise_filter_tc_supported(dtype, PCB_VARIANT_16_PRODUCT, g)) return pointwise_filter_tc_launch(dtype, g, a, b, out, scratch, status, stream);
+    if (narrow_filter_tc_supported(dtype, PCB_VARIANT_16_PRODUCT, g)) return narrow_filter_tc_launch(dtype, g, a, b, out, scratch, status, stream);
     if (conv_filter_tc_supported(dtype, PCB_VARIANT_16_PRODUCT, g)) return conv_filter_tc_launch(dtype, g, a, b, out, scratch, status, stream);
     const int tiles = ((p.M + TBM - 1) / TBM) * ((p.N + TBN - 1) / TBN);
     int splits = (2 * sm_count() + tiles - 1) / tiles;

@@ -32,6 +32,16 @@ size_t conv_filter_tc_scratch_bytes(const Geom& g);
 int conv_filter_tc_launch(int dtype, const Geom& g, const void* dy, const void* x, void* dw, void* scratch, int* status,
                           cudaStream_t stream);
 
+// Narrow layers (<= 16 reduced channels, stride-1 correlation): halo tiles in shared memory serve every tap; see narrow_tc.cu.
+bool narrow_tc_supported(Pass pass, int dtype, int variant, const Geom& g);
+size_t narrow_tc_scratch_bytes(Pass pass, const Geom& g);
+int narrow_tc_launch(Pass pass, int dtype, const Geom& g, const void* w, const void* act, const void* bias, void* out, void* scratch,
+                     int* status, cudaStream_t stream);
+
+bool narrow_filter_tc_supported(int dtype, int variant, const Geom& g);
+size_t narrow_filter_tc_scratch_bytes(const Geom& g);
+int narrow_filter_tc_launch(int dtype, const Geom& g, const void* dy, const void* x, void* dw, void* scratch, int* status, cudaStream_t stream);
+
 // fp32 tensors on the tensor cores with error-compensated TF32 (convolution and dense); see conv_tf32.cu.
 bool conv_tf32_supported(Pass pass, int dtype, int variant, const Geom& g);
 size_t conv_tf32_scratch_bytes(Pass pass, const Geom& g);

@@ -157,6 +157,37 @@ def test_general_conv_tensor_core_vs_oracle(gpu, oracle, shape, dtype):
     _check(dw, rdw, dtype, gpu, "dw")
 
 
+# shapes for the narrow-layer kernels (<= 16 reduced channels; halo tiles in shared memory serve every tap):
+# n, ci, co, h, w, kh, kw, stride, pad(t,l,b,r), dilation
+NARROW_SHAPES = [
+    (2, 16, 16, 56, 56, 3, 3, (1, 1), (1, 1, 1, 1), (1, 1)),     # the 16-channel stage: two 8 x 28 tiles per column
+    (3, 16, 32, 19, 13, 3, 3, (1, 1), (1, 1, 1, 1), (1, 1)),     # ragged plane, all 128 rows in use
+    (2, 12, 24, 20, 17, 5, 5, (1, 1), (2, 2, 2, 2), (1, 1)),     # 25 taps (weights fill the shared memory), 3 planes of dy
+    (2, 16, 8, 18, 22, 3, 3, (1, 1), (2, 2, 2, 2), (2, 2)),      # dilation 2: a 12 x .. halo tile
+    (2, 9, 16, 40, 12, 1, 3, (1, 1), (0, 1, 0, 1), (1, 1)),      # 1 x 3 filter, 40 rows = two tiles of 20
+    (2, 32, 16, 17, 15, 3, 3, (2, 2), (1, 1, 1, 1), (1, 1)),     # backward-data of a stride-2 layer: zero insertion, 16 reduced channels
+    (2, 2, 16, 24, 20, 3, 3, (2, 2), (0, 0, 1, 1), (1, 1)),      # stride 2 with 2 channels: space-to-depth, four components
+    (1, 4, 8, 33, 31, 5, 5, (2, 2), (1, 1, 2, 2), (1, 1)),       # space-to-depth with an odd 5 x 5 filter
+]
+
+
+@pytest.mark.parametrize("shape", NARROW_SHAPES)
+@pytest.mark.parametrize("dtype", ["f16", "bf16"])
+def test_narrow_layers_tensor_core_vs_oracle(gpu, oracle, shape, dtype):
+    n, ci, co, h, w_, kh, kw, stride, pad, dil = shape
+    x = gpu.rounded(uniform(91, (4 * n, ci, h, w_)), dtype)
+    w = gpu.rounded(normal(92, (4, co, ci, kh, kw), std=(2.0 / (4 * ci * kh * kw)) ** 0.5), dtype)
+    b = gpu.rounded(uniform(93, (4, co)), dtype)
+    ref = oracle.conv2d_fwd(x, w, b, stride, dil, pad)
+    got = gpu.run_conv_fwd(x, w, b, stride, pad, dtype, "16p", "tensor", dilation=dil)
+    _check(got, ref, dtype, gpu, "y")
+    dy = gpu.rounded(normal(94, ref.shape), dtype)
+    rdw, rdx = oracle.conv2d_bwd(x, w, dy, stride, dil, pad)
+    dw, dx = gpu.run_conv_bwd(x, w, dy, stride, pad, dtype, "16p", "tensor", True, dilation=dil)
+    _check(dx, rdx, dtype, gpu, "dx")
+    _check(dw, rdw, dtype, gpu, "dw")
+
+
 @pytest.mark.parametrize("shape", GENERAL_TENSOR_SHAPES + [(2, 40, 24, 6, 5, 1, 1, (1, 1), (0, 0, 0, 0))])
 def test_fp32_on_tensor_cores_3xtf32_vs_oracle(gpu, oracle, shape):
     """fp32 tensors through the error-compensated TF32 kernels must hold the fp32 tolerance (1e-5), and agree with
