@@ -170,6 +170,18 @@ int pcb_qdense_engine_for(const pcb_dense_desc* desc, int pass);
  * (synchronises the stream). Returns PCB_OK or PCB_ERR_DEVICE_TIMEOUT. */
 int pcb_check_device_status(const void* workspace, size_t workspace_bytes, void* stream);
 
+/* ---- Auxiliary kernels of the QResNet-18 training harness (not part of the drop-in path) ---------------------
+ * The reference has no normalisation layer (its TensorFlow plugin leaves batch-norm to TensorFlow), so these two
+ * have no counterpart there. Batch-norm with one mean / variance per channel over a stacked tensor
+ * [planes = D*N, channels, hw] of 16-bit elements, optionally fused with ReLU; statistics, gamma, beta and their
+ * gradients are fp32. `scratch` is 5*channels floats of device memory. Forward saves `mean` and `invstd`
+ * ([channels] each) for the backward call; backward needs `y` only when relu != 0. */
+int pcb_aux_bn_relu_fwd(int dtype, const void* x, const float* gamma, const float* beta, void* y, float* mean, float* invstd,
+                        float* scratch, int planes, int channels, int hw, float eps, int relu, void* stream);
+int pcb_aux_bn_relu_bwd(int dtype, const void* x, const void* y, const void* dy, const float* gamma, const float* mean,
+                        const float* invstd, void* dx, float* dgamma, float* dbeta, float* scratch, int planes, int channels,
+                        int hw, int relu, void* stream);
+
 #ifdef __cplusplus
 }
 #endif

@@ -1,0 +1,249 @@
+// Batch-norm (+ ReLU) over stacked hyper-complex activations [planes = D*N, C, H, W]: one mean / variance per channel,
+// shared by the D components. Auxiliary kernels of the QResNet-18 harness -- the reference has no normalisation layer
+// (its TensorFlow plugin relies on TensorFlow's); they exist because the framework kernels launch one block per channel
+// and leave the GPU idle at 16 channels. Three passes over the data forward (statistics, apply), seven backward.
+//
+// Every kernel sees the tensor as rows of HW contiguous elements, row r = plane * C + c.
+#include "common.cuh"
+
+namespace pcb {
+namespace {
+
+constexpr int BN_THREADS = 256;
+
+template <typename T> struct Vec8;
+template <> struct Vec8<__half> {
+    static __device__ __forceinline__ void unpack(const uint4& v, float (&f)[8]) {
+        const __half2* h = reinterpret_cast<const __half2*>(&v);
+#pragma unroll
+        for (int i = 0; i < 4; ++i) { const float2 t = __half22float2(h[i]); f[2 * i] = t.x; f[2 * i + 1] = t.y; }
+    }
+    static __device__ __forceinline__ uint4 pack(const float (&f)[8]) {
+        uint4 v;
+        __half2* h = reinterpret_cast<__half2*>(&v);
+#pragma unroll
+        for (int i = 0; i < 4; ++i) h[i] = __floats2half2_rn(f[2 * i], f[2 * i + 1]);
+        return v;
+    }
+};
+template <> struct Vec8<__nv_bfloat16> {
+    static __device__ __forceinline__ void unpack(const uint4& v, float (&f)[8]) {
+        const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&v);
+#pragma unroll
+        for (int i = 0; i < 4; ++i) { const float2 t = __bfloat1622float2(h[i]); f[2 * i] = t.x; f[2 * i + 1] = t.y; }
+    }
+    static __device__ __forceinline__ uint4 pack(const float (&f)[8]) {
+        uint4 v;
+        __nv_bfloat162* h = reinterpret_cast<__nv_bfloat162*>(&v);
+#pragma unroll
+        for (int i = 0; i < 4; ++i) h[i] = __floats2bfloat162_rn(f[2 * i], f[2 * i + 1]);
+        return v;
+    }
+};
+
+// Sums of two quantities per channel. MODE 0: (x, x*x). MODE 1: (g, g*x) with g = dy masked by y > 0 when relu.
+// Block (c, s): the planes s, s + S, ... of channel c; one atomic pair per block into sums[0..C) and sums[C..2C).
+template <typename T, int MODE, bool VEC>
+__global__ void __launch_bounds__(BN_THREADS)
+bn_sums_kernel(const T* __restrict__ x, const T* __restrict__ y, const T* __restrict__ dy, float* __restrict__ sums, int planes, int C, int HW, int relu) {
+    const int c = blockIdx.x, s = blockIdx.y, S = gridDim.y;
+    float a0 = 0.f, a1 = 0.f;
+    for (int pl = s; pl < planes; pl += S) {
+        const size_t row = ((size_t)pl * C + c) * HW;
+        if (VEC) {
+            for (int i = threadIdx.x; i < HW / 8; i += BN_THREADS) {
+                float fx[8];
+                Vec8<T>::unpack(__ldg(reinterpret_cast<const uint4*>(x + row) + i), fx);
+                if (MODE == 0) {
+#pragma unroll
+                    for (int e = 0; e < 8; ++e) { a0 += fx[e]; a1 = fmaf(fx[e], fx[e], a1); }
+                } else {
+                    float fg[8], fy[8];
+                    Vec8<T>::unpack(__ldg(reinterpret_cast<const uint4*>(dy + row) + i), fg);
+                    if (relu) Vec8<T>::unpack(__ldg(reinterpret_cast<const uint4*>(y + row) + i), fy);
+#pragma unroll
+                    for (int e = 0; e < 8; ++e) {
+                        const float g = (relu && !(fy[e] > 0.f)) ? 0.f : fg[e];
+                        a0 += g; a1 = fmaf(g, fx[e], a1);
+                    }
+                }
+            }
+        } else {
+            for (int i = threadIdx.x; i < HW; i += BN_THREADS) {
+                const float fx = DType<T>::load(x + row + i);
+                if (MODE == 0) { a0 += fx; a1 = fmaf(fx, fx, a1); }
+                else {
+                    float g = DType<T>::load(dy + row + i);
+                    if (relu && !(DType<T>::load(y + row + i) > 0.f)) g = 0.f;
+                    a0 += g; a1 = fmaf(g, fx, a1);
+                }
+            }
+        }
+    }
+    __shared__ float red[2][BN_THREADS / 32];
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) { a0 += __shfl_xor_sync(0xffffffffu, a0, o); a1 += __shfl_xor_sync(0xffffffffu, a1, o); }
+    if ((threadIdx.x & 31) == 0) { red[0][threadIdx.x >> 5] = a0; red[1][threadIdx.x >> 5] = a1; }
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        float t0 = 0.f, t1 = 0.f;
+#pragma unroll
+        for (int w = 0; w < BN_THREADS / 32; ++w) { t0 += red[0][w]; t1 += red[1][w]; }
+        atomicAdd(sums + c, t0);
+        atomicAdd(sums + C + c, t1);
+    }
+}
+
+// Forward coefficients: y = x * coef[c] + coef[C + c]; also the saved mean and 1/std.
+__global__ void bn_fwd_finalize_kernel(const float* __restrict__ sums, const float* __restrict__ gamma, const float* __restrict__ beta,
+                                       float* __restrict__ mean, float* __restrict__ invstd, float* __restrict__ coef, int C, float count, float eps) {
+    const int c = blockIdx.x * blockDim.x + threadIdx.x;
+    if (c >= C) return;
+    const float m = sums[c] / count;
+    const float var = fmaxf(sums[C + c] / count - m * m, 0.f);
+    const float is = rsqrtf(var + eps);
+    mean[c] = m; invstd[c] = is;
+    const float sc = gamma[c] * is;
+    coef[c] = sc; coef[C + c] = beta[c] - m * sc;
+}
+
+// Backward coefficients: dx = a*g + b*x + k per channel; also dgamma, dbeta.
+//   xhat = (x - mean) * invstd;  dgamma = sum(g * xhat);  dbeta = sum(g);  dx = gamma*invstd * (g - dbeta/m - xhat * dgamma/m)
+__global__ void bn_bwd_finalize_kernel(const float* __restrict__ sums, const float* __restrict__ gamma, const float* __restrict__ mean,
+                                       const float* __restrict__ invstd, float* __restrict__ dgamma, float* __restrict__ dbeta,
+                                       float* __restrict__ coef, int C, float count) {
+    const int c = blockIdx.x * blockDim.x + threadIdx.x;
+    if (c >= C) return;
+    const float sg = sums[c], sgx = sums[C + c], is = invstd[c], mu = mean[c];
+    const float dg = (sgx - mu * sg) * is;
+    dgamma[c] = dg; dbeta[c] = sg;
+    const float a = gamma[c] * is;
+    const float b = -a * is * dg / count;
+    coef[c] = a; coef[C + c] = b; coef[2 * C + c] = -a * sg / count - b * mu;
+}
+
+// MODE 0: y = max(x*coef0 + coef1, 0 if relu).  MODE 1: dx = coef0*g + coef1*x + coef2 with g = dy masked by y > 0.
+template <typename T, int MODE, bool VEC>
+__global__ void __launch_bounds__(BN_THREADS)
+bn_apply_kernel(const T* __restrict__ x, const T* __restrict__ y, const T* __restrict__ dy, T* __restrict__ out, const float* __restrict__ coef,
+                size_t rows, int C, int HW, int relu) {
+    const int per_row = VEC ? HW / 8 : HW;
+    const size_t total = rows * per_row;
+    for (size_t idx = (size_t)blockIdx.x * blockDim.x + threadIdx.x; idx < total; idx += (size_t)gridDim.x * blockDim.x) {
+        const size_t row = idx / per_row;
+        const int i = (int)(idx - row * per_row);
+        const int c = (int)(row % C);
+        const float k0 = coef[c], k1 = coef[C + c], k2 = MODE == 1 ? coef[2 * C + c] : 0.f;
+        if (VEC) {
+            const size_t off = row * HW;
+            float fx[8], fo[8];
+            Vec8<T>::unpack(__ldg(reinterpret_cast<const uint4*>(x + off) + i), fx);
+            if (MODE == 0) {
+#pragma unroll
+                for (int e = 0; e < 8; ++e) { const float v = fmaf(fx[e], k0, k1); fo[e] = relu ? fmaxf(v, 0.f) : v; }
+            } else {
+                float fg[8], fy[8];
+                Vec8<T>::unpack(__ldg(reinterpret_cast<const uint4*>(dy + off) + i), fg);
+                if (relu) Vec8<T>::unpack(__ldg(reinterpret_cast<const uint4*>(y + off) + i), fy);
+#pragma unroll
+                for (int e = 0; e < 8; ++e) {
+                    const float g = (relu && !(fy[e] > 0.f)) ? 0.f : fg[e];
+                    fo[e] = fmaf(k0, g, fmaf(k1, fx[e], k2));
+                }
+            }
+            reinterpret_cast<uint4*>(out + off)[i] = Vec8<T>::pack(fo);
+        } else {
+            const size_t off = row * HW + i;
+            const float fx = DType<T>::load(x + off);
+            float v;
+            if (MODE == 0) { v = fmaf(fx, k0, k1); if (relu) v = fmaxf(v, 0.f); }
+            else {
+                float g = DType<T>::load(dy + off);
+                if (relu && !(DType<T>::load(y + off) > 0.f)) g = 0.f;
+                v = fmaf(k0, g, fmaf(k1, fx, k2));
+            }
+            DType<T>::store(out + off, v);
+        }
+    }
+}
+
+int blocks_for(size_t work) {
+    int dev = 0, sms = 148;
+    if (cudaGetDevice(&dev) == cudaSuccess) cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
+    const size_t cap = (size_t)sms * 16, need = (work + BN_THREADS - 1) / BN_THREADS;
+    return (int)(need < cap ? (need ? need : 1) : cap);
+}
+
+template <typename T>
+int bn_fwd_typed(const T* x, const float* gamma, const float* beta, T* y, float* mean, float* invstd, float* scratch, int planes, int C, int HW,
+                 float eps, int relu, cudaStream_t stream) {
+    const bool vec = HW % 8 == 0 && (reinterpret_cast<uintptr_t>(x) | reinterpret_cast<uintptr_t>(y)) % 16 == 0;
+    int S = (8 * 148 + C - 1) / C;
+    if (S > planes) S = planes;
+    if (S < 1) S = 1;
+    PCB_CUDA_TRY(cudaMemsetAsync(scratch, 0, 2 * C * sizeof(float), stream));
+    const dim3 grid(C, S);
+    if (vec) bn_sums_kernel<T, 0, true><<<grid, BN_THREADS, 0, stream>>>(x, nullptr, nullptr, scratch, planes, C, HW, 0);
+    else bn_sums_kernel<T, 0, false><<<grid, BN_THREADS, 0, stream>>>(x, nullptr, nullptr, scratch, planes, C, HW, 0);
+    float* coef = scratch + 2 * C;
+    bn_fwd_finalize_kernel<<<(C + 127) / 128, 128, 0, stream>>>(scratch, gamma, beta, mean, invstd, coef, C, (float)planes * HW, eps);
+    const size_t rows = (size_t)planes * C;
+    if (vec) bn_apply_kernel<T, 0, true><<<blocks_for(rows * (HW / 8)), BN_THREADS, 0, stream>>>(x, nullptr, nullptr, y, coef, rows, C, HW, relu);
+    else bn_apply_kernel<T, 0, false><<<blocks_for(rows * HW), BN_THREADS, 0, stream>>>(x, nullptr, nullptr, y, coef, rows, C, HW, relu);
+    PCB_CUDA_TRY(cudaGetLastError());
+    return PCB_OK;
+}
+
+template <typename T>
+int bn_bwd_typed(const T* x, const T* y, const T* dy, const float* gamma, const float* mean, const float* invstd, T* dx, float* dgamma, float* dbeta,
+                 float* scratch, int planes, int C, int HW, int relu, cudaStream_t stream) {
+    const bool vec = HW % 8 == 0 && (reinterpret_cast<uintptr_t>(x) | reinterpret_cast<uintptr_t>(dy) | reinterpret_cast<uintptr_t>(dx) |
+                                     (relu ? reinterpret_cast<uintptr_t>(y) : 0)) % 16 == 0;
+    int S = (8 * 148 + C - 1) / C;
+    if (S > planes) S = planes;
+    if (S < 1) S = 1;
+    PCB_CUDA_TRY(cudaMemsetAsync(scratch, 0, 2 * C * sizeof(float), stream));
+    const dim3 grid(C, S);
+    if (vec) bn_sums_kernel<T, 1, true><<<grid, BN_THREADS, 0, stream>>>(x, y, dy, scratch, planes, C, HW, relu);
+    else bn_sums_kernel<T, 1, false><<<grid, BN_THREADS, 0, stream>>>(x, y, dy, scratch, planes, C, HW, relu);
+    float* coef = scratch + 2 * C;
+    bn_bwd_finalize_kernel<<<(C + 127) / 128, 128, 0, stream>>>(scratch, gamma, mean, invstd, dgamma, dbeta, coef, C, (float)planes * HW);
+    const size_t rows = (size_t)planes * C;
+    if (vec) bn_apply_kernel<T, 1, true><<<blocks_for(rows * (HW / 8)), BN_THREADS, 0, stream>>>(x, y, dy, dx, coef, rows, C, HW, relu);
+    else bn_apply_kernel<T, 1, false><<<blocks_for(rows * HW), BN_THREADS, 0, stream>>>(x, y, dy, dx, coef, rows, C, HW, relu);
+    PCB_CUDA_TRY(cudaGetLastError());
+    return PCB_OK;
+}
+
+}  // namespace
+}  // namespace pcb
+
+extern "C" {
+
+int pcb_aux_bn_relu_fwd(int dtype, const void* x, const float* gamma, const float* beta, void* y, float* mean, float* invstd, float* scratch,
+                        int planes, int channels, int hw, float eps, int relu, void* stream) {
+    using namespace pcb;
+    if (!x || !gamma || !beta || !y || !mean || !invstd || !scratch || planes <= 0 || channels <= 0 || hw <= 0) {
+        set_error("invalid batch-norm arguments");
+        return PCB_ERR_INVALID_ARGUMENT;
+    }
+    if (dtype == PCB_F16) return bn_fwd_typed<__half>((const __half*)x, gamma, beta, (__half*)y, mean, invstd, scratch, planes, channels, hw, eps, relu, (cudaStream_t)stream);
+    if (dtype == PCB_BF16) return bn_fwd_typed<__nv_bfloat16>((const __nv_bfloat16*)x, gamma, beta, (__nv_bfloat16*)y, mean, invstd, scratch, planes, channels, hw, eps, relu, (cudaStream_t)stream);
+    set_error("batch-norm helper: 16-bit tensors only");
+    return PCB_ERR_UNSUPPORTED;
+}
+
+int pcb_aux_bn_relu_bwd(int dtype, const void* x, const void* y, const void* dy, const float* gamma, const float* mean, const float* invstd, void* dx,
+                        float* dgamma, float* dbeta, float* scratch, int planes, int channels, int hw, int relu, void* stream) {
+    using namespace pcb;
+    if (!x || !dy || !gamma || !mean || !invstd || !dx || !dgamma || !dbeta || !scratch || (relu && !y) || planes <= 0 || channels <= 0 || hw <= 0) {
+        set_error("invalid batch-norm arguments");
+        return PCB_ERR_INVALID_ARGUMENT;
+    }
+    if (dtype == PCB_F16) return bn_bwd_typed<__half>((const __half*)x, (const __half*)y, (const __half*)dy, gamma, mean, invstd, (__half*)dx, dgamma, dbeta, scratch, planes, channels, hw, relu, (cudaStream_t)stream);
+    if (dtype == PCB_BF16) return bn_bwd_typed<__nv_bfloat16>((const __nv_bfloat16*)x, (const __nv_bfloat16*)y, (const __nv_bfloat16*)dy, gamma, mean, invstd, (__nv_bfloat16*)dx, dgamma, dbeta, scratch, planes, channels, hw, relu, (cudaStream_t)stream);
+    set_error("batch-norm helper: 16-bit tensors only");
+    return PCB_ERR_UNSUPPORTED;
+}
+
+}  // extern "C"

@@ -8,7 +8,7 @@ import sys
 
 HERE = os.path.dirname(os.path.abspath(__file__))
 LIB = os.path.join(HERE, "libphoenix_core_b200.so")
-SOURCES = ["api.cu", "simt_qgemm.cu", "tensor_path.cu", "pointwise_tc.cu", "conv_tc.cu", "narrow_tc.cu", "conv_tf32.cu"]
+SOURCES = ["api.cu", "simt_qgemm.cu", "tensor_path.cu", "pointwise_tc.cu", "conv_tc.cu", "narrow_tc.cu", "conv_tf32.cu", "aux_bn.cu"]
 HEADERS = ["common.cuh", "tensor_path.cuh", "umma.cuh", "tc_common.cuh", os.path.join("..", "..", "include", "phoenix_core_b200.h")]
 NVCC_FLAGS = [
     "-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "-std=c++17",

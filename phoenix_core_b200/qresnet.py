@@ -7,7 +7,8 @@ Standard ResNet-18 topology with every real channel count divided by 4 (quaterni
 versions (`conv2DFwd/Bwd`, `denseFwd/Bwd` of this package). The UpStride engine itself contains no model code:
 batch-norm, ReLU, pooling, loss and optimiser are plain torch ops and are harness glue, not part of the
 drop-in path. Batch-norm normalises each quaternion channel with one mean / variance shared by its four
-components (statistics over the stacked `[4N, C, H, W]` tensor), written with torch reductions and broadcasts.
+components (statistics over the stacked `[4N, C, H, W]` tensor); it runs on two helper kernels of the library
+(`pcb_aux_bn_relu_fwd/bwd`), because the framework's own batch-norm kernels idle the GPU at 16 channels.
 
 Precision: fp16 activations and filters (the reference's fp16 tensors; every kernel accumulates in fp32),
 fp32 master weights, static loss scale. All filter gradients are written by the kernels straight into ONE
@@ -30,9 +31,11 @@ if ROOT not in sys.path:
     sys.path.insert(0, ROOT)
 
 import phoenix_core_b200 as pcb  # noqa: E402
+from phoenix_core_b200 import _lib  # noqa: E402
 from phoenix_core_b200.context import Context  # noqa: E402
 
 LOSS_SCALE = 256.0
+_DT = {torch.float16: _lib.PCB_F16, torch.bfloat16: _lib.PCB_BF16}
 
 
 def reduce_and_apply(flat_w32, flat_mom, flat_grad, world, lr, momentum, loss_scale):
@@ -47,27 +50,54 @@ def reduce_and_apply(flat_w32, flat_mom, flat_grad, world, lr, momentum, loss_sc
 
 class _BNReLUFn(torch.autograd.Function):
     """Batch-norm over the stacked [4N, C, H, W] tensor (one mean / variance per quaternion channel, shared by its
-    four components) with an optional fused ReLU, written with plain reductions and broadcast element-wise ops:
-    torch's own batch-norm kernels (native and cuDNN alike) launch one block per channel, which at 16 channels and
-    a stacked batch of 512 leaves the GPU idle. Harness glue, not part of the drop-in path."""
+    four components) with an optional fused ReLU. Harness glue, not part of the drop-in path: torch's own batch-norm
+    kernels (native and cuDNN alike) launch one block per channel, which at 16 channels and a stacked batch of 512
+    leaves the GPU idle, so 16-bit CUDA tensors go to the two helper kernels of the library (statistics + apply:
+    three passes over the data forward, seven backward); anything else takes plain torch reductions."""
 
     @staticmethod
     def forward(ctx, x, gamma, beta, eps, relu):
-        var, mean = torch.var_mean(x.float() if x.numel() < (1 << 22) else x, dim=(0, 2, 3), unbiased=False)
-        var, mean = var.float(), mean.float()
+        ctx.relu = relu
+        if x.is_cuda and x.dtype in (torch.float16, torch.bfloat16) and x.is_contiguous():
+            planes, c = x.shape[0], x.shape[1]
+            hw = x.numel() // (planes * c)
+            y = torch.empty_like(x)
+            mean = torch.empty(c, dtype=torch.float32, device=x.device)
+            invstd = torch.empty_like(mean)
+            scratch = torch.empty(5 * c, dtype=torch.float32, device=x.device)
+            _lib.check(_lib.lib().pcb_aux_bn_relu_fwd(_DT[x.dtype], x.data_ptr(), gamma.data_ptr(), beta.data_ptr(), y.data_ptr(),
+                                                      mean.data_ptr(), invstd.data_ptr(), scratch.data_ptr(), planes, c, hw, eps, int(relu),
+                                                      torch.cuda.current_stream().cuda_stream))
+            ctx.fused = True
+            ctx.save_for_backward(x, y if relu else None, mean, invstd, gamma)
+            return y
+        var, mean = torch.var_mean(x.float(), dim=(0, 2, 3), unbiased=False)
         invstd = torch.rsqrt(var + eps)
         scale = (gamma * invstd)
         shift = beta - mean * scale
         y = torch.addcmul(shift.to(x.dtype).view(1, -1, 1, 1), x, scale.to(x.dtype).view(1, -1, 1, 1))
         if relu:
             y.clamp_min_(0)
-        ctx.relu = relu
+        ctx.fused = False
         ctx.save_for_backward(x, y if relu else None, mean, invstd, gamma)
         return y
 
     @staticmethod
     def backward(ctx, dy):
         x, y, mean, invstd, gamma = ctx.saved_tensors
+        if ctx.fused:
+            dy = dy.contiguous()
+            planes, c = x.shape[0], x.shape[1]
+            hw = x.numel() // (planes * c)
+            dx = torch.empty_like(x)
+            dgamma = torch.empty(c, dtype=torch.float32, device=x.device)
+            dbeta = torch.empty_like(dgamma)
+            scratch = torch.empty(5 * c, dtype=torch.float32, device=x.device)
+            _lib.check(_lib.lib().pcb_aux_bn_relu_bwd(_DT[x.dtype], x.data_ptr(), y.data_ptr() if ctx.relu else None, dy.data_ptr(),
+                                                      gamma.data_ptr(), mean.data_ptr(), invstd.data_ptr(), dx.data_ptr(), dgamma.data_ptr(),
+                                                      dbeta.data_ptr(), scratch.data_ptr(), planes, c, hw, int(ctx.relu),
+                                                      torch.cuda.current_stream().cuda_stream))
+            return dx, dgamma, dbeta, None, None
         g = dy * (y > 0) if ctx.relu else dy
         m = x.numel() // x.shape[1]
         sum_g = g.sum(dim=(0, 2, 3), dtype=torch.float32)
@@ -351,7 +381,7 @@ def run(batch, steps, warmup, image=224, quiet=False):
                   "parameters": model.num_parameters(),
                   "e2e": {"value": batch * world * e2e_steps / (e2e_ms * 1e-3), "unit": "images/s",
                           "h2d_bytes_per_step": host_images.numel() * 2 + host_labels.numel() * 8, "d2h_bytes_per_step": 4},
-                  "glue": "batch-norm / ReLU / pooling / loss / SGD are torch ops (not in the reference); convolutions and dense: this package only"}
+                  "glue": "convolutions and dense: this package only; batch-norm + ReLU: two helper kernels of the library; pooling / loss / SGD: torch ops (none of the three is in the reference)"}
         if not quiet:
             print(json.dumps(result), flush=True)
     if own_pg:
