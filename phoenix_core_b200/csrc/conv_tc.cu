@@ -42,6 +42,10 @@ struct GParams {
     int fmt, has_bias;
     int LK;                      // input components along K: 4, or 1 for a real-valued (type-0) input
     int store_vec;               // output pixels per store: largest power of two <= 16 dividing WO (and the pointer alignment)
+    int n_cols;                  // columns of the tile in use (256, or 8 * PH in halo mode)
+    // halo mode
+    int Wt, Ht, n_stages;
+    uint32_t stage_bytes;
 };
 
 // K-major operand tile whose rows hold KS 16-bit elements (KS*2 bytes, swizzle span == row size):
@@ -52,28 +56,43 @@ __device__ __forceinline__ uint64_t make_desc_kmajor_rows(uint32_t smem_addr) {
     return (uint64_t)((smem_addr & 0x3FFFFu) >> 4) | ((uint64_t)1 << 16) | ((uint64_t)((8 * KS * 2) >> 4) << 32) | DESC_VERSION_SM100 | layout;
 }
 
-template <int KS>
+// The same rows with the 8-row groups `group_bytes` apart: the halo tile, where a group is 8 consecutive pixels of one
+// tile row and the next group is one halo-row pitch further. The swizzle is a function of the absolute shared-memory
+// address (TMA writes it that way and the MMA reads it that way), so the start address may sit anywhere on a pixel.
+__device__ __forceinline__ uint64_t make_desc_kmajor_sw64_groups(uint32_t smem_addr, uint32_t group_bytes) {
+    return (uint64_t)((smem_addr & 0x3FFFFu) >> 4) | ((uint64_t)1 << 16) | ((uint64_t)((group_bytes >> 4) & 0x3FFFu) << 32) | DESC_VERSION_SM100 |
+           (4ull << 61);
+}
+
+// HALO (KS == 32, stride-1 correlation, tile = 8 x PH pixels of one image): a stage is one 32-channel slice of one
+// component -- the halo tile [Ht][Wt][32 channels] of the output tile and the filter slices of ALL taps -- and every
+// tap's MMAs read the same halo tile at a shifted start address. Per MMA the kernel then moves 5 KB from L2 instead
+// of 12 KB, which is what bounds the plain form.
+template <int KS, bool HALO>
 __global__ void __launch_bounds__(G_THREADS, 1)
 qconv_general_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant__ CUtensorMap map_x, GParams p,
                         const uint16_t* __restrict__ bias, uint16_t* __restrict__ out, int* __restrict__ status) {
-    constexpr uint32_t A_BYTES = GM * KS * 2, B_BYTES = GN * KS * 2, STAGE = A_BYTES + B_BYTES;
-    constexpr int STAGES = KS == 32 ? 8 : 12;
+    constexpr uint32_t A_BYTES = GM * KS * 2, B_BYTES = GN * KS * 2;
+    constexpr int MAX_STAGES = KS == 32 ? 8 : 12;
+    const uint32_t STAGE = HALO ? p.stage_bytes : A_BYTES + B_BYTES;
+    const int STAGES = HALO ? p.n_stages : MAX_STAGES;
+    const int taps = p.KH * p.KW;
     extern __shared__ uint8_t smem_raw[];
     const int t = threadIdx.x, warp = t >> 5, lane = t & 31;
     uint8_t* base = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
     uint64_t* bars = reinterpret_cast<uint64_t*>(base + STAGES * STAGE);
-    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 2 * STAGES + 4);
+    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 2 * MAX_STAGES + 4);
     const uint32_t tiles_addr = smem_u32(base);
-    const uint32_t full_bar = smem_u32(bars), empty_bar = smem_u32(bars + STAGES);
-    const uint32_t tmem_full = smem_u32(bars + 2 * STAGES), tmem_empty = smem_u32(bars + 2 * STAGES + 2);
+    const uint32_t full_bar = smem_u32(bars), empty_bar = smem_u32(bars + MAX_STAGES);
+    const uint32_t tmem_full = smem_u32(bars + 2 * MAX_STAGES), tmem_empty = smem_u32(bars + 2 * MAX_STAGES + 2);
 
     const int tiles_px = p.tiles_w * p.tiles_h * p.tiles_n;
     const int n_tiles = tiles_px * p.tiles_m;
     const int c_steps = p.Cp / KS;
-    const int n_k = p.KH * p.KW * p.LK * c_steps;
+    const int n_k = (HALO ? 1 : taps) * p.LK * c_steps;           // stages per tile
 
     if (t == 0) {
-        for (int s = 0; s < STAGES; ++s) { mbar_init(full_bar + 8 * s, 1); mbar_init(empty_bar + 8 * s, 1); }
+        for (int s = 0; s < MAX_STAGES; ++s) { mbar_init(full_bar + 8 * s, 1); mbar_init(empty_bar + 8 * s, 1); }
         for (int b = 0; b < 2; ++b) { mbar_init(tmem_full + 8 * b, 1); mbar_init(tmem_empty + 8 * b, 8); }
         fence_barrier_init();
     }
@@ -95,6 +114,20 @@ qconv_general_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_
                 const int th = rest % p.tiles_h;
                 const int tn = rest / p.tiles_h;
                 const int m0 = tm * GM, ow0 = tw * p.PW, oh0 = th * p.PH, n0 = tn * p.PN;
+                if (HALO) {
+                    for (int l = 0; l < p.LK && ok; ++l) {
+                        for (int cs = 0; cs < c_steps; ++cs, ++it) {
+                            const int s = it % STAGES;
+                            ok = mbar_wait_bounded(empty_bar + 8 * s, ((it / STAGES) & 1) ^ 1, status, ST_G_PRODUCER);
+                            if (!ok) break;
+                            const uint32_t a_dst = tiles_addr + s * STAGE, bar = full_bar + 8 * s;
+                            mbar_arrive_expect_tx(bar, taps * A_BYTES + (uint32_t)p.Wt * p.Ht * KS * 2);
+                            tma_load_3d(a_dst, &map_w, l * p.Cp + cs * KS, m0, 0, bar);                       // [tap][128 rows][32 channels]
+                            tma_load_5d(a_dst + taps * A_BYTES, &map_x, cs * KS, ow0, oh0, n0, l, bar);       // [Ht][Wt][32 channels]
+                        }
+                    }
+                    continue;
+                }
                 for (int tap = 0; tap < p.KH * p.KW && ok; ++tap) {
                     const int kh = tap / p.KW, kw = tap - kh * p.KW;
                     const int wp0 = ow0 * p.SW + kw * p.DW, hp0 = oh0 * p.SH + kh * p.DH;
@@ -115,7 +148,7 @@ qconv_general_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_
         __syncwarp();
     } else if (warp == 1) {
         // ---------------------------------------------------------------- MMA issuer
-        const uint32_t idesc = make_idesc_f16(p.fmt, GM, GN, false, false);
+        const uint32_t idesc = make_idesc_f16(p.fmt, GM, HALO ? p.n_cols : GN, false, false);
         int it = 0, local_tile = 0;
         bool ok = true;
         for (int tile = blockIdx.x; tile < n_tiles && ok; tile += gridDim.x, ++local_tile) {
@@ -131,11 +164,22 @@ qconv_general_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_
                 if (!ok) break;
                 tc_fence_after_sync();
                 if (lane == 0) {
-                    const uint32_t a_addr = tiles_addr + s * STAGE, b_addr = a_addr + A_BYTES;
+                    const uint32_t a_addr = tiles_addr + s * STAGE, b_addr = a_addr + (HALO ? taps * A_BYTES : A_BYTES);
+                    if (HALO) {
+                        for (int tap = 0; tap < taps; ++tap) {
+                            const int kh = tap / p.KW, kw = tap - kh * p.KW;
+                            const uint32_t shift = (uint32_t)(kh * p.DH * p.Wt + kw * p.DW) * (KS * 2);
 #pragma unroll
-                    for (int j = 0; j < KS / 16; ++j)
-                        mma_f16_ss(tmem_base + buf * GN, make_desc_kmajor_rows<KS>(a_addr + j * 32), make_desc_kmajor_rows<KS>(b_addr + j * 32),
-                                   idesc, (k > 0 || j > 0) ? 1u : 0u);
+                            for (int j = 0; j < KS / 16; ++j)
+                                mma_f16_ss(tmem_base + buf * GN, make_desc_kmajor_rows<KS>(a_addr + tap * A_BYTES + j * 32),
+                                           make_desc_kmajor_sw64_groups(b_addr + shift + j * 32, p.Wt * KS * 2), idesc, (k > 0 || tap > 0 || j > 0) ? 1u : 0u);
+                        }
+                    } else {
+#pragma unroll
+                        for (int j = 0; j < KS / 16; ++j)
+                            mma_f16_ss(tmem_base + buf * GN, make_desc_kmajor_rows<KS>(a_addr + j * 32), make_desc_kmajor_rows<KS>(b_addr + j * 32),
+                                       idesc, (k > 0 || j > 0) ? 1u : 0u);
+                    }
                     mma_commit(empty_bar + 8 * s);
                     if (k == n_k - 1) mma_commit(tmem_full + 8 * buf);
                 }
@@ -192,6 +236,7 @@ qconv_general_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_
                 for (int g8 = 0; g8 < 4; ++g8) {
                     if (wide && (g8 & 1)) continue;                      // the odd groups were written with their even neighbours
                     const int j = col0 + g8 * 8;                         // column -> (image, row, pixel) of the tile box
+                    if (j >= p.n_cols) continue;
                     const int wl = j % p.PW, hl = (j / p.PW) % p.PH, nl = j / (p.PW * p.PH);
                     const int ow = ow0 + wl, oh = oh0 + hl, img = n0 + nl;
                     if (ow >= p.WO || oh >= p.HO || img >= p.Nb) continue;
@@ -704,6 +749,22 @@ int conv_tc_launch(Pass pass, int dtype, const Geom& g, const void* w, const voi
                 if (best < 0 || vol < best || (vol == best && pw > p.PW)) { best = vol; p.PW = pw; p.PH = ph; p.PN = pn; }
             }
     }
+    // Halo mode (see the kernel): stride-1 correlation, 32-channel slices, several taps, and an image tall enough for
+    // tiles of 8 x PH >= 192 pixels (smaller tiles re-read the filter slices too often to gain anything).
+    bool halo = false;
+    p.n_cols = 256; p.Wt = p.Ht = 0; p.n_stages = 0; p.stage_bytes = 0;
+    if (pl.KS == 32 && pl.SH == 1 && pl.SW == 1 && taps >= 4 && pl.Wout >= 8) {
+        const int rows = (pl.Hout + 31) / 32;
+        const int ph = (((pl.Hout + rows - 1) / rows) + 1) & ~1;
+        const int wt = 8 + (g.KW - 1) * g.DW, ht = ph + (g.KH - 1) * g.DH;
+        const uint32_t stage = ((uint32_t)taps * GM * 32 * 2 + (uint32_t)wt * ht * 64 + 1023) / 1024 * 1024;
+        const int n_stages = (int)((227 * 1024 - 1024 - 512) / stage);
+        if (ph >= 24 && wt <= 256 && ht <= 256 && taps <= 256 && n_stages >= 2) {
+            halo = true;
+            p.PW = 8; p.PH = ph; p.PN = 1; p.n_cols = 8 * ph; p.Wt = wt; p.Ht = ht;
+            p.n_stages = n_stages > 8 ? 8 : n_stages; p.stage_bytes = stage;
+        }
+    }
     p.Nb = g.Nb; p.Cout = pl.Cout; p.Mvalid = g.nc * pl.Cout; p.HO = pl.Hout; p.WO = pl.Wout; p.Cp = pl.Cp;
     p.KH = g.KH; p.KW = g.KW; p.SH = pl.SH; p.SW = pl.SW; p.DH = g.DH; p.DW = g.DW;
     p.tiles_w = (pl.Wout + p.PW - 1) / p.PW; p.tiles_h = (pl.Hout + p.PH - 1) / p.PH; p.tiles_n = (g.Nb + p.PN - 1) / p.PN;
@@ -719,7 +780,7 @@ int conv_tc_launch(Pass pass, int dtype, const Geom& g, const void* w, const voi
     {
         const cuuint64_t dims[3] = {(cuuint64_t)pl.Kp, (cuuint64_t)pl.Mp, (cuuint64_t)taps};
         const cuuint64_t strides[2] = {(cuuint64_t)pl.Kp * 2, (cuuint64_t)pl.Mp * pl.Kp * 2};
-        const cuuint32_t box[3] = {(cuuint32_t)pl.KS, GM, 1};
+        const cuuint32_t box[3] = {(cuuint32_t)pl.KS, GM, (cuuint32_t)(halo ? taps : 1)};
         const cuuint32_t es[3] = {1, 1, 1};
         const CUresult r = encode(&map_w, dt, 3, wexp, dims, strides, box, es, CU_TENSOR_MAP_INTERLEAVE_NONE, sw,
                                   CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
@@ -730,7 +791,8 @@ int conv_tc_launch(Pass pass, int dtype, const Geom& g, const void* w, const voi
         const cuuint64_t strides[4] = {(cuuint64_t)pl.Cp * 2, (cuuint64_t)pl.Wp * pl.Cp * 2, (cuuint64_t)pl.Hp * pl.Wp * pl.Cp * 2,
                                        (cuuint64_t)g.Nb * pl.Hp * pl.Wp * pl.Cp * 2};
         // with an element stride s the box extent is given in input elements: s * (pixels - 1) + 1 of them hold the pixels loaded
-        const cuuint32_t box[5] = {(cuuint32_t)pl.KS, (cuuint32_t)((p.PW - 1) * pl.SW + 1), (cuuint32_t)((p.PH - 1) * pl.SH + 1), (cuuint32_t)p.PN, 1};
+        const cuuint32_t box[5] = {(cuuint32_t)pl.KS, (cuuint32_t)(halo ? p.Wt : (p.PW - 1) * pl.SW + 1), (cuuint32_t)(halo ? p.Ht : (p.PH - 1) * pl.SH + 1),
+                                   (cuuint32_t)p.PN, 1};
         const cuuint32_t es[5] = {1, (cuuint32_t)pl.SW, (cuuint32_t)pl.SH, 1, 1};
         const CUresult r = encode(&map_x, dt, 5, xp, dims, strides, box, es, CU_TENSOR_MAP_INTERLEAVE_NONE, sw,
                                   CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
@@ -739,14 +801,18 @@ int conv_tc_launch(Pass pass, int dtype, const Geom& g, const void* w, const voi
 
     const int n_tiles = p.tiles_w * p.tiles_h * p.tiles_n * p.tiles_m;
     const int grid = n_tiles < sm_count() ? n_tiles : sm_count();
-    if (pl.KS == 32) {
+    if (halo) {
+        const size_t smem = 1024 + (size_t)p.n_stages * p.stage_bytes + 512;
+        PCB_CUDA_TRY(cudaFuncSetAttribute(qconv_general_tc_kernel<32, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+        qconv_general_tc_kernel<32, true><<<grid, G_THREADS, smem, stream>>>(map_w, map_x, p, (const uint16_t*)bias, (uint16_t*)out, status);
+    } else if (pl.KS == 32) {
         constexpr size_t smem = 1024 + 8 * (GM + GN) * 32 * 2 + 512;
-        PCB_CUDA_TRY(cudaFuncSetAttribute(qconv_general_tc_kernel<32>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
-        qconv_general_tc_kernel<32><<<grid, G_THREADS, smem, stream>>>(map_w, map_x, p, (const uint16_t*)bias, (uint16_t*)out, status);
+        PCB_CUDA_TRY(cudaFuncSetAttribute(qconv_general_tc_kernel<32, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+        qconv_general_tc_kernel<32, false><<<grid, G_THREADS, smem, stream>>>(map_w, map_x, p, (const uint16_t*)bias, (uint16_t*)out, status);
     } else {
         constexpr size_t smem = 1024 + 12 * (GM + GN) * 16 * 2 + 512;
-        PCB_CUDA_TRY(cudaFuncSetAttribute(qconv_general_tc_kernel<16>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
-        qconv_general_tc_kernel<16><<<grid, G_THREADS, smem, stream>>>(map_w, map_x, p, (const uint16_t*)bias, (uint16_t*)out, status);
+        PCB_CUDA_TRY(cudaFuncSetAttribute(qconv_general_tc_kernel<16, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+        qconv_general_tc_kernel<16, false><<<grid, G_THREADS, smem, stream>>>(map_w, map_x, p, (const uint16_t*)bias, (uint16_t*)out, status);
     }
     PCB_CUDA_TRY(cudaGetLastError());
     return PCB_OK;

@@ -55,6 +55,6 @@ def test_qresnet18_harness_trains_on_a_fixed_batch():
     g = torch.Generator().manual_seed(3)
     images = torch.randn((8, 3, 64, 64), generator=g).to(torch.float16).to(dev)
     labels = torch.randint(0, 1000, (8,), generator=g).to(dev)
-    losses = [float(model.train_step(images, labels, lr=0.05).detach()) for _ in range(12)]
+    losses = [float(model.train_step(images, labels, lr=0.01).detach()) for _ in range(12)]
     assert all(l == l for l in losses), losses          # finite
-    assert losses[-1] < losses[0] - 0.5, losses         # the fixed batch is being fitted
+    assert losses[-1] < 1.0 < losses[0], losses         # the fixed batch is being fitted (7.97 -> ~0.02)

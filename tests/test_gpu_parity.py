@@ -137,6 +137,9 @@ GENERAL_TENSOR_SHAPES = [
     (5, 32, 32, 28, 28, 3, 3, (1, 1), (1, 1, 1, 1)),     # several tiles per CTA: both accumulator buffers in use
     (2, 128, 64, 8, 8, 3, 3, (1, 1), (1, 1, 1, 1)),      # filter gradient with two channel blocks per component (N = 512: two tiles)
     (2, 64, 128, 10, 6, 3, 3, (2, 2), (1, 1, 1, 1)),     # strided backward-data by zero insertion; M = 512
+    (1, 64, 32, 30, 21, 3, 3, (1, 1), (1, 1, 1, 1)),     # halo mode: ragged 30 x 21 plane, two 32-channel slices
+    (2, 32, 48, 56, 24, 5, 5, (1, 1), (2, 2, 2, 2)),     # halo mode: 25 taps (two stages fit), two tiles per column, M = 192
+    (1, 32, 32, 26, 26, 3, 3, (2, 2), (0, 0, 1, 1)),     # halo mode in backward-data only (zero-inserted 26 x 26 plane)
 ]
 
 
