@@ -10,6 +10,7 @@
  *   - Every tensor pointer is DEVICE memory, dense, in the reference's layouts:
  *       activations   [4*N, C, H, W]   component c of sample n at leading index c*N + n   (NCHW)
  *       conv filters  [4, Co, Ci, kh, kw]                                                 (OIHW)
+ *     (NHWC activations and OHWI / HWIO filters: see pcb_data_format / pcb_filter_layout)
  *       conv bias     [4, Co]
  *       dense input   [4*B, I];  dense filters [4, I, O] (IO) or [4, O, I] (OI);  dense bias [4, O]
  *     (reference: src/backend/tensor.hpp:501-545 TensorSplit, src/backend/conv2d_descriptor.hpp:39-42,
@@ -48,6 +49,13 @@ typedef enum { PCB_F32 = 0, PCB_F16 = 1, PCB_BF16 = 2 } pcb_dtype;
  * zero-initialised descriptor describes a quaternion layer; host layers translate from the reference's enum. */
 typedef enum { PCB_ALGEBRA_QUATERNION = 0, PCB_ALGEBRA_REAL = 1, PCB_ALGEBRA_COMPLEX = 2, PCB_ALGEBRA_GA_300 = 3 } pcb_algebra;
 
+/* Tensor layouts (reference: upstride::DataFormat / FilterLayout, src/backend/types.hpp:85-97). Zero is the layout
+ * this header describes above (NCHW activations, OIHW filters). The other layouts keep the component axis leading:
+ * NHWC activations [D*N, H, W, C]; OHWI filters [D, Co, kh, kw, Ci]; HWIO filters [D, kh, kw, Ci, Co]. They run on
+ * the CUDA-core kernels (the tensor-core kernels read NCHW / OIHW only). */
+typedef enum { PCB_LAYOUT_NCHW = 0, PCB_LAYOUT_NHWC = 1 } pcb_data_format;
+typedef enum { PCB_FILTER_OIHW = 0, PCB_FILTER_OHWI = 1, PCB_FILTER_HWIO = 2 } pcb_filter_layout;
+
 /* Formulation of the Hamilton product (reference: UPSTRIDE_MEMORY_OPTIMIZED, src/backend/backend.hpp:58):
  * 16 real products through the 4x4 signed block, or the factorised 8-product form. */
 typedef enum { PCB_VARIANT_16_PRODUCT = 0, PCB_VARIANT_8_PRODUCT = 1 } pcb_variant;
@@ -80,6 +88,8 @@ typedef struct {
     int32_t fp16_policy;            /* pcb_fp16_policy                                                */
     int32_t engine;                 /* pcb_engine                                                     */
     int32_t algebra;                /* pcb_algebra; n / ci / co count multivectors, tensors carry D*n etc. */
+    int32_t data_format;            /* pcb_data_format of x, y and their gradients                    */
+    int32_t filter_layout;          /* pcb_filter_layout of w and dw                                  */
 } pcb_conv2d_desc;
 
 /* Mirrors upstride::DenseFwdDescriptor / DenseBwdDescriptor (src/backend/dense_descriptor.hpp:11-131). */

@@ -28,7 +28,7 @@ class ConvDesc(ctypes.Structure):
     _fields_ = [(k, ctypes.c_int32) for k in (
         "dtype", "n", "ci", "co", "h", "w", "kh", "kw", "stride_h", "stride_w", "dilation_h", "dilation_w",
         "pad_top", "pad_left", "pad_bottom", "pad_right", "groups", "has_bias", "require_input_grad",
-        "real_valued_input", "variant", "fp16_policy", "engine", "algebra")]
+        "real_valued_input", "variant", "fp16_policy", "engine", "algebra", "data_format", "filter_layout")]
 
 
 class DenseDesc(ctypes.Structure):

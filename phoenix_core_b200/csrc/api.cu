@@ -47,6 +47,12 @@ int conv_geom(const pcb_conv2d_desc* d, Geom& g) {
     g.WO = out_size(d->w, d->kw, d->dilation_w, d->stride_w, d->pad_left, d->pad_right);
     if (g.HO <= 0 || g.WO <= 0) { set_error("empty convolution output (%d x %d)", g.HO, g.WO); return PCB_ERR_INVALID_ARGUMENT; }
     g.w_io = 0; g.dw_io = 0; g.real_in = d->real_valued_input ? 1 : 0; g.has_bias = d->has_bias ? 1 : 0;
+    if (d->data_format < PCB_LAYOUT_NCHW || d->data_format > PCB_LAYOUT_NHWC || d->filter_layout < PCB_FILTER_OIHW || d->filter_layout > PCB_FILTER_HWIO) {
+        set_error("unknown tensor layout (data format %d, filter layout %d)", d->data_format, d->filter_layout);
+        return PCB_ERR_INVALID_ARGUMENT;
+    }
+    set_conv_strides(g, d->data_format, d->filter_layout, g.Ci, g.Co);
+    g.plain = (d->data_format == PCB_LAYOUT_NCHW && d->filter_layout == PCB_FILTER_OIHW) ? 1 : 0;
     const long long xn = (long long)(g.real_in ? 1 : g.nc) * g.Nb * g.Ci * g.H * g.W;
     const long long yn = (long long)g.nc * g.Nb * g.Co * g.HO * g.WO;
     const long long wn = (long long)g.nc * g.Co * g.Ci * g.KH * g.KW;
@@ -68,6 +74,11 @@ int dense_geom(const pcb_dense_desc* d, Geom& g) {
     g.w_io = d->filter_oi ? 0 : 1;
     g.dw_io = 1;   // both reference backends emit the filter gradient input-major (src/backend/cudnn/dense.hpp:187-195)
     g.real_in = 0; g.has_bias = d->has_bias ? 1 : 0;
+    // x [D*B, I], y [D*B, O]; filters [D, I, O] or [D, O, I]; the filter gradient always [D, I, O]
+    g.xp = g.Ci; g.xc = 1; g.xh = g.xw = 0; g.yp = g.Co; g.yc = 1; g.yh = g.yw = 0;
+    g.wr = g.Ci * g.Co; g.wh = g.ww = 0; g.wo = g.w_io ? 1 : g.Ci; g.wi = g.w_io ? g.Co : 1;
+    g.dr = g.wr; g.dkh = g.dkw = 0; g.dco = 1; g.dci = g.Co;
+    g.bias_ld = g.Co; g.plain = 1;
     if ((long long)g.nc * g.Nb * g.Ci > MAX_NUMEL || (long long)g.nc * g.Nb * g.Co > MAX_NUMEL || (long long)g.nc * g.Ci * g.Co > MAX_NUMEL) {
         set_error("tensor too large for 32-bit element offsets");
         return PCB_ERR_TOO_LARGE;
@@ -84,7 +95,7 @@ constexpr size_t WS_HEADER = 256;
 
 size_t workspace_bytes(Pass pass, int dtype, int variant, int engine, const Geom& g) {
     size_t s = simt_scratch_bytes(pass, dtype, variant, g);
-    const size_t t = tensor_scratch_bytes(pass, dtype, variant, engine, g);
+    const size_t t = g.plain ? tensor_scratch_bytes(pass, dtype, variant, engine, g) : 0;
     if (t > s) s = t;
     return WS_HEADER + ((s + 255) / 256) * 256;
 }
@@ -92,7 +103,7 @@ size_t workspace_bytes(Pass pass, int dtype, int variant, int engine, const Geom
 int run_pass(Pass pass, int dtype, int variant, int engine, const Geom& g, const void* a, const void* b, const void* bias,
              void* out, void* workspace, size_t ws_bytes, cudaStream_t stream) {
     const size_t need = workspace_bytes(pass, dtype, variant, engine, g);
-    const bool needs_ws = need > WS_HEADER || tensor_path_supported(pass, dtype, variant, g);
+    const bool needs_ws = need > WS_HEADER || (g.plain && tensor_path_supported(pass, dtype, variant, g));
     if (needs_ws && (workspace == nullptr || ws_bytes < need)) {
         set_error("workspace of %zu bytes required, %zu given", need, workspace ? ws_bytes : (size_t)0);
         return PCB_ERR_WORKSPACE;
@@ -102,7 +113,7 @@ int run_pass(Pass pass, int dtype, int variant, int engine, const Geom& g, const
     // the tensor-core kernels move 16-byte chunks: every tensor (and the workspace) must be 16-byte aligned
     const bool aligned = ((reinterpret_cast<uintptr_t>(a) | reinterpret_cast<uintptr_t>(b) | reinterpret_cast<uintptr_t>(out) |
                            reinterpret_cast<uintptr_t>(workspace)) & 15u) == 0;
-    if (engine != PCB_ENGINE_SIMT && aligned && tensor_path_supported(pass, dtype, variant, g))
+    if (engine != PCB_ENGINE_SIMT && aligned && g.plain && tensor_path_supported(pass, dtype, variant, g))
         return tensor_launch(pass, dtype, variant, g, a, b, bias, out, scratch, status, stream);
     if (engine == PCB_ENGINE_TENSOR) {
         set_error("no tensor-core kernel for this problem");
@@ -267,7 +278,7 @@ int pcb_qconv2d_engine_for(const pcb_conv2d_desc* desc, int pass) {
     const int rc = conv_geom(desc, g);
     if (rc != PCB_OK) return rc;
     if (pass < 0 || pass > 2) { set_error("pass must be 0, 1 or 2"); return PCB_ERR_INVALID_ARGUMENT; }
-    if (desc->engine != PCB_ENGINE_SIMT && tensor_path_supported((Pass)pass, desc->dtype, variant_for(g, desc->variant), g)) return PCB_ENGINE_TENSOR;
+    if (desc->engine != PCB_ENGINE_SIMT && g.plain && tensor_path_supported((Pass)pass, desc->dtype, variant_for(g, desc->variant), g)) return PCB_ENGINE_TENSOR;
     return desc->engine == PCB_ENGINE_TENSOR ? (int)PCB_ERR_UNSUPPORTED : (int)PCB_ENGINE_SIMT;
 }
 
@@ -276,7 +287,7 @@ int pcb_qdense_engine_for(const pcb_dense_desc* desc, int pass) {
     const int rc = dense_geom(desc, g);
     if (rc != PCB_OK) return rc;
     if (pass < 0 || pass > 2) { set_error("pass must be 0, 1 or 2"); return PCB_ERR_INVALID_ARGUMENT; }
-    if (desc->engine != PCB_ENGINE_SIMT && tensor_path_supported((Pass)pass, desc->dtype, variant_for(g, desc->variant), g)) return PCB_ENGINE_TENSOR;
+    if (desc->engine != PCB_ENGINE_SIMT && g.plain && tensor_path_supported((Pass)pass, desc->dtype, variant_for(g, desc->variant), g)) return PCB_ENGINE_TENSOR;
     return desc->engine == PCB_ENGINE_TENSOR ? (int)PCB_ERR_UNSUPPORTED : (int)PCB_ENGINE_SIMT;
 }
 

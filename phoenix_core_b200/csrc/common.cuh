@@ -50,7 +50,37 @@ struct Geom {
     int dw_io;           // filter gradient written [r][ci][co]
     int real_in;         // x holds the real component only ([Nb, Ci, H, W])
     int has_bias;
+    // Element strides (the CUDA-core kernels address every tensor through them; the tensor-core kernels need `plain`).
+    //   x (and dx):  plane * xp + c * xc + h * xh + w * xw      with plane = comp * Nb + img
+    //   y (and dy):  plane * yp + c * yc + h * yh + w * yw
+    //   filters:     r * wr + co * wo + ci * wi + kh * wh + kw * ww;   filter gradient: the same with the d-prefixed strides
+    int xp, xc, xh, xw, yp, yc, yh, yw;
+    int wr, wo, wi, wh, ww, dr, dco, dci, dkh, dkw;
+    int bias_ld;         // bias is [components][bias_ld]
+    int plain;           // NCHW activations, OIHW (or dense) filters, one group: the layouts the tensor-core kernels read
 };
+
+enum { LAYOUT_NCHW = 0, LAYOUT_NHWC = 1 };
+enum { FILTER_OIHW = 0, FILTER_OHWI = 1, FILTER_HWIO = 2 };
+
+// Fills the strides for a convolution over full tensors of Ci_total / Co_total channels of which this geometry covers
+// g.Ci / g.Co (one group); filters hold g.Ci input channels per output channel.
+inline void set_conv_strides(Geom& g, int data_format, int filter_layout, int Ci_total, int Co_total) {
+    const int T = g.KH * g.KW;
+    if (data_format == LAYOUT_NCHW) {
+        g.xp = Ci_total * g.H * g.W; g.xc = g.H * g.W; g.xh = g.W; g.xw = 1;
+        g.yp = Co_total * g.HO * g.WO; g.yc = g.HO * g.WO; g.yh = g.WO; g.yw = 1;
+    } else {
+        g.xp = Ci_total * g.H * g.W; g.xc = 1; g.xh = g.W * Ci_total; g.xw = Ci_total;
+        g.yp = Co_total * g.HO * g.WO; g.yc = 1; g.yh = g.WO * Co_total; g.yw = Co_total;
+    }
+    g.wr = Co_total * g.Ci * T;
+    if (filter_layout == FILTER_OIHW)      { g.wo = g.Ci * T; g.wi = T; g.wh = g.KW; g.ww = 1; }
+    else if (filter_layout == FILTER_OHWI) { g.wo = T * g.Ci; g.wh = g.KW * g.Ci; g.ww = g.Ci; g.wi = 1; }
+    else                                   { g.wh = g.KW * g.Ci * Co_total; g.ww = g.Ci * Co_total; g.wi = Co_total; g.wo = 1; }
+    g.dr = g.wr; g.dco = g.wo; g.dci = g.wi; g.dkh = g.wh; g.dkw = g.ww;
+    g.bias_ld = Co_total;
+}
 
 template <typename T> struct DType;
 template <> struct DType<float> {

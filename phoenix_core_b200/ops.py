@@ -14,7 +14,7 @@ import torch
 
 from . import _lib
 from .context import Context
-from .descriptors import MULTIVECTOR_DIM, Algebra, DataFormat, FilterLayout
+from .descriptors import MULTIVECTOR_DIM, Algebra, DataFormat, FilterLayout, _dims, _filter_dims
 
 _DTYPES = {torch.float32: _lib.PCB_F32, torch.float16: _lib.PCB_F16, torch.bfloat16: _lib.PCB_BF16}
 
@@ -72,25 +72,33 @@ def _stream():
 _ALGEBRAS = {Algebra.QUATERNION: 0, Algebra.REAL: 1, Algebra.COMPLEX: 2, Algebra.GA_300: 3}
 
 
+_DATA_FORMATS = {DataFormat.NCHW: 0, DataFormat.NHWC: 1}
+_FILTER_LAYOUTS = {FilterLayout.OIHW: 0, FilterLayout.OHWI: 1, FilterLayout.HWIO: 2}
+
+
 def _conv_desc(descriptor, dtype, context, engine, has_bias=False, require_input_grad=False):
     algebra = descriptor.getAlgebra()
     dim = MULTIVECTOR_DIM[algebra]
-    off = 0 if algebra == Algebra.REAL else 1       # real filters carry no leading component axis
-    if descriptor.getDataFormat() != DataFormat.NCHW or descriptor.getFilterLayout() != FilterLayout.OIHW:
-        raise _lib.BackendError(_lib.PCB_ERR_UNSUPPORTED, "only NCHW activations with OIHW filters are implemented")
+    data_format, filter_layout = descriptor.getDataFormat(), descriptor.getFilterLayout()
+    if data_format not in _DATA_FORMATS or filter_layout not in _FILTER_LAYOUTS:
+        raise _lib.BackendError(_lib.PCB_ERR_UNSUPPORTED, "unsupported tensor layout for a convolution")
+    cd, hd, wd = _dims(data_format)                 # real filters carry no leading component axis: _filter_dims accounts for it
+    fo, fi, fh, fw = _filter_dims(filter_layout, algebra)
     ishape, fshape = descriptor.getInputShape(), descriptor.getFilterShape()
     real = descriptor.isRealValuedInput() and algebra != Algebra.REAL
     if not real and ishape[0] % dim != 0:
         raise ValueError("leading input dimension must be a multiple of %d (components stacked on the batch axis)" % dim)
-    if ishape[1] != fshape[off + 1] * descriptor.getGroups():
-        raise ValueError("input channels mismatch: %d vs %d" % (ishape[1], fshape[off + 1]))
+    if ishape[cd] != fshape[fi] * descriptor.getGroups():
+        raise ValueError("input channels mismatch: %d vs %d" % (ishape[cd], fshape[fi]))
     d = _lib.ConvDesc()
     d.dtype = _DTYPES[dtype]
     d.algebra = _ALGEBRAS[algebra]
+    d.data_format = _DATA_FORMATS[data_format]
+    d.filter_layout = _FILTER_LAYOUTS[filter_layout]
     d.n = ishape[0] if real else ishape[0] // dim
-    d.ci, d.co = fshape[off + 1], fshape[off]
-    d.h, d.w = ishape[2], ishape[3]
-    d.kh, d.kw = fshape[off + 2], fshape[off + 3]
+    d.ci, d.co = fshape[fi], fshape[fo]
+    d.h, d.w = ishape[hd], ishape[wd]
+    d.kh, d.kw = fshape[fh], fshape[fw]
     d.stride_h, d.stride_w = descriptor.getStride()
     d.dilation_h, d.dilation_w = descriptor.getDilation()
     d.pad_top, d.pad_left = descriptor.getPaddingBefore()

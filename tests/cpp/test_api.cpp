@@ -150,9 +150,17 @@ static void gpuTests() {
             denseFwd<Device, float>(device, device, input, filter, nullptr, output, descriptor);
             CHECK(same(output, {28, 10, 0, 0, 0, 0, 0, 0, -4, 20, -8, 40, -6, 30, 0, 0}));
         }
-        {   // unsupported layout: no CPU fallback
-            AllocatedTensor<Device, float> input(device, {4, 2, 2, 3}), kernel(device, {4, 2, 3, 1, 1}), output(device, {4, 2, 2, 2});
-            Conv2DFwdDescriptor descriptor(input.getShape(), kernel.getShape(), 1, 1, Padding::VALID, {}, 1, Algebra::QUATERNION, DataFormat::NHWC, FilterLayout::OIHW, false);
+        {   // real convolution, channels-last with an OHWI filter: the reference's known answer (tests/tests.cpp:438-480)
+            AllocatedTensor<Device, float> input(device, {1, 2, 2, 3}), kernel(device, {2, 1, 1, 3}), output(device, {1, 2, 2, 2});
+            input = {0, -1, 1, 0, 0, 2, 0, 0, 3, 1, 0, 4};
+            kernel = {1, 1, 1, 0, 0, 2};
+            Conv2DFwdDescriptor descriptor(input.getShape(), kernel.getShape(), 1, 1, Padding::VALID, {}, 1, Algebra::REAL, DataFormat::NHWC, FilterLayout::OHWI, false);
+            conv2DFwd<Device, float>(device, device, input, kernel, nullptr, output, descriptor);
+            CHECK(same(output, {0, 2, 2, 4, 3, 6, 5, 8}));
+        }
+        {   // grouped convolution: not built, and there is no CPU fallback
+            AllocatedTensor<Device, float> input(device, {4, 4, 2, 2}), kernel(device, {4, 2, 2, 1, 1}), output(device, {4, 2, 2, 2});
+            Conv2DFwdDescriptor descriptor(input.getShape(), kernel.getShape(), 1, 1, Padding::VALID, {}, 2, Algebra::QUATERNION, DataFormat::NCHW, FilterLayout::OIHW, false);
             CHECK_THROWS((conv2DFwd<Device, float>(device, device, input, kernel, nullptr, output, descriptor)), std::runtime_error);
         }
         {   // empty batch: forward is a no-op, backward zeroes the filter gradient

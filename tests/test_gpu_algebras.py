@@ -154,3 +154,74 @@ def test_engines_for_other_algebras(gpu):
                               dilation_w=1, pad_top=1, pad_left=1, pad_bottom=1, pad_right=1, groups=1, algebra=algebra)
             for p in (0, 1, 2):
                 assert L.pcb_qconv2d_engine_for(ctypes.byref(d), p) == _lib.ENGINE_TENSOR, (algebra, dtype, p)
+
+
+# ---- tensor layouts (reference: DataFormat / FilterLayout, src/backend/types.hpp:85-97) -------------------------
+def _to_layout(a, fmt):
+    """NCHW / OIHW numpy array -> the named layout (the component axis, if any, stays leading)."""
+    if fmt in ("NCHW", "OIHW"):
+        return np.ascontiguousarray(a)
+    lead = a.ndim - 4                       # 1 for filters with a component axis, 0 otherwise
+    perm = {"NHWC": (0, 2, 3, 1), "OHWI": (0, 2, 3, 1), "HWIO": (2, 3, 1, 0)}[fmt]
+    return np.ascontiguousarray(a.transpose(tuple(range(lead)) + tuple(lead + p for p in perm)))
+
+
+def _from_layout(a, fmt):
+    if fmt in ("NCHW", "OIHW"):
+        return a
+    lead = a.ndim - 4
+    inv = {"NHWC": (0, 3, 1, 2), "OHWI": (0, 3, 1, 2), "HWIO": (3, 2, 0, 1)}[fmt]
+    return np.ascontiguousarray(a.transpose(tuple(range(lead)) + tuple(lead + p for p in inv)))
+
+
+def test_reference_layout_kats_on_gpu(gpu):
+    """Real channels-last convolutions with OHWI and HWIO filters: the reference's known answers (tests/tests.cpp:438-547)."""
+    with open(GOLDEN) as f:
+        cases = [c for c in json.load(f)["cases"] if c["op"] == "conv2d_layout"]
+    assert len(cases) == 2
+    for case in cases:
+        x = np.asarray(case["x"], np.float32).reshape(case["x_shape"])
+        w = np.asarray(case["w"], np.float32).reshape(case["w_shape"])
+        want = np.asarray(case["y"], np.float32).reshape(case["y_shape"])
+        got = _run_layout_fwd(gpu, x, w, None, (1, 1), (0, 0, 0, 0), "f32", pcb.Algebra.REAL, case["data_format"], case["filter_layout"])
+        assert np.array_equal(got, want), case["name"]
+
+
+def _descs(xshape, wshape, stride, pad, algebra, data_format, filter_layout, use_bias, need_dx):
+    args = (xshape, wshape, stride, (1, 1), pcb.Padding.EXPLICIT, pad, 1, algebra, getattr(pcb.DataFormat, data_format),
+            getattr(pcb.FilterLayout, filter_layout))
+    return pcb.Conv2DFwdDescriptor(*args, use_bias), pcb.Conv2DBwdDescriptor(*args, need_dx)
+
+
+def _run_layout_fwd(gpu, x, w, b, stride, pad, dtype, algebra, data_format, filter_layout):
+    fwd, _ = _descs(x.shape, w.shape, stride, pad, algebra, data_format, filter_layout, b is not None, False)
+    y = torch.full(fwd.getOutputShape(), float("nan"), dtype=gpu.TORCH_DTYPES[dtype], device="cuda")
+    pcb.conv2DFwd(gpu.dev(x, dtype), gpu.dev(w, dtype), None if b is None else gpu.dev(b, dtype), y, fwd, gpu.context("16p"))
+    return gpu.host(y)
+
+
+@pytest.mark.parametrize("data_format,filter_layout", [("NHWC", "OHWI"), ("NHWC", "HWIO"), ("NCHW", "HWIO"), ("NHWC", "OIHW")])
+@pytest.mark.parametrize("name", ["quaternion", "complex"])
+@pytest.mark.parametrize("dtype,variant", [("f32", "16p"), ("f32", "8p"), ("f16", "16p")])
+def test_conv_layouts_vs_oracle(gpu, oracle, data_format, filter_layout, name, dtype, variant):
+    """The other activation / filter layouts against the oracle (which computes in NCHW / OIHW on permuted copies)."""
+    alg, code, D = ALGEBRAS[name]
+    n, ci, co, h, w_, kh, kw, stride, pad = 2, 5, 6, 9, 7, 3, 2, (2, 1), (1, 0, 1, 1)
+    x = gpu.rounded(uniform(101, (D * n, ci, h, w_)), dtype)
+    w = gpu.rounded(normal(102, (D, co, ci, kh, kw), std=0.2), dtype)
+    b = gpu.rounded(uniform(103, (D, co)), dtype)
+    ref = oracle.conv2d_fwd(x, w, b, stride, (1, 1), pad, code, 0)
+    dy = gpu.rounded(normal(104, ref.shape), dtype)
+    rdw, rdx = oracle.conv2d_bwd(x, w, dy, stride, (1, 1), pad, code, 0, True)
+    xl, wl, dyl = _to_layout(x, data_format), _to_layout(w, filter_layout), _to_layout(dy, data_format)
+    fwd, bwd = _descs(xl.shape, wl.shape, stride, pad, alg, data_format, filter_layout, True, True)
+    ctx = gpu.context(variant)
+    td = gpu.TORCH_DTYPES[dtype]
+    y = torch.full(fwd.getOutputShape(), float("nan"), dtype=td, device="cuda")
+    pcb.conv2DFwd(gpu.dev(xl, dtype), gpu.dev(wl, dtype), gpu.dev(b, dtype), y, fwd, ctx)
+    _check(_from_layout(gpu.host(y), data_format), ref, dtype, gpu, "y")
+    dw = torch.full(wl.shape, float("nan"), dtype=td, device="cuda")
+    dx = torch.full(xl.shape, float("nan"), dtype=td, device="cuda")
+    pcb.conv2DBwd(gpu.dev(xl, dtype), gpu.dev(wl, dtype), gpu.dev(dyl, dtype), dw, dx, bwd, ctx)
+    _check(_from_layout(gpu.host(dx), data_format), rdx, dtype, gpu, "dx")
+    _check(_from_layout(gpu.host(dw), filter_layout), rdw, dtype, gpu, "dw")
