@@ -62,6 +62,8 @@ SYMBOLS = {
     "pcb_check_device_status": (_i, [_vp, _sz, _vp]),
     "pcb_aux_bn_relu_fwd": (_i, [_i, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _i, _i, _i, ctypes.c_float, _i, _vp]),
     "pcb_aux_bn_relu_bwd": (_i, [_i, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _vp]),
+    "pcb_aux_maxpool3x3s2_fwd": (_i, [_i, _vp, _vp, _vp, _i, _i, _i, _vp]),
+    "pcb_aux_maxpool3x3s2_bwd": (_i, [_i, _vp, _vp, _vp, _i, _i, _i, _vp]),
 }
 
 _lib = None

@@ -1,3 +1,5 @@
+// Auxiliary kernels of the QResNet-18 harness: batch-norm (+ ReLU) and 3x3 stride-2 max pooling.
+//
 // Batch-norm (+ ReLU) over stacked hyper-complex activations [planes = D*N, C, H, W]: one mean / variance per channel,
 // shared by the D components. Auxiliary kernels of the QResNet-18 harness -- the reference has no normalisation layer
 // (its TensorFlow plugin relies on TensorFlow's); they exist because the framework kernels launch one block per channel
@@ -167,6 +169,62 @@ bn_apply_kernel(const T* __restrict__ x, const T* __restrict__ y, const T* __res
     }
 }
 
+// 3x3 stride-2 pad-1 max pooling over rows of H x W elements (one row per (plane, channel)); the forward pass keeps the
+// position of the maximum inside its window (0..8), the backward pass gathers: every input pixel looks at the at most four
+// windows that contain it, so there are no atomics.
+template <typename T>
+__global__ void __launch_bounds__(BN_THREADS)
+maxpool_fwd_kernel(const T* __restrict__ x, T* __restrict__ y, uint8_t* __restrict__ arg, size_t rows, int H, int W, int HO, int WO) {
+    const size_t total = rows * HO * WO;
+    for (size_t idx = (size_t)blockIdx.x * blockDim.x + threadIdx.x; idx < total; idx += (size_t)gridDim.x * blockDim.x) {
+        const int ow = (int)(idx % WO);
+        const int oh = (int)((idx / WO) % HO);
+        const size_t row = idx / ((size_t)WO * HO);
+        const T* src = x + row * H * W;
+        float best = -INFINITY;
+        int where = 0;
+#pragma unroll
+        for (int kh = 0; kh < 3; ++kh) {
+            const int ih = 2 * oh - 1 + kh;
+#pragma unroll
+            for (int kw = 0; kw < 3; ++kw) {
+                const int iw = 2 * ow - 1 + kw;
+                if ((unsigned)ih < (unsigned)H && (unsigned)iw < (unsigned)W) {
+                    const float v = DType<T>::load(src + ih * W + iw);
+                    if (v > best || (v != v)) { best = v; where = kh * 3 + kw; }
+                }
+            }
+        }
+        DType<T>::store(y + idx, best);
+        arg[idx] = (uint8_t)where;
+    }
+}
+
+template <typename T>
+__global__ void __launch_bounds__(BN_THREADS)
+maxpool_bwd_kernel(const T* __restrict__ dy, const uint8_t* __restrict__ arg, T* __restrict__ dx, size_t rows, int H, int W, int HO, int WO) {
+    const size_t total = rows * H * W;
+    for (size_t idx = (size_t)blockIdx.x * blockDim.x + threadIdx.x; idx < total; idx += (size_t)gridDim.x * blockDim.x) {
+        const int iw = (int)(idx % W);
+        const int ih = (int)((idx / W) % H);
+        const size_t row = idx / ((size_t)W * H);
+        const size_t obase = row * HO * WO;
+        float acc = 0.f;
+        // windows oh with 2*oh - 1 <= ih <= 2*oh + 1
+        for (int oh = ih >> 1; oh <= (ih + 1) >> 1; ++oh) {
+            if (oh >= HO) continue;
+            const int kh = ih - (2 * oh - 1);
+            for (int ow = iw >> 1; ow <= (iw + 1) >> 1; ++ow) {
+                if (ow >= WO) continue;
+                const int kw = iw - (2 * ow - 1);
+                const size_t o = obase + (size_t)oh * WO + ow;
+                if (arg[o] == kh * 3 + kw) acc += DType<T>::load(dy + o);
+            }
+        }
+        DType<T>::store(dx + idx, acc);
+    }
+}
+
 int blocks_for(size_t work) {
     int dev = 0, sms = 148;
     if (cudaGetDevice(&dev) == cudaSuccess) cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
@@ -244,6 +302,30 @@ int pcb_aux_bn_relu_bwd(int dtype, const void* x, const void* y, const void* dy,
     if (dtype == PCB_BF16) return bn_bwd_typed<__nv_bfloat16>((const __nv_bfloat16*)x, (const __nv_bfloat16*)y, (const __nv_bfloat16*)dy, gamma, mean, invstd, (__nv_bfloat16*)dx, dgamma, dbeta, scratch, planes, channels, hw, relu, (cudaStream_t)stream);
     set_error("batch-norm helper: 16-bit tensors only");
     return PCB_ERR_UNSUPPORTED;
+}
+
+int pcb_aux_maxpool3x3s2_fwd(int dtype, const void* x, void* y, void* argmax, int rows, int h, int w, void* stream) {
+    using namespace pcb;
+    if (!x || !y || !argmax || rows <= 0 || h <= 0 || w <= 0) { set_error("invalid max-pool arguments"); return PCB_ERR_INVALID_ARGUMENT; }
+    const int ho = (h - 1) / 2 + 1, wo = (w - 1) / 2 + 1;
+    const int blocks = blocks_for((size_t)rows * ho * wo);
+    if (dtype == PCB_F16) maxpool_fwd_kernel<__half><<<blocks, BN_THREADS, 0, (cudaStream_t)stream>>>((const __half*)x, (__half*)y, (uint8_t*)argmax, rows, h, w, ho, wo);
+    else if (dtype == PCB_BF16) maxpool_fwd_kernel<__nv_bfloat16><<<blocks, BN_THREADS, 0, (cudaStream_t)stream>>>((const __nv_bfloat16*)x, (__nv_bfloat16*)y, (uint8_t*)argmax, rows, h, w, ho, wo);
+    else { set_error("max-pool helper: 16-bit tensors only"); return PCB_ERR_UNSUPPORTED; }
+    PCB_CUDA_TRY(cudaGetLastError());
+    return PCB_OK;
+}
+
+int pcb_aux_maxpool3x3s2_bwd(int dtype, const void* dy, const void* argmax, void* dx, int rows, int h, int w, void* stream) {
+    using namespace pcb;
+    if (!dy || !dx || !argmax || rows <= 0 || h <= 0 || w <= 0) { set_error("invalid max-pool arguments"); return PCB_ERR_INVALID_ARGUMENT; }
+    const int ho = (h - 1) / 2 + 1, wo = (w - 1) / 2 + 1;
+    const int blocks = blocks_for((size_t)rows * h * w);
+    if (dtype == PCB_F16) maxpool_bwd_kernel<__half><<<blocks, BN_THREADS, 0, (cudaStream_t)stream>>>((const __half*)dy, (const uint8_t*)argmax, (__half*)dx, rows, h, w, ho, wo);
+    else if (dtype == PCB_BF16) maxpool_bwd_kernel<__nv_bfloat16><<<blocks, BN_THREADS, 0, (cudaStream_t)stream>>>((const __nv_bfloat16*)dy, (const uint8_t*)argmax, (__nv_bfloat16*)dx, rows, h, w, ho, wo);
+    else { set_error("max-pool helper: 16-bit tensors only"); return PCB_ERR_UNSUPPORTED; }
+    PCB_CUDA_TRY(cudaGetLastError());
+    return PCB_OK;
 }
 
 }  // extern "C"

@@ -115,6 +115,37 @@ class _BNReLUFn(torch.autograd.Function):
         return dx, dgamma, dbeta, None, None
 
 
+class _MaxPoolFn(torch.autograd.Function):
+    """3x3 stride-2 pad-1 max pooling on the library's helper kernels (the framework's backward kernel scatters with atomics and
+    takes three times as long as the forward pass). Harness glue."""
+
+    @staticmethod
+    def forward(ctx, x):
+        rows, h, w = x.shape[0] * x.shape[1], x.shape[2], x.shape[3]
+        y = torch.empty((x.shape[0], x.shape[1], (h - 1) // 2 + 1, (w - 1) // 2 + 1), dtype=x.dtype, device=x.device)
+        arg = torch.empty(y.shape, dtype=torch.uint8, device=x.device)
+        _lib.check(_lib.lib().pcb_aux_maxpool3x3s2_fwd(_DT[x.dtype], x.data_ptr(), y.data_ptr(), arg.data_ptr(), rows, h, w,
+                                                       torch.cuda.current_stream().cuda_stream))
+        ctx.save_for_backward(arg)
+        ctx.shape = x.shape
+        return y
+
+    @staticmethod
+    def backward(ctx, dy):
+        (arg,) = ctx.saved_tensors
+        dy = dy.contiguous()
+        dx = torch.empty(ctx.shape, dtype=dy.dtype, device=dy.device)
+        _lib.check(_lib.lib().pcb_aux_maxpool3x3s2_bwd(_DT[dy.dtype], dy.data_ptr(), arg.data_ptr(), dx.data_ptr(), ctx.shape[0] * ctx.shape[1],
+                                                       ctx.shape[2], ctx.shape[3], torch.cuda.current_stream().cuda_stream))
+        return dx
+
+
+def max_pool_3x3_s2(x):
+    if x.is_cuda and x.dtype in _DT and x.is_contiguous():
+        return _MaxPoolFn.apply(x)
+    return F.max_pool2d(x, 3, 2, 1)
+
+
 class BNReLU:
     def __init__(self, c, device, relu):
         self.weight = torch.ones(c, dtype=torch.float32, device=device, requires_grad=True)
@@ -284,7 +315,7 @@ class QResNet18:
         """images: [N, 3, H, W] real RGB (the quaternion with zero imaginary parts) -> logits [N, classes]."""
         n = images.shape[0]
         x = self.bn1(self.conv1(images.contiguous()))
-        x = F.max_pool2d(x, 3, 2, 1)
+        x = max_pool_3x3_s2(x)
         for blocks in self.stages:
             for blk in blocks:
                 idt = x

@@ -45,3 +45,23 @@ def test_bn_relu_helpers(shape, dtype, relu):
     assert err(xin.grad, rdx) < 5e-2
     assert err(gamma.grad, rdg) < tol
     assert err(beta.grad, rdb) < tol
+
+
+@pytest.mark.parametrize("shape", [(8, 16, 12, 12), (4, 5, 9, 7), (2, 3, 16, 11)])
+@pytest.mark.parametrize("dtype", [torch.float16, torch.bfloat16])
+def test_maxpool_helpers(shape, dtype):
+    if not torch.cuda.is_available():
+        pytest.skip("no CUDA device")
+    from phoenix_core_b200.qresnet import max_pool_3x3_s2
+    g = torch.Generator().manual_seed(9)
+    x = torch.randn(shape, generator=g).to(dtype).cuda()
+    xin = x.clone().requires_grad_(True)
+    y = max_pool_3x3_s2(xin)
+    xref = x.clone().float().requires_grad_(True)
+    yref = torch.nn.functional.max_pool2d(xref, 3, 2, 1)
+    assert y.shape == yref.shape and torch.equal(y.float(), yref)
+    dy = torch.randn(y.shape, generator=g).to(dtype).cuda()
+    y.backward(dy)
+    yref.backward(dy.float())
+    # random data has no ties inside a window, so the arg-max is unique
+    assert torch.allclose(xin.grad.float(), xref.grad, atol=2e-2, rtol=2e-2)
