@@ -13,72 +13,79 @@ namespace {
 
 constexpr int BN_THREADS = 256;
 
-template <typename T> struct Vec8;
-template <> struct Vec8<__half> {
-    static __device__ __forceinline__ void unpack(const uint4& v, float (&f)[8]) {
-        const __half2* h = reinterpret_cast<const __half2*>(&v);
+// V consecutive elements (8, 4 or 1) as floats.
+template <typename T, int V> struct VecIO;
+template <typename T> struct VecIO<T, 1> {
+    static __device__ __forceinline__ void load(const T* p, float (&f)[1]) { f[0] = DType<T>::load(p); }
+    static __device__ __forceinline__ void store(T* p, const float (&f)[1]) { DType<T>::store(p, f[0]); }
+};
+template <int V> struct VecIO<__half, V> {
+    static __device__ __forceinline__ void load(const __half* p, float (&f)[V]) {
+        alignas(16) __half2 h[V / 2];
+        if (V == 8) *reinterpret_cast<uint4*>(h) = __ldg(reinterpret_cast<const uint4*>(p));
+        else *reinterpret_cast<uint2*>(h) = __ldg(reinterpret_cast<const uint2*>(p));
 #pragma unroll
-        for (int i = 0; i < 4; ++i) { const float2 t = __half22float2(h[i]); f[2 * i] = t.x; f[2 * i + 1] = t.y; }
+        for (int i = 0; i < V / 2; ++i) { const float2 t = __half22float2(h[i]); f[2 * i] = t.x; f[2 * i + 1] = t.y; }
     }
-    static __device__ __forceinline__ uint4 pack(const float (&f)[8]) {
-        uint4 v;
-        __half2* h = reinterpret_cast<__half2*>(&v);
+    static __device__ __forceinline__ void store(__half* p, const float (&f)[V]) {
+        alignas(16) __half2 h[V / 2];
 #pragma unroll
-        for (int i = 0; i < 4; ++i) h[i] = __floats2half2_rn(f[2 * i], f[2 * i + 1]);
-        return v;
+        for (int i = 0; i < V / 2; ++i) h[i] = __floats2half2_rn(f[2 * i], f[2 * i + 1]);
+        if (V == 8) *reinterpret_cast<uint4*>(p) = *reinterpret_cast<const uint4*>(h);
+        else *reinterpret_cast<uint2*>(p) = *reinterpret_cast<const uint2*>(h);
     }
 };
-template <> struct Vec8<__nv_bfloat16> {
-    static __device__ __forceinline__ void unpack(const uint4& v, float (&f)[8]) {
-        const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&v);
+template <int V> struct VecIO<__nv_bfloat16, V> {
+    static __device__ __forceinline__ void load(const __nv_bfloat16* p, float (&f)[V]) {
+        alignas(16) __nv_bfloat162 h[V / 2];
+        if (V == 8) *reinterpret_cast<uint4*>(h) = __ldg(reinterpret_cast<const uint4*>(p));
+        else *reinterpret_cast<uint2*>(h) = __ldg(reinterpret_cast<const uint2*>(p));
 #pragma unroll
-        for (int i = 0; i < 4; ++i) { const float2 t = __bfloat1622float2(h[i]); f[2 * i] = t.x; f[2 * i + 1] = t.y; }
+        for (int i = 0; i < V / 2; ++i) { const float2 t = __bfloat1622float2(h[i]); f[2 * i] = t.x; f[2 * i + 1] = t.y; }
     }
-    static __device__ __forceinline__ uint4 pack(const float (&f)[8]) {
-        uint4 v;
-        __nv_bfloat162* h = reinterpret_cast<__nv_bfloat162*>(&v);
+    static __device__ __forceinline__ void store(__nv_bfloat16* p, const float (&f)[V]) {
+        alignas(16) __nv_bfloat162 h[V / 2];
 #pragma unroll
-        for (int i = 0; i < 4; ++i) h[i] = __floats2bfloat162_rn(f[2 * i], f[2 * i + 1]);
-        return v;
+        for (int i = 0; i < V / 2; ++i) h[i] = __floats2bfloat162_rn(f[2 * i], f[2 * i + 1]);
+        if (V == 8) *reinterpret_cast<uint4*>(p) = *reinterpret_cast<const uint4*>(h);
+        else *reinterpret_cast<uint2*>(p) = *reinterpret_cast<const uint2*>(h);
     }
+};
+template <> struct VecIO<__half, 1> {
+    static __device__ __forceinline__ void load(const __half* p, float (&f)[1]) { f[0] = DType<__half>::load(p); }
+    static __device__ __forceinline__ void store(__half* p, const float (&f)[1]) { DType<__half>::store(p, f[0]); }
+};
+template <> struct VecIO<__nv_bfloat16, 1> {
+    static __device__ __forceinline__ void load(const __nv_bfloat16* p, float (&f)[1]) { f[0] = DType<__nv_bfloat16>::load(p); }
+    static __device__ __forceinline__ void store(__nv_bfloat16* p, const float (&f)[1]) { DType<__nv_bfloat16>::store(p, f[0]); }
 };
 
 // Sums of two quantities per channel. MODE 0: (x, x*x). MODE 1: (g, g*x) with g = dy masked by y > 0 when relu.
-// Block (c, s): the planes s, s + S, ... of channel c; one atomic pair per block into sums[0..C) and sums[C..2C).
-template <typename T, int MODE, bool VEC>
+// Block (c, s): the planes s, s + S, ... of channel c, walked as one flat index space of V-element groups (so that small
+// rows, e.g. 7 x 7 planes, still occupy every thread); one atomic pair per block into sums[0..C) and sums[C..2C).
+template <typename T, int MODE, int V>
 __global__ void __launch_bounds__(BN_THREADS)
 bn_sums_kernel(const T* __restrict__ x, const T* __restrict__ y, const T* __restrict__ dy, float* __restrict__ sums, int planes, int C, int HW, int relu) {
     const int c = blockIdx.x, s = blockIdx.y, S = gridDim.y;
+    const int per_row = HW / V;
+    const int my_planes = s < planes ? (planes - s + S - 1) / S : 0;
     float a0 = 0.f, a1 = 0.f;
-    for (int pl = s; pl < planes; pl += S) {
-        const size_t row = ((size_t)pl * C + c) * HW;
-        if (VEC) {
-            for (int i = threadIdx.x; i < HW / 8; i += BN_THREADS) {
-                float fx[8];
-                Vec8<T>::unpack(__ldg(reinterpret_cast<const uint4*>(x + row) + i), fx);
-                if (MODE == 0) {
+    for (int j = threadIdx.x; j < my_planes * per_row; j += BN_THREADS) {
+        const int pi = j / per_row, i = j - pi * per_row;
+        const size_t off = ((size_t)(s + pi * S) * C + c) * HW + (size_t)i * V;
+        float fx[V];
+        VecIO<T, V>::load(x + off, fx);
+        if (MODE == 0) {
 #pragma unroll
-                    for (int e = 0; e < 8; ++e) { a0 += fx[e]; a1 = fmaf(fx[e], fx[e], a1); }
-                } else {
-                    float fg[8], fy[8];
-                    Vec8<T>::unpack(__ldg(reinterpret_cast<const uint4*>(dy + row) + i), fg);
-                    if (relu) Vec8<T>::unpack(__ldg(reinterpret_cast<const uint4*>(y + row) + i), fy);
-#pragma unroll
-                    for (int e = 0; e < 8; ++e) {
-                        const float g = (relu && !(fy[e] > 0.f)) ? 0.f : fg[e];
-                        a0 += g; a1 = fmaf(g, fx[e], a1);
-                    }
-                }
-            }
+            for (int e = 0; e < V; ++e) { a0 += fx[e]; a1 = fmaf(fx[e], fx[e], a1); }
         } else {
-            for (int i = threadIdx.x; i < HW; i += BN_THREADS) {
-                const float fx = DType<T>::load(x + row + i);
-                if (MODE == 0) { a0 += fx; a1 = fmaf(fx, fx, a1); }
-                else {
-                    float g = DType<T>::load(dy + row + i);
-                    if (relu && !(DType<T>::load(y + row + i) > 0.f)) g = 0.f;
-                    a0 += g; a1 = fmaf(g, fx, a1);
-                }
+            float fg[V], fy[V];
+            VecIO<T, V>::load(dy + off, fg);
+            if (relu) VecIO<T, V>::load(y + off, fy);
+#pragma unroll
+            for (int e = 0; e < V; ++e) {
+                const float g = (relu && !(fy[e] > 0.f)) ? 0.f : fg[e];
+                a0 += g; a1 = fmaf(g, fx[e], a1);
             }
         }
     }
@@ -125,47 +132,34 @@ __global__ void bn_bwd_finalize_kernel(const float* __restrict__ sums, const flo
 }
 
 // MODE 0: y = max(x*coef0 + coef1, 0 if relu).  MODE 1: dx = coef0*g + coef1*x + coef2 with g = dy masked by y > 0.
-template <typename T, int MODE, bool VEC>
+template <typename T, int MODE, int V>
 __global__ void __launch_bounds__(BN_THREADS)
 bn_apply_kernel(const T* __restrict__ x, const T* __restrict__ y, const T* __restrict__ dy, T* __restrict__ out, const float* __restrict__ coef,
                 size_t rows, int C, int HW, int relu) {
-    const int per_row = VEC ? HW / 8 : HW;
+    const int per_row = HW / V;
     const size_t total = rows * per_row;
     for (size_t idx = (size_t)blockIdx.x * blockDim.x + threadIdx.x; idx < total; idx += (size_t)gridDim.x * blockDim.x) {
         const size_t row = idx / per_row;
         const int i = (int)(idx - row * per_row);
         const int c = (int)(row % C);
         const float k0 = coef[c], k1 = coef[C + c], k2 = MODE == 1 ? coef[2 * C + c] : 0.f;
-        if (VEC) {
-            const size_t off = row * HW;
-            float fx[8], fo[8];
-            Vec8<T>::unpack(__ldg(reinterpret_cast<const uint4*>(x + off) + i), fx);
-            if (MODE == 0) {
+        const size_t off = row * HW + (size_t)i * V;
+        float fx[V], fo[V];
+        VecIO<T, V>::load(x + off, fx);
+        if (MODE == 0) {
 #pragma unroll
-                for (int e = 0; e < 8; ++e) { const float v = fmaf(fx[e], k0, k1); fo[e] = relu ? fmaxf(v, 0.f) : v; }
-            } else {
-                float fg[8], fy[8];
-                Vec8<T>::unpack(__ldg(reinterpret_cast<const uint4*>(dy + off) + i), fg);
-                if (relu) Vec8<T>::unpack(__ldg(reinterpret_cast<const uint4*>(y + off) + i), fy);
-#pragma unroll
-                for (int e = 0; e < 8; ++e) {
-                    const float g = (relu && !(fy[e] > 0.f)) ? 0.f : fg[e];
-                    fo[e] = fmaf(k0, g, fmaf(k1, fx[e], k2));
-                }
-            }
-            reinterpret_cast<uint4*>(out + off)[i] = Vec8<T>::pack(fo);
+            for (int e = 0; e < V; ++e) { const float v = fmaf(fx[e], k0, k1); fo[e] = relu ? fmaxf(v, 0.f) : v; }
         } else {
-            const size_t off = row * HW + i;
-            const float fx = DType<T>::load(x + off);
-            float v;
-            if (MODE == 0) { v = fmaf(fx, k0, k1); if (relu) v = fmaxf(v, 0.f); }
-            else {
-                float g = DType<T>::load(dy + off);
-                if (relu && !(DType<T>::load(y + off) > 0.f)) g = 0.f;
-                v = fmaf(k0, g, fmaf(k1, fx, k2));
+            float fg[V], fy[V];
+            VecIO<T, V>::load(dy + off, fg);
+            if (relu) VecIO<T, V>::load(y + off, fy);
+#pragma unroll
+            for (int e = 0; e < V; ++e) {
+                const float g = (relu && !(fy[e] > 0.f)) ? 0.f : fg[e];
+                fo[e] = fmaf(k0, g, fmaf(k1, fx[e], k2));
             }
-            DType<T>::store(out + off, v);
         }
+        VecIO<T, V>::store(out + off, fo);
     }
 }
 
@@ -232,22 +226,44 @@ int blocks_for(size_t work) {
     return (int)(need < cap ? (need ? need : 1) : cap);
 }
 
+// Widest vector (8, 4 or 1 elements) that rows of HW elements starting at these pointers allow.
+int vec_width(int HW, uintptr_t ptr_bits) {
+    if (HW % 8 == 0 && ptr_bits % 16 == 0) return 8;
+    if (HW % 4 == 0 && ptr_bits % 8 == 0) return 4;
+    return 1;
+}
+
+template <typename T, int MODE, int V>
+void bn_launch(const T* x, const T* y, const T* dy, T* out, float* scratch, float* coef, int planes, int C, int HW, int relu, bool sums,
+               cudaStream_t stream) {
+    if (sums) {
+        int S = (8 * 148 + C - 1) / C;
+        if (S > planes) S = planes;
+        if (S < 1) S = 1;
+        bn_sums_kernel<T, MODE, V><<<dim3(C, S), BN_THREADS, 0, stream>>>(x, y, dy, scratch, planes, C, HW, relu);
+    } else {
+        const size_t rows = (size_t)planes * C;
+        bn_apply_kernel<T, MODE, V><<<blocks_for(rows * (HW / V)), BN_THREADS, 0, stream>>>(x, y, dy, out, coef, rows, C, HW, relu);
+    }
+}
+
+template <typename T, int MODE>
+void bn_dispatch(int V, const T* x, const T* y, const T* dy, T* out, float* scratch, float* coef, int planes, int C, int HW, int relu, bool sums,
+                 cudaStream_t stream) {
+    if (V == 8) bn_launch<T, MODE, 8>(x, y, dy, out, scratch, coef, planes, C, HW, relu, sums, stream);
+    else if (V == 4) bn_launch<T, MODE, 4>(x, y, dy, out, scratch, coef, planes, C, HW, relu, sums, stream);
+    else bn_launch<T, MODE, 1>(x, y, dy, out, scratch, coef, planes, C, HW, relu, sums, stream);
+}
+
 template <typename T>
 int bn_fwd_typed(const T* x, const float* gamma, const float* beta, T* y, float* mean, float* invstd, float* scratch, int planes, int C, int HW,
                  float eps, int relu, cudaStream_t stream) {
-    const bool vec = HW % 8 == 0 && (reinterpret_cast<uintptr_t>(x) | reinterpret_cast<uintptr_t>(y)) % 16 == 0;
-    int S = (8 * 148 + C - 1) / C;
-    if (S > planes) S = planes;
-    if (S < 1) S = 1;
+    const int V = vec_width(HW, reinterpret_cast<uintptr_t>(x) | reinterpret_cast<uintptr_t>(y));
     PCB_CUDA_TRY(cudaMemsetAsync(scratch, 0, 2 * C * sizeof(float), stream));
-    const dim3 grid(C, S);
-    if (vec) bn_sums_kernel<T, 0, true><<<grid, BN_THREADS, 0, stream>>>(x, nullptr, nullptr, scratch, planes, C, HW, 0);
-    else bn_sums_kernel<T, 0, false><<<grid, BN_THREADS, 0, stream>>>(x, nullptr, nullptr, scratch, planes, C, HW, 0);
     float* coef = scratch + 2 * C;
+    bn_dispatch<T, 0>(V, x, nullptr, nullptr, nullptr, scratch, coef, planes, C, HW, 0, true, stream);
     bn_fwd_finalize_kernel<<<(C + 127) / 128, 128, 0, stream>>>(scratch, gamma, beta, mean, invstd, coef, C, (float)planes * HW, eps);
-    const size_t rows = (size_t)planes * C;
-    if (vec) bn_apply_kernel<T, 0, true><<<blocks_for(rows * (HW / 8)), BN_THREADS, 0, stream>>>(x, nullptr, nullptr, y, coef, rows, C, HW, relu);
-    else bn_apply_kernel<T, 0, false><<<blocks_for(rows * HW), BN_THREADS, 0, stream>>>(x, nullptr, nullptr, y, coef, rows, C, HW, relu);
+    bn_dispatch<T, 0>(V, x, nullptr, nullptr, y, scratch, coef, planes, C, HW, relu, false, stream);
     PCB_CUDA_TRY(cudaGetLastError());
     return PCB_OK;
 }
@@ -255,20 +271,13 @@ int bn_fwd_typed(const T* x, const float* gamma, const float* beta, T* y, float*
 template <typename T>
 int bn_bwd_typed(const T* x, const T* y, const T* dy, const float* gamma, const float* mean, const float* invstd, T* dx, float* dgamma, float* dbeta,
                  float* scratch, int planes, int C, int HW, int relu, cudaStream_t stream) {
-    const bool vec = HW % 8 == 0 && (reinterpret_cast<uintptr_t>(x) | reinterpret_cast<uintptr_t>(dy) | reinterpret_cast<uintptr_t>(dx) |
-                                     (relu ? reinterpret_cast<uintptr_t>(y) : 0)) % 16 == 0;
-    int S = (8 * 148 + C - 1) / C;
-    if (S > planes) S = planes;
-    if (S < 1) S = 1;
+    const int V = vec_width(HW, reinterpret_cast<uintptr_t>(x) | reinterpret_cast<uintptr_t>(dy) | reinterpret_cast<uintptr_t>(dx) |
+                                    (relu ? reinterpret_cast<uintptr_t>(y) : 0));
     PCB_CUDA_TRY(cudaMemsetAsync(scratch, 0, 2 * C * sizeof(float), stream));
-    const dim3 grid(C, S);
-    if (vec) bn_sums_kernel<T, 1, true><<<grid, BN_THREADS, 0, stream>>>(x, y, dy, scratch, planes, C, HW, relu);
-    else bn_sums_kernel<T, 1, false><<<grid, BN_THREADS, 0, stream>>>(x, y, dy, scratch, planes, C, HW, relu);
     float* coef = scratch + 2 * C;
+    bn_dispatch<T, 1>(V, x, y, dy, nullptr, scratch, coef, planes, C, HW, relu, true, stream);
     bn_bwd_finalize_kernel<<<(C + 127) / 128, 128, 0, stream>>>(scratch, gamma, mean, invstd, dgamma, dbeta, coef, C, (float)planes * HW);
-    const size_t rows = (size_t)planes * C;
-    if (vec) bn_apply_kernel<T, 1, true><<<blocks_for(rows * (HW / 8)), BN_THREADS, 0, stream>>>(x, y, dy, dx, coef, rows, C, HW, relu);
-    else bn_apply_kernel<T, 1, false><<<blocks_for(rows * HW), BN_THREADS, 0, stream>>>(x, y, dy, dx, coef, rows, C, HW, relu);
+    bn_dispatch<T, 1>(V, x, y, dy, dx, scratch, coef, planes, C, HW, relu, false, stream);
     PCB_CUDA_TRY(cudaGetLastError());
     return PCB_OK;
 }
