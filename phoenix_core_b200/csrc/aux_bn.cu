@@ -194,28 +194,40 @@ maxpool_fwd_kernel(const T* __restrict__ x, T* __restrict__ y, uint8_t* __restri
     }
 }
 
-template <typename T>
+// One thread per (row, input line, V consecutive input pixels): the windows that can contain them are the V/2 + 1 output
+// columns from iw0/2 on and the one or two output lines around ih; their arg-max bytes and gradients are read once.
+template <typename T, int V>
 __global__ void __launch_bounds__(BN_THREADS)
 maxpool_bwd_kernel(const T* __restrict__ dy, const uint8_t* __restrict__ arg, T* __restrict__ dx, size_t rows, int H, int W, int HO, int WO) {
-    const size_t total = rows * H * W;
+    const int per_line = W / V;
+    const size_t total = rows * H * per_line;
+    constexpr int NC = V == 1 ? 2 : V / 2 + 1;
     for (size_t idx = (size_t)blockIdx.x * blockDim.x + threadIdx.x; idx < total; idx += (size_t)gridDim.x * blockDim.x) {
-        const int iw = (int)(idx % W);
-        const int ih = (int)((idx / W) % H);
-        const size_t row = idx / ((size_t)W * H);
+        const int iw0 = (int)(idx % per_line) * V;
+        const int ih = (int)((idx / per_line) % H);
+        const size_t row = idx / ((size_t)per_line * H);
         const size_t obase = row * HO * WO;
-        float acc = 0.f;
-        // windows oh with 2*oh - 1 <= ih <= 2*oh + 1
+        float acc[V];
+#pragma unroll
+        for (int e = 0; e < V; ++e) acc[e] = 0.f;
         for (int oh = ih >> 1; oh <= (ih + 1) >> 1; ++oh) {
             if (oh >= HO) continue;
             const int kh = ih - (2 * oh - 1);
-            for (int ow = iw >> 1; ow <= (iw + 1) >> 1; ++ow) {
+            const int ow0 = iw0 >> 1;                      // window ow covers input columns 2*ow - 1 .. 2*ow + 1
+#pragma unroll
+            for (int j = 0; j < NC; ++j) {
+                const int ow = ow0 + j;
                 if (ow >= WO) continue;
-                const int kw = iw - (2 * ow - 1);
                 const size_t o = obase + (size_t)oh * WO + ow;
-                if (arg[o] == kh * 3 + kw) acc += DType<T>::load(dy + o);
+                const int a = arg[o];
+                if (a / 3 != kh) continue;
+                const int e = 2 * ow - 1 + a % 3 - iw0;    // position of the maximum relative to iw0
+                const float g = DType<T>::load(dy + o);
+#pragma unroll
+                for (int q = 0; q < V; ++q) if (q == e) acc[q] += g;
             }
         }
-        DType<T>::store(dx + idx, acc);
+        VecIO<T, V>::store(dx + (row * H + ih) * W + iw0, acc);
     }
 }
 
@@ -329,10 +341,17 @@ int pcb_aux_maxpool3x3s2_bwd(int dtype, const void* dy, const void* argmax, void
     using namespace pcb;
     if (!dy || !dx || !argmax || rows <= 0 || h <= 0 || w <= 0) { set_error("invalid max-pool arguments"); return PCB_ERR_INVALID_ARGUMENT; }
     const int ho = (h - 1) / 2 + 1, wo = (w - 1) / 2 + 1;
-    const int blocks = blocks_for((size_t)rows * h * w);
-    if (dtype == PCB_F16) maxpool_bwd_kernel<__half><<<blocks, BN_THREADS, 0, (cudaStream_t)stream>>>((const __half*)dy, (const uint8_t*)argmax, (__half*)dx, rows, h, w, ho, wo);
-    else if (dtype == PCB_BF16) maxpool_bwd_kernel<__nv_bfloat16><<<blocks, BN_THREADS, 0, (cudaStream_t)stream>>>((const __nv_bfloat16*)dy, (const uint8_t*)argmax, (__nv_bfloat16*)dx, rows, h, w, ho, wo);
-    else { set_error("max-pool helper: 16-bit tensors only"); return PCB_ERR_UNSUPPORTED; }
+    if (dtype != PCB_F16 && dtype != PCB_BF16) { set_error("max-pool helper: 16-bit tensors only"); return PCB_ERR_UNSUPPORTED; }
+    const bool wide = w % 8 == 0 && reinterpret_cast<uintptr_t>(dx) % 16 == 0;
+    const int blocks = blocks_for((size_t)rows * h * (wide ? w / 8 : w));
+    cudaStream_t st = (cudaStream_t)stream;
+    if (dtype == PCB_F16) {
+        if (wide) maxpool_bwd_kernel<__half, 8><<<blocks, BN_THREADS, 0, st>>>((const __half*)dy, (const uint8_t*)argmax, (__half*)dx, rows, h, w, ho, wo);
+        else maxpool_bwd_kernel<__half, 1><<<blocks, BN_THREADS, 0, st>>>((const __half*)dy, (const uint8_t*)argmax, (__half*)dx, rows, h, w, ho, wo);
+    } else {
+        if (wide) maxpool_bwd_kernel<__nv_bfloat16, 8><<<blocks, BN_THREADS, 0, st>>>((const __nv_bfloat16*)dy, (const uint8_t*)argmax, (__nv_bfloat16*)dx, rows, h, w, ho, wo);
+        else maxpool_bwd_kernel<__nv_bfloat16, 1><<<blocks, BN_THREADS, 0, st>>>((const __nv_bfloat16*)dy, (const uint8_t*)argmax, (__nv_bfloat16*)dx, rows, h, w, ho, wo);
+    }
     PCB_CUDA_TRY(cudaGetLastError());
     return PCB_OK;
 }
