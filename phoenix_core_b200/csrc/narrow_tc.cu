@@ -526,17 +526,25 @@ int narrow_tc_launch(Pass pass, int dtype, const Geom& g, const void* w, const v
     {
         const size_t total = (size_t)pl.LK * g.Nb * 2 * pl.Hp * pl.Wp;
         const int blocks = grid_cap(total, 256, 16), wblocks = grid_cap((size_t)taps * NM * Kp, 256, 8);
-        if (fmt == 0) {
+        const bool fast = !pl.s2d && pack_rows4_ok(act, pl.Win, pl.Wp, pl.pad_left, pl.ins_h, pl.ins_w);
+        const int fblocks = grid_cap(total / 4 + 1, 256, 16);
+        if (fast && fmt == 0) {
+            pack_rows4_kernel<__half><<<fblocks, 256, 0, stream>>>((const __half*)act, (__half*)xp, pl.LK * g.Nb, src_c, pl.Hin, pl.Win, pl.Hp, pl.Wp, 2,
+                                                                  pl.pad_top, pl.pad_left, 1);
+        } else if (fast) {
+            pack_rows4_kernel<__nv_bfloat16><<<fblocks, 256, 0, stream>>>((const __nv_bfloat16*)act, (__nv_bfloat16*)xp, pl.LK * g.Nb, src_c, pl.Hin, pl.Win,
+                                                                         pl.Hp, pl.Wp, 2, pl.pad_top, pl.pad_left, 1);
+        } else if (fmt == 0) {
             pack_planar_kernel<__half><<<blocks, 256, 0, stream>>>((const __half*)act, (__half*)xp, pl.LK * g.Nb, src_c, pl.Hin, pl.Win, pl.Hp, pl.Wp,
                                                                   2, pl.pad_top, pl.pad_left, pl.ins_h, pl.ins_w, pl.s2d);
-            pack_filters_planar_kernel<__half><<<wblocks, 256, 0, stream>>>((const __half*)w, (__half*)wexp, g.Co, g.Ci, taps, Kp,
-                                                                           pass == PASS_BWD_DATA ? 1 : 0, g.nc, g.ga, g.neg, pl.s2d, g.KH, g.KW, pl.KWe);
         } else {
             pack_planar_kernel<__nv_bfloat16><<<blocks, 256, 0, stream>>>((const __nv_bfloat16*)act, (__nv_bfloat16*)xp, pl.LK * g.Nb, src_c, pl.Hin,
                                                                          pl.Win, pl.Hp, pl.Wp, 2, pl.pad_top, pl.pad_left, pl.ins_h, pl.ins_w, pl.s2d);
-            pack_filters_planar_kernel<__nv_bfloat16><<<wblocks, 256, 0, stream>>>((const __nv_bfloat16*)w, (__nv_bfloat16*)wexp, g.Co, g.Ci, taps, Kp,
-                                                                                  pass == PASS_BWD_DATA ? 1 : 0, g.nc, g.ga, g.neg, pl.s2d, g.KH, g.KW, pl.KWe);
         }
+        if (fmt == 0) pack_filters_planar_kernel<__half><<<wblocks, 256, 0, stream>>>((const __half*)w, (__half*)wexp, g.Co, g.Ci, taps, Kp,
+                                                                                      pass == PASS_BWD_DATA ? 1 : 0, g.nc, g.ga, g.neg, pl.s2d, g.KH, g.KW, pl.KWe);
+        else pack_filters_planar_kernel<__nv_bfloat16><<<wblocks, 256, 0, stream>>>((const __nv_bfloat16*)w, (__nv_bfloat16*)wexp, g.Co, g.Ci, taps, Kp,
+                                                                                    pass == PASS_BWD_DATA ? 1 : 0, g.nc, g.ga, g.neg, pl.s2d, g.KH, g.KW, pl.KWe);
         PCB_CUDA_TRY(cudaGetLastError());
     }
     NParams p;
@@ -641,17 +649,21 @@ int narrow_filter_tc_launch(int dtype, const Geom& g, const void* dy, const void
     uint8_t* dyp = xp + f.xp_bytes;
     float* acc = reinterpret_cast<float*>(dyp + f.dyp_bytes);
     {
-        const int bx = grid_cap((size_t)f.LK * g.Nb * 2 * f.Hp * f.Wp, 256, 16);
-        const int by = grid_cap((size_t)g.nc * g.Nb * f.y_planes * f.HOp * f.WOp, 256, 16);
-        if (fmt == 0) {
-            pack_planar_kernel<__half><<<bx, 256, 0, stream>>>((const __half*)x, (__half*)xp, f.LK * g.Nb, g.Ci, g.H, g.W, f.Hp, f.Wp, 2, g.PT, g.PL, 1, 1, f.s2d);
-            pack_planar_kernel<__half><<<by, 256, 0, stream>>>((const __half*)dy, (__half*)dyp, g.nc * g.Nb, g.Co, g.HO, g.WO, f.HOp, f.WOp, f.y_planes, 0, 0, 1, 1);
-        } else {
-            pack_planar_kernel<__nv_bfloat16><<<bx, 256, 0, stream>>>((const __nv_bfloat16*)x, (__nv_bfloat16*)xp, f.LK * g.Nb, g.Ci, g.H, g.W, f.Hp, f.Wp, 2,
-                                                                     g.PT, g.PL, 1, 1, f.s2d);
-            pack_planar_kernel<__nv_bfloat16><<<by, 256, 0, stream>>>((const __nv_bfloat16*)dy, (__nv_bfloat16*)dyp, g.nc * g.Nb, g.Co, g.HO, g.WO, f.HOp,
-                                                                     f.WOp, f.y_planes, 0, 0, 1, 1);
-        }
+        // x: padded planar copy (space-to-depth for the stride-2 stem); dy: planar copy rounded up to whole tiles
+        auto stage = [&](const void* src, void* dst, int planes_in, int C, int H, int W, int Hp, int Wp, int groups, int pt, int pleft, int s2d) {
+            const size_t total = (size_t)planes_in * groups * Hp * Wp;
+            if (!s2d && pack_rows4_ok(src, W, Wp, pleft, 1, 1)) {
+                const int blocks = grid_cap(total / 4 + 1, 256, 16);
+                if (fmt == 0) pack_rows4_kernel<__half><<<blocks, 256, 0, stream>>>((const __half*)src, (__half*)dst, planes_in, C, H, W, Hp, Wp, groups, pt, pleft, 1);
+                else pack_rows4_kernel<__nv_bfloat16><<<blocks, 256, 0, stream>>>((const __nv_bfloat16*)src, (__nv_bfloat16*)dst, planes_in, C, H, W, Hp, Wp, groups, pt, pleft, 1);
+            } else {
+                const int blocks = grid_cap(total, 256, 16);
+                if (fmt == 0) pack_planar_kernel<__half><<<blocks, 256, 0, stream>>>((const __half*)src, (__half*)dst, planes_in, C, H, W, Hp, Wp, groups, pt, pleft, 1, 1, s2d);
+                else pack_planar_kernel<__nv_bfloat16><<<blocks, 256, 0, stream>>>((const __nv_bfloat16*)src, (__nv_bfloat16*)dst, planes_in, C, H, W, Hp, Wp, groups, pt, pleft, 1, 1, s2d);
+            }
+        };
+        stage(x, xp, f.LK * g.Nb, g.Ci, g.H, g.W, f.Hp, f.Wp, 2, g.PT, g.PL, f.s2d);
+        stage(dy, dyp, g.nc * g.Nb, g.Co, g.HO, g.WO, f.HOp, f.WOp, f.y_planes, 0, 0, 0);
         PCB_CUDA_TRY(cudaGetLastError());
         PCB_CUDA_TRY(cudaMemsetAsync(acc, 0, (size_t)g.nc * g.Co * f.Cie * taps * sizeof(float), stream));
     }

@@ -48,6 +48,55 @@ __device__ __forceinline__ void red_add_f32x4(float* addr, float a, float b, flo
     asm volatile("red.global.add.v4.f32 [%0], {%1, %2, %3, %4};" ::"l"(addr), "f"(a), "f"(b), "f"(c), "f"(d) : "memory");
 }
 
+// Staging copy of NCHW activations for the TMA-fed kernels, fast form (no zero insertion, W a multiple of 4, 8-byte
+// aligned rows): one thread moves 8 channels x 4 pixels -- eight 8-byte loads (a warp reads 256 contiguous bytes per
+// channel) and four 16-byte stores. Destination: channels-last xp[plane][hp][wp][Cp] (planar == 0) or planar
+// xp[plane][c / 8][hp][wp][8] (planar == 1), zero outside the image and for c >= C. The threads at the ends of a row
+// also write the padding columns.
+template <typename T>
+__global__ void pack_rows4_kernel(const T* __restrict__ x, T* __restrict__ xp, int planes, int C, int H, int W, int Hp, int Wp, int groups,
+                                  int pad_top, int pad_left, int planar) {
+    const int Wq = W / 4;
+    const size_t total = (size_t)planes * groups * Hp * Wq;
+    const int Cp = groups * 8;
+    for (size_t idx = (size_t)blockIdx.x * blockDim.x + threadIdx.x; idx < total; idx += (size_t)gridDim.x * blockDim.x) {
+        const int q = (int)(idx % Wq);
+        size_t rest = idx / Wq;
+        const int hp = (int)(rest % Hp); rest /= Hp;
+        const int grp = (int)(rest % groups);
+        const int plane = (int)(rest / groups);
+        const int ih = hp - pad_top;
+        const bool row_in = ih >= 0 && ih < H;
+        alignas(8) T v[8][4];
+#pragma unroll
+        for (int e = 0; e < 8; ++e) {
+            const int c = grp * 8 + e;
+            uint2 raw = make_uint2(0u, 0u);
+            if (row_in && c < C) raw = __ldg(reinterpret_cast<const uint2*>(x + (((size_t)plane * C + c) * H + ih) * W + 4 * q));
+            *reinterpret_cast<uint2*>(v[e]) = raw;
+        }
+        auto dst = [&](int wp) {
+            return planar ? xp + ((((size_t)plane * groups + grp) * Hp + hp) * Wp + wp) * 8 : xp + (((size_t)plane * Hp + hp) * Wp + wp) * Cp + grp * 8;
+        };
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+            alignas(16) T o[8];
+#pragma unroll
+            for (int e = 0; e < 8; ++e) o[e] = v[e][j];
+            *reinterpret_cast<uint4*>(dst(pad_left + 4 * q + j)) = *reinterpret_cast<const uint4*>(o);
+        }
+        const uint4 zero = make_uint4(0u, 0u, 0u, 0u);
+        if (q == 0)
+            for (int wp = 0; wp < pad_left && wp < Wp; ++wp) *reinterpret_cast<uint4*>(dst(wp)) = zero;
+        if (q == Wq - 1)
+            for (int wp = pad_left + W; wp < Wp; ++wp) *reinterpret_cast<uint4*>(dst(wp)) = zero;
+    }
+}
+// Whether pack_rows4_kernel applies.
+inline bool pack_rows4_ok(const void* x, int W, int Wp, int pad_left, int ins_h, int ins_w) {
+    return ins_h == 1 && ins_w == 1 && W % 4 == 0 && W >= 4 && pad_left >= 0 && pad_left + W <= Wp && reinterpret_cast<uintptr_t>(x) % 8 == 0;
+}
+
 typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*, const cuuint64_t*,
                                   const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
                                   CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
