@@ -389,15 +389,34 @@ def run(batch, steps, warmup, image=224, quiet=False):
     # end to end: host images -> device every step, loss read back
     sync()
     a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-    e2e_steps = min(steps, 5)
+    e2e_steps = min(steps, 8)
+    # the next batch is copied in on a side stream while this one trains; every step's loss goes back to pinned host memory
+    copy_stream = torch.cuda.Stream()
+    bufs = [(images, labels), (torch.empty_like(images), torch.empty_like(labels))]
+    ready = [torch.cuda.Event(), torch.cuda.Event()]
+    used = [torch.cuda.Event(), torch.cuda.Event()]
+    losses_host = torch.zeros(e2e_steps, dtype=torch.float32).pin_memory()
+
+    def prefetch(i):
+        with torch.cuda.stream(copy_stream):
+            if i >= 2:
+                copy_stream.wait_event(used[i & 1])
+            bufs[i & 1][0].copy_(host_images, non_blocking=True)
+            bufs[i & 1][1].copy_(host_labels, non_blocking=True)
+            ready[i & 1].record(copy_stream)
+
     a.record()
-    for _ in range(e2e_steps):
-        images.copy_(host_images, non_blocking=True)
-        labels.copy_(host_labels, non_blocking=True)
-        loss = model.train_step(images, labels, world)
-        loss_host = float(loss.detach())
+    prefetch(0)
+    for i in range(e2e_steps):
+        torch.cuda.current_stream().wait_event(ready[i & 1])
+        if i + 1 < e2e_steps:
+            prefetch(i + 1)
+        loss = model.train_step(bufs[i & 1][0], bufs[i & 1][1], world)
+        used[i & 1].record()
+        losses_host[i].copy_(loss.detach(), non_blocking=True)
     b.record()
     sync()
+    loss_host = float(losses_host[-1])
     e2e_ms = a.elapsed_time(b)
     if world > 1:
         t = torch.tensor([ms, e2e_ms], device=device)
