@@ -130,9 +130,10 @@ qconv_narrow_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_c
                 tc_fence_after_sync();
                 if (lane == 0) {
                     const uint32_t b0 = b_addr + s * p.stage_bytes;
+                    int kh = 0, kw = 0;
                     for (int tap = 0; tap < p.taps; ++tap) {
-                        const int kh = tap / p.KW, kw = tap - kh * p.KW;
                         const uint32_t shift = (uint32_t)(kh * p.DH * p.Wt + kw * p.DW) * 16;
+                        if (++kw == p.KW) { kw = 0; ++kh; }
                         mma_f16_ss(tmem_base + buf * 256, desc_plain(a_addr + (tap * p.LK + l) * NA_BYTES, NM * 16, 128),
                                    desc_plain(b0 + shift, p.plane_bytes, p.Wt * 16), idesc, (l > 0 || tap > 0) ? 1u : 0u);
                     }
@@ -346,17 +347,16 @@ qconv_narrow_filter_tc_kernel(const __grid_constant__ CUtensorMap map_dy, const 
     if (warp == 0) {
         if (lane == 0) {
             bool ok = true;
+            int img = step_beg / tiles_img, th = (step_beg - img * tiles_img) / p.tiles_w, tw = step_beg - img * tiles_img - th * p.tiles_w;
             for (int it = 0; it < n_steps && ok; ++it) {
                 const int s = it % NF_STAGES;
                 ok = mbar_wait_bounded(empty_bar + 8 * s, ((it / NF_STAGES) & 1) ^ 1, status, ST_N_PRODUCER);
                 if (!ok) break;
-                const int tile = step_beg + it;
-                const int img = tile / tiles_img, r = tile - img * tiles_img;
-                const int th = r / p.tiles_w, tw = r - th * p.tiles_w;
                 const uint32_t dst = tiles_addr + s * p.stage_bytes, bar = full_bar + 8 * s;
                 mbar_arrive_expect_tx(bar, p.y_bytes + p.x_bytes);
                 tma_load_5d(dst, &map_dy, tw * 64, th * p.PH, 0, img, 0, bar);                 // [d][plane][PH][8 px][8]
                 tma_load_5d(dst + p.y_bytes, &map_x, tw * 64, th * p.PH, 0, img, 0, bar);      // [l][plane][Ht][Wt][8]
+                if (++tw == p.tiles_w) { tw = 0; if (++th == p.tiles_h) { th = 0; ++img; } }
             }
         }
         __syncwarp();
@@ -370,9 +370,10 @@ qconv_narrow_filter_tc_kernel(const __grid_constant__ CUtensorMap map_dy, const 
             tc_fence_after_sync();
             if (lane == 0) {
                 const uint32_t y0 = tiles_addr + s * p.stage_bytes, x0 = y0 + p.y_bytes;
+                int kh = tap0 / p.KW, kw = tap0 - kh * p.KW;
                 for (int tl = 0; tl < n_taps; ++tl) {
-                    const int tap = tap0 + tl, kh = tap / p.KW, kw = tap - kh * p.KW;
                     const uint32_t shift = (uint32_t)(kh * p.DH * p.Wt + kw * p.DW) * 16;
+                    if (++kw == p.KW) { kw = 0; ++kh; }
                     for (int kk = 0; kk < p.PH / 2; ++kk)               // 16 pixels = two rows of the tile per MMA
                         mma_f16_ss(tmem_base + tl * ncols, desc_plain(y0 + kk * 256, 128, p.PH * 128),
                                    desc_plain(x0 + shift + kk * 2 * p.Wt * 16, p.Wt * 16, p.plane_bytes), idesc, (it > 0 || kk > 0) ? 1u : 0u);
