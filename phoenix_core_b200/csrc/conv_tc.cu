@@ -277,7 +277,7 @@ qconv_general_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_
 // One thread per (pixel, 8-channel group): reads are coalesced along w, writes are 16-byte vectors.
 template <typename T>
 __global__ void pack_activations_kernel(const T* __restrict__ x, T* __restrict__ xp, int planes /*4*Nb*/, int C, int H, int W,
-                                        int Hp, int Wp, int Cp, int pad_top, int pad_left, int ins_h = 1, int ins_w = 1) {
+                                        int Hp, int Wp, int Cp, int pad_top, int pad_left, int ins_h = 1, int ins_w = 1, int cb = 0, int Nb = 1) {
     const int groups = Cp / 8;
     const size_t total = (size_t)planes * Hp * Wp * groups;
     for (size_t idx = (size_t)blockIdx.x * blockDim.x + threadIdx.x; idx < total; idx += (size_t)gridDim.x * blockDim.x) {
@@ -304,22 +304,28 @@ __global__ void pack_activations_kernel(const T* __restrict__ x, T* __restrict__
             if (c < C && inside) v = x[(((size_t)plane * C + c) * H + ih) * W + iw];
             vals[e] = v;
         }
-        *reinterpret_cast<uint4*>(xp + (((size_t)plane * Hp + hp) * Wp + wp) * Cp + grp * 8) = *reinterpret_cast<const uint4*>(vals);
+        T* dst = xp + (((size_t)plane * Hp + hp) * Wp + wp) * Cp + grp * 8;
+        if (cb > 0) {   // blocks of cb channels, block index outermost: xp[comp * (Cp / cb) + c / cb][img][hp][wp][cb]
+            const int comp = plane / Nb, img = plane - comp * Nb, b = (grp * 8) / cb;
+            dst = xp + (((((size_t)comp * (Cp / cb) + b) * Nb + img) * Hp + hp) * Wp + wp) * cb + (grp * 8 - b * cb);
+        }
+        *reinterpret_cast<uint4*>(dst) = *reinterpret_cast<const uint4*>(vals);
     }
 }
 
 // Host dispatch of the activation staging: the 4-pixel form where it applies, the general form otherwise.
+// cb > 0 selects the channel-block layout of the filter-gradient kernels (Nb images per component).
 void stage_activations(int fmt, const void* src, void* dst, int planes, int C, int H, int W, int Hp, int Wp, int Cp, int pad_top, int pad_left,
-                       int ins_h, int ins_w, cudaStream_t stream) {
+                       int ins_h, int ins_w, cudaStream_t stream, int cb = 0, int Nb = 1) {
     const size_t total = (size_t)planes * Hp * Wp * (Cp / 8);
     if (pack_rows4_ok(src, W, Wp, pad_left, ins_h, ins_w)) {
         const int blocks = grid_cap(total / 4 + 1, 256, 16);
-        if (fmt == 0) pack_rows4_kernel<__half><<<blocks, 256, 0, stream>>>((const __half*)src, (__half*)dst, planes, C, H, W, Hp, Wp, Cp / 8, pad_top, pad_left, 0);
-        else pack_rows4_kernel<__nv_bfloat16><<<blocks, 256, 0, stream>>>((const __nv_bfloat16*)src, (__nv_bfloat16*)dst, planes, C, H, W, Hp, Wp, Cp / 8, pad_top, pad_left, 0);
+        if (fmt == 0) pack_rows4_kernel<__half><<<blocks, 256, 0, stream>>>((const __half*)src, (__half*)dst, planes, C, H, W, Hp, Wp, Cp / 8, pad_top, pad_left, 0, cb, Nb);
+        else pack_rows4_kernel<__nv_bfloat16><<<blocks, 256, 0, stream>>>((const __nv_bfloat16*)src, (__nv_bfloat16*)dst, planes, C, H, W, Hp, Wp, Cp / 8, pad_top, pad_left, 0, cb, Nb);
     } else {
         const int blocks = grid_cap(total, 256, 16);
-        if (fmt == 0) pack_activations_kernel<__half><<<blocks, 256, 0, stream>>>((const __half*)src, (__half*)dst, planes, C, H, W, Hp, Wp, Cp, pad_top, pad_left, ins_h, ins_w);
-        else pack_activations_kernel<__nv_bfloat16><<<blocks, 256, 0, stream>>>((const __nv_bfloat16*)src, (__nv_bfloat16*)dst, planes, C, H, W, Hp, Wp, Cp, pad_top, pad_left, ins_h, ins_w);
+        if (fmt == 0) pack_activations_kernel<__half><<<blocks, 256, 0, stream>>>((const __half*)src, (__half*)dst, planes, C, H, W, Hp, Wp, Cp, pad_top, pad_left, ins_h, ins_w, cb, Nb);
+        else pack_activations_kernel<__nv_bfloat16><<<blocks, 256, 0, stream>>>((const __nv_bfloat16*)src, (__nv_bfloat16*)dst, planes, C, H, W, Hp, Wp, Cp, pad_top, pad_left, ins_h, ins_w, cb, Nb);
     }
 }
 
@@ -373,7 +379,6 @@ struct FGParams {
     int tiles_w, tiles_h, tiles_n;
     int m_tiles, n_tiles, n_tile_cols;   // N columns per tile (multiple of 16, <= 256)
     int splits, steps_per_split;
-    int merged_a, merged_b;       // one TMA box brings all channel blocks of the tile (one block per component)
     int fmt;
     int LK;                       // components of x (1 for a real-valued input)
     int TPG;                      // x-major variant: taps stacked along M per work item
@@ -423,7 +428,7 @@ qconv_filter_general_tc_kernel(const __grid_constant__ CUtensorMap map_dy, const
         mbar_init(tmem_full, 1);
         fence_barrier_init();
     }
-    if (warp == 1) tmem_alloc(smem_u32(tmem_slot), 256);
+    if (warp == 1) tmem_alloc(smem_u32(tmem_slot), 512);
     tc_fence_before_sync();
     __syncthreads();
     tc_fence_after_sync();
@@ -431,11 +436,9 @@ qconv_filter_general_tc_kernel(const __grid_constant__ CUtensorMap map_dy, const
 
     if (warp == 0) {
         if (lane == 0) {
-            // channel-block coordinates of the tile's operand blocks and the running (tw, th, tn) of the pixel box:
-            // the loop below then issues its copies without a division
-            int a_c[GM / 16], a_comp[GM / 16], b_c[GN / 16], b_comp[GN / 16];
-            for (int b = 0; b < nblkA; ++b) { const int blk = blockA0 + b; a_c[b] = (blk % bpcA) * p.cbA; a_comp[b] = blk / bpcA; }
-            for (int b = 0; b < nblkB; ++b) { const int blk = blockB0 + b; b_c[b] = (blk % bpcB) * p.cbB; b_comp[b] = blk / bpcB; }
+            // one copy per operand and stage (the staged tensors keep the channel-block index outermost, so the blocks of
+            // a tile are one box even across components), and a running (tw, th, tn) of the pixel box: the thread that
+            // issues the copies runs no division in this loop -- at a few hundred cycles per copy it used to bound the kernel
             int tw = step_beg % p.tiles_w, th = (step_beg / p.tiles_w) % p.tiles_h, tn = step_beg / (p.tiles_w * p.tiles_h);
             int s = 0, phase = 1;
             bool ok = true;
@@ -447,17 +450,8 @@ qconv_filter_general_tc_kernel(const __grid_constant__ CUtensorMap map_dy, const
                 if (++tw == p.tiles_w) { tw = 0; if (++th == p.tiles_h) { th = 0; ++tn; } }
                 if (++s == F_STAGES) { s = 0; phase ^= 1; }
                 mbar_arrive_expect_tx(bar, a_bytes + b_bytes);
-                if (p.merged_a) {
-                    tma_load_5d(a_dst, &map_dy, 0, ow0, oh0, n0, blockA0, bar);
-                } else {
-                    for (int b = 0; b < nblkA; ++b) tma_load_5d(a_dst + b * blkA_bytes, &map_dy, a_c[b], ow0, oh0, n0, a_comp[b], bar);
-                }
-                const int wp0 = ow0 * p.SW + kw * p.DW, hp0 = oh0 * p.SH + kh * p.DH;
-                if (p.merged_b) {
-                    tma_load_5d(b_dst, &map_x, 0, wp0, hp0, n0, blockB0, bar);
-                } else {
-                    for (int b = 0; b < nblkB; ++b) tma_load_5d(b_dst + b * blkB_bytes, &map_x, b_c[b], wp0, hp0, n0, b_comp[b], bar);
-                }
+                tma_load_5d(a_dst, &map_dy, 0, ow0, oh0, n0, blockA0, bar);
+                tma_load_5d(b_dst, &map_x, 0, ow0 * p.SW + kw * p.DW, oh0 * p.SH + kh * p.DH, n0, blockB0, bar);
             }
         }
         __syncwarp();
@@ -471,10 +465,12 @@ qconv_filter_general_tc_kernel(const __grid_constant__ CUtensorMap map_dy, const
             tc_fence_after_sync();
             if (lane == 0) {
                 const uint32_t a_addr = tiles_addr + s * F_STAGE, b_addr = a_addr + GM * FK * 2;
+                // consecutive MMAs alternate between two accumulators (summed by the epilogue): back-to-back MMAs into one
+                // accumulator run at about two thirds of the rate of independent ones
 #pragma unroll
                 for (int j = 0; j < FK / 16; ++j)
-                    mma_f16_ss(tmem_base, make_desc_mn_blocks(a_addr + j * 16 * p.cbA * 2, p.cbA, blkA_bytes),
-                               make_desc_mn_blocks(b_addr + j * 16 * p.cbB * 2, p.cbB, blkB_bytes), idesc, (it > 0 || j > 0) ? 1u : 0u);
+                    mma_f16_ss(tmem_base + (j & 1) * GN, make_desc_mn_blocks(a_addr + j * 16 * p.cbA * 2, p.cbA, blkA_bytes),
+                               make_desc_mn_blocks(b_addr + j * 16 * p.cbB * 2, p.cbB, blkB_bytes), idesc, (it > 0 || j > 1) ? 1u : 0u);
                 mma_commit(empty_bar + 8 * s);
                 if (it == n_steps - 1) mma_commit(tmem_full);
             }
@@ -499,10 +495,13 @@ qconv_filter_general_tc_kernel(const __grid_constant__ CUtensorMap map_dy, const
             for (int cb = 0; cb < 4; ++cb) {
                 const int col0 = chalf * 128 + cb * 32;
                 if (col0 >= p.n_tile_cols) break;                         // warp-uniform
-                uint32_t v[32];
+                uint32_t v[32], u[32];
                 tmem_ld_32x32b_x32(tmem_base + ((uint32_t)(q * 32) << 16) + col0, v);
+                tmem_ld_32x32b_x32(tmem_base + ((uint32_t)(q * 32) << 16) + GN + col0, u);
                 tmem_ld_wait();
                 if (!row_ok) continue;
+#pragma unroll
+                for (int e = 0; e < 32; ++e) v[e] = __float_as_uint(__uint_as_float(v[e]) + __uint_as_float(u[e]));
 #pragma unroll
                 for (int g4 = 0; g4 < 8; ++g4) {
                     const int col = col0 + g4 * 4;                        // 4 consecutive columns share (l, channel block)
@@ -526,7 +525,7 @@ qconv_filter_general_tc_kernel(const __grid_constant__ CUtensorMap map_dy, const
     }
     tc_fence_before_sync();
     __syncthreads();
-    if (warp == 1) tmem_dealloc(tmem_base, 256);
+    if (warp == 1) tmem_dealloc(tmem_base, 512);
 }
 
 // ---------------------------------------------------------------------------------------------------
@@ -562,7 +561,7 @@ qconv_filter_xmajor_tc_kernel(const __grid_constant__ CUtensorMap map_x, const _
         mbar_init(tmem_full, 1);
         fence_barrier_init();
     }
-    if (warp == 1) tmem_alloc(smem_u32(tmem_slot), 256);
+    if (warp == 1) tmem_alloc(smem_u32(tmem_slot), 512);
     tc_fence_before_sync();
     __syncthreads();
     tc_fence_after_sync();
@@ -606,9 +605,9 @@ qconv_filter_xmajor_tc_kernel(const __grid_constant__ CUtensorMap map_x, const _
             if (lane == 0) {
                 const uint32_t a_addr = tiles_addr + s * F_STAGE, b_addr = a_addr + GM * FK * 2;
 #pragma unroll
-                for (int j = 0; j < FK / 16; ++j)
-                    mma_f16_ss(tmem_base, make_desc_mn_blocks(a_addr + j * 16 * p.cbB * 2, p.cbB, blkX_bytes),
-                               make_desc_mn_blocks(b_addr + j * 16 * p.cbA * 2, p.cbA, blkY_bytes), idesc, (it > 0 || j > 0) ? 1u : 0u);
+                for (int j = 0; j < FK / 16; ++j)           // two accumulators in turn, as in the general kernel
+                    mma_f16_ss(tmem_base + (j & 1) * GN, make_desc_mn_blocks(a_addr + j * 16 * p.cbB * 2, p.cbB, blkX_bytes),
+                               make_desc_mn_blocks(b_addr + j * 16 * p.cbA * 2, p.cbA, blkY_bytes), idesc, (it > 0 || j > 1) ? 1u : 0u);
                 mma_commit(empty_bar + 8 * s);
                 if (it == n_steps - 1) mma_commit(tmem_full);
             }
@@ -632,8 +631,9 @@ qconv_filter_xmajor_tc_kernel(const __grid_constant__ CUtensorMap map_x, const _
             for (int cb = 0; cb < 4; ++cb) {
                 const int col0 = chalf * 128 + cb * 32;
                 if (col0 >= n_cols) break;
-                uint32_t v[32];
+                uint32_t v[32], u[32];
                 tmem_ld_32x32b_x32(tmem_base + ((uint32_t)(q * 32) << 16) + col0, v);
+                tmem_ld_32x32b_x32(tmem_base + ((uint32_t)(q * 32) << 16) + GN + col0, u);
                 tmem_ld_wait();
                 if (!row_ok) continue;
 #pragma unroll
@@ -641,7 +641,7 @@ qconv_filter_xmajor_tc_kernel(const __grid_constant__ CUtensorMap map_x, const _
                     const int col = col0 + e;
                     const int d = col / p.cbA, co = col - d * p.cbA;
                     if (col < n_cols && co < p.Co) {
-                        const float val = __uint_as_float(v[e]);
+                        const float val = __uint_as_float(v[e]) + __uint_as_float(u[e]);
                         atomicAdd(tap_base + (size_t)alg_pair(p.ga, l, d) * comp_stride + (size_t)co * p.Ci, alg_negative(p.neg, l, d) ? -val : val);
                     }
                 }
@@ -650,7 +650,7 @@ qconv_filter_xmajor_tc_kernel(const __grid_constant__ CUtensorMap map_x, const _
     }
     tc_fence_before_sync();
     __syncthreads();
-    if (warp == 1) tmem_dealloc(tmem_base, 256);
+    if (warp == 1) tmem_dealloc(tmem_base, 512);
 }
 
 // scratch [tap][r][co][ci] fp32 -> dw [r][co][ci][tap] in the tensor type
@@ -901,8 +901,8 @@ int conv_filter_tc_launch(int dtype, const Geom& g, const void* dy, const void* 
         const size_t cap = (size_t)sm_count() * 16;
         const int bx = (int)((tx + 255) / 256 < cap ? (tx + 255) / 256 : cap), by = (int)((ty + 255) / 256 < cap ? (ty + 255) / 256 : cap);
         (void)bx; (void)by;
-        stage_activations(fmt, x, xp, lk * g.Nb, g.Ci, g.H, g.W, f.Hp, f.Wp, f.Cip, g.PT, g.PL, 1, 1, stream);
-        stage_activations(fmt, dy, dyp, g.nc * g.Nb, g.Co, g.HO, g.WO, g.HO, g.WO, f.Cop, 0, 0, 1, 1, stream);
+        stage_activations(fmt, x, xp, lk * g.Nb, g.Ci, g.H, g.W, f.Hp, f.Wp, f.Cip, g.PT, g.PL, 1, 1, stream, channel_block(f.Cip), g.Nb);
+        stage_activations(fmt, dy, dyp, g.nc * g.Nb, g.Co, g.HO, g.WO, g.HO, g.WO, f.Cop, 0, 0, 1, 1, stream, channel_block(f.Cop), g.Nb);
         PCB_CUDA_TRY(cudaGetLastError());
         PCB_CUDA_TRY(cudaMemsetAsync(acc, 0, (size_t)g.nc * g.Co * g.Ci * taps * sizeof(float), stream));
     }
@@ -926,8 +926,6 @@ int conv_filter_tc_launch(int dtype, const Geom& g, const void* dy, const void* 
     p.m_tiles = (m_cols + GM - 1) / GM;
     p.n_tiles = (n_cols + GN - 1) / GN;
     p.n_tile_cols = n_cols < GN ? n_cols : GN;           // 4*Cip is a multiple of 64; tiles of a multi-tile problem are full or padded by zero blocks
-    p.merged_a = (f.Cop == p.cbA) ? 1 : 0;
-    p.merged_b = (f.Cip == p.cbB) ? 1 : 0;
     p.LK = g.real_in ? 1 : g.nc;
     const bool xmajor = filter_xmajor(g, f);
     p.TPG = xmajor ? GM / (p.LK * p.cbB) : 1;
@@ -942,23 +940,24 @@ int conv_filter_tc_launch(int dtype, const Geom& g, const void* dy, const void* 
     const CUtensorMapDataType dt = fmt == 0 ? CU_TENSOR_MAP_DATA_TYPE_FLOAT16 : CU_TENSOR_MAP_DATA_TYPE_BFLOAT16;
     auto swz = [](int cb) { return cb == 64 ? CU_TENSOR_MAP_SWIZZLE_128B : (cb == 32 ? CU_TENSOR_MAP_SWIZZLE_64B : CU_TENSOR_MAP_SWIZZLE_32B); };
     alignas(64) CUtensorMap map_dy, map_x;
+    // staged tensors: [component * blocks per component + channel block][image][h][w][cb channels]; the last box extent is
+    // the number of channel blocks one tile takes (blocks past the end read as zeros)
     {
-        const cuuint64_t dims[5] = {(cuuint64_t)f.Cop, (cuuint64_t)g.WO, (cuuint64_t)g.HO, (cuuint64_t)g.Nb, (cuuint64_t)g.nc};
-        const cuuint64_t strides[4] = {(cuuint64_t)f.Cop * 2, (cuuint64_t)g.WO * f.Cop * 2, (cuuint64_t)g.HO * g.WO * f.Cop * 2,
-                                       (cuuint64_t)g.Nb * g.HO * g.WO * f.Cop * 2};
-        const cuuint32_t box[5] = {(cuuint32_t)p.cbA, (cuuint32_t)p.PW, (cuuint32_t)p.PH, (cuuint32_t)p.PN,
-                                   (cuuint32_t)(xmajor ? g.nc : (p.merged_a ? GM / p.cbA : 1))};
+        const cuuint64_t dims[5] = {(cuuint64_t)p.cbA, (cuuint64_t)g.WO, (cuuint64_t)g.HO, (cuuint64_t)g.Nb, (cuuint64_t)(g.nc * (f.Cop / p.cbA))};
+        const cuuint64_t strides[4] = {(cuuint64_t)p.cbA * 2, (cuuint64_t)g.WO * p.cbA * 2, (cuuint64_t)g.HO * g.WO * p.cbA * 2,
+                                       (cuuint64_t)g.Nb * g.HO * g.WO * p.cbA * 2};
+        const cuuint32_t box[5] = {(cuuint32_t)p.cbA, (cuuint32_t)p.PW, (cuuint32_t)p.PH, (cuuint32_t)p.PN, (cuuint32_t)(xmajor ? g.nc : GM / p.cbA)};
         const cuuint32_t es[5] = {1, 1, 1, 1, 1};
         const CUresult r = encode(&map_dy, dt, 5, dyp, dims, strides, box, es, CU_TENSOR_MAP_INTERLEAVE_NONE, swz(p.cbA),
                                   CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
         if (r != CUDA_SUCCESS) { set_error("cuTensorMapEncodeTiled (dy) failed with code %d", (int)r); return PCB_ERR_CUDA; }
     }
     {
-        const cuuint64_t dims[5] = {(cuuint64_t)f.Cip, (cuuint64_t)f.Wp, (cuuint64_t)f.Hp, (cuuint64_t)g.Nb, (cuuint64_t)p.LK};
-        const cuuint64_t strides[4] = {(cuuint64_t)f.Cip * 2, (cuuint64_t)f.Wp * f.Cip * 2, (cuuint64_t)f.Hp * f.Wp * f.Cip * 2,
-                                       (cuuint64_t)g.Nb * f.Hp * f.Wp * f.Cip * 2};
+        const cuuint64_t dims[5] = {(cuuint64_t)p.cbB, (cuuint64_t)f.Wp, (cuuint64_t)f.Hp, (cuuint64_t)g.Nb, (cuuint64_t)(p.LK * (f.Cip / p.cbB))};
+        const cuuint64_t strides[4] = {(cuuint64_t)p.cbB * 2, (cuuint64_t)f.Wp * p.cbB * 2, (cuuint64_t)f.Hp * f.Wp * p.cbB * 2,
+                                       (cuuint64_t)g.Nb * f.Hp * f.Wp * p.cbB * 2};
         const cuuint32_t box[5] = {(cuuint32_t)p.cbB, (cuuint32_t)((p.PW - 1) * g.SW + 1), (cuuint32_t)((p.PH - 1) * g.SH + 1), (cuuint32_t)p.PN,
-                                   (cuuint32_t)(xmajor ? p.LK : (p.merged_b ? p.n_tile_cols / p.cbB : 1))};
+                                   (cuuint32_t)(xmajor ? p.LK : p.n_tile_cols / p.cbB)};
         const cuuint32_t es[5] = {1, (cuuint32_t)g.SW, (cuuint32_t)g.SH, 1, 1};
         const CUresult r = encode(&map_x, dt, 5, xp, dims, strides, box, es, CU_TENSOR_MAP_INTERLEAVE_NONE, swz(p.cbB),
                                   CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);

@@ -50,12 +50,14 @@ __device__ __forceinline__ void red_add_f32x4(float* addr, float a, float b, flo
 
 // Staging copy of NCHW activations for the TMA-fed kernels, fast form (no zero insertion, W a multiple of 4, 8-byte
 // aligned rows): one thread moves 8 channels x 4 pixels -- eight 8-byte loads (a warp reads 256 contiguous bytes per
-// channel) and four 16-byte stores. Destination: channels-last xp[plane][hp][wp][Cp] (planar == 0) or planar
-// xp[plane][c / 8][hp][wp][8] (planar == 1), zero outside the image and for c >= C. The threads at the ends of a row
-// also write the padding columns.
+// channel) and four 16-byte stores. Destination: channels-last xp[plane][hp][wp][Cp] (planar == 0), planar
+// xp[plane][c / 8][hp][wp][8] (planar == 1), or -- cb > 0 -- blocks of cb channels with the block index outermost,
+// xp[comp * (Cp / cb) + c / cb][img][hp][wp][cb] where plane = comp * Nb + img (one TMA box can then span the channel
+// blocks of several components). Zero outside the image and for c >= C. The threads at the ends of a row also write
+// the padding columns.
 template <typename T>
 __global__ void pack_rows4_kernel(const T* __restrict__ x, T* __restrict__ xp, int planes, int C, int H, int W, int Hp, int Wp, int groups,
-                                  int pad_top, int pad_left, int planar) {
+                                  int pad_top, int pad_left, int planar, int cb = 0, int Nb = 1) {
     const int Wq = W / 4;
     const size_t total = (size_t)planes * groups * Hp * Wq;
     const int Cp = groups * 8;
@@ -75,7 +77,15 @@ __global__ void pack_rows4_kernel(const T* __restrict__ x, T* __restrict__ xp, i
             if (row_in && c < C) raw = __ldg(reinterpret_cast<const uint2*>(x + (((size_t)plane * C + c) * H + ih) * W + 4 * q));
             *reinterpret_cast<uint2*>(v[e]) = raw;
         }
+        size_t blk_plane = 0;                       // (block, image) index and channel offset inside the block
+        int c_lo = 0;
+        if (cb > 0) {
+            const int comp = plane / Nb, img = plane - comp * Nb, b = (grp * 8) / cb;
+            c_lo = grp * 8 - b * cb;
+            blk_plane = ((size_t)comp * (Cp / cb) + b) * Nb + img;
+        }
         auto dst = [&](int wp) {
+            if (cb > 0) return xp + ((blk_plane * Hp + hp) * Wp + wp) * cb + c_lo;
             return planar ? xp + ((((size_t)plane * groups + grp) * Hp + hp) * Wp + wp) * 8 : xp + (((size_t)plane * Hp + hp) * Wp + wp) * Cp + grp * 8;
         };
 #pragma unroll
