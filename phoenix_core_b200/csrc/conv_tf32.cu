@@ -253,7 +253,8 @@ __device__ __forceinline__ void split_tf32(float x, float& hi, float& lo) {
 }
 
 __global__ void pack_activations_f32_kernel(const float* __restrict__ x, float* __restrict__ hi, float* __restrict__ lo, int planes, int C,
-                                            int H, int W, int Hp, int Wp, int Cp, int pad_top, int pad_left, int ins_h, int ins_w) {
+                                            int H, int W, int Hp, int Wp, int Cp, int pad_top, int pad_left, int ins_h, int ins_w,
+                                            int cb = 0, int Nb = 1) {
     const int groups = Cp / 4;
     const size_t total = (size_t)planes * Hp * Wp * groups;
     for (size_t idx = (size_t)blockIdx.x * blockDim.x + threadIdx.x; idx < total; idx += (size_t)gridDim.x * blockDim.x) {
@@ -278,7 +279,11 @@ __global__ void pack_activations_f32_kernel(const float* __restrict__ x, float* 
             if (c < C && inside) v = __ldg(x + (((size_t)plane * C + c) * H + ih) * W + iw);
             split_tf32(v, ph[e], pl[e]);
         }
-        const size_t o = (((size_t)plane * Hp + hp) * Wp + wp) * Cp + grp * 4;
+        size_t o = (((size_t)plane * Hp + hp) * Wp + wp) * Cp + grp * 4;
+        if (cb > 0) {   // blocks of cb channels, block index outermost: [comp * (Cp / cb) + c / cb][img][hp][wp][cb]
+            const int comp = plane / Nb, img = plane - comp * Nb, b = (grp * 4) / cb;
+            o = (((((size_t)comp * (Cp / cb) + b) * Nb + img) * Hp + hp) * Wp + wp) * cb + (grp * 4 - b * cb);
+        }
         *reinterpret_cast<float4*>(hi + o) = vh;
         *reinterpret_cast<float4*>(lo + o) = vl;
     }
@@ -324,7 +329,7 @@ constexpr uint32_t TF_STAGE = 2 * (TM + TN) * TFK * 4;      // 48 KB
 struct TFParams {
     int Nb, Co, Ci, HO, WO, Cop, Cip, cbA, cbB;             // channel-block width in fp32 elements: 32
     int KH, KW, SH, SW, DH, DW, PW, PH, PN, tiles_w, tiles_h, tiles_n;
-    int m_tiles, n_tiles, n_tile_cols, splits, steps_per_split, merged_a, merged_b;
+    int m_tiles, n_tiles, n_tile_cols, splits, steps_per_split;
     int nc, ga;                                              // algebra: components, GA(3,0,0) component order
     unsigned long long neg;                                  // negative entries of the block, bit (8*l + d)
 };
@@ -380,40 +385,26 @@ qconv_filter_tf32_kernel(const __grid_constant__ CUtensorMap map_dy_hi, const __
 
     if (warp == 0) {
         if (lane == 0) {
+            // one copy per operand half and stage (the staged tensors keep the channel-block index outermost, so the blocks
+            // of a tile are one box even across components) and a running (tw, th, tn) of the pixel box: no division in
+            // this loop -- a division per copy used to bound the kernel
+            int tw = step_beg % p.tiles_w, th = (step_beg / p.tiles_w) % p.tiles_h, tn = step_beg / (p.tiles_w * p.tiles_h);
+            int s = 0, phase = 1;
             bool ok = true;
             for (int it = 0; it < n_steps && ok; ++it) {
-                const int s = it % T_STAGES;
-                ok = mbar_wait_bounded(empty_bar + 8 * s, ((it / T_STAGES) & 1) ^ 1, status, ST_T_PRODUCER);
+                ok = mbar_wait_bounded(empty_bar + 8 * s, phase, status, ST_T_PRODUCER);
                 if (!ok) break;
-                int step = step_beg + it;
-                const int tw = step % p.tiles_w; step /= p.tiles_w;
-                const int th = step % p.tiles_h;
-                const int tn = step / p.tiles_h;
                 const int ow0 = tw * p.PW, oh0 = th * p.PH, n0 = tn * p.PN;
                 const uint32_t a_hi = tiles_addr + s * TF_STAGE, a_lo = a_hi + A_REGION, b_hi = a_hi + 2 * A_REGION, b_lo = b_hi + B_REGION;
                 const uint32_t bar = full_bar + 8 * s;
+                if (++tw == p.tiles_w) { tw = 0; if (++th == p.tiles_h) { th = 0; ++tn; } }
+                if (++s == T_STAGES) { s = 0; phase ^= 1; }
                 mbar_arrive_expect_tx(bar, 2 * (a_bytes + b_bytes));
-                if (p.merged_a) {
-                    tma_load_5d(a_hi, &map_dy_hi, 0, ow0, oh0, n0, blockA0, bar);
-                    tma_load_5d(a_lo, &map_dy_lo, 0, ow0, oh0, n0, blockA0, bar);
-                } else {
-                    for (int b = 0; b < nblkA; ++b) {
-                        const int blk = blockA0 + b;
-                        tma_load_5d(a_hi + b * blkA_bytes, &map_dy_hi, (blk % bpcA) * p.cbA, ow0, oh0, n0, blk / bpcA, bar);
-                        tma_load_5d(a_lo + b * blkA_bytes, &map_dy_lo, (blk % bpcA) * p.cbA, ow0, oh0, n0, blk / bpcA, bar);
-                    }
-                }
+                tma_load_5d(a_hi, &map_dy_hi, 0, ow0, oh0, n0, blockA0, bar);
+                tma_load_5d(a_lo, &map_dy_lo, 0, ow0, oh0, n0, blockA0, bar);
                 const int wp0 = ow0 * p.SW + kw * p.DW, hp0 = oh0 * p.SH + kh * p.DH;
-                if (p.merged_b) {
-                    tma_load_5d(b_hi, &map_x_hi, 0, wp0, hp0, n0, blockB0, bar);
-                    tma_load_5d(b_lo, &map_x_lo, 0, wp0, hp0, n0, blockB0, bar);
-                } else {
-                    for (int b = 0; b < nblkB; ++b) {
-                        const int blk = blockB0 + b;
-                        tma_load_5d(b_hi + b * blkB_bytes, &map_x_hi, (blk % bpcB) * p.cbB, wp0, hp0, n0, blk / bpcB, bar);
-                        tma_load_5d(b_lo + b * blkB_bytes, &map_x_lo, (blk % bpcB) * p.cbB, wp0, hp0, n0, blk / bpcB, bar);
-                    }
-                }
+                tma_load_5d(b_hi, &map_x_hi, 0, wp0, hp0, n0, blockB0, bar);
+                tma_load_5d(b_lo, &map_x_lo, 0, wp0, hp0, n0, blockB0, bar);
             }
         }
         __syncwarp();
@@ -628,9 +619,9 @@ static int conv_tf32_filter_launch(const Geom& g, const float* dy, const float* 
     float* y_lo = reinterpret_cast<float*>(s8 + 2 * f.xp_bytes + f.dyp_bytes);
     float* acc = reinterpret_cast<float*>(s8 + 2 * f.xp_bytes + 2 * f.dyp_bytes);
     pack_activations_f32_kernel<<<grid_cap((size_t)g.nc * g.Nb * f.Hp * f.Wp * (f.Cip / 4), 256, 16), 256, 0, stream>>>(
-        x, x_hi, x_lo, g.nc * g.Nb, g.Ci, g.H, g.W, f.Hp, f.Wp, f.Cip, g.PT, g.PL, 1, 1);
+        x, x_hi, x_lo, g.nc * g.Nb, g.Ci, g.H, g.W, f.Hp, f.Wp, f.Cip, g.PT, g.PL, 1, 1, 32, g.Nb);
     pack_activations_f32_kernel<<<grid_cap((size_t)g.nc * g.Nb * g.HO * g.WO * (f.Cop / 4), 256, 16), 256, 0, stream>>>(
-        dy, y_hi, y_lo, g.nc * g.Nb, g.Co, g.HO, g.WO, g.HO, g.WO, f.Cop, 0, 0, 1, 1);
+        dy, y_hi, y_lo, g.nc * g.Nb, g.Co, g.HO, g.WO, g.HO, g.WO, f.Cop, 0, 0, 1, 1, 32, g.Nb);
     PCB_CUDA_TRY(cudaGetLastError());
     PCB_CUDA_TRY(cudaMemsetAsync(acc, 0, (size_t)g.nc * g.Co * g.Ci * taps * sizeof(float), stream));
 
@@ -653,8 +644,6 @@ static int conv_tf32_filter_launch(const Geom& g, const float* dy, const float* 
     p.m_tiles = (m_cols + TM - 1) / TM;
     p.n_tiles = (n_cols + TN - 1) / TN;
     p.n_tile_cols = n_cols < TN ? n_cols : TN;
-    p.merged_a = (f.Cop == p.cbA) ? 1 : 0;
-    p.merged_b = (f.Cip == p.cbB) ? 1 : 0;
     const int steps_total = p.tiles_w * p.tiles_h * p.tiles_n;
     const int items = taps * p.m_tiles * p.n_tiles;
     int splits = split_count(items, sm_count());
@@ -666,20 +655,22 @@ static int conv_tf32_filter_launch(const Geom& g, const float* dy, const float* 
     auto swz = [](int) { return CU_TENSOR_MAP_SWIZZLE_128B_ATOM_32B; };
     alignas(64) CUtensorMap m_dy_hi, m_dy_lo, m_x_hi, m_x_lo;
     {
-        const cuuint64_t dims[5] = {(cuuint64_t)f.Cop, (cuuint64_t)g.WO, (cuuint64_t)g.HO, (cuuint64_t)g.Nb, (cuuint64_t)g.nc};
-        const cuuint64_t strides[4] = {(cuuint64_t)f.Cop * 4, (cuuint64_t)g.WO * f.Cop * 4, (cuuint64_t)g.HO * g.WO * f.Cop * 4,
-                                       (cuuint64_t)g.Nb * g.HO * g.WO * f.Cop * 4};
-        const cuuint32_t box[5] = {(cuuint32_t)p.cbA, (cuuint32_t)p.PW, (cuuint32_t)p.PH, (cuuint32_t)p.PN, (cuuint32_t)(p.merged_a ? TM / p.cbA : 1)};
+        // staged tensors: [component * blocks per component + channel block][image][h][w][32 channels]; the last box extent
+        // is the number of channel blocks of a tile (blocks past the end read as zeros)
+        const cuuint64_t dims[5] = {(cuuint64_t)p.cbA, (cuuint64_t)g.WO, (cuuint64_t)g.HO, (cuuint64_t)g.Nb, (cuuint64_t)(g.nc * (f.Cop / p.cbA))};
+        const cuuint64_t strides[4] = {(cuuint64_t)p.cbA * 4, (cuuint64_t)g.WO * p.cbA * 4, (cuuint64_t)g.HO * g.WO * p.cbA * 4,
+                                       (cuuint64_t)g.Nb * g.HO * g.WO * p.cbA * 4};
+        const cuuint32_t box[5] = {(cuuint32_t)p.cbA, (cuuint32_t)p.PW, (cuuint32_t)p.PH, (cuuint32_t)p.PN, (cuuint32_t)(TM / p.cbA)};
         int rc = make_tensor_map(&m_dy_hi, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, y_hi, 5, dims, strides, box, nullptr, swz(p.cbA), "dy hi");
         if (rc == PCB_OK) rc = make_tensor_map(&m_dy_lo, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, y_lo, 5, dims, strides, box, nullptr, swz(p.cbA), "dy lo");
         if (rc != PCB_OK) return rc;
     }
     {
-        const cuuint64_t dims[5] = {(cuuint64_t)f.Cip, (cuuint64_t)f.Wp, (cuuint64_t)f.Hp, (cuuint64_t)g.Nb, (cuuint64_t)g.nc};
-        const cuuint64_t strides[4] = {(cuuint64_t)f.Cip * 4, (cuuint64_t)f.Wp * f.Cip * 4, (cuuint64_t)f.Hp * f.Wp * f.Cip * 4,
-                                       (cuuint64_t)g.Nb * f.Hp * f.Wp * f.Cip * 4};
+        const cuuint64_t dims[5] = {(cuuint64_t)p.cbB, (cuuint64_t)f.Wp, (cuuint64_t)f.Hp, (cuuint64_t)g.Nb, (cuuint64_t)(g.nc * (f.Cip / p.cbB))};
+        const cuuint64_t strides[4] = {(cuuint64_t)p.cbB * 4, (cuuint64_t)f.Wp * p.cbB * 4, (cuuint64_t)f.Hp * f.Wp * p.cbB * 4,
+                                       (cuuint64_t)g.Nb * f.Hp * f.Wp * p.cbB * 4};
         const cuuint32_t box[5] = {(cuuint32_t)p.cbB, (cuuint32_t)((p.PW - 1) * g.SW + 1), (cuuint32_t)((p.PH - 1) * g.SH + 1), (cuuint32_t)p.PN,
-                                   (cuuint32_t)(p.merged_b ? p.n_tile_cols / p.cbB : 1)};
+                                   (cuuint32_t)(p.n_tile_cols / p.cbB)};
         const cuuint32_t es[5] = {1, (cuuint32_t)g.SW, (cuuint32_t)g.SH, 1, 1};
         int rc = make_tensor_map(&m_x_hi, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, x_hi, 5, dims, strides, box, es, swz(p.cbB), "x hi");
         if (rc == PCB_OK) rc = make_tensor_map(&m_x_lo, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, x_lo, 5, dims, strides, box, es, swz(p.cbB), "x lo");
