@@ -1,6 +1,7 @@
 """Shape sweep of the quaternion conv2d kernels at ResNet-stage shapes.
 
     python -m phoenix_core_b200.sweep [--batch 128] [--dtypes f16,f32] [--reps 10] [--variant 16p|8p] [--quick]
+                                      [--shape C,HW,K,S]   (one shape only, e.g. for a profiler capture)
 
 For every shape times forward, backward-data and backward-filter separately (CUDA events on the current stream,
 3 warm-up + `reps` timed launches; every shape's tensors exceed L2 or the output is overwritten between
@@ -129,7 +130,9 @@ def main():
     ap.add_argument("--variant", default="16p")
     ap.add_argument("--quick", action="store_true", help="3x3 stride 1 and 1x1 stride 1 only")
     ap.add_argument("--markdown", action="store_true", help="print a markdown table instead of JSON lines")
+    ap.add_argument("--shape", default=None, help="channels,size,kernel,stride of the single shape to run")
     a = ap.parse_args()
+    only = tuple(int(v) for v in a.shape.split(",")) if a.shape else None
     if a.markdown:
         print("| c | hw | k | s | dtype | pass | fam | ms | TFLOP/s | GB/s | f_tensor | f_hbm |")
         print("|---|---|---|---|---|---|---|---|---|---|---|---|")
@@ -137,6 +140,8 @@ def main():
         for c, hw in STAGES:
             for k in (3, 1):
                 for stride in ((1,) if a.quick else (1, 2)):
+                    if only is not None and only != (c, hw, k, stride):
+                        continue
                     for rec in run_shape(a.batch, c, hw, k, stride, dtype, a.variant, a.reps if dtype != "f32" else max(2, a.reps // 3)):
                         if a.markdown:
                             print("| %d | %d | %d | %d | %s | %s | %d | %.3f | %.1f | %.0f | %.3f | %.3f |" % (
