@@ -367,6 +367,139 @@ bool pointwise(const Geom& g) {
            g.DH == 1 && g.DW == 1;
 }
 
+
+// ---------------------------------------------------------------------------------------------------
+// Pointwise (1x1) layers with a stride touch only every SH-th row and SW-th column of the input: they run as
+// stride-1 pointwise layers on a compact copy of those pixels (forward, filter gradient), or produce the compact
+// input gradient and scatter it between zeros (backward-data). Without this the strided layers went through the
+// general kernel, which staged the whole input and, backward, convolved a zero-inserted dy at full resolution.
+// (reference: the same layers are ordinary strided cuDNN / oneDNN convolutions, src/backend/cudnn/conv2d.hpp:181-310)
+// ---------------------------------------------------------------------------------------------------
+template <int BYTES> struct VecBytes;
+template <> struct VecBytes<2> { typedef uint16_t type; };
+template <> struct VecBytes<4> { typedef uint32_t type; };
+template <> struct VecBytes<8> { typedef uint2 type; };
+template <> struct VecBytes<16> { typedef uint4 type; };
+
+// dst[plane][oh][ow] = src[plane][oh*SH - PT][ow*SW - PL] (zero outside); planes = components * images * channels.
+// V = 0: any stride and padding, one output per thread. V >= 1: V outputs per thread from one load of 2 V inputs;
+// requires SW == 2, PL == 0, WO % V == 0, W % (2 V) == 0 and 16-byte aligned bases. Indices are 32-bit: tensors hold
+// fewer than 2^31 elements.
+template <typename E, int V>
+__global__ void subsample_kernel(const E* __restrict__ src, E* __restrict__ dst, unsigned planes, int H, int W, int HO, int WO,
+                                 int SH, int SW, int PT, int PL) {
+    constexpr int VV = V > 0 ? V : 1;
+    const unsigned wq = WO / VV;
+    const unsigned total = planes * HO * wq;
+    for (unsigned idx = blockIdx.x * blockDim.x + threadIdx.x; idx < total; idx += gridDim.x * blockDim.x) {
+        const unsigned q = idx % wq, rest = idx / wq;
+        const unsigned oh = rest % HO, plane = rest / HO;
+        const int ih = (int)oh * SH - PT;
+        alignas(16) E out[VV];
+        if (V == 0) {
+            const int iw = (int)q * SW - PL;
+            out[0] = (ih >= 0 && ih < H && iw >= 0 && iw < W) ? src[((size_t)plane * H + ih) * W + iw] : E(0);
+        } else {
+            alignas(16) E in[2 * VV];
+            typedef typename VecBytes<2 * VV * sizeof(E)>::type In;
+            if (ih >= 0 && ih < H) *reinterpret_cast<In*>(in) = __ldg(reinterpret_cast<const In*>(src + ((size_t)plane * H + ih) * W + 2 * VV * q));
+            else *reinterpret_cast<In*>(in) = In();
+#pragma unroll
+            for (int e = 0; e < VV; ++e) out[e] = in[2 * e];
+        }
+        typedef typename VecBytes<VV * sizeof(E)>::type Out;
+        *reinterpret_cast<Out*>(dst + ((size_t)plane * HO + oh) * WO + (size_t)VV * q) = *reinterpret_cast<const Out*>(out);
+    }
+}
+
+// dst[plane][ih][iw] = src[plane][oh][ow] where ih = oh*SH - PT, iw = ow*SW - PL, zero everywhere else.
+// V = 0: any stride and padding, one destination element per thread. V >= 1: V source elements (2 V destination elements)
+// per thread; requires SW == 2, PL == 0, W == 2 WO, W % (2 V) == 0 and 16-byte aligned bases.
+template <typename E, int V>
+__global__ void scatter_strided_kernel(const E* __restrict__ src, E* __restrict__ dst, unsigned planes, int H, int W, int HO, int WO,
+                                       int SH, int SW, int PT, int PL) {
+    constexpr int VV = V > 0 ? V : 1;
+    const unsigned wq = V == 0 ? W : W / (2 * VV);
+    const unsigned total = planes * H * wq;
+    for (unsigned idx = blockIdx.x * blockDim.x + threadIdx.x; idx < total; idx += gridDim.x * blockDim.x) {
+        const unsigned q = idx % wq, rest = idx / wq;
+        const unsigned ih = rest % H, plane = rest / H;
+        const int th = (int)ih + PT, oh = th / SH;
+        const bool row = (th % SH == 0) && oh < HO;
+        if (V == 0) {
+            const int tw = (int)q + PL, ow = tw / SW;
+            dst[((size_t)plane * H + ih) * W + q] = (row && tw % SW == 0 && ow < WO) ? src[((size_t)plane * HO + oh) * WO + ow] : E(0);
+        } else {
+            alignas(16) E in[VV], out[2 * VV];
+            typedef typename VecBytes<VV * sizeof(E)>::type In;
+            typedef typename VecBytes<2 * VV * sizeof(E)>::type Out;
+            if (row) *reinterpret_cast<In*>(in) = __ldg(reinterpret_cast<const In*>(src + ((size_t)plane * HO + oh) * WO + (size_t)VV * q));
+#pragma unroll
+            for (int e = 0; e < VV; ++e) { out[2 * e] = row ? in[e] : E(0); out[2 * e + 1] = E(0); }
+            *reinterpret_cast<Out*>(dst + ((size_t)plane * H + ih) * W + (size_t)2 * VV * q) = *reinterpret_cast<const Out*>(out);
+        }
+    }
+}
+
+bool strided_pointwise(const Geom& g) {
+    return g.KH == 1 && g.KW == 1 && (g.SH > 1 || g.SW > 1) && g.plain && !g.w_io && !g.dw_io;
+}
+
+// The stride-1 pointwise layer on the compact copy: input plane = output plane.
+Geom compact_geom(const Geom& g) {
+    Geom s = g;
+    s.H = g.HO; s.W = g.WO; s.SH = s.SW = 1; s.PT = s.PL = 0;
+    s.xp = g.Ci * s.H * s.W; s.xc = s.H * s.W; s.xh = s.W; s.xw = 1;
+    return s;
+}
+
+size_t compact_bytes(Pass pass, int dtype, const Geom& g) {
+    const size_t comps = (pass != PASS_BWD_DATA && g.real_in) ? 1 : g.nc;
+    return (comps * g.Nb * g.Ci * g.HO * g.WO * dtype_size(dtype) + 1023) / 1024 * 1024;
+}
+
+template <typename E>
+int launch_subsample(const void* src, void* dst, size_t planes, const Geom& g, cudaStream_t stream) {
+    const bool al = ((reinterpret_cast<uintptr_t>(src) | reinterpret_cast<uintptr_t>(dst)) & 15u) == 0;
+    const bool v = g.SW == 2 && g.PL == 0 && al && g.W >= 2 * g.WO;
+    int V = 0;                                            // outputs per thread; loads of up to 16 bytes
+    if (v && sizeof(E) == 2 && g.WO % 4 == 0 && g.W % 8 == 0) V = 4;
+    else if (v && g.WO % 2 == 0 && g.W % 4 == 0) V = 2;
+    else if (v && g.W % 2 == 0) V = 1;
+    const size_t total = planes * g.HO * (g.WO / (V ? V : 1));
+    const size_t want = (total + 255) / 256, cap = (size_t)sm_count() * 16;
+    const int blocks = (int)(want < cap ? (want ? want : 1) : cap);
+    const E* s = static_cast<const E*>(src); E* d = static_cast<E*>(dst);
+    const unsigned pl = (unsigned)planes;
+    if (V == 4) subsample_kernel<E, (sizeof(E) == 2 ? 4 : 2)><<<blocks, 256, 0, stream>>>(s, d, pl, g.H, g.W, g.HO, g.WO, g.SH, g.SW, g.PT, g.PL);
+    else if (V == 2) subsample_kernel<E, 2><<<blocks, 256, 0, stream>>>(s, d, pl, g.H, g.W, g.HO, g.WO, g.SH, g.SW, g.PT, g.PL);
+    else if (V == 1) subsample_kernel<E, 1><<<blocks, 256, 0, stream>>>(s, d, pl, g.H, g.W, g.HO, g.WO, g.SH, g.SW, g.PT, g.PL);
+    else subsample_kernel<E, 0><<<blocks, 256, 0, stream>>>(s, d, pl, g.H, g.W, g.HO, g.WO, g.SH, g.SW, g.PT, g.PL);
+    PCB_CUDA_TRY(cudaGetLastError());
+    return PCB_OK;
+}
+
+template <typename E>
+int launch_scatter(const void* src, void* dst, size_t planes, const Geom& g, cudaStream_t stream) {
+    const bool al = ((reinterpret_cast<uintptr_t>(src) | reinterpret_cast<uintptr_t>(dst)) & 15u) == 0;
+    const bool v = g.SW == 2 && g.PL == 0 && al && g.W == 2 * g.WO;
+    int V = 0;                                            // source elements per thread; stores of up to 16 bytes
+    if (v && sizeof(E) == 2 && g.W % 8 == 0) V = 4;
+    else if (v && g.W % 4 == 0) V = 2;
+    else if (v) V = 1;
+    const size_t total = planes * g.H * (V == 0 ? g.W : g.W / (2 * V));
+    const size_t want = (total + 255) / 256, cap = (size_t)sm_count() * 16;
+    const int blocks = (int)(want < cap ? (want ? want : 1) : cap);
+    const E* s = static_cast<const E*>(src); E* d = static_cast<E*>(dst);
+    const unsigned pl = (unsigned)planes;
+    if (V == 4) scatter_strided_kernel<E, (sizeof(E) == 2 ? 4 : 2)><<<blocks, 256, 0, stream>>>(s, d, pl, g.H, g.W, g.HO, g.WO, g.SH, g.SW, g.PT, g.PL);
+    else if (V == 2) scatter_strided_kernel<E, 2><<<blocks, 256, 0, stream>>>(s, d, pl, g.H, g.W, g.HO, g.WO, g.SH, g.SW, g.PT, g.PL);
+    else if (V == 1) scatter_strided_kernel<E, 1><<<blocks, 256, 0, stream>>>(s, d, pl, g.H, g.W, g.HO, g.WO, g.SH, g.SW, g.PT, g.PL);
+    else scatter_strided_kernel<E, 0><<<blocks, 256, 0, stream>>>(s, d, pl, g.H, g.W, g.HO, g.WO, g.SH, g.SW, g.PT, g.PL);
+    PCB_CUDA_TRY(cudaGetLastError());
+    return PCB_OK;
+}
+
 }  // namespace
 
 namespace {
@@ -383,6 +516,7 @@ bool legacy_supported(int dtype, int variant, const Geom& g) {
 }  // namespace
 
 bool tensor_path_supported(Pass pass, int dtype, int variant, const Geom& g) {
+    if (strided_pointwise(g) && tensor_path_supported(pass, dtype, variant, compact_geom(g))) return true;
     if (dtype == PCB_F32) return conv_tf32_supported(pass, dtype, variant, g);
     if (pass == PASS_BWD_FILTER)
         return pointwise_filter_tc_supported(dtype, variant, g) || narrow_filter_tc_supported(dtype, variant, g) ||
@@ -393,6 +527,8 @@ bool tensor_path_supported(Pass pass, int dtype, int variant, const Geom& g) {
 
 size_t tensor_scratch_bytes(Pass pass, int dtype, int variant, int engine, const Geom& g) {
     if (engine == PCB_ENGINE_SIMT || !tensor_path_supported(pass, dtype, variant, g)) return 0;
+    if (strided_pointwise(g) && tensor_path_supported(pass, dtype, variant, compact_geom(g)))
+        return compact_bytes(pass, dtype, g) + tensor_scratch_bytes(pass, dtype, variant, engine, compact_geom(g));
     if (dtype == PCB_F32) return conv_tf32_scratch_bytes(pass, g);
     if (pass == PASS_BWD_FILTER) {
         if (pointwise_filter_tc_supported(dtype, variant, g)) return (size_t)g.nc * g.Co * g.Ci * g.KH * g.KW * sizeof(float);
@@ -406,8 +542,22 @@ size_t tensor_scratch_bytes(Pass pass, int dtype, int variant, int engine, const
     return 0;
 }
 
-int tensor_launch(Pass pass, int dtype, int /*variant*/, const Geom& g, const void* a, const void* b, const void* bias,
+int tensor_launch(Pass pass, int dtype, int variant, const Geom& g, const void* a, const void* b, const void* bias,
                   void* out, float* scratch, int* status, cudaStream_t stream) {
+    if (strided_pointwise(g) && tensor_path_supported(pass, dtype, variant, compact_geom(g))) {
+        const Geom s = compact_geom(g);
+        void* compact = scratch;
+        float* rest = reinterpret_cast<float*>(reinterpret_cast<char*>(scratch) + compact_bytes(pass, dtype, g));
+        const size_t planes = (size_t)((pass != PASS_BWD_DATA && g.real_in) ? 1 : g.nc) * g.Nb * g.Ci;
+        if (pass == PASS_BWD_DATA) {
+            const int rc = tensor_launch(pass, dtype, variant, s, a, b, bias, compact, rest, status, stream);
+            if (rc != PCB_OK) return rc;
+            return dtype == PCB_F32 ? launch_scatter<uint32_t>(compact, out, planes, g, stream) : launch_scatter<uint16_t>(compact, out, planes, g, stream);
+        }
+        const int rc = dtype == PCB_F32 ? launch_subsample<uint32_t>(b, compact, planes, g, stream) : launch_subsample<uint16_t>(b, compact, planes, g, stream);
+        if (rc != PCB_OK) return rc;
+        return tensor_launch(pass, dtype, variant, s, a, compact, bias, out, rest, status, stream);
+    }
     if (dtype == PCB_F32) {
         PCB_CUDA_TRY(cudaMemsetAsync(status, 0, sizeof(int), stream));
         return conv_tf32_launch(pass, g, a, b, bias, out, scratch, status, stream);

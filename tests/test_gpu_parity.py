@@ -140,6 +140,12 @@ GENERAL_TENSOR_SHAPES = [
     (1, 64, 32, 30, 21, 3, 3, (1, 1), (1, 1, 1, 1)),     # halo mode: ragged 30 x 21 plane, two 32-channel slices
     (2, 32, 48, 56, 24, 5, 5, (1, 1), (2, 2, 2, 2)),     # halo mode: 25 taps (two stages fit), two tiles per column, M = 192
     (1, 32, 32, 26, 26, 3, 3, (2, 2), (0, 0, 1, 1)),     # halo mode in backward-data only (zero-inserted 26 x 26 plane)
+    (2, 64, 32, 16, 16, 1, 1, (2, 2), (0, 0, 0, 0)),     # strided 1x1 on a compact copy (8-pixel vectors), then the direct pointwise kernels
+    (1, 24, 40, 9, 7, 1, 1, (2, 3), (1, 1, 0, 1)),       # strided 1x1 with padding, stride 3 across, odd planes (scalar copies)
+    (2, 32, 32, 12, 12, 1, 1, (2, 2), (0, 0, 0, 0)),     # strided 1x1: 6 x 6 compact planes (4-pixel vectors), staged general kernel
+    (5, 32, 128, 7, 7, 1, 1, (1, 1), (0, 0, 0, 0)),      # whole 7 x 7 planes per tile (4 images, the last tile ragged): bulk-copy epilogue
+    (2, 128, 256, 14, 14, 1, 1, (1, 1), (0, 0, 0, 0)),   # whole 14 x 14 planes, 64-channel K slices with three stages, both directions
+    (3, 128, 128, 14, 14, 3, 3, (2, 2), (1, 1, 1, 1)),   # bulk-copy epilogue behind a 3x3 stride-2 layer (7 x 7 output planes)
 ]
 
 
