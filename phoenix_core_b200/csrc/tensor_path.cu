@@ -441,6 +441,121 @@ __global__ void scatter_strided_kernel(const E* __restrict__ src, E* __restrict_
     }
 }
 
+
+// ---------------------------------------------------------------------------------------------------
+// Backward-data of a strided layer with taps. dx[ih] collects only the taps kh with (ih + PT - kh) divisible by the
+// stride, so the input pixels fall into SH x SW classes by (ih mod SH, iw mod SW), and the gradient of one class is the
+// backward-data pass of a STRIDE-1 layer over the same dy whose filters are every SH-th / SW-th tap:
+//     dx[SH i + a] = sum_k' dy[i + c - k'] w[r + SH k'],   r = (a + PT) mod SH,  c = (a + PT) div SH
+// -- a layer with ceil((KH - r) / SH) taps and padding c before. Each class runs through the stride-1 kernels into a
+// compact tensor and one kernel interleaves the classes into dx. The classes together execute the FLOPs of the layer;
+// convolving a zero-inserted dy at full resolution, the route this replaces, executed SH x SW times as many.
+// ---------------------------------------------------------------------------------------------------
+struct StrideClass {
+    int a, b;            // class: input row and column modulo the strides
+    int rh, rw;          // first tap of the class
+    Geom g;              // the stride-1 layer (g.KH == 0 or g.KW == 0: the class receives no tap, its pixels are zero)
+    size_t dx_off, w_off;   // byte offsets of the compact gradient / the class's filters in the scratch area
+};
+
+// Taken from 512 gradient rows (128 quaternion channels) up: each class pays its own staging pass and launch, and below that
+// width those cost more than the zero-insertion route's extra MMAs (measured at batch 128: 0.47 -> 0.38 ms at 128
+// channels and 28 x 28, 0.51 -> 0.34 ms at 256 and 14 x 14, but 0.12 -> 0.27 ms at 64 -> 128 channels and 14 x 14).
+bool strided_taps(const Geom& g) {
+    return (g.KH > 1 || g.KW > 1) && (g.SH > 1 || g.SW > 1) && g.SH <= 2 && g.SW <= 2 && g.DH == 1 && g.DW == 1 && g.plain && !g.w_io &&
+           !g.dw_io && !g.real_in && g.nc * g.Ci >= 512;
+}
+
+// Fills the classes; returns their number. `bytes` receives the scratch the classes' tensors take.
+int stride_classes(const Geom& g, int dtype, StrideClass* cls, size_t* bytes) {
+    const size_t es = dtype_size(dtype);
+    size_t off = 0;
+    int n = 0;
+    for (int a = 0; a < g.SH; ++a)
+        for (int b = 0; b < g.SW; ++b) {
+            StrideClass& c = cls[n++];
+            c.a = a; c.b = b;
+            c.rh = (a + g.PT) % g.SH; c.rw = (b + g.PL) % g.SW;
+            Geom s = g;
+            s.H = (g.H - a + g.SH - 1) / g.SH; s.W = (g.W - b + g.SW - 1) / g.SW;
+            s.KH = c.rh < g.KH ? (g.KH - c.rh + g.SH - 1) / g.SH : 0;
+            s.KW = c.rw < g.KW ? (g.KW - c.rw + g.SW - 1) / g.SW : 0;
+            s.SH = s.SW = 1; s.PT = (a + g.PT) / g.SH; s.PL = (b + g.PL) / g.SW;
+            s.xp = g.Ci * s.H * s.W; s.xc = s.H * s.W; s.xh = s.W; s.xw = 1;
+            s.wr = g.Co * g.Ci * s.KH * s.KW; s.wo = g.Ci * s.KH * s.KW; s.wi = s.KH * s.KW; s.wh = s.KW; s.ww = 1;
+            s.dr = s.wr; s.dco = s.wo; s.dci = s.wi; s.dkh = s.wh; s.dkw = s.ww;
+            c.g = s;
+            c.dx_off = off;
+            off += ((size_t)g.nc * g.Nb * g.Ci * s.H * s.W * es + 1023) / 1024 * 1024;
+            c.w_off = off;
+            off += ((size_t)g.nc * g.Co * g.Ci * s.KH * s.KW * es + 1023) / 1024 * 1024;
+        }
+    *bytes = off;
+    return n;
+}
+
+bool strided_classes_supported(int dtype, int variant, const Geom& g) {
+    if (!strided_taps(g)) return false;
+    StrideClass cls[4];
+    size_t bytes;
+    const int n = stride_classes(g, dtype, cls, &bytes);
+    for (int i = 0; i < n; ++i) {
+        const Geom& s = cls[i].g;
+        if (s.H <= 0 || s.W <= 0) return false;
+        if (s.KH == 0 || s.KW == 0) continue;
+        if (!tensor_path_supported(PASS_BWD_DATA, dtype, variant, s)) return false;
+    }
+    return true;
+}
+
+// w_sub[r][co][ci][u][v] = w[r][co][ci][rh + SH u][rw + SW v]
+template <typename E>
+__global__ void gather_taps_kernel(const E* __restrict__ w, E* __restrict__ sub, unsigned rows /*components * Co * Ci*/, int KH, int KW,
+                                   int KHs, int KWs, int rh, int rw, int SH, int SW) {
+    const unsigned total = rows * KHs * KWs;
+    for (unsigned idx = blockIdx.x * blockDim.x + threadIdx.x; idx < total; idx += gridDim.x * blockDim.x) {
+        const unsigned v = idx % KWs, rest = idx / KWs;
+        const unsigned u = rest % KHs, row = rest / KHs;
+        sub[idx] = w[((size_t)row * KH + rh + SH * u) * KW + rw + SW * v];
+    }
+}
+
+struct ClassPtrs { const void* p[4]; int H[4], W[4], live[4]; };
+
+// dx[plane][ih][iw] = class (ih mod SH, iw mod SW) [plane][ih div SH][iw div SW], zero for a class without taps.
+template <typename E>
+__global__ void interleave_classes_kernel(ClassPtrs c, E* __restrict__ dx, unsigned planes, int H, int W, int SH, int SW) {
+    const unsigned total = planes * H * W;
+    for (unsigned idx = blockIdx.x * blockDim.x + threadIdx.x; idx < total; idx += gridDim.x * blockDim.x) {
+        const unsigned iw = idx % W, rest = idx / W;
+        const unsigned ih = rest % H, plane = rest / H;
+        const int k = (ih % SH) * SW + (iw % SW);
+        dx[idx] = c.live[k] ? static_cast<const E*>(c.p[k])[((size_t)plane * c.H[k] + ih / SH) * c.W[k] + iw / SW] : E(0);
+    }
+}
+// The same for SH == SW == 2, 16-bit elements and W a multiple of 2 V: one thread writes 2 V pixels of a row from V + V
+// pixels of the two classes of that row (V = 4, 2 or 1: stores of 16, 8 or 4 bytes).
+template <int V>
+__global__ void interleave_classes_2x2_kernel(ClassPtrs c, uint16_t* __restrict__ dx, unsigned planes, int H, int W) {
+    typedef typename VecBytes<2 * V>::type In;
+    typedef typename VecBytes<4 * V>::type Out;
+    const unsigned wq = W / (2 * V), total = planes * H * wq;
+    for (unsigned idx = blockIdx.x * blockDim.x + threadIdx.x; idx < total; idx += gridDim.x * blockDim.x) {
+        const unsigned q = idx % wq, rest = idx / wq;
+        const unsigned ih = rest % H, plane = rest / H;
+        const int k0 = (ih & 1) * 2;
+        alignas(8) uint16_t even[V], odd[V];
+        alignas(16) uint16_t o[2 * V];
+        if (c.live[k0])
+            *reinterpret_cast<In*>(even) = __ldg(reinterpret_cast<const In*>(static_cast<const uint16_t*>(c.p[k0]) + ((size_t)plane * c.H[k0] + (ih >> 1)) * c.W[k0] + V * q));
+        if (c.live[k0 + 1])
+            *reinterpret_cast<In*>(odd) = __ldg(reinterpret_cast<const In*>(static_cast<const uint16_t*>(c.p[k0 + 1]) + ((size_t)plane * c.H[k0 + 1] + (ih >> 1)) * c.W[k0 + 1] + V * q));
+#pragma unroll
+        for (int e = 0; e < V; ++e) { o[2 * e] = c.live[k0] ? even[e] : (uint16_t)0; o[2 * e + 1] = c.live[k0 + 1] ? odd[e] : (uint16_t)0; }
+        *reinterpret_cast<Out*>(dx + ((size_t)plane * H + ih) * W + 2 * V * q) = *reinterpret_cast<const Out*>(o);
+    }
+}
+
 bool strided_pointwise(const Geom& g) {
     return g.KH == 1 && g.KW == 1 && (g.SH > 1 || g.SW > 1) && g.plain && !g.w_io && !g.dw_io;
 }
@@ -517,6 +632,7 @@ bool legacy_supported(int dtype, int variant, const Geom& g) {
 
 bool tensor_path_supported(Pass pass, int dtype, int variant, const Geom& g) {
     if (strided_pointwise(g) && tensor_path_supported(pass, dtype, variant, compact_geom(g))) return true;
+    if (pass == PASS_BWD_DATA && strided_classes_supported(dtype, variant, g)) return true;
     if (dtype == PCB_F32) return conv_tf32_supported(pass, dtype, variant, g);
     if (pass == PASS_BWD_FILTER)
         return pointwise_filter_tc_supported(dtype, variant, g) || narrow_filter_tc_supported(dtype, variant, g) ||
@@ -529,6 +645,17 @@ size_t tensor_scratch_bytes(Pass pass, int dtype, int variant, int engine, const
     if (engine == PCB_ENGINE_SIMT || !tensor_path_supported(pass, dtype, variant, g)) return 0;
     if (strided_pointwise(g) && tensor_path_supported(pass, dtype, variant, compact_geom(g)))
         return compact_bytes(pass, dtype, g) + tensor_scratch_bytes(pass, dtype, variant, engine, compact_geom(g));
+    if (pass == PASS_BWD_DATA && strided_classes_supported(dtype, variant, g)) {
+        StrideClass cls[4];
+        size_t bytes, inner = 0;
+        const int n = stride_classes(g, dtype, cls, &bytes);
+        for (int i = 0; i < n; ++i)
+            if (cls[i].g.KH > 0 && cls[i].g.KW > 0) {
+                const size_t t = tensor_scratch_bytes(pass, dtype, variant, engine, cls[i].g);
+                if (t > inner) inner = t;
+            }
+        return bytes + inner;
+    }
     if (dtype == PCB_F32) return conv_tf32_scratch_bytes(pass, g);
     if (pass == PASS_BWD_FILTER) {
         if (pointwise_filter_tc_supported(dtype, variant, g)) return (size_t)g.nc * g.Co * g.Ci * g.KH * g.KW * sizeof(float);
@@ -557,6 +684,47 @@ int tensor_launch(Pass pass, int dtype, int variant, const Geom& g, const void* 
         const int rc = dtype == PCB_F32 ? launch_subsample<uint32_t>(b, compact, planes, g, stream) : launch_subsample<uint16_t>(b, compact, planes, g, stream);
         if (rc != PCB_OK) return rc;
         return tensor_launch(pass, dtype, variant, s, a, compact, bias, out, rest, status, stream);
+    }
+    if (pass == PASS_BWD_DATA && strided_classes_supported(dtype, variant, g)) {
+        StrideClass cls[4];
+        size_t bytes;
+        const int n = stride_classes(g, dtype, cls, &bytes);
+        char* area = reinterpret_cast<char*>(scratch);
+        float* rest = reinterpret_cast<float*>(area + bytes);
+        ClassPtrs ptrs;
+        for (int i = 0; i < 4; ++i) { ptrs.p[i] = nullptr; ptrs.H[i] = ptrs.W[i] = 1; ptrs.live[i] = 0; }
+        const unsigned rows = (unsigned)g.nc * g.Co * g.Ci;
+        for (int i = 0; i < n; ++i) {
+            const Geom& s = cls[i].g;
+            const int slot = cls[i].a * g.SW + cls[i].b;
+            ptrs.p[slot] = area + cls[i].dx_off; ptrs.H[slot] = s.H; ptrs.W[slot] = s.W;
+            if (s.KH == 0 || s.KW == 0) continue;
+            ptrs.live[slot] = 1;
+            void* w_sub = area + cls[i].w_off;
+            const unsigned total = rows * s.KH * s.KW;
+            const int blocks = (int)((total + 255) / 256 < (unsigned)sm_count() * 8 ? (total + 255) / 256 : (unsigned)sm_count() * 8);
+            if (dtype == PCB_F32)
+                gather_taps_kernel<uint32_t><<<blocks, 256, 0, stream>>>((const uint32_t*)a, (uint32_t*)w_sub, rows, g.KH, g.KW, s.KH, s.KW, cls[i].rh, cls[i].rw, g.SH, g.SW);
+            else
+                gather_taps_kernel<uint16_t><<<blocks, 256, 0, stream>>>((const uint16_t*)a, (uint16_t*)w_sub, rows, g.KH, g.KW, s.KH, s.KW, cls[i].rh, cls[i].rw, g.SH, g.SW);
+            PCB_CUDA_TRY(cudaGetLastError());
+            const int rc = tensor_launch(pass, dtype, variant, s, w_sub, b, nullptr, area + cls[i].dx_off, rest, status, stream);
+            if (rc != PCB_OK) return rc;
+        }
+        const unsigned planes = (unsigned)g.nc * g.Nb * g.Ci;
+        int V = 0;                                   // pixels per class and thread of the vector form
+        if (dtype != PCB_F32 && g.SH == 2 && g.SW == 2 && (reinterpret_cast<uintptr_t>(out) & 15u) == 0)
+            V = g.W % 8 == 0 ? 4 : (g.W % 4 == 0 ? 2 : (g.W % 2 == 0 ? 1 : 0));
+        const size_t items = V ? (size_t)planes * g.H * (g.W / (2 * V)) : (size_t)planes * g.H * g.W;
+        const size_t want = (items + 255) / 256, cap = (size_t)sm_count() * 16;
+        const int blocks = (int)(want < cap ? (want ? want : 1) : cap);
+        if (V == 4) interleave_classes_2x2_kernel<4><<<blocks, 256, 0, stream>>>(ptrs, (uint16_t*)out, planes, g.H, g.W);
+        else if (V == 2) interleave_classes_2x2_kernel<2><<<blocks, 256, 0, stream>>>(ptrs, (uint16_t*)out, planes, g.H, g.W);
+        else if (V == 1) interleave_classes_2x2_kernel<1><<<blocks, 256, 0, stream>>>(ptrs, (uint16_t*)out, planes, g.H, g.W);
+        else if (dtype == PCB_F32) interleave_classes_kernel<uint32_t><<<blocks, 256, 0, stream>>>(ptrs, (uint32_t*)out, planes, g.H, g.W, g.SH, g.SW);
+        else interleave_classes_kernel<uint16_t><<<blocks, 256, 0, stream>>>(ptrs, (uint16_t*)out, planes, g.H, g.W, g.SH, g.SW);
+        PCB_CUDA_TRY(cudaGetLastError());
+        return PCB_OK;
     }
     if (dtype == PCB_F32) {
         PCB_CUDA_TRY(cudaMemsetAsync(status, 0, sizeof(int), stream));

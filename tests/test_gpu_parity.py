@@ -145,7 +145,10 @@ GENERAL_TENSOR_SHAPES = [
     (2, 32, 32, 12, 12, 1, 1, (2, 2), (0, 0, 0, 0)),     # strided 1x1: 6 x 6 compact planes (4-pixel vectors), staged general kernel
     (5, 32, 128, 7, 7, 1, 1, (1, 1), (0, 0, 0, 0)),      # whole 7 x 7 planes per tile (4 images, the last tile ragged): bulk-copy epilogue
     (2, 128, 256, 14, 14, 1, 1, (1, 1), (0, 0, 0, 0)),   # whole 14 x 14 planes, 64-channel K slices with three stages, both directions
-    (3, 128, 128, 14, 14, 3, 3, (2, 2), (1, 1, 1, 1)),   # bulk-copy epilogue behind a 3x3 stride-2 layer (7 x 7 output planes)
+    (3, 128, 128, 14, 14, 3, 3, (2, 2), (1, 1, 1, 1)),   # bulk-copy epilogue behind a 3x3 stride-2 layer (7 x 7 output planes); backward-data by stride classes
+    (2, 128, 64, 10, 12, 3, 3, (2, 2), (0, 0, 1, 1)),    # stride classes with SAME-style padding (first tap of a class at 0 or 1)
+    (1, 128, 32, 9, 11, 3, 2, (1, 2), (1, 0, 1, 1)),     # stride classes along one axis only, odd planes (scalar interleave)
+    (1, 128, 16, 9, 9, 5, 5, (2, 2), (2, 2, 2, 2)),      # stride classes of a 5x5 layer: 3x3, 3x2, 2x3 and 2x2 taps
 ]
 
 
