@@ -376,7 +376,7 @@ def run(batch, steps, warmup, image=224, quiet=False):
             dist.barrier()
         torch.cuda.synchronize()
 
-    for _ in range(max(3, warmup)):
+    for _ in range(max(5, warmup)):                              # the first steps grow the device workspace
         loss = model.train_step(images, labels, world)
     sync()
     e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
