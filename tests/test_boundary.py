@@ -64,9 +64,11 @@ def test_c_abi_geometry_and_validation_without_gpu(built_lib):
         assert built_lib.pcb_qconv2d_engine_for(ctypes.byref(p), pass_) == _lib.ENGINE_TENSOR
     p.dtype = _lib.PCB_F32                                   # fp32: error-compensated TF32 on the tensor cores
     assert built_lib.pcb_qconv2d_engine_for(ctypes.byref(p), 0) == _lib.ENGINE_TENSOR
-    p.variant = _lib.VARIANT_8_PRODUCT                       # the factorised form exists on the CUDA cores only
+    p.variant = _lib.VARIANT_8_PRODUCT                       # automatic engine: the request is a speed preference
+    assert built_lib.pcb_qconv2d_engine_for(ctypes.byref(p), 0) == _lib.ENGINE_TENSOR
+    p.engine = _lib.ENGINE_SIMT                              # the factorised kernels themselves run on the CUDA cores
     assert built_lib.pcb_qconv2d_engine_for(ctypes.byref(p), 0) == _lib.ENGINE_SIMT
-    p.engine = _lib.ENGINE_TENSOR
+    p.engine = _lib.ENGINE_TENSOR                            # taken literally: the tensor cores have no 8-product kernel
     assert built_lib.pcb_qconv2d_engine_for(ctypes.byref(p), 0) == _lib.PCB_ERR_UNSUPPORTED
 
 

@@ -16,6 +16,10 @@ pytestmark = pytest.mark.gpu
 
 GOLDEN = os.path.join(os.path.dirname(__file__), "golden", "reference_kats.json")
 
+# (formulation, engine): under the automatic engine the 8-product request is a speed preference (tensor-core kernels where
+# they exist, the factorised CUDA-core kernels elsewhere); the CUDA-core engine runs the factorised kernels always
+FORMULATIONS = [("16p", "auto"), ("8p", "auto"), ("8p", "simt")]
+
 # n, ci, co, h, w, kh, kw, stride, pad(t,l,b,r)
 CONV_SHAPES = [
     (2, 3, 5, 7, 6, 3, 3, (1, 1), (1, 1, 1, 1)),
@@ -62,25 +66,25 @@ def test_reference_kats_on_gpu(gpu, oracle):
 
 @pytest.mark.parametrize("shape", CONV_SHAPES)
 @pytest.mark.parametrize("dtype", ["f32", "f16", "bf16"])
-@pytest.mark.parametrize("variant", ["16p", "8p"])
-def test_conv_fwd_bwd_vs_oracle(gpu, oracle, shape, dtype, variant):
+@pytest.mark.parametrize("variant,engine", FORMULATIONS)
+def test_conv_fwd_bwd_vs_oracle(gpu, oracle, shape, dtype, variant, engine):
     n, ci, co, h, w_, kh, kw, stride, pad = shape
     x = gpu.rounded(uniform(1, (4 * n, ci, h, w_)), dtype)
     w = gpu.rounded(uniform(2, (4, co, ci, kh, kw)), dtype)
     b = gpu.rounded(uniform(3, (4, co)), dtype)
     ov = oracle.VARIANT_16P if variant == "16p" else oracle.VARIANT_8P
     ref = oracle.conv2d_fwd(x, w, b, stride, (1, 1), pad, oracle.QUATERNION, ov)
-    got = gpu.run_conv_fwd(x, w, b, stride, pad, dtype, variant, "auto")
+    got = gpu.run_conv_fwd(x, w, b, stride, pad, dtype, variant, engine)
     _check(got, ref, dtype, gpu, "y")
-    nob = gpu.run_conv_fwd(x, w, None, stride, pad, dtype, variant, "auto")
+    nob = gpu.run_conv_fwd(x, w, None, stride, pad, dtype, variant, engine)
     _check(nob, oracle.conv2d_fwd(x, w, None, stride, (1, 1), pad, oracle.QUATERNION, ov), dtype, gpu, "y (no bias)")
 
     dy = gpu.rounded(normal(4, ref.shape), dtype)
     rdw, rdx = oracle.conv2d_bwd(x, w, dy, stride, (1, 1), pad, oracle.QUATERNION, ov, True)
-    dw, dx = gpu.run_conv_bwd(x, w, dy, stride, pad, dtype, variant, "auto", True)
+    dw, dx = gpu.run_conv_bwd(x, w, dy, stride, pad, dtype, variant, engine, True)
     _check(dw, rdw, dtype, gpu, "dw")
     _check(dx, rdx, dtype, gpu, "dx")
-    dw2, none = gpu.run_conv_bwd(x, w, dy, stride, pad, dtype, variant, "auto", False)
+    dw2, none = gpu.run_conv_bwd(x, w, dy, stride, pad, dtype, variant, engine, False)
     assert none is None
     _check(dw2, rdw, dtype, gpu, "dw (no input gradient)")
 
@@ -296,20 +300,20 @@ DENSE_SHAPES = [(3, 5, 7), (8, 16, 4), (1, 1, 1), (32, 64, 48), (17, 130, 70)]
 
 @pytest.mark.parametrize("shape", DENSE_SHAPES)
 @pytest.mark.parametrize("dtype", ["f32", "f16", "bf16"])
-@pytest.mark.parametrize("variant", ["16p", "8p"])
+@pytest.mark.parametrize("variant,engine", FORMULATIONS)
 @pytest.mark.parametrize("oi", [False, True])
-def test_dense_fwd_bwd_vs_oracle(gpu, oracle, shape, dtype, variant, oi):
+def test_dense_fwd_bwd_vs_oracle(gpu, oracle, shape, dtype, variant, engine, oi):
     b_, i, o = shape
     x = gpu.rounded(normal(31, (4 * b_, i)), dtype)
     w = gpu.rounded(normal(32, (4, o, i) if oi else (4, i, o), std=(2.0 / (4 * i)) ** 0.5), dtype)
     bias = gpu.rounded(uniform(33, (4, o)), dtype)
     ov = oracle.VARIANT_16P if variant == "16p" else oracle.VARIANT_8P
     ref = oracle.dense_fwd(x, w, bias, oi, oracle.QUATERNION, ov)
-    got = gpu.run_dense_fwd(x, w, bias, oi, dtype, variant, "auto")
+    got = gpu.run_dense_fwd(x, w, bias, oi, dtype, variant, engine)
     _check(got, ref, dtype, gpu, "y")
     dy = gpu.rounded(normal(34, ref.shape), dtype)
     rdw, rdx = oracle.dense_bwd(x, w, dy, oi, oracle.QUATERNION, ov, True)
-    dw, dx = gpu.run_dense_bwd(x, w, dy, oi, dtype, variant, "auto", True)
+    dw, dx = gpu.run_dense_bwd(x, w, dy, oi, dtype, variant, engine, True)
     _check(dw, rdw, dtype, gpu, "dw")
     _check(dx, rdx, dtype, gpu, "dx")
 
@@ -318,10 +322,11 @@ def test_baseline_config1_conv3x3_fp32(gpu, oracle):
     """Single quaternion conv2d forward, fp32: N=8, 16->16 channels, 32x32, 3x3, stride 1, pad 1, U[-1,1]."""
     x = uniform(101, (4 * 8, 16, 32, 32))
     w = uniform(102, (4, 16, 16, 3, 3))
-    for variant, ov in (("16p", oracle.VARIANT_16P), ("8p", oracle.VARIANT_8P)):
+    for variant, engine in FORMULATIONS:
+        ov = oracle.VARIANT_16P if variant == "16p" else oracle.VARIANT_8P
         ref = oracle.conv2d_fwd(x, w, None, (1, 1), (1, 1), (1, 1, 1, 1), oracle.QUATERNION, ov)
-        got = gpu.run_conv_fwd(x, w, None, (1, 1), (1, 1, 1, 1), "f32", variant, "auto")
-        _check(got, ref, "f32", gpu, "config 1 " + variant)
+        got = gpu.run_conv_fwd(x, w, None, (1, 1), (1, 1, 1, 1), "f32", variant, engine)
+        _check(got, ref, "f32", gpu, "config 1 " + variant + " " + engine)
 
 
 def test_baseline_config2_dense_fp32(gpu, oracle):
@@ -330,11 +335,12 @@ def test_baseline_config2_dense_fp32(gpu, oracle):
     w = normal(202, (4, 512, 512), std=(2.0 / (4 * 512)) ** 0.5)
     bias = np.zeros((4, 512), np.float32)
     dy = normal(203, (4 * 256, 512))
-    for variant, ov in (("16p", oracle.VARIANT_16P), ("8p", oracle.VARIANT_8P)):
-        _check(gpu.run_dense_fwd(x, w, bias, False, "f32", variant, "auto"),
-               oracle.dense_fwd(x, w, bias, False, oracle.QUATERNION, ov), "f32", gpu, "config 2 y " + variant)
+    for variant, engine in FORMULATIONS:
+        ov = oracle.VARIANT_16P if variant == "16p" else oracle.VARIANT_8P
+        _check(gpu.run_dense_fwd(x, w, bias, False, "f32", variant, engine),
+               oracle.dense_fwd(x, w, bias, False, oracle.QUATERNION, ov), "f32", gpu, "config 2 y " + variant + " " + engine)
         rdw, rdx = oracle.dense_bwd(x, w, dy, False, oracle.QUATERNION, ov, True)
-        dw, dx = gpu.run_dense_bwd(x, w, dy, False, "f32", variant, "auto", True)
+        dw, dx = gpu.run_dense_bwd(x, w, dy, False, "f32", variant, engine, True)
         _check(dw, rdw, "f32", gpu, "config 2 dw " + variant)
         _check(dx, rdx, "f32", gpu, "config 2 dx " + variant)
 
@@ -346,11 +352,12 @@ def test_baseline_config3_pointwise_fp16_reduced_batch(gpu, oracle):
     x = gpu.rounded(normal(301, (4 * 1, 128, 56, 56)), "f16")
     w = gpu.rounded(normal(302, (4, 256, 128, 1, 1), std=(2.0 / (4 * 128)) ** 0.5), "f16")
     pad, stride = (0, 0, 0, 0), (1, 1)
-    for variant, ov in (("16p", oracle.VARIANT_16P), ("8p", oracle.VARIANT_8P)):
+    for variant, engine in FORMULATIONS:
+        ov = oracle.VARIANT_16P if variant == "16p" else oracle.VARIANT_8P
         ref = oracle.conv2d_fwd(x, w, None, stride, (1, 1), pad, oracle.QUATERNION, ov)
-        _check(gpu.run_conv_fwd(x, w, None, stride, pad, "f16", variant, "auto"), ref, "f16", gpu, "config 3 y " + variant)
+        _check(gpu.run_conv_fwd(x, w, None, stride, pad, "f16", variant, engine), ref, "f16", gpu, "config 3 y " + variant)
         dy = gpu.rounded(normal(303, ref.shape), "f16")
         rdw, rdx = oracle.conv2d_bwd(x, w, dy, stride, (1, 1), pad, oracle.QUATERNION, ov, True)
-        dw, dx = gpu.run_conv_bwd(x, w, dy, stride, pad, "f16", variant, "auto", True)
+        dw, dx = gpu.run_conv_bwd(x, w, dy, stride, pad, "f16", variant, engine, True)
         _check(dw, rdw, "f16", gpu, "config 3 dw " + variant)
         _check(dx, rdx, "f16", gpu, "config 3 dx " + variant)
