@@ -417,7 +417,8 @@ void stage_activations(int fmt, const void* src, void* dst, int planes, int C, i
 // Backward-data: Wexp[tap][m = l*Ci + ci][k = d*Cop + co] = s(l,d) * w[l^d][co][ci][taps-1-tap]   (flipped taps)
 template <typename T>
 __global__ void pack_filters_kernel(const T* __restrict__ w, T* __restrict__ wexp, int Co, int Ci, int taps, int Mp, int Kp,
-                                    int Cp /*padded channels of the reduced side*/, int transposed, int nc, int ga, unsigned long long neg) {
+                                    int Cp /*padded channels of the reduced side*/, int transposed, int nc, int ga, unsigned long long neg,
+                                    int w_io = 0 /*dense filters stored [r][ci][co], one tap*/) {
     // one row (tap, m) of the expanded matrix per threadIdx.y; the row is decoded once, the threads of a row walk k
     const int Cm = transposed ? Ci : Co;     // channels on the M side
     const int Ck = transposed ? Co : Ci;     // channels on the K side
@@ -432,9 +433,14 @@ __global__ void pack_filters_kernel(const T* __restrict__ w, T* __restrict__ wex
             const bool comp_ok = cm_comp < nc && ck_comp < nc;
             const bool negative = comp_ok && alg_negative(neg, l, d);
             // forward: w[r][co = cm][ci = ck][tap]; backward-data: w[r][co = ck][ci = cm][tap]
-            const T* src = comp_ok ? w + ((size_t)alg_pair(ga, l, d) * Co + (transposed ? 0 : cm)) * Ci * taps + (size_t)(transposed ? cm : 0) * taps + src_tap
-                                   : nullptr;
-            const size_t ck_stride = transposed ? (size_t)Ci * taps : (size_t)taps;
+            const T* src = nullptr;
+            size_t ck_stride = transposed ? (size_t)Ci * taps : (size_t)taps;
+            if (comp_ok && !w_io)
+                src = w + ((size_t)alg_pair(ga, l, d) * Co + (transposed ? 0 : cm)) * Ci * taps + (size_t)(transposed ? cm : 0) * taps + src_tap;
+            if (comp_ok && w_io) {       // [r][ci][co]: forward walks ci (stride Co) at co = cm, backward-data walks co at ci = cm
+                src = w + (size_t)alg_pair(ga, l, d) * Ci * Co + (transposed ? (size_t)cm * Co : (size_t)cm);
+                ck_stride = transposed ? 1 : (size_t)Co;
+            }
             for (int ck = threadIdx.x; ck < Cp; ck += blockDim.x) {
                 float v = 0.f;
                 if (comp_ok && ck < Ck) { v = DType<T>::load(src + ck * ck_stride); if (negative) v = -v; }
@@ -743,9 +749,18 @@ qconv_filter_xmajor_tc_kernel(const __grid_constant__ CUtensorMap map_x, const _
 
 // scratch [tap][r][co][ci] fp32 -> dw [r][co][ci][tap] in the tensor type
 template <typename T>
-__global__ void unpack_filter_grad_kernel(const float* __restrict__ src, T* __restrict__ dw, int taps, size_t per_tap) {
+__global__ void unpack_filter_grad_kernel(const float* __restrict__ src, T* __restrict__ dw, int taps, size_t per_tap, int dw_io = 0,
+                                          int Co = 0, int Ci = 0) {
     const size_t total = per_tap * taps;
     for (size_t idx = (size_t)blockIdx.x * blockDim.x + threadIdx.x; idx < total; idx += (size_t)gridDim.x * blockDim.x) {
+        if (dw_io) {     // dense: one tap, gradient written input-major [r][ci][co]
+            const int co = (int)(idx % Co);
+            const size_t rest = idx / Co;
+            const int ci = (int)(rest % Ci);
+            const size_t r = rest / Ci;
+            DType<T>::store(dw + idx, src[(r * Co + co) * Ci + ci]);
+            continue;
+        }
         const int tap = (int)(idx % taps);
         const size_t e = idx / taps;
         DType<T>::store(dw + idx, src[(size_t)tap * per_tap + e]);
@@ -794,9 +809,9 @@ Plan make_plan(Pass pass, const Geom& g) {
 bool conv_tc_supported(Pass pass, int dtype, int variant, const Geom& g) {
     if (pass != PASS_FWD && pass != PASS_BWD_DATA) return false;
     if (dtype != PCB_F16 && dtype != PCB_BF16) return false;
-    if (variant != PCB_VARIANT_16_PRODUCT || g.w_io || g.dw_io) return false;
+    if (variant != PCB_VARIANT_16_PRODUCT) return false;
+    if (g.w_io && g.KH * g.KW != 1) return false;                       // input-major filters: dense layers (1x1 images, one tap)
     if (g.real_in && pass != PASS_FWD) return false;
-    if (g.H * g.W == 1) return false;                                   // dense layers stay on the CUDA-core kernels
     if (g.SH > 2 || g.SW > 2) return false;
     if (pass == PASS_BWD_DATA) {
         if ((g.KH - 1) * g.DH < g.PT || (g.KW - 1) * g.DW < g.PL) return false;
@@ -832,10 +847,10 @@ int conv_tc_launch(Pass pass, int dtype, const Geom& g, const void* w, const voi
         stage_activations(fmt, act, xp, pl.LK * g.Nb, pl.Cin, pl.Hin, pl.Win, pl.Hp, pl.Wp, pl.Cp, pl.pad_top, pl.pad_left, pl.ins_h, pl.ins_w, stream);
         if (fmt == 0) {
             pack_filters_kernel<__half><<<wblocks, wthreads, 0, stream>>>((const __half*)w, (__half*)wexp, g.Co, g.Ci, taps, pl.Mp, pl.Kp, pl.Cp,
-                                                                    pass == PASS_BWD_DATA ? 1 : 0, g.nc, g.ga, g.neg);
+                                                                    pass == PASS_BWD_DATA ? 1 : 0, g.nc, g.ga, g.neg, g.w_io);
         } else {
             pack_filters_kernel<__nv_bfloat16><<<wblocks, wthreads, 0, stream>>>((const __nv_bfloat16*)w, (__nv_bfloat16*)wexp, g.Co, g.Ci, taps,
-                                                                           pl.Mp, pl.Kp, pl.Cp, pass == PASS_BWD_DATA ? 1 : 0, g.nc, g.ga, g.neg);
+                                                                           pl.Mp, pl.Kp, pl.Cp, pass == PASS_BWD_DATA ? 1 : 0, g.nc, g.ga, g.neg, g.w_io);
         }
         PCB_CUDA_TRY(cudaGetLastError());
     }
@@ -979,9 +994,9 @@ bool filter_xmajor(const Geom& g, const FilterPlan& f) {
 
 bool conv_filter_tc_supported(int dtype, int variant, const Geom& g) {
     if (dtype != PCB_F16 && dtype != PCB_BF16) return false;
-    if (variant != PCB_VARIANT_16_PRODUCT || g.w_io || g.dw_io) return false;
+    if (variant != PCB_VARIANT_16_PRODUCT) return false;
+    if (g.dw_io && g.KH * g.KW != 1) return false;                      // input-major gradient: dense layers
     if (g.real_in && !filter_xmajor(g, make_filter_plan(g))) return false;
-    if (g.H * g.W == 1) return false;
     if (g.SH > 2 || g.SW > 2) return false;
     const FilterPlan f = make_filter_plan(g);
     if (f.Hp > 65535 || f.Wp > 65535 || f.xp_bytes + f.dyp_bytes > (size_t)12 << 30) return false;
@@ -1082,8 +1097,8 @@ int conv_filter_tc_launch(int dtype, const Geom& g, const void* dy, const void* 
     PCB_CUDA_TRY(cudaGetLastError());
     const size_t per_tap = (size_t)g.nc * g.Co * g.Ci, total = per_tap * taps;
     const int blocks = (int)((total + 255) / 256 < 2368 ? (total + 255) / 256 : 2368);
-    if (fmt == 0) unpack_filter_grad_kernel<__half><<<blocks, 256, 0, stream>>>(acc, (__half*)dw, taps, per_tap);
-    else unpack_filter_grad_kernel<__nv_bfloat16><<<blocks, 256, 0, stream>>>(acc, (__nv_bfloat16*)dw, taps, per_tap);
+    if (fmt == 0) unpack_filter_grad_kernel<__half><<<blocks, 256, 0, stream>>>(acc, (__half*)dw, taps, per_tap, g.dw_io, g.Co, g.Ci);
+    else unpack_filter_grad_kernel<__nv_bfloat16><<<blocks, 256, 0, stream>>>(acc, (__nv_bfloat16*)dw, taps, per_tap, g.dw_io, g.Co, g.Ci);
     PCB_CUDA_TRY(cudaGetLastError());
     return PCB_OK;
 }

@@ -72,6 +72,18 @@ def test_c_abi_geometry_and_validation_without_gpu(built_lib):
     assert built_lib.pcb_qconv2d_engine_for(ctypes.byref(p), 0) == _lib.PCB_ERR_UNSUPPORTED
 
 
+def test_dense_kernel_family_selection(built_lib):
+    """Dense layers of every dtype go to the tensor cores (fp32 as error-compensated TF32, 16-bit through the general
+    kernels with input-major filters and the always-input-major filter gradient)."""
+    for dtype in (_lib.PCB_F32, _lib.PCB_F16, _lib.PCB_BF16):
+        for oi in (0, 1):
+            d = _lib.DenseDesc(dtype=dtype, batch=256, in_features=512, out_features=512, filter_oi=oi, has_bias=1, require_input_grad=1)
+            for pass_ in range(3):
+                assert built_lib.pcb_qdense_engine_for(ctypes.byref(d), pass_) == _lib.ENGINE_TENSOR, (dtype, oi, pass_)
+            d.engine = _lib.ENGINE_SIMT
+            assert built_lib.pcb_qdense_engine_for(ctypes.byref(d), 0) == _lib.ENGINE_SIMT
+
+
 def test_reference_same_padding_descriptor():
     with open(GOLDEN) as f:
         (case,) = [c for c in json.load(f)["cases"] if c["op"] == "output_shape"]
