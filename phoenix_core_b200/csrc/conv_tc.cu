@@ -397,15 +397,20 @@ __global__ void pack_activations_kernel(const T* __restrict__ x, T* __restrict__
     }
 }
 
-// Host dispatch of the activation staging: the 4-pixel form where it applies, the general form otherwise.
+// Host dispatch of the activation staging: the 4- or 2-pixel form where it applies, the general form otherwise.
 // cb > 0 selects the channel-block layout of the filter-gradient kernels (Nb images per component).
 void stage_activations(int fmt, const void* src, void* dst, int planes, int C, int H, int W, int Hp, int Wp, int Cp, int pad_top, int pad_left,
                        int ins_h, int ins_w, cudaStream_t stream, int cb = 0, int Nb = 1) {
     const size_t total = (size_t)planes * Hp * Wp * (Cp / 8);
-    if (pack_rows4_ok(src, W, Wp, pad_left, ins_h, ins_w)) {
+    const int px = pack_rows_px(src, W, Wp, pad_left, ins_h, ins_w);
+    if (px == 4) {
         const int blocks = grid_cap(total / 4 + 1, 256, 16);
-        if (fmt == 0) pack_rows4_kernel<__half><<<blocks, 256, 0, stream>>>((const __half*)src, (__half*)dst, planes, C, H, W, Hp, Wp, Cp / 8, pad_top, pad_left, 0, cb, Nb);
-        else pack_rows4_kernel<__nv_bfloat16><<<blocks, 256, 0, stream>>>((const __nv_bfloat16*)src, (__nv_bfloat16*)dst, planes, C, H, W, Hp, Wp, Cp / 8, pad_top, pad_left, 0, cb, Nb);
+        if (fmt == 0) pack_rows_kernel<__half, 4><<<blocks, 256, 0, stream>>>((const __half*)src, (__half*)dst, planes, C, H, W, Hp, Wp, Cp / 8, pad_top, pad_left, 0, cb, Nb);
+        else pack_rows_kernel<__nv_bfloat16, 4><<<blocks, 256, 0, stream>>>((const __nv_bfloat16*)src, (__nv_bfloat16*)dst, planes, C, H, W, Hp, Wp, Cp / 8, pad_top, pad_left, 0, cb, Nb);
+    } else if (px == 2) {
+        const int blocks = grid_cap(total / 2 + 1, 256, 16);
+        if (fmt == 0) pack_rows_kernel<__half, 2><<<blocks, 256, 0, stream>>>((const __half*)src, (__half*)dst, planes, C, H, W, Hp, Wp, Cp / 8, pad_top, pad_left, 0, cb, Nb);
+        else pack_rows_kernel<__nv_bfloat16, 2><<<blocks, 256, 0, stream>>>((const __nv_bfloat16*)src, (__nv_bfloat16*)dst, planes, C, H, W, Hp, Wp, Cp / 8, pad_top, pad_left, 0, cb, Nb);
     } else {
         const int blocks = grid_cap(total, 256, 16);
         if (fmt == 0) pack_activations_kernel<__half><<<blocks, 256, 0, stream>>>((const __half*)src, (__half*)dst, planes, C, H, W, Hp, Wp, Cp, pad_top, pad_left, ins_h, ins_w, cb, Nb);

@@ -527,13 +527,13 @@ int narrow_tc_launch(Pass pass, int dtype, const Geom& g, const void* w, const v
     {
         const size_t total = (size_t)pl.LK * g.Nb * 2 * pl.Hp * pl.Wp;
         const int blocks = grid_cap(total, 256, 16), wblocks = grid_cap((size_t)taps * NM * Kp, 256, 8);
-        const bool fast = !pl.s2d && pack_rows4_ok(act, pl.Win, pl.Wp, pl.pad_left, pl.ins_h, pl.ins_w);
+        const bool fast = !pl.s2d && pack_rows_px(act, pl.Win, pl.Wp, pl.pad_left, pl.ins_h, pl.ins_w) == 4;
         const int fblocks = grid_cap(total / 4 + 1, 256, 16);
         if (fast && fmt == 0) {
-            pack_rows4_kernel<__half><<<fblocks, 256, 0, stream>>>((const __half*)act, (__half*)xp, pl.LK * g.Nb, src_c, pl.Hin, pl.Win, pl.Hp, pl.Wp, 2,
+            pack_rows_kernel<__half, 4><<<fblocks, 256, 0, stream>>>((const __half*)act, (__half*)xp, pl.LK * g.Nb, src_c, pl.Hin, pl.Win, pl.Hp, pl.Wp, 2,
                                                                   pl.pad_top, pl.pad_left, 1);
         } else if (fast) {
-            pack_rows4_kernel<__nv_bfloat16><<<fblocks, 256, 0, stream>>>((const __nv_bfloat16*)act, (__nv_bfloat16*)xp, pl.LK * g.Nb, src_c, pl.Hin, pl.Win,
+            pack_rows_kernel<__nv_bfloat16, 4><<<fblocks, 256, 0, stream>>>((const __nv_bfloat16*)act, (__nv_bfloat16*)xp, pl.LK * g.Nb, src_c, pl.Hin, pl.Win,
                                                                          pl.Hp, pl.Wp, 2, pl.pad_top, pl.pad_left, 1);
         } else if (fmt == 0) {
             pack_planar_kernel<__half><<<blocks, 256, 0, stream>>>((const __half*)act, (__half*)xp, pl.LK * g.Nb, src_c, pl.Hin, pl.Win, pl.Hp, pl.Wp,
@@ -653,10 +653,10 @@ int narrow_filter_tc_launch(int dtype, const Geom& g, const void* dy, const void
         // x: padded planar copy (space-to-depth for the stride-2 stem); dy: planar copy rounded up to whole tiles
         auto stage = [&](const void* src, void* dst, int planes_in, int C, int H, int W, int Hp, int Wp, int groups, int pt, int pleft, int s2d) {
             const size_t total = (size_t)planes_in * groups * Hp * Wp;
-            if (!s2d && pack_rows4_ok(src, W, Wp, pleft, 1, 1)) {
+            if (!s2d && pack_rows_px(src, W, Wp, pleft, 1, 1) == 4) {
                 const int blocks = grid_cap(total / 4 + 1, 256, 16);
-                if (fmt == 0) pack_rows4_kernel<__half><<<blocks, 256, 0, stream>>>((const __half*)src, (__half*)dst, planes_in, C, H, W, Hp, Wp, groups, pt, pleft, 1);
-                else pack_rows4_kernel<__nv_bfloat16><<<blocks, 256, 0, stream>>>((const __nv_bfloat16*)src, (__nv_bfloat16*)dst, planes_in, C, H, W, Hp, Wp, groups, pt, pleft, 1);
+                if (fmt == 0) pack_rows_kernel<__half, 4><<<blocks, 256, 0, stream>>>((const __half*)src, (__half*)dst, planes_in, C, H, W, Hp, Wp, groups, pt, pleft, 1);
+                else pack_rows_kernel<__nv_bfloat16, 4><<<blocks, 256, 0, stream>>>((const __nv_bfloat16*)src, (__nv_bfloat16*)dst, planes_in, C, H, W, Hp, Wp, groups, pt, pleft, 1);
             } else {
                 const int blocks = grid_cap(total, 256, 16);
                 if (fmt == 0) pack_planar_kernel<__half><<<blocks, 256, 0, stream>>>((const __half*)src, (__half*)dst, planes_in, C, H, W, Hp, Wp, groups, pt, pleft, 1, 1, s2d);

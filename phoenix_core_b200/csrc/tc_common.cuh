@@ -52,34 +52,40 @@ __device__ __forceinline__ void red_add_f32x4(float* addr, float a, float b, flo
     asm volatile("red.global.add.v4.f32 [%0], {%1, %2, %3, %4};" ::"l"(addr), "f"(a), "f"(b), "f"(c), "f"(d) : "memory");
 }
 
-// Staging copy of NCHW activations for the TMA-fed kernels, fast form (no zero insertion, W a multiple of 4, 8-byte
-// aligned rows): one thread moves 8 channels x 4 pixels -- eight 8-byte loads (a warp reads 256 contiguous bytes per
-// channel) and four 16-byte stores. Destination: channels-last xp[plane][hp][wp][Cp] (planar == 0), planar
-// xp[plane][c / 8][hp][wp][8] (planar == 1), or -- cb > 0 -- blocks of cb channels with the block index outermost,
+// Staging copy of NCHW activations for the TMA-fed kernels, fast form (no zero insertion, W a multiple of PX = 4 or 2,
+// rows aligned to PX elements): one thread moves 8 channels x PX pixels -- eight loads of 2 PX bytes (a warp reads 64 PX
+// contiguous bytes per channel) and PX 16-byte stores. Destination: channels-last xp[plane][hp][wp][Cp] (planar == 0),
+// planar xp[plane][c / 8][hp][wp][8] (planar == 1), or -- cb > 0 -- blocks of cb channels with the block index outermost,
 // xp[comp * (Cp / cb) + c / cb][img][hp][wp][cb] where plane = comp * Nb + img (one TMA box can then span the channel
 // blocks of several components). Zero outside the image and for c >= C. The threads at the ends of a row also write
 // the padding columns.
-template <typename T>
-__global__ void pack_rows4_kernel(const T* __restrict__ x, T* __restrict__ xp, int planes, int C, int H, int W, int Hp, int Wp, int groups,
-                                  int pad_top, int pad_left, int planar, int cb = 0, int Nb = 1) {
-    const int Wq = W / 4;
-    const size_t total = (size_t)planes * groups * Hp * Wq;
+template <typename T, int PX>
+__global__ void pack_rows_kernel(const T* __restrict__ x, T* __restrict__ xp, int planes, int C, int H, int W, int Hp, int Wp, int groups,
+                                 int pad_top, int pad_left, int planar, int cb = 0, int Nb = 1) {
+    const int Wq = W / PX;
+    const unsigned total = (unsigned)planes * groups * Hp * Wq;         // 32-bit indices: staged copies stay below 2^32 / 8 threads
     const int Cp = groups * 8;
-    for (size_t idx = (size_t)blockIdx.x * blockDim.x + threadIdx.x; idx < total; idx += (size_t)gridDim.x * blockDim.x) {
+    for (unsigned idx = blockIdx.x * blockDim.x + threadIdx.x; idx < total; idx += gridDim.x * blockDim.x) {
         const int q = (int)(idx % Wq);
-        size_t rest = idx / Wq;
+        unsigned rest = idx / Wq;
         const int hp = (int)(rest % Hp); rest /= Hp;
         const int grp = (int)(rest % groups);
         const int plane = (int)(rest / groups);
         const int ih = hp - pad_top;
         const bool row_in = ih >= 0 && ih < H;
-        alignas(8) T v[8][4];
+        alignas(8) T v[8][PX];
 #pragma unroll
         for (int e = 0; e < 8; ++e) {
             const int c = grp * 8 + e;
-            uint2 raw = make_uint2(0u, 0u);
-            if (row_in && c < C) raw = __ldg(reinterpret_cast<const uint2*>(x + (((size_t)plane * C + c) * H + ih) * W + 4 * q));
-            *reinterpret_cast<uint2*>(v[e]) = raw;
+            if (PX == 4) {
+                uint2 raw = make_uint2(0u, 0u);
+                if (row_in && c < C) raw = __ldg(reinterpret_cast<const uint2*>(x + (((size_t)plane * C + c) * H + ih) * W + 4 * q));
+                *reinterpret_cast<uint2*>(v[e]) = raw;
+            } else {
+                uint32_t raw = 0u;
+                if (row_in && c < C) raw = __ldg(reinterpret_cast<const uint32_t*>(x + (((size_t)plane * C + c) * H + ih) * W + 2 * q));
+                *reinterpret_cast<uint32_t*>(v[e]) = raw;
+            }
         }
         size_t blk_plane = 0;                       // (block, image) index and channel offset inside the block
         int c_lo = 0;
@@ -93,11 +99,11 @@ __global__ void pack_rows4_kernel(const T* __restrict__ x, T* __restrict__ xp, i
             return planar ? xp + ((((size_t)plane * groups + grp) * Hp + hp) * Wp + wp) * 8 : xp + (((size_t)plane * Hp + hp) * Wp + wp) * Cp + grp * 8;
         };
 #pragma unroll
-        for (int j = 0; j < 4; ++j) {
+        for (int j = 0; j < PX; ++j) {
             alignas(16) T o[8];
 #pragma unroll
             for (int e = 0; e < 8; ++e) o[e] = v[e][j];
-            *reinterpret_cast<uint4*>(dst(pad_left + 4 * q + j)) = *reinterpret_cast<const uint4*>(o);
+            *reinterpret_cast<uint4*>(dst(pad_left + PX * q + j)) = *reinterpret_cast<const uint4*>(o);
         }
         const uint4 zero = make_uint4(0u, 0u, 0u, 0u);
         if (q == 0)
@@ -106,9 +112,12 @@ __global__ void pack_rows4_kernel(const T* __restrict__ x, T* __restrict__ xp, i
             for (int wp = pad_left + W; wp < Wp; ++wp) *reinterpret_cast<uint4*>(dst(wp)) = zero;
     }
 }
-// Whether pack_rows4_kernel applies.
-inline bool pack_rows4_ok(const void* x, int W, int Wp, int pad_left, int ins_h, int ins_w) {
-    return ins_h == 1 && ins_w == 1 && W % 4 == 0 && W >= 4 && pad_left >= 0 && pad_left + W <= Wp && reinterpret_cast<uintptr_t>(x) % 8 == 0;
+// Pixels per thread pack_rows_kernel can take for this tensor: 4, 2, or 0 (the general staging kernel must run).
+inline int pack_rows_px(const void* x, int W, int Wp, int pad_left, int ins_h, int ins_w) {
+    if (ins_h != 1 || ins_w != 1 || pad_left < 0 || pad_left + W > Wp) return 0;
+    if (W % 4 == 0 && W >= 4 && reinterpret_cast<uintptr_t>(x) % 8 == 0) return 4;
+    if (W % 2 == 0 && W >= 2 && reinterpret_cast<uintptr_t>(x) % 4 == 0) return 2;
+    return 0;
 }
 
 typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*, const cuuint64_t*,
