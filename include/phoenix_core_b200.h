@@ -35,7 +35,7 @@ extern "C" {
 typedef enum {
     PCB_OK = 0,
     PCB_ERR_INVALID_ARGUMENT = -1,  /* bad shape / null pointer; the C++ layer rethrows std::invalid_argument */
-    PCB_ERR_UNSUPPORTED = -2,       /* groups != 1, NHWC, ...: no CPU fallback exists                        */
+    PCB_ERR_UNSUPPORTED = -2,       /* no kernel takes the request (e.g. grouped NHWC): no CPU fallback exists */
     PCB_ERR_WORKSPACE = -3,         /* workspace missing or too small                                        */
     PCB_ERR_CUDA = -4,              /* a CUDA runtime call failed; see pcb_last_error_message()              */
     PCB_ERR_DEVICE_TIMEOUT = -5,    /* a bounded device-side wait expired (reported by pcb_check_device_status) */
@@ -84,7 +84,7 @@ typedef struct {
     int32_t stride_h, stride_w;
     int32_t dilation_h, dilation_w; /* >= 1                                                           */
     int32_t pad_top, pad_left, pad_bottom, pad_right;
-    int32_t groups;                 /* must be 1                                                      */
+    int32_t groups;                 /* ci = input channels of one group; co (total) divisible by it  */
     int32_t has_bias;               /* forward only                                                   */
     int32_t require_input_grad;     /* backward only                                                  */
     int32_t real_valued_input;      /* forward/backward-filter: x is [n, ci, h, w] (type-0 input)     */

@@ -36,11 +36,17 @@ int conv_geom(const pcb_conv2d_desc* d, Geom& g) {
         set_error("invalid convolution geometry");
         return PCB_ERR_INVALID_ARGUMENT;
     }
-    if (d->groups != 1) { set_error("grouped convolution is not supported (groups = %d)", d->groups); return PCB_ERR_UNSUPPORTED; }
+    if (d->groups < 1 || d->co % d->groups != 0) { set_error("invalid groups (%d groups, %d output channels)", d->groups, d->co); return PCB_ERR_INVALID_ARGUMENT; }
+    if (d->groups != 1 && (d->data_format != PCB_LAYOUT_NCHW || d->filter_layout != PCB_FILTER_OIHW)) {
+        set_error("grouped convolution takes NCHW tensors and OIHW filters only (groups = %d)", d->groups);
+        return PCB_ERR_UNSUPPORTED;
+    }
     if (d->dilation_h < 1 || d->dilation_w < 1) { set_error("dilation must be >= 1"); return PCB_ERR_INVALID_ARGUMENT; }
     if (d->variant != PCB_VARIANT_16_PRODUCT && d->variant != PCB_VARIANT_8_PRODUCT) { set_error("unknown variant"); return PCB_ERR_INVALID_ARGUMENT; }
     if (!algebra_setup(d->algebra, g)) { set_error("unknown algebra %d", d->algebra); return PCB_ERR_INVALID_ARGUMENT; }
-    g.Nb = d->n; g.Ci = d->ci; g.Co = d->co; g.H = d->h; g.W = d->w;
+    // groups: the descriptor's ci is the filters' input channels (the input tensor holds ci * groups), co the total
+    g.groups = d->groups;
+    g.Nb = d->n; g.Ci = d->ci; g.Co = d->co / d->groups; g.H = d->h; g.W = d->w;
     g.KH = d->kh; g.KW = d->kw; g.SH = d->stride_h; g.SW = d->stride_w; g.DH = d->dilation_h; g.DW = d->dilation_w;
     g.PT = d->pad_top; g.PL = d->pad_left;
     g.HO = out_size(d->h, d->kh, d->dilation_h, d->stride_h, d->pad_top, d->pad_bottom);
@@ -51,11 +57,11 @@ int conv_geom(const pcb_conv2d_desc* d, Geom& g) {
         set_error("unknown tensor layout (data format %d, filter layout %d)", d->data_format, d->filter_layout);
         return PCB_ERR_INVALID_ARGUMENT;
     }
-    set_conv_strides(g, d->data_format, d->filter_layout, g.Ci, g.Co);
-    g.plain = (d->data_format == PCB_LAYOUT_NCHW && d->filter_layout == PCB_FILTER_OIHW) ? 1 : 0;
-    const long long xn = (long long)(g.real_in ? 1 : g.nc) * g.Nb * g.Ci * g.H * g.W;
-    const long long yn = (long long)g.nc * g.Nb * g.Co * g.HO * g.WO;
-    const long long wn = (long long)g.nc * g.Co * g.Ci * g.KH * g.KW;
+    set_conv_strides(g, d->data_format, d->filter_layout, g.Ci * g.groups, g.Co * g.groups);
+    g.plain = (d->data_format == PCB_LAYOUT_NCHW && d->filter_layout == PCB_FILTER_OIHW && g.groups == 1) ? 1 : 0;
+    const long long xn = (long long)(g.real_in ? 1 : g.nc) * g.Nb * g.Ci * g.groups * g.H * g.W;
+    const long long yn = (long long)g.nc * g.Nb * g.Co * g.groups * g.HO * g.WO;
+    const long long wn = (long long)g.nc * g.Co * g.groups * g.Ci * g.KH * g.KW;
     if (xn > MAX_NUMEL || yn > MAX_NUMEL || wn > MAX_NUMEL || g.H > 32767 || g.W > 32767) {
         set_error("tensor too large for 32-bit element offsets");
         return PCB_ERR_TOO_LARGE;
@@ -78,7 +84,7 @@ int dense_geom(const pcb_dense_desc* d, Geom& g) {
     g.xp = g.Ci; g.xc = 1; g.xh = g.xw = 0; g.yp = g.Co; g.yc = 1; g.yh = g.yw = 0;
     g.wr = g.Ci * g.Co; g.wh = g.ww = 0; g.wo = g.w_io ? 1 : g.Ci; g.wi = g.w_io ? g.Co : 1;
     g.dr = g.wr; g.dkh = g.dkw = 0; g.dco = 1; g.dci = g.Co;
-    g.bias_ld = g.Co; g.plain = 1;
+    g.bias_ld = g.Co; g.plain = 1; g.groups = 1;
     if ((long long)g.nc * g.Nb * g.Ci > MAX_NUMEL || (long long)g.nc * g.Nb * g.Co > MAX_NUMEL || (long long)g.nc * g.Ci * g.Co > MAX_NUMEL) {
         set_error("tensor too large for 32-bit element offsets");
         return PCB_ERR_TOO_LARGE;
@@ -129,6 +135,58 @@ int run_pass(Pass pass, int dtype, int variant, int engine, const Geom& g, const
     return simt_launch(pass, dtype, variant, g, a, b, bias, out, scratch, stream);
 }
 
+// Grouped convolution (reference: the groups argument of the scalar convolutions, src/backend/cudnn/conv2d.hpp:126-127):
+// one pass per group on the CUDA-core kernels, which address every tensor through strides -- a group is a channel slice
+// of x, y and the filters. The filter gradient of a group is produced contiguously in the workspace and copied into its
+// slice (component r of the gradient is Co_total * Ci * taps elements apart, a group's slice Co * Ci * taps wide).
+size_t group_slice_bytes(int dtype, const Geom& g) {
+    return (((size_t)g.nc * g.Co * g.Ci * g.KH * g.KW * dtype_size(dtype)) + 255) / 256 * 256;
+}
+
+size_t conv_workspace_bytes(Pass pass, int dtype, int variant, int engine, const Geom& g) {
+    if (g.groups == 1) return workspace_bytes(pass, dtype, variant, engine, g);
+    return workspace_bytes(pass, dtype, variant, PCB_ENGINE_SIMT, g) + (pass == PASS_BWD_FILTER ? group_slice_bytes(dtype, g) : 0);
+}
+
+int run_conv_pass(Pass pass, int dtype, int variant, int engine, const Geom& g, const void* a, const void* b, const void* bias,
+                  void* out, void* workspace, size_t ws_bytes, cudaStream_t stream) {
+    if (g.groups == 1) return run_pass(pass, dtype, variant, engine, g, a, b, bias, out, workspace, ws_bytes, stream);
+    if (engine == PCB_ENGINE_TENSOR) { set_error("no tensor-core kernel for grouped convolutions"); return PCB_ERR_UNSUPPORTED; }
+    const size_t es = dtype_size(dtype);
+    const size_t need = conv_workspace_bytes(pass, dtype, variant, engine, g);
+    if (need > WS_HEADER && (workspace == nullptr || ws_bytes < need)) {
+        set_error("workspace of %zu bytes required, %zu given", need, workspace ? ws_bytes : (size_t)0);
+        return PCB_ERR_WORKSPACE;
+    }
+    const size_t taps = (size_t)g.KH * g.KW;
+    const size_t x_step = (size_t)g.Ci * g.H * g.W * es, y_step = (size_t)g.Co * g.HO * g.WO * es;
+    const size_t w_step = (size_t)g.Co * g.Ci * taps * es, bias_step = (size_t)g.Co * es;
+    const char* ca = static_cast<const char*>(a);
+    const char* cb = static_cast<const char*>(b);
+    char* co = static_cast<char*>(out);
+    for (int gi = 0; gi < g.groups; ++gi) {
+        int rc;
+        if (pass == PASS_FWD) {            // a = filters, b = x, out = y
+            rc = run_pass(pass, dtype, variant, PCB_ENGINE_SIMT, g, ca + gi * w_step, cb + gi * x_step,
+                          bias ? static_cast<const char*>(bias) + gi * bias_step : nullptr, co + gi * y_step, workspace, ws_bytes, stream);
+        } else if (pass == PASS_BWD_DATA) { // a = filters, b = dy, out = dx
+            rc = run_pass(pass, dtype, variant, PCB_ENGINE_SIMT, g, ca + gi * w_step, cb + gi * y_step, nullptr, co + gi * x_step, workspace, ws_bytes, stream);
+        } else {                           // a = dy, b = x, out = dw: contiguous slice first
+            Geom gs = g;
+            gs.dr = g.Co * g.Ci * (int)taps;
+            const size_t inner = workspace_bytes(pass, dtype, variant, PCB_ENGINE_SIMT, g);   // a multiple of 256 bytes
+            char* tmp = static_cast<char*>(workspace) + inner;                             // the slice follows the pass's own scratch
+            rc = run_pass(pass, dtype, variant, PCB_ENGINE_SIMT, gs, ca + gi * y_step, cb + gi * x_step, nullptr, tmp, workspace, inner, stream);
+            if (rc == PCB_OK) {
+                const size_t row = (size_t)g.Co * g.Ci * taps * es;
+                PCB_CUDA_TRY(cudaMemcpy2DAsync(co + gi * w_step, row * g.groups, tmp, row, row, g.nc, cudaMemcpyDeviceToDevice, stream));
+            }
+        }
+        if (rc != PCB_OK) return rc;
+    }
+    return PCB_OK;
+}
+
 }  // namespace
 }  // namespace pcb
 
@@ -165,14 +223,14 @@ int pcb_conv2d_output_size(const pcb_conv2d_desc* desc, int32_t* out_h, int32_t*
 size_t pcb_qconv2d_fwd_workspace_size(const pcb_conv2d_desc* desc) {
     Geom g;
     if (conv_geom(desc, g) != PCB_OK) return 0;
-    return workspace_bytes(PASS_FWD, desc->dtype, variant_for(g, desc->variant), desc->engine, g);
+    return conv_workspace_bytes(PASS_FWD, desc->dtype, variant_for(g, desc->variant), desc->engine, g);
 }
 
 size_t pcb_qconv2d_bwd_workspace_size(const pcb_conv2d_desc* desc) {
     Geom g;
     if (conv_geom(desc, g) != PCB_OK) return 0;
-    const size_t a = workspace_bytes(PASS_BWD_DATA, desc->dtype, variant_for(g, desc->variant), desc->engine, g);
-    const size_t b = workspace_bytes(PASS_BWD_FILTER, desc->dtype, variant_for(g, desc->variant), desc->engine, g);
+    const size_t a = conv_workspace_bytes(PASS_BWD_DATA, desc->dtype, variant_for(g, desc->variant), desc->engine, g);
+    const size_t b = conv_workspace_bytes(PASS_BWD_FILTER, desc->dtype, variant_for(g, desc->variant), desc->engine, g);
     return a > b ? a : b;
 }
 
@@ -198,7 +256,7 @@ int pcb_qconv2d_fwd(const pcb_conv2d_desc* desc, const void* x, const void* w, c
     if (g.Nb == 0) return PCB_OK;   // empty input: silent no-op, as the reference (src/conv2d.hpp:81-82)
     if (!x || !w || !y || (g.has_bias && !bias)) { set_error("null tensor pointer"); return PCB_ERR_INVALID_ARGUMENT; }
     if (g.real_in && g.has_bias) { set_error("bias addition is not supported for real-valued inputs"); return PCB_ERR_UNSUPPORTED; }
-    return run_pass(PASS_FWD, desc->dtype, variant_for(g, desc->variant), desc->engine, g, w, x, bias, y, workspace, workspace_bytes_, (cudaStream_t)stream);
+    return run_conv_pass(PASS_FWD, desc->dtype, variant_for(g, desc->variant), desc->engine, g, w, x, bias, y, workspace, workspace_bytes_, (cudaStream_t)stream);
 }
 
 int pcb_qconv2d_bwd_data(const pcb_conv2d_desc* desc, const void* w, const void* dy, void* dx,
@@ -209,7 +267,7 @@ int pcb_qconv2d_bwd_data(const pcb_conv2d_desc* desc, const void* w, const void*
     if (g.Nb == 0) return PCB_OK;
     if (g.real_in) { set_error("input gradient required for a real-valued input tensor"); return PCB_ERR_UNSUPPORTED; }
     if (!w || !dy || !dx) { set_error("null tensor pointer"); return PCB_ERR_INVALID_ARGUMENT; }
-    return run_pass(PASS_BWD_DATA, desc->dtype, variant_for(g, desc->variant), desc->engine, g, w, dy, nullptr, dx, workspace, workspace_bytes_, (cudaStream_t)stream);
+    return run_conv_pass(PASS_BWD_DATA, desc->dtype, variant_for(g, desc->variant), desc->engine, g, w, dy, nullptr, dx, workspace, workspace_bytes_, (cudaStream_t)stream);
 }
 
 int pcb_qconv2d_bwd_filter(const pcb_conv2d_desc* desc, const void* x, const void* dy, void* dw,
@@ -219,11 +277,11 @@ int pcb_qconv2d_bwd_filter(const pcb_conv2d_desc* desc, const void* x, const voi
     if (rc != PCB_OK) return rc;
     if (!dw) { set_error("null tensor pointer"); return PCB_ERR_INVALID_ARGUMENT; }
     if (g.Nb == 0) {   // empty input: zero filter gradient, as the reference (src/conv2d.hpp:341-344)
-        PCB_CUDA_TRY(cudaMemsetAsync(dw, 0, (size_t)g.nc * g.Co * g.Ci * g.KH * g.KW * dtype_size(desc->dtype), (cudaStream_t)stream));
+        PCB_CUDA_TRY(cudaMemsetAsync(dw, 0, (size_t)g.nc * g.Co * g.groups * g.Ci * g.KH * g.KW * dtype_size(desc->dtype), (cudaStream_t)stream));
         return PCB_OK;
     }
     if (!x || !dy) { set_error("null tensor pointer"); return PCB_ERR_INVALID_ARGUMENT; }
-    return run_pass(PASS_BWD_FILTER, desc->dtype, variant_for(g, desc->variant), desc->engine, g, dy, x, nullptr, dw, workspace, workspace_bytes_, (cudaStream_t)stream);
+    return run_conv_pass(PASS_BWD_FILTER, desc->dtype, variant_for(g, desc->variant), desc->engine, g, dy, x, nullptr, dw, workspace, workspace_bytes_, (cudaStream_t)stream);
 }
 
 int pcb_qconv2d_bwd_filter_noalloc(const pcb_conv2d_desc* desc, const void* x, const void* dy, void* dw, void* stream) {
@@ -231,6 +289,7 @@ int pcb_qconv2d_bwd_filter_noalloc(const pcb_conv2d_desc* desc, const void* x, c
     int rc = conv_geom(desc, g);
     if (rc != PCB_OK) return rc;
     if (!dw) { set_error("null tensor pointer"); return PCB_ERR_INVALID_ARGUMENT; }
+    if (g.groups != 1) { set_error("the allocation-free filter gradient takes one group"); return PCB_ERR_UNSUPPORTED; }
     if ((size_t)g.nc * g.Co * g.Ci * g.KH * g.KW > simt_static_scratch_capacity()) {
         set_error("filter gradient of %zu elements exceeds the built-in scratch of %zu elements",
                   (size_t)g.nc * g.Co * g.Ci * g.KH * g.KW, simt_static_scratch_capacity());

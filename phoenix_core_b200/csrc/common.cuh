@@ -58,6 +58,7 @@ struct Geom {
     int wr, wo, wi, wh, ww, dr, dco, dci, dkh, dkw;
     int bias_ld;         // bias is [components][bias_ld]
     int plain;           // NCHW activations, OIHW (or dense) filters, one group: the layouts the tensor-core kernels read
+    int groups;          // host side only: groups of the convolution; Ci / Co above are the channels of ONE group
 };
 
 enum { LAYOUT_NCHW = 0, LAYOUT_NHWC = 1 };

@@ -477,7 +477,7 @@ qgemm8_simt_kernel(SimtParams p, const T* __restrict__ a, const T* __restrict__ 
     }
 
     // epilogue: recombine the 8 lanes into the 4 components and write them
-    const size_t out_comp = PASS == PASS_FWD ? y_comp : (PASS == PASS_BWD_DATA ? x_comp : w_comp);
+    const size_t out_comp = PASS == PASS_FWD ? y_comp : (PASS == PASS_BWD_DATA ? x_comp : (size_t)g.dr);   // the gradient has its own component stride
 #pragma unroll
     for (int i = 0; i < 4; ++i) {
         const int4 me = mtab[ty * 4 + i];

@@ -158,10 +158,25 @@ static void gpuTests() {
             conv2DFwd<Device, float>(device, device, input, kernel, nullptr, output, descriptor);
             CHECK(same(output, {0, 2, 2, 4, 3, 6, 5, 8}));
         }
-        {   // grouped convolution: not built, and there is no CPU fallback
+        {   // grouped convolution: two groups of two input channels and one output channel each; every component of
+            // input channel c is c + 1 and every filter entry 1, so an output quaternion is (-2, 2, 2, 2) times the
+            // channel sum of its group: 1 + 2 = 3 and 3 + 4 = 7
             AllocatedTensor<Device, float> input(device, {4, 4, 2, 2}), kernel(device, {4, 2, 2, 1, 1}), output(device, {4, 2, 2, 2});
+            std::vector<float> xin, win(4 * 2 * 2, 1.0f), want;
+            for (int comp = 0; comp < 4; ++comp)
+                for (int c = 0; c < 4; ++c)
+                    for (int px = 0; px < 4; ++px) xin.push_back((float)(c + 1));
+            for (int comp = 0; comp < 4; ++comp)
+                for (int co = 0; co < 2; ++co)
+                    for (int px = 0; px < 4; ++px) want.push_back((comp == 0 ? -2.0f : 2.0f) * (co == 0 ? 3.0f : 7.0f));
+            input = xin; kernel = win;
             Conv2DFwdDescriptor descriptor(input.getShape(), kernel.getShape(), 1, 1, Padding::VALID, {}, 2, Algebra::QUATERNION, DataFormat::NCHW, FilterLayout::OIHW, false);
-            CHECK_THROWS((conv2DFwd<Device, float>(device, device, input, kernel, nullptr, output, descriptor)), std::runtime_error);
+            conv2DFwd<Device, float>(device, device, input, kernel, nullptr, output, descriptor);
+            CHECK(same(output, want));
+            // grouped channels-last tensors: not built, and there is no CPU fallback
+            Conv2DFwdDescriptor nhwc(Shape({4, 2, 2, 4}), Shape({4, 2, 1, 1, 2}), 1, 1, Padding::VALID, {}, 2, Algebra::QUATERNION, DataFormat::NHWC, FilterLayout::OHWI, false);
+            AllocatedTensor<Device, float> input2(device, {4, 2, 2, 4}), kernel2(device, {4, 2, 1, 1, 2}), output2(device, {4, 2, 2, 2});
+            CHECK_THROWS((conv2DFwd<Device, float>(device, device, input2, kernel2, nullptr, output2, nhwc)), std::runtime_error);
         }
         {   // empty batch: forward is a no-op, backward zeroes the filter gradient
             AllocatedTensor<Device, float> input(device, {0, 3, 5, 5}), kernel(device, {4, 2, 3, 3, 3}), output(device, {0, 2, 3, 3}), kernelGrad(device, {4, 2, 3, 3, 3});

@@ -34,9 +34,9 @@ def host(t):
 
 
 def conv_descriptors(xshape, wshape, stride, pad, use_bias, need_dx, real_input=False, algebra=pcb.Algebra.QUATERNION,
-                     dilation=(1, 1)):
+                     dilation=(1, 1), groups=1):
     pt, pl, pb, pr = pad
-    args = (xshape, wshape, stride, dilation, pcb.Padding.EXPLICIT, (pt, pl, pb, pr), 1, algebra,
+    args = (xshape, wshape, stride, dilation, pcb.Padding.EXPLICIT, (pt, pl, pb, pr), groups, algebra,
             pcb.DataFormat.NCHW, pcb.FilterLayout.OIHW)
     fwd = pcb.Conv2DFwdDescriptor(*args, use_bias, real_input)
     bwd = pcb.Conv2DBwdDescriptor(*args, need_dx, real_input)
@@ -44,8 +44,8 @@ def conv_descriptors(xshape, wshape, stride, pad, use_bias, need_dx, real_input=
 
 
 def run_conv_fwd(x, w, bias, stride, pad, dtype, variant, engine, real_input=False, algebra=pcb.Algebra.QUATERNION,
-                 dilation=(1, 1)):
-    fwd, _ = conv_descriptors(x.shape, w.shape, stride, pad, bias is not None, False, real_input, algebra, dilation)
+                 dilation=(1, 1), groups=1):
+    fwd, _ = conv_descriptors(x.shape, w.shape, stride, pad, bias is not None, False, real_input, algebra, dilation, groups)
     xd, wd = dev(x, dtype), dev(w, dtype)
     bd = None if bias is None else dev(bias, dtype)
     y = torch.full(fwd.getOutputShape(), float("nan"), dtype=TORCH_DTYPES[dtype], device="cuda")
@@ -53,8 +53,8 @@ def run_conv_fwd(x, w, bias, stride, pad, dtype, variant, engine, real_input=Fal
     return host(y)
 
 
-def run_conv_bwd(x, w, dy, stride, pad, dtype, variant, engine, need_dx=True, algebra=pcb.Algebra.QUATERNION, dilation=(1, 1)):
-    _, bwd = conv_descriptors(x.shape, w.shape, stride, pad, False, need_dx, False, algebra, dilation)
+def run_conv_bwd(x, w, dy, stride, pad, dtype, variant, engine, need_dx=True, algebra=pcb.Algebra.QUATERNION, dilation=(1, 1), groups=1):
+    _, bwd = conv_descriptors(x.shape, w.shape, stride, pad, False, need_dx, False, algebra, dilation, groups)
     xd, wd, gd = dev(x, dtype), dev(w, dtype), dev(dy, dtype)
     dw = torch.full(w.shape, float("nan"), dtype=TORCH_DTYPES[dtype], device="cuda")
     dx = torch.full(x.shape, float("nan"), dtype=TORCH_DTYPES[dtype], device="cuda") if need_dx else None

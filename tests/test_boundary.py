@@ -45,9 +45,15 @@ def test_c_abi_geometry_and_validation_without_gpu(built_lib):
     oh, ow = ctypes.c_int32(), ctypes.c_int32()
     assert built_lib.pcb_conv2d_output_size(ctypes.byref(d), ctypes.byref(oh), ctypes.byref(ow)) == 0
     assert (oh.value, ow.value) == (32, 32)
-    d.groups = 2
-    assert built_lib.pcb_conv2d_output_size(ctypes.byref(d), None, None) == _lib.PCB_ERR_UNSUPPORTED
+    d.groups = 2                                             # two groups of 8 output channels: fine (CUDA-core kernels)
+    assert built_lib.pcb_conv2d_output_size(ctypes.byref(d), None, None) == 0
+    assert built_lib.pcb_qconv2d_engine_for(ctypes.byref(d), 0) == _lib.ENGINE_SIMT
+    d.groups = 3                                             # 16 output channels do not split into 3 groups
+    assert built_lib.pcb_conv2d_output_size(ctypes.byref(d), None, None) == _lib.PCB_ERR_INVALID_ARGUMENT
     assert b"group" in built_lib.pcb_last_error_message()
+    d.groups, d.data_format = 2, 1                           # grouped channels-last tensors: not built
+    assert built_lib.pcb_conv2d_output_size(ctypes.byref(d), None, None) == _lib.PCB_ERR_UNSUPPORTED
+    d.data_format = 0
     d.groups, d.kh = 1, 0
     assert built_lib.pcb_conv2d_output_size(ctypes.byref(d), None, None) == _lib.PCB_ERR_INVALID_ARGUMENT
     # fp16 backward-filter needs fp32 scratch; fp32 forward needs only the status header

@@ -225,3 +225,32 @@ def test_conv_layouts_vs_oracle(gpu, oracle, data_format, filter_layout, name, d
     pcb.conv2DBwd(gpu.dev(xl, dtype), gpu.dev(wl, dtype), gpu.dev(dyl, dtype), dw, dx, bwd, ctx)
     _check(_from_layout(gpu.host(dx), data_format), rdx, dtype, gpu, "dx")
     _check(_from_layout(gpu.host(dw), filter_layout), rdw, dtype, gpu, "dw")
+
+
+@pytest.mark.parametrize("dtype,variant", [("f32", "16p"), ("f32", "8p"), ("f16", "16p"), ("bf16", "8p")])
+@pytest.mark.parametrize("groups,ci,co", [(2, 6, 4), (4, 4, 8), (8, 8, 8)])      # the last one is depthwise
+def test_grouped_conv_vs_oracle(gpu, oracle, dtype, variant, groups, ci, co):
+    """Grouped quaternion convolution (reference: the groups argument, src/conv2d.hpp:70-91, :329-353) against the oracle run
+    group by group on channel slices: forward with bias, both gradients."""
+    n, h, w_, k = 2, 9, 7, 3
+    cig, cog = ci // groups, co // groups
+    x = gpu.rounded(uniform(71, (4 * n, ci, h, w_)), dtype)
+    w = gpu.rounded(uniform(72, (4, co, cig, k, k)), dtype)
+    b = gpu.rounded(uniform(73, (4, co)), dtype)
+    stride, pad = (2, 1), (1, 1, 1, 1)
+    ov = oracle.VARIANT_16P if variant == "16p" else oracle.VARIANT_8P
+    ys = [oracle.conv2d_fwd(np.ascontiguousarray(x[:, g * cig:(g + 1) * cig]), np.ascontiguousarray(w[:, g * cog:(g + 1) * cog]),
+                            np.ascontiguousarray(b[:, g * cog:(g + 1) * cog]), stride, (1, 1), pad, oracle.QUATERNION, ov) for g in range(groups)]
+    ref = np.concatenate(ys, axis=1)
+    got = gpu.run_conv_fwd(x, w, b, stride, pad, dtype, variant, "auto", groups=groups)
+    assert got.shape == ref.shape
+    _check(got, ref, dtype, gpu, "y")
+    dy = gpu.rounded(normal(74, ref.shape), dtype)
+    dws, dxs = [], []
+    for g in range(groups):
+        dwg, dxg = oracle.conv2d_bwd(np.ascontiguousarray(x[:, g * cig:(g + 1) * cig]), np.ascontiguousarray(w[:, g * cog:(g + 1) * cog]),
+                                     np.ascontiguousarray(dy[:, g * cog:(g + 1) * cog]), stride, (1, 1), pad, oracle.QUATERNION, ov, True)
+        dws.append(dwg); dxs.append(dxg)
+    dw, dx = gpu.run_conv_bwd(x, w, dy, stride, pad, dtype, variant, "auto", True, groups=groups)
+    _check(dw, np.concatenate(dws, axis=1), dtype, gpu, "dw")
+    _check(dx, np.concatenate(dxs, axis=1), dtype, gpu, "dx")
