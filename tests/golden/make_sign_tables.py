@@ -13,7 +13,9 @@ import sys
 
 
 def main():
-    ref = sys.argv[1] if len(sys.argv) > 1 else "/root/reference"
+    if len(sys.argv) < 2:
+        sys.exit("usage: make_sign_tables.py /path/to/reference")
+    ref = sys.argv[1]
     text = open(os.path.join(ref, "src", "algebras.cc")).read()
     out = {"_comment": "Product tables of the reference (src/algebras.cc:5-145), transcribed as data by make_sign_tables.py: "
                        "entries are [left component (input), right component (filter), sign], D per output component."}
