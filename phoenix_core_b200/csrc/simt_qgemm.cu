@@ -383,7 +383,6 @@ qgemm8_simt_kernel(SimtParams p, const T* __restrict__ a, const T* __restrict__ 
     const int m0 = blockIdx.y * BM8, n0 = blockIdx.x * BN8;
     const int kbeg = blockIdx.z * p.k_per_split;
     const int kend = min(p.K, kbeg + p.k_per_split);
-    const int P = g.HO * g.WO, HW = g.H * g.W, TAPS = g.KH * g.KW;
     const size_t w_comp = (size_t)g.wr;                    // one component of the filters
     const size_t x_comp = (size_t)g.Nb * g.xp;             // one component of the input
     const size_t y_comp = (size_t)g.Nb * g.yp;             // one component of the output
