@@ -258,3 +258,43 @@ def test_library_orchestration_agrees_with_oracle(oracle, variant8):
     ddw, ddx = ro.dense_bwd(torch.from_numpy(xd), torch.from_numpy(wd), torch.from_numpy(gd), variant8)
     rddw, rddx = oracle.dense_bwd(xd, wd, gd, False, oracle.QUATERNION, v)
     assert rel_err(ddw.numpy(), rddw) < 1e-5 and rel_err(ddx.numpy(), rddx) < 1e-5
+
+
+@pytest.mark.parametrize("h,w_,kh,kw,stride,pad", [
+    (10, 12, 3, 3, (2, 2), (1, 1, 1, 1)),     # the ResNet downsampling layer
+    (10, 12, 3, 3, (2, 2), (0, 0, 1, 1)),     # SAME-style padding: the classes start at the other tap
+    (9, 11, 3, 2, (1, 2), (1, 0, 1, 1)),      # classes along one axis, odd planes
+    (9, 9, 5, 5, (2, 2), (2, 2, 2, 2)),       # 3 / 2 taps per class and axis
+    (8, 8, 1, 1, (2, 2), (0, 0, 0, 0)),       # strided 1x1: one class holds every tap, the others are zero
+    (11, 7, 7, 7, (2, 2), (2, 2, 3, 3)),      # the stem's geometry
+])
+def test_strided_backward_data_by_stride_classes(oracle, h, w_, kh, kw, stride, pad):
+    """The identity behind the GPU path's strided backward-data: input pixels of class (ih mod SH, iw mod SW) receive
+    only the taps r + S k' with r = (a + pad) mod S, and their gradient is a stride-1 correlation of dy with those taps,
+    dx[S i + a] = sum_k' dy[i + c - k'] w[r + S k'] with c = (a + pad) div S. Checked against the oracle's strided
+    backward-data pass (real algebra, one channel: the algebra and the channels do not enter the identity)."""
+    sh, sw = stride
+    pt, pl = pad[0], pad[1]
+    x = uniform(81, (1, 1, h, w_))
+    w = uniform(82, (1, 1, kh, kw))
+    y = oracle.conv2d_fwd(x, w, None, stride, (1, 1), pad, oracle.REAL)
+    dy = normal(83, y.shape)
+    _, dx_ref = oracle.conv2d_bwd(x, w, dy, stride, (1, 1), pad, oracle.REAL, oracle.VARIANT_16P, True)
+    ho, wo = y.shape[2], y.shape[3]
+    dx = np.zeros((h, w_), np.float64)
+    for a in range(sh):
+        for b in range(sw):
+            rh, ch = (a + pt) % sh, (a + pt) // sh
+            rw, cw = (b + pl) % sw, (b + pl) // sw
+            taps_h = range(0, (kh - rh + sh - 1) // sh) if rh < kh else range(0)
+            taps_w = range(0, (kw - rw + sw - 1) // sw) if rw < kw else range(0)
+            for i in range((h - a + sh - 1) // sh):
+                for j in range((w_ - b + sw - 1) // sw):
+                    acc = 0.0
+                    for u in taps_h:
+                        for v in taps_w:
+                            oh, ow = i + ch - u, j + cw - v
+                            if 0 <= oh < ho and 0 <= ow < wo:
+                                acc += float(dy[0, 0, oh, ow]) * float(w[0, 0, rh + sh * u, rw + sw * v])
+                    dx[sh * i + a, sw * j + b] = acc
+    assert rel_err(dx.astype(np.float32), dx_ref[0, 0]) < 1e-6
