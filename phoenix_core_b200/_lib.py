@@ -60,6 +60,7 @@ SYMBOLS = {
     "pcb_qconv2d_engine_for": (_i, [_cd, _i]),
     "pcb_qdense_engine_for": (_i, [_dd, _i]),
     "pcb_check_device_status": (_i, [_vp, _sz, _vp]),
+    "pcb_selftest_wait_expiry": (_i, [_cd, _vp, _vp, _vp, _vp, _sz, ctypes.c_longlong, _vp]),
     "pcb_aux_bn_relu_fwd": (_i, [_i, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _i, _i, _i, ctypes.c_float, _i, _vp]),
     "pcb_aux_bn_relu_bwd": (_i, [_i, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _vp]),
     "pcb_aux_maxpool3x3s2_fwd": (_i, [_i, _vp, _vp, _vp, _i, _i, _i, _vp]),

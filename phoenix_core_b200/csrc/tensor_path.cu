@@ -726,10 +726,8 @@ int tensor_launch(Pass pass, int dtype, int variant, const Geom& g, const void* 
         PCB_CUDA_TRY(cudaGetLastError());
         return PCB_OK;
     }
-    if (dtype == PCB_F32) {
-        PCB_CUDA_TRY(cudaMemsetAsync(status, 0, sizeof(int), stream));
-        return conv_tf32_launch(pass, g, a, b, bias, out, scratch, status, stream);
-    }
+    // the status word is cleared once per API call by the caller of this function; the kernels only OR into it
+    if (dtype == PCB_F32) return conv_tf32_launch(pass, g, a, b, bias, out, scratch, status, stream);
     TcParams p;
     p.g = g;
     p.pass = pass;
@@ -740,7 +738,6 @@ int tensor_launch(Pass pass, int dtype, int variant, const Geom& g, const void* 
     else                            { p.M = 4 * g.Co; p.N = g.Ci;      p.K = 4 * g.Nb * HW; }
     p.k_per_split = (p.K + TBK - 1) / TBK * TBK;
     p.atomic_out = 0;
-    PCB_CUDA_TRY(cudaMemsetAsync(status, 0, sizeof(int), stream));
     if (pointwise_tc_supported(pass, dtype, PCB_VARIANT_16_PRODUCT, g)) return pointwise_tc_launch(pass, dtype, g, a, b, bias, out, status, stream);
     if (pass != PASS_BWD_FILTER && narrow_tc_supported(pass, dtype, PCB_VARIANT_16_PRODUCT, g))
         return narrow_tc_launch(pass, dtype, g, a, b, bias, out, scratch, status, stream);

@@ -74,11 +74,14 @@ __device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
         : "=r"(ok) : "r"(bar), "r"(parity) : "memory");
     return ok != 0;
 }
-// Waits for the phase with the given parity to complete, for at most ~2^31 SM clocks (about a second).
-// On expiry ORs `code` into *status and returns false; the caller then skips its remaining work and
-// proceeds to the common teardown, so a lost signal can never hang the GPU.
+// Waits for the phase with the given parity to complete, for at most `limit` SM clocks (default ~2^31, about a
+// second). On expiry ORs `code` into *status and returns false; the caller then skips its remaining work and
+// proceeds to the common teardown, so a lost signal can never hang the GPU. Kernels only ever OR into the status
+// word: it is cleared once per API call by the host, so an expiry in an earlier launch of the call stays visible
+// (and makes the later launches of that call give up at their first slow wait).
 constexpr long long WAIT_LIMIT_CLOCKS = 1ll << 31;
-__device__ __forceinline__ bool mbar_wait_bounded(uint32_t bar, uint32_t parity, int* status, int code) {
+__device__ __forceinline__ bool mbar_wait_bounded(uint32_t bar, uint32_t parity, int* status, int code,
+                                                  long long limit = WAIT_LIMIT_CLOCKS) {
     if (mbar_try_wait(bar, parity)) return true;
     const long long t0 = clock64();
     while (true) {
@@ -86,7 +89,7 @@ __device__ __forceinline__ bool mbar_wait_bounded(uint32_t bar, uint32_t parity,
         for (int i = 0; i < 64; ++i)
             if (mbar_try_wait(bar, parity)) return true;
         if (*reinterpret_cast<volatile int*>(status) != 0) return false;   // another wait of this launch already expired
-        if (clock64() - t0 > WAIT_LIMIT_CLOCKS) {
+        if (clock64() - t0 > limit) {
             atomicOr(status, code);
             return false;
         }

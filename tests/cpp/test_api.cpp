@@ -85,6 +85,16 @@ static void cpuTests() {
         unsetenv("UPSTRIDE_MEMORY_OPTIMIZED"); unsetenv("UPSTRIDE_CONV_FP16_POLICY");
         Context d; CHECK(d.preferSpeedToMemory()); CHECK(!d.isFp16ConvForwardAllowed());
     }
+    {   // one device per CUDA stream, created on first use, dropped by cleanUp (reference: cudnn::Context::registerDevice).
+        // Stream handles are only used as keys here; nothing is launched.
+        cuda::Context context;
+        cudaStream_t s1 = reinterpret_cast<cudaStream_t>(0x10), s2 = reinterpret_cast<cudaStream_t>(0x20);
+        device::CUDA& a = context.registerDevice(s1);
+        device::CUDA& b = context.registerDevice(s2);
+        CHECK(&a != &b); CHECK(&context.registerDevice(s1) == &a); CHECK(context.getNumDevices() == 2);
+        CHECK(a.stream() == s1 && b.stream() == s2); CHECK(&a.getContext() == &context);
+        context.cleanUp(); CHECK(context.getNumDevices() == 0);
+    }
 }
 
 static bool same(const std::vector<float>& a, const std::vector<float>& b) { return a.size() == b.size() && std::equal(a.begin(), a.end(), b.begin()); }
@@ -177,6 +187,22 @@ static void gpuTests() {
             Conv2DFwdDescriptor nhwc(Shape({4, 2, 2, 4}), Shape({4, 2, 1, 1, 2}), 1, 1, Padding::VALID, {}, 2, Algebra::QUATERNION, DataFormat::NHWC, FilterLayout::OHWI, false);
             AllocatedTensor<Device, float> input2(device, {4, 2, 2, 4}), kernel2(device, {4, 2, 1, 1, 2}), output2(device, {4, 2, 2, 2});
             CHECK_THROWS((conv2DFwd<Device, float>(device, device, input2, kernel2, nullptr, output2, nhwc)), std::runtime_error);
+        }
+        {   // a device obtained from the per-stream registry runs on its own stream and reports a clean wait status
+            cuda::Context registry;
+            cudaStream_t stream = nullptr;
+            CHECK(cudaStreamCreate(&stream) == cudaSuccess);
+            Device& dev = registry.registerDevice(stream);
+            AllocatedTensor<Device, float> input(dev, {4, 1}), filter(dev, {4, 1, 1}), output(dev, {4, 1});
+            input = {1, 2, 3, 4}; filter = {5, 6, 7, 8};
+            DenseFwdDescriptor descriptor(input.getShape(), filter.getShape(), Algebra::QUATERNION, FilterLayout::IO, false);
+            denseFwd<Device, float>(dev, dev, input, filter, nullptr, output, descriptor);
+            dev.checkDeviceStatus();
+            CHECK(same(output, {-60, 12, 30, 24}));
+            CHECK(&registry.registerDevice(stream) == &dev);
+            dev.synchronize();
+            registry.cleanUp();
+            cudaStreamDestroy(stream);
         }
         {   // empty batch: forward is a no-op, backward zeroes the filter gradient
             AllocatedTensor<Device, float> input(device, {0, 3, 5, 5}), kernel(device, {4, 2, 3, 3, 3}), output(device, {0, 2, 3, 3}), kernelGrad(device, {4, 2, 3, 3, 3});

@@ -125,7 +125,7 @@ def test_pointwise_tensor_core_vs_oracle(gpu, oracle, shape, dtype):
     _check(dw, rdw, dtype, gpu, "dw")
     # and the two kernel families agree with each other far inside the tolerance
     simt = gpu.run_conv_fwd(x, w, b, stride, pad, dtype, "16p", "simt")
-    assert rel_err(got, simt) <= 4e-3 if dtype == "f16" else 2e-2
+    assert rel_err(got, simt) <= (4e-3 if dtype == "f16" else 2e-2)
 
 
 # shapes for the general implicit-GEMM tensor-core kernel (staged channels-last activations, expanded filters):

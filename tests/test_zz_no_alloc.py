@@ -1,4 +1,4 @@
-"""The allocation-free filter-gradient entry point, checked against the regular one.
+"""The allocation-free filter-gradient entry point, checked against the regular one and against the CPU oracle.
 
 Some hosts of the library cannot allocate device memory while running (a plugin inside a framework that owns
 the device heap through its own arena; a deployment with a memory plan frozen at start-up) and have no
@@ -16,47 +16,93 @@ from helpers import normal, rel_err
 
 pytestmark = pytest.mark.gpu
 
+TOL = {torch.float16: 2e-2, torch.bfloat16: 2e-2, torch.float32: 1e-5}     # the tolerances of the parity tests
 
-def _desc(_lib, dtype, n, ci, co, h, w, k, stride, pad, variant):
+
+def _desc(_lib, dtype, n, ci, co, h, w, k, stride, pad, variant, filter_layout=0):
     return _lib.ConvDesc(dtype=dtype, n=n, ci=ci, co=co, h=h, w=w, kh=k, kw=k, stride_h=stride, stride_w=stride,
                          dilation_h=1, dilation_w=1, pad_top=pad, pad_left=pad, pad_bottom=pad, pad_right=pad, groups=1,
-                         variant=variant, engine=_lib.ENGINE_SIMT)
+                         variant=variant, engine=_lib.ENGINE_SIMT, filter_layout=filter_layout)
 
 
-def _both(_lib, L, d, x, dy, wshape):
-    """Filter gradient through the new entry point and through the existing one (same kernels, workspace scratch)."""
-    stream = ctypes.c_void_p(torch.cuda.current_stream().cuda_stream)
-    dw_new = torch.full(wshape, float("nan"), dtype=x.dtype, device="cuda")
-    _lib.check(L.pcb_qconv2d_bwd_filter_noalloc(ctypes.byref(d), x.data_ptr(), dy.data_ptr(), dw_new.data_ptr(), stream))
+def _stream():
+    return ctypes.c_void_p(torch.cuda.current_stream().cuda_stream)
+
+
+def _new(_lib, L, d, x, dy, wshape):
+    dw = torch.full(wshape, float("nan"), dtype=x.dtype, device="cuda")
+    _lib.check(L.pcb_qconv2d_bwd_filter_noalloc(ctypes.byref(d), x.data_ptr(), dy.data_ptr(), dw.data_ptr(), _stream()))
+    return dw
+
+
+def _old(_lib, L, d, x, dy, wshape):
     ws = torch.empty(L.pcb_qconv2d_bwd_workspace_size(ctypes.byref(d)), dtype=torch.uint8, device="cuda")
-    dw_old = torch.full(wshape, float("nan"), dtype=x.dtype, device="cuda")
-    _lib.check(L.pcb_qconv2d_bwd_filter(ctypes.byref(d), x.data_ptr(), dy.data_ptr(), dw_old.data_ptr(), ws.data_ptr(),
-                                        ws.numel(), stream))
-    torch.cuda.synchronize()
-    return dw_new.float().cpu().numpy(), dw_old.float().cpu().numpy()
+    dw = torch.full(wshape, float("nan"), dtype=x.dtype, device="cuda")
+    _lib.check(L.pcb_qconv2d_bwd_filter(ctypes.byref(d), x.data_ptr(), dy.data_ptr(), dw.data_ptr(), ws.data_ptr(), ws.numel(), _stream()))
+    return dw
 
 
-def test_noalloc_filter_gradient_matches_regular_entry_point_twice():
+# dtype code name, torch dtype, n, ci, co, h, w, k, stride, pad, 8-product?, HWIO filter gradient?
+# Two calls in a row on different problems. Both reductions are long enough to be split over the grid, so both go
+# through the shared array, and the second filter is the smaller one: anything the first call left behind in the part
+# of the array the second call uses would show up in its result.
+CASES = [
+    ("PCB_F16", torch.float16, 4, 24, 40, 12, 10, 3, 1, 1, False, False),     # 34560 accumulators, reduction over 4*120 pixels
+    ("PCB_BF16", torch.bfloat16, 8, 16, 8, 16, 16, 1, 1, 0, True, False),     # 512 accumulators, reduction over 8*256 pixels
+    ("PCB_F32", torch.float32, 4, 8, 12, 14, 14, 3, 1, 1, False, False),      # fp32: the accumulator is dw itself
+    ("PCB_F16", torch.float16, 4, 8, 16, 12, 12, 3, 1, 1, False, True),       # HWIO filter-gradient layout
+]
+
+
+def test_noalloc_filter_gradient_matches_regular_entry_point_and_oracle(oracle):
     if not torch.cuda.is_available():
         pytest.skip("no CUDA device")
     from phoenix_core_b200 import _lib
     L = _lib.lib()
-    # two calls in a row on different problems: the second must not see what the first left in the shared array
-    cases = [
-        (_lib.PCB_F16, torch.float16, 4, 24, 40, 12, 10, 3, 1, 1, _lib.VARIANT_16_PRODUCT),
-        (_lib.PCB_BF16, torch.bfloat16, 3, 16, 8, 9, 9, 1, 2, 0, _lib.VARIANT_8_PRODUCT),
-    ]
-    for seed, (code, tdt, n, ci, co, h, w, k, stride, pad, variant) in enumerate(cases):
-        d = _desc(_lib, code, n, ci, co, h, w, k, stride, pad, variant)
+    for seed, (code, tdt, n, ci, co, h, w, k, stride, pad, eight, hwio) in enumerate(CASES):
+        variant = _lib.VARIANT_8_PRODUCT if eight else _lib.VARIANT_16_PRODUCT
+        d = _desc(_lib, getattr(_lib, code), n, ci, co, h, w, k, stride, pad, variant, 2 if hwio else 0)
         oh, ow = ctypes.c_int32(), ctypes.c_int32()
         _lib.check(L.pcb_conv2d_output_size(ctypes.byref(d), ctypes.byref(oh), ctypes.byref(ow)))
-        x = torch.from_numpy(normal(50 + seed, (4 * n, ci, h, w))).to(tdt).cuda()
-        dy = torch.from_numpy(normal(60 + seed, (4 * n, co, oh.value, ow.value))).to(tdt).cuda()
-        got, want = _both(_lib, L, d, x, dy, (4, co, ci, k, k))
+        xh = normal(50 + seed, (4 * n, ci, h, w))
+        gh = normal(60 + seed, (4 * n, co, oh.value, ow.value))
+        x, dy = torch.from_numpy(xh).to(tdt).cuda(), torch.from_numpy(gh).to(tdt).cuda()
+        wshape = (4, k, k, ci, co) if hwio else (4, co, ci, k, k)
+        got = _new(_lib, L, d, x, dy, wshape).float().cpu().numpy()
+        want = _old(_lib, L, d, x, dy, wshape).float().cpu().numpy()
         assert np.all(np.isfinite(got))
-        # same kernels, same inputs; only the order of the fp32 atomic additions may differ. 2e-2 is the
-        # tolerance the 16-bit parity tests use.
-        assert rel_err(got, want) <= 2e-2, rel_err(got, want)
+        # same kernels, same inputs; only the order of the fp32 atomic additions may differ
+        assert rel_err(got, want) <= TOL[tdt], (code, rel_err(got, want))
+        # and against the CPU oracle on the values the GPU saw (an error the two entry points share would pass the line above)
+        ov = oracle.VARIANT_8P if eight else oracle.VARIANT_16P
+        ref, _ = oracle.conv2d_bwd(x.float().cpu().numpy(), np.zeros((4, co, ci, k, k), np.float32), dy.float().cpu().numpy(),
+                                   (stride, stride), (1, 1), (pad, pad, pad, pad), oracle.QUATERNION, ov, False)
+        if hwio:
+            ref = np.ascontiguousarray(ref.transpose(0, 3, 4, 2, 1))
+        assert rel_err(got, ref) <= TOL[tdt], (code, rel_err(got, ref))
+
+
+def test_noalloc_call_allocates_no_device_memory():
+    if not torch.cuda.is_available():
+        pytest.skip("no CUDA device")
+    from phoenix_core_b200 import _lib
+    L = _lib.lib()
+    code, tdt, n, ci, co, h, w, k, stride, pad = _lib.PCB_F16, torch.float16, 4, 24, 40, 12, 10, 3, 1, 1
+    d = _desc(_lib, code, n, ci, co, h, w, k, stride, pad, _lib.VARIANT_16_PRODUCT)
+    x = torch.from_numpy(normal(70, (4 * n, ci, h, w))).to(tdt).cuda()
+    dy = torch.from_numpy(normal(71, (4 * n, co, 12, 10))).to(tdt).cuda()
+    dw = torch.empty((4, co, ci, k, k), dtype=tdt, device="cuda")
+    call = lambda: _lib.check(L.pcb_qconv2d_bwd_filter_noalloc(ctypes.byref(d), x.data_ptr(), dy.data_ptr(), dw.data_ptr(), _stream()))
+    call()                                              # warm call: resolves the array's address on this device
+    torch.cuda.synchronize()
+    free_before, _ = torch.cuda.mem_get_info()
+    reserved_before, allocs_before = torch.cuda.memory_reserved(), torch.cuda.memory_stats().get("allocation.all.allocated", 0)
+    call()
+    torch.cuda.synchronize()
+    free_after, _ = torch.cuda.mem_get_info()
+    assert free_after == free_before                    # the driver handed out nothing
+    assert torch.cuda.memory_reserved() == reserved_before
+    assert torch.cuda.memory_stats().get("allocation.all.allocated", 0) == allocs_before    # nor did torch's allocator
 
 
 def test_noalloc_rejects_sizes_beyond_the_built_in_array():
