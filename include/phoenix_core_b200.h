@@ -59,9 +59,11 @@ typedef enum { PCB_FILTER_OIHW = 0, PCB_FILTER_OHWI = 1, PCB_FILTER_HWIO = 2 } p
 /* Formulation of the Hamilton product (reference: UPSTRIDE_MEMORY_OPTIMIZED, src/backend/backend.hpp:58):
  * 16 real products through the 4x4 signed block, or the factorised 8-product form. The reference picks the
  * 8-product form when the caller prefers speed to memory; under PCB_ENGINE_AUTO this backend reads the request the
- * same way: problems a tensor-core kernel takes run on it (one formulation, no lane temporaries, faster than
- * either CUDA-core form), everything else runs the factorised CUDA-core kernels. PCB_ENGINE_SIMT and
- * PCB_ENGINE_TENSOR take the field literally (the tensor cores have no 8-product kernel: PCB_ERR_UNSUPPORTED). */
+ * same way: problems a 16-product tensor-core kernel takes run on it (measured faster than the factorised tensor-core
+ * kernels on this hardware, and without lane temporaries either), everything else runs the factorised CUDA-core
+ * kernels. PCB_ENGINE_SIMT and PCB_ENGINE_TENSOR take the field literally: the tensor cores have factorised kernels
+ * for pointwise (1x1, stride 1) fp16 / bf16 quaternion layers, all three passes, with the lane sums formed in shared
+ * memory and the recombination in the epilogue; other 8-product requests return PCB_ERR_UNSUPPORTED there. */
 typedef enum { PCB_VARIANT_16_PRODUCT = 0, PCB_VARIANT_8_PRODUCT = 1 } pcb_variant;
 
 /* fp16 convolution policy (reference: UPSTRIDE_CONV_FP16_POLICY, src/backend/backend.hpp:36-66). The field is

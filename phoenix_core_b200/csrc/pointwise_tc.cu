@@ -24,6 +24,8 @@
 // delayed the MMA warp's own instruction issue by ~4000 cycles per tile; the bulk stores do not).
 // Every mbarrier wait is bounded; an expired wait sets the status word and the CTA leaves through the common
 // teardown.
+#include <cstdlib>
+
 #include "tc_common.cuh"
 #include "tensor_path.cuh"
 
@@ -68,7 +70,7 @@ __device__ __forceinline__ uint64_t make_desc_kmajor_sw64(uint32_t smem_addr) {
     return (uint64_t)((smem_addr & 0x3FFFFu) >> 4) | ((uint64_t)1 << 16) | ((uint64_t)(512 >> 4) << 32) | DESC_VERSION_SM100 | DESC_SWIZZLE_64B;
 }
 
-template <bool BWD>
+template <bool BWD, int EDGE_J>
 __global__ void __launch_bounds__(U_THREADS, 1)
 qconv_pointwise_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant__ CUtensorMap map_act,
                           const __grid_constant__ CUtensorMap map_out, UParams p, const uint16_t* __restrict__ bias, int* __restrict__ status) {
@@ -76,15 +78,17 @@ qconv_pointwise_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __gri
     const int t = threadIdx.x, warp = t >> 5, lane = t & 31;
     uint8_t* base = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
     uint64_t* bars = reinterpret_cast<uint64_t*>(base + OPERAND_BYTES + OUT_BYTES);
-    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 2 * U_STAGES + 7);
+    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 2 * U_STAGES + 8);
     const uint32_t tiles_addr = smem_u32(base);
     const uint32_t full_bar = smem_u32(bars), empty_bar = smem_u32(bars + U_STAGES);
     const uint32_t a_full = smem_u32(bars + 2 * U_STAGES + 5);
     const uint32_t epi_bar = smem_u32(bars + 2 * U_STAGES + 6);   // the eight epilogue warps among themselves
     const uint32_t out_addr = tiles_addr + OPERAND_BYTES;         // staging for the TMA store
     // one "accumulator drained" barrier per component, so the next tile's MMAs can start on component 0 while
-    // the epilogue is still reading components 1..3
-    const uint32_t tmem_full = smem_u32(bars + 2 * U_STAGES), tmem_empty = smem_u32(bars + 2 * U_STAGES + 1);
+    // the epilogue is still reading components 1..3; one "accumulators complete" barrier per PAIR of components
+    // (0,1 and 2,3), so the epilogue drains the first pair while the last MMAs of the tile still run on the second
+    const uint32_t tmem_empty = smem_u32(bars + 2 * U_STAGES + 1);
+    const uint32_t tmem_full0 = smem_u32(bars + 2 * U_STAGES), tmem_full1 = smem_u32(bars + 2 * U_STAGES + 7);
 
     const int n_tiles = p.n_px_tiles * p.n_c_tiles;
     const int n_k = (p.Cred + KS - 1) / KS;
@@ -96,7 +100,8 @@ qconv_pointwise_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __gri
 
     if (t == 0) {
         for (int s = 0; s < U_STAGES; ++s) { mbar_init(full_bar + 8 * s, 1); mbar_init(empty_bar + 8 * s, 1); }
-        mbar_init(tmem_full, 1);
+        mbar_init(tmem_full0, 1);
+        mbar_init(tmem_full1, 1);
         mbar_init(a_full, 1);
         mbar_init(epi_bar, 8);
         for (int o = 0; o < 4; ++o) mbar_init(tmem_empty + 8 * o, 8);
@@ -167,40 +172,51 @@ qconv_pointwise_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __gri
                 if (!ok) break;
                 tc_fence_after_sync();
                 const uint32_t a_addr = a_slot(k, s), b_addr = b_slot(s);
-                if (k == 0) {
-                    // first K slice of a tile: the accumulators in two pairs, each pair as soon as the epilogue of the
-                    // previous tile has drained it. Inside a pair the MMAs alternate between the two accumulators:
-                    // back-to-back MMAs into one accumulator run at two thirds of the rate of independent ones.
-                    // (i = streamed component, o = accumulator component)
-                    for (int pair = 0; pair < 2 && ok; ++pair) {
-                        if (local_tile > 0) {
-                            ok = mbar_wait_bounded(tmem_empty + 8 * (2 * pair), (local_tile - 1) & 1, status, ST_U_MMA) &&
-                                 mbar_wait_bounded(tmem_empty + 8 * (2 * pair + 1), (local_tile - 1) & 1, status, ST_U_MMA);
-                            if (!ok) break;
-                            tc_fence_after_sync();
-                        }
-                        if (lane == 0) {
-#pragma unroll
-                            for (int j = 0; j < KS / 16; ++j)
-#pragma unroll
-                                for (int i = 0; i < 4; ++i)
-#pragma unroll
-                                    for (int oo = 0; oo < 2; ++oo) issue(a_addr, b_addr, j, i, 2 * pair + oo, (j > 0 || i > 0) ? 1u : 0u);
-                        }
-                        __syncwarp();
+                // A tile's MMAs go round the four accumulators (i = streamed component, o = accumulator component), except at
+                // its two ends, where they are issued pair-wise (accumulators 0,1 then 2,3):
+                //  - the first EDGE_J K steps of the first slice: each pair starts as soon as the epilogue of the previous tile has
+                //    drained it;
+                //  - the last EDGE_J K steps of the last slice: the first pair is complete (and signalled) while the second still
+                //    computes, so its drain overlaps those MMAs and the next tile can start on it without a bubble.
+                // Inside a pair the MMAs alternate between the two accumulators (back-to-back MMAs into one accumulator run at two
+                // thirds of the rate of independent ones).
+                constexpr int J = KS / 16;
+                const bool first = k == 0, last = k == n_k - 1;
+                const int head = first ? (last ? J : EDGE_J) : 0;            // a one-slice tile is issued pair-wise throughout
+                const int tail = (last && !first) ? EDGE_J : 0;
+                for (int pair = 0; pair < 2 && ok && head > 0; ++pair) {
+                    if (local_tile > 0) {
+                        ok = mbar_wait_bounded(tmem_empty + 8 * (2 * pair), (local_tile - 1) & 1, status, ST_U_MMA) &&
+                             mbar_wait_bounded(tmem_empty + 8 * (2 * pair + 1), (local_tile - 1) & 1, status, ST_U_MMA);
+                        if (!ok) break;
+                        tc_fence_after_sync();
                     }
-                    if (!ok) break;
-                } else if (lane == 0) {
+                    if (lane == 0) {
+                        for (int j = 0; j < head; ++j)
 #pragma unroll
-                    for (int j = 0; j < KS / 16; ++j)
+                            for (int i = 0; i < 4; ++i)
+#pragma unroll
+                                for (int oo = 0; oo < 2; ++oo) issue(a_addr, b_addr, j, i, 2 * pair + oo, (j > 0 || i > 0) ? 1u : 0u);
+                        if (last) mma_commit(pair == 0 ? tmem_full0 : tmem_full1);
+                    }
+                    __syncwarp();
+                }
+                if (!ok) break;
+                if (lane == 0) {
+                    for (int j = head; j < J - tail; ++j)
 #pragma unroll
                         for (int i = 0; i < 4; ++i)
 #pragma unroll
                             for (int o = 0; o < 4; ++o) issue(a_addr, b_addr, j, i, o, 1u);
-                }
-                if (lane == 0) {
+                    for (int pair = 0; pair < 2 && tail > 0; ++pair) {
+                        for (int j = J - tail; j < J; ++j)
+#pragma unroll
+                            for (int i = 0; i < 4; ++i)
+#pragma unroll
+                                for (int oo = 0; oo < 2; ++oo) issue(a_addr, b_addr, j, i, 2 * pair + oo, 1u);
+                        mma_commit(pair == 0 ? tmem_full0 : tmem_full1);
+                    }
                     mma_commit(empty_bar + 8 * s);
-                    if (k == n_k - 1) mma_commit(tmem_full);
                 }
                 __syncwarp();
             }
@@ -230,17 +246,20 @@ qconv_pointwise_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __gri
         for (int tile = blockIdx.x; tile < n_tiles && ok; tile += gridDim.x, ++local_tile) {
             const int px_tile = tile / p.n_c_tiles, c_tile = tile - px_tile * p.n_c_tiles;
             const int c = c_tile * CT + row;
-            ok = mbar_wait_bounded(tmem_full, local_tile & 1, status, ST_U_EPILOGUE);
-            ok = __all_sync(0xffffffffu, ok && (*reinterpret_cast<volatile int*>(status) == 0));
-            if (!ok) break;
-            tc_fence_after_sync();
             // Drain: all eight warps read component 0 (a 64-column half each) and release it, then 1, 2, 3, so the MMA
-            // warp starts the next tile on component 0 while the others are still being read. The values wait as
-            // packed 16-bit pairs in registers; nothing slow sits between two releases.
+            // warp starts the next tile on component 0 while the others are still being read. Components 0 and 1 are
+            // complete before 2 and 3 (see the MMA warp). The values wait as packed 16-bit pairs in registers; nothing
+            // slow sits between two releases.
             uint32_t packed[4][32];
             const uint32_t lane_addr = tmem_base + ((uint32_t)(q * 32) << 16) + chalf * 64;
 #pragma unroll
             for (int o = 0; o < 4; ++o) {
+                if ((o & 1) == 0) {
+                    ok = mbar_wait_bounded(o == 0 ? tmem_full0 : tmem_full1, local_tile & 1, status, ST_U_EPILOGUE);
+                    ok = __all_sync(0xffffffffu, ok && (*reinterpret_cast<volatile int*>(status) == 0));
+                    if (!ok) break;
+                    tc_fence_after_sync();
+                }
                 float badd = 0.f;
                 if (!BWD && p.has_bias && c < p.Cout) {
                     const uint16_t raw = bias[o * p.Cout + c];
@@ -260,6 +279,7 @@ qconv_pointwise_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __gri
                     else { const __nv_bfloat162 h = __floats2bfloat162_rn(f0, f1); packed[o][e] = *reinterpret_cast<const uint32_t*>(&h); }
                 }
             }
+            if (!ok) break;
             int img[2], pix[2];
 #pragma unroll
             for (int b = 0; b < 2; ++b) {
@@ -499,13 +519,16 @@ int pointwise_tc_launch(Pass pass, int dtype, const Geom& g, const void* w, cons
         grid -= grid % p.n_c_tiles;
         p.a_resident = 1;
     }
-    if (!bwd) {
-        PCB_CUDA_TRY(cudaFuncSetAttribute(qconv_pointwise_tc_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)U_SMEM_BYTES));
-        qconv_pointwise_tc_kernel<false><<<grid, U_THREADS, U_SMEM_BYTES, stream>>>(map_w, map_act, map_out, p, (const uint16_t*)bias, status);
-    } else {
-        PCB_CUDA_TRY(cudaFuncSetAttribute(qconv_pointwise_tc_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)U_SMEM_BYTES));
-        qconv_pointwise_tc_kernel<true><<<grid, U_THREADS, U_SMEM_BYTES, stream>>>(map_w, map_act, map_out, p, (const uint16_t*)bias, status);
-    }
+    static const int edge = [] { const char* e = getenv("PCB_PW_EDGE"); return e ? atoi(e) : 2; }();
+    auto launch = [&](auto kernel) -> int {
+        PCB_CUDA_TRY(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)U_SMEM_BYTES));
+        kernel<<<grid, U_THREADS, U_SMEM_BYTES, stream>>>(map_w, map_act, map_out, p, (const uint16_t*)bias, status);
+        return PCB_OK;
+    };
+    int rc;
+    if (!bwd) rc = edge == 1 ? launch(qconv_pointwise_tc_kernel<false, 1>) : launch(qconv_pointwise_tc_kernel<false, 2>);
+    else rc = edge == 1 ? launch(qconv_pointwise_tc_kernel<true, 1>) : launch(qconv_pointwise_tc_kernel<true, 2>);
+    if (rc != PCB_OK) return rc;
     PCB_CUDA_TRY(cudaGetLastError());
     return PCB_OK;
 }

@@ -21,6 +21,13 @@ bool pointwise_filter_tc_supported(int dtype, int variant, const Geom& g);
 int pointwise_filter_tc_launch(int dtype, const Geom& g, const void* dy, const void* x, void* dw, float* scratch, int* status,
                                cudaStream_t stream);
 
+// The factorised 8-product form of pointwise layers (all three passes) with the lane sums formed in shared memory and the
+// recombination in the epilogue; see pointwise8_tc.cu.
+bool pointwise8_tc_supported(Pass pass, int dtype, int variant, const Geom& g);
+size_t pointwise8_tc_scratch_bytes(Pass pass, const Geom& g);
+int pointwise8_tc_launch(Pass pass, int dtype, const Geom& g, const void* a, const void* b, const void* bias, void* out,
+                         float* scratch, int* status, cudaStream_t stream);
+
 // General implicit-GEMM convolution (any taps / stride <= 2 / padding) on staged operands; see conv_tc.cu.
 bool conv_tc_supported(Pass pass, int dtype, int variant, const Geom& g);
 size_t conv_tc_scratch_bytes(Pass pass, const Geom& g);

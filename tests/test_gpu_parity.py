@@ -128,6 +128,26 @@ def test_pointwise_tensor_core_vs_oracle(gpu, oracle, shape, dtype):
     assert rel_err(got, simt) <= (4e-3 if dtype == "f16" else 2e-2)
 
 
+@pytest.mark.parametrize("shape", TENSOR_SHAPES)
+@pytest.mark.parametrize("dtype", ["f16", "bf16"])
+def test_pointwise_8_product_on_tensor_cores_vs_oracle(gpu, oracle, shape, dtype):
+    """The factorised form on its own tcgen05 kernels (lane sums in shared memory, recombination in the epilogue)
+    against the oracle's restatement of the reference's 8-product path, all three passes."""
+    n, ci, co, h, w_ = shape
+    x = gpu.rounded(normal(15, (4 * n, ci, h, w_)), dtype)
+    w = gpu.rounded(normal(16, (4, co, ci, 1, 1), std=(2.0 / (4 * ci)) ** 0.5), dtype)
+    b = gpu.rounded(uniform(17, (4, co)), dtype)
+    pad, stride = (0, 0, 0, 0), (1, 1)
+    ref = oracle.conv2d_fwd(x, w, b, stride, (1, 1), pad, oracle.QUATERNION, oracle.VARIANT_8P)
+    got = gpu.run_conv_fwd(x, w, b, stride, pad, dtype, "8p", "tensor")
+    _check(got, ref, dtype, gpu, "y")
+    dy = gpu.rounded(normal(18, ref.shape), dtype)
+    rdw, rdx = oracle.conv2d_bwd(x, w, dy, stride, (1, 1), pad, oracle.QUATERNION, oracle.VARIANT_8P, True)
+    dw, dx = gpu.run_conv_bwd(x, w, dy, stride, pad, dtype, "8p", "tensor", True)
+    _check(dx, rdx, dtype, gpu, "dx")
+    _check(dw, rdw, dtype, gpu, "dw")
+
+
 # shapes for the general implicit-GEMM tensor-core kernel (staged channels-last activations, expanded filters):
 # n, ci, co, h, w, kh, kw, stride, pad(t,l,b,r)
 GENERAL_TENSOR_SHAPES = [
@@ -247,7 +267,7 @@ def test_tensor_engine_refuses_unsupported_shapes(gpu):
     with pytest.raises(_lib.BackendError) as e:      # stride 3 has no tensor-core kernel
         gpu.run_conv_fwd(x, w, None, (3, 3), (1, 1, 1, 1), "f16", "16p", "tensor")
     assert e.value.status == _lib.PCB_ERR_UNSUPPORTED
-    with pytest.raises(_lib.BackendError) as e:      # the factorised 8-product form stays on the CUDA-core kernels
+    with pytest.raises(_lib.BackendError) as e:      # the factorised tensor-core kernels cover pointwise layers only
         gpu.run_conv_fwd(x, w, None, (1, 1), (1, 1, 1, 1), "f16", "8p", "tensor")
     assert e.value.status == _lib.PCB_ERR_UNSUPPORTED
 
