@@ -115,7 +115,7 @@ int reset_status(void* workspace, size_t ws_bytes, cudaStream_t stream) {
 
 size_t workspace_bytes(Pass pass, int dtype, int variant, int engine, const Geom& g) {
     size_t s = simt_scratch_bytes(pass, dtype, variant, g);
-    const size_t t = g.plain ? tensor_scratch_bytes(pass, dtype, tensor_variant(variant, engine), engine, g) : 0;
+    const size_t t = tensor_scratch_bytes(pass, dtype, tensor_variant(variant, engine), engine, g);
     if (t > s) s = t;
     return WS_HEADER + ((s + 255) / 256) * 256;
 }
@@ -124,17 +124,19 @@ int run_pass(Pass pass, int dtype, int variant, int engine, const Geom& g, const
              void* out, void* workspace, size_t ws_bytes, cudaStream_t stream) {
     const size_t need = workspace_bytes(pass, dtype, variant, engine, g);
     const int tv = tensor_variant(variant, engine);
-    const bool needs_ws = need > WS_HEADER || (g.plain && tensor_path_supported(pass, dtype, tv, g));
+    const bool needs_ws = need > WS_HEADER || tensor_path_supported(pass, dtype, tv, g);
     if (needs_ws && (workspace == nullptr || ws_bytes < need)) {
         set_error("workspace of %zu bytes required, %zu given", need, workspace ? ws_bytes : (size_t)0);
         return PCB_ERR_WORKSPACE;
     }
     float* scratch = workspace ? reinterpret_cast<float*>(static_cast<char*>(workspace) + WS_HEADER) : nullptr;
     int* status = static_cast<int*>(workspace);
-    // the tensor-core kernels move 16-byte chunks: every tensor (and the workspace) must be 16-byte aligned
-    const bool aligned = ((reinterpret_cast<uintptr_t>(a) | reinterpret_cast<uintptr_t>(b) | reinterpret_cast<uintptr_t>(out) |
-                           reinterpret_cast<uintptr_t>(workspace)) & 15u) == 0;
-    if (engine != PCB_ENGINE_SIMT && aligned && g.plain && tensor_path_supported(pass, dtype, tv, g))
+    // the tensor-core kernels move 16-byte chunks of NCHW / OIHW tensors: every tensor (and the workspace) must be 16-byte
+    // aligned. Tensors of other layouts and the channel slices of grouped layers are addressed element by element (staged
+    // operands, strided stores), so there only the workspace has to be.
+    const uintptr_t tensors = g.plain ? (reinterpret_cast<uintptr_t>(a) | reinterpret_cast<uintptr_t>(b) | reinterpret_cast<uintptr_t>(out)) : 0;
+    const bool aligned = ((tensors | reinterpret_cast<uintptr_t>(workspace)) & 15u) == 0;
+    if (engine != PCB_ENGINE_SIMT && aligned && tensor_path_supported(pass, dtype, tv, g))
         return tensor_launch(pass, dtype, tv, g, a, b, bias, out, scratch, status, stream);
     if (engine == PCB_ENGINE_TENSOR) {
         set_error("no tensor-core kernel for this problem");
@@ -153,13 +155,12 @@ size_t group_slice_bytes(int dtype, const Geom& g) {
 
 size_t conv_workspace_bytes(Pass pass, int dtype, int variant, int engine, const Geom& g) {
     if (g.groups == 1) return workspace_bytes(pass, dtype, variant, engine, g);
-    return workspace_bytes(pass, dtype, variant, PCB_ENGINE_SIMT, g) + (pass == PASS_BWD_FILTER ? group_slice_bytes(dtype, g) : 0);
+    return workspace_bytes(pass, dtype, variant, engine, g) + (pass == PASS_BWD_FILTER ? group_slice_bytes(dtype, g) : 0);
 }
 
 int run_conv_pass(Pass pass, int dtype, int variant, int engine, const Geom& g, const void* a, const void* b, const void* bias,
                   void* out, void* workspace, size_t ws_bytes, cudaStream_t stream) {
     if (g.groups == 1) return run_pass(pass, dtype, variant, engine, g, a, b, bias, out, workspace, ws_bytes, stream);
-    if (engine == PCB_ENGINE_TENSOR) { set_error("no tensor-core kernel for grouped convolutions"); return PCB_ERR_UNSUPPORTED; }
     const size_t es = dtype_size(dtype);
     const size_t need = conv_workspace_bytes(pass, dtype, variant, engine, g);
     if (need > WS_HEADER && (workspace == nullptr || ws_bytes < need)) {
@@ -175,16 +176,16 @@ int run_conv_pass(Pass pass, int dtype, int variant, int engine, const Geom& g, 
     for (int gi = 0; gi < g.groups; ++gi) {
         int rc;
         if (pass == PASS_FWD) {            // a = filters, b = x, out = y
-            rc = run_pass(pass, dtype, variant, PCB_ENGINE_SIMT, g, ca + gi * w_step, cb + gi * x_step,
+            rc = run_pass(pass, dtype, variant, engine, g, ca + gi * w_step, cb + gi * x_step,
                           bias ? static_cast<const char*>(bias) + gi * bias_step : nullptr, co + gi * y_step, workspace, ws_bytes, stream);
         } else if (pass == PASS_BWD_DATA) { // a = filters, b = dy, out = dx
-            rc = run_pass(pass, dtype, variant, PCB_ENGINE_SIMT, g, ca + gi * w_step, cb + gi * y_step, nullptr, co + gi * x_step, workspace, ws_bytes, stream);
+            rc = run_pass(pass, dtype, variant, engine, g, ca + gi * w_step, cb + gi * y_step, nullptr, co + gi * x_step, workspace, ws_bytes, stream);
         } else {                           // a = dy, b = x, out = dw: contiguous slice first
             Geom gs = g;
             gs.dr = g.Co * g.Ci * (int)taps;
-            const size_t inner = workspace_bytes(pass, dtype, variant, PCB_ENGINE_SIMT, g);   // a multiple of 256 bytes
+            const size_t inner = workspace_bytes(pass, dtype, variant, engine, g);   // a multiple of 256 bytes
             char* tmp = static_cast<char*>(workspace) + inner;                             // the slice follows the pass's own scratch
-            rc = run_pass(pass, dtype, variant, PCB_ENGINE_SIMT, gs, ca + gi * y_step, cb + gi * x_step, nullptr, tmp, workspace, inner, stream);
+            rc = run_pass(pass, dtype, variant, engine, gs, ca + gi * y_step, cb + gi * x_step, nullptr, tmp, workspace, inner, stream);
             if (rc == PCB_OK) {
                 const size_t row = (size_t)g.Co * g.Ci * taps * es;
                 PCB_CUDA_TRY(cudaMemcpy2DAsync(co + gi * w_step, row * g.groups, tmp, row, row, g.nc, cudaMemcpyDeviceToDevice, stream));
@@ -389,7 +390,7 @@ int pcb_qconv2d_engine_for(const pcb_conv2d_desc* desc, int pass) {
     const int rc = conv_geom(desc, g);
     if (rc != PCB_OK) return rc;
     if (pass < 0 || pass > 2) { set_error("pass must be 0, 1 or 2"); return PCB_ERR_INVALID_ARGUMENT; }
-    if (desc->engine != PCB_ENGINE_SIMT && g.plain && tensor_path_supported((Pass)pass, desc->dtype, tensor_variant(variant_for(g, desc->variant), desc->engine), g)) return PCB_ENGINE_TENSOR;
+    if (desc->engine != PCB_ENGINE_SIMT && tensor_path_supported((Pass)pass, desc->dtype, tensor_variant(variant_for(g, desc->variant), desc->engine), g)) return PCB_ENGINE_TENSOR;
     return desc->engine == PCB_ENGINE_TENSOR ? (int)PCB_ERR_UNSUPPORTED : (int)PCB_ENGINE_SIMT;
 }
 
@@ -398,7 +399,7 @@ int pcb_qdense_engine_for(const pcb_dense_desc* desc, int pass) {
     const int rc = dense_geom(desc, g);
     if (rc != PCB_OK) return rc;
     if (pass < 0 || pass > 2) { set_error("pass must be 0, 1 or 2"); return PCB_ERR_INVALID_ARGUMENT; }
-    if (desc->engine != PCB_ENGINE_SIMT && g.plain && tensor_path_supported((Pass)pass, desc->dtype, tensor_variant(variant_for(g, desc->variant), desc->engine), g)) return PCB_ENGINE_TENSOR;
+    if (desc->engine != PCB_ENGINE_SIMT && tensor_path_supported((Pass)pass, desc->dtype, tensor_variant(variant_for(g, desc->variant), desc->engine), g)) return PCB_ENGINE_TENSOR;
     return desc->engine == PCB_ENGINE_TENSOR ? (int)PCB_ERR_UNSUPPORTED : (int)PCB_ENGINE_SIMT;
 }
 

@@ -50,6 +50,11 @@ struct GParams {
     // halo mode
     int Wt, Ht;
     uint32_t stage_bytes;
+    int off_w, off_h;            // added to the pixel coordinates of every activation box: 0 for a staged (padded) copy, minus the
+                                 // padding when the caller's channels-last tensor is read in place (the padding is TMA zero fill)
+    int o_generic;               // the output is addressed through the element strides below (channels-last tensors, channel
+    int o_p, o_c, o_h, o_w;      // slices of grouped layers, boxes narrower than 8 pixels): one 16-bit store per element
+    int bias_ld;                 // bias is [components][bias_ld]
 };
 constexpr uint32_t G_PLANE_BYTES = GM * GN * 2;      // staging buffer of the plane-mode epilogue
 
@@ -160,7 +165,7 @@ qconv_general_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_
                             const uint32_t a_dst = tiles_addr + s * STAGE, bar = full_bar + 8 * s;
                             mbar_arrive_expect_tx(bar, taps * A_BYTES + (uint32_t)p.Wt * p.Ht * KS * 2);
                             tma_load_3d(a_dst, &map_w, l * p.Cp + cs * KS, m0, 0, bar);                       // [tap][128 rows][32 channels]
-                            tma_load_5d(a_dst + taps * A_BYTES, &map_x, cs * KS, ow0, oh0, n0, l, bar);       // [Ht][Wt][32 channels]
+                            tma_load_5d(a_dst + taps * A_BYTES, &map_x, cs * KS, ow0 + p.off_w, oh0 + p.off_h, n0, l, bar);   // [Ht][Wt][32 channels]
                             if (++s == STAGES) { s = 0; phase ^= 1; }
                         }
                     }
@@ -168,7 +173,7 @@ qconv_general_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_
                 }
                 for (int tap = 0; tap < p.KH * p.KW && ok; ++tap) {
                     const int kh = tap / p.KW, kw = tap - kh * p.KW;
-                    const int wp0 = ow0 * p.SW + kw * p.DW, hp0 = oh0 * p.SH + kh * p.DH;
+                    const int wp0 = ow0 * p.SW + kw * p.DW + p.off_w, hp0 = oh0 * p.SH + kh * p.DH + p.off_h;
                     for (int l = 0; l < p.LK && ok; ++l) {
                         for (int cs = 0; cs < c_steps; ++cs) {
                             ok = mbar_wait_bounded(empty_bar + 8 * s, phase, status, ST_G_PRODUCER);
@@ -186,45 +191,55 @@ qconv_general_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_
         __syncwarp();
     } else if (warp == 1) {
         // ---------------------------------------------------------------- MMA issuer
-        const uint32_t idesc = make_idesc_f16(p.fmt, GM, HALO ? p.n_cols : GN, false, false);
-        int s = 0, phase = 0, local_tile = 0;
-        bool ok = true;
-        for (int tile = blockIdx.x; tile < n_tiles && ok; tile += gridDim.x, ++local_tile) {
-            const int buf = local_tile & 1, use = local_tile >> 1;       // use-th time this accumulator buffer is filled
-            if (use > 0) {
-                ok = mbar_wait_bounded(tmem_empty + 8 * buf, (use - 1) & 1, status, ST_G_MMA);
-                if (!ok) break;
-                tc_fence_after_sync();
-            }
-            for (int k = 0; k < n_k && ok; ++k) {
-                ok = mbar_wait_bounded(full_bar + 8 * s, phase, status, ST_G_MMA);
-                if (!ok) break;
-                tc_fence_after_sync();
-                if (lane == 0) {
+        // One thread runs the whole loop (waits, descriptor stepping, MMAs, commits): whatever it executes between two MMAs is
+        // time the tensor pipe idles, so there is no warp synchronisation inside and a stage's two descriptors are built once
+        // and stepped by adding to the address field of their low words (16-byte units, never carrying out of the field).
+        if (lane == 0) {
+            const uint32_t idesc = make_idesc_f16(p.fmt, GM, HALO ? p.n_cols : GN, false, false);
+            int s = 0, phase = 0, local_tile = 0;
+            bool ok = true;
+            for (int tile = blockIdx.x; tile < n_tiles && ok; tile += gridDim.x, ++local_tile) {
+                const int buf = local_tile & 1, use = local_tile >> 1;       // use-th time this accumulator buffer is filled
+                if (use > 0) {
+                    ok = mbar_wait_bounded(tmem_empty + 8 * buf, (use - 1) & 1, status, ST_G_MMA);
+                    if (!ok) break;
+                    tc_fence_after_sync();
+                }
+                const uint32_t d_tmem = tmem_base + buf * GN;
+                for (int k = 0; k < n_k && ok; ++k) {
+                    ok = mbar_wait_bounded(full_bar + 8 * s, phase, status, ST_G_MMA);
+                    if (!ok) break;
+                    tc_fence_after_sync();
                     const uint32_t a_addr = tiles_addr + s * STAGE, b_addr = a_addr + (HALO ? taps * A_BYTES : A_BYTES);
+                    const uint64_t ad = make_desc_kmajor_rows<KS>(a_addr);
+                    const uint32_t a_lo = (uint32_t)ad, a_hi = (uint32_t)(ad >> 32);
                     if (HALO) {
-                        int kh = 0, kw = 0;
+                        const uint64_t bd = make_desc_kmajor_sw64_groups(b_addr, p.Wt * KS * 2);
+                        const uint32_t b_lo = (uint32_t)bd, b_hi = (uint32_t)(bd >> 32);
+                        const uint32_t row_step = (uint32_t)(p.DH * p.Wt * KS * 2) >> 4, col_step = (uint32_t)(p.DW * KS * 2) >> 4;
+                        uint32_t a_tap = a_lo, b_row = b_lo, b_tap = b_lo;
+                        int kw = 0;
                         for (int tap = 0; tap < taps; ++tap) {
-                            const uint32_t shift = (uint32_t)(kh * p.DH * p.Wt + kw * p.DW) * (KS * 2);
-                            if (++kw == p.KW) { kw = 0; ++kh; }
 #pragma unroll
                             for (int j = 0; j < KS / 16; ++j)
-                                mma_f16_ss(tmem_base + buf * GN, make_desc_kmajor_rows<KS>(a_addr + tap * A_BYTES + j * 32),
-                                           make_desc_kmajor_sw64_groups(b_addr + shift + j * 32, p.Wt * KS * 2), idesc, (k > 0 || tap > 0 || j > 0) ? 1u : 0u);
+                                mma_f16_ss_words(d_tmem, a_tap + 2 * j, a_hi, b_tap + 2 * j, b_hi, idesc, (k > 0 || tap > 0 || j > 0) ? 1u : 0u);
+                            a_tap += A_BYTES >> 4;
+                            if (++kw == p.KW) { kw = 0; b_row += row_step; b_tap = b_row; } else b_tap += col_step;
                         }
                     } else {
+                        const uint64_t bd = make_desc_kmajor_rows<KS>(b_addr);
+                        const uint32_t b_lo = (uint32_t)bd, b_hi = (uint32_t)(bd >> 32);
 #pragma unroll
                         for (int j = 0; j < KS / 16; ++j)
-                            mma_f16_ss(tmem_base + buf * GN, make_desc_kmajor_rows<KS>(a_addr + j * 32), make_desc_kmajor_rows<KS>(b_addr + j * 32),
-                                       idesc, (k > 0 || j > 0) ? 1u : 0u);
+                            mma_f16_ss_words(d_tmem, a_lo + 2 * j, a_hi, b_lo + 2 * j, b_hi, idesc, (k > 0 || j > 0) ? 1u : 0u);
                     }
                     mma_commit(empty_bar + 8 * s);
                     if (k == n_k - 1) mma_commit(tmem_full + 8 * buf);
+                    if (++s == STAGES) { s = 0; phase ^= 1; }
                 }
-                __syncwarp();
-                if (++s == STAGES) { s = 0; phase ^= 1; }
             }
         }
+        __syncwarp();
     } else {
         // ---------------------------------------------------------------- epilogue (warps 2..9)
         const int q = warp & 3;                    // TMEM lane quadrant
@@ -256,7 +271,7 @@ qconv_general_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_
             const int d = row_ok ? m / p.Cout : 0, co = m - d * p.Cout;
             float badd = 0.f;
             if (row_ok && p.has_bias) {
-                const uint16_t raw = bias[d * p.Cout + co];
+                const uint16_t raw = bias[d * p.bias_ld + co];
                 badd = p.fmt == 0 ? __half2float(__ushort_as_half(raw)) : __bfloat162float(__ushort_as_bfloat16(raw));
             }
             ok = mbar_wait_bounded(tmem_full + 8 * buf, use & 1, status, ST_G_EPILOGUE);
@@ -314,12 +329,29 @@ qconv_general_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_
                     if (p.fmt == 0) { const __half2 h = __floats2half2_rn(f0, f1); packed[e] = *reinterpret_cast<const uint32_t*>(&h); }
                     else { const __nv_bfloat162 h = __floats2bfloat162_rn(f0, f1); packed[e] = *reinterpret_cast<const uint32_t*>(&h); }
                 }
-                const bool wide = sv >= 16 && (p.PW % 16) == 0;
+                const bool wide = !p.o_generic && sv >= 16 && (p.PW % 16) == 0;
 #pragma unroll
                 for (int g8 = 0; g8 < 4; ++g8) {
                     if (wide && (g8 & 1)) continue;                      // the odd groups were written with their even neighbours
                     const int j = col0 + g8 * 8;                         // column -> (image, row, pixel) of the tile box
                     if (j >= p.n_cols) continue;
+                    if (p.o_generic) {
+                        // Output addressed through element strides: channels-last tensors (consecutive lanes hold consecutive
+                        // channels, so a warp's stores of one pixel are contiguous), channel slices of grouped layers, and boxes
+                        // narrower than 8 pixels (dense layers are 1 x 1 images: the columns are batch rows). Every column is
+                        // decoded on its own.
+#pragma unroll
+                        for (int e = 0; e < 8; ++e) {
+                            const int je = j + e;
+                            if (je >= p.n_cols) continue;
+                            const int wl = je & (p.PW - 1), hl = p.lh >= 0 ? ((je >> p.lw) & (p.PH - 1)) : (je >> p.lw), nl = p.lh >= 0 ? (je >> (p.lw + p.lh)) : 0;
+                            const int ow = ow0 + wl, oh = oh0 + hl, img = n0 + nl;
+                            if (ow >= p.WO || oh >= p.HO || img >= p.Nb) continue;
+                            out[(size_t)(d * p.Nb + img) * p.o_p + (size_t)co * p.o_c + (size_t)oh * p.o_h + (size_t)ow * p.o_w] =
+                                (uint16_t)((packed[4 * g8 + (e >> 1)] >> ((e & 1) * 16)) & 0xffffu);
+                        }
+                        continue;
+                    }
                     // PW is a power of two; PH too unless the tile is one image tall (PN == 1, halo mode)
                     const int wl = j & (p.PW - 1), hl = p.lh >= 0 ? ((j >> p.lw) & (p.PH - 1)) : (j >> p.lw), nl = p.lh >= 0 ? (j >> (p.lw + p.lh)) : 0;
                     const int ow = ow0 + wl, oh = oh0 + hl, img = n0 + nl;
@@ -359,9 +391,12 @@ qconv_general_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_
 // ---- staging kernels ------------------------------------------------------------------------------
 // xp[comp][img][hp][wp][c] = x[comp][img][c][hp - pad_top][wp - pad_left] (zero outside, zero for c >= C).
 // One thread per (pixel, 8-channel group): reads are coalesced along w, writes are 16-byte vectors.
+// The source is addressed through element strides (plane, channel, row, pixel), so it may be NCHW, channels-last, or a
+// channel slice of a wider tensor (one group of a grouped layer).
+struct SrcStrides { long long p, c, h, w; };
 template <typename T>
 __global__ void pack_activations_kernel(const T* __restrict__ x, T* __restrict__ xp, int planes /*4*Nb*/, int C, int H, int W,
-                                        int Hp, int Wp, int Cp, int pad_top, int pad_left, int ins_h = 1, int ins_w = 1, int cb = 0, int Nb = 1) {
+                                        int Hp, int Wp, int Cp, int pad_top, int pad_left, int ins_h, int ins_w, int cb, int Nb, SrcStrides ss) {
     const int groups = Cp / 8;
     const unsigned total = (unsigned)planes * Hp * Wp * groups;       // 32-bit indices: the staged copy is capped at 8 GB
     for (unsigned idx = blockIdx.x * blockDim.x + threadIdx.x; idx < total; idx += gridDim.x * blockDim.x) {
@@ -385,7 +420,7 @@ __global__ void pack_activations_kernel(const T* __restrict__ x, T* __restrict__
         for (int e = 0; e < 8; ++e) {
             const int c = grp * 8 + e;
             T v = T(0.f);
-            if (c < C && inside) v = x[(((size_t)plane * C + c) * H + ih) * W + iw];
+            if (c < C && inside) v = x[(long long)plane * ss.p + (long long)c * ss.c + (long long)ih * ss.h + (long long)iw * ss.w];
             vals[e] = v;
         }
         T* dst = xp + (((size_t)plane * Hp + hp) * Wp + wp) * Cp + grp * 8;
@@ -399,10 +434,13 @@ __global__ void pack_activations_kernel(const T* __restrict__ x, T* __restrict__
 
 // Host dispatch of the activation staging: the 4- or 2-pixel form where it applies, the general form otherwise.
 // cb > 0 selects the channel-block layout of the filter-gradient kernels (Nb images per component).
+// `ss` = nullptr: a dense NCHW source (the fast forms apply); otherwise its element strides.
 void stage_activations(int fmt, const void* src, void* dst, int planes, int C, int H, int W, int Hp, int Wp, int Cp, int pad_top, int pad_left,
-                       int ins_h, int ins_w, cudaStream_t stream, int cb = 0, int Nb = 1) {
+                       int ins_h, int ins_w, cudaStream_t stream, int cb = 0, int Nb = 1, const SrcStrides* ss = nullptr) {
     const size_t total = (size_t)planes * Hp * Wp * (Cp / 8);
-    const int px = pack_rows_px(src, W, Wp, pad_left, ins_h, ins_w);
+    const int px = ss ? 0 : pack_rows_px(src, W, Wp, pad_left, ins_h, ins_w);
+    const SrcStrides dense = {(long long)C * H * W, (long long)H * W, (long long)W, 1};
+    const SrcStrides st = ss ? *ss : dense;
     if (px == 4) {
         const int blocks = grid_cap(total / 4 + 1, 256, 16);
         if (fmt == 0) pack_rows_kernel<__half, 4><<<blocks, 256, 0, stream>>>((const __half*)src, (__half*)dst, planes, C, H, W, Hp, Wp, Cp / 8, pad_top, pad_left, 0, cb, Nb);
@@ -413,17 +451,20 @@ void stage_activations(int fmt, const void* src, void* dst, int planes, int C, i
         else pack_rows_kernel<__nv_bfloat16, 2><<<blocks, 256, 0, stream>>>((const __nv_bfloat16*)src, (__nv_bfloat16*)dst, planes, C, H, W, Hp, Wp, Cp / 8, pad_top, pad_left, 0, cb, Nb);
     } else {
         const int blocks = grid_cap(total, 256, 16);
-        if (fmt == 0) pack_activations_kernel<__half><<<blocks, 256, 0, stream>>>((const __half*)src, (__half*)dst, planes, C, H, W, Hp, Wp, Cp, pad_top, pad_left, ins_h, ins_w, cb, Nb);
-        else pack_activations_kernel<__nv_bfloat16><<<blocks, 256, 0, stream>>>((const __nv_bfloat16*)src, (__nv_bfloat16*)dst, planes, C, H, W, Hp, Wp, Cp, pad_top, pad_left, ins_h, ins_w, cb, Nb);
+        if (fmt == 0) pack_activations_kernel<__half><<<blocks, 256, 0, stream>>>((const __half*)src, (__half*)dst, planes, C, H, W, Hp, Wp, Cp, pad_top, pad_left, ins_h, ins_w, cb, Nb, st);
+        else pack_activations_kernel<__nv_bfloat16><<<blocks, 256, 0, stream>>>((const __nv_bfloat16*)src, (__nv_bfloat16*)dst, planes, C, H, W, Hp, Wp, Cp, pad_top, pad_left, ins_h, ins_w, cb, Nb, st);
     }
 }
 
 // Forward:       Wexp[tap][m = d*Co + co][k = l*Cp + ci]  = s(l,d) * w[l^d][co][ci][tap]
 // Backward-data: Wexp[tap][m = l*Ci + ci][k = d*Cop + co] = s(l,d) * w[l^d][co][ci][taps-1-tap]   (flipped taps)
+// The filters are addressed through element strides (component, output channel, input channel, tap row, tap column): OIHW, OHWI,
+// HWIO, the input-major dense layout, or the slice of one group.
+struct FilterStrides { long long r, o, i, h, w; int KW; };
 template <typename T>
 __global__ void pack_filters_kernel(const T* __restrict__ w, T* __restrict__ wexp, int Co, int Ci, int taps, int Mp, int Kp,
                                     int Cp /*padded channels of the reduced side*/, int transposed, int nc, int ga, unsigned long long neg,
-                                    int w_io = 0 /*dense filters stored [r][ci][co], one tap*/) {
+                                    FilterStrides fs) {
     // one row (tap, m) of the expanded matrix per threadIdx.y; the row is decoded once, the threads of a row walk k
     const int Cm = transposed ? Ci : Co;     // channels on the M side
     const int Ck = transposed ? Co : Ci;     // channels on the K side
@@ -439,12 +480,10 @@ __global__ void pack_filters_kernel(const T* __restrict__ w, T* __restrict__ wex
             const bool negative = comp_ok && alg_negative(neg, l, d);
             // forward: w[r][co = cm][ci = ck][tap]; backward-data: w[r][co = ck][ci = cm][tap]
             const T* src = nullptr;
-            size_t ck_stride = transposed ? (size_t)Ci * taps : (size_t)taps;
-            if (comp_ok && !w_io)
-                src = w + ((size_t)alg_pair(ga, l, d) * Co + (transposed ? 0 : cm)) * Ci * taps + (size_t)(transposed ? cm : 0) * taps + src_tap;
-            if (comp_ok && w_io) {       // [r][ci][co]: forward walks ci (stride Co) at co = cm, backward-data walks co at ci = cm
-                src = w + (size_t)alg_pair(ga, l, d) * Ci * Co + (transposed ? (size_t)cm * Co : (size_t)cm);
-                ck_stride = transposed ? 1 : (size_t)Co;
+            const long long ck_stride = transposed ? fs.o : fs.i;
+            if (comp_ok) {
+                const int kh = src_tap / fs.KW, kw = src_tap - kh * fs.KW;
+                src = w + (long long)alg_pair(ga, l, d) * fs.r + (long long)kh * fs.h + (long long)kw * fs.w + (long long)cm * (transposed ? fs.i : fs.o);
             }
             for (int ck = threadIdx.x; ck < Cp; ck += blockDim.x) {
                 float v = 0.f;
@@ -752,23 +791,27 @@ qconv_filter_xmajor_tc_kernel(const __grid_constant__ CUtensorMap map_x, const _
     if (warp == 1) tmem_dealloc(tmem_base, 512);
 }
 
-// scratch [tap][r][co][ci] fp32 -> dw [r][co][ci][tap] in the tensor type
+// scratch [tap][r][co][ci] fp32 -> dw in the tensor type. `dense_oihw`: dw is [r][co][ci][tap] and the threads walk the
+// destination (coalesced stores); otherwise the destination is addressed through the filter-gradient strides (OHWI, HWIO,
+// the input-major dense gradient, the slice of one group) and the threads walk the source.
 template <typename T>
-__global__ void unpack_filter_grad_kernel(const float* __restrict__ src, T* __restrict__ dw, int taps, size_t per_tap, int dw_io = 0,
-                                          int Co = 0, int Ci = 0) {
+__global__ void unpack_filter_grad_kernel(const float* __restrict__ src, T* __restrict__ dw, int taps, size_t per_tap, int dense_oihw,
+                                          int Co, int Ci, FilterStrides ds) {
     const size_t total = per_tap * taps;
     for (size_t idx = (size_t)blockIdx.x * blockDim.x + threadIdx.x; idx < total; idx += (size_t)gridDim.x * blockDim.x) {
-        if (dw_io) {     // dense: one tap, gradient written input-major [r][ci][co]
-            const int co = (int)(idx % Co);
-            const size_t rest = idx / Co;
-            const int ci = (int)(rest % Ci);
-            const size_t r = rest / Ci;
-            DType<T>::store(dw + idx, src[(r * Co + co) * Ci + ci]);
+        if (dense_oihw) {
+            const int tap = (int)(idx % taps);
+            const size_t e = idx / taps;
+            DType<T>::store(dw + idx, src[(size_t)tap * per_tap + e]);
             continue;
         }
-        const int tap = (int)(idx % taps);
-        const size_t e = idx / taps;
-        DType<T>::store(dw + idx, src[(size_t)tap * per_tap + e]);
+        const int ci = (int)(idx % Ci);
+        size_t rest = idx / Ci;
+        const int co = (int)(rest % Co); rest /= Co;
+        const size_t comps = per_tap / ((size_t)Co * Ci);
+        const int r = (int)(rest % comps), tap = (int)(rest / comps);
+        const int kh = tap / ds.KW, kw = tap - kh * ds.KW;
+        DType<T>::store(dw + (long long)r * ds.r + (long long)co * ds.o + (long long)ci * ds.i + (long long)kh * ds.h + (long long)kw * ds.w, src[idx]);
     }
 }
 
@@ -841,6 +884,14 @@ int conv_tc_launch(Pass pass, int dtype, const Geom& g, const void* w, const voi
     const int taps = g.KH * g.KW;
     uint8_t* xp = static_cast<uint8_t*>(scratch);
     uint8_t* wexp = xp + pl.xp_bytes;
+    // element strides of the convolved tensor (x forward, dy backward-data) and of the produced one
+    const SrcStrides sa = pass == PASS_FWD ? SrcStrides{g.xp, g.xc, g.xh, g.xw} : SrcStrides{g.yp, g.yc, g.yh, g.yw};
+    const SrcStrides so = pass == PASS_FWD ? SrcStrides{g.yp, g.yc, g.yh, g.yw} : SrcStrides{g.xp, g.xc, g.xh, g.xw};
+    // A channels-last tensor whose channel count is a multiple of 16 already IS the staged layout: it is read in place, the
+    // padding comes from the zero fill of out-of-range TMA coordinates, and no copy of the activations is made at all.
+    // (Not for zero-inserted gradients, channel slices of grouped layers, or images smaller than a tile box.)
+    bool direct = !g.plain && sa.c == 1 && sa.w == pl.Cin && sa.h == (long long)pl.Win * pl.Cin && sa.p == (long long)pl.Hin * pl.Win * pl.Cin &&
+                  pl.Cin % 16 == 0 && pl.ins_h == 1 && pl.ins_w == 1 && (reinterpret_cast<uintptr_t>(act) & 15u) == 0;
 
     // stage the operands
     {
@@ -849,13 +900,16 @@ int conv_tc_launch(Pass pass, int dtype, const Geom& g, const void* w, const voi
         const dim3 wthreads(pl.Cp >= 64 ? 64 : 32, pl.Cp >= 64 ? 4 : 8);
         const int wblocks = grid_cap((size_t)taps * pl.Mp, (int)wthreads.y, 32);
         (void)blocks;
-        stage_activations(fmt, act, xp, pl.LK * g.Nb, pl.Cin, pl.Hin, pl.Win, pl.Hp, pl.Wp, pl.Cp, pl.pad_top, pl.pad_left, pl.ins_h, pl.ins_w, stream);
+        if (!direct)
+            stage_activations(fmt, act, xp, pl.LK * g.Nb, pl.Cin, pl.Hin, pl.Win, pl.Hp, pl.Wp, pl.Cp, pl.pad_top, pl.pad_left, pl.ins_h, pl.ins_w, stream,
+                              0, 1, g.plain ? nullptr : &sa);
+        const FilterStrides fs = {g.wr, g.wo, g.wi, g.wh, g.ww, g.KW};
         if (fmt == 0) {
             pack_filters_kernel<__half><<<wblocks, wthreads, 0, stream>>>((const __half*)w, (__half*)wexp, g.Co, g.Ci, taps, pl.Mp, pl.Kp, pl.Cp,
-                                                                    pass == PASS_BWD_DATA ? 1 : 0, g.nc, g.ga, g.neg, g.w_io);
+                                                                    pass == PASS_BWD_DATA ? 1 : 0, g.nc, g.ga, g.neg, fs);
         } else {
             pack_filters_kernel<__nv_bfloat16><<<wblocks, wthreads, 0, stream>>>((const __nv_bfloat16*)w, (__nv_bfloat16*)wexp, g.Co, g.Ci, taps,
-                                                                           pl.Mp, pl.Kp, pl.Cp, pass == PASS_BWD_DATA ? 1 : 0, g.nc, g.ga, g.neg, g.w_io);
+                                                                           pl.Mp, pl.Kp, pl.Cp, pass == PASS_BWD_DATA ? 1 : 0, g.nc, g.ga, g.neg, fs);
         }
         PCB_CUDA_TRY(cudaGetLastError());
     }
@@ -864,7 +918,9 @@ int conv_tc_launch(Pass pass, int dtype, const Geom& g, const void* w, const voi
     GParams p;
     {
         long long best = -1;
-        for (int pw = 8; pw <= 128; pw *= 2)
+        // (dense layers are 1 x 1 images: their box is 1 x 1 x 256, so that the columns of a tile are batch rows and none is wasted)
+        const bool dense_like = pl.Wout == 1 && pl.Hout == 1;
+        for (int pw = dense_like ? 1 : 8; pw <= 128; pw *= 2)
             for (int ph = 1; ph * pw <= 256; ph *= 2) {
                 const int pn = 256 / (pw * ph);
                 if (pw * pl.SW > 256 || ph * pl.SH > 256) continue;
@@ -879,7 +935,7 @@ int conv_tc_launch(Pass pass, int dtype, const Geom& g, const void* w, const voi
         int pw = 8, ph = 1;
         while (pw < pl.Wout) pw *= 2;
         while (ph < pl.Hout) ph *= 2;
-        if (pw * ph <= 256 && pl.Cout % GM == 0 && pl.Wout % 8 != 0) { p.PW = pw; p.PH = ph; p.PN = 256 / (pw * ph); }
+        if (pw * ph <= 256 && pl.Cout % GM == 0 && pl.Wout % 8 != 0 && !(pl.Wout == 1 && pl.Hout == 1)) { p.PW = pw; p.PH = ph; p.PN = 256 / (pw * ph); }
     }
     // Halo mode (see the kernel): stride-1 correlation, 32-channel slices, several taps, and an image tall enough for
     // tiles of 8 x PH >= 192 pixels (smaller tiles re-read the filter slices too often to gain anything).
@@ -902,7 +958,12 @@ int conv_tc_launch(Pass pass, int dtype, const Geom& g, const void* w, const voi
         p.lw = log2i(p.PW); p.lh = log2i(p.PH);
     }
     // plane mode (see the epilogue): whole output planes per tile, 128 rows = 128 consecutive channels of one component
-    p.plane_mode = (!halo && p.PW >= pl.Wout && p.PH >= pl.Hout && pl.Cout % GM == 0 && p.lh >= 0 && (p.lw == 3 || p.lw == 4) &&
+    // strided output: anything but a dense NCHW tensor, and the narrow boxes of dense layers
+    p.o_generic = (!g.plain || p.lw < 3) ? 1 : 0;
+    p.o_p = (int)so.p; p.o_c = (int)so.c; p.o_h = (int)so.h; p.o_w = (int)so.w;
+    p.bias_ld = g.bias_ld;
+    p.off_w = direct ? -pl.pad_left : 0; p.off_h = direct ? -pl.pad_top : 0;
+    p.plane_mode = (!p.o_generic && !halo && p.PW >= pl.Wout && p.PH >= pl.Hout && pl.Cout % GM == 0 && p.lh >= 0 && (p.lw == 3 || p.lw == 4) &&
                     (reinterpret_cast<uintptr_t>(out) & 15u) == 0) ? 1 : 0;
     if (!halo) {
         const int max_stages = pl.KS == 64 ? 4 : (pl.KS == 32 ? 8 : 12);
@@ -932,14 +993,16 @@ int conv_tc_launch(Pass pass, int dtype, const Geom& g, const void* w, const voi
         if (r != CUDA_SUCCESS) { set_error("cuTensorMapEncodeTiled (filters) failed with code %d", (int)r); return PCB_ERR_CUDA; }
     }
     {
-        const cuuint64_t dims[5] = {(cuuint64_t)pl.Cp, (cuuint64_t)pl.Wp, (cuuint64_t)pl.Hp, (cuuint64_t)g.Nb, (cuuint64_t)pl.LK};
-        const cuuint64_t strides[4] = {(cuuint64_t)pl.Cp * 2, (cuuint64_t)pl.Wp * pl.Cp * 2, (cuuint64_t)pl.Hp * pl.Wp * pl.Cp * 2,
-                                       (cuuint64_t)g.Nb * pl.Hp * pl.Wp * pl.Cp * 2};
+        // staged copy [comp][img][Hp][Wp][Cp], or the caller's channels-last tensor [comp][img][Hin][Win][Cin] read in place
+        const int Wd = direct ? pl.Win : pl.Wp, Hd = direct ? pl.Hin : pl.Hp;
+        const cuuint64_t dims[5] = {(cuuint64_t)pl.Cp, (cuuint64_t)Wd, (cuuint64_t)Hd, (cuuint64_t)g.Nb, (cuuint64_t)pl.LK};
+        const cuuint64_t strides[4] = {(cuuint64_t)pl.Cp * 2, (cuuint64_t)Wd * pl.Cp * 2, (cuuint64_t)Hd * Wd * pl.Cp * 2,
+                                       (cuuint64_t)g.Nb * Hd * Wd * pl.Cp * 2};
         // with an element stride s the box extent is given in input elements: s * (pixels - 1) + 1 of them hold the pixels loaded
         const cuuint32_t box[5] = {(cuuint32_t)ks, (cuuint32_t)(halo ? p.Wt : (p.PW - 1) * pl.SW + 1), (cuuint32_t)(halo ? p.Ht : (p.PH - 1) * pl.SH + 1),
                                    (cuuint32_t)p.PN, 1};
         const cuuint32_t es[5] = {1, (cuuint32_t)pl.SW, (cuuint32_t)pl.SH, 1, 1};
-        const CUresult r = encode(&map_x, dt, 5, xp, dims, strides, box, es, CU_TENSOR_MAP_INTERLEAVE_NONE, sw,
+        const CUresult r = encode(&map_x, dt, 5, direct ? const_cast<void*>(act) : static_cast<void*>(xp), dims, strides, box, es, CU_TENSOR_MAP_INTERLEAVE_NONE, sw,
                                   CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
         if (r != CUDA_SUCCESS) { set_error("cuTensorMapEncodeTiled (activations) failed with code %d", (int)r); return PCB_ERR_CUDA; }
     }
@@ -1030,8 +1093,9 @@ int conv_filter_tc_launch(int dtype, const Geom& g, const void* dy, const void* 
         const size_t cap = (size_t)sm_count() * 16;
         const int bx = (int)((tx + 255) / 256 < cap ? (tx + 255) / 256 : cap), by = (int)((ty + 255) / 256 < cap ? (ty + 255) / 256 : cap);
         (void)bx; (void)by;
-        stage_activations(fmt, x, xp, lk * g.Nb, g.Ci, g.H, g.W, f.Hp, f.Wp, f.Cip, g.PT, g.PL, 1, 1, stream, channel_block(f.Cip), g.Nb);
-        stage_activations(fmt, dy, dyp, g.nc * g.Nb, g.Co, g.HO, g.WO, g.HO, g.WO, f.Cop, 0, 0, 1, 1, stream, channel_block(f.Cop), g.Nb);
+        const SrcStrides sx = {g.xp, g.xc, g.xh, g.xw}, sy = {g.yp, g.yc, g.yh, g.yw};
+        stage_activations(fmt, x, xp, lk * g.Nb, g.Ci, g.H, g.W, f.Hp, f.Wp, f.Cip, g.PT, g.PL, 1, 1, stream, channel_block(f.Cip), g.Nb, g.plain ? nullptr : &sx);
+        stage_activations(fmt, dy, dyp, g.nc * g.Nb, g.Co, g.HO, g.WO, g.HO, g.WO, f.Cop, 0, 0, 1, 1, stream, channel_block(f.Cop), g.Nb, g.plain ? nullptr : &sy);
         PCB_CUDA_TRY(cudaGetLastError());
         PCB_CUDA_TRY(cudaMemsetAsync(acc, 0, (size_t)g.nc * g.Co * g.Ci * taps * sizeof(float), stream));
     }
@@ -1102,8 +1166,10 @@ int conv_filter_tc_launch(int dtype, const Geom& g, const void* dy, const void* 
     PCB_CUDA_TRY(cudaGetLastError());
     const size_t per_tap = (size_t)g.nc * g.Co * g.Ci, total = per_tap * taps;
     const int blocks = (int)((total + 255) / 256 < 2368 ? (total + 255) / 256 : 2368);
-    if (fmt == 0) unpack_filter_grad_kernel<__half><<<blocks, 256, 0, stream>>>(acc, (__half*)dw, taps, per_tap, g.dw_io, g.Co, g.Ci);
-    else unpack_filter_grad_kernel<__nv_bfloat16><<<blocks, 256, 0, stream>>>(acc, (__nv_bfloat16*)dw, taps, per_tap, g.dw_io, g.Co, g.Ci);
+    const FilterStrides ds = {g.dr, g.dco, g.dci, g.dkh, g.dkw, g.KW};
+    const int dense_oihw = (g.dci == taps && g.dco == g.Ci * taps && (long long)g.dr == (long long)g.Co * g.Ci * taps && g.dkh == g.KW && g.dkw == 1) ? 1 : 0;
+    if (fmt == 0) unpack_filter_grad_kernel<__half><<<blocks, 256, 0, stream>>>(acc, (__half*)dw, taps, per_tap, dense_oihw, g.Co, g.Ci, ds);
+    else unpack_filter_grad_kernel<__nv_bfloat16><<<blocks, 256, 0, stream>>>(acc, (__nv_bfloat16*)dw, taps, per_tap, dense_oihw, g.Co, g.Ci, ds);
     PCB_CUDA_TRY(cudaGetLastError());
     return PCB_OK;
 }

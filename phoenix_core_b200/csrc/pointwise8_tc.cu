@@ -467,7 +467,7 @@ bool pointwise_1x1(const Geom& g) {
 bool pointwise8_tc_supported(Pass /*pass*/, int dtype, int variant, const Geom& g) {
     if (variant != PCB_VARIANT_8_PRODUCT) return false;
     if (dtype != PCB_F16 && dtype != PCB_BF16) return false;
-    if (g.nc != 4 || g.real_in || g.w_io || g.dw_io) return false;        // the factorisation exists for quaternions only
+    if (g.nc != 4 || g.real_in || g.w_io || g.dw_io || !g.plain) return false;   // quaternions only; NCHW / OIHW tensors
     if (!pointwise_1x1(g)) return false;
     // TMA: every global stride a multiple of 16 bytes
     return (g.Ci % 8 == 0) && (g.Co % 8 == 0) && ((g.H * g.W) % 8 == 0);

@@ -24,8 +24,6 @@
 // delayed the MMA warp's own instruction issue by ~4000 cycles per tile; the bulk stores do not).
 // Every mbarrier wait is bounded; an expired wait sets the status word and the CTA leaves through the common
 // teardown.
-#include <cstdlib>
-
 #include "tc_common.cuh"
 #include "tensor_path.cuh"
 
@@ -38,6 +36,7 @@ using namespace tc;
 constexpr int CT = 128;             // channel tile (MMA M)
 constexpr int PT = 128;             // pixel tile (MMA N): two TMA boxes of 64 pixels
 constexpr int KS = 32;              // channels per component per stage
+static_assert(KS / 16 == 2, "the MMA issuer handles the first and the last K step of a slice separately");
 constexpr int U_STAGES = 3;
 constexpr uint32_t A_BYTES = 4 * CT * KS * 2;      // 32 KB: 4 weight components
 constexpr uint32_t B_BYTES = 2 * 4 * KS * 64 * 2;  // 32 KB: 2 pixel boxes x 4 activation components
@@ -70,7 +69,7 @@ __device__ __forceinline__ uint64_t make_desc_kmajor_sw64(uint32_t smem_addr) {
     return (uint64_t)((smem_addr & 0x3FFFFu) >> 4) | ((uint64_t)1 << 16) | ((uint64_t)(512 >> 4) << 32) | DESC_VERSION_SM100 | DESC_SWIZZLE_64B;
 }
 
-template <bool BWD, int EDGE_J>
+template <bool BWD>
 __global__ void __launch_bounds__(U_THREADS, 1)
 qconv_pointwise_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant__ CUtensorMap map_act,
                           const __grid_constant__ CUtensorMap map_out, UParams p, const uint16_t* __restrict__ bias, int* __restrict__ status) {
@@ -154,73 +153,95 @@ qconv_pointwise_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __gri
         __syncwarp();
     } else if (warp == 1) {
         // ---------------------------------------------------------------- MMA issuer
-        int it = 0, local_tile = 0;
-        bool ok = true;
-        auto issue = [&](uint32_t a_addr, uint32_t b_addr, int j, int i, int o, uint32_t accumulate) {
-            const int r = i ^ o;
-            const bool neg = BWD ? quat_negative(o, i) : quat_negative(i, o);
-            const uint64_t ad = BWD ? make_desc_mnmajor(a_addr + r * (KS * 128) + j * 2048, A_BYTES / 2)
-                                    : make_desc_kmajor_sw64(a_addr + r * (CT * KS * 2) + j * 32);
-            const uint64_t bd = make_desc_mnmajor(b_addr + i * (KS * 128) + j * 2048, B_BOX_BYTES);
-            mma_f16_ss(tmem_base + o * PT, ad, bd, make_idesc_f16(p.fmt, CT, PT, BWD, true, neg, false), accumulate);
-        };
-        if (resident && blockIdx.x < n_tiles) ok = mbar_wait_bounded(a_full, 0, status, ST_U_MMA);
-        for (int tile = blockIdx.x; tile < n_tiles && ok; tile += gridDim.x, ++local_tile) {
-            for (int k = 0; k < n_k && ok; ++k, ++it) {
-                const int s = it % n_stages;
-                ok = mbar_wait_bounded(full_bar + 8 * s, (it / n_stages) & 1, status, ST_U_MMA);
-                if (!ok) break;
-                tc_fence_after_sync();
-                const uint32_t a_addr = a_slot(k, s), b_addr = b_slot(s);
-                // A tile's MMAs go round the four accumulators (i = streamed component, o = accumulator component), except at
-                // its two ends, where they are issued pair-wise (accumulators 0,1 then 2,3):
-                //  - the first EDGE_J K steps of the first slice: each pair starts as soon as the epilogue of the previous tile has
-                //    drained it;
-                //  - the last EDGE_J K steps of the last slice: the first pair is complete (and signalled) while the second still
-                //    computes, so its drain overlaps those MMAs and the next tile can start on it without a bubble.
-                // Inside a pair the MMAs alternate between the two accumulators (back-to-back MMAs into one accumulator run at two
-                // thirds of the rate of independent ones).
-                constexpr int J = KS / 16;
-                const bool first = k == 0, last = k == n_k - 1;
-                const int head = first ? (last ? J : EDGE_J) : 0;            // a one-slice tile is issued pair-wise throughout
-                const int tail = (last && !first) ? EDGE_J : 0;
-                for (int pair = 0; pair < 2 && ok && head > 0; ++pair) {
-                    if (local_tile > 0) {
-                        ok = mbar_wait_bounded(tmem_empty + 8 * (2 * pair), (local_tile - 1) & 1, status, ST_U_MMA) &&
-                             mbar_wait_bounded(tmem_empty + 8 * (2 * pair + 1), (local_tile - 1) & 1, status, ST_U_MMA);
+        // ONE thread runs this whole loop: waits, descriptor arithmetic and tcgen05.mma / commit. What that thread executes
+        // between two MMAs is time the tensor pipe idles (its queue is shallow), so the loop carries no division, no warp
+        // synchronisation and no descriptor construction: the two 64-bit shared-memory descriptors of a stage are built
+        // once, and an MMA's descriptors are those with a constant added to the address field of the low word (addresses
+        // are 16-byte units below 2^14, so the addition never carries into the neighbouring field).
+        if (lane == 0) {
+            int s = 0, local_tile = 0;
+            uint32_t par = 0;                                    // phase parity of stage s
+            bool ok = true;
+            const uint32_t idesc_pos = make_idesc_f16(p.fmt, CT, PT, BWD, true, false, false);
+            const uint32_t idesc_neg = make_idesc_f16(p.fmt, CT, PT, BWD, true, true, false);
+            uint32_t a_lo = 0, a_hi = 0, b_lo = 0, b_hi = 0;
+            auto issue = [&](int j, int i, int o, uint32_t accumulate) {
+                const int r = i ^ o;
+                const bool neg = BWD ? quat_negative(o, i) : quat_negative(i, o);
+                const uint32_t a_off = BWD ? (uint32_t)(r * (KS * 128) + j * 2048) >> 4 : (uint32_t)(r * (CT * KS * 2) + j * 32) >> 4;
+                const uint32_t b_off = (uint32_t)(i * (KS * 128) + j * 2048) >> 4;
+                mma_f16_ss_words(tmem_base + o * PT, a_lo + a_off, a_hi, b_lo + b_off, b_hi, neg ? idesc_neg : idesc_pos, accumulate);
+            };
+            if (resident && blockIdx.x < n_tiles) ok = mbar_wait_bounded(a_full, 0, status, ST_U_MMA);
+            for (int tile = blockIdx.x; tile < n_tiles && ok; tile += gridDim.x, ++local_tile) {
+                for (int k = 0; k < n_k && ok; ++k) {
+                    ok = mbar_wait_bounded(full_bar + 8 * s, par, status, ST_U_MMA);
+                    if (!ok) break;
+                    tc_fence_after_sync();
+                    {
+                        const uint64_t ad = BWD ? make_desc_mnmajor(a_slot(k, s), A_BYTES / 2) : make_desc_kmajor_sw64(a_slot(k, s));
+                        const uint64_t bd = make_desc_mnmajor(b_slot(s), B_BOX_BYTES);
+                        a_lo = (uint32_t)ad; a_hi = (uint32_t)(ad >> 32); b_lo = (uint32_t)bd; b_hi = (uint32_t)(bd >> 32);
+                    }
+                    // A tile's MMAs go round the four accumulators (i = streamed component, o = accumulator component), except at
+                    // its two ends, where they are issued pair-wise (accumulators 0,1 then 2,3):
+                    //  - the first K step of the first slice: each pair starts as soon as the epilogue of the previous tile has
+                    //    drained it;
+                    //  - the last K step of the last slice: the first pair is complete (and signalled) while the second still
+                    //    computes, so its drain overlaps those MMAs.
+                    // Inside a pair the MMAs alternate between the two accumulators (back-to-back MMAs into one accumulator run at
+                    // two thirds of the rate of independent ones).
+                    constexpr int J = KS / 16;
+                    const bool first = k == 0, last = k == n_k - 1;
+                    if (first) {
+#pragma unroll
+                        for (int pair = 0; pair < 2; ++pair) {
+                            if (local_tile > 0) {
+                                ok = ok && mbar_wait_bounded(tmem_empty + 8 * (2 * pair), (local_tile - 1) & 1, status, ST_U_MMA) &&
+                                     mbar_wait_bounded(tmem_empty + 8 * (2 * pair + 1), (local_tile - 1) & 1, status, ST_U_MMA);
+                                tc_fence_after_sync();
+                            }
+                            if (ok) {
+#pragma unroll
+                                for (int i = 0; i < 4; ++i)
+#pragma unroll
+                                    for (int oo = 0; oo < 2; ++oo) issue(0, i, 2 * pair + oo, i > 0 ? 1u : 0u);
+                            }
+                        }
                         if (!ok) break;
-                        tc_fence_after_sync();
-                    }
-                    if (lane == 0) {
-                        for (int j = 0; j < head; ++j)
-#pragma unroll
-                            for (int i = 0; i < 4; ++i)
-#pragma unroll
-                                for (int oo = 0; oo < 2; ++oo) issue(a_addr, b_addr, j, i, 2 * pair + oo, (j > 0 || i > 0) ? 1u : 0u);
-                        if (last) mma_commit(pair == 0 ? tmem_full0 : tmem_full1);
-                    }
-                    __syncwarp();
-                }
-                if (!ok) break;
-                if (lane == 0) {
-                    for (int j = head; j < J - tail; ++j)
+                    } else {
 #pragma unroll
                         for (int i = 0; i < 4; ++i)
 #pragma unroll
-                            for (int o = 0; o < 4; ++o) issue(a_addr, b_addr, j, i, o, 1u);
-                    for (int pair = 0; pair < 2 && tail > 0; ++pair) {
-                        for (int j = J - tail; j < J; ++j)
+                            for (int o = 0; o < 4; ++o) issue(0, i, o, 1u);
+                    }
+#pragma unroll
+                    for (int j = 1; j < J - 1; ++j)
+#pragma unroll
+                        for (int i = 0; i < 4; ++i)
+#pragma unroll
+                            for (int o = 0; o < 4; ++o) issue(j, i, o, 1u);
+                    if (last) {
+#pragma unroll
+                        for (int pair = 0; pair < 2; ++pair) {
 #pragma unroll
                             for (int i = 0; i < 4; ++i)
 #pragma unroll
-                                for (int oo = 0; oo < 2; ++oo) issue(a_addr, b_addr, j, i, 2 * pair + oo, 1u);
-                        mma_commit(pair == 0 ? tmem_full0 : tmem_full1);
+                                for (int oo = 0; oo < 2; ++oo) issue(J - 1, i, 2 * pair + oo, 1u);
+                            mma_commit(pair == 0 ? tmem_full0 : tmem_full1);
+                        }
+                    } else {
+#pragma unroll
+                        for (int i = 0; i < 4; ++i)
+#pragma unroll
+                            for (int o = 0; o < 4; ++o) issue(J - 1, i, o, 1u);
                     }
                     mma_commit(empty_bar + 8 * s);
+                    if (++s == n_stages) { s = 0; par ^= 1u; }
                 }
-                __syncwarp();
             }
         }
+        __syncwarp();
     } else {
         // ---------------------------------------------------------------- epilogue (warps 2..9)
         // Ordinary global stores from here cost more than their bandwidth: every lane owns another channel row, so
@@ -383,14 +404,19 @@ qconv_pointwise_filter_tc_kernel(const __grid_constant__ CUtensorMap map_dy, con
         }
         __syncwarp();
     } else if (warp == 1) {
-        bool ok = true;
-        for (int it = 0; it < n_steps && ok; ++it) {
-            const int s = it % U_STAGES;
-            ok = mbar_wait_bounded(full_bar + 8 * s, (it / U_STAGES) & 1, status, ST_U_MMA);
-            if (!ok) break;
-            tc_fence_after_sync();
-            if (lane == 0) {
-                const uint32_t a_addr = tiles_addr + s * F_STAGE_BYTES, b_addr = a_addr + F_OP_BYTES;
+        if (lane == 0) {                       // one thread: waits, stepped descriptors, MMAs (see the forward kernel)
+            bool ok = true;
+            int s = 0;
+            uint32_t par = 0;
+            const uint32_t idesc_pos = make_idesc_f16(p.fmt, 128, 128, false, false, false, false);
+            const uint32_t idesc_neg = make_idesc_f16(p.fmt, 128, 128, false, false, true, false);
+            for (int it = 0; it < n_steps && ok; ++it) {
+                ok = mbar_wait_bounded(full_bar + 8 * s, par, status, ST_U_MMA);
+                if (!ok) break;
+                tc_fence_after_sync();
+                const uint64_t ad = make_desc_kmajor_sw64(tiles_addr + s * F_STAGE_BYTES);
+                const uint64_t bd = make_desc_kmajor_sw64(tiles_addr + s * F_STAGE_BYTES + F_OP_BYTES);
+                const uint32_t a_lo = (uint32_t)ad, a_hi = (uint32_t)(ad >> 32), b_lo = (uint32_t)bd, b_hi = (uint32_t)(bd >> 32);
 #pragma unroll
                 for (int j = 0; j < FKP / 16; ++j) {
 #pragma unroll
@@ -398,19 +424,18 @@ qconv_pointwise_filter_tc_kernel(const __grid_constant__ CUtensorMap map_dy, con
 #pragma unroll
                         for (int r = 0; r < 4; ++r) {
                             const int d = l ^ r;
-                            const uint64_t ad = make_desc_kmajor_sw64(a_addr + d * (128 * FKP * 2) + j * 32);
-                            const uint64_t bd = make_desc_kmajor_sw64(b_addr + l * (128 * FKP * 2) + j * 32);
-                            const uint32_t idesc = make_idesc_f16(p.fmt, 128, 128, false, false, quat_negative(l, d), false);
-                            mma_f16_ss(tmem_base + r * 128, ad, bd, idesc, (it > 0 || j > 0 || l > 0) ? 1u : 0u);
+                            const uint32_t a_off = (uint32_t)(d * (128 * FKP * 2) + j * 32) >> 4, b_off = (uint32_t)(l * (128 * FKP * 2) + j * 32) >> 4;
+                            mma_f16_ss_words(tmem_base + r * 128, a_lo + a_off, a_hi, b_lo + b_off, b_hi, quat_negative(l, d) ? idesc_neg : idesc_pos,
+                                             (it > 0 || j > 0 || l > 0) ? 1u : 0u);
                         }
                     }
                 }
                 mma_commit(empty_bar + 8 * s);
                 if (it == n_steps - 1) mma_commit(tmem_full);
+                if (++s == U_STAGES) { s = 0; par ^= 1u; }
             }
-            __syncwarp();
+            if (n_steps == 0) mbar_arrive(tmem_full);
         }
-        if (n_steps == 0 && lane == 0) mbar_arrive(tmem_full);
         __syncwarp();
     } else {
         const int q = warp & 3, half = (warp - 2) >> 2;
@@ -519,16 +544,13 @@ int pointwise_tc_launch(Pass pass, int dtype, const Geom& g, const void* w, cons
         grid -= grid % p.n_c_tiles;
         p.a_resident = 1;
     }
-    static const int edge = [] { const char* e = getenv("PCB_PW_EDGE"); return e ? atoi(e) : 2; }();
-    auto launch = [&](auto kernel) -> int {
-        PCB_CUDA_TRY(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)U_SMEM_BYTES));
-        kernel<<<grid, U_THREADS, U_SMEM_BYTES, stream>>>(map_w, map_act, map_out, p, (const uint16_t*)bias, status);
-        return PCB_OK;
-    };
-    int rc;
-    if (!bwd) rc = edge == 1 ? launch(qconv_pointwise_tc_kernel<false, 1>) : launch(qconv_pointwise_tc_kernel<false, 2>);
-    else rc = edge == 1 ? launch(qconv_pointwise_tc_kernel<true, 1>) : launch(qconv_pointwise_tc_kernel<true, 2>);
-    if (rc != PCB_OK) return rc;
+    if (!bwd) {
+        PCB_CUDA_TRY(cudaFuncSetAttribute(qconv_pointwise_tc_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)U_SMEM_BYTES));
+        qconv_pointwise_tc_kernel<false><<<grid, U_THREADS, U_SMEM_BYTES, stream>>>(map_w, map_act, map_out, p, (const uint16_t*)bias, status);
+    } else {
+        PCB_CUDA_TRY(cudaFuncSetAttribute(qconv_pointwise_tc_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)U_SMEM_BYTES));
+        qconv_pointwise_tc_kernel<true><<<grid, U_THREADS, U_SMEM_BYTES, stream>>>(map_w, map_act, map_out, p, (const uint16_t*)bias, status);
+    }
     PCB_CUDA_TRY(cudaGetLastError());
     return PCB_OK;
 }

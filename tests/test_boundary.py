@@ -129,7 +129,9 @@ def test_grouped_descriptor_reaches_the_c_abi_per_group(built_lib):
     assert d.getOutputShape() == (8, 6, 9, 7) and d.getGroups() == 2
     c = _conv_desc(d, torch.float16, Context({"UPSTRIDE_MEMORY_OPTIMIZED": "1"}), _lib.ENGINE_AUTO, has_bias=True)
     assert (c.ci, c.co, c.groups, c.n) == (4, 6, 2, 2)
-    assert built_lib.pcb_qconv2d_engine_for(ctypes.byref(c), 0) == _lib.ENGINE_SIMT
+    assert built_lib.pcb_qconv2d_engine_for(ctypes.byref(c), 0) == _lib.ENGINE_TENSOR      # 16-bit groups: the general tensor-core kernels
+    c32 = _conv_desc(d, torch.float32, Context({"UPSTRIDE_MEMORY_OPTIMIZED": "1"}), _lib.ENGINE_AUTO, has_bias=True)
+    assert built_lib.pcb_qconv2d_engine_for(ctypes.byref(c32), 0) == _lib.ENGINE_SIMT    # fp32 groups stay on the CUDA cores
     assert built_lib.pcb_qconv2d_fwd_workspace_size(ctypes.byref(c)) >= 256
     # the filter gradient of a group is staged in the workspace: 4 components x 3 filters x 4 channels x 9 taps of fp16
     assert built_lib.pcb_qconv2d_bwd_workspace_size(ctypes.byref(c)) >= 256 + 4 * 3 * 4 * 9 * 2

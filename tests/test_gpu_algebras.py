@@ -202,9 +202,11 @@ def _run_layout_fwd(gpu, x, w, b, stride, pad, dtype, algebra, data_format, filt
 
 @pytest.mark.parametrize("data_format,filter_layout", [("NHWC", "OHWI"), ("NHWC", "HWIO"), ("NCHW", "HWIO"), ("NHWC", "OIHW")])
 @pytest.mark.parametrize("name", ["quaternion", "complex"])
-@pytest.mark.parametrize("dtype,variant", [("f32", "16p"), ("f32", "8p"), ("f16", "16p")])
-def test_conv_layouts_vs_oracle(gpu, oracle, data_format, filter_layout, name, dtype, variant):
-    """The other activation / filter layouts against the oracle (which computes in NCHW / OIHW on permuted copies)."""
+@pytest.mark.parametrize("dtype,variant,engine", [("f32", "16p", "auto"), ("f32", "8p", "auto"), ("f16", "16p", "simt"), ("f16", "16p", "tensor"),
+                                                  ("bf16", "16p", "tensor")])
+def test_conv_layouts_vs_oracle(gpu, oracle, data_format, filter_layout, name, dtype, variant, engine):
+    """The other activation / filter layouts against the oracle (which computes in NCHW / OIHW on permuted copies), on the
+    CUDA-core kernels and, for 16-bit tensors, on the tensor cores (every tensor addressed through element strides)."""
     alg, code, D = ALGEBRAS[name]
     n, ci, co, h, w_, kh, kw, stride, pad = 2, 5, 6, 9, 7, 3, 2, (2, 1), (1, 0, 1, 1)
     x = gpu.rounded(uniform(101, (D * n, ci, h, w_)), dtype)
@@ -218,18 +220,19 @@ def test_conv_layouts_vs_oracle(gpu, oracle, data_format, filter_layout, name, d
     ctx = gpu.context(variant)
     td = gpu.TORCH_DTYPES[dtype]
     y = torch.full(fwd.getOutputShape(), float("nan"), dtype=td, device="cuda")
-    pcb.conv2DFwd(gpu.dev(xl, dtype), gpu.dev(wl, dtype), gpu.dev(b, dtype), y, fwd, ctx)
+    pcb.conv2DFwd(gpu.dev(xl, dtype), gpu.dev(wl, dtype), gpu.dev(b, dtype), y, fwd, ctx, gpu.ENGINES[engine])
     _check(_from_layout(gpu.host(y), data_format), ref, dtype, gpu, "y")
     dw = torch.full(wl.shape, float("nan"), dtype=td, device="cuda")
     dx = torch.full(xl.shape, float("nan"), dtype=td, device="cuda")
-    pcb.conv2DBwd(gpu.dev(xl, dtype), gpu.dev(wl, dtype), gpu.dev(dyl, dtype), dw, dx, bwd, ctx)
+    pcb.conv2DBwd(gpu.dev(xl, dtype), gpu.dev(wl, dtype), gpu.dev(dyl, dtype), dw, dx, bwd, ctx, gpu.ENGINES[engine])
     _check(_from_layout(gpu.host(dx), data_format), rdx, dtype, gpu, "dx")
     _check(_from_layout(gpu.host(dw), filter_layout), rdw, dtype, gpu, "dw")
 
 
-@pytest.mark.parametrize("dtype,variant", [("f32", "16p"), ("f32", "8p"), ("f16", "16p"), ("bf16", "8p")])
-@pytest.mark.parametrize("groups,ci,co", [(2, 6, 4), (4, 4, 8), (8, 8, 8)])      # the last one is depthwise
-def test_grouped_conv_vs_oracle(gpu, oracle, dtype, variant, groups, ci, co):
+@pytest.mark.parametrize("dtype,variant,engine", [("f32", "16p", "auto"), ("f32", "8p", "auto"), ("f16", "16p", "simt"), ("bf16", "8p", "simt"),
+                                                  ("f16", "16p", "tensor"), ("bf16", "16p", "tensor")])
+@pytest.mark.parametrize("groups,ci,co", [(2, 6, 4), (4, 4, 8), (8, 8, 8), (2, 64, 96)])      # (8, 8, 8) is depthwise
+def test_grouped_conv_vs_oracle(gpu, oracle, dtype, variant, engine, groups, ci, co):
     """Grouped quaternion convolution (reference: the groups argument, src/conv2d.hpp:70-91, :329-353) against the oracle run
     group by group on channel slices: forward with bias, both gradients."""
     n, h, w_, k = 2, 9, 7, 3
@@ -242,7 +245,7 @@ def test_grouped_conv_vs_oracle(gpu, oracle, dtype, variant, groups, ci, co):
     ys = [oracle.conv2d_fwd(np.ascontiguousarray(x[:, g * cig:(g + 1) * cig]), np.ascontiguousarray(w[:, g * cog:(g + 1) * cog]),
                             np.ascontiguousarray(b[:, g * cog:(g + 1) * cog]), stride, (1, 1), pad, oracle.QUATERNION, ov) for g in range(groups)]
     ref = np.concatenate(ys, axis=1)
-    got = gpu.run_conv_fwd(x, w, b, stride, pad, dtype, variant, "auto", groups=groups)
+    got = gpu.run_conv_fwd(x, w, b, stride, pad, dtype, variant, engine, groups=groups)
     assert got.shape == ref.shape
     _check(got, ref, dtype, gpu, "y")
     dy = gpu.rounded(normal(74, ref.shape), dtype)
@@ -251,6 +254,41 @@ def test_grouped_conv_vs_oracle(gpu, oracle, dtype, variant, groups, ci, co):
         dwg, dxg = oracle.conv2d_bwd(np.ascontiguousarray(x[:, g * cig:(g + 1) * cig]), np.ascontiguousarray(w[:, g * cog:(g + 1) * cog]),
                                      np.ascontiguousarray(dy[:, g * cog:(g + 1) * cog]), stride, (1, 1), pad, oracle.QUATERNION, ov, True)
         dws.append(dwg); dxs.append(dxg)
-    dw, dx = gpu.run_conv_bwd(x, w, dy, stride, pad, dtype, variant, "auto", True, groups=groups)
+    dw, dx = gpu.run_conv_bwd(x, w, dy, stride, pad, dtype, variant, engine, True, groups=groups)
     _check(dw, np.concatenate(dws, axis=1), dtype, gpu, "dw")
     _check(dx, np.concatenate(dxs, axis=1), dtype, gpu, "dx")
+
+
+# n, ci, co, h, w, k, stride, pad: channels-last layers whose channel counts are multiples of 16, which the tensor-core kernels
+# read in place (no staged copy; the padding is the zero fill of out-of-range TMA coordinates)
+DIRECT_SHAPES = [
+    (2, 32, 48, 12, 10, 3, (1, 1), (1, 1, 1, 1)),      # plain form, 32-channel slices
+    (1, 64, 32, 30, 21, 3, (1, 1), (1, 1, 1, 1)),      # halo form: one tile per image column, negative start coordinates
+    (2, 64, 64, 14, 14, 3, (2, 2), (0, 0, 1, 1)),      # stride 2 through the element stride of the tensor map; backward-data staged
+    (3, 16, 16, 9, 9, 1, (1, 1), (0, 0, 0, 0)),        # pointwise: a plain GEMM over [pixel][channel] rows
+    (2, 128, 64, 8, 8, 5, (1, 1), (2, 2, 2, 2)),       # 25 taps, 64-channel slices
+]
+
+
+@pytest.mark.parametrize("shape", DIRECT_SHAPES)
+@pytest.mark.parametrize("dtype", ["f16", "bf16"])
+@pytest.mark.parametrize("filter_layout", ["OHWI", "HWIO"])
+def test_channels_last_read_in_place_on_tensor_cores(gpu, oracle, shape, dtype, filter_layout):
+    n, ci, co, h, w_, k, stride, pad = shape
+    x = gpu.rounded(uniform(111, (4 * n, ci, h, w_)), dtype)
+    w = gpu.rounded(normal(112, (4, co, ci, k, k), std=(2.0 / (4 * ci * k * k)) ** 0.5), dtype)
+    b = gpu.rounded(uniform(113, (4, co)), dtype)
+    ref = oracle.conv2d_fwd(x, w, b, stride, (1, 1), pad)
+    dy = gpu.rounded(normal(114, ref.shape), dtype)
+    rdw, rdx = oracle.conv2d_bwd(x, w, dy, stride, (1, 1), pad)
+    xl, wl, dyl = _to_layout(x, "NHWC"), _to_layout(w, filter_layout), _to_layout(dy, "NHWC")
+    fwd, bwd = _descs(xl.shape, wl.shape, stride, pad, pcb.Algebra.QUATERNION, "NHWC", filter_layout, True, True)
+    ctx, td = gpu.context("16p"), gpu.TORCH_DTYPES[dtype]
+    y = torch.full(fwd.getOutputShape(), float("nan"), dtype=td, device="cuda")
+    pcb.conv2DFwd(gpu.dev(xl, dtype), gpu.dev(wl, dtype), gpu.dev(b, dtype), y, fwd, ctx, gpu.ENGINES["tensor"])
+    _check(_from_layout(gpu.host(y), "NHWC"), ref, dtype, gpu, "y")
+    dw = torch.full(wl.shape, float("nan"), dtype=td, device="cuda")
+    dx = torch.full(xl.shape, float("nan"), dtype=td, device="cuda")
+    pcb.conv2DBwd(gpu.dev(xl, dtype), gpu.dev(wl, dtype), gpu.dev(dyl, dtype), dw, dx, bwd, ctx, gpu.ENGINES["tensor"])
+    _check(_from_layout(gpu.host(dx), "NHWC"), rdx, dtype, gpu, "dx")
+    _check(_from_layout(gpu.host(dw), filter_layout), rdw, dtype, gpu, "dw")
