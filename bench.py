@@ -264,10 +264,12 @@ def dense_leg(torch, pcb, _lib, peaks):
     return out
 
 
-def sweep_leg(torch, pcb, _lib, peaks, reps=5, batch=128):
+def sweep_leg(torch, pcb, _lib, peaks, reps=5, batch=128, only=None, layouts=("nchw",), extra_nhwc=((64, 56, 3, 1),), dtype="f16"):
     """The ResNet-stage sweep, fp16: 3x3 (pad 1) and 1x1, stride 1 and 2, forward / backward-data / backward-filter of each
     shape timed separately (3 warm-up + `reps` launches, CUDA events; times include every staging kernel of the call).
-    Inputs are seeded U[-1,1] generated on the device; every shape's tensors exceed the L2 or are rewritten each launch."""
+    Inputs are seeded U[-1,1] generated on the device; every shape's tensors exceed the L2 or are rewritten each launch.
+    `extra_nhwc`: shapes repeated with channels-last activations and OHWI filters (read in place by the tensor-core kernels).
+    `only` = (c, hw, k, stride) restricts the sweep to one shape (profiling)."""
     from phoenix_core_b200.context import Context
     from phoenix_core_b200.ops import Device, _conv_desc, _ptr, _stream
     L = _lib.lib()
@@ -275,41 +277,49 @@ def sweep_leg(torch, pcb, _lib, peaks, reps=5, batch=128):
     dev = torch.device("cuda", torch.cuda.current_device())
     rows = []
     gen = torch.Generator(device=dev).manual_seed(SEED + 11)
-    for c, hw in STAGES:
-        for k in (3, 1):
-            for stride in (1, 2):
-                pad = 1 if k == 3 else 0
-                a = ((4 * batch, c, hw, hw), (4, c, c, k, k), stride, 1, pcb.Padding.EXPLICIT, (pad, pad, pad, pad), 1,
-                     pcb.Algebra.QUATERNION, pcb.DataFormat.NCHW, pcb.FilterLayout.OIHW)
-                fwd, bwd = pcb.Conv2DFwdDescriptor(*a, False), pcb.Conv2DBwdDescriptor(*a, True)
-                x = (torch.rand((4 * batch, c, hw, hw), generator=gen, device=dev) * 2 - 1).to(torch.float16)
-                w = (torch.rand((4, c, c, k, k), generator=gen, device=dev) * 2 - 1).to(torch.float16)
-                y = torch.empty(fwd.getOutputShape(), dtype=torch.float16, device=dev)
-                dy = (torch.rand(tuple(y.shape), generator=gen, device=dev) * 2 - 1).to(torch.float16)
-                dw, dx = torch.empty_like(w), torch.empty_like(x)
-                d = _conv_desc(bwd, torch.float16, ctx, _lib.ENGINE_AUTO, require_input_grad=True)
-                ws = Device.get(dev).requestWorkspace(max(L.pcb_qconv2d_bwd_workspace_size(ctypes.byref(d)),
-                                                          L.pcb_qconv2d_fwd_workspace_size(ctypes.byref(d))))
-                ho = y.shape[2]
-                fl = 32.0 * batch * ho * ho * c * c * k * k
-                xb, yb, wb = 2 * x.numel(), 2 * y.numel(), 2 * w.numel()
-                passes = (
-                    ("fwd", lambda: pcb.conv2DFwd(x, w, None, y, fwd, ctx), xb + yb + wb, 0),
-                    ("bwd_data", lambda: _lib.check(L.pcb_qconv2d_bwd_data(ctypes.byref(d), _ptr(w), _ptr(dy), _ptr(dx), _ptr(ws), ws.numel(), _stream())), yb + wb + xb, 1),
-                    ("bwd_filter", lambda: _lib.check(L.pcb_qconv2d_bwd_filter(ctypes.byref(d), _ptr(x), _ptr(dy), _ptr(dw), _ptr(ws), ws.numel(), _stream())), xb + yb + 2 * wb, 2),
-                )
-                for name, fn, nbytes, pid in passes:
-                    ms = event_time(torch, fn, reps, 3)
-                    rows.append({"c": c, "hw": hw, "k": k, "s": stride, "pass": name, "ms": round(ms, 4),
-                                 "tflops": round(fl / (ms * 1e-3) / 1e12, 1), "gbs": round(nbytes / (ms * 1e-3) / 1e9, 0),
-                                 "f_tensor": round(fl / (ms * 1e-3) / 1e12 / peaks["tflops_sustained"], 3),
-                                 "f_hbm": round(nbytes / (ms * 1e-3) / 1e9 / peaks["hbm_gbs"], 3),
-                                 "engine": L.pcb_qconv2d_engine_for(ctypes.byref(d), pid)})
-                _lib.check(L.pcb_check_device_status(_ptr(ws), ws.numel(), _stream()))
-                del x, w, y, dy, dw, dx
-                torch.cuda.empty_cache()
-    return {"config": "batch %d, fp16, 16-product, NCHW, U[-1,1]; f_tensor against the sustained tensor peak, f_hbm = algorithmic "
-                      "bytes / time against the copy bandwidth; engine 2 = tcgen05, 1 = CUDA cores" % batch,
+    tdt = torch.float32 if dtype == "f32" else torch.float16
+    eb = 4 if dtype == "f32" else 2
+    cases = [(c, hw, k, s_, lay) for lay in layouts for c, hw in STAGES for k in (3, 1) for s_ in (1, 2)]
+    cases += [(c, hw, k, s_, "nhwc") for c, hw, k, s_ in extra_nhwc if "nhwc" not in layouts]
+    for c, hw, k, stride, layout in cases:
+        if only is not None and tuple(only) != (c, hw, k, stride):
+            continue
+        pad = 1 if k == 3 else 0
+        nhwc = layout == "nhwc"
+        xshape = (4 * batch, hw, hw, c) if nhwc else (4 * batch, c, hw, hw)
+        wshape = (4, c, k, k, c) if nhwc else (4, c, c, k, k)
+        a = (xshape, wshape, stride, 1, pcb.Padding.EXPLICIT, (pad, pad, pad, pad), 1, pcb.Algebra.QUATERNION,
+             pcb.DataFormat.NHWC if nhwc else pcb.DataFormat.NCHW, pcb.FilterLayout.OHWI if nhwc else pcb.FilterLayout.OIHW)
+        fwd, bwd = pcb.Conv2DFwdDescriptor(*a, False), pcb.Conv2DBwdDescriptor(*a, True)
+        x = (torch.rand(xshape, generator=gen, device=dev) * 2 - 1).to(tdt)
+        w = (torch.rand(wshape, generator=gen, device=dev) * 2 - 1).to(tdt)
+        y = torch.empty(fwd.getOutputShape(), dtype=tdt, device=dev)
+        dy = (torch.rand(tuple(y.shape), generator=gen, device=dev) * 2 - 1).to(tdt)
+        dw, dx = torch.empty_like(w), torch.empty_like(x)
+        d = _conv_desc(bwd, tdt, ctx, _lib.ENGINE_AUTO, require_input_grad=True)
+        ws = Device.get(dev).requestWorkspace(max(L.pcb_qconv2d_bwd_workspace_size(ctypes.byref(d)),
+                                                  L.pcb_qconv2d_fwd_workspace_size(ctypes.byref(d))))
+        ho = y.shape[1] if nhwc else y.shape[2]
+        fl = 32.0 * batch * ho * ho * c * c * k * k
+        xb, yb, wb = eb * x.numel(), eb * y.numel(), eb * w.numel()
+        passes = (
+            ("fwd", lambda: pcb.conv2DFwd(x, w, None, y, fwd, ctx), xb + yb + wb, 0),
+            ("bwd_data", lambda: _lib.check(L.pcb_qconv2d_bwd_data(ctypes.byref(d), _ptr(w), _ptr(dy), _ptr(dx), _ptr(ws), ws.numel(), _stream())), yb + wb + xb, 1),
+            ("bwd_filter", lambda: _lib.check(L.pcb_qconv2d_bwd_filter(ctypes.byref(d), _ptr(x), _ptr(dy), _ptr(dw), _ptr(ws), ws.numel(), _stream())), xb + yb + 2 * wb, 2),
+        )
+        for name, fn, nbytes, pid in passes:
+            ms = event_time(torch, fn, reps, 3)
+            rows.append({"c": c, "hw": hw, "k": k, "s": stride, "layout": layout, "dtype": dtype, "pass": name, "ms": round(ms, 4),
+                         "tflops": round(fl / (ms * 1e-3) / 1e12, 1), "gbs": round(nbytes / (ms * 1e-3) / 1e9, 0),
+                         "f_tensor": round(fl / (ms * 1e-3) / 1e12 / peaks["tflops_sustained"], 3),
+                         "f_hbm": round(nbytes / (ms * 1e-3) / 1e9 / peaks["hbm_gbs"], 3),
+                         "engine": L.pcb_qconv2d_engine_for(ctypes.byref(d), pid)})
+        _lib.check(L.pcb_check_device_status(_ptr(ws), ws.numel(), _stream()))
+        del x, w, y, dy, dw, dx
+        torch.cuda.empty_cache()
+    return {"config": "batch %d, fp16, 16-product, U[-1,1]; layout nchw = NCHW activations + OIHW filters, nhwc = channels-last activations "
+                      "+ OHWI filters; f_tensor against the sustained tensor peak, f_hbm = algorithmic bytes / time against the copy "
+                      "bandwidth; engine 2 = tcgen05, 1 = CUDA cores" % batch,
             "reps": reps, "rows": rows}
 
 
@@ -329,8 +339,24 @@ def run_ours(args):
     if world > 1:
         dist.init_process_group("nccl", device_id=device)
 
+    if args.sweep_only:            # profiling: one leg of the record on its own, e.g. one shape for an ncu capture
+        only = tuple(int(v) for v in args.sweep_shape.split(",")) if args.sweep_shape else None
+        out = sweep_leg(torch, pcb, _lib, read_peaks(), reps=args.sweep_reps, batch=args.sweep_batch, only=only,
+                        layouts=(args.sweep_layout,), extra_nhwc=(), dtype=args.sweep_dtype)
+        print(json.dumps(out), flush=True)
+        return
+    if args.dense_only:
+        print(json.dumps(dense_leg(torch, pcb, _lib, read_peaks())), flush=True)
+        return
+
     n, ci, co, h, w = (WORKLOAD[k] for k in ("n", "ci", "co", "h", "w"))
     ctx16 = Context({"UPSTRIDE_MEMORY_OPTIMIZED": "1", "UPSTRIDE_CONV_FP16_POLICY": "full16"})
+    main_engine = _lib.ENGINE_AUTO
+    if args.formulation == "8p":   # profiling: the factorised tensor-core kernels as the main step (the line is marked)
+        ctx16 = Context({"UPSTRIDE_MEMORY_OPTIMIZED": "0", "UPSTRIDE_CONV_FP16_POLICY": "full16"})
+        main_engine = _lib.ENGINE_TENSOR
+    if args.engine != "auto":
+        main_engine = _lib.ENGINE_SIMT if args.engine == "simt" else _lib.ENGINE_TENSOR
     args_d = ((4 * n, ci, h, w), (4, co, ci, 1, 1), (1, 1), (1, 1), pcb.Padding.VALID, (), 1, pcb.Algebra.QUATERNION,
               pcb.DataFormat.NCHW, pcb.FilterLayout.OIHW)
     fwd_desc = pcb.Conv2DFwdDescriptor(*args_d, False)
@@ -351,12 +377,12 @@ def run_ours(args):
             pending.append(dist.all_reduce(grad, async_op=True))
 
     def step():
-        pcb.conv2DFwd(x, wt, None, y, fwd_desc, ctx16)
+        pcb.conv2DFwd(x, wt, None, y, fwd_desc, ctx16, main_engine)
         if world > 1:
-            pcb.conv2DBwd(x, wt, dy, dw, dx, bwd_desc, ctx16, on_filter_grad=start_allreduce)
+            pcb.conv2DBwd(x, wt, dy, dw, dx, bwd_desc, ctx16, main_engine, on_filter_grad=start_allreduce)
             pending.pop().wait()                      # the current stream waits for the sum; the host does not block
         else:
-            pcb.conv2DBwd(x, wt, dy, dw, dx, bwd_desc, ctx16)
+            pcb.conv2DBwd(x, wt, dy, dw, dx, bwd_desc, ctx16, main_engine)
 
     def sync_all():
         if world > 1:
@@ -397,10 +423,10 @@ def run_ours(args):
     # per-kernel device times (same inputs, same stream): a short window (burst clocks) and >= kernel_seconds of
     # back-to-back launches (sustained clocks), the SM clock sampled during each
     L = _lib.lib()
-    d = _conv_desc(bwd_desc, torch.float16, ctx16, _lib.ENGINE_AUTO, require_input_grad=True)
+    d = _conv_desc(bwd_desc, torch.float16, ctx16, main_engine, require_input_grad=True)
     ws = Device.get(device).requestWorkspace(L.pcb_qconv2d_bwd_workspace_size(ctypes.byref(d)))
     kernel_fns = {
-        "forward": lambda: pcb.conv2DFwd(x, wt, None, y, fwd_desc, ctx16),
+        "forward": lambda: pcb.conv2DFwd(x, wt, None, y, fwd_desc, ctx16, main_engine),
         "backward_filter": lambda: _lib.check(L.pcb_qconv2d_bwd_filter(ctypes.byref(d), _ptr(x), _ptr(dy), _ptr(dw), _ptr(ws), ws.numel(), _stream())),
         "backward_data": lambda: _lib.check(L.pcb_qconv2d_bwd_data(ctypes.byref(d), _ptr(wt), _ptr(dy), _ptr(dx), _ptr(ws), ws.numel(), _stream())),
     }
@@ -555,6 +581,8 @@ def run_ours(args):
         torch.cuda.empty_cache()
         from phoenix_core_b200 import qresnet
         qres = qresnet.run(batch=128, steps=max(3, min(args.steps, 10)), warmup=3, quiet=True)
+        if rank == 0 and world == 1 and qres is not None:     # every distinct convolution layer of the network on its own
+            qres["layers"] = qresnet.layer_table(128, 10, peaks["tflops_sustained"])
 
     if rank == 0:
         fl = flops_per_pass(n, ci, co, h, w)
@@ -613,6 +641,8 @@ def run_ours(args):
             line["sweep"] = sweep
         if args.batch is not None:
             line["reduced_batch"] = "profiling run, not a benchmark value"
+        if args.formulation != "16p" or args.engine != "auto":
+            line["formulation"] = "profiling run (formulation %s, engine %s), not a benchmark value" % (args.formulation, args.engine)
         if cpu is not None:
             line["cpu_baseline"] = {"value": cpu[0], "unit": "TFLOP/s", "cores": cpu[1], "kind": "port", "sample": cpu[2],
                                     "sixteen_product": {"value": cpu16[0], "unit": "TFLOP/s", "sample": cpu16[2]}}
@@ -634,6 +664,17 @@ def main():
     ap.add_argument("--no-qresnet", action="store_true", help="skip the QResNet-18 training leg")
     ap.add_argument("--batch", type=int, default=None,
                     help="profiling only: per-GPU batch instead of 64 (the line is then marked 'reduced_batch' and is not a benchmark value)")
+    ap.add_argument("--formulation", default="16p", choices=["16p", "8p"],
+                    help="profiling only: 8p times the factorised tensor-core kernels as the main step (use with --kernels-only)")
+    ap.add_argument("--sweep-only", action="store_true", help="profiling only: run the shape sweep (or one shape of it) and print its record")
+    ap.add_argument("--sweep-shape", default=None, help="channels,size,kernel,stride of the single sweep shape to run")
+    ap.add_argument("--sweep-batch", type=int, default=128)
+    ap.add_argument("--sweep-reps", type=int, default=5)
+    ap.add_argument("--sweep-layout", default="nchw", choices=["nchw", "nhwc"])
+    ap.add_argument("--sweep-dtype", default="f16", choices=["f16", "f32"])
+    ap.add_argument("--engine", default="auto", choices=["auto", "simt", "tensor"],
+                    help="profiling only: kernel family of the main step (with --formulation 8p: simt = the factorised CUDA-core kernels)")
+    ap.add_argument("--dense-only", action="store_true", help="profiling only: run the dense leg and print its record")
     ap.add_argument("--kernels-only", action="store_true",
                     help="profiling only: skip the end-to-end, per-kernel and CPU-baseline legs")
     args = ap.parse_args()

@@ -130,9 +130,14 @@ __device__ __forceinline__ void lane_chunk(uint32_t raw, uint32_t comp_stride, u
 }
 
 // Byte offset, inside one component of a K-major tile with 64-byte rows and 64-byte swizzle, of chunk slot `t` of the K
-// half `h` (16 K elements = two 16-byte chunks per row): row = t / 2, logical chunk 2h + (t & 1).
+// half `h` (16 K elements = two 16-byte chunks per row; chunk c of row r sits at position c ^ ((r / 2) % 4)).
+// Slots are handed out so that eight consecutive threads touch eight different 16-byte bank groups: the two chunks of
+// rows {0, 1, 4, 5} of an 8-row group (rows 0 and 2 would share their bank groups, rows 0 and 4 do not), the next
+// eight threads rows {2, 3, 6, 7}.
 __device__ __forceinline__ uint32_t kmajor_half_offset(int t, int h) {
-    const int row = t >> 1, c = 2 * h + (t & 1);
+    const int v = t & 7, sub = (t >> 3) & 1, grp = t >> 4;
+    const int sel = v >> 1;
+    const int row = grp * 8 + 2 * sub + (sel & 1) + 4 * (sel >> 1), c = 2 * h + (v & 1);
     return (uint32_t)row * 64u + (uint32_t)((c ^ ((row >> 1) & 3)) << 4);
 }
 
