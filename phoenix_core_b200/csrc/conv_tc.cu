@@ -55,6 +55,9 @@ struct GParams {
     int o_generic;               // the output is addressed through the element strides below (channels-last tensors, channel
     int o_p, o_c, o_h, o_w;      // slices of grouped layers, boxes narrower than 8 pixels): one 16-bit store per element
     int bias_ld;                 // bias is [components][bias_ld]
+    int exact;                   // plane mode with a tile box of exactly PN whole planes (WO x HO x PN pixels, any plane size up to
+                                 // 256 pixels): the MMAs are n_cols = PN * WO * HO rounded up to 16 columns wide
+    uint32_t b_tx;               // bytes one activation box brings (plain form)
 };
 constexpr uint32_t G_PLANE_BYTES = GM * GN * 2;      // staging buffer of the plane-mode epilogue
 
@@ -101,6 +104,23 @@ __device__ __forceinline__ void plane_pack(const uint32_t (&v)[32], int col0, co
                 if (wl + 1 < p.WO) dst[wl + 1] = (uint16_t)(both >> 16);
             }
         }
+    }
+}
+
+// The same for a box of exactly PN whole planes: column j is pixel j % (HO * WO) of image j / (HO * WO) of the tile, in the
+// order the plane is stored, so a thread's columns are runs of consecutive elements of its channel plane.
+__device__ __forceinline__ void plane_pack_exact(const uint32_t (&v)[32], int col0, const GParams& p, uint16_t* mine, int HWo, float badd) {
+    int nl = col0 / HWo, pix = col0 - nl * HWo;
+    const int valid = p.PN * HWo;
+#pragma unroll
+    for (int e = 0; e < 32; ++e) {
+        if (col0 + e < valid) {
+            const float f = __uint_as_float(v[e]) + badd;
+            uint16_t bits;
+            if (p.fmt == 0) bits = __half_as_ushort(__float2half_rn(f)); else bits = __bfloat16_as_ushort(__float2bfloat16_rn(f));
+            mine[(size_t)nl * GM * HWo + pix] = bits;
+        }
+        if (++pix == HWo) { pix = 0; ++nl; }
     }
 }
 
@@ -179,7 +199,7 @@ qconv_general_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_
                             ok = mbar_wait_bounded(empty_bar + 8 * s, phase, status, ST_G_PRODUCER);
                             if (!ok) break;
                             const uint32_t a_dst = tiles_addr + s * STAGE, bar = full_bar + 8 * s;
-                            mbar_arrive_expect_tx(bar, STAGE);
+                            mbar_arrive_expect_tx(bar, A_BYTES + p.b_tx);
                             tma_load_3d(a_dst, &map_w, l * p.Cp + cs * KS, m0, tap, bar);
                             tma_load_5d(a_dst + A_BYTES, &map_x, cs * KS, wp0, hp0, n0, l, bar);
                             if (++s == STAGES) { s = 0; phase ^= 1; }
@@ -195,7 +215,7 @@ qconv_general_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_
         // time the tensor pipe idles, so there is no warp synchronisation inside and a stage's two descriptors are built once
         // and stepped by adding to the address field of their low words (16-byte units, never carrying out of the field).
         if (lane == 0) {
-            const uint32_t idesc = make_idesc_f16(p.fmt, GM, HALO ? p.n_cols : GN, false, false);
+            const uint32_t idesc = make_idesc_f16(p.fmt, GM, (HALO || p.exact) ? p.n_cols : GN, false, false);
             int s = 0, phase = 0, local_tile = 0;
             bool ok = true;
             for (int tile = blockIdx.x; tile < n_tiles && ok; tile += gridDim.x, ++local_tile) {
@@ -293,7 +313,8 @@ qconv_general_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_
                     const int col0 = chalf * 128 + cb * 32;
                     tmem_ld_32x32b_x32(tmem_base + ((uint32_t)(q * 32) << 16) + buf * GN + col0, v);
                     tmem_ld_wait();
-                    if (p.lw == 3) plane_pack<3>(v, col0, p, mine, HWo, badd);
+                    if (p.exact) { if (col0 < p.n_cols) plane_pack_exact(v, col0, p, mine, HWo, badd); }
+                    else if (p.lw == 3) plane_pack<3>(v, col0, p, mine, HWo, badd);
                     else plane_pack<4>(v, col0, p, mine, HWo, badd);
                 }
                 tc_fence_before_sync();
@@ -522,6 +543,8 @@ struct FGParams {
     int TPG;                      // x-major variant: taps stacked along M per work item
     int nc, ga;                   // algebra: components, GA(3,0,0) component order
     unsigned long long neg;       // negative entries of the block, bit (8*l + d)
+    int off_w, off_h;             // added to the pixel coordinates of every x box: 0 for the staged (padded) copy, minus the padding
+                                  // when the caller's channels-last x is read in place
 };
 
 __device__ __forceinline__ uint64_t make_desc_mn_blocks(uint32_t smem_addr, int cb, uint32_t block_bytes) {
@@ -589,7 +612,7 @@ qconv_filter_general_tc_kernel(const __grid_constant__ CUtensorMap map_dy, const
                 if (++s == F_STAGES) { s = 0; phase ^= 1; }
                 mbar_arrive_expect_tx(bar, a_bytes + b_bytes);
                 tma_load_5d(a_dst, &map_dy, 0, ow0, oh0, n0, blockA0, bar);
-                tma_load_5d(b_dst, &map_x, 0, ow0 * p.SW + kw * p.DW, oh0 * p.SH + kh * p.DH, n0, blockB0, bar);
+                tma_load_5d(b_dst, &map_x, 0, ow0 * p.SW + kw * p.DW + p.off_w, oh0 * p.SH + kh * p.DH + p.off_h, n0, blockB0, bar);
             }
         }
         __syncwarp();
@@ -727,7 +750,7 @@ qconv_filter_xmajor_tc_kernel(const __grid_constant__ CUtensorMap map_x, const _
                 if (++s == F_STAGES) { s = 0; phase ^= 1; }
                 mbar_arrive_expect_tx(bar, a_bytes + b_bytes);
                 for (int tl = 0; tl < p.TPG; ++tl)
-                    tma_load_5d(a_dst + tl * tap_bytes, &map_x, 0, ow0 * p.SW + w_ofs[tl], oh0 * p.SH + h_ofs[tl], n0, comp[tl], bar);
+                    tma_load_5d(a_dst + tl * tap_bytes, &map_x, 0, ow0 * p.SW + w_ofs[tl] + p.off_w, oh0 * p.SH + h_ofs[tl] + p.off_h, n0, comp[tl], bar);
                 tma_load_5d(b_dst, &map_dy, 0, ow0, oh0, n0, 0, bar);
             }
         }
@@ -965,6 +988,26 @@ int conv_tc_launch(Pass pass, int dtype, const Geom& g, const void* w, const voi
     p.off_w = direct ? -pl.pad_left : 0; p.off_h = direct ? -pl.pad_top : 0;
     p.plane_mode = (!p.o_generic && !halo && p.PW >= pl.Wout && p.PH >= pl.Hout && pl.Cout % GM == 0 && p.lh >= 0 && (p.lw == 3 || p.lw == 4) &&
                     (reinterpret_cast<uintptr_t>(out) & 15u) == 0) ? 1 : 0;
+    // Planes of at most 256 pixels: the box is exactly PN whole planes (7 x 7 x 5 = 245 of 256 columns instead of 8 x 8 x 4 with
+    // 49 of every 64 in use; 14 x 14 x 1 = 196 columns in MMAs 208 wide instead of 256), and the tile still leaves as one bulk
+    // copy per image.
+    p.exact = 0;
+    if (!p.o_generic && !halo && pl.Cout % GM == 0 && pl.Hout * pl.Wout <= 256 && pl.Wout <= 256 && pl.Hout <= 256 &&
+        (pl.Wout - 1) * pl.SW + 1 <= 256 && (pl.Hout - 1) * pl.SH + 1 <= 256 && (reinterpret_cast<uintptr_t>(out) & 15u) == 0) {
+        const int HWo = pl.Hout * pl.Wout;
+        int pn = 256 / HWo;
+        if (pn > g.Nb) pn = g.Nb;
+        // only where it puts more pixels into a tile than the power-of-two box does (measured: a 14 x 14 plane gains nothing
+        // from MMAs 208 instead of 256 columns wide)
+        const int pow2_valid = p.plane_mode ? HWo * p.PN : 0;
+        if (pn * HWo > pow2_valid) {
+            p.exact = 1; p.plane_mode = 1;
+            p.PW = pl.Wout; p.PH = pl.Hout; p.PN = pn;
+            p.n_cols = round_up(p.PW * p.PH * p.PN, 16);
+            p.lw = p.lh = 0;
+        }
+    }
+    p.b_tx = (uint32_t)(p.exact ? p.PW * p.PH * p.PN : GN) * (uint32_t)pl.KS * 2u;
     if (!halo) {
         const int max_stages = pl.KS == 64 ? 4 : (pl.KS == 32 ? 8 : 12);
         const int fit = (int)((227 * 1024 - 1024 - 512 - (p.plane_mode ? G_PLANE_BYTES : 0)) / ((GM + GN) * pl.KS * 2));
@@ -1087,6 +1130,12 @@ int conv_filter_tc_launch(int dtype, const Geom& g, const void* dy, const void* 
     uint8_t* dyp = xp + f.xp_bytes;
     float* acc = reinterpret_cast<float*>(dyp + f.dyp_bytes);
 
+    // A channels-last tensor with one channel block per component (16, 32 or 64 channels) already is the staged layout
+    // [component][image][h][w][channels]: it is read in place, x with its padding supplied by out-of-range TMA coordinates.
+    const bool direct_x = !g.plain && g.xc == 1 && g.xw == g.Ci && g.xh == g.W * g.Ci && (long long)g.xp == (long long)g.H * g.W * g.Ci &&
+                          channel_block(f.Cip) == g.Ci && (reinterpret_cast<uintptr_t>(x) & 15u) == 0;
+    const bool direct_dy = !g.plain && g.yc == 1 && g.yw == g.Co && g.yh == g.WO * g.Co && (long long)g.yp == (long long)g.HO * g.WO * g.Co &&
+                           channel_block(f.Cop) == g.Co && (reinterpret_cast<uintptr_t>(dy) & 15u) == 0;
     {   // stage both activations channels-last
         const int lk = g.real_in ? 1 : g.nc;
         const size_t tx = (size_t)lk * g.Nb * f.Hp * f.Wp * (f.Cip / 8), ty = (size_t)g.nc * g.Nb * g.HO * g.WO * (f.Cop / 8);
@@ -1094,8 +1143,10 @@ int conv_filter_tc_launch(int dtype, const Geom& g, const void* dy, const void* 
         const int bx = (int)((tx + 255) / 256 < cap ? (tx + 255) / 256 : cap), by = (int)((ty + 255) / 256 < cap ? (ty + 255) / 256 : cap);
         (void)bx; (void)by;
         const SrcStrides sx = {g.xp, g.xc, g.xh, g.xw}, sy = {g.yp, g.yc, g.yh, g.yw};
-        stage_activations(fmt, x, xp, lk * g.Nb, g.Ci, g.H, g.W, f.Hp, f.Wp, f.Cip, g.PT, g.PL, 1, 1, stream, channel_block(f.Cip), g.Nb, g.plain ? nullptr : &sx);
-        stage_activations(fmt, dy, dyp, g.nc * g.Nb, g.Co, g.HO, g.WO, g.HO, g.WO, f.Cop, 0, 0, 1, 1, stream, channel_block(f.Cop), g.Nb, g.plain ? nullptr : &sy);
+        if (!direct_x)
+            stage_activations(fmt, x, xp, lk * g.Nb, g.Ci, g.H, g.W, f.Hp, f.Wp, f.Cip, g.PT, g.PL, 1, 1, stream, channel_block(f.Cip), g.Nb, g.plain ? nullptr : &sx);
+        if (!direct_dy)
+            stage_activations(fmt, dy, dyp, g.nc * g.Nb, g.Co, g.HO, g.WO, g.HO, g.WO, f.Cop, 0, 0, 1, 1, stream, channel_block(f.Cop), g.Nb, g.plain ? nullptr : &sy);
         PCB_CUDA_TRY(cudaGetLastError());
         PCB_CUDA_TRY(cudaMemsetAsync(acc, 0, (size_t)g.nc * g.Co * g.Ci * taps * sizeof(float), stream));
     }
@@ -1120,6 +1171,7 @@ int conv_filter_tc_launch(int dtype, const Geom& g, const void* dy, const void* 
     p.n_tiles = (n_cols + GN - 1) / GN;
     p.n_tile_cols = n_cols < GN ? n_cols : GN;           // 4*Cip is a multiple of 64; tiles of a multi-tile problem are full or padded by zero blocks
     p.LK = g.real_in ? 1 : g.nc;
+    p.off_w = direct_x ? -g.PL : 0; p.off_h = direct_x ? -g.PT : 0;
     const bool xmajor = filter_xmajor(g, f);
     p.TPG = xmajor ? GM / (p.LK * p.cbB) : 1;
     const int steps_total = p.tiles_w * p.tiles_h * p.tiles_n;
@@ -1141,18 +1193,19 @@ int conv_filter_tc_launch(int dtype, const Geom& g, const void* dy, const void* 
                                        (cuuint64_t)g.Nb * g.HO * g.WO * p.cbA * 2};
         const cuuint32_t box[5] = {(cuuint32_t)p.cbA, (cuuint32_t)p.PW, (cuuint32_t)p.PH, (cuuint32_t)p.PN, (cuuint32_t)(xmajor ? g.nc : GM / p.cbA)};
         const cuuint32_t es[5] = {1, 1, 1, 1, 1};
-        const CUresult r = encode(&map_dy, dt, 5, dyp, dims, strides, box, es, CU_TENSOR_MAP_INTERLEAVE_NONE, swz(p.cbA),
+        const CUresult r = encode(&map_dy, dt, 5, direct_dy ? const_cast<void*>(dy) : static_cast<void*>(dyp), dims, strides, box, es, CU_TENSOR_MAP_INTERLEAVE_NONE, swz(p.cbA),
                                   CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
         if (r != CUDA_SUCCESS) { set_error("cuTensorMapEncodeTiled (dy) failed with code %d", (int)r); return PCB_ERR_CUDA; }
     }
     {
-        const cuuint64_t dims[5] = {(cuuint64_t)p.cbB, (cuuint64_t)f.Wp, (cuuint64_t)f.Hp, (cuuint64_t)g.Nb, (cuuint64_t)(p.LK * (f.Cip / p.cbB))};
-        const cuuint64_t strides[4] = {(cuuint64_t)p.cbB * 2, (cuuint64_t)f.Wp * p.cbB * 2, (cuuint64_t)f.Hp * f.Wp * p.cbB * 2,
-                                       (cuuint64_t)g.Nb * f.Hp * f.Wp * p.cbB * 2};
+        const int Wd = direct_x ? g.W : f.Wp, Hd = direct_x ? g.H : f.Hp;
+        const cuuint64_t dims[5] = {(cuuint64_t)p.cbB, (cuuint64_t)Wd, (cuuint64_t)Hd, (cuuint64_t)g.Nb, (cuuint64_t)(p.LK * (f.Cip / p.cbB))};
+        const cuuint64_t strides[4] = {(cuuint64_t)p.cbB * 2, (cuuint64_t)Wd * p.cbB * 2, (cuuint64_t)Hd * Wd * p.cbB * 2,
+                                       (cuuint64_t)g.Nb * Hd * Wd * p.cbB * 2};
         const cuuint32_t box[5] = {(cuuint32_t)p.cbB, (cuuint32_t)((p.PW - 1) * g.SW + 1), (cuuint32_t)((p.PH - 1) * g.SH + 1), (cuuint32_t)p.PN,
                                    (cuuint32_t)(xmajor ? p.LK : p.n_tile_cols / p.cbB)};
         const cuuint32_t es[5] = {1, (cuuint32_t)g.SW, (cuuint32_t)g.SH, 1, 1};
-        const CUresult r = encode(&map_x, dt, 5, xp, dims, strides, box, es, CU_TENSOR_MAP_INTERLEAVE_NONE, swz(p.cbB),
+        const CUresult r = encode(&map_x, dt, 5, direct_x ? const_cast<void*>(x) : static_cast<void*>(xp), dims, strides, box, es, CU_TENSOR_MAP_INTERLEAVE_NONE, swz(p.cbB),
                                   CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
         if (r != CUDA_SUCCESS) { set_error("cuTensorMapEncodeTiled (x) failed with code %d", (int)r); return PCB_ERR_CUDA; }
     }

@@ -53,8 +53,7 @@ __device__ __forceinline__ void red_add_f32x4(float* addr, float a, float b, flo
 }
 
 // Staging copy of NCHW activations for the TMA-fed kernels, fast form (no zero insertion, W a multiple of PX = 4 or 2,
-// rows aligned to PX elements): one thread moves 8 channels x PX pixels -- eight loads of 2 PX bytes (a warp reads 64 PX
-// contiguous bytes per channel) and PX 16-byte stores. Destination: channels-last xp[plane][hp][wp][Cp] (planar == 0),
+// rows aligned to PX elements): one thread moves 8 channels x PX pixels -- eight loads of 2 PX bytes and PX 16-byte stores. Destination: channels-last xp[plane][hp][wp][Cp] (planar == 0),
 // planar xp[plane][c / 8][hp][wp][8] (planar == 1), or -- cb > 0 -- blocks of cb channels with the block index outermost,
 // xp[comp * (Cp / cb) + c / cb][img][hp][wp][cb] where plane = comp * Nb + img (one TMA box can then span the channel
 // blocks of several components). Zero outside the image and for c >= C. The threads at the ends of a row also write
@@ -66,11 +65,15 @@ __global__ void pack_rows_kernel(const T* __restrict__ x, T* __restrict__ xp, in
     const unsigned total = (unsigned)planes * groups * Hp * Wq;         // 32-bit indices: staged copies stay below 2^32 / 8 threads
     const int Cp = groups * 8;
     for (unsigned idx = blockIdx.x * blockDim.x + threadIdx.x; idx < total; idx += gridDim.x * blockDim.x) {
-        const int q = (int)(idx % Wq);
-        unsigned rest = idx / Wq;
-        const int hp = (int)(rest % Hp); rest /= Hp;
-        const int grp = (int)(rest % groups);
-        const int plane = (int)(rest / groups);
+        // The channel group runs fastest across threads: the lanes of a warp that share a pixel group then write the channel
+        // groups of a pixel side by side (whole 32- to 128-byte runs per pixel instead of one 16-byte piece per lane and
+        // 32 half-filled sectors per store), while every load instruction still fetches full 32-byte sectors (PX * 2 bytes
+        // from each of the neighbouring pixel groups of one channel row).
+        const int grp = (int)(idx % groups);
+        unsigned rest = idx / groups;
+        const int q = (int)(rest % Wq); rest /= Wq;
+        const int hp = (int)(rest % Hp);
+        const int plane = (int)(rest / Hp);
         const int ih = hp - pad_top;
         const bool row_in = ih >= 0 && ih < H;
         alignas(8) T v[8][PX];
