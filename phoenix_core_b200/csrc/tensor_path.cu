@@ -461,9 +461,11 @@ struct StrideClass {
 // Taken from 512 gradient rows (128 quaternion channels) up: each class pays its own staging pass and launch, and below that
 // width those cost more than the zero-insertion route's extra MMAs (measured at batch 128: 0.47 -> 0.38 ms at 128
 // channels and 28 x 28, 0.51 -> 0.34 ms at 256 and 14 x 14, but 0.12 -> 0.27 ms at 64 -> 128 channels and 14 x 14).
+// From 256 rows (64 quaternion channels) the classes also win when the gradient is large (at least ~200k pixels per component).
 bool strided_taps(const Geom& g) {
+    const bool wide = g.nc * g.Ci >= 512 || (g.nc * g.Ci >= 256 && (long long)g.Nb * g.H * g.W >= 200000);
     return (g.KH > 1 || g.KW > 1) && (g.SH > 1 || g.SW > 1) && g.SH <= 2 && g.SW <= 2 && g.DH == 1 && g.DW == 1 && g.plain && !g.w_io &&
-           !g.dw_io && !g.real_in && g.nc * g.Ci >= 512;
+           !g.dw_io && !g.real_in && wide;
 }
 
 // Fills the classes; returns their number. `bytes` receives the scratch the classes' tensors take.
