@@ -753,6 +753,7 @@ int tensor_launch(Pass pass, int dtype, int variant, const Geom& g, const void* 
     else                            { p.M = 4 * g.Co; p.N = g.Ci;      p.K = 4 * g.Nb * HW; }
     p.k_per_split = (p.K + TBK - 1) / TBK * TBK;
     p.atomic_out = 0;
+    if (pointwise_pair_tc_supported(pass, dtype, PCB_VARIANT_16_PRODUCT, g)) return pointwise_pair_tc_launch(dtype, g, a, b, bias, out, status, stream);
     if (pointwise_tc_supported(pass, dtype, PCB_VARIANT_16_PRODUCT, g)) return pointwise_tc_launch(pass, dtype, g, a, b, bias, out, status, stream);
     if (pass != PASS_BWD_FILTER && narrow_tc_supported(pass, dtype, PCB_VARIANT_16_PRODUCT, g))
         return narrow_tc_launch(pass, dtype, g, a, b, bias, out, scratch, status, stream);

@@ -148,6 +148,31 @@ def test_pointwise_8_product_on_tensor_cores_vs_oracle(gpu, oracle, shape, dtype
     _check(dw, rdw, dtype, gpu, "dw")
 
 
+# wide pointwise layers with a multiple of 256 output channels and >= 96 input channels: forward on pairs of SMs
+# (cta_group::2 MMAs, 256 x 128 tiles): n, ci, co, h, w
+PAIR_SHAPES = [
+    (8, 128, 256, 56, 56),      # the benchmark layer at batch 8: several tiles per pair, image boundaries inside tiles
+    (10, 104, 512, 28, 36),     # two channel pairs, ragged last K slice (104 = 3 x 32 + 8), 1008-pixel images (partial last block)
+    (3, 96, 256, 56, 57),       # odd number of 64-pixel blocks in total: the last tile's second half is out of range
+]
+
+
+@pytest.mark.parametrize("shape", PAIR_SHAPES)
+@pytest.mark.parametrize("dtype", ["f16", "bf16"])
+def test_pointwise_forward_on_sm_pairs_vs_oracle(gpu, oracle, shape, dtype):
+    import ctypes
+    from phoenix_core_b200 import _lib
+    n, ci, co, h, w_ = shape
+    x = gpu.rounded(normal(21, (4 * n, ci, h, w_)), dtype)
+    w = gpu.rounded(normal(22, (4, co, ci, 1, 1), std=(2.0 / (4 * ci)) ** 0.5), dtype)
+    b = gpu.rounded(uniform(23, (4, co)), dtype)
+    ref = oracle.conv2d_fwd(x, w, b)
+    got = gpu.run_conv_fwd(x, w, b, (1, 1), (0, 0, 0, 0), dtype, "16p", "tensor")
+    _check(got, ref, dtype, gpu, "y")
+    nob = gpu.run_conv_fwd(x, w, None, (1, 1), (0, 0, 0, 0), dtype, "16p", "tensor")
+    _check(nob, oracle.conv2d_fwd(x, w, None), dtype, gpu, "y (no bias)")
+
+
 # shapes for the general implicit-GEMM tensor-core kernel (staged channels-last activations, expanded filters):
 # n, ci, co, h, w, kh, kw, stride, pad(t,l,b,r)
 GENERAL_TENSOR_SHAPES = [
