@@ -297,6 +297,25 @@ def test_tensor_engine_refuses_unsupported_shapes(gpu):
     assert e.value.status == _lib.PCB_ERR_UNSUPPORTED
 
 
+def test_fp16_policies_give_one_result(gpu, oracle):
+    """UPSTRIDE_CONV_FP16_POLICY is carried for API parity and not consulted: under each of the three policies the same
+    kernels run (products exact, fp32 accumulation), so the outputs are bit-identical and within tolerance of the oracle."""
+    import phoenix_core_b200 as pcb
+    from phoenix_core_b200.context import Context
+    x = gpu.rounded(uniform(81, (4 * 2, 32, 10, 12)), "f16")
+    w = gpu.rounded(uniform(82, (4, 32, 32, 3, 3)) * 0.1, "f16")
+    ref = oracle.conv2d_fwd(x, w, None, (1, 1), (1, 1), (1, 1, 1, 1))
+    fwd, _ = gpu.conv_descriptors(x.shape, w.shape, (1, 1), (1, 1, 1, 1), False, False)
+    outs = []
+    for policy in ("full16", "backward32", "fp32"):
+        ctx = Context({"UPSTRIDE_MEMORY_OPTIMIZED": "1", "UPSTRIDE_CONV_FP16_POLICY": policy})
+        y = torch.full(fwd.getOutputShape(), float("nan"), dtype=torch.float16, device="cuda")
+        pcb.conv2DFwd(gpu.dev(x, "f16"), gpu.dev(w, "f16"), None, y, fwd, ctx)
+        outs.append(gpu.host(y))
+        _check(outs[-1], ref, "f16", gpu, "y under " + policy)
+    assert np.array_equal(outs[0], outs[1]) and np.array_equal(outs[0], outs[2])
+
+
 def test_real_valued_input(gpu, oracle):
     x = uniform(21, (3, 4, 9, 7))
     w = uniform(22, (4, 6, 4, 3, 3))
