@@ -26,10 +26,12 @@
  * double-precision accumulation and one rounding to float per output element. Between scalar
  * operations every intermediate is a float tensor, as in the reference.
  *
- * Parity pinning: forward results are pinned by the reference's known-answer tests
- * (tests/tests.cpp:224-369, :562-603). The reference has no backward, bias, quaternion-dense or fp16
- * test, so for those the oracle is pinned only indirectly (16-product == 8-product == an independent
- * float64 block-matrix formulation, and finite differences); parity for them is "unpinned".
+ * Parity pinning: (1) forward results are pinned by the reference's known-answer tests
+ * (tests/tests.cpp:224-369, :562-603); (2) forward AND backward results, bias, dense, the other algebras,
+ * layouts, groups and real-valued input, in both formulations, are pinned by vectors that the reference's
+ * own composition code produced (tests/golden/reference_composition.npz; the reference's sources compiled
+ * over a stand-in for oneDNN, see ref_driver.cc and dnnl_stub/dnnl.hpp): this file reproduces every one of
+ * them bit for bit. fp16 / bf16 have no reference-held vector (the reference's CPU backend is fp32 only).
  */
 #include <math.h>
 #include <stdint.h>
