@@ -515,6 +515,86 @@ __global__ void pack_filters_kernel(const T* __restrict__ w, T* __restrict__ wex
     }
 }
 
+// The same matrix for filters whose (input channel, tap) run is contiguous (OIHW), tile by tile through shared memory: a block
+// takes one filter component r and a 32 x 64 block of (M-side, K-side) channels with all its taps, reads it as whole runs
+// (coalesced, where the row-per-thread kernel above strides by a whole output channel in the transposed case), and writes, for
+// every (l, d) pair whose product component is r, 64 consecutive K columns per row. Requires taps <= PACK_TILE_MAX_TAPS and no
+// padded rows beyond the last component (Mp == nc * Cm).
+constexpr int PACK_TM = 32, PACK_TK = 64;   // rows (M-side channels) and K columns of a tile
+constexpr int PACK_TILE_MAX_TAPS = 9;     // 37 KB of shared memory at 9 taps
+// (16-bit elements are moved as raw bits; a negative coefficient flips the sign bit; every thread writes 8 consecutive K columns
+// with one 16-byte store)
+__global__ void __launch_bounds__(256)
+pack_filters_tiled_kernel(const uint16_t* __restrict__ w, uint16_t* __restrict__ wexp, int Co, int Ci, int taps, int Mp, int Kp, int Cp, int transposed,
+                          int nc, int ga, unsigned long long neg, FilterStrides fs) {
+    extern __shared__ uint8_t pack_smem[];
+    uint16_t* tile = reinterpret_cast<uint16_t*>(pack_smem);
+    const int Cm = transposed ? Ci : Co, Ck = transposed ? Co : Ci;
+    const int ck0 = blockIdx.x * PACK_TK, cm0 = blockIdx.y * PACK_TM, r = blockIdx.z;
+    const int co0 = transposed ? ck0 : cm0, ci0 = transposed ? cm0 : ck0;
+    const int n_co = transposed ? PACK_TK : PACK_TM, n_ci = transposed ? PACK_TM : PACK_TK;
+    const int run = n_ci * taps;               // elements of the tile's input channels x all taps of one output channel
+    const int pitch = run + 2;                 // an odd number of 32-bit words
+    {   // load: a warp takes whole runs (one output channel each); a run is a multiple of 32 elements, so the loop unrolls into
+        // independent loads
+        const int e_limit = min(run, max(0, (Ci - ci0) * taps));      // elements of a run that belong to existing input channels
+        const uint16_t* src = w + (long long)r * fs.r + (long long)co0 * fs.o + (long long)ci0 * fs.i;
+        const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+        for (int co = warp; co < n_co; co += 8) {
+            const uint16_t* row = src + (long long)co * fs.o;
+            const int limit = co0 + co < Co ? e_limit : 0;
+            uint16_t* trow = tile + co * pitch;
+#pragma unroll 9
+            for (int e = lane; e < run; e += 32) trow[e] = e < limit ? __ldg(row + e) : (uint16_t)0;
+        }
+    }
+    __syncthreads();
+    // write: a thread keeps its row cm and its 8 K columns for every tap and every (l, d) pair
+    const int j = threadIdx.x & (PACK_TK / 8 - 1), cm = threadIdx.x >> 3;
+    const int ck = ck0 + 8 * j;
+    if (cm0 + cm >= Cm || ck >= Cp) return;
+    const uint16_t* src0 = transposed ? tile + (8 * j) * pitch + cm * taps : tile + cm * pitch + (8 * j) * taps;
+    const int step = transposed ? pitch : taps;
+    uint32_t keep[4];                     // columns beyond the K-side channel count are zero
+#pragma unroll
+    for (int t = 0; t < 4; ++t) keep[t] = (ck + 2 * t < Ck ? 0xFFFFu : 0u) | (ck + 2 * t + 1 < Ck ? 0xFFFF0000u : 0u);
+    for (int l = 0; l < nc; ++l) {
+        int d = -1;
+        for (int dd = 0; dd < nc; ++dd)
+            if (alg_pair(ga, l, dd) == r) d = dd;
+        if (d < 0) continue;
+        const uint32_t flip = alg_negative(neg, l, d) ? 0x80008000u : 0u;
+        const int m_comp = transposed ? l : d, k_comp = transposed ? d : l;
+        uint16_t* dst = wexp + ((size_t)m_comp * Cm + cm0 + cm) * Kp + (size_t)k_comp * Cp + ck;
+        for (int tap = 0; tap < taps; ++tap) {
+            const uint16_t* src = src0 + (transposed ? taps - 1 - tap : tap);
+            uint32_t q[4];
+#pragma unroll
+            for (int t = 0; t < 4; ++t)
+                q[t] = (((uint32_t)src[(2 * t) * step] | ((uint32_t)src[(2 * t + 1) * step] << 16)) ^ flip) & keep[t];
+            *reinterpret_cast<uint4*>(dst + (size_t)tap * Mp * Kp) = make_uint4(q[0], q[1], q[2], q[3]);
+        }
+    }
+}
+
+template <typename T>
+void pack_filters(const T* w, T* wexp, int Co, int Ci, int taps, int Mp, int Kp, int Cp, int transposed, int nc, int ga, unsigned long long neg,
+                  const FilterStrides& fs, cudaStream_t stream) {
+    const int Cm = transposed ? Ci : Co;
+    const bool runs = fs.w == 1 && fs.h == fs.KW && fs.i == taps;
+    if (runs && taps <= PACK_TILE_MAX_TAPS && Mp == nc * Cm && Cm >= PACK_TM && (reinterpret_cast<uintptr_t>(wexp) & 15u) == 0) {
+        const dim3 grid((Cp + PACK_TK - 1) / PACK_TK, (Cm + PACK_TM - 1) / PACK_TM, nc);
+        static_assert(sizeof(T) == 2, "the tiled kernel moves 16-bit elements");
+        const size_t smem = (size_t)(transposed ? PACK_TK * (PACK_TM * taps + 2) : PACK_TM * (PACK_TK * taps + 2)) * 2;
+        pack_filters_tiled_kernel<<<grid, 256, smem, stream>>>(reinterpret_cast<const uint16_t*>(w), reinterpret_cast<uint16_t*>(wexp), Co, Ci, taps, Mp,
+                                                              Kp, Cp, transposed, nc, ga, neg, fs);
+    } else {
+        const dim3 wthreads(Cp >= 64 ? 64 : 32, Cp >= 64 ? 4 : 8);
+        const int wblocks = grid_cap((size_t)taps * Mp, (int)wthreads.y, 32);
+        pack_filters_kernel<T><<<wblocks, wthreads, 0, stream>>>(w, wexp, Co, Ci, taps, Mp, Kp, Cp, transposed, nc, ga, neg, fs);
+    }
+}
+
 // ===================================================================================================
 // General backward-filter. Both operands come from channels-last staged copies (dy unpadded, x padded as for
 // the forward pass) and are MN-major: K = output pixels, M = (d, co), N = (l, ci). One work item = one
@@ -920,19 +1000,17 @@ int conv_tc_launch(Pass pass, int dtype, const Geom& g, const void* w, const voi
     {
         const size_t total = (size_t)pl.LK * g.Nb * pl.Hp * pl.Wp * (pl.Cp / 8);
         const int blocks = (int)((total + 255) / 256 < (size_t)sm_count() * 16 ? (total + 255) / 256 : (size_t)sm_count() * 16);
-        const dim3 wthreads(pl.Cp >= 64 ? 64 : 32, pl.Cp >= 64 ? 4 : 8);
-        const int wblocks = grid_cap((size_t)taps * pl.Mp, (int)wthreads.y, 32);
         (void)blocks;
         if (!direct)
             stage_activations(fmt, act, xp, pl.LK * g.Nb, pl.Cin, pl.Hin, pl.Win, pl.Hp, pl.Wp, pl.Cp, pl.pad_top, pl.pad_left, pl.ins_h, pl.ins_w, stream,
                               0, 1, g.plain ? nullptr : &sa);
         const FilterStrides fs = {g.wr, g.wo, g.wi, g.wh, g.ww, g.KW};
         if (fmt == 0) {
-            pack_filters_kernel<__half><<<wblocks, wthreads, 0, stream>>>((const __half*)w, (__half*)wexp, g.Co, g.Ci, taps, pl.Mp, pl.Kp, pl.Cp,
-                                                                    pass == PASS_BWD_DATA ? 1 : 0, g.nc, g.ga, g.neg, fs);
+            pack_filters<__half>((const __half*)w, (__half*)wexp, g.Co, g.Ci, taps, pl.Mp, pl.Kp, pl.Cp, pass == PASS_BWD_DATA ? 1 : 0, g.nc, g.ga, g.neg, fs,
+                                 stream);
         } else {
-            pack_filters_kernel<__nv_bfloat16><<<wblocks, wthreads, 0, stream>>>((const __nv_bfloat16*)w, (__nv_bfloat16*)wexp, g.Co, g.Ci, taps,
-                                                                           pl.Mp, pl.Kp, pl.Cp, pass == PASS_BWD_DATA ? 1 : 0, g.nc, g.ga, g.neg, fs);
+            pack_filters<__nv_bfloat16>((const __nv_bfloat16*)w, (__nv_bfloat16*)wexp, g.Co, g.Ci, taps, pl.Mp, pl.Kp, pl.Cp,
+                                        pass == PASS_BWD_DATA ? 1 : 0, g.nc, g.ga, g.neg, fs, stream);
         }
         PCB_CUDA_TRY(cudaGetLastError());
     }
