@@ -35,7 +35,9 @@ struct TParams {
     int PW, PH, PN;
     int tiles_w, tiles_h, tiles_n, tiles_m;
     int has_bias, LK, store_vec;
-    int n_chunks, chunk_len;          // the K loop runs in n_chunks pieces of at most chunk_len stages
+    int n_chunks, chunk_len;          // a work item's K range runs in n_chunks pieces of at most chunk_len stages
+    int splits, k_per_split;          // the K loop of a tile is cut into `splits` work items of k_per_split stages; with more than one
+                                      // the partial results meet in the (zeroed) output by fp32 reductions
 };
 
 // K-major tile with 64-byte rows (16 fp32), 64-byte swizzle.
@@ -63,7 +65,7 @@ qconv_general_tf32_kernel(const __grid_constant__ CUtensorMap map_w_hi, const __
     const uint32_t full_bar = smem_u32(bars), empty_bar = smem_u32(bars + T_STAGES);
     const uint32_t tmem_full = smem_u32(bars + 2 * T_STAGES), tmem_empty = smem_u32(bars + 2 * T_STAGES + 2);
 
-    const int n_tiles = p.tiles_w * p.tiles_h * p.tiles_n * p.tiles_m;
+    const int n_items = p.tiles_w * p.tiles_h * p.tiles_n * p.tiles_m * p.splits;
     const int c_steps = p.Cp / TKS;
     const int n_k = p.KH * p.KW * p.LK * c_steps;
 
@@ -82,29 +84,30 @@ qconv_general_tf32_kernel(const __grid_constant__ CUtensorMap map_w_hi, const __
         if (lane == 0) {
             int it = 0;
             bool ok = true;
-            for (int tile = blockIdx.x; tile < n_tiles && ok; tile += gridDim.x) {
+            for (int item = blockIdx.x; item < n_items && ok; item += gridDim.x) {
+                const int tile = item / p.splits, split = item - tile * p.splits;
                 const int tm = tile % p.tiles_m;
                 int rest = tile / p.tiles_m;
                 const int tw = rest % p.tiles_w; rest /= p.tiles_w;
                 const int th = rest % p.tiles_h;
                 const int tn = rest / p.tiles_h;
                 const int m0 = tm * TM, ow0 = tw * p.PW, oh0 = th * p.PH, n0 = tn * p.PN;
-                for (int tap = 0; tap < p.KH * p.KW && ok; ++tap) {
+                const int k0 = split * p.k_per_split, k1 = min(n_k, k0 + p.k_per_split);
+                // stage k = (tap * LK + l) * c_steps + cs
+                int cs = k0 % c_steps, l = (k0 / c_steps) % p.LK, tap = k0 / (c_steps * p.LK);
+                for (int k = k0; k < k1; ++k, ++it) {
                     const int kh = tap / p.KW, kw = tap - kh * p.KW;
                     const int wp0 = ow0 * p.SW + kw * p.DW, hp0 = oh0 * p.SH + kh * p.DH;
-                    for (int l = 0; l < p.LK && ok; ++l) {
-                        for (int cs = 0; cs < c_steps; ++cs, ++it) {
-                            const int s = it % T_STAGES;
-                            ok = mbar_wait_bounded(empty_bar + 8 * s, ((it / T_STAGES) & 1) ^ 1, status, ST_T_PRODUCER);
-                            if (!ok) break;
-                            const uint32_t dst = tiles_addr + s * T_STAGE, bar = full_bar + 8 * s;
-                            mbar_arrive_expect_tx(bar, T_STAGE);
-                            tma_load_3d(dst, &map_w_hi, l * p.Cp + cs * TKS, m0, tap, bar);
-                            tma_load_3d(dst + TA_BYTES, &map_w_lo, l * p.Cp + cs * TKS, m0, tap, bar);
-                            tma_load_5d(dst + 2 * TA_BYTES, &map_x_hi, cs * TKS, wp0, hp0, n0, l, bar);
-                            tma_load_5d(dst + 2 * TA_BYTES + TB_BYTES, &map_x_lo, cs * TKS, wp0, hp0, n0, l, bar);
-                        }
-                    }
+                    const int s = it % T_STAGES;
+                    ok = mbar_wait_bounded(empty_bar + 8 * s, ((it / T_STAGES) & 1) ^ 1, status, ST_T_PRODUCER);
+                    if (!ok) break;
+                    const uint32_t dst = tiles_addr + s * T_STAGE, bar = full_bar + 8 * s;
+                    mbar_arrive_expect_tx(bar, T_STAGE);
+                    tma_load_3d(dst, &map_w_hi, l * p.Cp + cs * TKS, m0, tap, bar);
+                    tma_load_3d(dst + TA_BYTES, &map_w_lo, l * p.Cp + cs * TKS, m0, tap, bar);
+                    tma_load_5d(dst + 2 * TA_BYTES, &map_x_hi, cs * TKS, wp0, hp0, n0, l, bar);
+                    tma_load_5d(dst + 2 * TA_BYTES + TB_BYTES, &map_x_lo, cs * TKS, wp0, hp0, n0, l, bar);
+                    if (++cs == c_steps) { cs = 0; if (++l == p.LK) { l = 0; ++tap; } }
                 }
             }
         }
@@ -113,7 +116,9 @@ qconv_general_tf32_kernel(const __grid_constant__ CUtensorMap map_w_hi, const __
         const uint32_t idesc = make_idesc_f16(2, TM, TN, false, false);
         int it = 0, unit = 0;                       // unit = one accumulator's worth of work: a chunk of a tile
         bool ok = true;
-        for (int tile = blockIdx.x; tile < n_tiles && ok; tile += gridDim.x) {
+        for (int item = blockIdx.x; item < n_items && ok; item += gridDim.x) {
+            const int split = item % p.splits;
+            const int k0 = split * p.k_per_split, k1 = min(n_k, k0 + p.k_per_split);
             for (int c = 0; c < p.n_chunks && ok; ++c, ++unit) {
                 const int buf = unit & 1, use = unit >> 1;
                 if (use > 0) {
@@ -121,7 +126,7 @@ qconv_general_tf32_kernel(const __grid_constant__ CUtensorMap map_w_hi, const __
                     if (!ok) break;
                     tc_fence_after_sync();
                 }
-                const int k_beg = c * p.chunk_len, k_end = min(n_k, k_beg + p.chunk_len);
+                const int k_beg = k0 + c * p.chunk_len, k_end = min(k1, k_beg + p.chunk_len);
                 for (int k = k_beg; k < k_end && ok; ++k, ++it) {
                     const int s = it % T_STAGES;
                     ok = mbar_wait_bounded(full_bar + 8 * s, (it / T_STAGES) & 1, status, ST_T_MMA);
@@ -148,7 +153,9 @@ qconv_general_tf32_kernel(const __grid_constant__ CUtensorMap map_w_hi, const __
         const int sv = p.store_vec;                  // pixels per store: 8, 4, 2 or 1
         int unit = 0;
         bool ok = true;
-        for (int tile = blockIdx.x; tile < n_tiles && ok; tile += gridDim.x) {
+        const bool reduce = p.splits > 1;            // partial sums of a tile meet in the zeroed output
+        for (int item = blockIdx.x; item < n_items && ok; item += gridDim.x) {
+            const int tile = item / p.splits, split = item - tile * p.splits;
             const int tm = tile % p.tiles_m;
             int rest = tile / p.tiles_m;
             const int tw = rest % p.tiles_w; rest /= p.tiles_w;
@@ -158,7 +165,7 @@ qconv_general_tf32_kernel(const __grid_constant__ CUtensorMap map_w_hi, const __
             const int m = tm * TM + q * 32 + lane;
             const bool row_ok = m < p.Mvalid;
             const int d = row_ok ? m / p.Cout : 0, co = m - d * p.Cout;
-            const float badd = (row_ok && p.has_bias) ? bias[d * p.Cout + co] : 0.f;
+            const float badd = (row_ok && p.has_bias && split == 0) ? bias[d * p.Cout + co] : 0.f;
             float part[CHUNKED ? 4 : 1][CHUNKED ? 32 : 1];          // this thread's 128 columns, summed over the chunks so far
             if (CHUNKED) {
 #pragma unroll
@@ -209,7 +216,19 @@ qconv_general_tf32_kernel(const __grid_constant__ CUtensorMap map_w_hi, const __
                     if (p.PW >= 8) {
                         if (ow >= p.WO || oh >= p.HO || img >= p.Nb) continue;
                         float* dst = out + (((size_t)(d * p.Nb + img) * p.Cout + co) * p.HO + oh) * p.WO + ow;
-                        if (sv >= 8) {
+                        if (reduce) {
+                            if (sv >= 4) {
+#pragma unroll
+                                for (int h = 0; h < 2; ++h)
+                                    if (ow + 4 * h < p.WO)
+                                        red_add_f32x4(dst + 4 * h, __uint_as_float(v[8 * g8 + 4 * h]), __uint_as_float(v[8 * g8 + 4 * h + 1]),
+                                                      __uint_as_float(v[8 * g8 + 4 * h + 2]), __uint_as_float(v[8 * g8 + 4 * h + 3]));
+                            } else {
+#pragma unroll
+                                for (int e = 0; e < 8; ++e)
+                                    if (ow + e < p.WO) atomicAdd(dst + e, __uint_as_float(v[8 * g8 + e]));
+                            }
+                        } else if (sv >= 8) {
                             st_global_v8(dst, &v[8 * g8]);
                         } else if (sv == 4) {
 #pragma unroll
@@ -230,8 +249,11 @@ qconv_general_tf32_kernel(const __grid_constant__ CUtensorMap map_w_hi, const __
                         for (int e = 0; e < 8; ++e) {
                             const int je = j + e;
                             const int w2 = je % p.PW, h2 = (je / p.PW) % p.PH, n2 = je / (p.PW * p.PH);
-                            if (ow0 + w2 < p.WO && oh0 + h2 < p.HO && n0 + n2 < p.Nb)
-                                out[(((size_t)(d * p.Nb + n0 + n2) * p.Cout + co) * p.HO + oh0 + h2) * p.WO + ow0 + w2] = __uint_as_float(v[8 * g8 + e]);
+                            if (ow0 + w2 < p.WO && oh0 + h2 < p.HO && n0 + n2 < p.Nb) {
+                                float* dst = out + (((size_t)(d * p.Nb + n0 + n2) * p.Cout + co) * p.HO + oh0 + h2) * p.WO + ow0 + w2;
+                                if (reduce) atomicAdd(dst, __uint_as_float(v[8 * g8 + e]));
+                                else *dst = __uint_as_float(v[8 * g8 + e]);
+                            }
                         }
                     }
                 }
@@ -743,10 +765,21 @@ int conv_tf32_launch(Pass pass, const Geom& g, const void* a, const void* b, con
         if (rc != PCB_OK) return rc;
     }
     const int n_tiles = p.tiles_w * p.tiles_h * p.tiles_n * p.tiles_m;
-    const int grid = n_tiles < sm_count() ? n_tiles : sm_count();
     const int n_k = taps * pl.LK * (pl.Cp / TKS);
-    p.n_chunks = (n_k + T_CHUNK - 1) / T_CHUNK;
-    p.chunk_len = (n_k + p.n_chunks - 1) / p.n_chunks;
+    // Too few tiles for the SMs (dense layers, small planes): cut the K loop of every tile into work items of at least one chunk
+    // each; their partial sums meet in the output, zeroed first, by fp32 reductions (the order of which is not fixed).
+    p.splits = 1;
+    if (2 * n_tiles <= sm_count() && n_k >= 2 * T_CHUNK) {
+        p.splits = sm_count() / n_tiles;
+        if (p.splits > n_k / T_CHUNK) p.splits = n_k / T_CHUNK;
+        while (n_k % p.splits != 0) --p.splits;                      // equal work items: every chunk of every item holds stages
+    }
+    p.k_per_split = n_k / p.splits;
+    if (p.splits > 1) PCB_CUDA_TRY(cudaMemsetAsync(out, 0, (size_t)g.nc * g.Nb * pl.Cout * pl.Hout * pl.Wout * sizeof(float), stream));
+    const int n_items = n_tiles * p.splits;
+    const int grid = n_items < sm_count() ? n_items : sm_count();
+    p.n_chunks = (p.k_per_split + T_CHUNK - 1) / T_CHUNK;
+    p.chunk_len = (p.k_per_split + p.n_chunks - 1) / p.n_chunks;
     if (p.n_chunks > 1) {
         PCB_CUDA_TRY(cudaFuncSetAttribute(qconv_general_tf32_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)T_SMEM));
         qconv_general_tf32_kernel<true><<<grid, T_THREADS, T_SMEM, stream>>>(m_w_hi, m_w_lo, m_x_hi, m_x_lo, p, (const float*)bias, (float*)out, status);
