@@ -316,28 +316,31 @@ __global__ void pack_activations_f32_kernel(const float* __restrict__ x, float* 
 // w_io: the filters are stored [r][ci][co] (dense input-major layout, one tap).
 __global__ void pack_filters_f32_kernel(const float* __restrict__ w, float* __restrict__ hi, float* __restrict__ lo, int Co, int Ci, int taps,
                                         int Mp, int Kp, int Cp, int transposed, int w_io, int nc, int ga, unsigned long long neg) {
-    const size_t total = (size_t)taps * Mp * Kp;
+    // one row (tap, m) of the expanded matrix per block iteration; the row is decoded once and the threads walk k
     const int Cm = transposed ? Ci : Co, Ck = transposed ? Co : Ci;
-    for (size_t idx = (size_t)blockIdx.x * blockDim.x + threadIdx.x; idx < total; idx += (size_t)gridDim.x * blockDim.x) {
-        const int k = (int)(idx % Kp);
-        const int m = (int)((idx / Kp) % Mp);
-        const int tap = (int)(idx / ((size_t)Kp * Mp));
+    const int rows = taps * Mp;
+    for (int row = blockIdx.x; row < rows; row += gridDim.x) {
+        const int tap = row / Mp, m = row - tap * Mp;
         const int cm_comp = m / Cm, cm = m - cm_comp * Cm;
-        const int ck_comp = k / Cp, ck = k - ck_comp * Cp;
-        float v = 0.f;
-        if (cm_comp < nc && ck_comp < nc && ck < Ck) {
-            const int d = transposed ? ck_comp : cm_comp, l = transposed ? cm_comp : ck_comp;
-            const int co = transposed ? ck : cm, ci = transposed ? cm : ck;
-            const int src_tap = transposed ? taps - 1 - tap : tap;
-            const int r = alg_pair(ga, l, d);
-            const size_t src = w_io ? ((size_t)r * Ci + ci) * Co + co : ((size_t)(r * Co + co) * Ci + ci) * taps + src_tap;
-            v = __ldg(w + src);
-            if (alg_negative(neg, l, d)) v = -v;
+        const int src_tap = transposed ? taps - 1 - tap : tap;
+        float* hrow = hi + (size_t)row * Kp;
+        float* lrow = lo + (size_t)row * Kp;
+        for (int k = threadIdx.x; k < Kp; k += blockDim.x) {
+            const int ck_comp = k / Cp, ck = k - ck_comp * Cp;
+            float v = 0.f;
+            if (cm_comp < nc && ck_comp < nc && ck < Ck) {
+                const int d = transposed ? ck_comp : cm_comp, l = transposed ? cm_comp : ck_comp;
+                const int co = transposed ? ck : cm, ci = transposed ? cm : ck;
+                const int r = alg_pair(ga, l, d);
+                const size_t src = w_io ? ((size_t)r * Ci + ci) * Co + co : ((size_t)(r * Co + co) * Ci + ci) * taps + src_tap;
+                v = __ldg(w + src);
+                if (alg_negative(neg, l, d)) v = -v;
+            }
+            float h, lw;
+            split_tf32(v, h, lw);
+            hrow[k] = h;
+            lrow[k] = lw;
         }
-        float h, lw;
-        split_tf32(v, h, lw);
-        hi[idx] = h;
-        lo[idx] = lw;
     }
 }
 
@@ -720,7 +723,7 @@ int conv_tf32_launch(Pass pass, const Geom& g, const void* a, const void* b, con
     float* w_lo = reinterpret_cast<float*>(s8 + 2 * pl.xp_bytes + pl.w_bytes);
     pack_activations_f32_kernel<<<grid_cap((size_t)pl.LK * g.Nb * pl.Hp * pl.Wp * (pl.Cp / 4), 256, 16), 256, 0, stream>>>(
         (const float*)b, x_hi, x_lo, pl.LK * g.Nb, pl.Cin, pl.Hin, pl.Win, pl.Hp, pl.Wp, pl.Cp, pl.pad_top, pl.pad_left, pl.ins_h, pl.ins_w);
-    pack_filters_f32_kernel<<<grid_cap((size_t)taps * pl.Mp * pl.Kp, 256, 8), 256, 0, stream>>>(
+    pack_filters_f32_kernel<<<grid_cap((size_t)taps * pl.Mp, 1, 8), pl.Kp >= 256 ? 256 : 128, 0, stream>>>(
         (const float*)a, w_hi, w_lo, g.Co, g.Ci, taps, pl.Mp, pl.Kp, pl.Cp, pass == PASS_BWD_DATA ? 1 : 0, g.w_io, g.nc, g.ga, g.neg);
     PCB_CUDA_TRY(cudaGetLastError());
 
