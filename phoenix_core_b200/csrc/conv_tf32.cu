@@ -274,9 +274,61 @@ __device__ __forceinline__ void split_tf32(float x, float& hi, float& lo) {
     lo = x - hi;
 }
 
-__global__ void pack_activations_f32_kernel(const float* __restrict__ x, float* __restrict__ hi, float* __restrict__ lo, int planes, int C,
-                                            int H, int W, int Hp, int Wp, int Cp, int pad_top, int pad_left, int ins_h, int ins_w,
-                                            int cb = 0, int Nb = 1) {
+// A block takes 32 consecutive padded pixels of one plane and up to 64 channels at a time through shared memory: the NCHW reads
+// run along the pixels of one channel (coalesced), the channels-last writes along the channel groups of one pixel (coalesced;
+// a thread per (pixel, 4 channels) writes one float4 of hi and one of lo).
+__global__ void __launch_bounds__(256)
+pack_activations_f32_kernel(const float* __restrict__ x, float* __restrict__ hi, float* __restrict__ lo, int planes, int C,
+                            int H, int W, int Hp, int Wp, int Cp, int pad_top, int pad_left, int ins_h, int ins_w,
+                            int cb, int Nb) {
+    __shared__ float tile[64][33];
+    const int PP = Hp * Wp, tiles_pp = (PP + 31) / 32;
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const long long n_tiles = (long long)planes * tiles_pp;
+    for (long long t = blockIdx.x; t < n_tiles; t += gridDim.x) {
+        const int plane = (int)(t / tiles_pp), pp0 = (int)(t - (long long)plane * tiles_pp) * 32;
+        const int pp = pp0 + lane;
+        const int hp = pp / Wp, wp = pp - hp * Wp;
+        int ih = hp - pad_top, iw = wp - pad_left;
+        bool inside = pp < PP && ih >= 0 && iw >= 0;
+        if (inside && (ins_h > 1 || ins_w > 1)) {
+            inside = (ih % ins_h == 0) && (iw % ins_w == 0);
+            ih /= ins_h; iw /= ins_w;
+        }
+        inside = inside && ih < H && iw < W;
+        const float* src = x + ((size_t)plane * C * H + ih) * W + iw;      // + c * H * W
+        for (int c0 = 0; c0 < Cp; c0 += 64) {
+            const int c_pass = min(64, Cp - c0);
+            for (int c = warp; c < c_pass; c += 8) tile[c][lane] = (inside && c0 + c < C) ? __ldg(src + (size_t)(c0 + c) * H * W) : 0.f;
+            __syncthreads();
+            const int groups = c_pass / 4;
+            for (int idx = threadIdx.x; idx < 32 * groups; idx += 256) {
+                const int g = idx % groups, px = idx / groups;
+                if (pp0 + px >= PP) continue;
+                float4 vh, vl;
+                split_tf32(tile[4 * g][px], vh.x, vl.x);
+                split_tf32(tile[4 * g + 1][px], vh.y, vl.y);
+                split_tf32(tile[4 * g + 2][px], vh.z, vl.z);
+                split_tf32(tile[4 * g + 3][px], vh.w, vl.w);
+                const int ch = c0 + 4 * g;
+                size_t o = ((size_t)plane * PP + pp0 + px) * Cp + ch;
+                if (cb > 0) {   // blocks of cb channels, block index outermost: [comp * (Cp / cb) + c / cb][img][hp][wp][cb]
+                    const int comp = plane / Nb, img = plane - comp * Nb, bl = ch / cb;
+                    o = ((((size_t)comp * (Cp / cb) + bl) * Nb + img) * PP + pp0 + px) * cb + (ch - bl * cb);
+                }
+                *reinterpret_cast<float4*>(hi + o) = vh;
+                *reinterpret_cast<float4*>(lo + o) = vl;
+            }
+            __syncthreads();
+        }
+    }
+}
+
+// The same staging, one thread per (pixel, 4 channels), for planes of fewer than 32 padded pixels (dense layers are 1 x 1 images:
+// consecutive threads then walk the channel groups of one row, and both sides are contiguous).
+__global__ void pack_activations_f32_small_kernel(const float* __restrict__ x, float* __restrict__ hi, float* __restrict__ lo, int planes, int C,
+                                                  int H, int W, int Hp, int Wp, int Cp, int pad_top, int pad_left, int ins_h, int ins_w,
+                                                  int cb, int Nb) {
     const int groups = Cp / 4;
     const size_t total = (size_t)planes * Hp * Wp * groups;
     for (size_t idx = (size_t)blockIdx.x * blockDim.x + threadIdx.x; idx < total; idx += (size_t)gridDim.x * blockDim.x) {
@@ -302,12 +354,24 @@ __global__ void pack_activations_f32_kernel(const float* __restrict__ x, float* 
             split_tf32(v, ph[e], pl[e]);
         }
         size_t o = (((size_t)plane * Hp + hp) * Wp + wp) * Cp + grp * 4;
-        if (cb > 0) {   // blocks of cb channels, block index outermost: [comp * (Cp / cb) + c / cb][img][hp][wp][cb]
+        if (cb > 0) {
             const int comp = plane / Nb, img = plane - comp * Nb, b = (grp * 4) / cb;
             o = (((((size_t)comp * (Cp / cb) + b) * Nb + img) * Hp + hp) * Wp + wp) * cb + (grp * 4 - b * cb);
         }
         *reinterpret_cast<float4*>(hi + o) = vh;
         *reinterpret_cast<float4*>(lo + o) = vl;
+    }
+}
+
+void stage_activations_f32(const float* x, float* hi, float* lo, int planes, int C, int H, int W, int Hp, int Wp, int Cp, int pad_top, int pad_left,
+                           int ins_h, int ins_w, int cb, int Nb, cudaStream_t stream) {
+    if (Hp * Wp < 32) {
+        pack_activations_f32_small_kernel<<<grid_cap((size_t)planes * Hp * Wp * (Cp / 4), 256, 16), 256, 0, stream>>>(
+            x, hi, lo, planes, C, H, W, Hp, Wp, Cp, pad_top, pad_left, ins_h, ins_w, cb, Nb);
+    } else {
+        const size_t tiles = (size_t)planes * ((Hp * Wp + 31) / 32);
+        pack_activations_f32_kernel<<<grid_cap(tiles, 1, 16), 256, 0, stream>>>(x, hi, lo, planes, C, H, W, Hp, Wp, Cp, pad_top, pad_left, ins_h,
+                                                                                 ins_w, cb, Nb);
     }
 }
 
@@ -643,10 +707,8 @@ static int conv_tf32_filter_launch(const Geom& g, const float* dy, const float* 
     float* y_hi = reinterpret_cast<float*>(s8 + 2 * f.xp_bytes);
     float* y_lo = reinterpret_cast<float*>(s8 + 2 * f.xp_bytes + f.dyp_bytes);
     float* acc = reinterpret_cast<float*>(s8 + 2 * f.xp_bytes + 2 * f.dyp_bytes);
-    pack_activations_f32_kernel<<<grid_cap((size_t)g.nc * g.Nb * f.Hp * f.Wp * (f.Cip / 4), 256, 16), 256, 0, stream>>>(
-        x, x_hi, x_lo, g.nc * g.Nb, g.Ci, g.H, g.W, f.Hp, f.Wp, f.Cip, g.PT, g.PL, 1, 1, 32, g.Nb);
-    pack_activations_f32_kernel<<<grid_cap((size_t)g.nc * g.Nb * g.HO * g.WO * (f.Cop / 4), 256, 16), 256, 0, stream>>>(
-        dy, y_hi, y_lo, g.nc * g.Nb, g.Co, g.HO, g.WO, g.HO, g.WO, f.Cop, 0, 0, 1, 1, 32, g.Nb);
+    stage_activations_f32(x, x_hi, x_lo, g.nc * g.Nb, g.Ci, g.H, g.W, f.Hp, f.Wp, f.Cip, g.PT, g.PL, 1, 1, 32, g.Nb, stream);
+    stage_activations_f32(dy, y_hi, y_lo, g.nc * g.Nb, g.Co, g.HO, g.WO, g.HO, g.WO, f.Cop, 0, 0, 1, 1, 32, g.Nb, stream);
     PCB_CUDA_TRY(cudaGetLastError());
     PCB_CUDA_TRY(cudaMemsetAsync(acc, 0, (size_t)g.nc * g.Co * g.Ci * taps * sizeof(float), stream));
 
@@ -721,8 +783,8 @@ int conv_tf32_launch(Pass pass, const Geom& g, const void* a, const void* b, con
     float* x_lo = reinterpret_cast<float*>(s8 + pl.xp_bytes);
     float* w_hi = reinterpret_cast<float*>(s8 + 2 * pl.xp_bytes);
     float* w_lo = reinterpret_cast<float*>(s8 + 2 * pl.xp_bytes + pl.w_bytes);
-    pack_activations_f32_kernel<<<grid_cap((size_t)pl.LK * g.Nb * pl.Hp * pl.Wp * (pl.Cp / 4), 256, 16), 256, 0, stream>>>(
-        (const float*)b, x_hi, x_lo, pl.LK * g.Nb, pl.Cin, pl.Hin, pl.Win, pl.Hp, pl.Wp, pl.Cp, pl.pad_top, pl.pad_left, pl.ins_h, pl.ins_w);
+    stage_activations_f32((const float*)b, x_hi, x_lo, pl.LK * g.Nb, pl.Cin, pl.Hin, pl.Win, pl.Hp, pl.Wp, pl.Cp, pl.pad_top, pl.pad_left, pl.ins_h,
+                          pl.ins_w, 0, 1, stream);
     pack_filters_f32_kernel<<<grid_cap((size_t)taps * pl.Mp, 1, 8), pl.Kp >= 256 ? 256 : 128, 0, stream>>>(
         (const float*)a, w_hi, w_lo, g.Co, g.Ci, taps, pl.Mp, pl.Kp, pl.Cp, pass == PASS_BWD_DATA ? 1 : 0, g.w_io, g.nc, g.ga, g.neg);
     PCB_CUDA_TRY(cudaGetLastError());
