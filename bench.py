@@ -20,6 +20,7 @@ Prints one JSON line:
   eight_product  the factorised 8-product formulation of the same step on its own tcgen05 kernels
   dense          the quaternion dense configuration (batch 256, 512 -> 512, fp32) forward + backward
   sweep          the ResNet-stage shape sweep (batch 128, fp16): every pass of every shape
+  sweep_f32      the same sweep in fp32 (error-compensated TF32 kernels), with the executed-TF32 fraction
   qresnet18      images/s of a quaternion ResNet-18 training step (batch 128 per GPU, 224x224, fp16, data-parallel)
   cpu_baseline   the reference's CPU orchestration (8-product default and 16-product) over oneDNN via torch CPU
                  ops on a bounded sample, on the box's host cores
@@ -264,8 +265,9 @@ def dense_leg(torch, pcb, _lib, peaks):
     return out
 
 
-def sweep_leg(torch, pcb, _lib, peaks, reps=5, batch=128, only=None, layouts=("nchw",), extra_nhwc=((64, 56, 3, 1),), dtype="f16"):
-    """The ResNet-stage sweep, fp16: 3x3 (pad 1) and 1x1, stride 1 and 2, forward / backward-data / backward-filter of each
+def sweep_leg(torch, pcb, _lib, peaks, reps=5, batch=128, only=None, layouts=("nchw",), extra_nhwc=((64, 56, 3, 1),), dtype="f16",
+              tf32_peak=None):
+    """The ResNet-stage sweep, fp16 or fp32: 3x3 (pad 1) and 1x1, stride 1 and 2, forward / backward-data / backward-filter of each
     shape timed separately (3 warm-up + `reps` launches, CUDA events; times include every staging kernel of the call).
     Inputs are seeded U[-1,1] generated on the device; every shape's tensors exceed the L2 or are rewritten each launch.
     `extra_nhwc`: shapes repeated with channels-last activations and OHWI filters (read in place by the tensor-core kernels).
@@ -309,17 +311,23 @@ def sweep_leg(torch, pcb, _lib, peaks, reps=5, batch=128, only=None, layouts=("n
         )
         for name, fn, nbytes, pid in passes:
             ms = event_time(torch, fn, reps, 3)
-            rows.append({"c": c, "hw": hw, "k": k, "s": stride, "layout": layout, "dtype": dtype, "pass": name, "ms": round(ms, 4),
-                         "tflops": round(fl / (ms * 1e-3) / 1e12, 1), "gbs": round(nbytes / (ms * 1e-3) / 1e9, 0),
-                         "f_tensor": round(fl / (ms * 1e-3) / 1e12 / peaks["tflops_sustained"], 3),
-                         "f_hbm": round(nbytes / (ms * 1e-3) / 1e9 / peaks["hbm_gbs"], 3),
-                         "engine": L.pcb_qconv2d_engine_for(ctypes.byref(d), pid)})
+            row = {"c": c, "hw": hw, "k": k, "s": stride, "layout": layout, "dtype": dtype, "pass": name, "ms": round(ms, 4),
+                   "tflops": round(fl / (ms * 1e-3) / 1e12, 1), "gbs": round(nbytes / (ms * 1e-3) / 1e9, 0),
+                   "f_hbm": round(nbytes / (ms * 1e-3) / 1e9 / peaks["hbm_gbs"], 3),
+                   "engine": L.pcb_qconv2d_engine_for(ctypes.byref(d), pid)}
+            if dtype == "f32":       # the fp32 kernels execute three TF32 MMAs per product
+                if tf32_peak:
+                    row["f_tf32_executed"] = round(3 * fl / (ms * 1e-3) / 1e12 / tf32_peak, 3)
+            else:
+                row["f_tensor"] = round(fl / (ms * 1e-3) / 1e12 / peaks["tflops_sustained"], 3)
+            rows.append(row)
         _lib.check(L.pcb_check_device_status(_ptr(ws), ws.numel(), _stream()))
         del x, w, y, dy, dw, dx
         torch.cuda.empty_cache()
-    return {"config": "batch %d, fp16, 16-product, U[-1,1]; layout nchw = NCHW activations + OIHW filters, nhwc = channels-last activations "
-                      "+ OHWI filters; f_tensor against the sustained tensor peak, f_hbm = algorithmic bytes / time against the copy "
-                      "bandwidth; engine 2 = tcgen05, 1 = CUDA cores" % batch,
+    return {"config": "batch %d, %s, 16-product, U[-1,1]; layout nchw = NCHW activations + OIHW filters, nhwc = channels-last activations "
+                      "+ OHWI filters; f_tensor against the sustained tensor peak (fp16), f_tf32_executed = 3 x FLOPs / time against a TF32 "
+                      "cuBLAS GEMM timed in this run (fp32: three TF32 MMAs per product), f_hbm = algorithmic bytes / time against the "
+                      "copy bandwidth; engine 2 = tcgen05, 1 = CUDA cores" % (batch, "fp32" if dtype == "f32" else "fp16"),
             "reps": reps, "rows": rows}
 
 
@@ -566,12 +574,14 @@ def run_ours(args):
         del hx, hw, hdy, hy, hdx, hdw, sets
 
     peaks = read_peaks()
-    dense = sweep = None
+    dense = sweep = sweep_f32 = None
     if world == 1 and not args.kernels_only and args.batch is None:      # single-GPU records; the scaling runs skip them
         torch.cuda.empty_cache()
         dense = dense_leg(torch, pcb, _lib, peaks)
         if not args.no_sweep:
             sweep = sweep_leg(torch, pcb, _lib, peaks)
+            tf32_peak = dense["f32"].get("tf32_peak_tflops_measured") if dense and "f32" in dense else None
+            sweep_f32 = sweep_leg(torch, pcb, _lib, peaks, reps=3, extra_nhwc=(), dtype="f32", tf32_peak=tf32_peak)
     if world > 1:
         dist.barrier()
 
@@ -639,6 +649,8 @@ def run_ours(args):
             line["dense"] = dense
         if sweep is not None:
             line["sweep"] = sweep
+        if sweep_f32 is not None:
+            line["sweep_f32"] = sweep_f32
         if args.batch is not None:
             line["reduced_batch"] = "profiling run, not a benchmark value"
         if args.formulation != "16p" or args.engine != "auto":
