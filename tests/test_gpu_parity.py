@@ -190,6 +190,9 @@ GENERAL_TENSOR_SHAPES = [
     (2, 32, 48, 56, 24, 5, 5, (1, 1), (2, 2, 2, 2)),     # halo mode: 25 taps (two stages fit), two tiles per column, M = 192
     (1, 32, 32, 26, 26, 3, 3, (2, 2), (0, 0, 1, 1)),     # halo mode in backward-data only (zero-inserted 26 x 26 plane)
     (2, 64, 32, 16, 16, 1, 1, (2, 2), (0, 0, 0, 0)),     # strided 1x1 on a compact copy (8-pixel vectors), then the direct pointwise kernels
+    (1, 96, 160, 9, 9, 3, 3, (1, 1), (1, 1, 1, 1)),      # tiled filter packing with partial 64-column tiles on both sides (96 and 160 channels)
+    (1, 72, 64, 9, 9, 3, 3, (1, 1), (1, 1, 1, 1)),       # tiled filter packing with K-side channels padded (72 -> 80): zero columns
+    (1, 40, 32, 9, 9, 1, 1, (1, 1), (0, 0, 0, 0)),       # one tap: 32- and 64-element runs in the tiled filter packing
     (1, 24, 40, 9, 7, 1, 1, (2, 3), (1, 1, 0, 1)),       # strided 1x1 with padding, stride 3 across, odd planes (scalar copies)
     (2, 32, 32, 12, 12, 1, 1, (2, 2), (0, 0, 0, 0)),     # strided 1x1: 6 x 6 compact planes (4-pixel vectors), staged general kernel
     (5, 32, 128, 7, 7, 1, 1, (1, 1), (0, 0, 0, 0)),      # whole 7 x 7 planes per tile (4 images, the last tile ragged): bulk-copy epilogue
