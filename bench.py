@@ -185,6 +185,41 @@ def event_time(torch, fn, reps, warm=1):
     return a.elapsed_time(b) / reps
 
 
+class ClockProbe:
+    """The clock the SMs really run at while other kernels execute: the library's one-thread probe kernel, launched on a second
+    stream in the middle of a timed loop, counts a million of its own cycles against the device's nanosecond timer. (NVML's
+    clock is sampled every few hundred milliseconds; the power cap pulls the clock down within a burst of launches.)"""
+
+    def __init__(self, torch, lib, cycles=1000000):
+        self.torch, self.lib, self.cycles = torch, lib, cycles
+        self.out = torch.zeros(2, dtype=torch.int64, device=torch.device("cuda", torch.cuda.current_device()))
+        self.stream = torch.cuda.Stream()
+
+    def launch(self):
+        self.lib.pcb_aux_clock_probe(self.cycles, ctypes.c_void_p(self.out.data_ptr()), ctypes.c_void_p(self.stream.cuda_stream))
+
+    def mhz(self):
+        self.stream.synchronize()
+        c, ns = self.out.tolist()
+        return round(c / ns * 1e3) if ns > 0 else None
+
+
+def event_time_probed(torch, fn, reps, probe, warm=1):
+    """event_time with the clock probe launched beside the middle of the loop; returns (ms, effective SM MHz)."""
+    for _ in range(warm):
+        fn()
+    torch.cuda.synchronize()
+    a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    a.record()
+    for i in range(reps):
+        fn()
+        if i == reps // 2:
+            probe.launch()
+    b.record()
+    torch.cuda.synchronize()
+    return a.elapsed_time(b) / reps, probe.mhz()
+
+
 def check_parity(torch, x, wt, dy, y, dw, dx, n):
     """Compares the tensors the timed steps produced with the CPU checker: y and dx on three whole images against the
     direct-loop oracle, the full filter gradient against the float64 block form of the product (sixteen matrix
@@ -440,18 +475,27 @@ def run_ours(args):
     }
     kreps = 1 if args.kernels_only else max(3, args.steps)
     kernels, kernels_long, kernel_clocks = {}, {}, {}
+    probe = ClockProbe(torch, L)
     for name, fn in kernel_fns.items():
         cs = ClockSampler(local_rank).start()
-        kernels[name] = event_time(torch, fn, kreps, 1)
+        kernels[name] = event_time(torch, fn, kreps, 1)      # (no probe here: it would share an SM with a CTA for a sixth of the window)
         kernel_clocks[name] = {"short": cs.stop()["sm_mhz"]}
     if not args.kernels_only:
         for name, fn in kernel_fns.items():
             reps_long = max(kreps, int(args.kernel_seconds * 1e3 / max(kernels[name], 1e-3)))
             cs = ClockSampler(local_rank).start()
-            kernels_long[name] = event_time(torch, fn, reps_long, 1)
+            kernels_long[name], mhz_eff = event_time_probed(torch, fn, reps_long, probe, 1)
             c = cs.stop()
-            kernel_clocks[name].update({"long": c["sm_mhz"], "long_reasons": c["reasons"], "long_launches": reps_long})
+            kernel_clocks[name].update({"long": c["sm_mhz"], "long_effective": mhz_eff, "long_reasons": c["reasons"], "long_launches": reps_long})
     _lib.check(L.pcb_check_device_status(_ptr(ws), ws.numel(), _stream()))
+    gemm_probe = None
+    if rank == 0 and not args.kernels_only:     # a library GEMM as the yardstick of "per clock" (measurement only, not on the path)
+        ga, gb = (torch.randn(8192, 8192, device=device, dtype=torch.bfloat16) for _ in range(2))
+        g_ms, g_mhz = event_time_probed(torch, lambda: torch.mm(ga, gb), max(20, int(args.kernel_seconds * 400)), probe, 3)
+        g_tf = 2 * 8192 ** 3 / (g_ms * 1e-3) / 1e12
+        gemm_probe = {"tflops": g_tf, "sm_mhz_effective": g_mhz,
+                      "frac_of_8192_flop_per_clk_sm": (g_tf * 1e12 / (torch.cuda.get_device_properties(device).multi_processor_count * 8192 * g_mhz * 1e6)) if g_mhz else None}
+        del ga, gb
 
     # the factorised 8-product formulation of the same step on its own tensor-core kernels (rank 0, no collective)
     eight = None
@@ -602,6 +646,14 @@ def run_ours(args):
         worst = max(timing, key=timing.get)
         achieved = fl / (timing[worst] * 1e-3) / 1e12
         achieved_short = fl / (kernels[worst] * 1e-3) / 1e12
+        # the same kernel per SM clock: 8192 dense 16-bit FLOPs per clock and SM, at the clock the probe saw beside the kernel, with a
+        # cuBLAS bf16 GEMM measured the same way in this run beside it
+        sms = torch.cuda.get_device_properties(device).multi_processor_count
+        per_clock = None
+        eff = kernel_clocks[worst].get("long_effective")
+        if eff:
+            per_clock = {"sm_mhz_effective": eff, "frac_of_8192_flop_per_clk_sm": achieved * 1e12 / (sms * 8192 * eff * 1e6),
+                         "cublas_bf16_gemm": gemm_probe}
         traffic = traffic_note = None
         traffic_path = os.path.join(ROOT, "profiles", "traffic.json")
         if os.path.exists(traffic_path) and n == 64:
@@ -634,6 +686,7 @@ def run_ours(args):
                                         % (peaks["source"], kernel_clocks[worst].get("long_launches", kreps), args.kernel_seconds, kernel_clocks[worst].get("long")),
                          "short_window": {"achieved": achieved_short, "peak": peaks["tflops_burst"], "frac": achieved_short / peaks["tflops_burst"],
                                           "launches": kreps, "sm_mhz": kernel_clocks[worst]["short"], "peak_source": peaks["source"] + ", burst bf16 GEMM"},
+                         "per_clock": per_clock,
                          "algorithmic_bytes": algorithmic_bytes[worst],
                          "hbm_frac": algorithmic_bytes[worst] / (timing[worst] * 1e-3) / 1e9 / peaks["hbm_gbs"],
                          "traffic": traffic, "traffic_note": traffic_note},

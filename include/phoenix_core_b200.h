@@ -217,6 +217,11 @@ int pcb_aux_bn_relu_bwd(int dtype, const void* x, const void* y, const void* dy,
 int pcb_aux_maxpool3x3s2_fwd(int dtype, const void* x, void* y, void* argmax, int rows, int h, int w, void* stream);
 int pcb_aux_maxpool3x3s2_bwd(int dtype, const void* dy, const void* argmax, void* dx, int rows, int h, int w, void* stream);
 
+/* Measurement aid (no reference counterpart): one device thread counts `spin_cycles` (1 .. 2^32) of its SM clock against the
+ * device's nanosecond timer and writes {cycles, nanoseconds} to `out_cycles_and_ns` (device memory, two 64-bit integers).
+ * Launched on a second stream beside other kernels it gives the clock the SMs really run at while those execute. */
+int pcb_aux_clock_probe(long long spin_cycles, long long* out_cycles_and_ns, void* stream);
+
 #ifdef __cplusplus
 }
 #endif

@@ -65,6 +65,7 @@ SYMBOLS = {
     "pcb_aux_bn_relu_bwd": (_i, [_i, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _vp]),
     "pcb_aux_maxpool3x3s2_fwd": (_i, [_i, _vp, _vp, _vp, _i, _i, _i, _vp]),
     "pcb_aux_maxpool3x3s2_bwd": (_i, [_i, _vp, _vp, _vp, _i, _i, _i, _vp]),
+    "pcb_aux_clock_probe": (_i, [ctypes.c_longlong, _vp, _vp]),
 }
 
 _lib = None

@@ -14,7 +14,7 @@ HERE = os.path.dirname(os.path.abspath(__file__))
 LIB = os.path.join(HERE, "libphoenix_core_b200.so")
 OBJ_DIR = os.path.join(HERE, "build")
 SOURCES = ["api.cu", "simt_qgemm.cu", "tensor_path.cu", "pointwise_tc.cu", "pointwise2_tc.cu", "pointwise8_tc.cu", "conv_tc.cu", "narrow_tc.cu",
-           "conv_tf32.cu", "dense_tc.cu", "aux_bn.cu"]
+           "conv_tf32.cu", "aux_bn.cu", "probe.cu"]
 HEADERS = ["common.cuh", "tensor_path.cuh", "umma.cuh", "tc_common.cuh", os.path.join("..", "..", "include", "phoenix_core_b200.h")]
 NVCC_FLAGS = [
     "-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "-std=c++17",
