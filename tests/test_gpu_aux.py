@@ -65,3 +65,21 @@ def test_maxpool_helpers(shape, dtype):
     yref.backward(dy.float())
     # random data has no ties inside a window, so the arg-max is unique
     assert torch.allclose(xin.grad.float(), xref.grad, atol=2e-2, rtol=2e-2)
+
+
+def test_clock_probe_reports_a_plausible_sm_clock():
+    """The measurement aid: a million SM cycles against the device's nanosecond timer, and its argument checks."""
+    if not torch.cuda.is_available():
+        pytest.skip("no CUDA device")
+    import ctypes
+    from phoenix_core_b200 import _lib
+    L = _lib.lib()
+    out = torch.zeros(2, dtype=torch.int64, device="cuda")
+    stream = torch.cuda.current_stream().cuda_stream
+    assert L.pcb_aux_clock_probe(1000000, ctypes.c_void_p(out.data_ptr()), ctypes.c_void_p(stream)) == _lib.PCB_OK
+    torch.cuda.synchronize()
+    cycles, ns = out.tolist()
+    assert 1000000 <= cycles < 1100000 and ns > 0
+    assert 300 < cycles / ns * 1e3 < 3000            # MHz
+    assert L.pcb_aux_clock_probe(0, ctypes.c_void_p(out.data_ptr()), ctypes.c_void_p(stream)) == _lib.PCB_ERR_INVALID_ARGUMENT
+    assert L.pcb_aux_clock_probe(1000, None, ctypes.c_void_p(stream)) == _lib.PCB_ERR_INVALID_ARGUMENT
