@@ -127,7 +127,7 @@ qconv_pointwise_pair_tc_kernel(const __grid_constant__ CUtensorMap map_w, const 
     const uint32_t full_bar = smem_u32(bars), empty_bar = smem_u32(bars + P_STAGES);
     const uint32_t tmem_full0 = smem_u32(bars + 2 * P_STAGES), tmem_full1 = smem_u32(bars + 2 * P_STAGES + 1);
     const uint32_t tmem_empty = smem_u32(bars + 2 * P_STAGES + 2);        // four barriers, one per component (even CTA)
-    const uint32_t a_full = smem_u32(bars + 2 * P_STAGES + 6), epi_bar = smem_u32(bars + 2 * P_STAGES + 7);
+    const uint32_t a_full = smem_u32(bars + 2 * P_STAGES + 6);
     const uint32_t out_addr = tiles_addr + OPERANDS;
 
     const int n_tiles = p.n_px_tiles * p.n_cp;
@@ -141,7 +141,7 @@ qconv_pointwise_pair_tc_kernel(const __grid_constant__ CUtensorMap map_w, const 
         for (int s = 0; s < P_STAGES; ++s) { mbar_init(full_bar + 8 * s, 1); mbar_init(empty_bar + 8 * s, 1); }
         mbar_init(tmem_full0, 1); mbar_init(tmem_full1, 1);
         for (int o = 0; o < 4; ++o) mbar_init(tmem_empty + 8 * o, 16);   // eight epilogue warps of each CTA
-        mbar_init(a_full, 1); mbar_init(epi_bar, 8);
+        mbar_init(a_full, 1);
         fence_barrier_init();
     }
     if (warp == 1) tmem_alloc_pair(smem_u32(tmem_slot), 512);
@@ -254,20 +254,14 @@ qconv_pointwise_pair_tc_kernel(const __grid_constant__ CUtensorMap map_w, const 
         // ---------------------------------------------------------------- epilogue (warps 2..9, both CTAs: own 128 channels)
         const int q = warp & 3;                   // TMEM lane quadrant this warp may read
         const int chalf = (warp - 2) >> 2;        // which 64-pixel block of the tile (64 accumulator columns)
-        const bool issuer = warp == 2 && lane == 0;
         const int row = q * 32 + lane;
         const int c = c0 + row;
-        const uint32_t my_out = out_addr + chalf * P_OUT_HALF + row * 128;
+        // every warp owns the 4 KB of the staging box that hold its 32 rows and stores them itself: no warp waits for another
+        const uint32_t warp_out = out_addr + chalf * P_OUT_HALF + q * (32 * 128);
+        const uint32_t my_out = warp_out + lane * 128;
         const uint32_t lead_tmem_empty = map_to_cta(tmem_empty, 0);
-        int local_tile = 0, epi_phase = 0;
+        int local_tile = 0;
         bool ok = true;
-        auto epi_sync = [&]() {
-            __syncwarp();
-            if (lane == 0) mbar_arrive(epi_bar);
-            const bool done = mbar_wait_bounded(epi_bar, epi_phase & 1, status, ST_P_EPILOGUE);
-            ++epi_phase;
-            return __all_sync(0xffffffffu, done);
-        };
         for (int tile = pair; tile < n_tiles && ok; tile += n_pairs, ++local_tile) {
             const int px_tile = tile / p.n_cp;
             uint32_t packed[4][32];
@@ -300,33 +294,25 @@ qconv_pointwise_pair_tc_kernel(const __grid_constant__ CUtensorMap map_w, const 
                 }
             }
             if (!ok) break;
-            int img[2], pix[2];
+            const int blk = 2 * px_tile + chalf;
+            const int img = blk / p.blocks_per_image;
+            const int pix = (blk - img * p.blocks_per_image) * 64;
 #pragma unroll
-            for (int b = 0; b < 2; ++b) {
-                const int blk = 2 * px_tile + b;
-                img[b] = blk / p.blocks_per_image;
-                pix[b] = (blk - img[b] * p.blocks_per_image) * 64;
-            }
-#pragma unroll
-            for (int o = 0; o < 4 && ok; ++o) {
-                if (issuer) bulk_wait_read_all();          // the previous component has left the staging buffer
-                ok = epi_sync();
-                if (!ok) break;
+            for (int o = 0; o < 4; ++o) {
+                if (lane == 0) bulk_wait_read_all();       // this warp's previous store has read its rows
+                __syncwarp();
 #pragma unroll
                 for (int ch = 0; ch < 8; ++ch)              // 16-byte chunk ch of this row sits at position ch ^ (row % 8)
                     st_shared_v4(my_out + ((ch ^ (row & 7)) << 4), packed[o][4 * ch], packed[o][4 * ch + 1], packed[o][4 * ch + 2], packed[o][4 * ch + 3]);
                 fence_proxy_async_smem();
-                ok = epi_sync();
-                if (!ok) break;
-                if (issuer) {
-#pragma unroll
-                    for (int b = 0; b < 2; ++b)
-                        if (img[b] < p.Nb) tma_store_4d(&map_out, out_addr + b * P_OUT_HALF, pix[b], c0, img[b], o);
+                __syncwarp();
+                if (lane == 0) {
+                    if (img < p.Nb) tma_store_4d(&map_out, warp_out, pix, c0 + q * 32, img, o);
                     bulk_commit_group();
                 }
             }
         }
-        if (issuer) bulk_wait_read_all();                   // shared memory must outlive the last bulk store's reads
+        if (lane == 0) bulk_wait_read_all();                // shared memory must outlive the last bulk store's reads
     }
 
     // teardown: nobody leaves while its peer may still signal its barriers or read its shared memory
@@ -383,10 +369,10 @@ int pointwise_pair_tc_launch(int dtype, const Geom& g, const void* w, const void
         const int rc = make_map_p(&map_act, fmt, x, 4, dims, strides, box, CU_TENSOR_MAP_SWIZZLE_128B);
         if (rc != PCB_OK) return rc;
     }
-    {   // y [4][Nb][Co][HW]; the epilogue stores [128 channels][64 pixels] boxes
+    {   // y [4][Nb][Co][HW]; every epilogue warp stores [32 channels][64 pixels] boxes
         const cuuint64_t dims[4] = {(cuuint64_t)HW, (cuuint64_t)g.Co, (cuuint64_t)g.Nb, 4};
         const cuuint64_t strides[3] = {(cuuint64_t)HW * 2, (cuuint64_t)g.Co * HW * 2, (cuuint64_t)g.Nb * g.Co * HW * 2};
-        const cuuint32_t box[4] = {64, P_CT, 1, 1};
+        const cuuint32_t box[4] = {64, 32, 1, 1};
         const int rc = make_map_p(&map_out, fmt, y, 4, dims, strides, box, CU_TENSOR_MAP_SWIZZLE_128B);
         if (rc != PCB_OK) return rc;
     }

@@ -81,7 +81,6 @@ qconv_pointwise_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __gri
     const uint32_t tiles_addr = smem_u32(base);
     const uint32_t full_bar = smem_u32(bars), empty_bar = smem_u32(bars + U_STAGES);
     const uint32_t a_full = smem_u32(bars + 2 * U_STAGES + 5);
-    const uint32_t epi_bar = smem_u32(bars + 2 * U_STAGES + 6);   // the eight epilogue warps among themselves
     const uint32_t out_addr = tiles_addr + OPERAND_BYTES;         // staging for the TMA store
     // one "accumulator drained" barrier per component, so the next tile's MMAs can start on component 0 while
     // the epilogue is still reading components 1..3; one "accumulators complete" barrier per PAIR of components
@@ -102,7 +101,6 @@ qconv_pointwise_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __gri
         mbar_init(tmem_full0, 1);
         mbar_init(tmem_full1, 1);
         mbar_init(a_full, 1);
-        mbar_init(epi_bar, 8);
         for (int o = 0; o < 4; ++o) mbar_init(tmem_empty + 8 * o, 8);
         fence_barrier_init();
     }
@@ -247,23 +245,17 @@ qconv_pointwise_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __gri
         // Ordinary global stores from here cost more than their bandwidth: every lane owns another channel row, so
         // a warp store scatters 32 segments, and while those queue up the MMA warp's own instructions wait behind
         // them. The tile therefore leaves through shared memory and TMA stores: each thread writes its row of one
-        // component into a 128-byte-swizzled [128 channels][64 pixels] box (conflict-free 16-byte stores), one
-        // thread issues the bulk stores, and out-of-range rows / pixels are clipped by the tensor map.
+        // component into a 128-byte-swizzled [128 channels][64 pixels] box (conflict-free 16-byte stores). Every warp owns the
+        // 4 KB of that box that hold its 32 rows and stores them itself ([32 channels][64 pixels] per bulk store), so the eight
+        // warps never wait for one another: a warp only waits for its own previous store to have read its 4 KB. Out-of-range rows
+        // and pixels are clipped by the tensor map.
         const int q = warp & 3;                   // TMEM lane quadrant this warp may read
         const int chalf = (warp - 2) >> 2;        // which 64-pixel block of the tile (64 accumulator columns)
-        const bool issuer = warp == 2 && lane == 0;
         const int row = q * 32 + lane;
-        const uint32_t my_out = out_addr + chalf * OUT_HALF_BYTES + row * 128;
-        int local_tile = 0, epi_phase = 0;
+        const uint32_t warp_out = out_addr + chalf * OUT_HALF_BYTES + q * (32 * 128);   // this warp's 32 rows of 128 bytes
+        const uint32_t my_out = warp_out + lane * 128;
+        int local_tile = 0;
         bool ok = true;
-        // all eight warps meet; bounded like every other wait of the kernel
-        auto epi_sync = [&]() {
-            __syncwarp();
-            if (lane == 0) mbar_arrive(epi_bar);
-            const bool done = mbar_wait_bounded(epi_bar, epi_phase & 1, status, ST_U_EPILOGUE);
-            ++epi_phase;
-            return __all_sync(0xffffffffu, done);
-        };
         for (int tile = blockIdx.x; tile < n_tiles && ok; tile += gridDim.x, ++local_tile) {
             const int px_tile = tile / p.n_c_tiles, c_tile = tile - px_tile * p.n_c_tiles;
             const int c = c_tile * CT + row;
@@ -301,33 +293,25 @@ qconv_pointwise_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __gri
                 }
             }
             if (!ok) break;
-            int img[2], pix[2];
+            const int blk = 2 * px_tile + chalf;
+            const int img = blk / p.blocks_per_image;
+            const int pix = (blk - img * p.blocks_per_image) * 64;
 #pragma unroll
-            for (int b = 0; b < 2; ++b) {
-                const int blk = 2 * px_tile + b;
-                img[b] = blk / p.blocks_per_image;
-                pix[b] = (blk - img[b] * p.blocks_per_image) * 64;
-            }
-#pragma unroll
-            for (int o = 0; o < 4 && ok; ++o) {
-                if (issuer) bulk_wait_read_all();          // the previous component has left the staging buffer
-                ok = epi_sync();
-                if (!ok) break;
+            for (int o = 0; o < 4; ++o) {
+                if (lane == 0) bulk_wait_read_all();       // this warp's previous store has read its rows
+                __syncwarp();
 #pragma unroll
                 for (int ch = 0; ch < 8; ++ch)              // 16-byte chunk ch of this row sits at position ch ^ (row % 8)
                     st_shared_v4(my_out + ((ch ^ (row & 7)) << 4), packed[o][4 * ch], packed[o][4 * ch + 1], packed[o][4 * ch + 2], packed[o][4 * ch + 3]);
                 fence_proxy_async_smem();
-                ok = epi_sync();
-                if (!ok) break;
-                if (issuer) {
-#pragma unroll
-                    for (int b = 0; b < 2; ++b)
-                        if (img[b] < p.Nb) tma_store_4d(&map_out, out_addr + b * OUT_HALF_BYTES, pix[b], c_tile * CT, img[b], o);
+                __syncwarp();
+                if (lane == 0) {
+                    if (img < p.Nb) tma_store_4d(&map_out, warp_out, pix, c_tile * CT + q * 32, img, o);
                     bulk_commit_group();
                 }
             }
         }
-        if (issuer) bulk_wait_read_all();                   // shared memory must outlive the last bulk store's reads
+        if (lane == 0) bulk_wait_read_all();                // shared memory must outlive the last bulk store's reads
     }
 
     tc_fence_before_sync();
@@ -528,10 +512,10 @@ int pointwise_tc_launch(Pass pass, int dtype, const Geom& g, const void* w, cons
         const int rc = make_map(&map_act, fmt, act, 4, dims, strides, box, CU_TENSOR_MAP_SWIZZLE_128B);
         if (rc != PCB_OK) return rc;
     }
-    {   // output [4][Nb][Cout][HW]: (px, channel, image, component); the epilogue stores [128 channels][64 pixels] boxes
+    {   // output [4][Nb][Cout][HW]: (px, channel, image, component); every epilogue warp stores [32 channels][64 pixels] boxes
         const cuuint64_t dims[4] = {(cuuint64_t)HW, (cuuint64_t)p.Cout, (cuuint64_t)g.Nb, 4};
         const cuuint64_t strides[3] = {(cuuint64_t)HW * 2, (cuuint64_t)p.Cout * HW * 2, (cuuint64_t)g.Nb * p.Cout * HW * 2};
-        const cuuint32_t box[4] = {64, CT, 1, 1};
+        const cuuint32_t box[4] = {64, 32, 1, 1};
         const int rc = make_map(&map_out, fmt, out, 4, dims, strides, box, CU_TENSOR_MAP_SWIZZLE_128B);
         if (rc != PCB_OK) return rc;
     }
