@@ -193,59 +193,52 @@ qconv_pointwise_pair_tc_kernel(const __grid_constant__ CUtensorMap map_w, const 
                 const uint32_t b_off = (uint32_t)(i * (P_KS * 128) + j * 2048) >> 4;
                 mma_f16_pair(tmem_base + o * P_PT, a_lo + a_off, a_hi, b_lo + b_off, b_hi, quat_negative(i, o) ? idesc_neg : idesc_pos, accumulate);
             };
+            // A tile is issued in two phases. All its K slices fit the activation ring (n_k <= P_STAGES), so phase A runs every
+            // slice into accumulators 0,1 and signals them complete, and phase B runs the same slices again into accumulators
+            // 2,3, releasing each stage as it goes. The epilogue drains 0,1 while phase B computes and 2,3 while the next tile's
+            // phase A computes: the turnover of the single-buffered accumulators costs no tensor time (with one pass over
+            // the slices, both pairs completed at the very end of the tile and the next tile waited for their drain).
+            // Inside a phase the MMAs alternate between the two accumulators of the pair.
             if (pair < n_tiles) ok = mbar_wait_bounded(a_full, 0, status, ST_P_MMA);
+            uint32_t a_lo_k[P_MAX_K], a_hi_k[P_MAX_K], b_lo_k[P_MAX_K], b_hi_k[P_MAX_K];
+            int s_k[P_MAX_K];
             for (int tile = pair; tile < n_tiles && ok; tile += n_pairs, ++local_tile) {
-                for (int k = 0; k < n_k && ok; ++k) {
-                    ok = mbar_wait_bounded(full_bar + 8 * s, par, status, ST_P_MMA);
-                    if (!ok) break;
-                    tc_fence_after_sync();
-                    {
-                        const uint64_t ad = desc_kmajor_sw64_p(a_slot(k));
-                        const uint64_t bd = make_desc_mnmajor(b_slot(s), P_B_BYTES);
-                        a_lo = (uint32_t)ad; a_hi = (uint32_t)(ad >> 32); b_lo = (uint32_t)bd; b_hi = (uint32_t)(bd >> 32);
-                    }
-                    const bool first = k == 0, last = k == n_k - 1;
-                    if (first) {        // pair-wise, each accumulator pair as soon as both CTAs' epilogues have drained it
 #pragma unroll
-                        for (int pr = 0; pr < 2; ++pr) {
-                            if (local_tile > 0) {
-                                ok = ok && mbar_wait_bounded(tmem_empty + 8 * (2 * pr), (local_tile - 1) & 1, status, ST_P_MMA) &&
-                                     mbar_wait_bounded(tmem_empty + 8 * (2 * pr + 1), (local_tile - 1) & 1, status, ST_P_MMA);
-                                tc_fence_after_sync();
-                            }
-                            if (ok) {
-#pragma unroll
-                                for (int i = 0; i < 4; ++i)
-#pragma unroll
-                                    for (int oo = 0; oo < 2; ++oo) issue(0, i, 2 * pr + oo, i > 0 ? 1u : 0u);
-                            }
-                        }
+                for (int ph = 0; ph < 2; ++ph) {
+                    if (local_tile > 0) {           // both CTAs' epilogues have drained this pair of the previous tile
+                        ok = ok && mbar_wait_bounded(tmem_empty + 8 * (2 * ph), (local_tile - 1) & 1, status, ST_P_MMA) &&
+                             mbar_wait_bounded(tmem_empty + 8 * (2 * ph + 1), (local_tile - 1) & 1, status, ST_P_MMA);
                         if (!ok) break;
-                    } else {
-#pragma unroll
-                        for (int i = 0; i < 4; ++i)
-#pragma unroll
-                            for (int o = 0; o < 4; ++o) issue(0, i, o, 1u);
+                        tc_fence_after_sync();
                     }
-                    if (last) {         // pair-wise again: components 0,1 are complete (and signalled) before 2,3
 #pragma unroll
-                        for (int pr = 0; pr < 2; ++pr) {
+                    for (int k = 0; k < P_MAX_K; ++k) {
+                        if (k >= n_k) break;
+                        if (ph == 0) {              // first touch of the slice: wait for its data, keep its descriptors
+                            ok = mbar_wait_bounded(full_bar + 8 * s, par, status, ST_P_MMA);
+                            if (!ok) break;
+                            tc_fence_after_sync();
+                            const uint64_t ad = desc_kmajor_sw64_p(a_slot(k));
+                            const uint64_t bd = make_desc_mnmajor(b_slot(s), P_B_BYTES);
+                            a_lo_k[k] = (uint32_t)ad; a_hi_k[k] = (uint32_t)(ad >> 32); b_lo_k[k] = (uint32_t)bd; b_hi_k[k] = (uint32_t)(bd >> 32);
+                            s_k[k] = s;
+                            if (++s == P_STAGES) { s = 0; par ^= 1u; }
+                        }
+                        a_lo = a_lo_k[k]; a_hi = a_hi_k[k]; b_lo = b_lo_k[k]; b_hi = b_hi_k[k];
+#pragma unroll
+                        for (int j = 0; j < P_KS / 16; ++j)
 #pragma unroll
                             for (int i = 0; i < 4; ++i)
 #pragma unroll
-                                for (int oo = 0; oo < 2; ++oo) issue(1, i, 2 * pr + oo, 1u);
-                            mma_commit_pair(pr == 0 ? tmem_full0 : tmem_full1);
-                            mma_commit_pair(pr == 0 ? peer_full0 : peer_full1);
+                                for (int oo = 0; oo < 2; ++oo) issue(j, i, 2 * ph + oo, (k > 0 || j > 0 || i > 0) ? 1u : 0u);
+                        if (ph == 1) {              // the stage is free in both CTAs
+                            mma_commit_pair(empty_bar + 8 * s_k[k]);
+                            mma_commit_pair(peer_empty + 8 * s_k[k]);
                         }
-                    } else {
-#pragma unroll
-                        for (int i = 0; i < 4; ++i)
-#pragma unroll
-                            for (int o = 0; o < 4; ++o) issue(1, i, o, 1u);
                     }
-                    mma_commit_pair(empty_bar + 8 * s);                    // the stage is free in both CTAs
-                    mma_commit_pair(peer_empty + 8 * s);
-                    if (++s == P_STAGES) { s = 0; par ^= 1u; }
+                    if (!ok) break;
+                    mma_commit_pair(ph == 0 ? tmem_full0 : tmem_full1);
+                    mma_commit_pair(ph == 0 ? peer_full0 : peer_full1);
                 }
             }
         }
