@@ -315,6 +315,155 @@ qconv_pointwise_pair_tc_kernel(const __grid_constant__ CUtensorMap map_w, const 
     if (warp == 1) tmem_dealloc_pair(tmem_base, 512);
 }
 
+// ===================================================================================================
+// Backward-filter of the pointwise convolution on pairs of SMs (layers with a multiple of 256 output channels):
+//   D_r[co, ci] += s(l, l^r) * dy_{l^r}[co, px-slice] * x_l[ci, px-slice]^T          l, r = 0..3
+// A pair accumulates a 256 (co) x 128 (ci) block per filter component r: each SM holds its own 128 rows of dy and HALF (64
+// rows) of the x tile, so a stage is 48 KB per SM instead of 64 KB, four stages fit where the single-SM kernel
+// (pointwise_tc.cu) has three, and every x tile is fetched once per 256 output channels. K = all pixels of all images, split
+// over the pairs; both SMs add their 4 x 128 x 128 partial sums into the fp32 scratch with vector reductions.
+// Roles and barriers as in the forward kernel above (no accumulator hand-back: one accumulation per CTA pair).
+// ===================================================================================================
+constexpr int PF_KP = 32;                                // pixels per stage and component: 64-byte rows, 64-byte swizzle
+constexpr int PF_STAGES = 4;
+constexpr uint32_t PF_A_BYTES = 4 * 128 * PF_KP * 2;     // 32 KB: this CTA's 128 rows of the four dy components
+constexpr uint32_t PF_B_BYTES = 4 * 64 * PF_KP * 2;      // 16 KB: this CTA's 64 rows of the four x components
+constexpr uint32_t PF_STAGE_BYTES = PF_A_BYTES + PF_B_BYTES;
+constexpr size_t PF_SMEM_BYTES = 1024 + PF_STAGES * PF_STAGE_BYTES + 256;
+
+struct PFParams {
+    int Nb, Co, Ci, HW;
+    int blocks_per_image;     // ceil(HW / 32)
+    int n_co_pairs, n_ci_tiles;
+    int steps_total;          // Nb * blocks_per_image
+    int steps_per_split;
+    int fmt;
+};
+
+__global__ void __launch_bounds__(P_THREADS, 1)
+qconv_pointwise_filter_pair_tc_kernel(const __grid_constant__ CUtensorMap map_dy, const __grid_constant__ CUtensorMap map_x, PFParams p,
+                                      float* __restrict__ dw32, int* __restrict__ status) {
+    extern __shared__ uint8_t smem_raw[];
+    const int t = threadIdx.x, warp = t >> 5, lane = t & 31;
+    const uint32_t rank = cluster_ctarank();
+    uint8_t* base = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+    uint64_t* bars = reinterpret_cast<uint64_t*>(base + PF_STAGES * PF_STAGE_BYTES);
+    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 2 * PF_STAGES + 1);
+    const uint32_t tiles_addr = smem_u32(base);
+    const uint32_t full_bar = smem_u32(bars), empty_bar = smem_u32(bars + PF_STAGES), tmem_full = smem_u32(bars + 2 * PF_STAGES);
+
+    const int n_out_tiles = p.n_co_pairs * p.n_ci_tiles;
+    const int pair = blockIdx.x >> 1;
+    const int out_tile = pair % n_out_tiles, split = pair / n_out_tiles;
+    const int co0 = (out_tile / p.n_ci_tiles) * 256 + (int)rank * 128;      // this CTA's rows of dy and of the result
+    const int ci0 = (out_tile % p.n_ci_tiles) * 128;
+    const int step_beg = split * p.steps_per_split;
+    const int step_end = min(p.steps_total, step_beg + p.steps_per_split);
+    const int n_steps = max(0, step_end - step_beg);
+
+    if (t == 0) {
+        for (int s = 0; s < PF_STAGES; ++s) { mbar_init(full_bar + 8 * s, 1); mbar_init(empty_bar + 8 * s, 1); }
+        mbar_init(tmem_full, 1);
+        fence_barrier_init();
+    }
+    if (warp == 1) tmem_alloc_pair(smem_u32(tmem_slot), 512);
+    tc_fence_before_sync();
+    __syncthreads();
+    cluster_sync_all();                 // both CTAs' barriers exist before anybody signals across the pair
+    tc_fence_after_sync();
+    const uint32_t tmem_base = *tmem_slot;
+
+    if (warp == 0) {
+        // ---------------------------------------------------------------- TMA producer (both CTAs: own dy rows, own half of x)
+        if (lane == 0) {
+            bool ok = true;
+            int s = 0;
+            uint32_t par = 1;           // parity of a stage that has never been used: the wait passes at once
+            for (int it = 0; it < n_steps && ok; ++it) {
+                ok = mbar_wait_bounded(empty_bar + 8 * s, par, status, ST_P_PRODUCER);
+                if (!ok) break;
+                const int step = step_beg + it;
+                const int img = step / p.blocks_per_image, px0 = (step - img * p.blocks_per_image) * PF_KP;
+                const uint32_t dst = tiles_addr + s * PF_STAGE_BYTES, lead_full = map_to_cta(full_bar + 8 * s, 0);
+                if (rank == 0) mbar_arrive_expect_tx(full_bar + 8 * s, 2u * PF_STAGE_BYTES);
+                tma_load_4d_pair(dst, &map_dy, px0, co0, img, 0, lead_full);                          // [d][128 co][32 px]
+                tma_load_4d_pair(dst + PF_A_BYTES, &map_x, px0, ci0 + (int)rank * 64, img, 0, lead_full);   // [l][64 ci][32 px]
+                if (++s == PF_STAGES) { s = 0; par ^= 1u; }
+            }
+        }
+        __syncwarp();
+    } else if (warp == 1) {
+        // ---------------------------------------------------------------- MMA issuer (even CTA, one thread)
+        if (lane == 0 && rank == 0) {
+            bool ok = true;
+            int s = 0;
+            uint32_t par = 0;
+            const uint32_t idesc_pos = make_idesc_f16(p.fmt, 256, 128, false, false, false, false);
+            const uint32_t idesc_neg = make_idesc_f16(p.fmt, 256, 128, false, false, true, false);
+            const uint32_t peer_empty = map_to_cta(empty_bar, 1), peer_tmem_full = map_to_cta(tmem_full, 1);
+            for (int it = 0; it < n_steps && ok; ++it) {
+                ok = mbar_wait_bounded(full_bar + 8 * s, par, status, ST_P_MMA);
+                if (!ok) break;
+                tc_fence_after_sync();
+                const uint64_t ad = desc_kmajor_sw64_p(tiles_addr + s * PF_STAGE_BYTES);
+                const uint64_t bd = desc_kmajor_sw64_p(tiles_addr + s * PF_STAGE_BYTES + PF_A_BYTES);
+                const uint32_t a_lo = (uint32_t)ad, a_hi = (uint32_t)(ad >> 32), b_lo = (uint32_t)bd, b_hi = (uint32_t)(bd >> 32);
+#pragma unroll
+                for (int j = 0; j < PF_KP / 16; ++j) {
+#pragma unroll
+                    for (int l = 0; l < 4; ++l) {
+#pragma unroll
+                        for (int r = 0; r < 4; ++r) {
+                            const int d = l ^ r;
+                            const uint32_t a_off = (uint32_t)(d * (128 * PF_KP * 2) + j * 32) >> 4, b_off = (uint32_t)(l * (64 * PF_KP * 2) + j * 32) >> 4;
+                            mma_f16_pair(tmem_base + r * 128, a_lo + a_off, a_hi, b_lo + b_off, b_hi, quat_negative(l, d) ? idesc_neg : idesc_pos,
+                                         (it > 0 || j > 0 || l > 0) ? 1u : 0u);
+                        }
+                    }
+                }
+                mma_commit_pair(empty_bar + 8 * s);
+                mma_commit_pair(peer_empty + 8 * s);
+                if (it == n_steps - 1) { mma_commit_pair(tmem_full); mma_commit_pair(peer_tmem_full); }
+                if (++s == PF_STAGES) { s = 0; par ^= 1u; }
+            }
+            if (n_steps == 0) { mbar_arrive(tmem_full); mbar_arrive_cluster(peer_tmem_full); }
+        }
+        __syncwarp();
+    } else {
+        // ---------------------------------------------------------------- epilogue (warps 2..9 of both CTAs: own 128 rows)
+        const int q = warp & 3, half = (warp - 2) >> 2;
+        bool ok = mbar_wait_bounded(tmem_full, 0, status, ST_P_EPILOGUE);
+        ok = __all_sync(0xffffffffu, ok && (*reinterpret_cast<volatile int*>(status) == 0));
+        tc_fence_after_sync();
+        if (ok && n_steps > 0) {
+            const int co = co0 + q * 32 + lane;
+#pragma unroll 1
+            for (int rr = 0; rr < 2; ++rr) {
+                const int r = 2 * half + rr;
+#pragma unroll 1
+                for (int cb = 0; cb < 4; ++cb) {
+                    uint32_t v[32];
+                    tmem_ld_32x32b_x32(tmem_base + ((uint32_t)(q * 32) << 16) + r * 128 + cb * 32, v);
+                    tmem_ld_wait();
+                    if (co >= p.Co) continue;
+                    float* dst = dw32 + ((size_t)r * p.Co + co) * p.Ci + ci0 + cb * 32;
+#pragma unroll
+                    for (int g4 = 0; g4 < 8; ++g4) {
+                        if (ci0 + cb * 32 + g4 * 4 < p.Ci)
+                            red_add_f32x4(dst + g4 * 4, __uint_as_float(v[4 * g4]), __uint_as_float(v[4 * g4 + 1]),
+                                          __uint_as_float(v[4 * g4 + 2]), __uint_as_float(v[4 * g4 + 3]));
+                    }
+                }
+            }
+        }
+    }
+    // teardown: nobody leaves while its peer may still signal its barriers or read its shared memory
+    tc_fence_before_sync();
+    __syncthreads();
+    cluster_sync_all();
+    if (warp == 1) tmem_dealloc_pair(tmem_base, 512);
+}
+
 int make_map_p(CUtensorMap* map, int fmt, const void* ptr, int rank, const cuuint64_t* dims, const cuuint64_t* strides_bytes,
                const cuuint32_t* box, CUtensorMapSwizzle swizzle) {
     return make_tensor_map(map, fmt == 0 ? CU_TENSOR_MAP_DATA_TYPE_FLOAT16 : CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, ptr, rank, dims, strides_bytes,
@@ -386,6 +535,60 @@ int pointwise_pair_tc_launch(int dtype, const Geom& g, const void* w, const void
     cfg.attrs = attr;
     cfg.numAttrs = 1;
     PCB_CUDA_TRY(cudaLaunchKernelEx(&cfg, qconv_pointwise_pair_tc_kernel, map_w, map_act, map_out, p, (const uint16_t*)bias, status));
+    return PCB_OK;
+}
+
+// The pair form of the pointwise filter gradient: the caller (pointwise_tc.cu) has zeroed the fp32 scratch and casts it afterwards.
+bool pointwise_filter_pair_tc_supported(const Geom& g) {
+    if ((g.Co % 256) || (g.Ci % 4) || ((g.H * g.W) % 8)) return false;
+    const long long steps = (long long)g.Nb * ((g.H * g.W + PF_KP - 1) / PF_KP);
+    const int n_out_tiles = (g.Co / 256) * ((g.Ci + 127) / 128);
+    // every pair of SMs gets a share of the pixels that is worth a pipeline
+    return n_out_tiles <= sm_count() / 2 && steps >= 8ll * (sm_count() / 2 / n_out_tiles);
+}
+
+int pointwise_filter_pair_tc_launch(int fmt, const Geom& g, const void* dy, const void* x, float* scratch, int* status, cudaStream_t stream) {
+    const int HW = g.H * g.W;
+    PFParams p;
+    p.Nb = g.Nb; p.Co = g.Co; p.Ci = g.Ci; p.HW = HW; p.fmt = fmt;
+    p.blocks_per_image = (HW + PF_KP - 1) / PF_KP;
+    p.n_co_pairs = g.Co / 256;
+    p.n_ci_tiles = (g.Ci + 127) / 128;
+    p.steps_total = g.Nb * p.blocks_per_image;
+    const int n_out_tiles = p.n_co_pairs * p.n_ci_tiles;
+    int splits = (sm_count() / 2) / n_out_tiles;
+    if (splits < 1) splits = 1;
+    if (splits > p.steps_total) splits = p.steps_total;
+    p.steps_per_split = (p.steps_total + splits - 1) / splits;
+    splits = (p.steps_total + p.steps_per_split - 1) / p.steps_per_split;
+
+    alignas(64) CUtensorMap map_dy, map_x;
+    {
+        const cuuint64_t dims[4] = {(cuuint64_t)HW, (cuuint64_t)g.Co, (cuuint64_t)g.Nb, 4};
+        const cuuint64_t strides[3] = {(cuuint64_t)HW * 2, (cuuint64_t)g.Co * HW * 2, (cuuint64_t)g.Nb * g.Co * HW * 2};
+        const cuuint32_t box[4] = {PF_KP, 128, 1, 4};
+        const int rc = make_map_p(&map_dy, fmt, dy, 4, dims, strides, box, CU_TENSOR_MAP_SWIZZLE_64B);
+        if (rc != PCB_OK) return rc;
+    }
+    {
+        const cuuint64_t dims[4] = {(cuuint64_t)HW, (cuuint64_t)g.Ci, (cuuint64_t)g.Nb, 4};
+        const cuuint64_t strides[3] = {(cuuint64_t)HW * 2, (cuuint64_t)g.Ci * HW * 2, (cuuint64_t)g.Nb * g.Ci * HW * 2};
+        const cuuint32_t box[4] = {PF_KP, 64, 1, 4};
+        const int rc = make_map_p(&map_x, fmt, x, 4, dims, strides, box, CU_TENSOR_MAP_SWIZZLE_64B);
+        if (rc != PCB_OK) return rc;
+    }
+    PCB_CUDA_TRY(cudaFuncSetAttribute(qconv_pointwise_filter_pair_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)PF_SMEM_BYTES));
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3(2 * n_out_tiles * splits, 1, 1);
+    cfg.blockDim = dim3(P_THREADS, 1, 1);
+    cfg.dynamicSmemBytes = PF_SMEM_BYTES;
+    cfg.stream = stream;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeClusterDimension;
+    attr[0].val.clusterDim.x = 2; attr[0].val.clusterDim.y = 1; attr[0].val.clusterDim.z = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = 1;
+    PCB_CUDA_TRY(cudaLaunchKernelEx(&cfg, qconv_pointwise_filter_pair_tc_kernel, map_dy, map_x, p, scratch, status));
     return PCB_OK;
 }
 

@@ -579,9 +579,14 @@ int pointwise_filter_tc_launch(int dtype, const Geom& g, const void* dy, const v
     }
     const size_t numel = (size_t)4 * g.Co * g.Ci;
     PCB_CUDA_TRY(cudaMemsetAsync(scratch, 0, numel * sizeof(float), stream));
-    PCB_CUDA_TRY(cudaFuncSetAttribute(qconv_pointwise_filter_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)F_SMEM_BYTES));
-    qconv_pointwise_filter_tc_kernel<<<n_out_tiles * splits, U_THREADS, F_SMEM_BYTES, stream>>>(map_dy, map_x, p, scratch, status);
-    PCB_CUDA_TRY(cudaGetLastError());
+    if (pointwise_filter_pair_tc_supported(g)) {        // multiples of 256 output channels: 256 x 128 blocks on pairs of SMs
+        const int rc = pointwise_filter_pair_tc_launch(fmt, g, dy, x, scratch, status, stream);
+        if (rc != PCB_OK) return rc;
+    } else {
+        PCB_CUDA_TRY(cudaFuncSetAttribute(qconv_pointwise_filter_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)F_SMEM_BYTES));
+        qconv_pointwise_filter_tc_kernel<<<n_out_tiles * splits, U_THREADS, F_SMEM_BYTES, stream>>>(map_dy, map_x, p, scratch, status);
+        PCB_CUDA_TRY(cudaGetLastError());
+    }
     const int blocks = (int)((numel + 255) / 256 < 1184 ? (numel + 255) / 256 : 1184);
     if (dtype == PCB_F16) cast_f32_kernel<__half><<<blocks, 256, 0, stream>>>(scratch, (__half*)dw, numel);
     else cast_f32_kernel<__nv_bfloat16><<<blocks, 256, 0, stream>>>(scratch, (__nv_bfloat16*)dw, numel);

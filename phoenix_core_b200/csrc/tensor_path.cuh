@@ -20,6 +20,8 @@ int pointwise_tc_launch(Pass pass, int dtype, const Geom& g, const void* w, cons
 // The forward kernel on pairs of SMs (cta_group::2 MMAs) for layers with a multiple of 256 output channels; see pointwise2_tc.cu.
 bool pointwise_pair_tc_supported(Pass pass, int dtype, int variant, const Geom& g);
 int pointwise_pair_tc_launch(int dtype, const Geom& g, const void* w, const void* x, const void* bias, void* y, int* status, cudaStream_t stream);
+bool pointwise_filter_pair_tc_supported(const Geom& g);
+int pointwise_filter_pair_tc_launch(int fmt, const Geom& g, const void* dy, const void* x, float* scratch, int* status, cudaStream_t stream);
 
 bool pointwise_filter_tc_supported(int dtype, int variant, const Geom& g);
 int pointwise_filter_tc_launch(int dtype, const Geom& g, const void* dy, const void* x, void* dw, float* scratch, int* status,

@@ -173,6 +173,26 @@ def test_pointwise_forward_on_sm_pairs_vs_oracle(gpu, oracle, shape, dtype):
     _check(nob, oracle.conv2d_fwd(x, w, None), dtype, gpu, "y (no bias)")
 
 
+# the filter gradient of such layers on pairs of SMs (256 x 128 blocks, K split over the pairs) and backward-data beside it
+PAIR_FILTER_SHAPES = PAIR_SHAPES + [
+    (6, 200, 256, 40, 40),      # two input-channel tiles, the second ragged (200 = 128 + 72: rows past the end read as zeros)
+    (12, 64, 512, 28, 28),      # two output-channel pairs, one 64-row half of the x tile out of range in the odd CTA
+]
+
+
+@pytest.mark.parametrize("shape", PAIR_FILTER_SHAPES)
+@pytest.mark.parametrize("dtype", ["f16", "bf16"])
+def test_pointwise_backward_on_sm_pairs_vs_oracle(gpu, oracle, shape, dtype):
+    n, ci, co, h, w_ = shape
+    x = gpu.rounded(normal(31, (4 * n, ci, h, w_)), dtype)
+    w = gpu.rounded(normal(32, (4, co, ci, 1, 1), std=(2.0 / (4 * ci)) ** 0.5), dtype)
+    dy = gpu.rounded(normal(33, (4 * n, co, h, w_), std=0.25), dtype)
+    rdw, rdx = oracle.conv2d_bwd(x, w, dy)
+    dw, dx = gpu.run_conv_bwd(x, w, dy, (1, 1), (0, 0, 0, 0), dtype, "16p", "tensor", True)
+    _check(dx, rdx, dtype, gpu, "dx")
+    _check(dw, rdw, dtype, gpu, "dw")
+
+
 # shapes for the general implicit-GEMM tensor-core kernel (staged channels-last activations, expanded filters):
 # n, ci, co, h, w, kh, kw, stride, pad(t,l,b,r)
 GENERAL_TENSOR_SHAPES = [
