@@ -6,9 +6,11 @@
 // resident in its shared memory) and HALF of the 128 pixels of the streamed activation tile; the tensor cores of both SMs read
 // the two halves across the pair. Per MMA and SM that is 4 KB + 2 KB of shared-memory operand reads instead of 8 KB, and each
 // activation tile is fetched from L2 once per 256 channels instead of once per 128.
-// What it buys, measured: 3-4 % on tensor-bound layers. A clock trace of the issuing thread shows the same 75-80 clocks per
-// MMA in steady state as the single-SM kernel, so that rate is the tensor pipe's own for 128-column MMAs, not a shared-memory
-// limit; the gain comes from the halved activation traffic and the deeper (four-stage) activation ring.
+// What it buys, measured on the 128 -> 256 channel layer at 56 x 56: with one pass over the K slices per tile, 3-4 % (the steady
+// 75-80 clocks per MMA are the tensor pipe's own rate for 128-column MMAs, not a shared-memory limit). The larger gain is the
+// schedule the four-stage activation ring allows: all K slices of a tile are resident at once, so a tile is issued in TWO
+// PHASES (accumulators 0,1 over every slice, then 2,3 over every slice) and the epilogue's drain of one accumulator pair always
+// overlaps the MMAs of the other: forward 0.185 -> 0.165 ms.
 //
 //   D_d[co, px] += s(l,d) * w[l^d][co, ci-slice] * x_l[ci-slice, px]      d, l = 0..3       (src/algebras.cc:28-49)
 //
@@ -43,7 +45,6 @@ constexpr uint32_t P_OUT_BYTES = 2 * P_OUT_HALF;
 constexpr int P_THREADS = 320;
 constexpr size_t P_SMEM_BYTES = 1024 + P_MAX_K * P_A_BYTES + P_STAGES * P_B_BYTES + P_OUT_BYTES + 256;
 constexpr int ST_P_PRODUCER = 0x10000, ST_P_MMA = 0x20000, ST_P_EPILOGUE = 0x40000;
-static_assert(P_KS / 16 == 2, "the issuing loop handles the first and the last K step of a slice separately");
 
 struct PParams {
     int Nb, Cout, Cred, HW;
