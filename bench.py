@@ -411,6 +411,9 @@ def run_ours(args):
     dx = torch.empty_like(x)
     comm = torch.cuda.Stream(priority=-1) if world > 1 else None
     pending = []
+    # data-parallel runs leave a few SMs free of the persistent kernels so that the all-reduce's kernel runs beside backward-data
+    sm_margin = args.sm_margin if args.sm_margin is not None else (2 if world > 1 else 0)
+    pcb.setSmMargin(sm_margin)
 
     def start_allreduce(grad):
         # the filter gradient is complete once the kernels enqueued so far have run: sum it across ranks on the side
@@ -675,7 +678,8 @@ def run_ours(args):
                                    "%d->%d quaternion channels, %dx%d, 16-product, NCHW" % (n, ci, co, h, w),
                        "parallelism": "dp%d" % world, "l2": "inputs (196 MiB) and outputs (392 MiB) exceed the 126 MB L2",
                        "flop_per_step_per_gpu": 3 * fl,
-                       "allreduce": "filter gradient, started after backward-filter on a side stream, beside backward-data" if world > 1 else None},
+                       "allreduce": "filter gradient, started after backward-filter on a side stream, beside backward-data" if world > 1 else None,
+                       "sm_margin": sm_margin},
             "parity": parity,
             "pct_of_tensor_peak": {"sustained": value / world / peaks["tflops_sustained"], "burst": value / world / peaks["tflops_burst"],
                                    "peaks": peaks["source"]},
@@ -732,6 +736,7 @@ def main():
     ap.add_argument("--formulation", default="16p", choices=["16p", "8p"],
                     help="profiling only: 8p times the factorised tensor-core kernels as the main step (use with --kernels-only)")
     ap.add_argument("--sweep-only", action="store_true", help="profiling only: run the shape sweep (or one shape of it) and print its record")
+    ap.add_argument("--sm-margin", type=int, default=None, help="SMs left free of the persistent kernels (default: 2 on more than one GPU, else 0)")
     ap.add_argument("--sweep-shape", default=None, help="channels,size,kernel,stride of the single sweep shape to run")
     ap.add_argument("--sweep-batch", type=int, default=128)
     ap.add_argument("--sweep-reps", type=int, default=5)

@@ -217,6 +217,13 @@ int pcb_aux_bn_relu_bwd(int dtype, const void* x, const void* y, const void* dy,
 int pcb_aux_maxpool3x3s2_fwd(int dtype, const void* x, void* y, void* argmax, int rows, int h, int w, void* stream);
 int pcb_aux_maxpool3x3s2_bwd(int dtype, const void* dy, const void* argmax, void* dx, int rows, int h, int w, void* stream);
 
+/* Deployment knob (no reference counterpart): the persistent tensor-core kernels occupy every SM with one CTA each; with a margin
+ * of `sms` (0 .. 64, process-wide, default 0) they size their grids for that many SMs fewer, so that a kernel enqueued on another
+ * stream -- a data-parallel all-reduce of the filter gradient beside backward-data -- finds SMs to run on instead of waiting
+ * for a CTA to retire. Takes effect from the next call. */
+int pcb_set_sm_margin(int sms);
+int pcb_get_sm_margin(void);
+
 /* Measurement aid (no reference counterpart): one device thread counts `spin_cycles` (1 .. 2^32) of its SM clock against the
  * device's nanosecond timer and writes {cycles, nanoseconds} to `out_cycles_and_ns` (device memory, two 64-bit integers).
  * Launched on a second stream beside other kernels it gives the clock the SMs really run at while those execute. */

@@ -66,6 +66,8 @@ SYMBOLS = {
     "pcb_aux_maxpool3x3s2_fwd": (_i, [_i, _vp, _vp, _vp, _i, _i, _i, _vp]),
     "pcb_aux_maxpool3x3s2_bwd": (_i, [_i, _vp, _vp, _vp, _i, _i, _i, _vp]),
     "pcb_aux_clock_probe": (_i, [ctypes.c_longlong, _vp, _vp]),
+    "pcb_set_sm_margin": (_i, [_i]),
+    "pcb_get_sm_margin": (_i, []),
 }
 
 _lib = None

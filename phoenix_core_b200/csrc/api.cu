@@ -9,6 +9,7 @@
 #include "umma.cuh"
 
 namespace pcb {
+int g_sm_margin = 0;         // SMs the persistent kernels leave free (pcb_set_sm_margin)
 
 static thread_local char g_error[512] = {0};
 
@@ -251,6 +252,14 @@ int conv_bwd_filter(const pcb_conv2d_desc* desc, const void* x, const void* dy, 
 using namespace pcb;
 
 extern "C" {
+
+int pcb_set_sm_margin(int sms) {
+    if (sms < 0 || sms > 64) return PCB_ERR_INVALID_ARGUMENT;
+    pcb::g_sm_margin = sms;
+    return PCB_OK;
+}
+int pcb_get_sm_margin(void) { return pcb::g_sm_margin; }
+
 
 const char* pcb_version(void) { return "phoenix_core_b200 0.1 (sm_100a)"; }
 

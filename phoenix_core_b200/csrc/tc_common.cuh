@@ -8,6 +8,7 @@
 #include "umma.cuh"
 
 namespace pcb {
+extern int g_sm_margin;      // defined in api.cu
 namespace tc {
 
 __device__ __forceinline__ void tma_load_3d(uint32_t dst, const CUtensorMap* map, int c0, int c1, int c2, uint32_t bar) {
@@ -151,6 +152,8 @@ inline int make_tensor_map(CUtensorMap* map, CUtensorMapDataType dt, const void*
     return PCB_OK;
 }
 
+// SMs the persistent kernels size their grids for: the device's count minus the margin set through pcb_set_sm_margin (SMs left
+// free so that another kernel, e.g. a collective's, can run beside them), never fewer than two.
 inline int sm_count() {
     static int sms = 0;
     if (sms == 0) {
@@ -158,7 +161,8 @@ inline int sm_count() {
         if (cudaGetDevice(&dev) != cudaSuccess || cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || sms <= 0)
             sms = 148;
     }
-    return sms;
+    const int left = sms - pcb::g_sm_margin;
+    return left < 2 ? 2 : left;
 }
 
 inline int round_up(int v, int m) { return (v + m - 1) / m * m; }

@@ -25,6 +25,7 @@
 #include "umma.cuh"
 
 namespace pcb {
+extern int g_sm_margin;
 namespace {
 
 using namespace umma;
@@ -348,7 +349,8 @@ int sm_count() {
         if (cudaGetDevice(&dev) != cudaSuccess || cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || sms <= 0)
             sms = 148;
     }
-    return sms;
+    const int left = sms - g_sm_margin;      // see pcb_set_sm_margin
+    return left < 2 ? 2 : left;
 }
 
 template <int PASS>

@@ -78,6 +78,16 @@ class Device:
         return self.context
 
 
+def setSmMargin(sms):
+    """Leaves `sms` SMs free of the persistent tensor-core kernels from the next call on (process-wide), so that a kernel on
+    another stream -- the all-reduce of a filter gradient beside backward-data -- finds SMs to run on. 0 restores the default."""
+    _lib.check(_lib.lib().pcb_set_sm_margin(int(sms)))
+
+
+def getSmMargin():
+    return int(_lib.lib().pcb_get_sm_margin())
+
+
 def _ptr(t):
     return None if t is None else ctypes.c_void_p(t.data_ptr())
 

@@ -193,6 +193,29 @@ def test_pointwise_backward_on_sm_pairs_vs_oracle(gpu, oracle, shape, dtype):
     _check(dw, rdw, dtype, gpu, "dw")
 
 
+def test_sm_margin_leaves_results_unchanged(gpu, oracle):
+    """With SMs held back for a collective's kernel the persistent kernels run on smaller grids (73 pairs / 146 CTAs on a B200);
+    the results are the same."""
+    import phoenix_core_b200 as pcb
+    n, ci, co, h, w_ = 8, 128, 256, 56, 56
+    x = gpu.rounded(normal(51, (4 * n, ci, h, w_)), "f16")
+    w = gpu.rounded(normal(52, (4, co, ci, 1, 1), std=(2.0 / (4 * ci)) ** 0.5), "f16")
+    dy = gpu.rounded(normal(53, (4 * n, co, h, w_), std=0.25), "f16")
+    ref = oracle.conv2d_fwd(x, w, None)
+    rdw, rdx = oracle.conv2d_bwd(x, w, dy)
+    assert pcb.getSmMargin() == 0
+    try:
+        for margin in (2, 5):
+            pcb.setSmMargin(margin)
+            assert pcb.getSmMargin() == margin
+            _check(gpu.run_conv_fwd(x, w, None, (1, 1), (0, 0, 0, 0), "f16", "16p", "tensor"), ref, "f16", gpu, "y")
+            dw, dx = gpu.run_conv_bwd(x, w, dy, (1, 1), (0, 0, 0, 0), "f16", "16p", "tensor", True)
+            _check(dx, rdx, "f16", gpu, "dx")
+            _check(dw, rdw, "f16", gpu, "dw")
+    finally:
+        pcb.setSmMargin(0)
+
+
 # shapes for the general implicit-GEMM tensor-core kernel (staged channels-last activations, expanded filters):
 # n, ci, co, h, w, kh, kw, stride, pad(t,l,b,r)
 GENERAL_TENSOR_SHAPES = [
