@@ -480,10 +480,10 @@ bool pointwise_pair_tc_supported(Pass pass, int dtype, int variant, const Geom& 
     if (!(g.KH == 1 && g.KW == 1 && g.SH == 1 && g.SW == 1 && g.PT == 0 && g.PL == 0 && g.HO == g.H && g.WO == g.W)) return false;
     if ((g.Ci % 8) || (g.Co % 256) || ((g.H * g.W) % 8)) return false;
     if ((g.Ci + P_KS - 1) / P_KS > P_MAX_K) return false;                 // the filter rows of a CTA stay in its shared memory
-    // Measured against the single-SM kernel (batch 64..128, forward): 0.186 vs 0.192 ms at 128 -> 256 channels and 56 x 56,
-    // 0.190 vs 0.196 ms at 128 -> 512 and 28 x 28, 0.353 vs 0.368 ms at 128 -> 1024; 3 % slower at 64 or 32 input channels, where the
-    // layer is bound by HBM and the pair's common tile schedule costs more than the halved activation traffic saves.
-    if (g.Ci < 96) return false;
+    // Measured against the single-SM kernel (batch 64..128, forward, two-phase schedule): 0.165 vs 0.189 ms at 128 -> 256 channels
+    // and 56 x 56; 0.112 vs 0.115 ms at 64 -> 256; 0.113 vs 0.115 ms at 64 -> 512 and 28 x 28; 3 % slower at 32 input channels, where
+    // the layer is bound by HBM and the pair's common tile schedule costs more than the halved activation traffic saves.
+    if (g.Ci < 64) return false;
     // enough pixel blocks to give every SM at least one
     return (long long)g.Nb * ((g.H * g.W + 63) / 64) >= (long long)sm_count();
 }

@@ -154,6 +154,7 @@ PAIR_SHAPES = [
     (8, 128, 256, 56, 56),      # the benchmark layer at batch 8: several tiles per pair, image boundaries inside tiles
     (10, 104, 512, 28, 36),     # two channel pairs, ragged last K slice (104 = 3 x 32 + 8), 1008-pixel images (partial last block)
     (3, 96, 256, 56, 57),       # odd number of 64-pixel blocks in total: the last tile's second half is out of range
+    (8, 64, 256, 40, 40),       # two K slices per tile: half of the activation ring per tile, tiles alternate ring halves
 ]
 
 
