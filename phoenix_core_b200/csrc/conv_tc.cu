@@ -54,6 +54,8 @@ struct GParams {
                                  // padding when the caller's channels-last tensor is read in place (the padding is TMA zero fill)
     int o_generic;               // the output is addressed through the element strides below (channels-last tensors, channel
     int o_p, o_c, o_h, o_w;      // slices of grouped layers, boxes narrower than 8 pixels): one 16-bit store per element
+    int o_cl32;                  // channels-last output whose channel count is a multiple of 32: a warp transposes its 32 rows x 32
+                                 // columns through shared memory and stores 16-byte runs of channels
     int bias_ld;                 // bias is [components][bias_ld]
     int exact;                   // plane mode with a tile box of exactly PN whole planes (WO x HO x PN pixels, any plane size up to
                                  // 256 pixels): the MMAs are n_cols = PN * WO * HO rounded up to 16 columns wide
@@ -349,6 +351,31 @@ qconv_general_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_
                     const float f0 = __uint_as_float(v[2 * e]) + badd, f1 = __uint_as_float(v[2 * e + 1]) + badd;
                     if (p.fmt == 0) { const __half2 h = __floats2half2_rn(f0, f1); packed[e] = *reinterpret_cast<const uint32_t*>(&h); }
                     else { const __nv_bfloat162 h = __floats2bfloat162_rn(f0, f1); packed[e] = *reinterpret_cast<const uint32_t*>(&h); }
+                }
+                if (p.o_cl32) {
+                    // channels-last output, 32 consecutive channels per warp: the 32 x 32 block goes through 2 KB of shared memory
+                    // ([pixel][32 channels]) and leaves as 16-byte stores, 64 contiguous bytes per pixel (the strided path below
+                    // writes one 2-byte element per store instruction)
+                    const uint32_t tbuf = smem_u32(plane_buf) + (uint32_t)(warp - 2) * 2048u;
+                    __syncwarp();
+#pragma unroll
+                    for (int e = 0; e < 16; ++e) {
+                        st_shared_u16(tbuf + (2 * e) * 64 + lane * 2, (uint16_t)(packed[e] & 0xffffu));
+                        st_shared_u16(tbuf + (2 * e + 1) * 64 + lane * 2, (uint16_t)(packed[e] >> 16));
+                    }
+                    __syncwarp();
+                    const int row0 = tm * GM + q * 32, d0 = row0 / p.Cout, cch = row0 - d0 * p.Cout + (lane & 3) * 8;
+#pragma unroll
+                    for (int it = 0; it < 4; ++it) {
+                        const int px = it * 8 + (lane >> 2), je = col0 + px;
+                        if (je >= p.n_cols) continue;
+                        const int wl = je & (p.PW - 1), hl = p.lh >= 0 ? ((je >> p.lw) & (p.PH - 1)) : (je >> p.lw), nl = p.lh >= 0 ? (je >> (p.lw + p.lh)) : 0;
+                        const int ow = ow0 + wl, oh = oh0 + hl, img = n0 + nl;
+                        if (ow >= p.WO || oh >= p.HO || img >= p.Nb) continue;
+                        const uint4 val = ld_shared_v4(tbuf + px * 64 + (lane & 3) * 16);
+                        *reinterpret_cast<uint4*>(out + (size_t)(d0 * p.Nb + img) * p.o_p + (size_t)oh * p.o_h + (size_t)ow * p.o_w + cch) = val;
+                    }
+                    continue;
                 }
                 const bool wide = !p.o_generic && sv >= 16 && (p.PW % 16) == 0;
 #pragma unroll
@@ -1040,6 +1067,10 @@ int conv_tc_launch(Pass pass, int dtype, const Geom& g, const void* w, const voi
     }
     // Halo mode (see the kernel): stride-1 correlation, 32-channel slices, several taps, and an image tall enough for
     // tiles of 8 x PH >= 192 pixels (smaller tiles re-read the filter slices too often to gain anything).
+    // channels-last output with a multiple of 32 channels and 16-byte aligned pixels: the transposing epilogue (16 KB of shared memory)
+    const bool cl32 = !g.plain && so.c == 1 && pl.Cout % 32 == 0 && so.w % 8 == 0 && so.h % 8 == 0 && so.p % 8 == 0 &&
+                      (reinterpret_cast<uintptr_t>(out) & 15u) == 0;
+    constexpr int CL32_BYTES = 8 * 2048;
     bool halo = false;
     p.n_cols = 256; p.Wt = p.Ht = 0; p.n_stages = 0; p.stage_bytes = 0;
     if (pl.Cp % 32 == 0 && pl.SH == 1 && pl.SW == 1 && taps >= 4 && pl.Wout >= 8) {
@@ -1047,7 +1078,7 @@ int conv_tc_launch(Pass pass, int dtype, const Geom& g, const void* w, const voi
         const int ph = (((pl.Hout + rows - 1) / rows) + 1) & ~1;
         const int wt = 8 + (g.KW - 1) * g.DW, ht = ph + (g.KH - 1) * g.DH;
         const uint32_t stage = ((uint32_t)taps * GM * 32 * 2 + (uint32_t)wt * ht * 64 + 1023) / 1024 * 1024;
-        const int n_stages = (int)((227 * 1024 - 1024 - 512) / stage);
+        const int n_stages = (int)((227 * 1024 - 1024 - 512 - (cl32 ? CL32_BYTES : 0)) / stage);
         if (ph >= 24 && wt <= 256 && ht <= 256 && taps <= 256 && n_stages >= 2) {
             halo = true;
             p.PW = 8; p.PH = ph; p.PN = 1; p.n_cols = 8 * ph; p.Wt = wt; p.Ht = ht;
@@ -1061,6 +1092,7 @@ int conv_tc_launch(Pass pass, int dtype, const Geom& g, const void* w, const voi
     // plane mode (see the epilogue): whole output planes per tile, 128 rows = 128 consecutive channels of one component
     // strided output: anything but a dense NCHW tensor, and the narrow boxes of dense layers
     p.o_generic = (!g.plain || p.lw < 3) ? 1 : 0;
+    p.o_cl32 = (cl32 && p.o_generic && p.lw >= 0) ? 1 : 0;
     p.o_p = (int)so.p; p.o_c = (int)so.c; p.o_h = (int)so.h; p.o_w = (int)so.w;
     p.bias_ld = g.bias_ld;
     p.off_w = direct ? -pl.pad_left : 0; p.off_h = direct ? -pl.pad_top : 0;
@@ -1088,7 +1120,7 @@ int conv_tc_launch(Pass pass, int dtype, const Geom& g, const void* w, const voi
     p.b_tx = (uint32_t)(p.exact ? p.PW * p.PH * p.PN : GN) * (uint32_t)pl.KS * 2u;
     if (!halo) {
         const int max_stages = pl.KS == 64 ? 4 : (pl.KS == 32 ? 8 : 12);
-        const int fit = (int)((227 * 1024 - 1024 - 512 - (p.plane_mode ? G_PLANE_BYTES : 0)) / ((GM + GN) * pl.KS * 2));
+        const int fit = (int)((227 * 1024 - 1024 - 512 - (p.plane_mode ? G_PLANE_BYTES : (p.o_cl32 ? CL32_BYTES : 0))) / ((GM + GN) * pl.KS * 2));
         p.n_stages = fit < max_stages ? fit : max_stages;
     }
     p.Nb = g.Nb; p.Cout = pl.Cout; p.Mvalid = g.nc * pl.Cout; p.HO = pl.Hout; p.WO = pl.Wout; p.Cp = pl.Cp;
@@ -1131,19 +1163,19 @@ int conv_tc_launch(Pass pass, int dtype, const Geom& g, const void* w, const voi
     const int n_tiles = p.tiles_w * p.tiles_h * p.tiles_n * p.tiles_m;
     const int grid = n_tiles < sm_count() ? n_tiles : sm_count();
     if (halo) {
-        const size_t smem = 1024 + (size_t)p.n_stages * p.stage_bytes + 512;
+        const size_t smem = 1024 + (size_t)p.n_stages * p.stage_bytes + 512 + (p.o_cl32 ? CL32_BYTES : 0);
         PCB_CUDA_TRY(cudaFuncSetAttribute(qconv_general_tc_kernel<32, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
         qconv_general_tc_kernel<32, true><<<grid, G_THREADS, smem, stream>>>(map_w, map_x, p, (const uint16_t*)bias, (uint16_t*)out, status);
     } else if (pl.KS == 64) {
-        const size_t smem = 1024 + (size_t)p.n_stages * (GM + GN) * 64 * 2 + 512 + (p.plane_mode ? G_PLANE_BYTES : 0);
+        const size_t smem = 1024 + (size_t)p.n_stages * (GM + GN) * 64 * 2 + 512 + (p.plane_mode ? G_PLANE_BYTES : (p.o_cl32 ? CL32_BYTES : 0));
         PCB_CUDA_TRY(cudaFuncSetAttribute(qconv_general_tc_kernel<64, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
         qconv_general_tc_kernel<64, false><<<grid, G_THREADS, smem, stream>>>(map_w, map_x, p, (const uint16_t*)bias, (uint16_t*)out, status);
     } else if (pl.KS == 32) {
-        const size_t smem = 1024 + (size_t)p.n_stages * (GM + GN) * 32 * 2 + 512 + (p.plane_mode ? G_PLANE_BYTES : 0);
+        const size_t smem = 1024 + (size_t)p.n_stages * (GM + GN) * 32 * 2 + 512 + (p.plane_mode ? G_PLANE_BYTES : (p.o_cl32 ? CL32_BYTES : 0));
         PCB_CUDA_TRY(cudaFuncSetAttribute(qconv_general_tc_kernel<32, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
         qconv_general_tc_kernel<32, false><<<grid, G_THREADS, smem, stream>>>(map_w, map_x, p, (const uint16_t*)bias, (uint16_t*)out, status);
     } else {
-        const size_t smem = 1024 + (size_t)p.n_stages * (GM + GN) * 16 * 2 + 512 + (p.plane_mode ? G_PLANE_BYTES : 0);
+        const size_t smem = 1024 + (size_t)p.n_stages * (GM + GN) * 16 * 2 + 512 + (p.plane_mode ? G_PLANE_BYTES : (p.o_cl32 ? CL32_BYTES : 0));
         PCB_CUDA_TRY(cudaFuncSetAttribute(qconv_general_tc_kernel<16, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
         qconv_general_tc_kernel<16, false><<<grid, G_THREADS, smem, stream>>>(map_w, map_x, p, (const uint16_t*)bias, (uint16_t*)out, status);
     }

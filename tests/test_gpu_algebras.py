@@ -267,6 +267,7 @@ DIRECT_SHAPES = [
     (2, 64, 64, 14, 14, 3, (2, 2), (0, 0, 1, 1)),      # stride 2 through the element stride of the tensor map; backward-data staged
     (3, 16, 16, 9, 9, 1, (1, 1), (0, 0, 0, 0)),        # pointwise: a plain GEMM over [pixel][channel] rows
     (2, 128, 64, 8, 8, 5, (1, 1), (2, 2, 2, 2)),       # 25 taps, 64-channel slices
+    (2, 96, 96, 20, 12, 3, (1, 1), (1, 1, 1, 1)),      # 96 = 3 x 32 channels: the transposing channels-last epilogue over three row tiles
 ]
 
 
