@@ -194,6 +194,86 @@ maxpool_fwd_kernel(const T* __restrict__ x, T* __restrict__ y, uint8_t* __restri
     }
 }
 
+// The same pooling for lines of a multiple of 8 pixels (and a multiple of 4 outputs): one thread makes 4 consecutive outputs from
+// three 16-byte loads (the 8 input columns 2*ow0 .. 2*ow0 + 7 of each window line) and three single elements (column 2*ow0 - 1),
+// and writes them with one 8-byte store and one 4-byte store of arg-max positions. Same scan order inside a window as above.
+template <typename T>
+__global__ void __launch_bounds__(BN_THREADS)
+maxpool_fwd4_kernel(const T* __restrict__ x, T* __restrict__ y, uint8_t* __restrict__ arg, size_t rows, int H, int W, int HO, int WO) {
+    const int groups = WO / 4;
+    const size_t total = rows * HO * groups;
+    for (size_t idx = (size_t)blockIdx.x * blockDim.x + threadIdx.x; idx < total; idx += (size_t)gridDim.x * blockDim.x) {
+        const int g = (int)(idx % groups);
+        const int oh = (int)((idx / groups) % HO);
+        const size_t row = idx / ((size_t)groups * HO);
+        const T* src = x + row * H * W;
+        float best[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
+        int where[4] = {0, 0, 0, 0};
+#pragma unroll
+        for (int kh = 0; kh < 3; ++kh) {
+            const int ih = 2 * oh - 1 + kh;
+            if ((unsigned)ih >= (unsigned)H) continue;
+            float f[8];
+            VecIO<T, 8>::load(src + (size_t)ih * W + 8 * g, f);
+            const float left = g > 0 ? DType<T>::load(src + (size_t)ih * W + 8 * g - 1) : 0.f;
+#pragma unroll
+            for (int j = 0; j < 4; ++j) {
+#pragma unroll
+                for (int kw = 0; kw < 3; ++kw) {
+                    const int rel = 2 * j - 1 + kw;                 // column relative to 8 * g
+                    if (rel < 0 && g == 0) continue;                // left padding
+                    const float v = rel < 0 ? left : f[rel];
+                    if (v > best[j] || (v != v)) { best[j] = v; where[j] = kh * 3 + kw; }
+                }
+            }
+        }
+        const size_t o = (row * HO + oh) * WO + 4 * g;
+        VecIO<T, 4>::store(y + o, best);
+        *reinterpret_cast<uint32_t*>(arg + o) = (uint32_t)where[0] | ((uint32_t)where[1] << 8) | ((uint32_t)where[2] << 16) | ((uint32_t)where[3] << 24);
+    }
+}
+
+// Backward for the same line shapes: one thread per 8 input pixels reads, for each of its one or two output lines, the arg-max
+// bytes of windows 4g .. 4g + 3 as one 32-bit word and their gradients as one 8-byte load, plus window 4g + 4 on its own.
+template <typename T>
+__global__ void __launch_bounds__(BN_THREADS)
+maxpool_bwd8_kernel(const T* __restrict__ dy, const uint8_t* __restrict__ arg, T* __restrict__ dx, size_t rows, int H, int W, int HO, int WO) {
+    const int per_line = W / 8;
+    const size_t total = rows * H * per_line;
+    for (size_t idx = (size_t)blockIdx.x * blockDim.x + threadIdx.x; idx < total; idx += (size_t)gridDim.x * blockDim.x) {
+        const int g = (int)(idx % per_line), iw0 = 8 * g;
+        const int ih = (int)((idx / per_line) % H);
+        const size_t row = idx / ((size_t)per_line * H);
+        const size_t obase = row * HO * WO;
+        float acc[8];
+#pragma unroll
+        for (int e = 0; e < 8; ++e) acc[e] = 0.f;
+        for (int oh = ih >> 1; oh <= (ih + 1) >> 1; ++oh) {
+            if (oh >= HO) continue;
+            const int kh = ih - (2 * oh - 1);
+            const size_t o = obase + (size_t)oh * WO + 4 * g;
+            const uint32_t a4 = __ldg(reinterpret_cast<const uint32_t*>(arg + o));
+            float g4[4];
+            VecIO<T, 4>::load(dy + o, g4);
+#pragma unroll
+            for (int j = 0; j < 5; ++j) {
+                int a;
+                float gr;
+                if (j < 4) { a = (int)((a4 >> (8 * j)) & 0xffu); gr = g4[j]; }
+                else {
+                    if (4 * g + 4 >= WO) continue;
+                    a = arg[o + 4]; gr = DType<T>::load(dy + o + 4);
+                }
+                if (a / 3 != kh) continue;
+                const int e = 2 * j - 1 + a % 3;                   // position of the maximum relative to iw0 (window 4g + j)
+#pragma unroll
+                for (int q = 0; q < 8; ++q) if (q == e) acc[q] += gr;
+            }
+        }
+        VecIO<T, 8>::store(dx + (row * H + ih) * W + iw0, acc);
+    }
+}
+
 // One thread per (row, input line, V consecutive input pixels): the windows that can contain them are the V/2 + 1 output
 // columns from iw0/2 on and the one or two output lines around ih; their arg-max bytes and gradients are read once.
 template <typename T, int V>
@@ -329,6 +409,15 @@ int pcb_aux_maxpool3x3s2_fwd(int dtype, const void* x, void* y, void* argmax, in
     using namespace pcb;
     if (!x || !y || !argmax || rows <= 0 || h <= 0 || w <= 0) { set_error("invalid max-pool arguments"); return PCB_ERR_INVALID_ARGUMENT; }
     const int ho = (h - 1) / 2 + 1, wo = (w - 1) / 2 + 1;
+    const bool lines8 = w % 8 == 0 && wo % 4 == 0 && reinterpret_cast<uintptr_t>(x) % 16 == 0 && reinterpret_cast<uintptr_t>(y) % 8 == 0 &&
+                        reinterpret_cast<uintptr_t>(argmax) % 4 == 0;
+    if (lines8 && (dtype == PCB_F16 || dtype == PCB_BF16)) {
+        const int b4 = blocks_for((size_t)rows * ho * (wo / 4));
+        if (dtype == PCB_F16) maxpool_fwd4_kernel<__half><<<b4, BN_THREADS, 0, (cudaStream_t)stream>>>((const __half*)x, (__half*)y, (uint8_t*)argmax, rows, h, w, ho, wo);
+        else maxpool_fwd4_kernel<__nv_bfloat16><<<b4, BN_THREADS, 0, (cudaStream_t)stream>>>((const __nv_bfloat16*)x, (__nv_bfloat16*)y, (uint8_t*)argmax, rows, h, w, ho, wo);
+        PCB_CUDA_TRY(cudaGetLastError());
+        return PCB_OK;
+    }
     const int blocks = blocks_for((size_t)rows * ho * wo);
     if (dtype == PCB_F16) maxpool_fwd_kernel<__half><<<blocks, BN_THREADS, 0, (cudaStream_t)stream>>>((const __half*)x, (__half*)y, (uint8_t*)argmax, rows, h, w, ho, wo);
     else if (dtype == PCB_BF16) maxpool_fwd_kernel<__nv_bfloat16><<<blocks, BN_THREADS, 0, (cudaStream_t)stream>>>((const __nv_bfloat16*)x, (__nv_bfloat16*)y, (uint8_t*)argmax, rows, h, w, ho, wo);
@@ -345,6 +434,12 @@ int pcb_aux_maxpool3x3s2_bwd(int dtype, const void* dy, const void* argmax, void
     const bool wide = w % 8 == 0 && reinterpret_cast<uintptr_t>(dx) % 16 == 0;
     const int blocks = blocks_for((size_t)rows * h * (wide ? w / 8 : w));
     cudaStream_t st = (cudaStream_t)stream;
+    if (wide && wo % 4 == 0 && reinterpret_cast<uintptr_t>(dy) % 8 == 0 && reinterpret_cast<uintptr_t>(argmax) % 4 == 0) {
+        if (dtype == PCB_F16) maxpool_bwd8_kernel<__half><<<blocks, BN_THREADS, 0, st>>>((const __half*)dy, (const uint8_t*)argmax, (__half*)dx, rows, h, w, ho, wo);
+        else maxpool_bwd8_kernel<__nv_bfloat16><<<blocks, BN_THREADS, 0, st>>>((const __nv_bfloat16*)dy, (const uint8_t*)argmax, (__nv_bfloat16*)dx, rows, h, w, ho, wo);
+        PCB_CUDA_TRY(cudaGetLastError());
+        return PCB_OK;
+    }
     if (dtype == PCB_F16) {
         if (wide) maxpool_bwd_kernel<__half, 8><<<blocks, BN_THREADS, 0, st>>>((const __half*)dy, (const uint8_t*)argmax, (__half*)dx, rows, h, w, ho, wo);
         else maxpool_bwd_kernel<__half, 1><<<blocks, BN_THREADS, 0, st>>>((const __half*)dy, (const uint8_t*)argmax, (__half*)dx, rows, h, w, ho, wo);

@@ -47,7 +47,7 @@ def test_bn_relu_helpers(shape, dtype, relu):
     assert err(beta.grad, rdb) < tol
 
 
-@pytest.mark.parametrize("shape", [(8, 16, 12, 12), (4, 5, 9, 7), (2, 3, 16, 11)])
+@pytest.mark.parametrize("shape", [(8, 16, 12, 12), (4, 5, 9, 7), (2, 3, 16, 11), (2, 3, 16, 24), (1, 2, 112, 112), (3, 2, 9, 8)])
 @pytest.mark.parametrize("dtype", [torch.float16, torch.bfloat16])
 def test_maxpool_helpers(shape, dtype):
     if not torch.cuda.is_available():
