@@ -553,11 +553,13 @@ constexpr int PACK_TILE_MAX_TAPS = 9;     // 37 KB of shared memory at 9 taps
 // with one 16-byte store)
 __global__ void __launch_bounds__(256)
 pack_filters_tiled_kernel(const uint16_t* __restrict__ w, uint16_t* __restrict__ wexp, int Co, int Ci, int taps, int Mp, int Kp, int Cp, int transposed,
-                          int nc, int ga, unsigned long long neg, FilterStrides fs) {
+                          int nc, int ga, unsigned long long neg, FilterStrides fs, int tap_split) {
     extern __shared__ uint8_t pack_smem[];
     uint16_t* tile = reinterpret_cast<uint16_t*>(pack_smem);
     const int Cm = transposed ? Ci : Co, Ck = transposed ? Co : Ci;
-    const int ck0 = blockIdx.x * PACK_TK, cm0 = blockIdx.y * PACK_TM, r = blockIdx.z;
+    // small layers have few tiles: then blockIdx.z also splits the taps a block WRITES (every block still reads whole runs)
+    const int ck0 = blockIdx.x * PACK_TK, cm0 = blockIdx.y * PACK_TM, r = blockIdx.z / tap_split, tpart = blockIdx.z - r * tap_split;
+    const int taps_per = (taps + tap_split - 1) / tap_split, tap_beg = tpart * taps_per, tap_end = min(taps, tap_beg + taps_per);
     const int co0 = transposed ? ck0 : cm0, ci0 = transposed ? cm0 : ck0;
     const int n_co = transposed ? PACK_TK : PACK_TM, n_ci = transposed ? PACK_TM : PACK_TK;
     const int run = n_ci * taps;               // elements of the tile's input channels x all taps of one output channel
@@ -593,7 +595,7 @@ pack_filters_tiled_kernel(const uint16_t* __restrict__ w, uint16_t* __restrict__
         const uint32_t flip = alg_negative(neg, l, d) ? 0x80008000u : 0u;
         const int m_comp = transposed ? l : d, k_comp = transposed ? d : l;
         uint16_t* dst = wexp + ((size_t)m_comp * Cm + cm0 + cm) * Kp + (size_t)k_comp * Cp + ck;
-        for (int tap = 0; tap < taps; ++tap) {
+        for (int tap = tap_beg; tap < tap_end; ++tap) {
             const uint16_t* src = src0 + (transposed ? taps - 1 - tap : tap);
             uint32_t q[4];
 #pragma unroll
@@ -610,11 +612,13 @@ void pack_filters(const T* w, T* wexp, int Co, int Ci, int taps, int Mp, int Kp,
     const int Cm = transposed ? Ci : Co;
     const bool runs = fs.w == 1 && fs.h == fs.KW && fs.i == taps;
     if (runs && taps <= PACK_TILE_MAX_TAPS && Mp == nc * Cm && Cm >= PACK_TM && (reinterpret_cast<uintptr_t>(wexp) & 15u) == 0) {
-        const dim3 grid((Cp + PACK_TK - 1) / PACK_TK, (Cm + PACK_TM - 1) / PACK_TM, nc);
+        const int tiles = ((Cp + PACK_TK - 1) / PACK_TK) * ((Cm + PACK_TM - 1) / PACK_TM) * nc;
+        const int tap_split = tiles < sm_count() / 2 ? taps : 1;
+        const dim3 grid((Cp + PACK_TK - 1) / PACK_TK, (Cm + PACK_TM - 1) / PACK_TM, nc * tap_split);
         static_assert(sizeof(T) == 2, "the tiled kernel moves 16-bit elements");
         const size_t smem = (size_t)(transposed ? PACK_TK * (PACK_TM * taps + 2) : PACK_TM * (PACK_TK * taps + 2)) * 2;
         pack_filters_tiled_kernel<<<grid, 256, smem, stream>>>(reinterpret_cast<const uint16_t*>(w), reinterpret_cast<uint16_t*>(wexp), Co, Ci, taps, Mp,
-                                                              Kp, Cp, transposed, nc, ga, neg, fs);
+                                                              Kp, Cp, transposed, nc, ga, neg, fs, tap_split);
     } else {
         const dim3 wthreads(Cp >= 64 ? 64 : 32, Cp >= 64 ? 4 : 8);
         const int wblocks = grid_cap((size_t)taps * Mp, (int)wthreads.y, 32);
