@@ -143,6 +143,22 @@ int pcb_qconv2d_fwd(const pcb_conv2d_desc* desc, const void* x, const void* w, c
 int pcb_qconv2d_bwd(const pcb_conv2d_desc* desc, const void* x, const void* w, const void* dy, void* dw, void* dx,
                     void* workspace, size_t workspace_bytes, void* stream);
 
+/* Backward pass that reads the staged copy of x which the forward call of the same layer left in ITS workspace, instead
+ * of staging x again (not in the reference, whose cuDNN calls keep nothing between passes; a layer object that owns a
+ * workspace per layer, like the reference's per-operation objects of src/backend/cudnn/conv2d.hpp, is where it fits).
+ *
+ * pcb_qconv2d_fwd_keeps_input(desc) is nonzero when the forward kernel of this layer stages x in the layout its
+ * filter-gradient kernel reads (the 16-bit tensor-core kernels of non-pointwise NCHW layers with at most 64 channels).
+ * For such a layer give pcb_qconv2d_fwd a workspace of its own, leave it untouched, and pass it to pcb_qconv2d_bwd_kept
+ * as `fwd_workspace`, with the same x (same address, same values) and a different `workspace` for the backward pass, on
+ * the same stream (or ordered after the forward call). The library records, on the host, which x and problem each
+ * workspace last staged and forgets the record as soon as another call is given that workspace; when the record does
+ * not match (or the layer keeps nothing) the call stages x itself and is pcb_qconv2d_bwd. Results are identical either way. */
+int pcb_qconv2d_fwd_keeps_input(const pcb_conv2d_desc* desc);
+int pcb_qconv2d_bwd_kept(const pcb_conv2d_desc* desc, const void* x, const void* w, const void* dy, void* dw, void* dx,
+                         const void* fwd_workspace, size_t fwd_workspace_bytes, void* workspace, size_t workspace_bytes,
+                         void* stream);
+
 /* The two halves of the backward pass, individually (the shape sweep times them separately).
  * Same reference code as pcb_qconv2d_bwd. */
 int pcb_qconv2d_bwd_data(const pcb_conv2d_desc* desc, const void* w, const void* dy, void* dx,

@@ -8,10 +8,10 @@ from . import _lib
 from .descriptors import (Algebra, Conv2DBwdDescriptor, Conv2DFwdDescriptor, DataFormat, DenseBwdDescriptor,
                           DenseFwdDescriptor, FilterLayout, Padding, compute_windowed_output_size_and_padding)
 from .context import Context, ConvFp16ComputePolicy
-from .ops import conv2DBwd, conv2DFwd, denseBwd, denseFwd, getSmMargin, setSmMargin
+from .ops import KeptInput, conv2DBwd, conv2DFwd, denseBwd, denseFwd, getSmMargin, setSmMargin
 
 __all__ = [
     "Algebra", "Padding", "DataFormat", "FilterLayout", "Conv2DFwdDescriptor", "Conv2DBwdDescriptor",
     "DenseFwdDescriptor", "DenseBwdDescriptor", "compute_windowed_output_size_and_padding", "Context",
-    "ConvFp16ComputePolicy", "conv2DFwd", "conv2DBwd", "denseFwd", "denseBwd", "setSmMargin", "getSmMargin",
+    "ConvFp16ComputePolicy", "conv2DFwd", "conv2DBwd", "denseFwd", "denseBwd", "setSmMargin", "getSmMargin", "KeptInput",
 ]

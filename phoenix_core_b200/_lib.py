@@ -52,6 +52,8 @@ SYMBOLS = {
     "pcb_qdense_bwd_workspace_size": (_sz, [_dd]),
     "pcb_qconv2d_fwd": (_i, [_cd, _vp, _vp, _vp, _vp, _vp, _sz, _vp]),
     "pcb_qconv2d_bwd": (_i, [_cd, _vp, _vp, _vp, _vp, _vp, _vp, _sz, _vp]),
+    "pcb_qconv2d_fwd_keeps_input": (_i, [_cd]),
+    "pcb_qconv2d_bwd_kept": (_i, [_cd, _vp, _vp, _vp, _vp, _vp, _vp, _sz, _vp, _sz, _vp]),
     "pcb_qconv2d_bwd_data": (_i, [_cd, _vp, _vp, _vp, _vp, _sz, _vp]),
     "pcb_qconv2d_bwd_filter": (_i, [_cd, _vp, _vp, _vp, _vp, _sz, _vp]),
     "pcb_qconv2d_bwd_filter_noalloc": (_i, [_cd, _vp, _vp, _vp, _vp]),

@@ -3,6 +3,8 @@
 #include <cstdarg>
 #include <cstdio>
 #include <cstring>
+#include <mutex>
+#include <unordered_map>
 
 #include "common.cuh"
 #include "tensor_path.cuh"
@@ -114,6 +116,36 @@ int reset_status(void* workspace, size_t ws_bytes, cudaStream_t stream) {
     return PCB_OK;
 }
 
+// Staged inputs kept by forward calls, by workspace address (host-side bookkeeping; the data itself lives in that workspace).
+// A forward call that stages x in the layout its filter gradient reads records (x, problem signature) under its workspace;
+// every later call that is given the same workspace erases the record before it writes there. pcb_qconv2d_bwd_kept reads the
+// staged copy only when the record still matches its own x and problem, and stages x itself otherwise.
+struct KeptInput { const void* x; unsigned long long signature; };
+std::mutex g_kept_mutex;
+std::unordered_map<const void*, KeptInput> g_kept;
+
+unsigned long long problem_signature(int dtype, const Geom& g) {
+    const int v[] = {dtype, g.nc, g.ga, g.real_in, g.Nb, g.Ci, g.Co, g.H, g.W, g.KH, g.KW, g.SH, g.SW, g.DH, g.DW, g.PT, g.PL, g.HO, g.WO};
+    unsigned long long h = 1469598103934665603ull;                   // FNV-1a over the geometry
+    for (int x : v) { h ^= (unsigned long long)(unsigned)x; h *= 1099511628211ull; }
+    return h;
+}
+void forget_kept(const void* workspace) {
+    if (!workspace) return;
+    std::lock_guard<std::mutex> lock(g_kept_mutex);
+    g_kept.erase(workspace);
+}
+void remember_kept(const void* workspace, const void* x, unsigned long long signature) {
+    std::lock_guard<std::mutex> lock(g_kept_mutex);
+    if (g_kept.size() >= 4096) g_kept.clear();                       // bounded: callers that never run the backward pass
+    g_kept[workspace] = KeptInput{x, signature};
+}
+bool kept_matches(const void* workspace, const void* x, unsigned long long signature) {
+    std::lock_guard<std::mutex> lock(g_kept_mutex);
+    const auto it = g_kept.find(workspace);
+    return it != g_kept.end() && it->second.x == x && it->second.signature == signature;
+}
+
 size_t workspace_bytes(Pass pass, int dtype, int variant, int engine, const Geom& g) {
     size_t s = simt_scratch_bytes(pass, dtype, variant, g);
     const size_t t = tensor_scratch_bytes(pass, dtype, tensor_variant(variant, engine), engine, g);
@@ -122,7 +154,8 @@ size_t workspace_bytes(Pass pass, int dtype, int variant, int engine, const Geom
 }
 
 int run_pass(Pass pass, int dtype, int variant, int engine, const Geom& g, const void* a, const void* b, const void* bias,
-             void* out, void* workspace, size_t ws_bytes, cudaStream_t stream) {
+             void* out, void* workspace, size_t ws_bytes, cudaStream_t stream, const void* kept_x = nullptr) {
+    forget_kept(workspace);
     const size_t need = workspace_bytes(pass, dtype, variant, engine, g);
     const int tv = tensor_variant(variant, engine);
     const bool needs_ws = need > WS_HEADER || tensor_path_supported(pass, dtype, tv, g);
@@ -137,8 +170,11 @@ int run_pass(Pass pass, int dtype, int variant, int engine, const Geom& g, const
     // operands, strided stores), so there only the workspace has to be.
     const uintptr_t tensors = g.plain ? (reinterpret_cast<uintptr_t>(a) | reinterpret_cast<uintptr_t>(b) | reinterpret_cast<uintptr_t>(out)) : 0;
     const bool aligned = ((tensors | reinterpret_cast<uintptr_t>(workspace)) & 15u) == 0;
-    if (engine != PCB_ENGINE_SIMT && aligned && tensor_path_supported(pass, dtype, tv, g))
-        return tensor_launch(pass, dtype, tv, g, a, b, bias, out, scratch, status, stream);
+    if (engine != PCB_ENGINE_SIMT && aligned && tensor_path_supported(pass, dtype, tv, g)) {
+        const int rc = tensor_launch(pass, dtype, tv, g, a, b, bias, out, scratch, status, stream, kept_x);
+        if (rc == PCB_OK && pass == PASS_FWD && forward_keeps_staged_input(dtype, tv, g)) remember_kept(workspace, b, problem_signature(dtype, g));
+        return rc;
+    }
     if (engine == PCB_ENGINE_TENSOR) {
         set_error("no tensor-core kernel for this problem");
         return PCB_ERR_UNSUPPORTED;
@@ -160,8 +196,8 @@ size_t conv_workspace_bytes(Pass pass, int dtype, int variant, int engine, const
 }
 
 int run_conv_pass(Pass pass, int dtype, int variant, int engine, const Geom& g, const void* a, const void* b, const void* bias,
-                  void* out, void* workspace, size_t ws_bytes, cudaStream_t stream) {
-    if (g.groups == 1) return run_pass(pass, dtype, variant, engine, g, a, b, bias, out, workspace, ws_bytes, stream);
+                  void* out, void* workspace, size_t ws_bytes, cudaStream_t stream, const void* kept_x = nullptr) {
+    if (g.groups == 1) return run_pass(pass, dtype, variant, engine, g, a, b, bias, out, workspace, ws_bytes, stream, kept_x);
     const size_t es = dtype_size(dtype);
     const size_t need = conv_workspace_bytes(pass, dtype, variant, engine, g);
     if (need > WS_HEADER && (workspace == nullptr || ws_bytes < need)) {
@@ -233,7 +269,7 @@ int conv_bwd_data(const pcb_conv2d_desc* desc, const void* w, const void* dy, vo
 }
 
 int conv_bwd_filter(const pcb_conv2d_desc* desc, const void* x, const void* dy, void* dw,
-                    void* workspace, size_t workspace_bytes_, cudaStream_t stream) {
+                    void* workspace, size_t workspace_bytes_, cudaStream_t stream, const void* kept_x = nullptr) {
     Geom g;
     int rc = conv_geom(desc, g);
     if (rc != PCB_OK) return rc;
@@ -243,7 +279,7 @@ int conv_bwd_filter(const pcb_conv2d_desc* desc, const void* x, const void* dy, 
         return PCB_OK;
     }
     if (!x || !dy) { set_error("null tensor pointer"); return PCB_ERR_INVALID_ARGUMENT; }
-    return run_conv_pass(PASS_BWD_FILTER, desc->dtype, variant_for(g, desc->variant), desc->engine, g, dy, x, nullptr, dw, workspace, workspace_bytes_, stream);
+    return run_conv_pass(PASS_BWD_FILTER, desc->dtype, variant_for(g, desc->variant), desc->engine, g, dy, x, nullptr, dw, workspace, workspace_bytes_, stream, kept_x);
 }
 
 }  // namespace
@@ -357,6 +393,28 @@ int pcb_qconv2d_bwd(const pcb_conv2d_desc* desc, const void* x, const void* w, c
     int rc = reset_status(workspace, workspace_bytes_, (cudaStream_t)stream);
     if (rc != PCB_OK) return rc;
     rc = conv_bwd_filter(desc, x, dy, dw, workspace, workspace_bytes_, (cudaStream_t)stream);
+    if (rc != PCB_OK) return rc;
+    if (desc->require_input_grad && desc->n > 0) rc = conv_bwd_data(desc, w, dy, dx, workspace, workspace_bytes_, (cudaStream_t)stream);
+    return rc;
+}
+
+int pcb_qconv2d_fwd_keeps_input(const pcb_conv2d_desc* desc) {
+    Geom g;
+    if (conv_geom(desc, g) != PCB_OK || desc->engine == PCB_ENGINE_SIMT || g.Nb == 0) return 0;
+    return forward_keeps_staged_input(desc->dtype, tensor_variant(variant_for(g, desc->variant), desc->engine), g) ? 1 : 0;
+}
+
+int pcb_qconv2d_bwd_kept(const pcb_conv2d_desc* desc, const void* x, const void* w, const void* dy, void* dw, void* dx,
+                         const void* fwd_workspace, size_t fwd_workspace_bytes, void* workspace, size_t workspace_bytes_, void* stream) {
+    int rc = reset_status(workspace, workspace_bytes_, (cudaStream_t)stream);
+    if (rc != PCB_OK) return rc;
+    const void* kept_x = nullptr;
+    Geom g;
+    if (fwd_workspace && fwd_workspace != workspace && (reinterpret_cast<uintptr_t>(fwd_workspace) & 15u) == 0 && conv_geom(desc, g) == PCB_OK &&
+        pcb_qconv2d_fwd_keeps_input(desc) && fwd_workspace_bytes >= pcb_qconv2d_fwd_workspace_size(desc) &&
+        kept_matches(fwd_workspace, x, problem_signature(desc->dtype, g)))
+        kept_x = static_cast<const char*>(fwd_workspace) + WS_HEADER;
+    rc = conv_bwd_filter(desc, x, dy, dw, workspace, workspace_bytes_, (cudaStream_t)stream, kept_x);
     if (rc != PCB_OK) return rc;
     if (desc->require_input_grad && desc->n > 0) rc = conv_bwd_data(desc, w, dy, dx, workspace, workspace_bytes_, (cudaStream_t)stream);
     return rc;

@@ -1233,15 +1233,21 @@ size_t conv_filter_tc_scratch_bytes(const Geom& g) {
     return f.xp_bytes + f.dyp_bytes + f.acc_bytes;
 }
 
+bool conv_filter_tc_stages_like_forward(const Geom& g) {
+    const FilterPlan f = make_filter_plan(g);
+    return g.plain && channel_block(f.Cip) == f.Cip && f.xp_bytes == make_plan(PASS_FWD, g).xp_bytes;
+}
+
 int conv_filter_tc_launch(int dtype, const Geom& g, const void* dy, const void* x, void* dw, void* scratch, int* status,
-                          cudaStream_t stream) {
+                          cudaStream_t stream, const void* kept_x) {
     EncodeTiledFn encode = encode_fn();
     if (!encode) { set_error("cuTensorMapEncodeTiled is not available from the driver"); return PCB_ERR_CUDA; }
     const int fmt = dtype == PCB_F16 ? 0 : 1;
     const FilterPlan f = make_filter_plan(g);
     const int taps = g.KH * g.KW;
-    uint8_t* xp = static_cast<uint8_t*>(scratch);
-    uint8_t* dyp = xp + f.xp_bytes;
+    // with one channel block per component the staged x is the forward pass's: a copy it kept is read in place
+    uint8_t* xp = kept_x ? static_cast<uint8_t*>(const_cast<void*>(kept_x)) : static_cast<uint8_t*>(scratch);
+    uint8_t* dyp = static_cast<uint8_t*>(scratch) + f.xp_bytes;
     float* acc = reinterpret_cast<float*>(dyp + f.dyp_bytes);
 
     // A channels-last tensor with one channel block per component (16, 32 or 64 channels) already is the staged layout
@@ -1257,7 +1263,7 @@ int conv_filter_tc_launch(int dtype, const Geom& g, const void* dy, const void* 
         const int bx = (int)((tx + 255) / 256 < cap ? (tx + 255) / 256 : cap), by = (int)((ty + 255) / 256 < cap ? (ty + 255) / 256 : cap);
         (void)bx; (void)by;
         const SrcStrides sx = {g.xp, g.xc, g.xh, g.xw}, sy = {g.yp, g.yc, g.yh, g.yw};
-        if (!direct_x)
+        if (!direct_x && !kept_x)
             stage_activations(fmt, x, xp, lk * g.Nb, g.Ci, g.H, g.W, f.Hp, f.Wp, f.Cip, g.PT, g.PL, 1, 1, stream, channel_block(f.Cip), g.Nb, g.plain ? nullptr : &sx);
         if (!direct_dy)
             stage_activations(fmt, dy, dyp, g.nc * g.Nb, g.Co, g.HO, g.WO, g.HO, g.WO, f.Cop, 0, 0, 1, 1, stream, channel_block(f.Cop), g.Nb, g.plain ? nullptr : &sy);

@@ -642,12 +642,14 @@ size_t narrow_filter_tc_scratch_bytes(const Geom& g) {
     return f.xp_bytes + f.dyp_bytes + f.acc_bytes;
 }
 
-int narrow_filter_tc_launch(int dtype, const Geom& g, const void* dy, const void* x, void* dw, void* scratch, int* status, cudaStream_t stream) {
+int narrow_filter_tc_launch(int dtype, const Geom& g, const void* dy, const void* x, void* dw, void* scratch, int* status, cudaStream_t stream,
+                            const void* kept_x) {
     const int fmt = dtype == PCB_F16 ? 0 : 1;
     const NFPlan f = make_nfplan(g);
     const int taps = f.KHe * f.KWe;
-    uint8_t* xp = static_cast<uint8_t*>(scratch);
-    uint8_t* dyp = xp + f.xp_bytes;
+    // the forward pass of a narrow layer stages x exactly as this one does: a copy it kept is read in place
+    uint8_t* xp = kept_x ? static_cast<uint8_t*>(const_cast<void*>(kept_x)) : static_cast<uint8_t*>(scratch);
+    uint8_t* dyp = static_cast<uint8_t*>(scratch) + f.xp_bytes;
     float* acc = reinterpret_cast<float*>(dyp + f.dyp_bytes);
     {
         // x: padded planar copy (space-to-depth for the stride-2 stem); dy: planar copy rounded up to whole tiles
@@ -663,7 +665,7 @@ int narrow_filter_tc_launch(int dtype, const Geom& g, const void* dy, const void
                 else pack_planar_kernel<__nv_bfloat16><<<blocks, 256, 0, stream>>>((const __nv_bfloat16*)src, (__nv_bfloat16*)dst, planes_in, C, H, W, Hp, Wp, groups, pt, pleft, 1, 1, s2d);
             }
         };
-        stage(x, xp, f.LK * g.Nb, g.Ci, g.H, g.W, f.Hp, f.Wp, 2, g.PT, g.PL, f.s2d);
+        if (!kept_x) stage(x, xp, f.LK * g.Nb, g.Ci, g.H, g.W, f.Hp, f.Wp, 2, g.PT, g.PL, f.s2d);
         stage(dy, dyp, g.nc * g.Nb, g.Co, g.HO, g.WO, f.HOp, f.WOp, f.y_planes, 0, 0, 0);
         PCB_CUDA_TRY(cudaGetLastError());
         PCB_CUDA_TRY(cudaMemsetAsync(acc, 0, (size_t)g.nc * g.Co * f.Cie * taps * sizeof(float), stream));

@@ -681,8 +681,20 @@ size_t tensor_scratch_bytes(Pass pass, int dtype, int variant, int engine, const
     return 0;
 }
 
+bool forward_keeps_staged_input(int dtype, int variant, const Geom& g) {
+    if ((dtype != PCB_F16 && dtype != PCB_BF16) || variant != PCB_VARIANT_16_PRODUCT || !g.plain || g.groups != 1) return false;
+    if (g.KH * g.KW == 1) return false;             // pointwise layers read x in place (or a compacted copy of their own)
+    // the same order of preference as tensor_launch
+    if (pointwise_pair_tc_supported(PASS_FWD, dtype, variant, g) || pointwise_tc_supported(PASS_FWD, dtype, variant, g)) return false;
+    if (pointwise_filter_tc_supported(dtype, variant, g)) return false;
+    const bool narrow_fwd = narrow_tc_supported(PASS_FWD, dtype, variant, g), narrow_flt = narrow_filter_tc_supported(dtype, variant, g);
+    if (narrow_fwd || narrow_flt) return narrow_fwd && narrow_flt;
+    return conv_tc_supported(PASS_FWD, dtype, variant, g) && conv_filter_tc_supported(dtype, variant, g) && conv_filter_tc_stages_like_forward(g);
+}
+
 int tensor_launch(Pass pass, int dtype, int variant, const Geom& g, const void* a, const void* b, const void* bias,
-                  void* out, float* scratch, int* status, cudaStream_t stream) {
+                  void* out, float* scratch, int* status, cudaStream_t stream, const void* kept_x) {
+    if (kept_x && !(pass == PASS_BWD_FILTER && forward_keeps_staged_input(dtype, variant, g))) kept_x = nullptr;
     if (variant == PCB_VARIANT_8_PRODUCT) return pointwise8_tc_launch(pass, dtype, g, a, b, bias, out, scratch, status, stream);
     if (!g.plain) {
         if (pass == PASS_BWD_FILTER) return conv_filter_tc_launch(dtype, g, a, b, out, scratch, status, stream);
@@ -768,8 +780,8 @@ int tensor_launch(Pass pass, int dtype, int variant, const Geom& g, const void* 
     // accumulate in fp32 scratch, then cast once.
     if (scratch == nullptr) { set_error("backward-filter needs fp32 scratch"); return PCB_ERR_WORKSPACE; }
     if (pointwise_filter_tc_supported(dtype, PCB_VARIANT_16_PRODUCT, g)) return pointwise_filter_tc_launch(dtype, g, a, b, out, scratch, status, stream);
-    if (narrow_filter_tc_supported(dtype, PCB_VARIANT_16_PRODUCT, g)) return narrow_filter_tc_launch(dtype, g, a, b, out, scratch, status, stream);
-    if (conv_filter_tc_supported(dtype, PCB_VARIANT_16_PRODUCT, g)) return conv_filter_tc_launch(dtype, g, a, b, out, scratch, status, stream);
+    if (narrow_filter_tc_supported(dtype, PCB_VARIANT_16_PRODUCT, g)) return narrow_filter_tc_launch(dtype, g, a, b, out, scratch, status, stream, kept_x);
+    if (conv_filter_tc_supported(dtype, PCB_VARIANT_16_PRODUCT, g)) return conv_filter_tc_launch(dtype, g, a, b, out, scratch, status, stream, kept_x);
     const int tiles = ((p.M + TBM - 1) / TBM) * ((p.N + TBN - 1) / TBN);
     int splits = (2 * sm_count() + tiles - 1) / tiles;
     const int max_splits = (p.K + 4 * TBK - 1) / (4 * TBK);

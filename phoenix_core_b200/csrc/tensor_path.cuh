@@ -9,8 +9,13 @@ bool tensor_path_supported(Pass pass, int dtype, int variant, const Geom& g);
 // Scratch bytes (beyond the workspace header) the tensor-core kernel of this problem needs.
 size_t tensor_scratch_bytes(Pass pass, int dtype, int variant, int engine, const Geom& g);
 // Operand roles as for simt_launch. `status` is the device status word of the workspace header.
+// `kept_x` (filter gradient only): the staged copy of x that the forward call of the same layer left in ITS workspace
+// scratch (see forward_keeps_staged_input); the kernels that share that layout read it instead of staging x again.
 int tensor_launch(Pass pass, int dtype, int variant, const Geom& g, const void* a, const void* b, const void* bias,
-                  void* out, float* scratch, int* status, cudaStream_t stream);
+                  void* out, float* scratch, int* status, cudaStream_t stream, const void* kept_x = nullptr);
+// True when the forward pass of this layer stages x, at the start of its scratch, in exactly the layout its filter
+// gradient reads: a narrow forward with a narrow filter gradient, or the general pair with one channel block per component.
+bool forward_keeps_staged_input(int dtype, int variant, const Geom& g);
 
 // Persistent TMA-fed kernel for wide pointwise layers (forward and backward-data); see pointwise_tc.cu.
 bool pointwise_tc_supported(Pass pass, int dtype, int variant, const Geom& g);
@@ -43,7 +48,9 @@ int conv_tc_launch(Pass pass, int dtype, const Geom& g, const void* w, const voi
 bool conv_filter_tc_supported(int dtype, int variant, const Geom& g);
 size_t conv_filter_tc_scratch_bytes(const Geom& g);
 int conv_filter_tc_launch(int dtype, const Geom& g, const void* dy, const void* x, void* dw, void* scratch, int* status,
-                          cudaStream_t stream);
+                          cudaStream_t stream, const void* kept_x = nullptr);
+// The filter gradient stages x as [component][image][h][w][channels], the layout of the forward pass.
+bool conv_filter_tc_stages_like_forward(const Geom& g);
 
 // Narrow layers (<= 16 reduced channels, stride-1 correlation): halo tiles in shared memory serve every tap; see narrow_tc.cu.
 bool narrow_tc_supported(Pass pass, int dtype, int variant, const Geom& g);
@@ -53,7 +60,8 @@ int narrow_tc_launch(Pass pass, int dtype, const Geom& g, const void* w, const v
 
 bool narrow_filter_tc_supported(int dtype, int variant, const Geom& g);
 size_t narrow_filter_tc_scratch_bytes(const Geom& g);
-int narrow_filter_tc_launch(int dtype, const Geom& g, const void* dy, const void* x, void* dw, void* scratch, int* status, cudaStream_t stream);
+int narrow_filter_tc_launch(int dtype, const Geom& g, const void* dy, const void* x, void* dw, void* scratch, int* status, cudaStream_t stream,
+                            const void* kept_x = nullptr);
 
 // fp32 tensors on the tensor cores with error-compensated TF32 (convolution and dense); see conv_tf32.cu.
 bool conv_tf32_supported(Pass pass, int dtype, int variant, const Geom& g);

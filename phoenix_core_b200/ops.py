@@ -78,6 +78,16 @@ class Device:
         return self.context
 
 
+class KeptInput:
+    """Holds the workspace of one layer's forward call between that call and the layer's backward call, so that the
+    filter gradient reads the staged copy of x the forward kernel made instead of staging x again (not in the
+    reference). Pass one object per layer as ``keep=`` to ``conv2DFwd`` and as ``kept=`` to ``conv2DBwd``; for layers
+    whose kernels share no staged layout it stays empty and both calls behave as without it."""
+
+    def __init__(self):
+        self.workspace = None
+
+
 def setSmMargin(sms):
     """Leaves `sms` SMs free of the persistent tensor-core kernels from the next call on (process-wide), so that a kernel on
     another stream -- the all-reduce of a filter gradient beside backward-data -- finds SMs to run on. 0 restores the default."""
@@ -152,8 +162,10 @@ def _conv_desc(descriptor, dtype, context, engine, has_bias=False, require_input
     return d
 
 
-def conv2DFwd(inputTensor, filterTensor, biasTensor, outputTensor, descriptor, context=None, engine=_lib.ENGINE_AUTO):
-    """y = x (*) w [+ bias]; mirrors ``upstride::conv2DFwd`` (reference ``src/upstride.hpp:18-33``)."""
+def conv2DFwd(inputTensor, filterTensor, biasTensor, outputTensor, descriptor, context=None, engine=_lib.ENGINE_AUTO, keep=None):
+    """y = x (*) w [+ bias]; mirrors ``upstride::conv2DFwd`` (reference ``src/upstride.hpp:18-33``).
+
+    ``keep`` (not in the reference): a ``KeptInput``; see there."""
     dev = Device.get(inputTensor.device)
     context = context or dev.getContext()
     _check_tensor(inputTensor, "input", shape=descriptor.getInputShape())
@@ -169,19 +181,25 @@ def conv2DFwd(inputTensor, filterTensor, biasTensor, outputTensor, descriptor, c
     L = _lib.lib()
     with dev.accessControl, torch.cuda.device(dev.index):
         need = L.pcb_qconv2d_fwd_workspace_size(ctypes.byref(d))
-        ws = dev.requestWorkspace(need)
+        if keep is not None and L.pcb_qconv2d_fwd_keeps_input(ctypes.byref(d)):
+            if keep.workspace is None or keep.workspace.numel() < need or keep.workspace.device != inputTensor.device:
+                keep.workspace = torch.empty(need, dtype=torch.uint8, device=inputTensor.device)
+            ws = keep.workspace
+        else:
+            ws = dev.requestWorkspace(need)
         _lib.check(L.pcb_qconv2d_fwd(ctypes.byref(d), _ptr(inputTensor), _ptr(filterTensor), _ptr(biasTensor),
                                      _ptr(outputTensor), _ptr(ws), ws.numel(), _stream()))
         dev._after_op()
 
 
 def conv2DBwd(inputTensor, filterTensor, gradTensor, filterGradTensor, inputGradTensor, descriptor, context=None,
-              engine=_lib.ENGINE_AUTO, on_filter_grad=None):
+              engine=_lib.ENGINE_AUTO, on_filter_grad=None, kept=None):
     """dW (always) and dX (when the descriptor requires it); mirrors ``upstride::conv2DBwd``
     (reference ``src/upstride.hpp:35-51``).
 
     ``on_filter_grad`` (not in the reference): a callable invoked after the filter gradient has been enqueued and
-    before backward-data is, e.g. to start its all-reduce on another stream so that it overlaps backward-data."""
+    before backward-data is, e.g. to start its all-reduce on another stream so that it overlaps backward-data.
+    ``kept`` (not in the reference): the ``KeptInput`` given to this layer's forward call."""
     dev = Device.get(filterTensor.device)
     context = context or dev.getContext()
     _check_tensor(inputTensor, "input", shape=descriptor.getInputShape())
@@ -201,7 +219,11 @@ def conv2DBwd(inputTensor, filterTensor, gradTensor, filterGradTensor, inputGrad
     with dev.accessControl, torch.cuda.device(dev.index):
         need = L.pcb_qconv2d_bwd_workspace_size(ctypes.byref(d))
         ws = dev.requestWorkspace(need)
-        if on_filter_grad is None:
+        if kept is not None and kept.workspace is not None and on_filter_grad is None:
+            _lib.check(L.pcb_qconv2d_bwd_kept(ctypes.byref(d), _ptr(inputTensor), _ptr(filterTensor), _ptr(gradTensor),
+                                              _ptr(filterGradTensor), _ptr(inputGradTensor) if need_dx else None,
+                                              _ptr(kept.workspace), kept.workspace.numel(), _ptr(ws), ws.numel(), _stream()))
+        elif on_filter_grad is None:
             _lib.check(L.pcb_qconv2d_bwd(ctypes.byref(d), _ptr(inputTensor), _ptr(filterTensor), _ptr(gradTensor),
                                          _ptr(filterGradTensor), _ptr(inputGradTensor) if need_dx else None,
                                          _ptr(ws), ws.numel(), _stream()))
