@@ -228,6 +228,13 @@ int pcb_aux_bn_relu_fwd(int dtype, const void* x, const float* gamma, const floa
 int pcb_aux_bn_relu_bwd(int dtype, const void* x, const void* y, const void* dy, const float* gamma, const float* mean,
                         const float* invstd, void* dx, float* dgamma, float* dbeta, float* scratch, int planes, int channels,
                         int hw, int relu, void* stream);
+/* The tail of a residual block in one pass: y = relu(batch_norm(x) + residual); the backward call also writes the gradient
+ * of the residual branch, dresidual = dy masked by y > 0 (the same masked gradient enters the batch-norm gradient). */
+int pcb_aux_bn_add_relu_fwd(int dtype, const void* x, const void* residual, const float* gamma, const float* beta, void* y,
+                            float* mean, float* invstd, float* scratch, int planes, int channels, int hw, float eps, void* stream);
+int pcb_aux_bn_add_relu_bwd(int dtype, const void* x, const void* y, const void* dy, const float* gamma, const float* mean,
+                            const float* invstd, void* dx, void* dresidual, float* dgamma, float* dbeta, float* scratch, int planes,
+                            int channels, int hw, void* stream);
 /* 3x3 stride-2 pad-1 max pooling of `rows` planes of h x w 16-bit elements (output ((h-1)/2+1) x ((w-1)/2+1)); `argmax`
  * holds one byte per output element for the backward pass, which gathers without atomics. Harness glue as above. */
 int pcb_aux_maxpool3x3s2_fwd(int dtype, const void* x, void* y, void* argmax, int rows, int h, int w, void* stream);

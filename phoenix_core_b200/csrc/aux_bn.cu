@@ -131,11 +131,12 @@ __global__ void bn_bwd_finalize_kernel(const float* __restrict__ sums, const flo
     coef[c] = a; coef[C + c] = b; coef[2 * C + c] = -a * sg / count - b * mu;
 }
 
-// MODE 0: y = max(x*coef0 + coef1, 0 if relu).  MODE 1: dx = coef0*g + coef1*x + coef2 with g = dy masked by y > 0.
+// MODE 0: y = max(x*coef0 + coef1 [+ res], 0 if relu).  MODE 1: dx = coef0*g + coef1*x + coef2 with g = dy masked by y > 0
+// [and dres = g: the gradient of the residual branch that was added before the ReLU].
 template <typename T, int MODE, int V>
 __global__ void __launch_bounds__(BN_THREADS)
 bn_apply_kernel(const T* __restrict__ x, const T* __restrict__ y, const T* __restrict__ dy, T* __restrict__ out, const float* __restrict__ coef,
-                size_t rows, int C, int HW, int relu) {
+                size_t rows, int C, int HW, int relu, const T* __restrict__ res, T* __restrict__ dres) {
     const int per_row = HW / V;
     const size_t total = rows * per_row;
     for (size_t idx = (size_t)blockIdx.x * blockDim.x + threadIdx.x; idx < total; idx += (size_t)gridDim.x * blockDim.x) {
@@ -147,8 +148,10 @@ bn_apply_kernel(const T* __restrict__ x, const T* __restrict__ y, const T* __res
         float fx[V], fo[V];
         VecIO<T, V>::load(x + off, fx);
         if (MODE == 0) {
+            float fr[V];
+            if (res) VecIO<T, V>::load(res + off, fr);
 #pragma unroll
-            for (int e = 0; e < V; ++e) { const float v = fmaf(fx[e], k0, k1); fo[e] = relu ? fmaxf(v, 0.f) : v; }
+            for (int e = 0; e < V; ++e) { const float v = fmaf(fx[e], k0, k1) + (res ? fr[e] : 0.f); fo[e] = relu ? fmaxf(v, 0.f) : v; }
         } else {
             float fg[V], fy[V];
             VecIO<T, V>::load(dy + off, fg);
@@ -157,7 +160,9 @@ bn_apply_kernel(const T* __restrict__ x, const T* __restrict__ y, const T* __res
             for (int e = 0; e < V; ++e) {
                 const float g = (relu && !(fy[e] > 0.f)) ? 0.f : fg[e];
                 fo[e] = fmaf(k0, g, fmaf(k1, fx[e], k2));
+                fg[e] = g;
             }
+            if (dres) VecIO<T, V>::store(dres + off, fg);
         }
         VecIO<T, V>::store(out + off, fo);
     }
@@ -327,7 +332,7 @@ int vec_width(int HW, uintptr_t ptr_bits) {
 
 template <typename T, int MODE, int V>
 void bn_launch(const T* x, const T* y, const T* dy, T* out, float* scratch, float* coef, int planes, int C, int HW, int relu, bool sums,
-               cudaStream_t stream) {
+               cudaStream_t stream, const T* res, T* dres) {
     if (sums) {
         int S = (8 * 148 + C - 1) / C;
         if (S > planes) S = planes;
@@ -335,41 +340,41 @@ void bn_launch(const T* x, const T* y, const T* dy, T* out, float* scratch, floa
         bn_sums_kernel<T, MODE, V><<<dim3(C, S), BN_THREADS, 0, stream>>>(x, y, dy, scratch, planes, C, HW, relu);
     } else {
         const size_t rows = (size_t)planes * C;
-        bn_apply_kernel<T, MODE, V><<<blocks_for(rows * (HW / V)), BN_THREADS, 0, stream>>>(x, y, dy, out, coef, rows, C, HW, relu);
+        bn_apply_kernel<T, MODE, V><<<blocks_for(rows * (HW / V)), BN_THREADS, 0, stream>>>(x, y, dy, out, coef, rows, C, HW, relu, res, dres);
     }
 }
 
 template <typename T, int MODE>
 void bn_dispatch(int V, const T* x, const T* y, const T* dy, T* out, float* scratch, float* coef, int planes, int C, int HW, int relu, bool sums,
-                 cudaStream_t stream) {
-    if (V == 8) bn_launch<T, MODE, 8>(x, y, dy, out, scratch, coef, planes, C, HW, relu, sums, stream);
-    else if (V == 4) bn_launch<T, MODE, 4>(x, y, dy, out, scratch, coef, planes, C, HW, relu, sums, stream);
-    else bn_launch<T, MODE, 1>(x, y, dy, out, scratch, coef, planes, C, HW, relu, sums, stream);
+                 cudaStream_t stream, const T* res = nullptr, T* dres = nullptr) {
+    if (V == 8) bn_launch<T, MODE, 8>(x, y, dy, out, scratch, coef, planes, C, HW, relu, sums, stream, res, dres);
+    else if (V == 4) bn_launch<T, MODE, 4>(x, y, dy, out, scratch, coef, planes, C, HW, relu, sums, stream, res, dres);
+    else bn_launch<T, MODE, 1>(x, y, dy, out, scratch, coef, planes, C, HW, relu, sums, stream, res, dres);
 }
 
 template <typename T>
 int bn_fwd_typed(const T* x, const float* gamma, const float* beta, T* y, float* mean, float* invstd, float* scratch, int planes, int C, int HW,
-                 float eps, int relu, cudaStream_t stream) {
-    const int V = vec_width(HW, reinterpret_cast<uintptr_t>(x) | reinterpret_cast<uintptr_t>(y));
+                 float eps, int relu, cudaStream_t stream, const T* res = nullptr) {
+    const int V = vec_width(HW, reinterpret_cast<uintptr_t>(x) | reinterpret_cast<uintptr_t>(y) | reinterpret_cast<uintptr_t>(res));
     PCB_CUDA_TRY(cudaMemsetAsync(scratch, 0, 2 * C * sizeof(float), stream));
     float* coef = scratch + 2 * C;
     bn_dispatch<T, 0>(V, x, nullptr, nullptr, nullptr, scratch, coef, planes, C, HW, 0, true, stream);
     bn_fwd_finalize_kernel<<<(C + 127) / 128, 128, 0, stream>>>(scratch, gamma, beta, mean, invstd, coef, C, (float)planes * HW, eps);
-    bn_dispatch<T, 0>(V, x, nullptr, nullptr, y, scratch, coef, planes, C, HW, relu, false, stream);
+    bn_dispatch<T, 0>(V, x, nullptr, nullptr, y, scratch, coef, planes, C, HW, relu, false, stream, res, nullptr);
     PCB_CUDA_TRY(cudaGetLastError());
     return PCB_OK;
 }
 
 template <typename T>
 int bn_bwd_typed(const T* x, const T* y, const T* dy, const float* gamma, const float* mean, const float* invstd, T* dx, float* dgamma, float* dbeta,
-                 float* scratch, int planes, int C, int HW, int relu, cudaStream_t stream) {
+                 float* scratch, int planes, int C, int HW, int relu, cudaStream_t stream, T* dres = nullptr) {
     const int V = vec_width(HW, reinterpret_cast<uintptr_t>(x) | reinterpret_cast<uintptr_t>(dy) | reinterpret_cast<uintptr_t>(dx) |
-                                    (relu ? reinterpret_cast<uintptr_t>(y) : 0));
+                                    reinterpret_cast<uintptr_t>(dres) | (relu ? reinterpret_cast<uintptr_t>(y) : 0));
     PCB_CUDA_TRY(cudaMemsetAsync(scratch, 0, 2 * C * sizeof(float), stream));
     float* coef = scratch + 2 * C;
     bn_dispatch<T, 1>(V, x, y, dy, nullptr, scratch, coef, planes, C, HW, relu, true, stream);
     bn_bwd_finalize_kernel<<<(C + 127) / 128, 128, 0, stream>>>(scratch, gamma, mean, invstd, dgamma, dbeta, coef, C, (float)planes * HW);
-    bn_dispatch<T, 1>(V, x, y, dy, dx, scratch, coef, planes, C, HW, relu, false, stream);
+    bn_dispatch<T, 1>(V, x, y, dy, dx, scratch, coef, planes, C, HW, relu, false, stream, nullptr, dres);
     PCB_CUDA_TRY(cudaGetLastError());
     return PCB_OK;
 }
@@ -401,6 +406,32 @@ int pcb_aux_bn_relu_bwd(int dtype, const void* x, const void* y, const void* dy,
     }
     if (dtype == PCB_F16) return bn_bwd_typed<__half>((const __half*)x, (const __half*)y, (const __half*)dy, gamma, mean, invstd, (__half*)dx, dgamma, dbeta, scratch, planes, channels, hw, relu, (cudaStream_t)stream);
     if (dtype == PCB_BF16) return bn_bwd_typed<__nv_bfloat16>((const __nv_bfloat16*)x, (const __nv_bfloat16*)y, (const __nv_bfloat16*)dy, gamma, mean, invstd, (__nv_bfloat16*)dx, dgamma, dbeta, scratch, planes, channels, hw, relu, (cudaStream_t)stream);
+    set_error("batch-norm helper: 16-bit tensors only");
+    return PCB_ERR_UNSUPPORTED;
+}
+
+int pcb_aux_bn_add_relu_fwd(int dtype, const void* x, const void* residual, const float* gamma, const float* beta, void* y, float* mean, float* invstd,
+                            float* scratch, int planes, int channels, int hw, float eps, void* stream) {
+    using namespace pcb;
+    if (!x || !residual || !gamma || !beta || !y || !mean || !invstd || !scratch || planes <= 0 || channels <= 0 || hw <= 0) {
+        set_error("invalid batch-norm arguments");
+        return PCB_ERR_INVALID_ARGUMENT;
+    }
+    if (dtype == PCB_F16) return bn_fwd_typed<__half>((const __half*)x, gamma, beta, (__half*)y, mean, invstd, scratch, planes, channels, hw, eps, 1, (cudaStream_t)stream, (const __half*)residual);
+    if (dtype == PCB_BF16) return bn_fwd_typed<__nv_bfloat16>((const __nv_bfloat16*)x, gamma, beta, (__nv_bfloat16*)y, mean, invstd, scratch, planes, channels, hw, eps, 1, (cudaStream_t)stream, (const __nv_bfloat16*)residual);
+    set_error("batch-norm helper: 16-bit tensors only");
+    return PCB_ERR_UNSUPPORTED;
+}
+
+int pcb_aux_bn_add_relu_bwd(int dtype, const void* x, const void* y, const void* dy, const float* gamma, const float* mean, const float* invstd, void* dx,
+                            void* dresidual, float* dgamma, float* dbeta, float* scratch, int planes, int channels, int hw, void* stream) {
+    using namespace pcb;
+    if (!x || !y || !dy || !gamma || !mean || !invstd || !dx || !dresidual || !dgamma || !dbeta || !scratch || planes <= 0 || channels <= 0 || hw <= 0) {
+        set_error("invalid batch-norm arguments");
+        return PCB_ERR_INVALID_ARGUMENT;
+    }
+    if (dtype == PCB_F16) return bn_bwd_typed<__half>((const __half*)x, (const __half*)y, (const __half*)dy, gamma, mean, invstd, (__half*)dx, dgamma, dbeta, scratch, planes, channels, hw, 1, (cudaStream_t)stream, (__half*)dresidual);
+    if (dtype == PCB_BF16) return bn_bwd_typed<__nv_bfloat16>((const __nv_bfloat16*)x, (const __nv_bfloat16*)y, (const __nv_bfloat16*)dy, gamma, mean, invstd, (__nv_bfloat16*)dx, dgamma, dbeta, scratch, planes, channels, hw, 1, (cudaStream_t)stream, (__nv_bfloat16*)dresidual);
     set_error("batch-norm helper: 16-bit tensors only");
     return PCB_ERR_UNSUPPORTED;
 }

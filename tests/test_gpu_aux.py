@@ -47,6 +47,43 @@ def test_bn_relu_helpers(shape, dtype, relu):
     assert err(beta.grad, rdb) < tol
 
 
+@pytest.mark.parametrize("shape", [(8, 16, 12, 12), (12, 5, 7, 7), (4, 64, 14, 14), (16, 3, 6, 10)])
+@pytest.mark.parametrize("dtype", [torch.float16, torch.bfloat16])
+def test_bn_add_relu_helper(shape, dtype):
+    """relu(batch_norm(x) + residual) in the batch-norm's own passes, and its three gradients, against float64."""
+    if not torch.cuda.is_available():
+        pytest.skip("no CUDA device")
+    from phoenix_core_b200.qresnet import BNReLU
+    g = torch.Generator().manual_seed(6)
+    x = (torch.randn(shape, generator=g) * 1.5 + 0.3).to(dtype).cuda()
+    res = torch.randn(shape, generator=g).to(dtype).cuda()
+    dy = torch.randn(shape, generator=g).to(dtype).cuda()
+    bn = BNReLU(shape[1], torch.device("cuda"), relu=False)
+    with torch.no_grad():
+        bn.weight.copy_((torch.rand(shape[1], generator=g) + 0.5).cuda())
+        bn.bias.copy_((torch.randn(shape[1], generator=g) * 0.2).cuda())
+    xin, rin = x.clone().requires_grad_(True), res.clone().requires_grad_(True)
+    y = bn.add_relu(xin, rin)
+    y.backward(dy)
+
+    xr, rr = x.cpu().double().requires_grad_(True), res.cpu().double().requires_grad_(True)
+    gr, br = bn.weight.detach().cpu().double().requires_grad_(True), bn.bias.detach().cpu().double().requires_grad_(True)
+    mean = xr.mean(dim=(0, 2, 3), keepdim=True)
+    var = xr.var(dim=(0, 2, 3), unbiased=False, keepdim=True)
+    yr = ((xr - mean) / torch.sqrt(var + 1e-5) * gr.view(1, -1, 1, 1) + br.view(1, -1, 1, 1) + rr).clamp_min(0)
+    yr.backward(dy.cpu().double())
+
+    def err(a, b):
+        return float((a.detach().cpu().double() - b).abs().max() / b.abs().max().clamp_min(1e-12))
+
+    assert err(y, yr.detach()) < 2e-2
+    # the mask of the float64 formulation is taken from its own output; outputs within rounding of zero may differ
+    assert err(xin.grad, xr.grad) < 5e-2
+    assert err(rin.grad, rr.grad) < 5e-2 or float(((rin.grad.cpu().double() - rr.grad).abs() > 1e-2).double().mean()) < 2e-3
+    assert err(bn.weight.grad, gr.grad) < 2e-2
+    assert err(bn.bias.grad, br.grad) < 2e-2
+
+
 @pytest.mark.parametrize("shape", [(8, 16, 12, 12), (4, 5, 9, 7), (2, 3, 16, 11), (2, 3, 16, 24), (1, 2, 112, 112), (3, 2, 9, 8)])
 @pytest.mark.parametrize("dtype", [torch.float16, torch.bfloat16])
 def test_maxpool_helpers(shape, dtype):
