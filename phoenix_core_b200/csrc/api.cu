@@ -154,16 +154,17 @@ size_t workspace_bytes(Pass pass, int dtype, int variant, int engine, const Geom
 }
 
 int run_pass(Pass pass, int dtype, int variant, int engine, const Geom& g, const void* a, const void* b, const void* bias,
-             void* out, void* workspace, size_t ws_bytes, cudaStream_t stream, const void* kept_x = nullptr) {
+             void* out, void* workspace, size_t ws_bytes, cudaStream_t stream, const PassExtras* extras = nullptr) {
     forget_kept(workspace);
-    const size_t need = workspace_bytes(pass, dtype, variant, engine, g);
+    const size_t offset = extras ? extras->scratch_offset : 0;       // scratch another pass of the same call still needs
+    const size_t need = workspace_bytes(pass, dtype, variant, engine, g) + offset;
     const int tv = tensor_variant(variant, engine);
     const bool needs_ws = need > WS_HEADER || tensor_path_supported(pass, dtype, tv, g);
     if (needs_ws && (workspace == nullptr || ws_bytes < need)) {
         set_error("workspace of %zu bytes required, %zu given", need, workspace ? ws_bytes : (size_t)0);
         return PCB_ERR_WORKSPACE;
     }
-    float* scratch = workspace ? reinterpret_cast<float*>(static_cast<char*>(workspace) + WS_HEADER) : nullptr;
+    float* scratch = workspace ? reinterpret_cast<float*>(static_cast<char*>(workspace) + WS_HEADER + offset) : nullptr;
     int* status = static_cast<int*>(workspace);
     // the tensor-core kernels move 16-byte chunks of NCHW / OIHW tensors: every tensor (and the workspace) must be 16-byte
     // aligned. Tensors of other layouts and the channel slices of grouped layers are addressed element by element (staged
@@ -171,7 +172,7 @@ int run_pass(Pass pass, int dtype, int variant, int engine, const Geom& g, const
     const uintptr_t tensors = g.plain ? (reinterpret_cast<uintptr_t>(a) | reinterpret_cast<uintptr_t>(b) | reinterpret_cast<uintptr_t>(out)) : 0;
     const bool aligned = ((tensors | reinterpret_cast<uintptr_t>(workspace)) & 15u) == 0;
     if (engine != PCB_ENGINE_SIMT && aligned && tensor_path_supported(pass, dtype, tv, g)) {
-        const int rc = tensor_launch(pass, dtype, tv, g, a, b, bias, out, scratch, status, stream, kept_x);
+        const int rc = tensor_launch(pass, dtype, tv, g, a, b, bias, out, scratch, status, stream, extras);
         if (rc == PCB_OK && pass == PASS_FWD && forward_keeps_staged_input(dtype, tv, g)) remember_kept(workspace, b, problem_signature(dtype, g));
         return rc;
     }
@@ -196,8 +197,8 @@ size_t conv_workspace_bytes(Pass pass, int dtype, int variant, int engine, const
 }
 
 int run_conv_pass(Pass pass, int dtype, int variant, int engine, const Geom& g, const void* a, const void* b, const void* bias,
-                  void* out, void* workspace, size_t ws_bytes, cudaStream_t stream, const void* kept_x = nullptr) {
-    if (g.groups == 1) return run_pass(pass, dtype, variant, engine, g, a, b, bias, out, workspace, ws_bytes, stream, kept_x);
+                  void* out, void* workspace, size_t ws_bytes, cudaStream_t stream, const PassExtras* extras = nullptr) {
+    if (g.groups == 1) return run_pass(pass, dtype, variant, engine, g, a, b, bias, out, workspace, ws_bytes, stream, extras);
     const size_t es = dtype_size(dtype);
     const size_t need = conv_workspace_bytes(pass, dtype, variant, engine, g);
     if (need > WS_HEADER && (workspace == nullptr || ws_bytes < need)) {
@@ -269,7 +270,7 @@ int conv_bwd_data(const pcb_conv2d_desc* desc, const void* w, const void* dy, vo
 }
 
 int conv_bwd_filter(const pcb_conv2d_desc* desc, const void* x, const void* dy, void* dw,
-                    void* workspace, size_t workspace_bytes_, cudaStream_t stream, const void* kept_x = nullptr) {
+                    void* workspace, size_t workspace_bytes_, cudaStream_t stream, const PassExtras* extras = nullptr) {
     Geom g;
     int rc = conv_geom(desc, g);
     if (rc != PCB_OK) return rc;
@@ -279,7 +280,46 @@ int conv_bwd_filter(const pcb_conv2d_desc* desc, const void* x, const void* dy, 
         return PCB_OK;
     }
     if (!x || !dy) { set_error("null tensor pointer"); return PCB_ERR_INVALID_ARGUMENT; }
-    return run_conv_pass(PASS_BWD_FILTER, desc->dtype, variant_for(g, desc->variant), desc->engine, g, dy, x, nullptr, dw, workspace, workspace_bytes_, stream, kept_x);
+    return run_conv_pass(PASS_BWD_FILTER, desc->dtype, variant_for(g, desc->variant), desc->engine, g, dy, x, nullptr, dw, workspace, workspace_bytes_, stream, extras);
+}
+
+// Staged dy shared by the two gradients of one call: the padded copy that backward-data makes at the start of the scratch
+// stays where it is, and the filter gradient -- run second, its own scratch placed behind that copy -- reads it through a
+// tensor map instead of staging dy again. Applies to 16-bit stride-1 tapped layers whose two kernels agree on the layout.
+bool bwd_shares_dy(const pcb_conv2d_desc* desc, const Geom& g, StagedView* view, size_t* offset) {
+    if (desc->engine == PCB_ENGINE_SIMT || !desc->require_input_grad || g.Nb == 0 || g.groups != 1) return false;
+    size_t bytes = 0;
+    if (!backward_shares_staged_dy(desc->dtype, tensor_variant(variant_for(g, desc->variant), desc->engine), g, view, &bytes)) return false;
+    *offset = (bytes + 1023) / 1024 * 1024;
+    return true;
+}
+
+// dw and dx of one call. `kept_x`: see pcb_qconv2d_bwd_kept.
+int conv_bwd_both(const pcb_conv2d_desc* desc, const void* x, const void* w, const void* dy, void* dw, void* dx,
+                  void* workspace, size_t workspace_bytes_, cudaStream_t stream, const void* kept_x) {
+    Geom g;
+    int rc = conv_geom(desc, g);
+    if (rc != PCB_OK) return rc;
+    PassExtras extras;
+    extras.kept_x = kept_x;
+    StagedView view;
+    size_t offset = 0;
+    const uintptr_t all = reinterpret_cast<uintptr_t>(x) | reinterpret_cast<uintptr_t>(w) | reinterpret_cast<uintptr_t>(dy) |
+                          reinterpret_cast<uintptr_t>(dw) | reinterpret_cast<uintptr_t>(dx) | reinterpret_cast<uintptr_t>(workspace);
+    if (x && w && dy && dw && dx && workspace && (all & 15u) == 0 && bwd_shares_dy(desc, g, &view, &offset) &&
+        workspace_bytes_ >= conv_workspace_bytes(PASS_BWD_FILTER, desc->dtype, variant_for(g, desc->variant), desc->engine, g) + offset) {
+        // backward-data first: it leaves the padded dy in [WS_HEADER, WS_HEADER + offset)
+        rc = conv_bwd_data(desc, w, dy, dx, workspace, workspace_bytes_, stream);
+        if (rc != PCB_OK) return rc;
+        view.base = static_cast<const char*>(workspace) + WS_HEADER;
+        extras.dy = view;
+        extras.scratch_offset = offset;
+        return conv_bwd_filter(desc, x, dy, dw, workspace, workspace_bytes_, stream, &extras);
+    }
+    rc = conv_bwd_filter(desc, x, dy, dw, workspace, workspace_bytes_, stream, &extras);
+    if (rc != PCB_OK) return rc;
+    if (desc->require_input_grad && desc->n > 0) rc = conv_bwd_data(desc, w, dy, dx, workspace, workspace_bytes_, stream);
+    return rc;
 }
 
 }  // namespace
@@ -333,7 +373,10 @@ size_t pcb_qconv2d_bwd_workspace_size(const pcb_conv2d_desc* desc) {
     Geom g;
     if (conv_geom(desc, g) != PCB_OK) return 0;
     const size_t a = conv_workspace_bytes(PASS_BWD_DATA, desc->dtype, variant_for(g, desc->variant), desc->engine, g);
-    const size_t b = conv_workspace_bytes(PASS_BWD_FILTER, desc->dtype, variant_for(g, desc->variant), desc->engine, g);
+    size_t b = conv_workspace_bytes(PASS_BWD_FILTER, desc->dtype, variant_for(g, desc->variant), desc->engine, g);
+    StagedView view;
+    size_t offset = 0;
+    if (bwd_shares_dy(desc, g, &view, &offset)) b += offset;          // the filter gradient's scratch lies behind the shared copy of dy
     return a > b ? a : b;
 }
 
@@ -390,12 +433,9 @@ int pcb_qconv2d_bwd_filter_noalloc(const pcb_conv2d_desc* desc, const void* x, c
 
 int pcb_qconv2d_bwd(const pcb_conv2d_desc* desc, const void* x, const void* w, const void* dy, void* dw, void* dx,
                     void* workspace, size_t workspace_bytes_, void* stream) {
-    int rc = reset_status(workspace, workspace_bytes_, (cudaStream_t)stream);
+    const int rc = reset_status(workspace, workspace_bytes_, (cudaStream_t)stream);
     if (rc != PCB_OK) return rc;
-    rc = conv_bwd_filter(desc, x, dy, dw, workspace, workspace_bytes_, (cudaStream_t)stream);
-    if (rc != PCB_OK) return rc;
-    if (desc->require_input_grad && desc->n > 0) rc = conv_bwd_data(desc, w, dy, dx, workspace, workspace_bytes_, (cudaStream_t)stream);
-    return rc;
+    return conv_bwd_both(desc, x, w, dy, dw, dx, workspace, workspace_bytes_, (cudaStream_t)stream, nullptr);
 }
 
 int pcb_qconv2d_fwd_keeps_input(const pcb_conv2d_desc* desc) {
@@ -414,10 +454,7 @@ int pcb_qconv2d_bwd_kept(const pcb_conv2d_desc* desc, const void* x, const void*
         pcb_qconv2d_fwd_keeps_input(desc) && fwd_workspace_bytes >= pcb_qconv2d_fwd_workspace_size(desc) &&
         kept_matches(fwd_workspace, x, problem_signature(desc->dtype, g)))
         kept_x = static_cast<const char*>(fwd_workspace) + WS_HEADER;
-    rc = conv_bwd_filter(desc, x, dy, dw, workspace, workspace_bytes_, (cudaStream_t)stream, kept_x);
-    if (rc != PCB_OK) return rc;
-    if (desc->require_input_grad && desc->n > 0) rc = conv_bwd_data(desc, w, dy, dx, workspace, workspace_bytes_, (cudaStream_t)stream);
-    return rc;
+    return conv_bwd_both(desc, x, w, dy, dw, dx, workspace, workspace_bytes_, (cudaStream_t)stream, kept_x);
 }
 
 int pcb_qdense_fwd(const pcb_dense_desc* desc, const void* x, const void* w, const void* bias, void* y,

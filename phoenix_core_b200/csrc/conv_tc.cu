@@ -1238,8 +1238,19 @@ bool conv_filter_tc_stages_like_forward(const Geom& g) {
     return g.plain && channel_block(f.Cip) == f.Cip && f.xp_bytes == make_plan(PASS_FWD, g).xp_bytes;
 }
 
+bool conv_tc_staged_dy_view(const Geom& g, StagedView* view, size_t* bytes) {
+    if (!g.plain || g.SH != 1 || g.SW != 1) return false;       // strided layers: backward-data reads a zero-inserted copy
+    const FilterPlan f = make_filter_plan(g);
+    if (channel_block(f.Cop) != f.Cop) return false;            // the filter gradient would block the channels
+    const Plan pl = make_plan(PASS_BWD_DATA, g);
+    if (pl.Cp != f.Cop || pl.pad_top < 0 || pl.pad_left < 0) return false;
+    view->Hp = pl.Hp; view->Wp = pl.Wp; view->pad_top = pl.pad_top; view->pad_left = pl.pad_left;
+    *bytes = pl.xp_bytes;
+    return true;
+}
+
 int conv_filter_tc_launch(int dtype, const Geom& g, const void* dy, const void* x, void* dw, void* scratch, int* status,
-                          cudaStream_t stream, const void* kept_x) {
+                          cudaStream_t stream, const void* kept_x, const StagedView* kept_dy) {
     EncodeTiledFn encode = encode_fn();
     if (!encode) { set_error("cuTensorMapEncodeTiled is not available from the driver"); return PCB_ERR_CUDA; }
     const int fmt = dtype == PCB_F16 ? 0 : 1;
@@ -1265,7 +1276,7 @@ int conv_filter_tc_launch(int dtype, const Geom& g, const void* dy, const void* 
         const SrcStrides sx = {g.xp, g.xc, g.xh, g.xw}, sy = {g.yp, g.yc, g.yh, g.yw};
         if (!direct_x && !kept_x)
             stage_activations(fmt, x, xp, lk * g.Nb, g.Ci, g.H, g.W, f.Hp, f.Wp, f.Cip, g.PT, g.PL, 1, 1, stream, channel_block(f.Cip), g.Nb, g.plain ? nullptr : &sx);
-        if (!direct_dy)
+        if (!direct_dy && !kept_dy)
             stage_activations(fmt, dy, dyp, g.nc * g.Nb, g.Co, g.HO, g.WO, g.HO, g.WO, f.Cop, 0, 0, 1, 1, stream, channel_block(f.Cop), g.Nb, g.plain ? nullptr : &sy);
         PCB_CUDA_TRY(cudaGetLastError());
         PCB_CUDA_TRY(cudaMemsetAsync(acc, 0, (size_t)g.nc * g.Co * g.Ci * taps * sizeof(float), stream));
@@ -1309,11 +1320,19 @@ int conv_filter_tc_launch(int dtype, const Geom& g, const void* dy, const void* 
     // the number of channel blocks one tile takes (blocks past the end read as zeros)
     {
         const cuuint64_t dims[5] = {(cuuint64_t)p.cbA, (cuuint64_t)g.WO, (cuuint64_t)g.HO, (cuuint64_t)g.Nb, (cuuint64_t)(g.nc * (f.Cop / p.cbA))};
-        const cuuint64_t strides[4] = {(cuuint64_t)p.cbA * 2, (cuuint64_t)g.WO * p.cbA * 2, (cuuint64_t)g.HO * g.WO * p.cbA * 2,
-                                       (cuuint64_t)g.Nb * g.HO * g.WO * p.cbA * 2};
+        cuuint64_t strides[4] = {(cuuint64_t)p.cbA * 2, (cuuint64_t)g.WO * p.cbA * 2, (cuuint64_t)g.HO * g.WO * p.cbA * 2,
+                                 (cuuint64_t)g.Nb * g.HO * g.WO * p.cbA * 2};
+        void* dy_base = direct_dy ? const_cast<void*>(dy) : static_cast<void*>(dyp);
+        if (kept_dy) {
+            // the copy backward-data staged: [d][img][Hp][Wp][Cop] with pixel (0, 0) at (pad_top, pad_left); the map covers the
+            // HO x WO pixels only, so the padding is never read and pixels past the end read as zeros, as in the compact copy
+            const size_t px = (size_t)f.Cop * 2, plane = (size_t)kept_dy->Hp * kept_dy->Wp * px;
+            strides[0] = px; strides[1] = (cuuint64_t)kept_dy->Wp * px; strides[2] = plane; strides[3] = (cuuint64_t)g.Nb * plane;
+            dy_base = static_cast<uint8_t*>(const_cast<void*>(kept_dy->base)) + ((size_t)kept_dy->pad_top * kept_dy->Wp + kept_dy->pad_left) * px;
+        }
         const cuuint32_t box[5] = {(cuuint32_t)p.cbA, (cuuint32_t)p.PW, (cuuint32_t)p.PH, (cuuint32_t)p.PN, (cuuint32_t)(xmajor ? g.nc : GM / p.cbA)};
         const cuuint32_t es[5] = {1, 1, 1, 1, 1};
-        const CUresult r = encode(&map_dy, dt, 5, direct_dy ? const_cast<void*>(dy) : static_cast<void*>(dyp), dims, strides, box, es, CU_TENSOR_MAP_INTERLEAVE_NONE, swz(p.cbA),
+        const CUresult r = encode(&map_dy, dt, 5, dy_base, dims, strides, box, es, CU_TENSOR_MAP_INTERLEAVE_NONE, swz(p.cbA),
                                   CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
         if (r != CUDA_SUCCESS) { set_error("cuTensorMapEncodeTiled (dy) failed with code %d", (int)r); return PCB_ERR_CUDA; }
     }

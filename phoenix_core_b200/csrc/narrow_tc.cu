@@ -642,8 +642,16 @@ size_t narrow_filter_tc_scratch_bytes(const Geom& g) {
     return f.xp_bytes + f.dyp_bytes + f.acc_bytes;
 }
 
+bool narrow_tc_staged_dy_view(const Geom& g, StagedView* view, size_t* bytes) {
+    if (g.SH != 1 || g.SW != 1) return false;                   // strided layers: backward-data reads a zero-inserted copy
+    const NPlan pl = make_nplan(PASS_BWD_DATA, g);
+    view->Hp = pl.Hp; view->Wp = pl.Wp; view->pad_top = pl.pad_top; view->pad_left = pl.pad_left;
+    *bytes = pl.xp_bytes;
+    return pl.pad_top >= 0 && pl.pad_left >= 0;
+}
+
 int narrow_filter_tc_launch(int dtype, const Geom& g, const void* dy, const void* x, void* dw, void* scratch, int* status, cudaStream_t stream,
-                            const void* kept_x) {
+                            const void* kept_x, const StagedView* kept_dy) {
     const int fmt = dtype == PCB_F16 ? 0 : 1;
     const NFPlan f = make_nfplan(g);
     const int taps = f.KHe * f.KWe;
@@ -666,7 +674,7 @@ int narrow_filter_tc_launch(int dtype, const Geom& g, const void* dy, const void
             }
         };
         if (!kept_x) stage(x, xp, f.LK * g.Nb, g.Ci, g.H, g.W, f.Hp, f.Wp, 2, g.PT, g.PL, f.s2d);
-        stage(dy, dyp, g.nc * g.Nb, g.Co, g.HO, g.WO, f.HOp, f.WOp, f.y_planes, 0, 0, 0);
+        if (!kept_dy) stage(dy, dyp, g.nc * g.Nb, g.Co, g.HO, g.WO, f.HOp, f.WOp, f.y_planes, 0, 0, 0);
         PCB_CUDA_TRY(cudaGetLastError());
         PCB_CUDA_TRY(cudaMemsetAsync(acc, 0, (size_t)g.nc * g.Co * f.Cie * taps * sizeof(float), stream));
     }
@@ -690,7 +698,18 @@ int narrow_filter_tc_launch(int dtype, const Geom& g, const void* dy, const void
         const cuuint64_t strides[4] = {(cuuint64_t)f.WOp * 16, (cuuint64_t)f.HOp * f.WOp * 16, (cuuint64_t)f.y_planes * f.HOp * f.WOp * 16,
                                        (cuuint64_t)g.Nb * f.y_planes * f.HOp * f.WOp * 16};
         const cuuint32_t box[5] = {64, (cuuint32_t)f.PH, (cuuint32_t)f.y_planes, 1, (cuuint32_t)g.nc};
-        const int rc = make_tensor_map(&map_dy, dt, dyp, 5, dims, strides, box, nullptr, CU_TENSOR_MAP_SWIZZLE_NONE, "narrow dy");
+        int rc;
+        if (kept_dy) {
+            // the copy backward-data staged: [d][img][2 planes][Hp][Wp][8] with pixel (0, 0) at (pad_top, pad_left); only the
+            // HO x WO pixels are inside the map, so whatever a tile box takes beyond them reads as zeros
+            const size_t plane = (size_t)kept_dy->Hp * kept_dy->Wp * 16;
+            const cuuint64_t kdims[5] = {(cuuint64_t)g.WO * 8, (cuuint64_t)g.HO, (cuuint64_t)f.y_planes, (cuuint64_t)g.Nb, (cuuint64_t)g.nc};
+            const cuuint64_t kstrides[4] = {(cuuint64_t)kept_dy->Wp * 16, plane, 2 * plane, (cuuint64_t)g.Nb * 2 * plane};
+            uint8_t* origin = static_cast<uint8_t*>(const_cast<void*>(kept_dy->base)) + ((size_t)kept_dy->pad_top * kept_dy->Wp + kept_dy->pad_left) * 16;
+            rc = make_tensor_map(&map_dy, dt, origin, 5, kdims, kstrides, box, nullptr, CU_TENSOR_MAP_SWIZZLE_NONE, "narrow dy (shared)");
+        } else {
+            rc = make_tensor_map(&map_dy, dt, dyp, 5, dims, strides, box, nullptr, CU_TENSOR_MAP_SWIZZLE_NONE, "narrow dy");
+        }
         if (rc != PCB_OK) return rc;
     }
     {   // xp[l][img][plane][Hp][Wp][8]; box = the halo tile of all components

@@ -692,9 +692,26 @@ bool forward_keeps_staged_input(int dtype, int variant, const Geom& g) {
     return conv_tc_supported(PASS_FWD, dtype, variant, g) && conv_filter_tc_supported(dtype, variant, g) && conv_filter_tc_stages_like_forward(g);
 }
 
+bool backward_shares_staged_dy(int dtype, int variant, const Geom& g, StagedView* view, size_t* bytes) {
+    if ((dtype != PCB_F16 && dtype != PCB_BF16) || variant != PCB_VARIANT_16_PRODUCT || !g.plain || g.groups != 1 || g.real_in) return false;
+    if (g.KH * g.KW == 1 || g.SH != 1 || g.SW != 1) return false;
+    // the same order of preference as tensor_launch, for both passes
+    if (pointwise_filter_tc_supported(dtype, variant, g)) return false;
+    const bool narrow_dat = narrow_tc_supported(PASS_BWD_DATA, dtype, variant, g), narrow_flt = narrow_filter_tc_supported(dtype, variant, g);
+    if (narrow_dat || narrow_flt) return narrow_dat && narrow_flt && narrow_tc_staged_dy_view(g, view, bytes);
+    return conv_tc_supported(PASS_BWD_DATA, dtype, variant, g) && conv_filter_tc_supported(dtype, variant, g) && conv_tc_staged_dy_view(g, view, bytes);
+}
+
 int tensor_launch(Pass pass, int dtype, int variant, const Geom& g, const void* a, const void* b, const void* bias,
-                  void* out, float* scratch, int* status, cudaStream_t stream, const void* kept_x) {
+                  void* out, float* scratch, int* status, cudaStream_t stream, const PassExtras* extras) {
+    const void* kept_x = extras ? extras->kept_x : nullptr;
+    const StagedView* kept_dy = (extras && extras->dy.base) ? &extras->dy : nullptr;
     if (kept_x && !(pass == PASS_BWD_FILTER && forward_keeps_staged_input(dtype, variant, g))) kept_x = nullptr;
+    if (kept_dy) {
+        StagedView v;
+        size_t bytes;
+        if (!(pass == PASS_BWD_FILTER && backward_shares_staged_dy(dtype, variant, g, &v, &bytes))) kept_dy = nullptr;
+    }
     if (variant == PCB_VARIANT_8_PRODUCT) return pointwise8_tc_launch(pass, dtype, g, a, b, bias, out, scratch, status, stream);
     if (!g.plain) {
         if (pass == PASS_BWD_FILTER) return conv_filter_tc_launch(dtype, g, a, b, out, scratch, status, stream);
@@ -780,8 +797,8 @@ int tensor_launch(Pass pass, int dtype, int variant, const Geom& g, const void* 
     // accumulate in fp32 scratch, then cast once.
     if (scratch == nullptr) { set_error("backward-filter needs fp32 scratch"); return PCB_ERR_WORKSPACE; }
     if (pointwise_filter_tc_supported(dtype, PCB_VARIANT_16_PRODUCT, g)) return pointwise_filter_tc_launch(dtype, g, a, b, out, scratch, status, stream);
-    if (narrow_filter_tc_supported(dtype, PCB_VARIANT_16_PRODUCT, g)) return narrow_filter_tc_launch(dtype, g, a, b, out, scratch, status, stream, kept_x);
-    if (conv_filter_tc_supported(dtype, PCB_VARIANT_16_PRODUCT, g)) return conv_filter_tc_launch(dtype, g, a, b, out, scratch, status, stream, kept_x);
+    if (narrow_filter_tc_supported(dtype, PCB_VARIANT_16_PRODUCT, g)) return narrow_filter_tc_launch(dtype, g, a, b, out, scratch, status, stream, kept_x, kept_dy);
+    if (conv_filter_tc_supported(dtype, PCB_VARIANT_16_PRODUCT, g)) return conv_filter_tc_launch(dtype, g, a, b, out, scratch, status, stream, kept_x, kept_dy);
     const int tiles = ((p.M + TBM - 1) / TBM) * ((p.N + TBN - 1) / TBN);
     int splits = (2 * sm_count() + tiles - 1) / tiles;
     const int max_splits = (p.K + 4 * TBK - 1) / (4 * TBK);

@@ -160,3 +160,51 @@ def test_fp32_and_simt_keep_nothing(gpu):
     assert L.pcb_qconv2d_fwd_keeps_input(ctypes.byref(ops._conv_desc(fwd, torch.float16, ctx, _lib.ENGINE_AUTO))) == 1
     assert L.pcb_qconv2d_fwd_keeps_input(ctypes.byref(ops._conv_desc(fwd, torch.float32, ctx, _lib.ENGINE_AUTO))) == 0
     assert L.pcb_qconv2d_fwd_keeps_input(ctypes.byref(ops._conv_desc(fwd, torch.float16, ctx, _lib.ENGINE_SIMT))) == 0
+
+
+# ---- dy staged once for both gradients of one backward call -------------------------------------------------
+# n, ci, co, h, w, k, dilation, pad
+SHARED_DY_SHAPES = [
+    (3, 16, 16, 24, 24, 3, 1, (1, 1, 1, 1)),     # narrow pair
+    (2, 8, 24, 17, 19, 3, 1, (1, 1, 1, 1)),      # narrow pair, ragged planes, three planes of dy rows
+    (2, 16, 8, 20, 16, 3, 1, (0, 0, 0, 0)),      # narrow pair without padding (the copy of dy is padded by two), one plane of dy
+    (2, 32, 32, 14, 14, 3, 1, (1, 1, 1, 1)),     # general pair
+    (2, 32, 64, 13, 11, 5, 1, (2, 2, 2, 2)),     # general pair, 25 taps, ragged
+    (2, 64, 32, 12, 12, 3, 2, (2, 2, 2, 2)),     # dilation 2
+    (2, 32, 32, 12, 12, 3, 1, (0, 1, 2, 0)),     # asymmetric padding
+    (1, 64, 32, 30, 21, 3, 1, (1, 1, 1, 1)),     # backward-data in halo mode
+    (2, 32, 48, 9, 9, 3, 1, (1, 1, 1, 1)),       # 48 = 3 x 16 output channels: blocked dy, nothing shared
+    (2, 32, 32, 14, 14, 3, 1, (1, 1, 1, 1)),     # (again, for bf16 below)
+]
+
+
+@pytest.mark.parametrize("dtype", ["f16", "bf16"])
+@pytest.mark.parametrize("shape", SHARED_DY_SHAPES[:-1])
+def test_backward_call_with_one_staged_dy_vs_oracle_and_vs_the_separate_passes(gpu, oracle, shape, dtype):
+    """pcb_qconv2d_bwd stages dy once (backward-data's padded copy, read by the filter gradient through a tensor map)
+    where the two kernels agree on the layout; the separate entry points stage it twice. Both against the oracle, and
+    against each other (dx bit for bit)."""
+    import torch
+    import phoenix_core_b200 as pcb
+    n, ci, co, h, w_, k, dil, pad = shape
+    x = gpu.rounded(normal(31, (4 * n, ci, h, w_)), dtype)
+    w = gpu.rounded(normal(32, (4, co, ci, k, k), std=(2.0 / (4 * ci * k * k)) ** 0.5), dtype)
+    _, bwd = gpu.conv_descriptors(x.shape, w.shape, (1, 1), pad, False, True, dilation=(dil, dil))
+    fwd, _ = gpu.conv_descriptors(x.shape, w.shape, (1, 1), pad, False, False, dilation=(dil, dil))
+    dy = gpu.rounded(normal(33, fwd.getOutputShape(), std=0.25), dtype)
+    rdw, rdx = oracle.conv2d_bwd(x, w, dy, (1, 1), (dil, dil), pad)
+    ctx, td = gpu.context("16p"), gpu.TORCH_DTYPES[dtype]
+    xd, wd, gd = gpu.dev(x, dtype), gpu.dev(w, dtype), gpu.dev(dy, dtype)
+    out = {}
+    for mode in ("one call", "separate passes"):
+        dw = torch.full(w.shape, float("nan"), dtype=td, device="cuda")
+        dx = torch.full(x.shape, float("nan"), dtype=td, device="cuda")
+        pcb.conv2DBwd(xd, wd, gd, dw, dx, bwd, ctx, on_filter_grad=(None if mode == "one call" else (lambda t: None)))
+        out[mode] = (gpu.host(dw), gpu.host(dx))
+        assert np.all(np.isfinite(out[mode][0])) and np.all(np.isfinite(out[mode][1])), mode
+        assert rel_err(out[mode][0], rdw) <= gpu.TOL[dtype], mode
+        assert rel_err(out[mode][1], rdx) <= gpu.TOL[dtype], mode
+    assert np.array_equal(out["one call"][1], out["separate passes"][1])
+    # same kernel, same staged values; the split-K atomic additions may land in another order, which can move a result by
+    # one unit in the last place of the storage type
+    assert rel_err(out["one call"][0], out["separate passes"][0]) <= (2e-3 if dtype == "f16" else 1e-2)
