@@ -298,6 +298,10 @@ __global__ void pack_filters_planar_kernel(const T* __restrict__ w, T* __restric
 // tiles; its accumulators stay in TMEM for the whole range and are folded into fp32 scratch at the end.
 // M is always 128: with fewer (d, plane) chunks than 16 the upper rows multiply whatever follows the dy tile in
 // shared memory and are never read back.
+// Folded form (p.fold = KW > 1): an MMA costs about the same whether it is 16 or 128 columns wide, so the kw taps of one
+// filter row become columns of ONE MMA. The x tensor map gets the tap as a dimension of its own with a stride of one pixel
+// (16 bytes) over the same staged copy -- overlapping views -- so that one box brings the tile shifted by every kw:
+// [kw][l][plane][Ht][8 px][8], planes at one uniform pitch, N = KW * LK * 16 columns, one MMA per filter row and 16 pixels.
 // ===================================================================================================
 constexpr int NF_STAGES = 2;
 
@@ -307,6 +311,7 @@ struct NFParams {
     int KH, KW, DH, DW;
     int PH, Wt, Ht, tiles_w, tiles_h;
     int LK, taps, taps_per_group, n_groups;
+    int fold, LKr;                       // kw taps folded into the columns of one MMA (1 = none); components of x
     int y_planes;                        // 8-channel planes of dy per component
     int steps_total, steps_per_split;
     int fmt;
@@ -355,7 +360,8 @@ qconv_narrow_filter_tc_kernel(const __grid_constant__ CUtensorMap map_dy, const 
                 const uint32_t dst = tiles_addr + s * p.stage_bytes, bar = full_bar + 8 * s;
                 mbar_arrive_expect_tx(bar, p.y_bytes + p.x_bytes);
                 tma_load_5d(dst, &map_dy, tw * 64, th * p.PH, 0, img, 0, bar);                 // [d][plane][PH][8 px][8]
-                tma_load_5d(dst + p.y_bytes, &map_x, tw * 64, th * p.PH, 0, img, 0, bar);      // [l][plane][Ht][Wt][8]
+                if (p.fold > 1) tma_load_5d(dst + p.y_bytes, &map_x, tw * 64, th * p.PH, img * 2, 0, 0, bar);   // [kw][l][plane][Ht][8][8]
+                else tma_load_5d(dst + p.y_bytes, &map_x, tw * 64, th * p.PH, 0, img, 0, bar);                  // [l][plane][Ht][Wt][8]
                 if (++tw == p.tiles_w) { tw = 0; if (++th == p.tiles_h) { th = 0; ++img; } }
             }
         }
@@ -396,13 +402,13 @@ qconv_narrow_filter_tc_kernel(const __grid_constant__ CUtensorMap map_dy, const 
             const bool row_ok = d < p.nc && co < p.Co;
             const size_t comp_stride = (size_t)p.Co * p.Ci;
             for (int tl = tsel; tl < n_taps; tl += 2) {
-                float* tap_base = dw32 + (size_t)(tap0 + tl) * p.nc * comp_stride;
-                for (int c0 = 0; c0 < ncols; c0 += 16) {                // 16 columns = the channels of one input component
+                for (int c0 = 0; c0 < ncols; c0 += 16) {                // 16 columns = the channels of one input component (of one kw tap)
                     uint32_t v[16];
                     tmem_ld_32x32b_x16(tmem_base + ((uint32_t)(q * 32) << 16) + tl * ncols + c0, v);
                     tmem_ld_wait();
                     if (!row_ok) continue;
-                    const int l = c0 >> 4;
+                    const int kwf = (c0 >> 4) / p.LKr, l = (c0 >> 4) - kwf * p.LKr;
+                    float* tap_base = dw32 + (size_t)((tap0 + tl) * p.fold + kwf) * p.nc * comp_stride;
                     const float sgn = alg_negative(p.neg, l, d) ? -1.f : 1.f;
                     float* dst = tap_base + (size_t)alg_pair(p.ga, l, d) * comp_stride + (size_t)co * p.Ci;
 #pragma unroll
@@ -587,6 +593,7 @@ namespace {
 struct NFPlan {
     int s2d, KHe, KWe, DHe, DWe, Cie;    // effective (staged) filter and channels
     int LK, PH, Wt, Ht, tiles_w, tiles_h, Hp, Wp, HOp, WOp, y_planes, taps_per_group, n_groups;
+    int fold, LKe, taps;                 // kw taps folded into one MMA (1 = none), columns / 16 of one MMA, MMAs per 16 pixels
     uint32_t y_bytes, x_bytes, stage_bytes;
     size_t xp_bytes, dyp_bytes, acc_bytes, smem;
 };
@@ -598,28 +605,39 @@ NFPlan make_nfplan(const Geom& g) {
     f.KHe = f.s2d ? (g.KH + 1) / 2 : g.KH; f.KWe = f.s2d ? (g.KW + 1) / 2 : g.KW;
     f.DHe = f.s2d ? 1 : g.DH; f.DWe = f.s2d ? 1 : g.DW;
     f.Cie = f.s2d ? 4 * g.Ci : g.Ci;
+    // the staged copies (shared with the forward pass, see forward_keeps_staged_input) follow the standard tile height
     const int rows = (g.HO + 31) / 32;
-    f.PH = (((g.HO + rows - 1) / rows) + 1) & ~1;
-    f.tiles_h = (g.HO + f.PH - 1) / f.PH;
+    const int ph_std = (((g.HO + rows - 1) / rows) + 1) & ~1;
     f.tiles_w = (g.WO + 7) / 8;
-    f.Wt = 8 + (f.KWe - 1) * f.DWe;
-    f.Ht = f.PH + (f.KHe - 1) * f.DHe;
-    f.HOp = f.tiles_h * f.PH; f.WOp = f.tiles_w * 8;
+    f.HOp = ((g.HO + ph_std - 1) / ph_std) * ph_std; f.WOp = f.tiles_w * 8;
     f.Hp = f.HOp + (f.KHe - 1) * f.DHe; f.Wp = f.WOp + (f.KWe - 1) * f.DWe;
     f.y_planes = (g.Co + 7) / 8;
-    const int taps = f.KHe * f.KWe, ncols = f.LK * 16;
-    f.n_groups = (taps * ncols + 511) / 512;
-    f.taps_per_group = (taps + f.n_groups - 1) / f.n_groups;
-    f.n_groups = (taps + f.taps_per_group - 1) / f.taps_per_group;
-    f.y_bytes = (uint32_t)g.nc * f.y_planes * f.PH * 128;
-    f.x_bytes = (uint32_t)f.LK * 2 * f.Ht * f.Wt * 16;
-    f.stage_bytes = (f.y_bytes + f.x_bytes + 1023) / 1024 * 1024;
+    // folded form: all kw taps of a filter row in the columns of one MMA, if those fit one MMA (N <= 256)
+    f.fold = (f.KWe > 1 && f.KWe * f.LK * 16 <= 256) ? f.KWe : 1;
+    f.LKe = f.LK * f.fold;
+    f.taps = f.fold > 1 ? f.KHe : f.KHe * f.KWe;
+    f.Wt = f.fold > 1 ? 8 : 8 + (f.KWe - 1) * f.DWe;
+    const int ncols = f.LKe * 16;
+    f.n_groups = (f.taps * ncols + 511) / 512;
+    f.taps_per_group = (f.taps + f.n_groups - 1) / f.n_groups;
+    f.n_groups = (f.taps + f.taps_per_group - 1) / f.taps_per_group;
+    // the kernel's own tile height: the standard one, lowered until two stages fit the shared memory (rows past the staged
+    // planes read as zeros through the tensor maps)
+    for (int r = rows;; ++r) {
+        f.PH = (((g.HO + r - 1) / r) + 1) & ~1;
+        f.tiles_h = (g.HO + f.PH - 1) / f.PH;
+        f.Ht = f.PH + (f.KHe - 1) * f.DHe;
+        f.y_bytes = (uint32_t)g.nc * f.y_planes * f.PH * 128;
+        f.x_bytes = (uint32_t)f.LKe * 2 * f.Ht * f.Wt * 16;
+        f.stage_bytes = (f.y_bytes + f.x_bytes + 1023) / 1024 * 1024;
+        // the M = 128 operand spans 16 chunks of PH * 128 bytes from the start of a dy tile
+        const size_t slack = (size_t)16 * f.PH * 128;
+        f.smem = 1024 + 1024 + (size_t)NF_STAGES * f.stage_bytes + slack;
+        if (f.smem <= 226 * 1024 || f.PH <= 2) break;
+    }
     f.xp_bytes = ((size_t)f.LK * g.Nb * 2 * f.Hp * f.Wp * 16 + 1023) / 1024 * 1024;
     f.dyp_bytes = ((size_t)g.nc * g.Nb * f.y_planes * f.HOp * f.WOp * 16 + 1023) / 1024 * 1024;
-    f.acc_bytes = ((size_t)g.nc * g.Co * f.Cie * taps * sizeof(float) + 1023) / 1024 * 1024;
-    // the M = 128 operand spans 16 chunks of PH * 128 bytes from the start of a dy tile
-    const size_t slack = (size_t)16 * f.PH * 128;
-    f.smem = 1024 + 1024 + (size_t)NF_STAGES * f.stage_bytes + slack;
+    f.acc_bytes = ((size_t)g.nc * g.Co * f.Cie * f.KHe * f.KWe * sizeof(float) + 1023) / 1024 * 1024;
     return f;
 }
 
@@ -654,7 +672,7 @@ int narrow_filter_tc_launch(int dtype, const Geom& g, const void* dy, const void
                             const void* kept_x, const StagedView* kept_dy) {
     const int fmt = dtype == PCB_F16 ? 0 : 1;
     const NFPlan f = make_nfplan(g);
-    const int taps = f.KHe * f.KWe;
+    const int taps = f.KHe * f.KWe;                 // filter taps of the staged problem (the folded form issues KHe MMAs per 16 pixels)
     // the forward pass of a narrow layer stages x exactly as this one does: a copy it kept is read in place
     uint8_t* xp = kept_x ? static_cast<uint8_t*>(const_cast<void*>(kept_x)) : static_cast<uint8_t*>(scratch);
     uint8_t* dyp = static_cast<uint8_t*>(scratch) + f.xp_bytes;
@@ -680,9 +698,10 @@ int narrow_filter_tc_launch(int dtype, const Geom& g, const void* dy, const void
     }
     NFParams p;
     p.Nb = g.Nb; p.Co = g.Co; p.Ci = f.Cie; p.nc = g.nc; p.ga = g.ga; p.neg = g.neg;
-    p.KH = f.KHe; p.KW = f.KWe; p.DH = f.DHe; p.DW = f.DWe;
+    p.KH = f.KHe; p.KW = f.fold > 1 ? 1 : f.KWe; p.DH = f.DHe; p.DW = f.DWe;
     p.PH = f.PH; p.Wt = f.Wt; p.Ht = f.Ht; p.tiles_w = f.tiles_w; p.tiles_h = f.tiles_h;
-    p.LK = f.LK; p.taps = taps; p.taps_per_group = f.taps_per_group; p.n_groups = f.n_groups; p.y_planes = f.y_planes;
+    p.LK = f.LKe; p.LKr = f.LK; p.fold = f.fold;
+    p.taps = f.taps; p.taps_per_group = f.taps_per_group; p.n_groups = f.n_groups; p.y_planes = f.y_planes;
     p.fmt = fmt; p.y_bytes = f.y_bytes; p.x_bytes = f.x_bytes; p.stage_bytes = f.stage_bytes; p.plane_bytes = (uint32_t)f.Ht * f.Wt * 16;
     p.steps_total = f.tiles_w * f.tiles_h * g.Nb;
     int splits = split_count(f.n_groups, sm_count());
@@ -712,7 +731,17 @@ int narrow_filter_tc_launch(int dtype, const Geom& g, const void* dy, const void
         }
         if (rc != PCB_OK) return rc;
     }
-    {   // xp[l][img][plane][Hp][Wp][8]; box = the halo tile of all components
+    if (f.fold > 1) {
+        // the same copy with the kw tap as a dimension of its own, one pixel (16 bytes) apart: (w x 8, h, image and plane, l, kw);
+        // box = the tile, 8 pixels wide, of every component at every kw shift. The first extent stops short of the halo columns so
+        // that the shifted views stay inside their rows.
+        const size_t plane = (size_t)f.Hp * f.Wp * 16;
+        const cuuint64_t dims[5] = {(cuuint64_t)f.WOp * 8, (cuuint64_t)f.Hp, (cuuint64_t)2 * g.Nb, (cuuint64_t)f.LK, (cuuint64_t)f.fold};
+        const cuuint64_t strides[4] = {(cuuint64_t)f.Wp * 16, plane, (cuuint64_t)g.Nb * 2 * plane, (cuuint64_t)f.DWe * 16};
+        const cuuint32_t box[5] = {64, (cuuint32_t)f.Ht, 2, (cuuint32_t)f.LK, (cuuint32_t)f.fold};
+        const int rc = make_tensor_map(&map_x, dt, xp, 5, dims, strides, box, nullptr, CU_TENSOR_MAP_SWIZZLE_NONE, "narrow x (folded)");
+        if (rc != PCB_OK) return rc;
+    } else {   // xp[l][img][plane][Hp][Wp][8]; box = the halo tile of all components
         const cuuint64_t dims[5] = {(cuuint64_t)f.Wp * 8, (cuuint64_t)f.Hp, 2, (cuuint64_t)g.Nb, (cuuint64_t)f.LK};
         const cuuint64_t strides[4] = {(cuuint64_t)f.Wp * 16, (cuuint64_t)f.Hp * f.Wp * 16, (cuuint64_t)2 * f.Hp * f.Wp * 16,
                                        (cuuint64_t)g.Nb * 2 * f.Hp * f.Wp * 16};
