@@ -302,8 +302,11 @@ __global__ void pack_filters_planar_kernel(const T* __restrict__ w, T* __restric
 // filter row become columns of ONE MMA. The x tensor map gets the tap as a dimension of its own with a stride of one pixel
 // (16 bytes) over the same staged copy -- overlapping views -- so that one box brings the tile shifted by every kw:
 // [kw][l][plane][Ht][8 px][8], planes at one uniform pitch, N = KW * LK * 16 columns, one MMA per filter row and 16 pixels.
+// A real-valued x (one component) leaves a map dimension free for the filter rows as well (stride: one staged row): the
+// box is then [kw][kh][plane][PH][8 px][8] without halo rows and ONE MMA of N = KH * KW * 16 columns serves every tap.
 // ===================================================================================================
 constexpr int NF_STAGES = 2;
+constexpr int NF_MAX_GROUPS = 16;        // tap groups that can be given CTA shares of their own
 
 struct NFParams {
     int Nb, Co, Ci, nc, ga;
@@ -311,9 +314,12 @@ struct NFParams {
     int KH, KW, DH, DW;
     int PH, Wt, Ht, tiles_w, tiles_h;
     int LK, taps, taps_per_group, n_groups;
-    int fold, LKr;                       // kw taps folded into the columns of one MMA (1 = none); components of x
+    int fold, fold_h, LKr;               // kw (and, for one-component x, kh) taps folded into the columns of one MMA (1 = none); components of x
     int y_planes;                        // 8-channel planes of dy per component
     int steps_total, steps_per_split;
+    // uneven != 0: group g owns the CTAs [cta_begin[g], cta_begin[g + 1]) and walks group_steps[g] pixel tiles per CTA -- a
+    // last group with fewer taps gets fewer CTAs, so that every CTA issues about the same number of MMAs
+    int uneven, cta_begin[NF_MAX_GROUPS + 1], group_steps[NF_MAX_GROUPS];
     int fmt;
     uint32_t y_bytes, x_bytes, stage_bytes, plane_bytes;
 };
@@ -330,11 +336,17 @@ qconv_narrow_filter_tc_kernel(const __grid_constant__ CUtensorMap map_dy, const 
     const uint32_t tiles_addr = smem_u32(base) + 1024;
     const uint32_t full_bar = smem_u32(bars), empty_bar = smem_u32(bars + NF_STAGES), tmem_full = smem_u32(bars + 2 * NF_STAGES);
 
-    const int group = blockIdx.x % p.n_groups, split = blockIdx.x / p.n_groups;
+    int group = blockIdx.x % p.n_groups, split = blockIdx.x / p.n_groups, steps_per_split = p.steps_per_split;
+    if (p.uneven) {
+        group = 0;
+        while (group + 1 < p.n_groups && (int)blockIdx.x >= p.cta_begin[group + 1]) ++group;
+        split = blockIdx.x - p.cta_begin[group];
+        steps_per_split = p.group_steps[group];
+    }
     const int tap0 = group * p.taps_per_group;
     const int n_taps = min(p.taps_per_group, p.taps - tap0);
-    const int step_beg = split * p.steps_per_split;
-    const int n_steps = max(0, min(p.steps_total, step_beg + p.steps_per_split) - step_beg);
+    const int step_beg = split * steps_per_split;
+    const int n_steps = max(0, min(p.steps_total, step_beg + steps_per_split) - step_beg);
     const int tiles_img = p.tiles_w * p.tiles_h;
     const int ncols = p.LK * 16;
 
@@ -407,8 +419,10 @@ qconv_narrow_filter_tc_kernel(const __grid_constant__ CUtensorMap map_dy, const 
                     tmem_ld_32x32b_x16(tmem_base + ((uint32_t)(q * 32) << 16) + tl * ncols + c0, v);
                     tmem_ld_wait();
                     if (!row_ok) continue;
-                    const int kwf = (c0 >> 4) / p.LKr, l = (c0 >> 4) - kwf * p.LKr;
-                    float* tap_base = dw32 + (size_t)((tap0 + tl) * p.fold + kwf) * p.nc * comp_stride;
+                    int kwf, l, tap;
+                    if (p.fold_h > 1) { kwf = (c0 >> 4) / p.fold_h; l = 0; tap = ((c0 >> 4) - kwf * p.fold_h) * p.fold + kwf; }
+                    else { kwf = (c0 >> 4) / p.LKr; l = (c0 >> 4) - kwf * p.LKr; tap = (tap0 + tl) * p.fold + kwf; }
+                    float* tap_base = dw32 + (size_t)tap * p.nc * comp_stride;
                     const float sgn = alg_negative(p.neg, l, d) ? -1.f : 1.f;
                     float* dst = tap_base + (size_t)alg_pair(p.ga, l, d) * comp_stride + (size_t)co * p.Ci;
 #pragma unroll
@@ -593,7 +607,7 @@ namespace {
 struct NFPlan {
     int s2d, KHe, KWe, DHe, DWe, Cie;    // effective (staged) filter and channels
     int LK, PH, Wt, Ht, tiles_w, tiles_h, Hp, Wp, HOp, WOp, y_planes, taps_per_group, n_groups;
-    int fold, LKe, taps;                 // kw taps folded into one MMA (1 = none), columns / 16 of one MMA, MMAs per 16 pixels
+    int fold, fold_h, LKe, taps;         // kw / kh taps folded into one MMA (1 = none), columns / 16 of one MMA, MMAs per 16 pixels
     uint32_t y_bytes, x_bytes, stage_bytes;
     size_t xp_bytes, dyp_bytes, acc_bytes, smem;
 };
@@ -614,8 +628,10 @@ NFPlan make_nfplan(const Geom& g) {
     f.y_planes = (g.Co + 7) / 8;
     // folded form: all kw taps of a filter row in the columns of one MMA, if those fit one MMA (N <= 256)
     f.fold = (f.KWe > 1 && f.KWe * f.LK * 16 <= 256) ? f.KWe : 1;
-    f.LKe = f.LK * f.fold;
-    f.taps = f.fold > 1 ? f.KHe : f.KHe * f.KWe;
+    // ... and the filter rows too for a one-component x (the tensor map has a dimension to spare)
+    f.fold_h = (f.fold > 1 && f.LK == 1 && f.KHe > 1 && f.KHe * f.KWe * 16 <= 256) ? f.KHe : 1;
+    f.LKe = f.LK * f.fold * f.fold_h;
+    f.taps = f.fold_h > 1 ? 1 : (f.fold > 1 ? f.KHe : f.KHe * f.KWe);
     f.Wt = f.fold > 1 ? 8 : 8 + (f.KWe - 1) * f.DWe;
     const int ncols = f.LKe * 16;
     f.n_groups = (f.taps * ncols + 511) / 512;
@@ -626,7 +642,7 @@ NFPlan make_nfplan(const Geom& g) {
     for (int r = rows;; ++r) {
         f.PH = (((g.HO + r - 1) / r) + 1) & ~1;
         f.tiles_h = (g.HO + f.PH - 1) / f.PH;
-        f.Ht = f.PH + (f.KHe - 1) * f.DHe;
+        f.Ht = f.fold_h > 1 ? f.PH : f.PH + (f.KHe - 1) * f.DHe;
         f.y_bytes = (uint32_t)g.nc * f.y_planes * f.PH * 128;
         f.x_bytes = (uint32_t)f.LKe * 2 * f.Ht * f.Wt * 16;
         f.stage_bytes = (f.y_bytes + f.x_bytes + 1023) / 1024 * 1024;
@@ -700,7 +716,7 @@ int narrow_filter_tc_launch(int dtype, const Geom& g, const void* dy, const void
     p.Nb = g.Nb; p.Co = g.Co; p.Ci = f.Cie; p.nc = g.nc; p.ga = g.ga; p.neg = g.neg;
     p.KH = f.KHe; p.KW = f.fold > 1 ? 1 : f.KWe; p.DH = f.DHe; p.DW = f.DWe;
     p.PH = f.PH; p.Wt = f.Wt; p.Ht = f.Ht; p.tiles_w = f.tiles_w; p.tiles_h = f.tiles_h;
-    p.LK = f.LKe; p.LKr = f.LK; p.fold = f.fold;
+    p.LK = f.LKe; p.LKr = f.LK; p.fold = f.fold; p.fold_h = f.fold_h;
     p.taps = f.taps; p.taps_per_group = f.taps_per_group; p.n_groups = f.n_groups; p.y_planes = f.y_planes;
     p.fmt = fmt; p.y_bytes = f.y_bytes; p.x_bytes = f.x_bytes; p.stage_bytes = f.stage_bytes; p.plane_bytes = (uint32_t)f.Ht * f.Wt * 16;
     p.steps_total = f.tiles_w * f.tiles_h * g.Nb;
@@ -709,6 +725,27 @@ int narrow_filter_tc_launch(int dtype, const Geom& g, const void* dy, const void
     if (splits < 1) splits = 1;
     p.steps_per_split = (p.steps_total + splits - 1) / splits;
     splits = (p.steps_total + p.steps_per_split - 1) / p.steps_per_split;
+    int grid = f.n_groups * splits;
+    p.uneven = 0;
+    const int last_taps = f.taps - (f.n_groups - 1) * f.taps_per_group;
+    if (f.n_groups > 1 && f.n_groups <= NF_MAX_GROUPS && last_taps < f.taps_per_group) {
+        // CTA shares in proportion to the taps of each group (one wave of CTAs)
+        const int sms = sm_count();
+        int begin = 0;
+        for (int gi = 0; gi < f.n_groups; ++gi) {
+            const int taps_g = gi + 1 < f.n_groups ? f.taps_per_group : last_taps;
+            int share = (int)((long long)sms * taps_g / f.taps);
+            if (share < 1) share = 1;
+            if (share > p.steps_total) share = p.steps_total;
+            p.group_steps[gi] = (p.steps_total + share - 1) / share;
+            share = (p.steps_total + p.group_steps[gi] - 1) / p.group_steps[gi];
+            p.cta_begin[gi] = begin;
+            begin += share;
+        }
+        p.cta_begin[f.n_groups] = begin;
+        p.uneven = 1;
+        grid = begin;
+    }
 
     const CUtensorMapDataType dt = fmt == 0 ? CU_TENSOR_MAP_DATA_TYPE_FLOAT16 : CU_TENSOR_MAP_DATA_TYPE_BFLOAT16;
     alignas(64) CUtensorMap map_dy, map_x;
@@ -735,10 +772,15 @@ int narrow_filter_tc_launch(int dtype, const Geom& g, const void* dy, const void
         // the same copy with the kw tap as a dimension of its own, one pixel (16 bytes) apart: (w x 8, h, image and plane, l, kw);
         // box = the tile, 8 pixels wide, of every component at every kw shift. The first extent stops short of the halo columns so
         // that the shifted views stay inside their rows.
+        // With the filter rows folded as well the fourth dimension is kh (one staged row apart) instead of the component, and
+        // the second extent stops short of the halo rows for the same reason.
         const size_t plane = (size_t)f.Hp * f.Wp * 16;
-        const cuuint64_t dims[5] = {(cuuint64_t)f.WOp * 8, (cuuint64_t)f.Hp, (cuuint64_t)2 * g.Nb, (cuuint64_t)f.LK, (cuuint64_t)f.fold};
-        const cuuint64_t strides[4] = {(cuuint64_t)f.Wp * 16, plane, (cuuint64_t)g.Nb * 2 * plane, (cuuint64_t)f.DWe * 16};
-        const cuuint32_t box[5] = {64, (cuuint32_t)f.Ht, 2, (cuuint32_t)f.LK, (cuuint32_t)f.fold};
+        const bool fh = f.fold_h > 1;
+        const cuuint64_t dims[5] = {(cuuint64_t)f.WOp * 8, (cuuint64_t)(fh ? f.HOp : f.Hp), (cuuint64_t)2 * g.Nb, (cuuint64_t)(fh ? f.fold_h : f.LK),
+                                    (cuuint64_t)f.fold};
+        const cuuint64_t strides[4] = {(cuuint64_t)f.Wp * 16, plane, fh ? (cuuint64_t)f.DHe * f.Wp * 16 : (cuuint64_t)g.Nb * 2 * plane,
+                                       (cuuint64_t)f.DWe * 16};
+        const cuuint32_t box[5] = {64, (cuuint32_t)f.Ht, 2, (cuuint32_t)(fh ? f.fold_h : f.LK), (cuuint32_t)f.fold};
         const int rc = make_tensor_map(&map_x, dt, xp, 5, dims, strides, box, nullptr, CU_TENSOR_MAP_SWIZZLE_NONE, "narrow x (folded)");
         if (rc != PCB_OK) return rc;
     } else {   // xp[l][img][plane][Hp][Wp][8]; box = the halo tile of all components
@@ -750,7 +792,7 @@ int narrow_filter_tc_launch(int dtype, const Geom& g, const void* dy, const void
         if (rc != PCB_OK) return rc;
     }
     PCB_CUDA_TRY(cudaFuncSetAttribute(qconv_narrow_filter_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)f.smem));
-    qconv_narrow_filter_tc_kernel<<<f.n_groups * splits, N_THREADS, f.smem, stream>>>(map_dy, map_x, p, acc, status);
+    qconv_narrow_filter_tc_kernel<<<grid, N_THREADS, f.smem, stream>>>(map_dy, map_x, p, acc, status);
     PCB_CUDA_TRY(cudaGetLastError());
     const size_t per_tap = (size_t)g.nc * g.Co * g.Ci;
     const int blocks = grid_cap(per_tap * g.KH * g.KW, 256, 16);
