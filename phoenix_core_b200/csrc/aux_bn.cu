@@ -60,13 +60,24 @@ template <> struct VecIO<__nv_bfloat16, 1> {
     static __device__ __forceinline__ void store(__nv_bfloat16* p, const float (&f)[1]) { DType<__nv_bfloat16>::store(p, f[0]); }
 };
 
+// The forward coefficients of a channel recomputed in the backward pass (relu == 2: the ReLU mask is taken from
+// x * k0 + k1 > 0 instead of from the stored output, which then need not be read).
+struct BnFwdParams { const float* gamma; const float* beta; const float* mean; const float* invstd; };
+__device__ __forceinline__ void bn_fwd_coef(const BnFwdParams& f, int c, float& k0, float& k1) {
+    k0 = f.gamma[c] * f.invstd[c];
+    k1 = f.beta[c] - f.mean[c] * k0;
+}
+
 // Sums of two quantities per channel. MODE 0: (x, x*x). MODE 1: (g, g*x) with g = dy masked by y > 0 when relu.
 // Block (c, s): the planes s, s + S, ... of channel c, walked as one flat index space of V-element groups (so that small
 // rows, e.g. 7 x 7 planes, still occupy every thread); one atomic pair per block into sums[0..C) and sums[C..2C).
 template <typename T, int MODE, int V>
 __global__ void __launch_bounds__(BN_THREADS)
-bn_sums_kernel(const T* __restrict__ x, const T* __restrict__ y, const T* __restrict__ dy, float* __restrict__ sums, int planes, int C, int HW, int relu) {
+bn_sums_kernel(const T* __restrict__ x, const T* __restrict__ y, const T* __restrict__ dy, float* __restrict__ sums, int planes, int C, int HW, int relu,
+               BnFwdParams fw) {
     const int c = blockIdx.x, s = blockIdx.y, S = gridDim.y;
+    float m0 = 0.f, m1 = 0.f;
+    if (MODE == 1 && relu == 2) bn_fwd_coef(fw, c, m0, m1);
     const int per_row = HW / V;
     const int my_planes = s < planes ? (planes - s + S - 1) / S : 0;
     float a0 = 0.f, a1 = 0.f;
@@ -81,10 +92,11 @@ bn_sums_kernel(const T* __restrict__ x, const T* __restrict__ y, const T* __rest
         } else {
             float fg[V], fy[V];
             VecIO<T, V>::load(dy + off, fg);
-            if (relu) VecIO<T, V>::load(y + off, fy);
+            if (relu == 1) VecIO<T, V>::load(y + off, fy);
 #pragma unroll
             for (int e = 0; e < V; ++e) {
-                const float g = (relu && !(fy[e] > 0.f)) ? 0.f : fg[e];
+                const float out = relu == 2 ? fmaf(fx[e], m0, m1) : fy[e];
+                const float g = (relu && !(out > 0.f)) ? 0.f : fg[e];
                 a0 += g; a1 = fmaf(g, fx[e], a1);
             }
         }
@@ -136,7 +148,7 @@ __global__ void bn_bwd_finalize_kernel(const float* __restrict__ sums, const flo
 template <typename T, int MODE, int V>
 __global__ void __launch_bounds__(BN_THREADS)
 bn_apply_kernel(const T* __restrict__ x, const T* __restrict__ y, const T* __restrict__ dy, T* __restrict__ out, const float* __restrict__ coef,
-                size_t rows, int C, int HW, int relu, const T* __restrict__ res, T* __restrict__ dres) {
+                size_t rows, int C, int HW, int relu, const T* __restrict__ res, T* __restrict__ dres, BnFwdParams fw) {
     const int per_row = HW / V;
     const size_t total = rows * per_row;
     for (size_t idx = (size_t)blockIdx.x * blockDim.x + threadIdx.x; idx < total; idx += (size_t)gridDim.x * blockDim.x) {
@@ -144,6 +156,8 @@ bn_apply_kernel(const T* __restrict__ x, const T* __restrict__ y, const T* __res
         const int i = (int)(idx - row * per_row);
         const int c = (int)(row % C);
         const float k0 = coef[c], k1 = coef[C + c], k2 = MODE == 1 ? coef[2 * C + c] : 0.f;
+        float m0 = 0.f, m1 = 0.f;
+        if (MODE == 1 && relu == 2) bn_fwd_coef(fw, c, m0, m1);
         const size_t off = row * HW + (size_t)i * V;
         float fx[V], fo[V];
         VecIO<T, V>::load(x + off, fx);
@@ -155,10 +169,11 @@ bn_apply_kernel(const T* __restrict__ x, const T* __restrict__ y, const T* __res
         } else {
             float fg[V], fy[V];
             VecIO<T, V>::load(dy + off, fg);
-            if (relu) VecIO<T, V>::load(y + off, fy);
+            if (relu == 1) VecIO<T, V>::load(y + off, fy);
 #pragma unroll
             for (int e = 0; e < V; ++e) {
-                const float g = (relu && !(fy[e] > 0.f)) ? 0.f : fg[e];
+                const float out = relu == 2 ? fmaf(fx[e], m0, m1) : fy[e];
+                const float g = (relu && !(out > 0.f)) ? 0.f : fg[e];
                 fo[e] = fmaf(k0, g, fmaf(k1, fx[e], k2));
                 fg[e] = g;
             }
@@ -332,24 +347,24 @@ int vec_width(int HW, uintptr_t ptr_bits) {
 
 template <typename T, int MODE, int V>
 void bn_launch(const T* x, const T* y, const T* dy, T* out, float* scratch, float* coef, int planes, int C, int HW, int relu, bool sums,
-               cudaStream_t stream, const T* res, T* dres) {
+               cudaStream_t stream, const T* res, T* dres, BnFwdParams fw) {
     if (sums) {
         int S = (8 * 148 + C - 1) / C;
         if (S > planes) S = planes;
         if (S < 1) S = 1;
-        bn_sums_kernel<T, MODE, V><<<dim3(C, S), BN_THREADS, 0, stream>>>(x, y, dy, scratch, planes, C, HW, relu);
+        bn_sums_kernel<T, MODE, V><<<dim3(C, S), BN_THREADS, 0, stream>>>(x, y, dy, scratch, planes, C, HW, relu, fw);
     } else {
         const size_t rows = (size_t)planes * C;
-        bn_apply_kernel<T, MODE, V><<<blocks_for(rows * (HW / V)), BN_THREADS, 0, stream>>>(x, y, dy, out, coef, rows, C, HW, relu, res, dres);
+        bn_apply_kernel<T, MODE, V><<<blocks_for(rows * (HW / V)), BN_THREADS, 0, stream>>>(x, y, dy, out, coef, rows, C, HW, relu, res, dres, fw);
     }
 }
 
 template <typename T, int MODE>
 void bn_dispatch(int V, const T* x, const T* y, const T* dy, T* out, float* scratch, float* coef, int planes, int C, int HW, int relu, bool sums,
-                 cudaStream_t stream, const T* res = nullptr, T* dres = nullptr) {
-    if (V == 8) bn_launch<T, MODE, 8>(x, y, dy, out, scratch, coef, planes, C, HW, relu, sums, stream, res, dres);
-    else if (V == 4) bn_launch<T, MODE, 4>(x, y, dy, out, scratch, coef, planes, C, HW, relu, sums, stream, res, dres);
-    else bn_launch<T, MODE, 1>(x, y, dy, out, scratch, coef, planes, C, HW, relu, sums, stream, res, dres);
+                 cudaStream_t stream, const T* res = nullptr, T* dres = nullptr, BnFwdParams fw = BnFwdParams{nullptr, nullptr, nullptr, nullptr}) {
+    if (V == 8) bn_launch<T, MODE, 8>(x, y, dy, out, scratch, coef, planes, C, HW, relu, sums, stream, res, dres, fw);
+    else if (V == 4) bn_launch<T, MODE, 4>(x, y, dy, out, scratch, coef, planes, C, HW, relu, sums, stream, res, dres, fw);
+    else bn_launch<T, MODE, 1>(x, y, dy, out, scratch, coef, planes, C, HW, relu, sums, stream, res, dres, fw);
 }
 
 template <typename T>
@@ -367,14 +382,15 @@ int bn_fwd_typed(const T* x, const float* gamma, const float* beta, T* y, float*
 
 template <typename T>
 int bn_bwd_typed(const T* x, const T* y, const T* dy, const float* gamma, const float* mean, const float* invstd, T* dx, float* dgamma, float* dbeta,
-                 float* scratch, int planes, int C, int HW, int relu, cudaStream_t stream, T* dres = nullptr) {
+                 float* scratch, int planes, int C, int HW, int relu, cudaStream_t stream, T* dres = nullptr, const float* beta = nullptr) {
     const int V = vec_width(HW, reinterpret_cast<uintptr_t>(x) | reinterpret_cast<uintptr_t>(dy) | reinterpret_cast<uintptr_t>(dx) |
-                                    reinterpret_cast<uintptr_t>(dres) | (relu ? reinterpret_cast<uintptr_t>(y) : 0));
+                                    reinterpret_cast<uintptr_t>(dres) | (relu == 1 ? reinterpret_cast<uintptr_t>(y) : 0));
+    const BnFwdParams fw = {gamma, beta, mean, invstd};
     PCB_CUDA_TRY(cudaMemsetAsync(scratch, 0, 2 * C * sizeof(float), stream));
     float* coef = scratch + 2 * C;
-    bn_dispatch<T, 1>(V, x, y, dy, nullptr, scratch, coef, planes, C, HW, relu, true, stream);
+    bn_dispatch<T, 1>(V, x, y, dy, nullptr, scratch, coef, planes, C, HW, relu, true, stream, nullptr, nullptr, fw);
     bn_bwd_finalize_kernel<<<(C + 127) / 128, 128, 0, stream>>>(scratch, gamma, mean, invstd, dgamma, dbeta, coef, C, (float)planes * HW);
-    bn_dispatch<T, 1>(V, x, y, dy, dx, scratch, coef, planes, C, HW, relu, false, stream, nullptr, dres);
+    bn_dispatch<T, 1>(V, x, y, dy, dx, scratch, coef, planes, C, HW, relu, false, stream, nullptr, dres, fw);
     PCB_CUDA_TRY(cudaGetLastError());
     return PCB_OK;
 }
@@ -406,6 +422,20 @@ int pcb_aux_bn_relu_bwd(int dtype, const void* x, const void* y, const void* dy,
     }
     if (dtype == PCB_F16) return bn_bwd_typed<__half>((const __half*)x, (const __half*)y, (const __half*)dy, gamma, mean, invstd, (__half*)dx, dgamma, dbeta, scratch, planes, channels, hw, relu, (cudaStream_t)stream);
     if (dtype == PCB_BF16) return bn_bwd_typed<__nv_bfloat16>((const __nv_bfloat16*)x, (const __nv_bfloat16*)y, (const __nv_bfloat16*)dy, gamma, mean, invstd, (__nv_bfloat16*)dx, dgamma, dbeta, scratch, planes, channels, hw, relu, (cudaStream_t)stream);
+    set_error("batch-norm helper: 16-bit tensors only");
+    return PCB_ERR_UNSUPPORTED;
+}
+
+int pcb_aux_bn_relu_bwd_from_input(int dtype, const void* x, const void* dy, const float* gamma, const float* beta, const float* mean,
+                                   const float* invstd, void* dx, float* dgamma, float* dbeta, float* scratch, int planes, int channels, int hw,
+                                   void* stream) {
+    using namespace pcb;
+    if (!x || !dy || !gamma || !beta || !mean || !invstd || !dx || !dgamma || !dbeta || !scratch || planes <= 0 || channels <= 0 || hw <= 0) {
+        set_error("invalid batch-norm arguments");
+        return PCB_ERR_INVALID_ARGUMENT;
+    }
+    if (dtype == PCB_F16) return bn_bwd_typed<__half>((const __half*)x, nullptr, (const __half*)dy, gamma, mean, invstd, (__half*)dx, dgamma, dbeta, scratch, planes, channels, hw, 2, (cudaStream_t)stream, nullptr, beta);
+    if (dtype == PCB_BF16) return bn_bwd_typed<__nv_bfloat16>((const __nv_bfloat16*)x, nullptr, (const __nv_bfloat16*)dy, gamma, mean, invstd, (__nv_bfloat16*)dx, dgamma, dbeta, scratch, planes, channels, hw, 2, (cudaStream_t)stream, nullptr, beta);
     set_error("batch-norm helper: 16-bit tensors only");
     return PCB_ERR_UNSUPPORTED;
 }

@@ -75,7 +75,8 @@ class _BNReLUFn(torch.autograd.Function):
                                                       mean.data_ptr(), invstd.data_ptr(), scratch.data_ptr(), planes, c, hw, eps, int(relu),
                                                       torch.cuda.current_stream().cuda_stream))
             ctx.fused = True
-            ctx.save_for_backward(x, y if relu else None, mean, invstd, gamma)
+            # the backward kernels recompute the ReLU mask from x, so the output is not kept for them
+            ctx.save_for_backward(x, None, mean, invstd, gamma, beta)
             return y
         var, mean = torch.var_mean(x.float(), dim=(0, 2, 3), unbiased=False)
         invstd = torch.rsqrt(var + eps)
@@ -85,12 +86,12 @@ class _BNReLUFn(torch.autograd.Function):
         if relu:
             y.clamp_min_(0)
         ctx.fused = False
-        ctx.save_for_backward(x, y if relu else None, mean, invstd, gamma)
+        ctx.save_for_backward(x, y if relu else None, mean, invstd, gamma, beta)
         return y
 
     @staticmethod
     def backward(ctx, dy):
-        x, y, mean, invstd, gamma = ctx.saved_tensors
+        x, y, mean, invstd, gamma, beta = ctx.saved_tensors
         if ctx.fused:
             dy = dy.contiguous()
             planes, c = x.shape[0], x.shape[1]
@@ -99,6 +100,12 @@ class _BNReLUFn(torch.autograd.Function):
             dgamma = torch.empty(c, dtype=torch.float32, device=x.device)
             dbeta = torch.empty_like(dgamma)
             scratch = torch.empty(5 * c, dtype=torch.float32, device=x.device)
+            if ctx.relu:
+                _lib.check(_lib.lib().pcb_aux_bn_relu_bwd_from_input(_DT[x.dtype], x.data_ptr(), dy.data_ptr(), gamma.data_ptr(), beta.data_ptr(),
+                                                                     mean.data_ptr(), invstd.data_ptr(), dx.data_ptr(), dgamma.data_ptr(),
+                                                                     dbeta.data_ptr(), scratch.data_ptr(), planes, c, hw,
+                                                                     torch.cuda.current_stream().cuda_stream))
+                return dx, dgamma, dbeta, None, None
             _lib.check(_lib.lib().pcb_aux_bn_relu_bwd(_DT[x.dtype], x.data_ptr(), y.data_ptr() if ctx.relu else None, dy.data_ptr(),
                                                       gamma.data_ptr(), mean.data_ptr(), invstd.data_ptr(), dx.data_ptr(), dgamma.data_ptr(),
                                                       dbeta.data_ptr(), scratch.data_ptr(), planes, c, hw, int(ctx.relu),
