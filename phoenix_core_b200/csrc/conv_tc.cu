@@ -480,6 +480,55 @@ __global__ void pack_activations_kernel(const T* __restrict__ x, T* __restrict__
     }
 }
 
+// The general staging through shared memory for dense NCHW sources whose plane (all channels of one image and component,
+// one contiguous block of C * H * W elements) fits there: the block is read once with coalesced 16-byte loads, and the
+// padded / zero-inserted / channel-blocked copy is written from it with the channel groups of a pixel on neighbouring
+// threads, so that a warp writes whole pixels (Cp * 2 contiguous bytes each). One CTA per plane. The general kernel above
+// reads 2-byte elements H * W apart, which on 7 x 7 planes and on zero-inserted copies runs at a quarter of this.
+constexpr int PACK_SMEM_THREADS = 256;
+constexpr size_t PACK_SMEM_MAX_BYTES = 96 * 1024;               // two CTAs per SM
+template <typename T>
+__global__ void __launch_bounds__(PACK_SMEM_THREADS)
+pack_activations_smem_kernel(const T* __restrict__ x, T* __restrict__ xp, int C, int H, int W, int Hp, int Wp, int Cp, int pad_top, int pad_left,
+                             int ins_h, int ins_w, int cb, int Nb) {
+    extern __shared__ __align__(16) uint8_t pack_smem[];
+    T* tile = reinterpret_cast<T*>(pack_smem);                   // [C][H * W]
+    const int plane = blockIdx.x, HW = H * W, n = C * HW;
+    const T* src = x + (size_t)plane * n;
+    if ((n & 7) == 0) {                                          // every plane starts on a 16-byte boundary (the tensor does)
+        for (int i = threadIdx.x; i < n / 8; i += PACK_SMEM_THREADS)
+            reinterpret_cast<uint4*>(tile)[i] = __ldg(reinterpret_cast<const uint4*>(src) + i);
+    } else {
+        for (int i = threadIdx.x; i < n; i += PACK_SMEM_THREADS) tile[i] = src[i];
+    }
+    __syncthreads();
+    const int groups = Cp / 8, items = Hp * Wp * groups;
+    const int comp = plane / Nb, img = plane - comp * Nb;
+    for (int idx = threadIdx.x; idx < items; idx += PACK_SMEM_THREADS) {
+        const int grp = idx % groups, pix = idx / groups;
+        const int hp = pix / Wp, wp = pix - hp * Wp;
+        int ih = hp - pad_top, iw = wp - pad_left;
+        bool inside = ih >= 0 && iw >= 0;
+        if (inside && (ins_h > 1 || ins_w > 1)) {
+            inside = (ih % ins_h == 0) && (iw % ins_w == 0);
+            ih /= ins_h; iw /= ins_w;
+        }
+        inside = inside && ih < H && iw < W;
+        alignas(16) T vals[8];
+#pragma unroll
+        for (int e = 0; e < 8; ++e) {
+            const int c = grp * 8 + e;
+            vals[e] = (inside && c < C) ? tile[c * HW + ih * W + iw] : T(0.f);
+        }
+        T* dst = xp + (((size_t)plane * Hp + hp) * Wp + wp) * Cp + grp * 8;
+        if (cb > 0) {
+            const int b = (grp * 8) / cb;
+            dst = xp + (((((size_t)comp * (Cp / cb) + b) * Nb + img) * Hp + hp) * Wp + wp) * cb + (grp * 8 - b * cb);
+        }
+        *reinterpret_cast<uint4*>(dst) = *reinterpret_cast<const uint4*>(vals);
+    }
+}
+
 // Host dispatch of the activation staging: the 4- or 2-pixel form where it applies, the general form otherwise.
 // cb > 0 selects the channel-block layout of the filter-gradient kernels (Nb images per component).
 // `ss` = nullptr: a dense NCHW source (the fast forms apply); otherwise its element strides.
@@ -497,6 +546,17 @@ void stage_activations(int fmt, const void* src, void* dst, int planes, int C, i
         const int blocks = grid_cap(total / 2 + 1, 256, 16);
         if (fmt == 0) pack_rows_kernel<__half, 2><<<blocks, 256, 0, stream>>>((const __half*)src, (__half*)dst, planes, C, H, W, Hp, Wp, Cp / 8, pad_top, pad_left, 0, cb, Nb);
         else pack_rows_kernel<__nv_bfloat16, 2><<<blocks, 256, 0, stream>>>((const __nv_bfloat16*)src, (__nv_bfloat16*)dst, planes, C, H, W, Hp, Wp, Cp / 8, pad_top, pad_left, 0, cb, Nb);
+    } else if (!ss && (size_t)C * H * W * 2 <= PACK_SMEM_MAX_BYTES && (reinterpret_cast<uintptr_t>(src) & 15u) == 0) {
+        const size_t smem = ((size_t)C * H * W * 2 + 15) / 16 * 16;
+        if (fmt == 0) {
+            cudaFuncSetAttribute(pack_activations_smem_kernel<__half>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)PACK_SMEM_MAX_BYTES);
+            pack_activations_smem_kernel<__half><<<planes, PACK_SMEM_THREADS, smem, stream>>>((const __half*)src, (__half*)dst, C, H, W, Hp, Wp, Cp, pad_top, pad_left,
+                                                                                           ins_h, ins_w, cb, Nb);
+        } else {
+            cudaFuncSetAttribute(pack_activations_smem_kernel<__nv_bfloat16>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)PACK_SMEM_MAX_BYTES);
+            pack_activations_smem_kernel<__nv_bfloat16><<<planes, PACK_SMEM_THREADS, smem, stream>>>((const __nv_bfloat16*)src, (__nv_bfloat16*)dst, C, H, W, Hp, Wp, Cp,
+                                                                                                  pad_top, pad_left, ins_h, ins_w, cb, Nb);
+        }
     } else {
         const int blocks = grid_cap(total, 256, 16);
         if (fmt == 0) pack_activations_kernel<__half><<<blocks, 256, 0, stream>>>((const __half*)src, (__half*)dst, planes, C, H, W, Hp, Wp, Cp, pad_top, pad_left, ins_h, ins_w, cb, Nb, st);
