@@ -412,16 +412,12 @@ class QResNet18:
         (loss * LOSS_SCALE).backward()
         reduce_and_apply(self.flat_w32, self.flat_mom, self.flat_g16, world, lr, momentum, LOSS_SCALE, self.split, self.pending)
         self.pending = None
+        grads = [p.grad for p in self.bn_params]                  # 40 small tensors: multi-tensor kernels, not one launch each
         if world > 1:
-            bn_flat = torch.cat([p.grad.reshape(-1) for p in self.bn_params])
+            bn_flat = torch.cat([g.reshape(-1) for g in grads])
             dist.all_reduce(bn_flat)
-            off = 0
-            for p in self.bn_params:
-                p.grad.copy_(bn_flat[off:off + p.numel()].view_as(p))
-                off += p.numel()
-        inv = 1.0 / (LOSS_SCALE * world)
-        for p in self.bn_params:
-            p.grad.mul_(inv)
+            torch._foreach_copy_(grads, [t.view_as(g) for t, g in zip(bn_flat.split([g.numel() for g in grads]), grads)])
+        torch._foreach_mul_(grads, 1.0 / (LOSS_SCALE * world))
         self.bn_opt.step()
         return loss
 
