@@ -240,6 +240,15 @@ int pcb_aux_bn_add_relu_fwd(int dtype, const void* x, const void* residual, cons
 int pcb_aux_bn_add_relu_bwd(int dtype, const void* x, const void* y, const void* dy, const float* gamma, const float* mean,
                             const float* invstd, void* dx, void* dresidual, float* dgamma, float* dbeta, float* scratch, int planes,
                             int channels, int hw, void* stream);
+/* The network's stem in two passes over x: batch-norm statistics, then relu(batch_norm(x)) and the 3x3 stride-2 pad-1 maximum
+ * of it in one kernel -- the normalised h x w tensor is never written; y and argmax are (h/2) x (w/2). The backward call gathers
+ * the pooled gradient through argmax inside the batch-norm gradient's own two passes. h even, w a multiple of 8, 16-byte
+ * aligned tensors (PCB_ERR_UNSUPPORTED otherwise: use the separate helpers). */
+int pcb_aux_bn_relu_maxpool_fwd(int dtype, const void* x, const float* gamma, const float* beta, void* y, void* argmax, float* mean,
+                                float* invstd, float* scratch, int planes, int channels, int h, int w, float eps, void* stream);
+int pcb_aux_bn_relu_maxpool_bwd(int dtype, const void* x, const void* dy, const void* argmax, const float* gamma, const float* beta,
+                                const float* mean, const float* invstd, void* dx, float* dgamma, float* dbeta, float* scratch,
+                                int planes, int channels, int h, int w, void* stream);
 /* 3x3 stride-2 pad-1 max pooling of `rows` planes of h x w 16-bit elements (output ((h-1)/2+1) x ((w-1)/2+1)); `argmax`
  * holds one byte per output element for the backward pass, which gathers without atomics. Harness glue as above. */
 int pcb_aux_maxpool3x3s2_fwd(int dtype, const void* x, void* y, void* argmax, int rows, int h, int w, void* stream);

@@ -331,6 +331,146 @@ maxpool_bwd_kernel(const T* __restrict__ dy, const uint8_t* __restrict__ arg, T*
     }
 }
 
+// ---- batch-norm + ReLU + 3x3 stride-2 max pooling in one (the network's stem) ----------------------------------------------
+// Forward: the pooled maximum of relu(x * k0 + k1) straight from x -- the normalised full-size tensor is never written.
+// Lines of a multiple of 8 pixels, an even number of lines; same window scan order and arg-max encoding as maxpool_fwd4_kernel.
+template <typename T>
+__global__ void __launch_bounds__(BN_THREADS)
+bn_relu_pool_fwd_kernel(const T* __restrict__ x, const float* __restrict__ coef, T* __restrict__ y, uint8_t* __restrict__ arg, size_t rows, int C,
+                        int H, int W, int HO, int WO) {
+    const int groups = WO / 4;
+    const size_t total = rows * HO * groups;
+    for (size_t idx = (size_t)blockIdx.x * blockDim.x + threadIdx.x; idx < total; idx += (size_t)gridDim.x * blockDim.x) {
+        const int g = (int)(idx % groups);
+        const int oh = (int)((idx / groups) % HO);
+        const size_t row = idx / ((size_t)groups * HO);
+        const int c = (int)(row % C);
+        const float k0 = coef[c], k1 = coef[C + c];
+        const T* src = x + row * H * W;
+        float best[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
+        int where[4] = {0, 0, 0, 0};
+#pragma unroll
+        for (int kh = 0; kh < 3; ++kh) {
+            const int ih = 2 * oh - 1 + kh;
+            if ((unsigned)ih >= (unsigned)H) continue;
+            float f[8];
+            VecIO<T, 8>::load(src + (size_t)ih * W + 8 * g, f);
+#pragma unroll
+            for (int e = 0; e < 8; ++e) f[e] = fmaxf(fmaf(f[e], k0, k1), 0.f);
+            const float left = g > 0 ? fmaxf(fmaf(DType<T>::load(src + (size_t)ih * W + 8 * g - 1), k0, k1), 0.f) : 0.f;
+#pragma unroll
+            for (int j = 0; j < 4; ++j) {
+#pragma unroll
+                for (int kw = 0; kw < 3; ++kw) {
+                    const int rel = 2 * j - 1 + kw;
+                    if (rel < 0 && g == 0) continue;
+                    const float v = rel < 0 ? left : f[rel];
+                    if (v > best[j] || (v != v)) { best[j] = v; where[j] = kh * 3 + kw; }
+                }
+            }
+        }
+        const size_t o = (row * HO + oh) * WO + 4 * g;
+        VecIO<T, 4>::store(y + o, best);
+        *reinterpret_cast<uint32_t*>(arg + o) = (uint32_t)where[0] | ((uint32_t)where[1] << 8) | ((uint32_t)where[2] << 16) | ((uint32_t)where[3] << 24);
+    }
+}
+
+// The gradient that reaches 8 consecutive pixels of the (never stored) normalised tensor: gathered from the pooled gradient
+// through the arg-max bytes, as in maxpool_bwd8_kernel.
+template <typename T>
+__device__ __forceinline__ void pool_gather8(const T* __restrict__ dp, const uint8_t* __restrict__ arg, size_t obase, int ih, int g, int HO, int WO,
+                                             float (&acc)[8]) {
+#pragma unroll
+    for (int e = 0; e < 8; ++e) acc[e] = 0.f;
+    for (int oh = ih >> 1; oh <= (ih + 1) >> 1; ++oh) {
+        if (oh >= HO) continue;
+        const int kh = ih - (2 * oh - 1);
+        const size_t o = obase + (size_t)oh * WO + 4 * g;
+        const uint32_t a4 = __ldg(reinterpret_cast<const uint32_t*>(arg + o));
+        float g4[4];
+        VecIO<T, 4>::load(dp + o, g4);
+#pragma unroll
+        for (int j = 0; j < 5; ++j) {
+            int a;
+            float gr;
+            if (j < 4) { a = (int)((a4 >> (8 * j)) & 0xffu); gr = g4[j]; }
+            else {
+                if (4 * g + 4 >= WO) continue;
+                a = arg[o + 4]; gr = DType<T>::load(dp + o + 4);
+            }
+            if (a / 3 != kh) continue;
+            const int e = 2 * j - 1 + a % 3;
+#pragma unroll
+            for (int q = 0; q < 8; ++q) if (q == e) acc[q] += gr;
+        }
+    }
+}
+
+// Backward sums (g, g * x) per channel with g gathered from the pooled gradient and masked by relu'(x * m0 + m1).
+template <typename T>
+__global__ void __launch_bounds__(BN_THREADS)
+bn_pool_sums_kernel(const T* __restrict__ x, const T* __restrict__ dp, const uint8_t* __restrict__ arg, float* __restrict__ sums, int planes, int C,
+                    int H, int W, int HO, int WO, BnFwdParams fw) {
+    const int c = blockIdx.x, s = blockIdx.y, S = gridDim.y;
+    float m0, m1;
+    bn_fwd_coef(fw, c, m0, m1);
+    const int per_line = W / 8, per_plane = H * per_line;
+    const int my_planes = s < planes ? (planes - s + S - 1) / S : 0;
+    float a0 = 0.f, a1 = 0.f;
+    for (int j = threadIdx.x; j < my_planes * per_plane; j += BN_THREADS) {
+        const int pi = j / per_plane, r = j - pi * per_plane, ih = r / per_line, g = r - ih * per_line;
+        const size_t row = (size_t)(s + pi * S) * C + c;
+        float fx[8], fg[8];
+        VecIO<T, 8>::load(x + (row * H + ih) * W + 8 * g, fx);
+        pool_gather8<T>(dp, arg, row * HO * WO, ih, g, HO, WO, fg);
+#pragma unroll
+        for (int e = 0; e < 8; ++e) {
+            const float gg = fmaf(fx[e], m0, m1) > 0.f ? fg[e] : 0.f;
+            a0 += gg; a1 = fmaf(gg, fx[e], a1);
+        }
+    }
+    __shared__ float red[2][BN_THREADS / 32];
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) { a0 += __shfl_xor_sync(0xffffffffu, a0, o); a1 += __shfl_xor_sync(0xffffffffu, a1, o); }
+    if ((threadIdx.x & 31) == 0) { red[0][threadIdx.x >> 5] = a0; red[1][threadIdx.x >> 5] = a1; }
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        float t0 = 0.f, t1 = 0.f;
+#pragma unroll
+        for (int w = 0; w < BN_THREADS / 32; ++w) { t0 += red[0][w]; t1 += red[1][w]; }
+        atomicAdd(sums + c, t0);
+        atomicAdd(sums + C + c, t1);
+    }
+}
+
+// dx = coef0 * g + coef1 * x + coef2 with the same gathered, masked g.
+template <typename T>
+__global__ void __launch_bounds__(BN_THREADS)
+bn_pool_apply_kernel(const T* __restrict__ x, const T* __restrict__ dp, const uint8_t* __restrict__ arg, T* __restrict__ dx,
+                     const float* __restrict__ coef, size_t rows, int C, int H, int W, int HO, int WO, BnFwdParams fw) {
+    const int per_line = W / 8;
+    const size_t total = rows * H * per_line;
+    for (size_t idx = (size_t)blockIdx.x * blockDim.x + threadIdx.x; idx < total; idx += (size_t)gridDim.x * blockDim.x) {
+        const int g = (int)(idx % per_line);
+        const int ih = (int)((idx / per_line) % H);
+        const size_t row = idx / ((size_t)per_line * H);
+        const int c = (int)(row % C);
+        const float k0 = coef[c], k1 = coef[C + c], k2 = coef[2 * C + c];
+        float m0, m1;
+        bn_fwd_coef(fw, c, m0, m1);
+        float fx[8], fg[8], fo[8];
+        const size_t off = (row * H + ih) * W + 8 * g;
+        VecIO<T, 8>::load(x + off, fx);
+        pool_gather8<T>(dp, arg, row * HO * WO, ih, g, HO, WO, fg);
+#pragma unroll
+        for (int e = 0; e < 8; ++e) {
+            const float gg = fmaf(fx[e], m0, m1) > 0.f ? fg[e] : 0.f;
+            fo[e] = fmaf(k0, gg, fmaf(k1, fx[e], k2));
+        }
+        VecIO<T, 8>::store(dx + off, fo);
+    }
+}
+
 int blocks_for(size_t work) {
     int dev = 0, sms = 148;
     if (cudaGetDevice(&dev) == cudaSuccess) cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
@@ -395,10 +535,77 @@ int bn_bwd_typed(const T* x, const T* y, const T* dy, const float* gamma, const 
     return PCB_OK;
 }
 
+template <typename T>
+int bn_pool_fwd_typed(const T* x, const float* gamma, const float* beta, T* y, uint8_t* arg, float* mean, float* invstd, float* scratch, int planes, int C,
+                      int H, int W, float eps, cudaStream_t stream) {
+    const int HW = H * W, HO = H / 2, WO = W / 2;
+    PCB_CUDA_TRY(cudaMemsetAsync(scratch, 0, 2 * C * sizeof(float), stream));
+    float* coef = scratch + 2 * C;
+    bn_dispatch<T, 0>(8, x, nullptr, nullptr, nullptr, scratch, coef, planes, C, HW, 0, true, stream);
+    bn_fwd_finalize_kernel<<<(C + 127) / 128, 128, 0, stream>>>(scratch, gamma, beta, mean, invstd, coef, C, (float)planes * HW, eps);
+    const size_t rows = (size_t)planes * C;
+    bn_relu_pool_fwd_kernel<T><<<blocks_for(rows * HO * (WO / 4)), BN_THREADS, 0, stream>>>(x, coef, y, arg, rows, C, H, W, HO, WO);
+    PCB_CUDA_TRY(cudaGetLastError());
+    return PCB_OK;
+}
+
+template <typename T>
+int bn_pool_bwd_typed(const T* x, const T* dp, const uint8_t* arg, const float* gamma, const float* beta, const float* mean, const float* invstd, T* dx,
+                      float* dgamma, float* dbeta, float* scratch, int planes, int C, int H, int W, cudaStream_t stream) {
+    const int HO = H / 2, WO = W / 2;
+    const BnFwdParams fw = {gamma, beta, mean, invstd};
+    PCB_CUDA_TRY(cudaMemsetAsync(scratch, 0, 2 * C * sizeof(float), stream));
+    float* coef = scratch + 2 * C;
+    int S = (8 * 148 + C - 1) / C;
+    if (S > planes) S = planes;
+    if (S < 1) S = 1;
+    bn_pool_sums_kernel<T><<<dim3(C, S), BN_THREADS, 0, stream>>>(x, dp, arg, scratch, planes, C, H, W, HO, WO, fw);
+    bn_bwd_finalize_kernel<<<(C + 127) / 128, 128, 0, stream>>>(scratch, gamma, mean, invstd, dgamma, dbeta, coef, C, (float)planes * H * W);
+    const size_t rows = (size_t)planes * C;
+    bn_pool_apply_kernel<T><<<blocks_for(rows * H * (W / 8)), BN_THREADS, 0, stream>>>(x, dp, arg, dx, coef, rows, C, H, W, HO, WO, fw);
+    PCB_CUDA_TRY(cudaGetLastError());
+    return PCB_OK;
+}
+
 }  // namespace
 }  // namespace pcb
 
 extern "C" {
+
+// Shapes the fused batch-norm + ReLU + max-pool kernels take: lines of a multiple of 8 pixels, an even number of them, 16-byte aligned tensors.
+static bool bn_pool_shape_ok(int h, int w, const void* a, const void* b, const void* c) {
+    return h > 0 && w > 0 && h % 2 == 0 && w % 8 == 0 &&
+           ((reinterpret_cast<uintptr_t>(a) | reinterpret_cast<uintptr_t>(b) | reinterpret_cast<uintptr_t>(c)) & 15u) == 0;
+}
+
+int pcb_aux_bn_relu_maxpool_fwd(int dtype, const void* x, const float* gamma, const float* beta, void* y, void* argmax, float* mean, float* invstd,
+                                float* scratch, int planes, int channels, int h, int w, float eps, void* stream) {
+    using namespace pcb;
+    if (!x || !gamma || !beta || !y || !argmax || !mean || !invstd || !scratch || planes <= 0 || channels <= 0) {
+        set_error("invalid batch-norm arguments");
+        return PCB_ERR_INVALID_ARGUMENT;
+    }
+    if (!bn_pool_shape_ok(h, w, x, y, argmax)) { set_error("fused batch-norm + pooling: lines of a multiple of 8 pixels, an even number of lines, 16-byte aligned tensors"); return PCB_ERR_UNSUPPORTED; }
+    if (dtype == PCB_F16) return bn_pool_fwd_typed<__half>((const __half*)x, gamma, beta, (__half*)y, (uint8_t*)argmax, mean, invstd, scratch, planes, channels, h, w, eps, (cudaStream_t)stream);
+    if (dtype == PCB_BF16) return bn_pool_fwd_typed<__nv_bfloat16>((const __nv_bfloat16*)x, gamma, beta, (__nv_bfloat16*)y, (uint8_t*)argmax, mean, invstd, scratch, planes, channels, h, w, eps, (cudaStream_t)stream);
+    set_error("batch-norm helper: 16-bit tensors only");
+    return PCB_ERR_UNSUPPORTED;
+}
+
+int pcb_aux_bn_relu_maxpool_bwd(int dtype, const void* x, const void* dy, const void* argmax, const float* gamma, const float* beta, const float* mean,
+                                const float* invstd, void* dx, float* dgamma, float* dbeta, float* scratch, int planes, int channels, int h, int w,
+                                void* stream) {
+    using namespace pcb;
+    if (!x || !dy || !argmax || !gamma || !beta || !mean || !invstd || !dx || !dgamma || !dbeta || !scratch || planes <= 0 || channels <= 0) {
+        set_error("invalid batch-norm arguments");
+        return PCB_ERR_INVALID_ARGUMENT;
+    }
+    if (!bn_pool_shape_ok(h, w, x, dy, dx) || (reinterpret_cast<uintptr_t>(argmax) & 15u)) { set_error("fused batch-norm + pooling: lines of a multiple of 8 pixels, an even number of lines, 16-byte aligned tensors"); return PCB_ERR_UNSUPPORTED; }
+    if (dtype == PCB_F16) return bn_pool_bwd_typed<__half>((const __half*)x, (const __half*)dy, (const uint8_t*)argmax, gamma, beta, mean, invstd, (__half*)dx, dgamma, dbeta, scratch, planes, channels, h, w, (cudaStream_t)stream);
+    if (dtype == PCB_BF16) return bn_pool_bwd_typed<__nv_bfloat16>((const __nv_bfloat16*)x, (const __nv_bfloat16*)dy, (const uint8_t*)argmax, gamma, beta, mean, invstd, (__nv_bfloat16*)dx, dgamma, dbeta, scratch, planes, channels, h, w, (cudaStream_t)stream);
+    set_error("batch-norm helper: 16-bit tensors only");
+    return PCB_ERR_UNSUPPORTED;
+}
 
 int pcb_aux_bn_relu_fwd(int dtype, const void* x, const float* gamma, const float* beta, void* y, float* mean, float* invstd, float* scratch,
                         int planes, int channels, int hw, float eps, int relu, void* stream) {

@@ -163,6 +163,40 @@ class _BNAddReLUFn(torch.autograd.Function):
         return dx, dres, dgamma, dbeta, None
 
 
+class _BNReLUPoolFn(torch.autograd.Function):
+    """max_pool_3x3_s2(relu(batch_norm(x))) without the full-size normalised tensor: statistics, then normalise + ReLU + pool
+    in one kernel; backward gathers the pooled gradient inside the batch-norm gradient's two passes (five passes over the
+    large tensor instead of thirteen). 16-bit contiguous CUDA tensors with lines of a multiple of 8 pixels."""
+
+    @staticmethod
+    def forward(ctx, x, gamma, beta, eps):
+        planes, c, h, w = x.shape
+        y = torch.empty((planes, c, h // 2, w // 2), dtype=x.dtype, device=x.device)
+        arg = torch.empty(y.shape, dtype=torch.uint8, device=x.device)
+        mean = torch.empty(c, dtype=torch.float32, device=x.device)
+        invstd = torch.empty_like(mean)
+        scratch = torch.empty(5 * c, dtype=torch.float32, device=x.device)
+        _lib.check(_lib.lib().pcb_aux_bn_relu_maxpool_fwd(_DT[x.dtype], x.data_ptr(), gamma.data_ptr(), beta.data_ptr(), y.data_ptr(), arg.data_ptr(),
+                                                          mean.data_ptr(), invstd.data_ptr(), scratch.data_ptr(), planes, c, h, w, eps,
+                                                          torch.cuda.current_stream().cuda_stream))
+        ctx.save_for_backward(x, arg, mean, invstd, gamma, beta)
+        return y
+
+    @staticmethod
+    def backward(ctx, dy):
+        x, arg, mean, invstd, gamma, beta = ctx.saved_tensors
+        dy = dy.contiguous()
+        planes, c, h, w = x.shape
+        dx = torch.empty_like(x)
+        dgamma = torch.empty(c, dtype=torch.float32, device=x.device)
+        dbeta = torch.empty_like(dgamma)
+        scratch = torch.empty(5 * c, dtype=torch.float32, device=x.device)
+        _lib.check(_lib.lib().pcb_aux_bn_relu_maxpool_bwd(_DT[x.dtype], x.data_ptr(), dy.data_ptr(), arg.data_ptr(), gamma.data_ptr(), beta.data_ptr(),
+                                                          mean.data_ptr(), invstd.data_ptr(), dx.data_ptr(), dgamma.data_ptr(), dbeta.data_ptr(),
+                                                          scratch.data_ptr(), planes, c, h, w, torch.cuda.current_stream().cuda_stream))
+        return dx, dgamma, dbeta, None
+
+
 class _MaxPoolFn(torch.autograd.Function):
     """3x3 stride-2 pad-1 max pooling on the library's helper kernels (the framework's backward kernel scatters with atomics and
     takes three times as long as the forward pass). Harness glue."""
@@ -202,6 +236,12 @@ class BNReLU:
 
     def __call__(self, x, relu=None):
         return _BNReLUFn.apply(x, self.weight, self.bias, 1e-5, self.relu if relu is None else relu)
+
+    def relu_pool(self, x):
+        """max_pool_3x3_s2(relu(batch_norm(x)))."""
+        if x.is_cuda and x.dtype in _DT and x.is_contiguous() and x.shape[2] % 2 == 0 and x.shape[3] % 8 == 0:
+            return _BNReLUPoolFn.apply(x, self.weight, self.bias, 1e-5)
+        return max_pool_3x3_s2(self(x, relu=True))
 
     def add_relu(self, x, residual):
         """relu(batch_norm(x) + residual)."""
@@ -390,8 +430,7 @@ class QResNet18:
     def forward(self, images):
         """images: [N, 3, H, W] real RGB (the quaternion with zero imaginary parts) -> logits [N, classes]."""
         n = images.shape[0]
-        x = self.bn1(self.conv1(images.contiguous()))
-        x = max_pool_3x3_s2(x)
+        x = self.bn1.relu_pool(self.conv1(images.contiguous()))
         for blocks in self.stages:
             for blk in blocks:
                 idt = x

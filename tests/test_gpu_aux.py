@@ -84,6 +84,38 @@ def test_bn_add_relu_helper(shape, dtype):
     assert err(bn.bias.grad, br.grad) < 2e-2
 
 
+@pytest.mark.parametrize("shape", [(8, 16, 12, 16), (4, 5, 6, 8), (2, 3, 16, 24), (4, 16, 112, 112)])
+@pytest.mark.parametrize("dtype", [torch.float16, torch.bfloat16])
+def test_bn_relu_maxpool_helper(shape, dtype):
+    """The fused stem tail against the two separate helpers (batch-norm + ReLU, then max-pool): the same pooled values to
+    within a unit in the last place; the same gradients except where two window elements tie after rounding to the storage type (the separate form stores the
+    normalised tensor in 16 bits before pooling, the fused form compares in fp32)."""
+    if not torch.cuda.is_available():
+        pytest.skip("no CUDA device")
+    from phoenix_core_b200.qresnet import BNReLU, max_pool_3x3_s2
+    g = torch.Generator().manual_seed(8)
+    x = (torch.randn(shape, generator=g) * 1.5 + 0.3).to(dtype).cuda()
+    outs = []
+    for fused in (True, False):
+        bn = BNReLU(shape[1], torch.device("cuda"), relu=True)
+        gg = torch.Generator().manual_seed(9)
+        with torch.no_grad():
+            bn.weight.copy_((torch.rand(shape[1], generator=gg) + 0.5).cuda())
+            bn.bias.copy_((torch.randn(shape[1], generator=gg) * 0.2).cuda())
+        xin = x.clone().requires_grad_(True)
+        y = bn.relu_pool(xin) if fused else max_pool_3x3_s2(bn(xin))
+        dy = torch.randn(y.shape, generator=gg).to(dtype).cuda()
+        y.backward(dy)
+        outs.append((y.detach().float(), xin.grad.float(), bn.weight.grad.clone(), bn.bias.grad.clone()))
+    (yf, dxf, dgf, dbf), (ys, dxs, dgs, dbs) = outs
+    # the statistics are summed with atomics, so mean and 1/std can differ in their last bits between two runs
+    assert yf.shape == ys.shape and float((yf - ys).abs().max()) <= 4e-3 * float(ys.abs().max())
+    differing = float(((dxf - dxs).abs() > 1e-3 * dxs.abs().max()).float().mean())
+    assert differing < 5e-3, differing
+    assert float((dgf - dgs).abs().max() / dgs.abs().max()) < 2e-2
+    assert float((dbf - dbs).abs().max() / dbs.abs().max()) < 2e-2
+
+
 @pytest.mark.parametrize("shape", [(8, 16, 12, 12), (4, 5, 9, 7), (2, 3, 16, 11), (2, 3, 16, 24), (1, 2, 112, 112), (3, 2, 9, 8)])
 @pytest.mark.parametrize("dtype", [torch.float16, torch.bfloat16])
 def test_maxpool_helpers(shape, dtype):
