@@ -183,6 +183,90 @@ bn_apply_kernel(const T* __restrict__ x, const T* __restrict__ y, const T* __res
     }
 }
 
+// ---- rows that are not a multiple of 4 elements (7 x 7 planes) --------------------------------------------------------------
+// The kernels above then fall back to 2-byte accesses. These two walk the tensor as one flat sequence of 16-byte groups
+// instead (the whole tensor is a multiple of 8 elements and 16-byte aligned even if its rows are not): the 8 elements of a
+// group belong to at most two channels when rows are at least 8 elements long, and the channel is tracked per element.
+template <typename T, int MODE>
+__global__ void __launch_bounds__(BN_THREADS)
+bn_sums_flat_kernel(const T* __restrict__ x, const T* __restrict__ y, const T* __restrict__ dy, float* __restrict__ sums, size_t groups, int C, int HW,
+                    int relu, BnFwdParams fw) {
+    extern __shared__ float bins[];                               // [2][C]
+    for (int i = threadIdx.x; i < 2 * C; i += BN_THREADS) bins[i] = 0.f;
+    __syncthreads();
+    for (size_t gi = (size_t)blockIdx.x * BN_THREADS + threadIdx.x; gi < groups; gi += (size_t)gridDim.x * BN_THREADS) {
+        const size_t i0 = gi * 8;
+        const size_t row = i0 / HW;
+        int r = (int)(i0 - row * HW), c = (int)(row % C);
+        float fx[8], fg[8], fy[8];
+        VecIO<T, 8>::load(x + i0, fx);
+        if (MODE == 1) {
+            VecIO<T, 8>::load(dy + i0, fg);
+            if (relu == 1) VecIO<T, 8>::load(y + i0, fy);
+        }
+        float a0 = 0.f, a1 = 0.f, m0 = 0.f, m1 = 0.f;
+        if (MODE == 1 && relu == 2) bn_fwd_coef(fw, c, m0, m1);
+#pragma unroll
+        for (int e = 0; e < 8; ++e) {
+            if (MODE == 0) { a0 += fx[e]; a1 = fmaf(fx[e], fx[e], a1); }
+            else {
+                const float out = relu == 2 ? fmaf(fx[e], m0, m1) : fy[e];
+                const float g = (relu && !(out > 0.f)) ? 0.f : fg[e];
+                a0 += g; a1 = fmaf(g, fx[e], a1);
+            }
+            if (++r == HW) {                                      // the next element starts the next channel's row
+                atomicAdd(bins + c, a0); atomicAdd(bins + C + c, a1);
+                a0 = a1 = 0.f; r = 0;
+                if (++c == C) c = 0;
+                if (MODE == 1 && relu == 2) bn_fwd_coef(fw, c, m0, m1);
+            }
+        }
+        atomicAdd(bins + c, a0); atomicAdd(bins + C + c, a1);
+    }
+    __syncthreads();
+    for (int i = threadIdx.x; i < 2 * C; i += BN_THREADS) atomicAdd(sums + i, bins[i]);
+}
+
+template <typename T, int MODE>
+__global__ void __launch_bounds__(BN_THREADS)
+bn_apply_flat_kernel(const T* __restrict__ x, const T* __restrict__ y, const T* __restrict__ dy, T* __restrict__ out, const float* __restrict__ coef,
+                     size_t groups, int C, int HW, int relu, const T* __restrict__ res, T* __restrict__ dres, BnFwdParams fw) {
+    for (size_t gi = (size_t)blockIdx.x * BN_THREADS + threadIdx.x; gi < groups; gi += (size_t)gridDim.x * BN_THREADS) {
+        const size_t i0 = gi * 8;
+        const size_t row = i0 / HW;
+        int r = (int)(i0 - row * HW), c = (int)(row % C);
+        float fx[8], fo[8], fg[8], fy[8], fr[8];
+        VecIO<T, 8>::load(x + i0, fx);
+        if (MODE == 0) { if (res) VecIO<T, 8>::load(res + i0, fr); }
+        else {
+            VecIO<T, 8>::load(dy + i0, fg);
+            if (relu == 1) VecIO<T, 8>::load(y + i0, fy);
+        }
+        float k0 = coef[c], k1 = coef[C + c], k2 = MODE == 1 ? coef[2 * C + c] : 0.f, m0 = 0.f, m1 = 0.f;
+        if (MODE == 1 && relu == 2) bn_fwd_coef(fw, c, m0, m1);
+#pragma unroll
+        for (int e = 0; e < 8; ++e) {
+            if (MODE == 0) {
+                const float v = fmaf(fx[e], k0, k1) + (res ? fr[e] : 0.f);
+                fo[e] = relu ? fmaxf(v, 0.f) : v;
+            } else {
+                const float o = relu == 2 ? fmaf(fx[e], m0, m1) : fy[e];
+                const float g = (relu && !(o > 0.f)) ? 0.f : fg[e];
+                fo[e] = fmaf(k0, g, fmaf(k1, fx[e], k2));
+                fg[e] = g;
+            }
+            if (++r == HW) {
+                r = 0;
+                if (++c == C) c = 0;
+                k0 = coef[c]; k1 = coef[C + c]; k2 = MODE == 1 ? coef[2 * C + c] : 0.f;
+                if (MODE == 1 && relu == 2) bn_fwd_coef(fw, c, m0, m1);
+            }
+        }
+        VecIO<T, 8>::store(out + i0, fo);
+        if (MODE == 1 && dres) VecIO<T, 8>::store(dres + i0, fg);
+    }
+}
+
 // 3x3 stride-2 pad-1 max pooling over rows of H x W elements (one row per (plane, channel)); the forward pass keeps the
 // position of the maximum inside its window (0..8), the backward pass gathers: every input pixel looks at the at most four
 // windows that contain it, so there are no atomics.
@@ -284,10 +368,12 @@ maxpool_bwd8_kernel(const T* __restrict__ dy, const uint8_t* __restrict__ arg, T
                     if (4 * g + 4 >= WO) continue;
                     a = arg[o + 4]; gr = DType<T>::load(dy + o + 4);
                 }
-                if (a / 3 != kh) continue;
-                const int e = 2 * j - 1 + a % 3;                   // position of the maximum relative to iw0 (window 4g + j)
-#pragma unroll
-                for (int q = 0; q < 8; ++q) if (q == e) acc[q] += gr;
+                // window 4g + j covers the columns 2j - 1 .. 2j + 1 relative to iw0; j is a constant of the unrolled loop
+                const int akh = (a * 11) >> 5, akw = a - 3 * akh;     // a / 3 and a % 3 for a in 0..8
+                const float m = akh == kh ? gr : 0.f;
+                if (2 * j - 1 >= 0) acc[(2 * j - 1) & 7] += akw == 0 ? m : 0.f;
+                if (2 * j < 8) acc[(2 * j) & 7] += akw == 1 ? m : 0.f;
+                if (2 * j + 1 < 8) acc[(2 * j + 1) & 7] += akw == 2 ? m : 0.f;
             }
         }
         VecIO<T, 8>::store(dx + (row * H + ih) * W + iw0, acc);
@@ -481,10 +567,13 @@ int blocks_for(size_t work) {
     return (int)(need < cap ? (need ? need : 1) : cap);
 }
 
-// Widest vector (8, 4 or 1 elements) that rows of HW elements starting at these pointers allow.
-int vec_width(int HW, uintptr_t ptr_bits) {
+// Widest vector (8, 4 or 1 elements) that rows of HW elements starting at these pointers allow; BN_FLAT where the rows
+// allow none but the tensor as a whole is a sequence of aligned 8-element groups (see bn_sums_flat_kernel).
+constexpr int BN_FLAT = -8;
+int vec_width(int HW, uintptr_t ptr_bits, size_t total = 0, int C = 0) {
     if (HW % 8 == 0 && ptr_bits % 16 == 0) return 8;
     if (HW % 4 == 0 && ptr_bits % 8 == 0) return 4;
+    if (total && total % 8 == 0 && ptr_bits % 16 == 0 && HW >= 8 && C <= 4096) return BN_FLAT;
     return 1;
 }
 
@@ -505,7 +594,16 @@ void bn_launch(const T* x, const T* y, const T* dy, T* out, float* scratch, floa
 template <typename T, int MODE>
 void bn_dispatch(int V, const T* x, const T* y, const T* dy, T* out, float* scratch, float* coef, int planes, int C, int HW, int relu, bool sums,
                  cudaStream_t stream, const T* res = nullptr, T* dres = nullptr, BnFwdParams fw = BnFwdParams{nullptr, nullptr, nullptr, nullptr}) {
-    if (V == 8) bn_launch<T, MODE, 8>(x, y, dy, out, scratch, coef, planes, C, HW, relu, sums, stream, res, dres, fw);
+    if (V == BN_FLAT) {
+        const size_t groups = (size_t)planes * C * HW / 8;
+        if (sums) {
+            const size_t want = (groups + BN_THREADS - 1) / BN_THREADS;
+            const int blocks = (int)(want < 4 * 148 ? (want ? want : 1) : 4 * 148);
+            bn_sums_flat_kernel<T, MODE><<<blocks, BN_THREADS, 2 * C * sizeof(float), stream>>>(x, y, dy, scratch, groups, C, HW, relu, fw);
+        } else {
+            bn_apply_flat_kernel<T, MODE><<<blocks_for(groups), BN_THREADS, 0, stream>>>(x, y, dy, out, coef, groups, C, HW, relu, res, dres, fw);
+        }
+    } else if (V == 8) bn_launch<T, MODE, 8>(x, y, dy, out, scratch, coef, planes, C, HW, relu, sums, stream, res, dres, fw);
     else if (V == 4) bn_launch<T, MODE, 4>(x, y, dy, out, scratch, coef, planes, C, HW, relu, sums, stream, res, dres, fw);
     else bn_launch<T, MODE, 1>(x, y, dy, out, scratch, coef, planes, C, HW, relu, sums, stream, res, dres, fw);
 }
@@ -513,7 +611,7 @@ void bn_dispatch(int V, const T* x, const T* y, const T* dy, T* out, float* scra
 template <typename T>
 int bn_fwd_typed(const T* x, const float* gamma, const float* beta, T* y, float* mean, float* invstd, float* scratch, int planes, int C, int HW,
                  float eps, int relu, cudaStream_t stream, const T* res = nullptr) {
-    const int V = vec_width(HW, reinterpret_cast<uintptr_t>(x) | reinterpret_cast<uintptr_t>(y) | reinterpret_cast<uintptr_t>(res));
+    const int V = vec_width(HW, reinterpret_cast<uintptr_t>(x) | reinterpret_cast<uintptr_t>(y) | reinterpret_cast<uintptr_t>(res), (size_t)planes * C * HW, C);
     PCB_CUDA_TRY(cudaMemsetAsync(scratch, 0, 2 * C * sizeof(float), stream));
     float* coef = scratch + 2 * C;
     bn_dispatch<T, 0>(V, x, nullptr, nullptr, nullptr, scratch, coef, planes, C, HW, 0, true, stream);
@@ -527,7 +625,7 @@ template <typename T>
 int bn_bwd_typed(const T* x, const T* y, const T* dy, const float* gamma, const float* mean, const float* invstd, T* dx, float* dgamma, float* dbeta,
                  float* scratch, int planes, int C, int HW, int relu, cudaStream_t stream, T* dres = nullptr, const float* beta = nullptr) {
     const int V = vec_width(HW, reinterpret_cast<uintptr_t>(x) | reinterpret_cast<uintptr_t>(dy) | reinterpret_cast<uintptr_t>(dx) |
-                                    reinterpret_cast<uintptr_t>(dres) | (relu == 1 ? reinterpret_cast<uintptr_t>(y) : 0));
+                                    reinterpret_cast<uintptr_t>(dres) | (relu == 1 ? reinterpret_cast<uintptr_t>(y) : 0), (size_t)planes * C * HW, C);
     const BnFwdParams fw = {gamma, beta, mean, invstd};
     PCB_CUDA_TRY(cudaMemsetAsync(scratch, 0, 2 * C * sizeof(float), stream));
     float* coef = scratch + 2 * C;

@@ -19,7 +19,7 @@ def _ref(x, gamma, beta, dy, eps, relu):
     return y.detach(), x.grad, gamma.grad, beta.grad
 
 
-@pytest.mark.parametrize("shape", [(8, 16, 12, 12), (12, 5, 7, 7), (4, 64, 14, 14), (16, 3, 6, 10)])
+@pytest.mark.parametrize("shape", [(8, 16, 12, 12), (12, 5, 7, 7), (4, 64, 14, 14), (16, 3, 6, 10), (8, 6, 7, 7), (16, 128, 7, 7), (8, 3, 3, 3)])
 @pytest.mark.parametrize("dtype", [torch.float16, torch.bfloat16])
 @pytest.mark.parametrize("relu", [False, True])
 def test_bn_relu_helpers(shape, dtype, relu):
@@ -47,7 +47,7 @@ def test_bn_relu_helpers(shape, dtype, relu):
     assert err(beta.grad, rdb) < tol
 
 
-@pytest.mark.parametrize("shape", [(8, 16, 12, 12), (12, 5, 7, 7), (4, 64, 14, 14), (16, 3, 6, 10)])
+@pytest.mark.parametrize("shape", [(8, 16, 12, 12), (12, 5, 7, 7), (4, 64, 14, 14), (16, 3, 6, 10), (8, 6, 7, 7), (16, 128, 7, 7)])
 @pytest.mark.parametrize("dtype", [torch.float16, torch.bfloat16])
 def test_bn_add_relu_helper(shape, dtype):
     """relu(batch_norm(x) + residual) in the batch-norm's own passes, and its three gradients, against float64."""
