@@ -68,6 +68,48 @@ __device__ __forceinline__ void bn_fwd_coef(const BnFwdParams& f, int c, float& 
     k1 = f.beta[c] - f.mean[c] * k0;
 }
 
+// Per-channel coefficients of the apply passes, computed where they are used from the channel sums (there is no separate
+// finalize launch). Forward (MODE 0): y = x * k0 + k1 with k0 = gamma / std, k1 = beta - mean * k0; block 0 also saves mean
+// and 1/std through out0 / out1. Backward (MODE 1): dx = k0 * g + k1 * x + k2 from
+//   xhat = (x - mean) * invstd;  dgamma = sum(g * xhat);  dbeta = sum(g);  dx = gamma * invstd * (g - dbeta / m - xhat * dgamma / m);
+// block 0 writes dgamma / dbeta through out0 / out1.
+struct BnCoef {
+    const float* sums;                                          // [2][C]: (x, x*x) forward, (g, g*x) backward
+    const float* gamma; const float* beta; const float* mean; const float* invstd;
+    float* out0; float* out1;
+    float count, eps;
+};
+template <int MODE>
+__device__ __forceinline__ void bn_coef(const BnCoef& q, int C, int c, float& k0, float& k1, float& k2) {
+    if (MODE == 0) {
+        const float m = q.sums[c] / q.count;
+        const float var = fmaxf(q.sums[C + c] / q.count - m * m, 0.f);
+        k0 = q.gamma[c] * rsqrtf(var + q.eps);
+        k1 = q.beta[c] - m * k0;
+        k2 = 0.f;
+    } else {
+        const float sg = q.sums[c], sgx = q.sums[C + c], is = q.invstd[c], mu = q.mean[c];
+        const float dg = (sgx - mu * sg) * is;
+        k0 = q.gamma[c] * is;
+        k1 = -k0 * is * dg / q.count;
+        k2 = -k0 * sg / q.count - k1 * mu;
+    }
+}
+template <int MODE>
+__device__ __forceinline__ void bn_coef_outputs(const BnCoef& q, int C) {
+    if (blockIdx.x != 0) return;
+    for (int c = threadIdx.x; c < C; c += blockDim.x) {
+        if (MODE == 0) {
+            const float m = q.sums[c] / q.count;
+            const float var = fmaxf(q.sums[C + c] / q.count - m * m, 0.f);
+            q.out0[c] = m; q.out1[c] = rsqrtf(var + q.eps);
+        } else {
+            const float sg = q.sums[c];
+            q.out0[c] = (q.sums[C + c] - q.mean[c] * sg) * q.invstd[c]; q.out1[c] = sg;
+        }
+    }
+}
+
 // Sums of two quantities per channel. MODE 0: (x, x*x). MODE 1: (g, g*x) with g = dy masked by y > 0 when relu.
 // Block (c, s): the planes s, s + S, ... of channel c, walked as one flat index space of V-element groups (so that small
 // rows, e.g. 7 x 7 planes, still occupy every thread); one atomic pair per block into sums[0..C) and sums[C..2C).
@@ -115,47 +157,21 @@ bn_sums_kernel(const T* __restrict__ x, const T* __restrict__ y, const T* __rest
     }
 }
 
-// Forward coefficients: y = x * coef[c] + coef[C + c]; also the saved mean and 1/std.
-__global__ void bn_fwd_finalize_kernel(const float* __restrict__ sums, const float* __restrict__ gamma, const float* __restrict__ beta,
-                                       float* __restrict__ mean, float* __restrict__ invstd, float* __restrict__ coef, int C, float count, float eps) {
-    const int c = blockIdx.x * blockDim.x + threadIdx.x;
-    if (c >= C) return;
-    const float m = sums[c] / count;
-    const float var = fmaxf(sums[C + c] / count - m * m, 0.f);
-    const float is = rsqrtf(var + eps);
-    mean[c] = m; invstd[c] = is;
-    const float sc = gamma[c] * is;
-    coef[c] = sc; coef[C + c] = beta[c] - m * sc;
-}
-
-// Backward coefficients: dx = a*g + b*x + k per channel; also dgamma, dbeta.
-//   xhat = (x - mean) * invstd;  dgamma = sum(g * xhat);  dbeta = sum(g);  dx = gamma*invstd * (g - dbeta/m - xhat * dgamma/m)
-__global__ void bn_bwd_finalize_kernel(const float* __restrict__ sums, const float* __restrict__ gamma, const float* __restrict__ mean,
-                                       const float* __restrict__ invstd, float* __restrict__ dgamma, float* __restrict__ dbeta,
-                                       float* __restrict__ coef, int C, float count) {
-    const int c = blockIdx.x * blockDim.x + threadIdx.x;
-    if (c >= C) return;
-    const float sg = sums[c], sgx = sums[C + c], is = invstd[c], mu = mean[c];
-    const float dg = (sgx - mu * sg) * is;
-    dgamma[c] = dg; dbeta[c] = sg;
-    const float a = gamma[c] * is;
-    const float b = -a * is * dg / count;
-    coef[c] = a; coef[C + c] = b; coef[2 * C + c] = -a * sg / count - b * mu;
-}
-
 // MODE 0: y = max(x*coef0 + coef1 [+ res], 0 if relu).  MODE 1: dx = coef0*g + coef1*x + coef2 with g = dy masked by y > 0
 // [and dres = g: the gradient of the residual branch that was added before the ReLU].
 template <typename T, int MODE, int V>
 __global__ void __launch_bounds__(BN_THREADS)
-bn_apply_kernel(const T* __restrict__ x, const T* __restrict__ y, const T* __restrict__ dy, T* __restrict__ out, const float* __restrict__ coef,
+bn_apply_kernel(const T* __restrict__ x, const T* __restrict__ y, const T* __restrict__ dy, T* __restrict__ out, BnCoef coef,
                 size_t rows, int C, int HW, int relu, const T* __restrict__ res, T* __restrict__ dres, BnFwdParams fw) {
+    bn_coef_outputs<MODE>(coef, C);
     const int per_row = HW / V;
     const size_t total = rows * per_row;
     for (size_t idx = (size_t)blockIdx.x * blockDim.x + threadIdx.x; idx < total; idx += (size_t)gridDim.x * blockDim.x) {
         const size_t row = idx / per_row;
         const int i = (int)(idx - row * per_row);
         const int c = (int)(row % C);
-        const float k0 = coef[c], k1 = coef[C + c], k2 = MODE == 1 ? coef[2 * C + c] : 0.f;
+        float k0, k1, k2;
+        bn_coef<MODE>(coef, C, c, k0, k1, k2);
         float m0 = 0.f, m1 = 0.f;
         if (MODE == 1 && relu == 2) bn_fwd_coef(fw, c, m0, m1);
         const size_t off = row * HW + (size_t)i * V;
@@ -229,8 +245,9 @@ bn_sums_flat_kernel(const T* __restrict__ x, const T* __restrict__ y, const T* _
 
 template <typename T, int MODE>
 __global__ void __launch_bounds__(BN_THREADS)
-bn_apply_flat_kernel(const T* __restrict__ x, const T* __restrict__ y, const T* __restrict__ dy, T* __restrict__ out, const float* __restrict__ coef,
+bn_apply_flat_kernel(const T* __restrict__ x, const T* __restrict__ y, const T* __restrict__ dy, T* __restrict__ out, BnCoef coef,
                      size_t groups, int C, int HW, int relu, const T* __restrict__ res, T* __restrict__ dres, BnFwdParams fw) {
+    bn_coef_outputs<MODE>(coef, C);
     for (size_t gi = (size_t)blockIdx.x * BN_THREADS + threadIdx.x; gi < groups; gi += (size_t)gridDim.x * BN_THREADS) {
         const size_t i0 = gi * 8;
         const size_t row = i0 / HW;
@@ -242,7 +259,8 @@ bn_apply_flat_kernel(const T* __restrict__ x, const T* __restrict__ y, const T* 
             VecIO<T, 8>::load(dy + i0, fg);
             if (relu == 1) VecIO<T, 8>::load(y + i0, fy);
         }
-        float k0 = coef[c], k1 = coef[C + c], k2 = MODE == 1 ? coef[2 * C + c] : 0.f, m0 = 0.f, m1 = 0.f;
+        float k0, k1, k2, m0 = 0.f, m1 = 0.f;
+        bn_coef<MODE>(coef, C, c, k0, k1, k2);
         if (MODE == 1 && relu == 2) bn_fwd_coef(fw, c, m0, m1);
 #pragma unroll
         for (int e = 0; e < 8; ++e) {
@@ -258,7 +276,7 @@ bn_apply_flat_kernel(const T* __restrict__ x, const T* __restrict__ y, const T* 
             if (++r == HW) {
                 r = 0;
                 if (++c == C) c = 0;
-                k0 = coef[c]; k1 = coef[C + c]; k2 = MODE == 1 ? coef[2 * C + c] : 0.f;
+                bn_coef<MODE>(coef, C, c, k0, k1, k2);
                 if (MODE == 1 && relu == 2) bn_fwd_coef(fw, c, m0, m1);
             }
         }
@@ -422,8 +440,9 @@ maxpool_bwd_kernel(const T* __restrict__ dy, const uint8_t* __restrict__ arg, T*
 // Lines of a multiple of 8 pixels, an even number of lines; same window scan order and arg-max encoding as maxpool_fwd4_kernel.
 template <typename T>
 __global__ void __launch_bounds__(BN_THREADS)
-bn_relu_pool_fwd_kernel(const T* __restrict__ x, const float* __restrict__ coef, T* __restrict__ y, uint8_t* __restrict__ arg, size_t rows, int C,
+bn_relu_pool_fwd_kernel(const T* __restrict__ x, BnCoef coef, T* __restrict__ y, uint8_t* __restrict__ arg, size_t rows, int C,
                         int H, int W, int HO, int WO) {
+    bn_coef_outputs<0>(coef, C);
     const int groups = WO / 4;
     const size_t total = rows * HO * groups;
     for (size_t idx = (size_t)blockIdx.x * blockDim.x + threadIdx.x; idx < total; idx += (size_t)gridDim.x * blockDim.x) {
@@ -431,7 +450,8 @@ bn_relu_pool_fwd_kernel(const T* __restrict__ x, const float* __restrict__ coef,
         const int oh = (int)((idx / groups) % HO);
         const size_t row = idx / ((size_t)groups * HO);
         const int c = (int)(row % C);
-        const float k0 = coef[c], k1 = coef[C + c];
+        float k0, k1, k2;
+        bn_coef<0>(coef, C, c, k0, k1, k2);
         const T* src = x + row * H * W;
         float best[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
         int where[4] = {0, 0, 0, 0};
@@ -536,7 +556,8 @@ bn_pool_sums_kernel(const T* __restrict__ x, const T* __restrict__ dp, const uin
 template <typename T>
 __global__ void __launch_bounds__(BN_THREADS)
 bn_pool_apply_kernel(const T* __restrict__ x, const T* __restrict__ dp, const uint8_t* __restrict__ arg, T* __restrict__ dx,
-                     const float* __restrict__ coef, size_t rows, int C, int H, int W, int HO, int WO, BnFwdParams fw) {
+                     BnCoef coef, size_t rows, int C, int H, int W, int HO, int WO, BnFwdParams fw) {
+    bn_coef_outputs<1>(coef, C);
     const int per_line = W / 8;
     const size_t total = rows * H * per_line;
     for (size_t idx = (size_t)blockIdx.x * blockDim.x + threadIdx.x; idx < total; idx += (size_t)gridDim.x * blockDim.x) {
@@ -544,7 +565,8 @@ bn_pool_apply_kernel(const T* __restrict__ x, const T* __restrict__ dp, const ui
         const int ih = (int)((idx / per_line) % H);
         const size_t row = idx / ((size_t)per_line * H);
         const int c = (int)(row % C);
-        const float k0 = coef[c], k1 = coef[C + c], k2 = coef[2 * C + c];
+        float k0, k1, k2;
+        bn_coef<1>(coef, C, c, k0, k1, k2);
         float m0, m1;
         bn_fwd_coef(fw, c, m0, m1);
         float fx[8], fg[8], fo[8];
@@ -578,7 +600,7 @@ int vec_width(int HW, uintptr_t ptr_bits, size_t total = 0, int C = 0) {
 }
 
 template <typename T, int MODE, int V>
-void bn_launch(const T* x, const T* y, const T* dy, T* out, float* scratch, float* coef, int planes, int C, int HW, int relu, bool sums,
+void bn_launch(const T* x, const T* y, const T* dy, T* out, float* scratch, BnCoef coef, int planes, int C, int HW, int relu, bool sums,
                cudaStream_t stream, const T* res, T* dres, BnFwdParams fw) {
     if (sums) {
         int S = (8 * 148 + C - 1) / C;
@@ -592,7 +614,7 @@ void bn_launch(const T* x, const T* y, const T* dy, T* out, float* scratch, floa
 }
 
 template <typename T, int MODE>
-void bn_dispatch(int V, const T* x, const T* y, const T* dy, T* out, float* scratch, float* coef, int planes, int C, int HW, int relu, bool sums,
+void bn_dispatch(int V, const T* x, const T* y, const T* dy, T* out, float* scratch, BnCoef coef, int planes, int C, int HW, int relu, bool sums,
                  cudaStream_t stream, const T* res = nullptr, T* dres = nullptr, BnFwdParams fw = BnFwdParams{nullptr, nullptr, nullptr, nullptr}) {
     if (V == BN_FLAT) {
         const size_t groups = (size_t)planes * C * HW / 8;
@@ -613,9 +635,8 @@ int bn_fwd_typed(const T* x, const float* gamma, const float* beta, T* y, float*
                  float eps, int relu, cudaStream_t stream, const T* res = nullptr) {
     const int V = vec_width(HW, reinterpret_cast<uintptr_t>(x) | reinterpret_cast<uintptr_t>(y) | reinterpret_cast<uintptr_t>(res), (size_t)planes * C * HW, C);
     PCB_CUDA_TRY(cudaMemsetAsync(scratch, 0, 2 * C * sizeof(float), stream));
-    float* coef = scratch + 2 * C;
+    const BnCoef coef = {scratch, gamma, beta, nullptr, nullptr, mean, invstd, (float)planes * HW, eps};
     bn_dispatch<T, 0>(V, x, nullptr, nullptr, nullptr, scratch, coef, planes, C, HW, 0, true, stream);
-    bn_fwd_finalize_kernel<<<(C + 127) / 128, 128, 0, stream>>>(scratch, gamma, beta, mean, invstd, coef, C, (float)planes * HW, eps);
     bn_dispatch<T, 0>(V, x, nullptr, nullptr, y, scratch, coef, planes, C, HW, relu, false, stream, res, nullptr);
     PCB_CUDA_TRY(cudaGetLastError());
     return PCB_OK;
@@ -628,9 +649,8 @@ int bn_bwd_typed(const T* x, const T* y, const T* dy, const float* gamma, const 
                                     reinterpret_cast<uintptr_t>(dres) | (relu == 1 ? reinterpret_cast<uintptr_t>(y) : 0), (size_t)planes * C * HW, C);
     const BnFwdParams fw = {gamma, beta, mean, invstd};
     PCB_CUDA_TRY(cudaMemsetAsync(scratch, 0, 2 * C * sizeof(float), stream));
-    float* coef = scratch + 2 * C;
+    const BnCoef coef = {scratch, gamma, nullptr, mean, invstd, dgamma, dbeta, (float)planes * HW, 0.f};
     bn_dispatch<T, 1>(V, x, y, dy, nullptr, scratch, coef, planes, C, HW, relu, true, stream, nullptr, nullptr, fw);
-    bn_bwd_finalize_kernel<<<(C + 127) / 128, 128, 0, stream>>>(scratch, gamma, mean, invstd, dgamma, dbeta, coef, C, (float)planes * HW);
     bn_dispatch<T, 1>(V, x, y, dy, dx, scratch, coef, planes, C, HW, relu, false, stream, nullptr, dres, fw);
     PCB_CUDA_TRY(cudaGetLastError());
     return PCB_OK;
@@ -641,9 +661,8 @@ int bn_pool_fwd_typed(const T* x, const float* gamma, const float* beta, T* y, u
                       int H, int W, float eps, cudaStream_t stream) {
     const int HW = H * W, HO = H / 2, WO = W / 2;
     PCB_CUDA_TRY(cudaMemsetAsync(scratch, 0, 2 * C * sizeof(float), stream));
-    float* coef = scratch + 2 * C;
+    const BnCoef coef = {scratch, gamma, beta, nullptr, nullptr, mean, invstd, (float)planes * HW, eps};
     bn_dispatch<T, 0>(8, x, nullptr, nullptr, nullptr, scratch, coef, planes, C, HW, 0, true, stream);
-    bn_fwd_finalize_kernel<<<(C + 127) / 128, 128, 0, stream>>>(scratch, gamma, beta, mean, invstd, coef, C, (float)planes * HW, eps);
     const size_t rows = (size_t)planes * C;
     bn_relu_pool_fwd_kernel<T><<<blocks_for(rows * HO * (WO / 4)), BN_THREADS, 0, stream>>>(x, coef, y, arg, rows, C, H, W, HO, WO);
     PCB_CUDA_TRY(cudaGetLastError());
@@ -656,12 +675,11 @@ int bn_pool_bwd_typed(const T* x, const T* dp, const uint8_t* arg, const float* 
     const int HO = H / 2, WO = W / 2;
     const BnFwdParams fw = {gamma, beta, mean, invstd};
     PCB_CUDA_TRY(cudaMemsetAsync(scratch, 0, 2 * C * sizeof(float), stream));
-    float* coef = scratch + 2 * C;
+    const BnCoef coef = {scratch, gamma, nullptr, mean, invstd, dgamma, dbeta, (float)planes * H * W, 0.f};
     int S = (8 * 148 + C - 1) / C;
     if (S > planes) S = planes;
     if (S < 1) S = 1;
     bn_pool_sums_kernel<T><<<dim3(C, S), BN_THREADS, 0, stream>>>(x, dp, arg, scratch, planes, C, H, W, HO, WO, fw);
-    bn_bwd_finalize_kernel<<<(C + 127) / 128, 128, 0, stream>>>(scratch, gamma, mean, invstd, dgamma, dbeta, coef, C, (float)planes * H * W);
     const size_t rows = (size_t)planes * C;
     bn_pool_apply_kernel<T><<<blocks_for(rows * H * (W / 8)), BN_THREADS, 0, stream>>>(x, dp, arg, dx, coef, rows, C, H, W, HO, WO, fw);
     PCB_CUDA_TRY(cudaGetLastError());
