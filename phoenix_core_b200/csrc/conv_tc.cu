@@ -1092,17 +1092,22 @@ int conv_tc_launch(Pass pass, int dtype, const Geom& g, const void* w, const voi
         const size_t total = (size_t)pl.LK * g.Nb * pl.Hp * pl.Wp * (pl.Cp / 8);
         const int blocks = (int)((total + 255) / 256 < (size_t)sm_count() * 16 ? (total + 255) / 256 : (size_t)sm_count() * 16);
         (void)blocks;
+        // the filter matrix is packed beside the staging pass, on the side stream (neither reads what the other writes): the
+        // side stream is forked off before the staging kernel is enqueued and joined before the convolution kernel
+        SideStream& ss = side_stream();
+        const cudaStream_t wstream = direct ? stream : ss.fork(stream);
         if (!direct)
             stage_activations(fmt, act, xp, pl.LK * g.Nb, pl.Cin, pl.Hin, pl.Win, pl.Hp, pl.Wp, pl.Cp, pl.pad_top, pl.pad_left, pl.ins_h, pl.ins_w, stream,
                               0, 1, g.plain ? nullptr : &sa);
         const FilterStrides fs = {g.wr, g.wo, g.wi, g.wh, g.ww, g.KW};
         if (fmt == 0) {
             pack_filters<__half>((const __half*)w, (__half*)wexp, g.Co, g.Ci, taps, pl.Mp, pl.Kp, pl.Cp, pass == PASS_BWD_DATA ? 1 : 0, g.nc, g.ga, g.neg, fs,
-                                 stream);
+                                 wstream);
         } else {
             pack_filters<__nv_bfloat16>((const __nv_bfloat16*)w, (__nv_bfloat16*)wexp, g.Co, g.Ci, taps, pl.Mp, pl.Kp, pl.Cp,
-                                        pass == PASS_BWD_DATA ? 1 : 0, g.nc, g.ga, g.neg, fs, stream);
+                                        pass == PASS_BWD_DATA ? 1 : 0, g.nc, g.ga, g.neg, fs, wstream);
         }
+        ss.join(stream, wstream);
         PCB_CUDA_TRY(cudaGetLastError());
     }
 

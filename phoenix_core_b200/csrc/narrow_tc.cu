@@ -549,6 +549,10 @@ int narrow_tc_launch(Pass pass, int dtype, const Geom& g, const void* w, const v
         const int blocks = grid_cap(total, 256, 16), wblocks = grid_cap((size_t)taps * NM * Kp, 256, 8);
         const bool fast = !pl.s2d && pack_rows_px(act, pl.Win, pl.Wp, pl.pad_left, pl.ins_h, pl.ins_w) == 4;
         const int fblocks = grid_cap(total / 4 + 1, 256, 16);
+        // the filter matrix is packed beside the staging pass, on the side stream (neither reads what the other writes): the
+        // side stream is forked off before the staging kernel is enqueued and joined before the convolution kernel
+        SideStream& ss = side_stream();
+        const cudaStream_t wstream = ss.fork(stream);
         if (fast && fmt == 0) {
             pack_rows_kernel<__half, 4><<<fblocks, 256, 0, stream>>>((const __half*)act, (__half*)xp, pl.LK * g.Nb, src_c, pl.Hin, pl.Win, pl.Hp, pl.Wp, 2,
                                                                   pl.pad_top, pl.pad_left, 1);
@@ -562,10 +566,11 @@ int narrow_tc_launch(Pass pass, int dtype, const Geom& g, const void* w, const v
             pack_planar_kernel<__nv_bfloat16><<<blocks, 256, 0, stream>>>((const __nv_bfloat16*)act, (__nv_bfloat16*)xp, pl.LK * g.Nb, src_c, pl.Hin,
                                                                          pl.Win, pl.Hp, pl.Wp, 2, pl.pad_top, pl.pad_left, pl.ins_h, pl.ins_w, pl.s2d);
         }
-        if (fmt == 0) pack_filters_planar_kernel<__half><<<wblocks, 256, 0, stream>>>((const __half*)w, (__half*)wexp, g.Co, g.Ci, taps, Kp,
-                                                                                      pass == PASS_BWD_DATA ? 1 : 0, g.nc, g.ga, g.neg, pl.s2d, g.KH, g.KW, pl.KWe);
-        else pack_filters_planar_kernel<__nv_bfloat16><<<wblocks, 256, 0, stream>>>((const __nv_bfloat16*)w, (__nv_bfloat16*)wexp, g.Co, g.Ci, taps, Kp,
-                                                                                    pass == PASS_BWD_DATA ? 1 : 0, g.nc, g.ga, g.neg, pl.s2d, g.KH, g.KW, pl.KWe);
+        if (fmt == 0) pack_filters_planar_kernel<__half><<<wblocks, 256, 0, wstream>>>((const __half*)w, (__half*)wexp, g.Co, g.Ci, taps, Kp,
+                                                                                       pass == PASS_BWD_DATA ? 1 : 0, g.nc, g.ga, g.neg, pl.s2d, g.KH, g.KW, pl.KWe);
+        else pack_filters_planar_kernel<__nv_bfloat16><<<wblocks, 256, 0, wstream>>>((const __nv_bfloat16*)w, (__nv_bfloat16*)wexp, g.Co, g.Ci, taps, Kp,
+                                                                                     pass == PASS_BWD_DATA ? 1 : 0, g.nc, g.ga, g.neg, pl.s2d, g.KH, g.KW, pl.KWe);
+        ss.join(stream, wstream);
         PCB_CUDA_TRY(cudaGetLastError());
     }
     NParams p;

@@ -124,6 +124,40 @@ __global__ void pack_rows_kernel(const T* __restrict__ x, T* __restrict__ xp, in
             for (int wp = pad_left + W; wp < Wp; ++wp) *reinterpret_cast<uint4*>(dst(wp)) = zero;
     }
 }
+// A side stream per host thread and device, for a prologue kernel that is independent of its neighbour: the filter matrix
+// is packed beside the staging of the activations instead of after it (both are short, one bound by memory, the other by
+// latency). fork() orders the side stream after everything enqueued so far on the caller's stream and returns it; join()
+// makes the caller's stream wait for it. Where the side stream cannot be made the caller's stream is returned and join()
+// does nothing. The fork / join pattern is also what stream capture expects.
+struct SideStream {
+    cudaStream_t side = nullptr;
+    cudaEvent_t forked = nullptr, joined = nullptr;
+    bool tried = false;
+    cudaStream_t fork(cudaStream_t main) {
+        if (!tried) {
+            tried = true;
+            if (cudaStreamCreateWithFlags(&side, cudaStreamNonBlocking) != cudaSuccess) side = nullptr;
+            if (side && (cudaEventCreateWithFlags(&forked, cudaEventDisableTiming) != cudaSuccess ||
+                         cudaEventCreateWithFlags(&joined, cudaEventDisableTiming) != cudaSuccess)) side = nullptr;
+            if (!side) (void)cudaGetLastError();
+        }
+        if (!side) return main;
+        if (cudaEventRecord(forked, main) != cudaSuccess || cudaStreamWaitEvent(side, forked, 0) != cudaSuccess) { (void)cudaGetLastError(); return main; }
+        return side;
+    }
+    void join(cudaStream_t main, cudaStream_t used) {
+        if (used == main) return;
+        cudaEventRecord(joined, used);
+        cudaStreamWaitEvent(main, joined, 0);
+    }
+};
+inline SideStream& side_stream() {
+    static thread_local SideStream per_device[16];
+    int dev = 0;
+    if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 16) dev = 0;
+    return per_device[dev];
+}
+
 // Pixels per thread pack_rows_kernel can take for this tensor: 4, 2, or 0 (the general staging kernel must run).
 inline int pack_rows_px(const void* x, int W, int Wp, int pad_left, int ins_h, int ins_w) {
     if (ins_h != 1 || ins_w != 1 || pad_left < 0 || pad_left + W > Wp) return 0;
