@@ -1,6 +1,7 @@
 // Helpers shared by the TMA-fed tcgen05 kernels: TMA load wrappers, wide stores, the tensor-map encoder
 // (fetched from the driver at run time, so the library does not link against libcuda), small host utilities.
 #pragma once
+#include <cstdlib>
 
 #include <cuda.h>
 
@@ -136,6 +137,8 @@ struct SideStream {
     cudaStream_t fork(cudaStream_t main) {
         if (!tried) {
             tried = true;
+            const char* off = getenv("PCB_NO_SIDE_STREAM");      // escape hatch: everything on the caller's stream
+            if (off && off[0] && off[0] != '0') return main;
             if (cudaStreamCreateWithFlags(&side, cudaStreamNonBlocking) != cudaSuccess) side = nullptr;
             if (side && (cudaEventCreateWithFlags(&forked, cudaEventDisableTiming) != cudaSuccess ||
                          cudaEventCreateWithFlags(&joined, cudaEventDisableTiming) != cudaSuccess)) side = nullptr;

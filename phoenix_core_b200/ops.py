@@ -50,7 +50,7 @@ class Device:
             return dev
 
     def requestWorkspace(self, nbytes):
-        key = torch.cuda.current_stream(self.index).cuda_stream
+        key = _raw_stream(self.index)
         ws = self.workspaces.get(key)
         if ws is None or ws.numel() < nbytes:
             with torch.cuda.device(self.index):
@@ -60,7 +60,7 @@ class Device:
 
     @property
     def workspace(self):
-        return self.workspaces.get(torch.cuda.current_stream(self.index).cuda_stream)
+        return self.workspaces.get(_raw_stream(self.index))
 
     def checkStatus(self):
         """Raises BackendError(PCB_ERR_DEVICE_TIMEOUT) if a bounded device-side wait expired in the last operation
@@ -113,8 +113,40 @@ def _check_tensor(t, name, dtype=None, shape=None):
         raise ValueError("%s shape mismatch: %s vs expected %s" % (name, tuple(t.shape), tuple(shape)))
 
 
-def _stream():
-    return ctypes.c_void_p(torch.cuda.current_stream().cuda_stream)
+def _raw_stream(index=None):
+    """The current CUDA stream of a device as an integer handle (the fast path of ``torch.cuda.current_stream``, which
+    builds a Python stream object on every call)."""
+    if index is None:
+        index = torch.cuda.current_device()
+    getter = getattr(torch._C, "_cuda_getCurrentRawStream", None)
+    if getter is not None:
+        return getter(index)
+    return torch.cuda.current_stream(index).cuda_stream
+
+
+def _stream(index=None):
+    return ctypes.c_void_p(_raw_stream(index))
+
+
+class _OnDevice:
+    """``torch.cuda.device(index)`` that does nothing when the device already is the current one (the usual case)."""
+
+    __slots__ = ("index", "guard")
+
+    def __init__(self, index):
+        self.index, self.guard = index, None
+
+    def __enter__(self):
+        if torch.cuda.current_device() != self.index:
+            self.guard = torch.cuda.device(self.index)
+            self.guard.__enter__()
+        return self
+
+    def __exit__(self, *exc):
+        if self.guard is not None:
+            self.guard.__exit__(*exc)
+            self.guard = None
+        return False
 
 
 # upstride::Algebra -> pcb_algebra (the C ABI keeps quaternion at zero)
@@ -126,6 +158,17 @@ _FILTER_LAYOUTS = {FilterLayout.OIHW: 0, FilterLayout.OHWI: 1, FilterLayout.HWIO
 
 
 def _conv_desc(descriptor, dtype, context, engine, has_bias=False, require_input_grad=False):
+    """The C descriptor of a call; built once per (descriptor object, dtype, context settings, engine, flags) and kept on
+    the descriptor object (descriptors do not change after construction)."""
+    key = (dtype, context.variant(), int(context.conv_fp16_policy), engine, bool(has_bias), bool(require_input_grad))
+    cache = descriptor.__dict__.setdefault("_pcb_conv_desc", {})
+    d = cache.get(key)
+    if d is None:
+        d = cache[key] = _build_conv_desc(descriptor, dtype, context, engine, has_bias, require_input_grad)
+    return d
+
+
+def _build_conv_desc(descriptor, dtype, context, engine, has_bias, require_input_grad):
     algebra = descriptor.getAlgebra()
     dim = MULTIVECTOR_DIM[algebra]
     data_format, filter_layout = descriptor.getDataFormat(), descriptor.getFilterLayout()
@@ -179,9 +222,12 @@ def conv2DFwd(inputTensor, filterTensor, biasTensor, outputTensor, descriptor, c
         return      # empty input: silent no-op (reference src/conv2d.hpp:81-82)
     d = _conv_desc(descriptor, inputTensor.dtype, context, engine, has_bias=biasTensor is not None)
     L = _lib.lib()
-    with dev.accessControl, torch.cuda.device(dev.index):
-        need = L.pcb_qconv2d_fwd_workspace_size(ctypes.byref(d))
-        if keep is not None and L.pcb_qconv2d_fwd_keeps_input(ctypes.byref(d)):
+    with dev.accessControl, _OnDevice(dev.index):
+        need = getattr(d, "_fwd_need", None)           # both queries depend on the descriptor alone: asked once
+        if need is None:
+            need = d._fwd_need = L.pcb_qconv2d_fwd_workspace_size(ctypes.byref(d))
+            d._keeps = bool(L.pcb_qconv2d_fwd_keeps_input(ctypes.byref(d)))
+        if keep is not None and d._keeps:
             if keep.workspace is None or keep.workspace.numel() < need or keep.workspace.device != inputTensor.device:
                 keep.workspace = torch.empty(need, dtype=torch.uint8, device=inputTensor.device)
             ws = keep.workspace
@@ -216,8 +262,10 @@ def conv2DBwd(inputTensor, filterTensor, gradTensor, filterGradTensor, inputGrad
         return
     d = _conv_desc(descriptor, inputTensor.dtype, context, engine, require_input_grad=need_dx)
     L = _lib.lib()
-    with dev.accessControl, torch.cuda.device(dev.index):
-        need = L.pcb_qconv2d_bwd_workspace_size(ctypes.byref(d))
+    with dev.accessControl, _OnDevice(dev.index):
+        need = getattr(d, "_bwd_need", None)
+        if need is None:
+            need = d._bwd_need = L.pcb_qconv2d_bwd_workspace_size(ctypes.byref(d))
         ws = dev.requestWorkspace(need)
         if kept is not None and kept.workspace is not None and on_filter_grad is None:
             _lib.check(L.pcb_qconv2d_bwd_kept(ctypes.byref(d), _ptr(inputTensor), _ptr(filterTensor), _ptr(gradTensor),
@@ -274,7 +322,7 @@ def denseFwd(inputTensor, filterTensor, biasTensor, outputTensor, descriptor, co
         return
     d = _dense_desc(descriptor, inputTensor.dtype, context, engine, has_bias=biasTensor is not None)
     L = _lib.lib()
-    with dev.accessControl, torch.cuda.device(dev.index):
+    with dev.accessControl, _OnDevice(dev.index):
         need = L.pcb_qdense_fwd_workspace_size(ctypes.byref(d))
         ws = dev.requestWorkspace(need)
         _lib.check(L.pcb_qdense_fwd(ctypes.byref(d), _ptr(inputTensor), _ptr(filterTensor), _ptr(biasTensor),
@@ -302,7 +350,7 @@ def denseBwd(inputTensor, filterTensor, gradTensor, filterGradTensor, inputGradT
         return
     d = _dense_desc(descriptor, inputTensor.dtype, context, engine, require_input_grad=need_dx)
     L = _lib.lib()
-    with dev.accessControl, torch.cuda.device(dev.index):
+    with dev.accessControl, _OnDevice(dev.index):
         need = L.pcb_qdense_bwd_workspace_size(ctypes.byref(d))
         ws = dev.requestWorkspace(need)
         _lib.check(L.pcb_qdense_bwd(ctypes.byref(d), _ptr(inputTensor), _ptr(filterTensor), _ptr(gradTensor),

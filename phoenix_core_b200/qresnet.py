@@ -32,6 +32,7 @@ if ROOT not in sys.path:
 
 import phoenix_core_b200 as pcb  # noqa: E402
 from phoenix_core_b200 import _lib  # noqa: E402
+from phoenix_core_b200.ops import _raw_stream  # noqa: E402
 from phoenix_core_b200.context import Context  # noqa: E402
 
 LOSS_SCALE = 256.0
@@ -73,7 +74,7 @@ class _BNReLUFn(torch.autograd.Function):
             scratch = torch.empty(5 * c, dtype=torch.float32, device=x.device)
             _lib.check(_lib.lib().pcb_aux_bn_relu_fwd(_DT[x.dtype], x.data_ptr(), gamma.data_ptr(), beta.data_ptr(), y.data_ptr(),
                                                       mean.data_ptr(), invstd.data_ptr(), scratch.data_ptr(), planes, c, hw, eps, int(relu),
-                                                      torch.cuda.current_stream().cuda_stream))
+                                                      _raw_stream()))
             ctx.fused = True
             # the backward kernels recompute the ReLU mask from x, so the output is not kept for them
             ctx.save_for_backward(x, None, mean, invstd, gamma, beta)
@@ -104,12 +105,12 @@ class _BNReLUFn(torch.autograd.Function):
                 _lib.check(_lib.lib().pcb_aux_bn_relu_bwd_from_input(_DT[x.dtype], x.data_ptr(), dy.data_ptr(), gamma.data_ptr(), beta.data_ptr(),
                                                                      mean.data_ptr(), invstd.data_ptr(), dx.data_ptr(), dgamma.data_ptr(),
                                                                      dbeta.data_ptr(), scratch.data_ptr(), planes, c, hw,
-                                                                     torch.cuda.current_stream().cuda_stream))
+                                                                     _raw_stream()))
                 return dx, dgamma, dbeta, None, None
             _lib.check(_lib.lib().pcb_aux_bn_relu_bwd(_DT[x.dtype], x.data_ptr(), y.data_ptr() if ctx.relu else None, dy.data_ptr(),
                                                       gamma.data_ptr(), mean.data_ptr(), invstd.data_ptr(), dx.data_ptr(), dgamma.data_ptr(),
                                                       dbeta.data_ptr(), scratch.data_ptr(), planes, c, hw, int(ctx.relu),
-                                                      torch.cuda.current_stream().cuda_stream))
+                                                      _raw_stream()))
             return dx, dgamma, dbeta, None, None
         g = dy * (y > 0) if ctx.relu else dy
         m = x.numel() // x.shape[1]
@@ -143,7 +144,7 @@ class _BNAddReLUFn(torch.autograd.Function):
         scratch = torch.empty(5 * c, dtype=torch.float32, device=x.device)
         _lib.check(_lib.lib().pcb_aux_bn_add_relu_fwd(_DT[x.dtype], x.data_ptr(), residual.data_ptr(), gamma.data_ptr(), beta.data_ptr(),
                                                       y.data_ptr(), mean.data_ptr(), invstd.data_ptr(), scratch.data_ptr(), planes, c, hw, eps,
-                                                      torch.cuda.current_stream().cuda_stream))
+                                                      _raw_stream()))
         ctx.save_for_backward(x, y, mean, invstd, gamma)
         return y
 
@@ -159,7 +160,7 @@ class _BNAddReLUFn(torch.autograd.Function):
         scratch = torch.empty(5 * c, dtype=torch.float32, device=x.device)
         _lib.check(_lib.lib().pcb_aux_bn_add_relu_bwd(_DT[x.dtype], x.data_ptr(), y.data_ptr(), dy.data_ptr(), gamma.data_ptr(), mean.data_ptr(),
                                                       invstd.data_ptr(), dx.data_ptr(), dres.data_ptr(), dgamma.data_ptr(), dbeta.data_ptr(),
-                                                      scratch.data_ptr(), planes, c, hw, torch.cuda.current_stream().cuda_stream))
+                                                      scratch.data_ptr(), planes, c, hw, _raw_stream()))
         return dx, dres, dgamma, dbeta, None
 
 
@@ -178,7 +179,7 @@ class _BNReLUPoolFn(torch.autograd.Function):
         scratch = torch.empty(5 * c, dtype=torch.float32, device=x.device)
         _lib.check(_lib.lib().pcb_aux_bn_relu_maxpool_fwd(_DT[x.dtype], x.data_ptr(), gamma.data_ptr(), beta.data_ptr(), y.data_ptr(), arg.data_ptr(),
                                                           mean.data_ptr(), invstd.data_ptr(), scratch.data_ptr(), planes, c, h, w, eps,
-                                                          torch.cuda.current_stream().cuda_stream))
+                                                          _raw_stream()))
         ctx.save_for_backward(x, arg, mean, invstd, gamma, beta)
         return y
 
@@ -193,7 +194,7 @@ class _BNReLUPoolFn(torch.autograd.Function):
         scratch = torch.empty(5 * c, dtype=torch.float32, device=x.device)
         _lib.check(_lib.lib().pcb_aux_bn_relu_maxpool_bwd(_DT[x.dtype], x.data_ptr(), dy.data_ptr(), arg.data_ptr(), gamma.data_ptr(), beta.data_ptr(),
                                                           mean.data_ptr(), invstd.data_ptr(), dx.data_ptr(), dgamma.data_ptr(), dbeta.data_ptr(),
-                                                          scratch.data_ptr(), planes, c, h, w, torch.cuda.current_stream().cuda_stream))
+                                                          scratch.data_ptr(), planes, c, h, w, _raw_stream()))
         return dx, dgamma, dbeta, None
 
 
@@ -207,7 +208,7 @@ class _MaxPoolFn(torch.autograd.Function):
         y = torch.empty((x.shape[0], x.shape[1], (h - 1) // 2 + 1, (w - 1) // 2 + 1), dtype=x.dtype, device=x.device)
         arg = torch.empty(y.shape, dtype=torch.uint8, device=x.device)
         _lib.check(_lib.lib().pcb_aux_maxpool3x3s2_fwd(_DT[x.dtype], x.data_ptr(), y.data_ptr(), arg.data_ptr(), rows, h, w,
-                                                       torch.cuda.current_stream().cuda_stream))
+                                                       _raw_stream()))
         ctx.save_for_backward(arg)
         ctx.shape = x.shape
         return y
@@ -218,7 +219,7 @@ class _MaxPoolFn(torch.autograd.Function):
         dy = dy.contiguous()
         dx = torch.empty(ctx.shape, dtype=dy.dtype, device=dy.device)
         _lib.check(_lib.lib().pcb_aux_maxpool3x3s2_bwd(_DT[dy.dtype], dy.data_ptr(), arg.data_ptr(), dx.data_ptr(), ctx.shape[0] * ctx.shape[1],
-                                                       ctx.shape[2], ctx.shape[3], torch.cuda.current_stream().cuda_stream))
+                                                       ctx.shape[2], ctx.shape[3], _raw_stream()))
         return dx
 
 
