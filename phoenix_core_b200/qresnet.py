@@ -63,8 +63,11 @@ class _BNReLUFn(torch.autograd.Function):
     three passes over the data forward, seven backward); anything else takes plain torch reductions."""
 
     @staticmethod
-    def forward(ctx, x, gamma, beta, eps, relu):
+    def forward(ctx, x, gamma, beta, eps, relu, grad_out=None):
+        """`grad_out` = (dgamma, dbeta) buffers of the caller: the backward kernels write the parameter gradients there and
+        autograd is given none for them (the model keeps all batch-norm parameters and gradients in flat buffers)."""
         ctx.relu = relu
+        ctx.grad_out = grad_out
         if x.is_cuda and x.dtype in (torch.float16, torch.bfloat16) and x.is_contiguous():
             planes, c = x.shape[0], x.shape[1]
             hw = x.numel() // (planes * c)
@@ -98,20 +101,23 @@ class _BNReLUFn(torch.autograd.Function):
             planes, c = x.shape[0], x.shape[1]
             hw = x.numel() // (planes * c)
             dx = torch.empty_like(x)
-            dgamma = torch.empty(c, dtype=torch.float32, device=x.device)
-            dbeta = torch.empty_like(dgamma)
+            if ctx.grad_out is not None:
+                dgamma, dbeta = ctx.grad_out
+            else:
+                dgamma = torch.empty(c, dtype=torch.float32, device=x.device)
+                dbeta = torch.empty_like(dgamma)
             scratch = torch.empty(5 * c, dtype=torch.float32, device=x.device)
             if ctx.relu:
                 _lib.check(_lib.lib().pcb_aux_bn_relu_bwd_from_input(_DT[x.dtype], x.data_ptr(), dy.data_ptr(), gamma.data_ptr(), beta.data_ptr(),
                                                                      mean.data_ptr(), invstd.data_ptr(), dx.data_ptr(), dgamma.data_ptr(),
                                                                      dbeta.data_ptr(), scratch.data_ptr(), planes, c, hw,
                                                                      _raw_stream()))
-                return dx, dgamma, dbeta, None, None
+                return (dx, None, None, None, None, None) if ctx.grad_out is not None else (dx, dgamma, dbeta, None, None, None)
             _lib.check(_lib.lib().pcb_aux_bn_relu_bwd(_DT[x.dtype], x.data_ptr(), y.data_ptr() if ctx.relu else None, dy.data_ptr(),
                                                       gamma.data_ptr(), mean.data_ptr(), invstd.data_ptr(), dx.data_ptr(), dgamma.data_ptr(),
                                                       dbeta.data_ptr(), scratch.data_ptr(), planes, c, hw, int(ctx.relu),
                                                       _raw_stream()))
-            return dx, dgamma, dbeta, None, None
+            return (dx, None, None, None, None, None) if ctx.grad_out is not None else (dx, dgamma, dbeta, None, None, None)
         g = dy * (y > 0) if ctx.relu else dy
         m = x.numel() // x.shape[1]
         sum_g = g.sum(dim=(0, 2, 3), dtype=torch.float32)
@@ -126,7 +132,11 @@ class _BNReLUFn(torch.autograd.Function):
         dx = g * a.to(g.dtype).view(1, -1, 1, 1)
         dx.addcmul_(x, b.to(g.dtype).view(1, -1, 1, 1))
         dx.add_(c.to(g.dtype).view(1, -1, 1, 1))
-        return dx, dgamma, dbeta, None, None
+        if ctx.grad_out is not None:
+            ctx.grad_out[0].copy_(dgamma)
+            ctx.grad_out[1].copy_(dbeta)
+            return dx, None, None, None, None, None
+        return dx, dgamma, dbeta, None, None, None
 
 
 class _BNAddReLUFn(torch.autograd.Function):
@@ -135,7 +145,8 @@ class _BNAddReLUFn(torch.autograd.Function):
     16-bit contiguous CUDA tensors only; the caller falls back to the separate operations otherwise."""
 
     @staticmethod
-    def forward(ctx, x, residual, gamma, beta, eps):
+    def forward(ctx, x, residual, gamma, beta, eps, grad_out=None):
+        ctx.grad_out = grad_out
         planes, c = x.shape[0], x.shape[1]
         hw = x.numel() // (planes * c)
         y = torch.empty_like(x)
@@ -155,13 +166,16 @@ class _BNAddReLUFn(torch.autograd.Function):
         planes, c = x.shape[0], x.shape[1]
         hw = x.numel() // (planes * c)
         dx, dres = torch.empty_like(x), torch.empty_like(x)
-        dgamma = torch.empty(c, dtype=torch.float32, device=x.device)
-        dbeta = torch.empty_like(dgamma)
+        if ctx.grad_out is not None:
+            dgamma, dbeta = ctx.grad_out
+        else:
+            dgamma = torch.empty(c, dtype=torch.float32, device=x.device)
+            dbeta = torch.empty_like(dgamma)
         scratch = torch.empty(5 * c, dtype=torch.float32, device=x.device)
         _lib.check(_lib.lib().pcb_aux_bn_add_relu_bwd(_DT[x.dtype], x.data_ptr(), y.data_ptr(), dy.data_ptr(), gamma.data_ptr(), mean.data_ptr(),
                                                       invstd.data_ptr(), dx.data_ptr(), dres.data_ptr(), dgamma.data_ptr(), dbeta.data_ptr(),
                                                       scratch.data_ptr(), planes, c, hw, _raw_stream()))
-        return dx, dres, dgamma, dbeta, None
+        return (dx, dres, None, None, None, None) if ctx.grad_out is not None else (dx, dres, dgamma, dbeta, None, None)
 
 
 class _BNReLUPoolFn(torch.autograd.Function):
@@ -170,7 +184,8 @@ class _BNReLUPoolFn(torch.autograd.Function):
     large tensor instead of thirteen). 16-bit contiguous CUDA tensors with lines of a multiple of 8 pixels."""
 
     @staticmethod
-    def forward(ctx, x, gamma, beta, eps):
+    def forward(ctx, x, gamma, beta, eps, grad_out=None):
+        ctx.grad_out = grad_out
         planes, c, h, w = x.shape
         y = torch.empty((planes, c, h // 2, w // 2), dtype=x.dtype, device=x.device)
         arg = torch.empty(y.shape, dtype=torch.uint8, device=x.device)
@@ -189,13 +204,16 @@ class _BNReLUPoolFn(torch.autograd.Function):
         dy = dy.contiguous()
         planes, c, h, w = x.shape
         dx = torch.empty_like(x)
-        dgamma = torch.empty(c, dtype=torch.float32, device=x.device)
-        dbeta = torch.empty_like(dgamma)
+        if ctx.grad_out is not None:
+            dgamma, dbeta = ctx.grad_out
+        else:
+            dgamma = torch.empty(c, dtype=torch.float32, device=x.device)
+            dbeta = torch.empty_like(dgamma)
         scratch = torch.empty(5 * c, dtype=torch.float32, device=x.device)
         _lib.check(_lib.lib().pcb_aux_bn_relu_maxpool_bwd(_DT[x.dtype], x.data_ptr(), dy.data_ptr(), arg.data_ptr(), gamma.data_ptr(), beta.data_ptr(),
                                                           mean.data_ptr(), invstd.data_ptr(), dx.data_ptr(), dgamma.data_ptr(), dbeta.data_ptr(),
                                                           scratch.data_ptr(), planes, c, h, w, _raw_stream()))
-        return dx, dgamma, dbeta, None
+        return (dx, None, None, None, None) if ctx.grad_out is not None else (dx, dgamma, dbeta, None, None)
 
 
 class _MaxPoolFn(torch.autograd.Function):
@@ -230,24 +248,36 @@ def max_pool_3x3_s2(x):
 
 
 class BNReLU:
-    def __init__(self, c, device, relu):
-        self.weight = torch.ones(c, dtype=torch.float32, device=device, requires_grad=True)
-        self.bias = torch.zeros(c, dtype=torch.float32, device=device, requires_grad=True)
+    """Batch-norm (+ ReLU) layer. Standalone (`flat` = None) it owns its parameters as autograd leaves; inside the model
+    its parameters and their gradients are slices of the model's flat fp32 buffers (`flat` = (weights, gradients, offset)),
+    the backward kernels write the gradients straight into their slices, and autograd sees no parameter at all."""
+
+    def __init__(self, c, device, relu, flat=None):
         self.relu = relu
+        self.grad_out = None
+        if flat is None:
+            self.weight = torch.ones(c, dtype=torch.float32, device=device, requires_grad=True)
+            self.bias = torch.zeros(c, dtype=torch.float32, device=device, requires_grad=True)
+        else:
+            w, g, off = flat
+            self.weight, self.bias = w[off:off + c], w[off + c:off + 2 * c]
+            self.weight.fill_(1.0)
+            self.bias.zero_()
+            self.grad_out = (g[off:off + c], g[off + c:off + 2 * c])
 
     def __call__(self, x, relu=None):
-        return _BNReLUFn.apply(x, self.weight, self.bias, 1e-5, self.relu if relu is None else relu)
+        return _BNReLUFn.apply(x, self.weight, self.bias, 1e-5, self.relu if relu is None else relu, self.grad_out)
 
     def relu_pool(self, x):
         """max_pool_3x3_s2(relu(batch_norm(x)))."""
         if x.is_cuda and x.dtype in _DT and x.is_contiguous() and x.shape[2] % 2 == 0 and x.shape[3] % 8 == 0:
-            return _BNReLUPoolFn.apply(x, self.weight, self.bias, 1e-5)
+            return _BNReLUPoolFn.apply(x, self.weight, self.bias, 1e-5, self.grad_out)
         return max_pool_3x3_s2(self(x, relu=True))
 
     def add_relu(self, x, residual):
         """relu(batch_norm(x) + residual)."""
         if x.is_cuda and x.dtype in _DT and x.is_contiguous() and residual.is_contiguous() and residual.shape == x.shape and residual.dtype == x.dtype:
-            return _BNAddReLUFn.apply(x, residual, self.weight, self.bias, 1e-5)
+            return _BNAddReLUFn.apply(x, residual, self.weight, self.bias, 1e-5, self.grad_out)
         return F.relu_(self(x, relu=False) + residual)
 
 
@@ -364,6 +394,10 @@ class QResNet18:
         self.gen = torch.Generator(device=device).manual_seed(seed)
         self._numel = 0
         self.convs, self.bns = [], []
+        # batch-norm parameters, their gradients and momenta: flat fp32 buffers (gamma and beta of a layer side by side)
+        self._bn_numel = 0
+        self.bn_w = torch.empty(8192, dtype=torch.float32, device=device)
+        self.bn_g = torch.zeros(8192, dtype=torch.float32, device=device)
         # the stem takes the RGB image as a real-valued (type-0) input: only the real component exists, which is the
         # engine's own way of entering the quaternion domain (reference src/conv2d.hpp:122-164) and a quarter of the work
         self.conv1 = self._conv(3, 16, 7, 2, real_input=True)
@@ -390,8 +424,8 @@ class QResNet18:
         for c in self.convs:
             c.bind()
         self.fc.bind()
-        self.bn_params = [p for bn in self.bns for p in (bn.weight, bn.bias)]
-        self.bn_opt = torch.optim.SGD(self.bn_params, lr=0.1, momentum=0.9)
+        self.bn_w, self.bn_g = self.bn_w[:self._bn_numel], self.bn_g[:self._bn_numel]
+        self.bn_m = torch.zeros_like(self.bn_w)
         # Data-parallel exchange in two parts. The flat bucket is laid out in forward order, so the last stage and the
         # classifier (72 % of the parameters) are its tail, and their gradients are complete when the backward pass
         # reaches the last convolution of stage 3: that layer's backward hook starts the tail's all-reduce on a side
@@ -421,7 +455,8 @@ class QResNet18:
         return c
 
     def _bn(self, c, relu=True):
-        bn = BNReLU(c, self.device, relu)
+        bn = BNReLU(c, self.device, relu, flat=(self.bn_w, self.bn_g, self._bn_numel))
+        self._bn_numel += 2 * c
         self.bns.append(bn)
         return bn
 
@@ -443,22 +478,50 @@ class QResNet18:
         y = self.fc(x.contiguous())                              # [4N, 250]
         return y.view(4, n, -1).permute(1, 0, 2).reshape(n, -1)  # class index = component * 250 + unit
 
+    def capture(self, images, labels, lr=0.1, momentum=0.9):
+        """Captures one single-GPU training step (forward, loss, backward, update) as a CUDA graph over static copies of
+        the batch; `step` then replays it. The step is ~400 launches behind ~4.7 ms of Python per step against ~6.5 ms
+        of kernels, so an eager loop turns host-bound as soon as the host is slower than usual; the replay is one launch.
+        Returns False (and stays eager) if the capture fails."""
+        self.graph = None
+        try:
+            # the caller has run a few eager steps (workspaces grown, kernels loaded); every parameter gradient is written by
+            # the kernels into flat buffers, so autograd holds no accumulation node tied to another stream
+            self.static_images, self.static_labels = images.clone(), labels.clone()
+            torch.cuda.synchronize()
+            graph = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(graph):
+                self.static_loss = self.train_step(self.static_images, self.static_labels, 1, lr, momentum)
+            self.graph = graph
+        except Exception as err:                                # noqa: BLE001 -- any capture problem: run eagerly
+            sys.stderr.write("qresnet: CUDA graph capture failed (%s); running eagerly\n" % (err,))
+            self.graph = None
+            torch.cuda.synchronize()
+        return self.graph is not None
+
+    def step(self, images, labels, world=1, lr=0.1, momentum=0.9):
+        """One training step: the captured graph if there is one (single GPU), the eager step otherwise."""
+        if world == 1 and getattr(self, "graph", None) is not None:
+            if images.data_ptr() != self.static_images.data_ptr():
+                self.static_images.copy_(images, non_blocking=True)
+                self.static_labels.copy_(labels, non_blocking=True)
+            self.graph.replay()
+            return self.static_loss
+        return self.train_step(images, labels, world, lr, momentum)
+
     def train_step(self, images, labels, world=1, lr=0.1, momentum=0.9):
         self.flat_w16.copy_(self.flat_w32)
         self.world, self.pending = world, None
         logits = self.forward(images)
         loss = F.cross_entropy(logits.float(), labels)
-        self.bn_opt.zero_grad(set_to_none=True)
         (loss * LOSS_SCALE).backward()
         reduce_and_apply(self.flat_w32, self.flat_mom, self.flat_g16, world, lr, momentum, LOSS_SCALE, self.split, self.pending)
         self.pending = None
-        grads = [p.grad for p in self.bn_params]                  # 40 small tensors: multi-tensor kernels, not one launch each
+        # the batch-norm parameters: one flat gradient buffer (written by the backward kernels), one all-reduce, one update
         if world > 1:
-            bn_flat = torch.cat([g.reshape(-1) for g in grads])
-            dist.all_reduce(bn_flat)
-            torch._foreach_copy_(grads, [t.view_as(g) for t, g in zip(bn_flat.split([g.numel() for g in grads]), grads)])
-        torch._foreach_mul_(grads, 1.0 / (LOSS_SCALE * world))
-        self.bn_opt.step()
+            dist.all_reduce(self.bn_g)
+        self.bn_m.mul_(momentum).add_(self.bn_g, alpha=1.0 / (LOSS_SCALE * world))
+        self.bn_w.add_(self.bn_m, alpha=-lr)
         return loss
 
 
@@ -545,10 +608,16 @@ def run(batch, steps, warmup, image=224, quiet=False):
     for _ in range(max(5, warmup)):                              # the first steps grow the device workspace
         loss = model.train_step(images, labels, world)
     sync()
+    graphed = False
+    if world == 1 and os.environ.get("PCB_QRESNET_GRAPH", "1") not in ("", "0"):
+        graphed = model.capture(images, labels)
+        for _ in range(2):
+            loss = model.step(images, labels, world)
+        sync()
     e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     e0.record()
     for _ in range(steps):
-        loss = model.train_step(images, labels, world)
+        loss = model.step(images, labels, world)
     e1.record()
     sync()
     ms = e0.elapsed_time(e1)
@@ -577,7 +646,7 @@ def run(batch, steps, warmup, image=224, quiet=False):
         torch.cuda.current_stream().wait_event(ready[i & 1])
         if i + 1 < e2e_steps:
             prefetch(i + 1)
-        loss = model.train_step(bufs[i & 1][0], bufs[i & 1][1], world)
+        loss = model.step(bufs[i & 1][0], bufs[i & 1][1], world)
         used[i & 1].record()
         losses_host[i].copy_(loss.detach(), non_blocking=True)
     b.record()
@@ -594,7 +663,7 @@ def run(batch, steps, warmup, image=224, quiet=False):
         result = {"metric": "QResNet-18 train images/s", "value": ips, "unit": "images/s", "n_gpus": world, "steps": steps,
                   "ms_per_step": ms / steps, "batch_per_gpu": batch, "image": image, "dtype": "f16",
                   "tflops_conv": 3 * FWD_GFLOP_PER_IMAGE * (image / 224.0) ** 2 * ips / 1e3, "loss": loss_host,
-                  "parameters": model.num_parameters(),
+                  "parameters": model.num_parameters(), "cuda_graph": graphed,
                   "e2e": {"value": batch * world * e2e_steps / (e2e_ms * 1e-3), "unit": "images/s",
                           "h2d_bytes_per_step": host_images.numel() * 2 + host_labels.numel() * 8, "d2h_bytes_per_step": 4},
                   "glue": "convolutions and dense: this package only; batch-norm (+ residual add) + ReLU and max-pool: helper kernels of the library; loss / SGD: torch ops (none of these is in the reference)"}
