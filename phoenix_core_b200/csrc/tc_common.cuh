@@ -212,7 +212,9 @@ inline int sm_count() {
 
 inline int round_up(int v, int m) { return (v + m - 1) / m * m; }
 // Number of slices to cut each of `items` work items into when every CTA occupies a whole SM: the CTAs must fill
-// one, two or three rounds of the machine as exactly as possible (one CTA more than a round costs a whole round).
+// one, two or three rounds of the machine as exactly as possible (one CTA more than a round costs a whole round). A further
+// round also costs every CTA's fixed part again (tensor-memory allocation, pipeline fill, the atomic fold of its
+// accumulator), so it has to fill the machine at least 5 % better to be taken.
 inline int split_count(int items, int sms) {
     int best = 1;
     double best_util = 0.0;
@@ -220,7 +222,7 @@ inline int split_count(int items, int sms) {
         const int splits = waves * sms / items;
         if (splits < 1) continue;
         const double util = (double)items * splits / ((double)waves * sms);
-        if (util > best_util + 0.01) { best_util = util; best = splits; }
+        if (util > best_util + (best_util > 0.0 ? 0.05 : 0.0)) { best_util = util; best = splits; }
     }
     return best;
 }
