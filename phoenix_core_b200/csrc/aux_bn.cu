@@ -3,7 +3,11 @@
 // Batch-norm (+ ReLU) over stacked hyper-complex activations [planes = D*N, C, H, W]: one mean / variance per channel,
 // shared by the D components. Auxiliary kernels of the QResNet-18 harness -- the reference has no normalisation layer
 // (its TensorFlow plugin relies on TensorFlow's); they exist because the framework kernels launch one block per channel
-// and leave the GPU idle at 16 channels. Three passes over the data forward (statistics, apply), seven backward.
+// and leave the GPU idle at 16 channels. Three passes over the data forward (statistics; apply: read, write), five to seven
+// backward (statistics: x and dy, and the stored output where the ReLU mask cannot be recomputed from x; apply: the same
+// reads and one or two writes). Variants: the residual add of a block's tail inside the apply pass, the stem's max-pool
+// fused into the apply pass (the normalised tensor is never stored), flat 16-byte kernels for rows of 7 x 7 elements.
+// The per-channel coefficients are computed inside the apply kernels from the channel sums; there is no finalize launch.
 //
 // Every kernel sees the tensor as rows of HW contiguous elements, row r = plane * C + c.
 #include "common.cuh"
