@@ -519,7 +519,10 @@ __device__ __forceinline__ void pool_gather8(const T* __restrict__ dp, const uin
     }
 }
 
-// Backward sums (g, g * x) per channel with g gathered from the pooled gradient and masked by relu'(x * m0 + m1).
+// Backward sums (g, g * x) per channel, g being the pooled gradient routed to its arg-max pixel and masked by
+// relu'(x * m0 + m1). The sums run over the POOLED outputs: each contributes its gradient once, at the pixel its arg-max byte
+// names (always inside the image: the forward pass only compares pixels that exist), so the pass reads the pooled gradient,
+// the arg-max bytes and one element of x per output instead of gathering around every input pixel.
 template <typename T>
 __global__ void __launch_bounds__(BN_THREADS)
 bn_pool_sums_kernel(const T* __restrict__ x, const T* __restrict__ dp, const uint8_t* __restrict__ arg, float* __restrict__ sums, int planes, int C,
@@ -527,19 +530,24 @@ bn_pool_sums_kernel(const T* __restrict__ x, const T* __restrict__ dp, const uin
     const int c = blockIdx.x, s = blockIdx.y, S = gridDim.y;
     float m0, m1;
     bn_fwd_coef(fw, c, m0, m1);
-    const int per_line = W / 8, per_plane = H * per_line;
+    const int per_line = WO / 4, per_plane = HO * per_line;
     const int my_planes = s < planes ? (planes - s + S - 1) / S : 0;
     float a0 = 0.f, a1 = 0.f;
     for (int j = threadIdx.x; j < my_planes * per_plane; j += BN_THREADS) {
-        const int pi = j / per_plane, r = j - pi * per_plane, ih = r / per_line, g = r - ih * per_line;
+        const int pi = j / per_plane, r = j - pi * per_plane, oh = r / per_line, g = r - oh * per_line;
         const size_t row = (size_t)(s + pi * S) * C + c;
-        float fx[8], fg[8];
-        VecIO<T, 8>::load(x + (row * H + ih) * W + 8 * g, fx);
-        pool_gather8<T>(dp, arg, row * HO * WO, ih, g, HO, WO, fg);
+        const size_t o = (row * HO + oh) * WO + 4 * g;
+        const uint32_t a4 = __ldg(reinterpret_cast<const uint32_t*>(arg + o));
+        float g4[4];
+        VecIO<T, 4>::load(dp + o, g4);
+        const T* xr = x + row * H * W;
 #pragma unroll
-        for (int e = 0; e < 8; ++e) {
-            const float gg = fmaf(fx[e], m0, m1) > 0.f ? fg[e] : 0.f;
-            a0 += gg; a1 = fmaf(gg, fx[e], a1);
+        for (int jj = 0; jj < 4; ++jj) {
+            const int a = (int)((a4 >> (8 * jj)) & 0xffu);
+            const int akh = (a * 11) >> 5, akw = a - 3 * akh;          // a / 3 and a % 3 for a in 0..8
+            const int ih = 2 * oh - 1 + akh, iw = 2 * (4 * g + jj) - 1 + akw;
+            const float xv = DType<T>::load(xr + (size_t)ih * W + iw);
+            if (fmaf(xv, m0, m1) > 0.f) { a0 += g4[jj]; a1 = fmaf(g4[jj], xv, a1); }
         }
     }
     __shared__ float red[2][BN_THREADS / 32];
