@@ -485,40 +485,6 @@ bn_relu_pool_fwd_kernel(const T* __restrict__ x, BnCoef coef, T* __restrict__ y,
     }
 }
 
-// The gradient that reaches 8 consecutive pixels of the (never stored) normalised tensor: gathered from the pooled gradient
-// through the arg-max bytes, as in maxpool_bwd8_kernel.
-template <typename T>
-__device__ __forceinline__ void pool_gather8(const T* __restrict__ dp, const uint8_t* __restrict__ arg, size_t obase, int ih, int g, int HO, int WO,
-                                             float (&acc)[8]) {
-#pragma unroll
-    for (int e = 0; e < 8; ++e) acc[e] = 0.f;
-    for (int oh = ih >> 1; oh <= (ih + 1) >> 1; ++oh) {
-        if (oh >= HO) continue;
-        const int kh = ih - (2 * oh - 1);
-        const size_t o = obase + (size_t)oh * WO + 4 * g;
-        const uint32_t a4 = __ldg(reinterpret_cast<const uint32_t*>(arg + o));
-        float g4[4];
-        VecIO<T, 4>::load(dp + o, g4);
-#pragma unroll
-        for (int j = 0; j < 5; ++j) {
-            int a;
-            float gr;
-            if (j < 4) { a = (int)((a4 >> (8 * j)) & 0xffu); gr = g4[j]; }
-            else {
-                if (4 * g + 4 >= WO) continue;
-                a = arg[o + 4]; gr = DType<T>::load(dp + o + 4);
-            }
-            // window 4g + j covers the columns 2j - 1 .. 2j + 1 (relative to the first of the 8 pixels); j is a compile-time
-            // constant of the unrolled loop, so each window costs three selects, not a scan over the 8 accumulators
-            const int akh = (a * 11) >> 5, akw = a - 3 * akh;      // a / 3 and a % 3 for a in 0..8
-            const float m = akh == kh ? gr : 0.f;
-            if (2 * j - 1 >= 0) acc[(2 * j - 1) & 7] += akw == 0 ? m : 0.f;
-            if (2 * j < 8) acc[(2 * j) & 7] += akw == 1 ? m : 0.f;
-            if (2 * j + 1 < 8) acc[(2 * j + 1) & 7] += akw == 2 ? m : 0.f;
-        }
-    }
-}
-
 // Backward sums (g, g * x) per channel, g being the pooled gradient routed to its arg-max pixel and masked by
 // relu'(x * m0 + m1). The sums run over the POOLED outputs: each contributes its gradient once, at the pixel its arg-max byte
 // names (always inside the image: the forward pass only compares pixels that exist), so the pass reads the pooled gradient,
@@ -564,33 +530,75 @@ bn_pool_sums_kernel(const T* __restrict__ x, const T* __restrict__ dp, const uin
     }
 }
 
-// dx = coef0 * g + coef1 * x + coef2 with the same gathered, masked g.
+// The gradient that reaches the 2 x 8 input pixels of lines 2r and 2r + 1, columns 8g .. 8g + 7: window line r holds line 2r
+// as its middle line (kh = 1) and line 2r + 1 as its last (kh = 2), window line r + 1 holds line 2r + 1 as its first (kh = 0).
+// The arg-max bytes and gradients of the five windows per window line are read and decoded once for both input lines.
+template <typename T>
+__device__ __forceinline__ void pool_gather2x8(const T* __restrict__ dp, const uint8_t* __restrict__ arg, size_t obase, int r, int g, int HO, int WO,
+                                               float (&even)[8], float (&odd)[8]) {
+#pragma unroll
+    for (int e = 0; e < 8; ++e) even[e] = odd[e] = 0.f;
+#pragma unroll
+    for (int line = 0; line < 2; ++line) {
+        const int oh = r + line;
+        if (oh >= HO) continue;
+        const size_t o = obase + (size_t)oh * WO + 4 * g;
+        const uint32_t a4 = __ldg(reinterpret_cast<const uint32_t*>(arg + o));
+        float g4[4];
+        VecIO<T, 4>::load(dp + o, g4);
+#pragma unroll
+        for (int j = 0; j < 5; ++j) {
+            int a;
+            float gr;
+            if (j < 4) { a = (int)((a4 >> (8 * j)) & 0xffu); gr = g4[j]; }
+            else {
+                if (4 * g + 4 >= WO) continue;
+                a = arg[o + 4]; gr = DType<T>::load(dp + o + 4);
+            }
+            const int akh = (a * 11) >> 5, akw = a - 3 * akh;          // a / 3 and a % 3 for a in 0..8
+            // window line r: kh = 1 -> even input line, kh = 2 -> odd input line; window line r + 1: kh = 0 -> odd input line
+            const float me = (line == 0 && akh == 1) ? gr : 0.f;
+            const float mo = (line == 0 ? akh == 2 : akh == 0) ? gr : 0.f;
+            if (2 * j - 1 >= 0) { even[(2 * j - 1) & 7] += akw == 0 ? me : 0.f; odd[(2 * j - 1) & 7] += akw == 0 ? mo : 0.f; }
+            if (2 * j < 8) { even[(2 * j) & 7] += akw == 1 ? me : 0.f; odd[(2 * j) & 7] += akw == 1 ? mo : 0.f; }
+            if (2 * j + 1 < 8) { even[(2 * j + 1) & 7] += akw == 2 ? me : 0.f; odd[(2 * j + 1) & 7] += akw == 2 ? mo : 0.f; }
+        }
+    }
+}
+
+// dx = coef0 * g + coef1 * x + coef2 with g gathered from the pooled gradient and masked by relu'(x * m0 + m1); one thread
+// per 2 x 8 input pixels (H is even).
 template <typename T>
 __global__ void __launch_bounds__(BN_THREADS)
 bn_pool_apply_kernel(const T* __restrict__ x, const T* __restrict__ dp, const uint8_t* __restrict__ arg, T* __restrict__ dx,
                      BnCoef coef, size_t rows, int C, int H, int W, int HO, int WO, BnFwdParams fw) {
     bn_coef_outputs<1>(coef, C);
-    const int per_line = W / 8;
-    const size_t total = rows * H * per_line;
+    const int per_line = W / 8, pairs = H / 2;
+    const size_t total = rows * pairs * per_line;
     for (size_t idx = (size_t)blockIdx.x * blockDim.x + threadIdx.x; idx < total; idx += (size_t)gridDim.x * blockDim.x) {
         const int g = (int)(idx % per_line);
-        const int ih = (int)((idx / per_line) % H);
-        const size_t row = idx / ((size_t)per_line * H);
+        const int r = (int)((idx / per_line) % pairs);
+        const size_t row = idx / ((size_t)per_line * pairs);
         const int c = (int)(row % C);
         float k0, k1, k2;
         bn_coef<1>(coef, C, c, k0, k1, k2);
         float m0, m1;
         bn_fwd_coef(fw, c, m0, m1);
-        float fx[8], fg[8], fo[8];
-        const size_t off = (row * H + ih) * W + 8 * g;
-        VecIO<T, 8>::load(x + off, fx);
-        pool_gather8<T>(dp, arg, row * HO * WO, ih, g, HO, WO, fg);
+        float ge[8], go[8];
+        pool_gather2x8<T>(dp, arg, row * HO * WO, r, g, HO, WO, ge, go);
 #pragma unroll
-        for (int e = 0; e < 8; ++e) {
-            const float gg = fmaf(fx[e], m0, m1) > 0.f ? fg[e] : 0.f;
-            fo[e] = fmaf(k0, gg, fmaf(k1, fx[e], k2));
+        for (int line = 0; line < 2; ++line) {
+            float fx[8], fo[8];
+            const size_t off = (row * H + 2 * r + line) * W + 8 * g;
+            VecIO<T, 8>::load(x + off, fx);
+#pragma unroll
+            for (int e = 0; e < 8; ++e) {
+                const float gv = line == 0 ? ge[e] : go[e];
+                const float gg = fmaf(fx[e], m0, m1) > 0.f ? gv : 0.f;
+                fo[e] = fmaf(k0, gg, fmaf(k1, fx[e], k2));
+            }
+            VecIO<T, 8>::store(dx + off, fo);
         }
-        VecIO<T, 8>::store(dx + off, fo);
     }
 }
 
@@ -693,7 +701,7 @@ int bn_pool_bwd_typed(const T* x, const T* dp, const uint8_t* arg, const float* 
     if (S < 1) S = 1;
     bn_pool_sums_kernel<T><<<dim3(C, S), BN_THREADS, 0, stream>>>(x, dp, arg, scratch, planes, C, H, W, HO, WO, fw);
     const size_t rows = (size_t)planes * C;
-    bn_pool_apply_kernel<T><<<blocks_for(rows * H * (W / 8)), BN_THREADS, 0, stream>>>(x, dp, arg, dx, coef, rows, C, H, W, HO, WO, fw);
+    bn_pool_apply_kernel<T><<<blocks_for(rows * (H / 2) * (W / 8)), BN_THREADS, 0, stream>>>(x, dp, arg, dx, coef, rows, C, H, W, HO, WO, fw);
     PCB_CUDA_TRY(cudaGetLastError());
     return PCB_OK;
 }
