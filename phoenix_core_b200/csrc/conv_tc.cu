@@ -490,7 +490,7 @@ constexpr size_t PACK_SMEM_MAX_BYTES = 96 * 1024;               // two CTAs per 
 template <typename T>
 __global__ void __launch_bounds__(PACK_SMEM_THREADS)
 pack_activations_smem_kernel(const T* __restrict__ x, T* __restrict__ xp, int C, int H, int W, int Hp, int Wp, int Cp, int pad_top, int pad_left,
-                             int ins_h, int ins_w, int cb, int Nb) {
+                             int ins_h, int ins_w, int cb, int Nb, int scatter) {
     extern __shared__ __align__(16) uint8_t pack_smem[];
     T* tile = reinterpret_cast<T*>(pack_smem);                   // [C][H * W]
     const int plane = blockIdx.x, HW = H * W, n = C * HW;
@@ -502,18 +502,29 @@ pack_activations_smem_kernel(const T* __restrict__ x, T* __restrict__ xp, int C,
         for (int i = threadIdx.x; i < n; i += PACK_SMEM_THREADS) tile[i] = src[i];
     }
     __syncthreads();
-    const int groups = Cp / 8, items = Hp * Wp * groups;
+    // scatter: the copy was zeroed beforehand (zero-inserted copies are three quarters zeros) and only the source pixels are
+    // visited and written to their places; otherwise every element of the copy is visited and written
+    const int groups = Cp / 8, items = (scatter ? H * W : Hp * Wp) * groups;
     const int comp = plane / Nb, img = plane - comp * Nb;
     for (int idx = threadIdx.x; idx < items; idx += PACK_SMEM_THREADS) {
         const int grp = idx % groups, pix = idx / groups;
-        const int hp = pix / Wp, wp = pix - hp * Wp;
-        int ih = hp - pad_top, iw = wp - pad_left;
-        bool inside = ih >= 0 && iw >= 0;
-        if (inside && (ins_h > 1 || ins_w > 1)) {
-            inside = (ih % ins_h == 0) && (iw % ins_w == 0);
-            ih /= ins_h; iw /= ins_w;
+        int hp, wp, ih, iw;
+        bool inside;
+        if (scatter) {
+            ih = pix / W; iw = pix - ih * W;
+            hp = pad_top + ih * ins_h; wp = pad_left + iw * ins_w;
+            if (hp < 0 || hp >= Hp || wp < 0 || wp >= Wp) continue;
+            inside = true;
+        } else {
+            hp = pix / Wp; wp = pix - hp * Wp;
+            ih = hp - pad_top; iw = wp - pad_left;
+            inside = ih >= 0 && iw >= 0;
+            if (inside && (ins_h > 1 || ins_w > 1)) {
+                inside = (ih % ins_h == 0) && (iw % ins_w == 0);
+                ih /= ins_h; iw /= ins_w;
+            }
+            inside = inside && ih < H && iw < W;
         }
-        inside = inside && ih < H && iw < W;
         alignas(16) T vals[8];
 #pragma unroll
         for (int e = 0; e < 8; ++e) {
@@ -548,14 +559,16 @@ void stage_activations(int fmt, const void* src, void* dst, int planes, int C, i
         else pack_rows_kernel<__nv_bfloat16, 2><<<blocks, 256, 0, stream>>>((const __nv_bfloat16*)src, (__nv_bfloat16*)dst, planes, C, H, W, Hp, Wp, Cp / 8, pad_top, pad_left, 0, cb, Nb);
     } else if (!ss && (size_t)C * H * W * 2 <= PACK_SMEM_MAX_BYTES && (reinterpret_cast<uintptr_t>(src) & 15u) == 0) {
         const size_t smem = ((size_t)C * H * W * 2 + 15) / 16 * 16;
+        const int scatter = (ins_h > 1 || ins_w > 1) ? 1 : 0;
+        if (scatter) cudaMemsetAsync(dst, 0, (size_t)planes * Hp * Wp * Cp * 2, stream);
         if (fmt == 0) {
             cudaFuncSetAttribute(pack_activations_smem_kernel<__half>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)PACK_SMEM_MAX_BYTES);
             pack_activations_smem_kernel<__half><<<planes, PACK_SMEM_THREADS, smem, stream>>>((const __half*)src, (__half*)dst, C, H, W, Hp, Wp, Cp, pad_top, pad_left,
-                                                                                           ins_h, ins_w, cb, Nb);
+                                                                                           ins_h, ins_w, cb, Nb, scatter);
         } else {
             cudaFuncSetAttribute(pack_activations_smem_kernel<__nv_bfloat16>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)PACK_SMEM_MAX_BYTES);
             pack_activations_smem_kernel<__nv_bfloat16><<<planes, PACK_SMEM_THREADS, smem, stream>>>((const __nv_bfloat16*)src, (__nv_bfloat16*)dst, C, H, W, Hp, Wp, Cp,
-                                                                                                  pad_top, pad_left, ins_h, ins_w, cb, Nb);
+                                                                                                  pad_top, pad_left, ins_h, ins_w, cb, Nb, scatter);
         }
     } else {
         const int blocks = grid_cap(total, 256, 16);
