@@ -256,6 +256,55 @@ __global__ void pack_planar_kernel(const T* __restrict__ x, T* __restrict__ xp, 
     }
 }
 
+// The space-to-depth copy for an even left padding and an even line length: a staged pixel's two source columns (dx = 0, 1)
+// are one aligned 32-bit word, so a thread makes BOTH 8-channel planes of one staged pixel from 2 * C coalesced 4-byte loads
+// (2 source lines x C channels) instead of 16 scattered 2-byte loads.
+template <typename T, int C>
+__global__ void pack_planar_s2d_pairs_kernel(const T* __restrict__ x, T* __restrict__ xp, int planes_in, int H, int W, int Hp, int Wp,
+                                             int pad_top, int pad_left) {
+    const size_t total = (size_t)planes_in * Hp * Wp;
+    const size_t plane_pitch = (size_t)Hp * Wp * 8;               // elements between the two 8-channel planes
+    for (size_t idx = (size_t)blockIdx.x * blockDim.x + threadIdx.x; idx < total; idx += (size_t)gridDim.x * blockDim.x) {
+        const int wp = (int)(idx % Wp);
+        size_t rest = idx / Wp;
+        const int hp = (int)(rest % Hp);
+        const int plane = (int)(rest / Hp);
+        alignas(16) T vals[16];
+#pragma unroll
+        for (int e = 0; e < 16; ++e) vals[e] = T(0.f);
+        const int sw = 2 * wp - pad_left;                        // even: the pair (sw, sw + 1) is one aligned word
+#pragma unroll
+        for (int dy = 0; dy < 2; ++dy) {
+            const int sh = 2 * hp + dy - pad_top;
+            if (sh < 0 || sh >= H || sw < 0 || sw >= W) continue; // W is even, so sw + 1 < W as well
+#pragma unroll
+            for (int cs = 0; cs < C; ++cs) {
+                const uint32_t pair = __ldg(reinterpret_cast<const uint32_t*>(x + (((size_t)plane * C + cs) * H + sh) * W + sw));
+                const uint16_t lo = (uint16_t)(pair & 0xffffu), hi = (uint16_t)(pair >> 16);
+                vals[(dy * 2 + 0) * C + cs] = *reinterpret_cast<const T*>(&lo);       // staged channel (dy, dx, c)
+                vals[(dy * 2 + 1) * C + cs] = *reinterpret_cast<const T*>(&hi);
+            }
+        }
+        T* dst = xp + (((size_t)plane * 2) * Hp + hp) * (size_t)Wp * 8 + (size_t)wp * 8;
+        *reinterpret_cast<uint4*>(dst) = *reinterpret_cast<const uint4*>(vals);
+        *reinterpret_cast<uint4*>(dst + plane_pitch) = *reinterpret_cast<const uint4*>(vals + 8);
+    }
+}
+
+// Launches the paired-load space-to-depth copy where it applies; false if the general kernel has to run.
+template <typename T>
+bool launch_s2d_pairs(const void* src, void* dst, int planes_in, int C, int H, int W, int Hp, int Wp, int pad_top, int pad_left, cudaStream_t stream) {
+    if (C < 1 || C > 4 || (pad_left & 1) || (W & 1) || (reinterpret_cast<uintptr_t>(src) & 3u) || (reinterpret_cast<uintptr_t>(dst) & 15u)) return false;
+    const int blocks = grid_cap((size_t)planes_in * Hp * Wp, 256, 16);
+    const T* x = static_cast<const T*>(src);
+    T* xp = static_cast<T*>(dst);
+    if (C == 1) pack_planar_s2d_pairs_kernel<T, 1><<<blocks, 256, 0, stream>>>(x, xp, planes_in, H, W, Hp, Wp, pad_top, pad_left);
+    else if (C == 2) pack_planar_s2d_pairs_kernel<T, 2><<<blocks, 256, 0, stream>>>(x, xp, planes_in, H, W, Hp, Wp, pad_top, pad_left);
+    else if (C == 3) pack_planar_s2d_pairs_kernel<T, 3><<<blocks, 256, 0, stream>>>(x, xp, planes_in, H, W, Hp, Wp, pad_top, pad_left);
+    else pack_planar_s2d_pairs_kernel<T, 4><<<blocks, 256, 0, stream>>>(x, xp, planes_in, H, W, Hp, Wp, pad_top, pad_left);
+    return true;
+}
+
 // Wexp[tap][k / 8][m][k % 8] with m = (d, co) or (l, ci), k = (l, ci) or (d, co) as in conv_tc.cu; 128 rows, K = LK * 16.
 // s2d: staged tap (a, b) of staged channel c' = (dy, dx, ci) is source tap (2a + dy, 2b + dx) of channel ci (zero past the
 // filter edge); `taps` counts staged taps, KH x KW is the source filter, KWe the staged filter width.
@@ -559,6 +608,9 @@ int narrow_tc_launch(Pass pass, int dtype, const Geom& g, const void* w, const v
         } else if (fast) {
             pack_rows_kernel<__nv_bfloat16, 4><<<fblocks, 256, 0, stream>>>((const __nv_bfloat16*)act, (__nv_bfloat16*)xp, pl.LK * g.Nb, src_c, pl.Hin, pl.Win,
                                                                          pl.Hp, pl.Wp, 2, pl.pad_top, pl.pad_left, 1);
+        } else if (pl.s2d && (fmt == 0 ? launch_s2d_pairs<__half>(act, xp, pl.LK * g.Nb, src_c, pl.Hin, pl.Win, pl.Hp, pl.Wp, pl.pad_top, pl.pad_left, stream)
+                                       : launch_s2d_pairs<__nv_bfloat16>(act, xp, pl.LK * g.Nb, src_c, pl.Hin, pl.Win, pl.Hp, pl.Wp, pl.pad_top, pl.pad_left, stream))) {
+            // space-to-depth copy from aligned source pairs
         } else if (fmt == 0) {
             pack_planar_kernel<__half><<<blocks, 256, 0, stream>>>((const __half*)act, (__half*)xp, pl.LK * g.Nb, src_c, pl.Hin, pl.Win, pl.Hp, pl.Wp,
                                                                   2, pl.pad_top, pl.pad_left, pl.ins_h, pl.ins_w, pl.s2d);
@@ -706,6 +758,9 @@ int narrow_filter_tc_launch(int dtype, const Geom& g, const void* dy, const void
                 const int blocks = grid_cap(total / 4 + 1, 256, 16);
                 if (fmt == 0) pack_rows_kernel<__half, 4><<<blocks, 256, 0, stream>>>((const __half*)src, (__half*)dst, planes_in, C, H, W, Hp, Wp, groups, pt, pleft, 1);
                 else pack_rows_kernel<__nv_bfloat16, 4><<<blocks, 256, 0, stream>>>((const __nv_bfloat16*)src, (__nv_bfloat16*)dst, planes_in, C, H, W, Hp, Wp, groups, pt, pleft, 1);
+            } else if (s2d && groups == 2 && (fmt == 0 ? launch_s2d_pairs<__half>(src, dst, planes_in, C, H, W, Hp, Wp, pt, pleft, stream)
+                                                       : launch_s2d_pairs<__nv_bfloat16>(src, dst, planes_in, C, H, W, Hp, Wp, pt, pleft, stream))) {
+                // space-to-depth copy from aligned source pairs
             } else {
                 const int blocks = grid_cap(total, 256, 16);
                 if (fmt == 0) pack_planar_kernel<__half><<<blocks, 256, 0, stream>>>((const __half*)src, (__half*)dst, planes_in, C, H, W, Hp, Wp, groups, pt, pleft, 1, 1, s2d);
